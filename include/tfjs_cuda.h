@@ -1,0 +1,293 @@
+/*
+ * tfjs_cuda.h -- C ABI of the B200 (sm_100a) backend for TensorFlow.js.
+ *
+ * This is the boundary a `tfjs-backend-cuda` package binds: the N-API addon
+ * (and the ctypes host layer used by the tests) call exactly these entry
+ * points.  The split follows the reference's WASM backend, where TypeScript
+ * computes shapes/padding and passes scalars plus tensor ids to a C function
+ * (tfjs-backend-wasm/src/kernels/FusedConv2D.ts:79-147 ->
+ * tfjs-backend-wasm/src/cc/kernels/FusedConv2D.cc:33-52), with two changes:
+ * an explicit context handle (one per GPU) instead of a process-wide singleton
+ * (tfjs-backend-wasm/src/cc/backend.cc:124-152), and a status code returned by
+ * every call instead of void.
+ *
+ * Conventions
+ *   - Every function returns TFJS_CUDA_OK (0) or an error code; the message is
+ *     available from tfjs_cuda_last_error() until the next failing call.
+ *   - Tensors are named by int32 ids > 0 handed out by tfjs_cuda_alloc(); id 0
+ *     means "absent optional input" (tfjs-backend-wasm/src/backend_wasm.ts:51).
+ *   - All tensors are dense row-major; activations NHWC, filters HWIO.
+ *   - Kernel launches are asynchronous on the context's single in-order stream;
+ *     only read, sync, time_end and destroy block the host.
+ *   - Enum values for activations and dtypes follow
+ *     tfjs-backend-wasm/src/cc/backend.h:23-40.
+ */
+#ifndef TFJS_CUDA_H_
+#define TFJS_CUDA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tfjs_cuda_ctx tfjs_cuda_ctx;
+
+enum tfjs_cuda_status {
+  TFJS_CUDA_OK = 0,
+  TFJS_CUDA_INVALID_ARG = 1,
+  TFJS_CUDA_OUT_OF_MEMORY = 2,
+  TFJS_CUDA_DRIVER_ERROR = 3,
+  TFJS_CUDA_UNKNOWN_ID = 4,
+  TFJS_CUDA_UNSUPPORTED = 5,
+  TFJS_CUDA_DEVICE_TIMEOUT = 6 /* a bounded device-side wait gave up */
+};
+
+/* tfjs-backend-wasm/src/cc/backend.h:23-31 (FusableActivation). */
+enum tfjs_cuda_activation {
+  TFJS_CUDA_ACT_LINEAR = 0,
+  TFJS_CUDA_ACT_RELU = 1,
+  TFJS_CUDA_ACT_RELU6 = 2,
+  TFJS_CUDA_ACT_PRELU = 3,
+  TFJS_CUDA_ACT_LEAKYRELU = 4,
+  TFJS_CUDA_ACT_SIGMOID = 5,
+  TFJS_CUDA_ACT_ELU = 6
+};
+
+/* tfjs-backend-wasm/src/cc/backend.h:33-40 (DType); bool is one byte. */
+enum tfjs_cuda_dtype {
+  TFJS_CUDA_FLOAT32 = 0,
+  TFJS_CUDA_INT32 = 1,
+  TFJS_CUDA_BOOL = 2
+};
+
+/* How FusedConv2D / _FusedMatMul / BatchMatMul do their arithmetic. */
+enum tfjs_cuda_math_mode {
+  TFJS_CUDA_MATH_TF32 = 0, /* tcgen05 tensor cores, TF32 inputs, fp32 accumulate */
+  TFJS_CUDA_MATH_FP32 = 1  /* SIMT fp32 FMA; for running fp32-tolerance suites   */
+};
+
+/* ---- context and storage: the device half of the KernelBackend contract
+ * (tfjs-core/src/backends/backend.ts:100-156; reference implementation
+ * tfjs-backend-cpu/src/backend_cpu.ts:52-204). ------------------------------ */
+
+int tfjs_cuda_device_count(int* out_count);
+int tfjs_cuda_create(int device_ordinal, tfjs_cuda_ctx** out_ctx);
+void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx);
+const char* tfjs_cuda_last_error(tfjs_cuda_ctx* ctx);
+
+/* Pool allocation (cudaMallocAsync on the context stream).  nbytes may be 0. */
+int tfjs_cuda_alloc(tfjs_cuda_ctx* ctx, uint64_t nbytes, int32_t* out_id);
+/* Stream-ordered free; also drops any packed-weight cache entry of the id
+ * (the disposal-callback idea of tfjs-backend-wasm/src/cc/backend.cc:58-67). */
+int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id);
+/* backend.write(): async H2D on the stream.  If `host` is pinned memory from
+ * tfjs_cuda_host_alloc the copy overlaps the host; the caller must leave the
+ * bytes untouched until the next blocking call. */
+int tfjs_cuda_write(tfjs_cuda_ctx* ctx, int32_t id, const void* host,
+                    uint64_t nbytes);
+/* backend.readSync(): D2H then stream sync; reports a pending device timeout. */
+int tfjs_cuda_read(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes);
+/* Queue a D2H copy without waiting (pair with tfjs_cuda_sync). */
+int tfjs_cuda_read_async(tfjs_cuda_ctx* ctx, int32_t id, void* host,
+                         uint64_t nbytes);
+int tfjs_cuda_sync(tfjs_cuda_ctx* ctx);
+int tfjs_cuda_size_of(tfjs_cuda_ctx* ctx, int32_t id, uint64_t* out_nbytes);
+/* Raw device address of a tensor, for interop (profilers, other libraries). */
+int tfjs_cuda_device_ptr(tfjs_cuda_ctx* ctx, int32_t id, void** out_ptr);
+/* backend.memory() (tfjs-core/src/engine.ts:959-974). */
+int tfjs_cuda_memory(tfjs_cuda_ctx* ctx, uint64_t* bytes_in_use,
+                     uint64_t* bytes_reserved, uint64_t* high_water,
+                     uint64_t* num_buffers);
+/* Pinned host buffers for write/read staging. */
+int tfjs_cuda_host_alloc(tfjs_cuda_ctx* ctx, uint64_t nbytes, void** out_ptr);
+int tfjs_cuda_host_free(tfjs_cuda_ctx* ctx, void* ptr);
+/* backend.time() (tfjs-core/src/engine.ts:1235-1240): CUDA events on the stream. */
+int tfjs_cuda_time_begin(tfjs_cuda_ctx* ctx);
+int tfjs_cuda_time_end(tfjs_cuda_ctx* ctx, float* out_kernel_ms);
+int tfjs_cuda_set_math_mode(tfjs_cuda_ctx* ctx, int mode);
+/* Number of this library's kernels launched on the context so far. */
+int tfjs_cuda_launch_count(tfjs_cuda_ctx* ctx, uint64_t* out_launches);
+/* Clears L2 by overwriting a scratch buffer larger than it (benchmark hygiene). */
+int tfjs_cuda_flush_l2(tfjs_cuda_ctx* ctx);
+
+/* ---- FusedConv2D / Conv2D: tfjs-backend-cpu/src/kernels/FusedConv2D.ts:26-95,
+ * Conv2D.ts:23-103; attrs tfjs-core/src/kernel_names.ts:1016-1031.  The caller
+ * computes the geometry with computeConv2DInfo (tfjs-core/src/ops/conv_util.ts:
+ * 177-236).  bias_len / prelu_len are 0 (absent), 1 (scalar) or out_c. -------- */
+typedef struct tfjs_cuda_conv2d_params {
+  int32_t batch, in_h, in_w, in_c;
+  int32_t out_h, out_w, out_c;
+  int32_t filter_h, filter_w;
+  int32_t stride_h, stride_w;
+  int32_t dilation_h, dilation_w;
+  int32_t pad_top, pad_left;
+  int32_t activation; /* tfjs_cuda_activation */
+  int32_t bias_len, prelu_len;
+  double leakyrelu_alpha;
+} tfjs_cuda_conv2d_params;
+
+int tfjs_cuda_fused_conv2d(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
+                           int32_t x_id, int32_t filter_id, int32_t bias_id,
+                           int32_t prelu_id, int32_t out_id);
+
+/* ---- FusedDepthwiseConv2D / DepthwiseConv2dNative:
+ * tfjs-backend-cpu/src/kernels/FusedDepthwiseConv2D.ts:25-61,
+ * DepthwiseConv2dNative.ts:23-102; attrs kernel_names.ts:1033-1048.  out_c is
+ * in_c * channel_multiplier; filter is [fh, fw, in_c, channel_multiplier]. ---- */
+int tfjs_cuda_fused_depthwise_conv2d(tfjs_cuda_ctx* ctx,
+                                     const tfjs_cuda_conv2d_params* p,
+                                     int32_t x_id, int32_t filter_id,
+                                     int32_t bias_id, int32_t prelu_id,
+                                     int32_t out_id);
+
+/* ---- _FusedMatMul / BatchMatMul: tfjs-backend-cpu/src/kernels/_FusedMatMul.ts:
+ * 26-62, BatchMatMul.ts:25-133; attrs kernel_names.ts:1000-1014, :119-124.
+ * a is [batch_a, M, K] (or [batch_a, K, M] when transpose_a), b is
+ * [batch_b, K, N] (or [batch_b, N, K] when transpose_b); the output batch is
+ * max(batch_a, batch_b) and operand batches wrap (BatchMatMul.ts:96-97).
+ * bias_len is 0, 1, N, or M*N-compatible lengths are rejected (the host adds
+ * those with the Add kernel). ------------------------------------------------ */
+typedef struct tfjs_cuda_matmul_params {
+  int32_t batch_a, batch_b;
+  int32_t m, n, k;
+  int32_t transpose_a, transpose_b;
+  int32_t activation;
+  int32_t bias_len, prelu_len;
+  double leakyrelu_alpha;
+} tfjs_cuda_matmul_params;
+
+int tfjs_cuda_fused_matmul(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
+                           int32_t a_id, int32_t b_id, int32_t bias_id,
+                           int32_t prelu_id, int32_t out_id);
+
+/* ---- MaxPool / AvgPool: tfjs-backend-cpu/src/kernels/MaxPool.ts:24-55,
+ * AvgPool.ts:24-55, utils/pool_utils.ts:20-87; attrs kernel_names.ts:83-90,
+ * :517-524.  Geometry from computePool2DInfo (conv_util.ts:119-140); filter_h/w
+ * are the effective (dilated) window extents. --------------------------------- */
+int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
+                     int32_t is_max, int32_t x_id, int32_t out_id);
+
+/* ---- broadcasting binary kernels: tfjs-backend-cpu/src/utils/binary_impl.ts:
+ * 25-69 (Add.ts, Sub.ts, Multiply.ts, RealDiv.ts, Maximum.ts, Minimum.ts, Pow.ts,
+ * SquaredDifference.ts, Prelu.ts).  Shapes are given right-aligned with the same
+ * rank (<= 6), padded with leading 1s. ---------------------------------------- */
+enum tfjs_cuda_binary_op {
+  TFJS_CUDA_ADD = 0,
+  TFJS_CUDA_SUB = 1,
+  TFJS_CUDA_MUL = 2,
+  TFJS_CUDA_DIV = 3,
+  TFJS_CUDA_MAXIMUM = 4,
+  TFJS_CUDA_MINIMUM = 5,
+  TFJS_CUDA_POW = 6,
+  TFJS_CUDA_SQUARED_DIFFERENCE = 7,
+  TFJS_CUDA_PRELU = 8
+};
+
+int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank,
+                     int32_t a_id, const int64_t* a_shape, int32_t b_id,
+                     const int64_t* b_shape, int32_t out_id,
+                     const int64_t* out_shape);
+
+/* ---- unary kernels: tfjs-backend-cpu/src/utils/unary_impl.ts:25-36 with Relu.ts,
+ * Relu6.ts, Elu.ts, Sigmoid.ts, LeakyRelu.ts, Exp.ts, Sqrt.ts, Rsqrt.ts, Square.ts,
+ * Tanh.ts, Neg.ts, ClipByValue.ts, Erf.ts, Abs.ts, Log.ts.  p0/p1: leakyrelu alpha,
+ * or clip min/max. -------------------------------------------------------------- */
+enum tfjs_cuda_unary_op {
+  TFJS_CUDA_RELU = 0,
+  TFJS_CUDA_RELU6 = 1,
+  TFJS_CUDA_ELU = 2,
+  TFJS_CUDA_SIGMOID = 3,
+  TFJS_CUDA_LEAKYRELU = 4,
+  TFJS_CUDA_EXP = 5,
+  TFJS_CUDA_SQRT = 6,
+  TFJS_CUDA_RSQRT = 7,
+  TFJS_CUDA_SQUARE = 8,
+  TFJS_CUDA_TANH = 9,
+  TFJS_CUDA_NEG = 10,
+  TFJS_CUDA_CLIP = 11,
+  TFJS_CUDA_ERF = 12,
+  TFJS_CUDA_ABS = 13,
+  TFJS_CUDA_LOG = 14
+};
+
+int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int32_t op, double p0, double p1,
+                    int32_t x_id, uint64_t n, int32_t out_id);
+
+/* ---- Softmax over the last axis: tfjs-backend-cpu/src/kernels/Softmax.ts:29-77. */
+int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
+                      uint64_t cols, int32_t out_id);
+
+/* ---- Sum / Mean / Max over the middle axis of an [outer, reduce, inner] view:
+ * tfjs-backend-cpu/src/kernels/Sum.ts:28-90, Mean.ts:25-53, Max.ts:28-72.  The
+ * host collapses the (contiguous) reduced axes; non-contiguous axes are first
+ * transposed, as the reference does (Sum.ts:46-54). ----------------------------- */
+enum tfjs_cuda_reduce_op {
+  TFJS_CUDA_REDUCE_SUM = 0,
+  TFJS_CUDA_REDUCE_MEAN = 1,
+  TFJS_CUDA_REDUCE_MAX = 2
+};
+
+int tfjs_cuda_reduce(tfjs_cuda_ctx* ctx, int32_t op, int32_t x_id,
+                     uint64_t outer, uint64_t reduce, uint64_t inner,
+                     int32_t out_id);
+
+/* ---- ArgMax over the middle axis of [outer, reduce, inner], int32 output:
+ * tfjs-backend-cpu/src/kernels/ArgMax.ts:24-71. --------------------------------- */
+int tfjs_cuda_argmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t outer,
+                     uint64_t reduce, uint64_t inner, int32_t out_id);
+
+/* ---- Transpose (rank <= 6, 4-byte or 1-byte elements):
+ * tfjs-backend-cpu/src/kernels/Transpose.ts:25-48, Transpose_impl.ts:21-45. ------ */
+int tfjs_cuda_transpose(tfjs_cuda_ctx* ctx, int32_t elem_bytes, int32_t rank,
+                        int32_t x_id, const int64_t* x_shape,
+                        const int32_t* perm, int32_t out_id);
+
+/* ---- GatherV2 on a [batch, outer, dim, slice] view of x and [batch, n_idx]
+ * indices: tfjs-backend-cpu/src/kernels/GatherV2.ts:25-90, GatherV2_impl.ts:20-41.
+ * An index outside [0, dim-1] makes the call fail (GatherV2.ts:36-46); the range
+ * check runs on the device and is reported through out_bad_index (first bad
+ * value, or -1), which the caller reads after the launch. ------------------------ */
+int tfjs_cuda_gather(tfjs_cuda_ctx* ctx, int32_t elem_bytes, int32_t x_id,
+                     int32_t indices_id, uint64_t batch, uint64_t outer,
+                     uint64_t dim, uint64_t slice, uint64_t n_idx,
+                     int32_t out_id, int32_t check_indices,
+                     int64_t* out_bad_index);
+
+/* ---- Cast: tfjs-backend-cpu/src/kernels/Cast.ts:27-95 (float32->int32 is JS
+ * ToInt32; anything->bool is x != 0; widening copies the values). --------------- */
+int tfjs_cuda_cast(tfjs_cuda_ctx* ctx, int32_t from_dtype, int32_t to_dtype,
+                   int32_t x_id, uint64_t n, int32_t out_id);
+
+/* ---- strided copy glue used by Concat / Slice / PadV2 / Tile
+ * (tfjs-backend-cpu/src/kernels/Concat.ts:29-103, Slice.ts, PadV2.ts, Tile.ts):
+ * out[o_off + idx(loc, o_strides)] = x[x_off + idx(loc mod x_shape, x_strides)]
+ * for every loc in `extent`.  rank <= 6, elem_bytes 1 or 4. --------------------- */
+int tfjs_cuda_copy_strided(tfjs_cuda_ctx* ctx, int32_t elem_bytes, int32_t rank,
+                           const int64_t* extent, int32_t x_id, int64_t x_off,
+                           const int64_t* x_strides, const int64_t* x_wrap,
+                           int32_t out_id, int64_t o_off,
+                           const int64_t* o_strides);
+int tfjs_cuda_fill(tfjs_cuda_ctx* ctx, int32_t elem_bytes, uint32_t bits,
+                   int32_t out_id, uint64_t n);
+
+/* ---- FusedBatchNorm: tfjs-backend-cpu/src/kernels/BatchNorm.ts:23-90; parameter
+ * tensors are indexed modulo their own length (:69-87). ------------------------- */
+int tfjs_cuda_batchnorm(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t n,
+                        int32_t mean_id, uint64_t n_mean, int32_t var_id,
+                        uint64_t n_var, int32_t scale_id, uint64_t n_scale,
+                        int32_t offset_id, uint64_t n_offset, double epsilon,
+                        int32_t out_id);
+
+/* ---- weight dequantisation at load: tfjs-core/src/io/io_utils.ts:221-227
+ * (float32 target) and :243-247 (int32 target).  q_dtype_bytes is 1 (uint8) or 2
+ * (uint16).  The 256/65536-entry table fl32(v*scale+min) is built on the host in
+ * double and looked up on the device, which makes the result bit-exact. -------- */
+int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_dtype_bytes,
+                         int32_t to_dtype, int32_t q_id, double scale,
+                         double min, uint64_t n, int32_t out_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TFJS_CUDA_H_ */

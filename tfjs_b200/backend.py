@@ -1,0 +1,291 @@
+"""CudaBackend: the host half of `tfjs-backend-cuda`.
+
+Python mirror of the TypeScript class a Node build would ship.  It implements the
+KernelBackend contract (tfjs-core/src/backends/backend.ts:100-156) with the
+semantics of the reference CPU backend (tfjs-backend-cpu/src/backend_cpu.ts):
+
+  write / move / read / readSync / disposeData / refCount / incRef / decRef /
+  numDataIds / memory / time / floatPrecision / dispose
+
+and owns one `tfjs_cuda_ctx` (one GPU).  DataIds are fresh objects, as in the
+reference (`const dataId = {id: this.nextDataId()}`, backend_cpu.ts:58).
+
+Small tensors written from the host stay host-resident and are uploaded only
+when a kernel first consumes them.  The graph executor reads axis / shape / perm
+Const tensors with dataSync() inside its node loop
+(tfjs-converter/src/operations/executors/utils.ts:55); with this rule those
+reads never touch the CUDA stream.
+"""
+import ctypes
+import time as _time
+from ctypes import byref, c_float, c_int32, c_uint64, c_void_p
+
+import numpy as np
+
+from . import _cabi
+from ._cabi import CudaError
+
+NP_DTYPES = {"float32": np.float32, "int32": np.int32, "bool": np.uint8}
+HOST_RESIDENT_BYTES = 4096  # keep a host copy of tensors up to this size
+
+
+class DataId(object):
+    """Opaque key object; identity is the key (a WeakMap key in tfjs)."""
+    __slots__ = ("id", "__weakref__")
+    _next = 0
+
+    def __init__(self):
+        DataId._next += 1
+        self.id = DataId._next
+
+    def __repr__(self):
+        return "DataId(%d)" % self.id
+
+
+class TensorInfo(object):
+    """tfjs-core/src/tensor_info.ts: {dataId, shape, dtype}."""
+    __slots__ = ("dataId", "shape", "dtype")
+
+    def __init__(self, dataId, shape, dtype):
+        self.dataId = dataId
+        self.shape = [int(s) for s in shape]
+        self.dtype = dtype
+
+    @property
+    def size(self):
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def __repr__(self):
+        return "TensorInfo(%r, %s, %s)" % (self.dataId, self.shape, self.dtype)
+
+
+class _Record(object):
+    __slots__ = ("dev", "nbytes", "dtype", "ref", "host")
+
+    def __init__(self, dev, nbytes, dtype, ref, host):
+        self.dev = dev        # device buffer id, 0 = not uploaded yet
+        self.nbytes = nbytes
+        self.dtype = dtype
+        self.ref = ref
+        self.host = host      # numpy copy for small host-written tensors
+
+
+def size_from_shape(shape):
+    n = 1
+    for s in shape:
+        n *= int(s)
+    return n
+
+
+class CudaBackend(object):
+    """One instance per GPU (`device_ordinal`)."""
+
+    def __init__(self, device_ordinal=0):
+        self.lib = _cabi.load()
+        ctx = c_void_p()
+        rc = self.lib.tfjs_cuda_create(int(device_ordinal), byref(ctx))
+        if rc != _cabi.OK:
+            raise CudaError(rc, "tfjs_cuda_create(device %d) failed with status "
+                            "%d: no usable sm_100a GPU" % (device_ordinal, rc))
+        self.ctx = ctx
+        self.device_ordinal = device_ordinal
+        self.data = {}        # DataId -> _Record
+        self._pinned = []
+
+    # ------------------------------------------------------------ plumbing --
+    def check(self, rc):
+        if rc != _cabi.OK:
+            msg = self.lib.tfjs_cuda_last_error(self.ctx)
+            raise CudaError(rc, msg.decode() if msg else "status %d" % rc)
+
+    def _alloc(self, nbytes):
+        out = c_int32()
+        self.check(self.lib.tfjs_cuda_alloc(self.ctx, int(nbytes), byref(out)))
+        return out.value
+
+    def floatPrecision(self):
+        return 32
+
+    def epsilon(self):
+        return 1e-7
+
+    # -------------------------------------------------- KernelBackend: data --
+    def write(self, values, shape, dtype):
+        """backend_cpu.ts:52-71."""
+        dataId = DataId()
+        self.move(dataId, values, shape, dtype, 1)
+        return dataId
+
+    def move(self, dataId, values, shape, dtype, refCount):
+        """backend_cpu.ts:119-123."""
+        if dtype not in NP_DTYPES:
+            raise ValueError("tfjs-backend-cuda: dtype %s is not supported" % dtype)
+        n = size_from_shape(shape)
+        arr = None
+        if values is not None:
+            arr = np.ascontiguousarray(np.asarray(values).astype(NP_DTYPES[dtype],
+                                                                 copy=False)).reshape(-1)
+            if arr.size != n:
+                raise ValueError("write: %d values for shape %s" % (arr.size, list(shape)))
+        nbytes = n * np.dtype(NP_DTYPES[dtype]).itemsize
+        rec = _Record(0, nbytes, dtype, refCount, None)
+        if arr is not None and nbytes <= HOST_RESIDENT_BYTES:
+            rec.host = arr.copy()
+        else:
+            rec.dev = self._alloc(nbytes)
+            if arr is not None and nbytes:
+                self.check(self.lib.tfjs_cuda_write(self.ctx, rec.dev,
+                                                    arr.ctypes.data_as(c_void_p), nbytes))
+        self.data[dataId] = rec
+
+    def make_output(self, shape, dtype):
+        """Allocate an uninitialised device tensor for a kernel result
+        (makeTensorInfo, backend_cpu.ts:83-95)."""
+        nbytes = size_from_shape(shape) * np.dtype(NP_DTYPES[dtype]).itemsize
+        dataId = DataId()
+        self.data[dataId] = _Record(self._alloc(nbytes), nbytes, dtype, 1, None)
+        return TensorInfo(dataId, shape, dtype)
+
+    def device_id(self, dataId):
+        """Device buffer id of a tensor, uploading a host-resident one first."""
+        rec = self.data[dataId]
+        if rec.dev == 0:
+            rec.dev = self._alloc(rec.nbytes)
+            if rec.nbytes:
+                self.check(self.lib.tfjs_cuda_write(
+                    self.ctx, rec.dev, rec.host.ctypes.data_as(c_void_p), rec.nbytes))
+        return rec.dev
+
+    def host_values(self, dataId):
+        """Host copy if the tensor is host-resident, else None (no sync)."""
+        return self.data[dataId].host
+
+    def readSync(self, dataId):
+        """backend_cpu.ts:129-144: the only blocking call besides time()."""
+        rec = self.data[dataId]
+        if rec.host is not None:
+            out = rec.host.copy()
+        else:
+            out = np.empty(rec.nbytes // np.dtype(NP_DTYPES[rec.dtype]).itemsize,
+                           NP_DTYPES[rec.dtype])
+            self.check(self.lib.tfjs_cuda_read(self.ctx, rec.dev,
+                                               out.ctypes.data_as(c_void_p), rec.nbytes))
+        return out.astype(np.bool_) if rec.dtype == "bool" else out
+
+    def read(self, dataId):
+        return self.readSync(dataId)
+
+    def read_into(self, dataId, host_array):
+        """readSync into caller-provided (ideally pinned) memory."""
+        rec = self.data[dataId]
+        if rec.host is not None:
+            host_array.reshape(-1)[:] = rec.host
+            return
+        self.check(self.lib.tfjs_cuda_read(self.ctx, rec.dev,
+                                           host_array.ctypes.data_as(c_void_p), rec.nbytes))
+
+    def disposeData(self, dataId, force=False):
+        """backend_cpu.ts:176-193: true iff the memory was released."""
+        rec = self.data.get(dataId)
+        if rec is None:
+            return False
+        rec.ref -= 1
+        if not force and rec.ref > 0:
+            return False
+        if rec.dev:
+            self.check(self.lib.tfjs_cuda_free(self.ctx, rec.dev))
+        del self.data[dataId]
+        return True
+
+    def refCount(self, dataId):
+        rec = self.data.get(dataId)
+        return rec.ref if rec is not None else 0
+
+    def incRef(self, dataId):
+        self.data[dataId].ref += 1
+
+    def decRef(self, dataId):
+        rec = self.data.get(dataId)
+        if rec is not None:
+            rec.ref -= 1
+
+    def numDataIds(self):
+        return len(self.data)
+
+    def memory(self):
+        """tfjs-core/src/engine.ts:959-974 merges this into tf.memory()."""
+        vals = [c_uint64() for _ in range(4)]
+        self.check(self.lib.tfjs_cuda_memory(self.ctx, *[byref(v) for v in vals]))
+        return {"unreliable": False, "numBytesInGPU": vals[0].value,
+                "numBytesInGPUAllocated": vals[1].value,
+                "poolHighWater": vals[2].value, "numDeviceBuffers": vals[3].value}
+
+    def time(self, f):
+        """backend.time(f) -> {kernelMs, wallMs} with CUDA events on the stream."""
+        t0 = _time.perf_counter()
+        self.check(self.lib.tfjs_cuda_time_begin(self.ctx))
+        f()
+        ms = c_float()
+        self.check(self.lib.tfjs_cuda_time_end(self.ctx, byref(ms)))
+        return {"kernelMs": ms.value, "wallMs": (_time.perf_counter() - t0) * 1e3}
+
+    def timerAvailable(self):
+        return True
+
+    def sync(self):
+        self.check(self.lib.tfjs_cuda_sync(self.ctx))
+
+    def set_math_mode(self, mode):
+        """'tf32' (tensor cores) or 'fp32' (SIMT fp32 FMA)."""
+        self.check(self.lib.tfjs_cuda_set_math_mode(
+            self.ctx, {"tf32": _cabi.MATH_TF32, "fp32": _cabi.MATH_FP32}[mode]))
+
+    def launch_count(self):
+        v = c_uint64()
+        self.check(self.lib.tfjs_cuda_launch_count(self.ctx, byref(v)))
+        return v.value
+
+    def flush_l2(self):
+        self.check(self.lib.tfjs_cuda_flush_l2(self.ctx))
+
+    def pinned_empty(self, shape, dtype):
+        """numpy array over pinned host memory owned by this backend."""
+        n = size_from_shape(shape)
+        npdt = np.dtype(NP_DTYPES[dtype] if isinstance(dtype, str) else dtype)
+        nbytes = max(n * npdt.itemsize, 1)
+        ptr = c_void_p()
+        self.check(self.lib.tfjs_cuda_host_alloc(self.ctx, nbytes, byref(ptr)))
+        self._pinned.append(ptr)
+        buf = (ctypes.c_uint8 * nbytes).from_address(ptr.value)
+        return np.frombuffer(buf, dtype=npdt, count=n).reshape(shape)
+
+    def write_from(self, host_array, shape, dtype):
+        """write() that always goes to the device straight from `host_array`
+        (use with pinned_empty for asynchronous H2D)."""
+        n = size_from_shape(shape)
+        nbytes = n * np.dtype(NP_DTYPES[dtype]).itemsize
+        dataId = DataId()
+        rec = _Record(self._alloc(nbytes), nbytes, dtype, 1, None)
+        if nbytes:
+            self.check(self.lib.tfjs_cuda_write(self.ctx, rec.dev,
+                                                host_array.ctypes.data_as(c_void_p), nbytes))
+        self.data[dataId] = rec
+        return dataId
+
+    def dispose(self):
+        if self.ctx:
+            for ptr in self._pinned:
+                self.lib.tfjs_cuda_host_free(self.ctx, ptr)
+            self._pinned = []
+            self.lib.tfjs_cuda_destroy(self.ctx)
+            self.ctx = None
+            self.data = {}
+
+    def __del__(self):
+        try:
+            self.dispose()
+        except Exception:
+            pass

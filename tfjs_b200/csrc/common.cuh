@@ -1,0 +1,133 @@
+// Internal declarations shared by the translation units of libtfjs_cuda.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "tfjs_cuda.h"
+
+struct Buffer {
+  void* ptr = nullptr;
+  uint64_t bytes = 0;
+  bool live = false;
+  bool from_host = false;  // last filled by write()/dequantize(): weight-like
+  uint32_t version = 0;    // bumped whenever the contents are (re)written
+};
+
+// A filter repacked for the tensor-core kernels: [rows = out channels][k_pad]
+// with K contiguous, values rounded to TF32 (round-to-nearest).
+struct PackedWeight {
+  float* ptr = nullptr;
+  uint64_t bytes = 0;
+  uint32_t version = 0;
+  int rows = 0, k_pad = 0;
+  int layout = 0;
+};
+
+struct tfjs_cuda_ctx {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  cudaMemPool_t pool = nullptr;
+  std::vector<Buffer> bufs;  // index = id; slot 0 unused
+  std::vector<int32_t> free_ids;
+  std::unordered_map<int32_t, PackedWeight> packed;
+  std::string err;
+  uint64_t in_use = 0, high_water = 0, n_live = 0;
+  uint64_t launches = 0;
+  int math_mode = TFJS_CUDA_MATH_TF32;
+  int* d_flag = nullptr;  // device error word written by bounded waits
+  int* h_flag = nullptr;  // pinned mirror
+  long long* d_bad_index = nullptr;
+  long long* h_bad_index = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  void* l2_scratch = nullptr;
+  uint64_t l2_scratch_bytes = 0;
+  // grow-only scratch for im2col / operand transposes
+  void* scratch = nullptr;
+  uint64_t scratch_bytes = 0;
+};
+
+int ctx_fail(tfjs_cuda_ctx* ctx, int code, const char* fmt, ...);
+int ctx_check(tfjs_cuda_ctx* ctx, cudaError_t e, const char* what);
+Buffer* ctx_buf(tfjs_cuda_ctx* ctx, int32_t id);
+// Returns the buffer of `id` after checking it holds at least `need` bytes.
+int ctx_get(tfjs_cuda_ctx* ctx, int32_t id, uint64_t need, const char* name,
+            Buffer** out);
+int ctx_scratch(tfjs_cuda_ctx* ctx, uint64_t bytes, void** out);
+void ctx_mark_written(tfjs_cuda_ctx* ctx, int32_t id);
+void ctx_drop_packed(tfjs_cuda_ctx* ctx, int32_t id);
+
+#define CUDA_TRY(ctx, expr)                                   \
+  do {                                                        \
+    int _rc = ctx_check((ctx), (expr), #expr);                \
+    if (_rc != TFJS_CUDA_OK) return _rc;                      \
+  } while (0)
+
+#define LAUNCH_CHECK(ctx, name)                               \
+  do {                                                        \
+    (ctx)->launches++;                                        \
+    int _rc = ctx_check((ctx), cudaGetLastError(), name);     \
+    if (_rc != TFJS_CUDA_OK) return _rc;                      \
+  } while (0)
+
+static inline unsigned grid_for(uint64_t work_items, int threads, int sm_count,
+                                int waves = 8) {
+  uint64_t blocks = (work_items + threads - 1) / threads;
+  uint64_t cap = (uint64_t)sm_count * waves;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  return (unsigned)blocks;
+}
+
+// ---- device helpers -------------------------------------------------------
+// Activations with JavaScript semantics (tfjs-backend-cpu/src/kernels/Relu.ts,
+// Relu6.ts, Elu.ts, Sigmoid.ts, LeakyRelu.ts, Prelu.ts): Math.max/Math.min
+// propagate NaN, which fmaxf/fminf do not, so comparisons are written so that
+// NaN falls through unchanged.  elu and sigmoid go through double exp so the
+// fp32 result matches a double evaluation rounded once.
+struct ActParams {
+  int act;
+  int prelu_len;        // 0, 1, or channel count
+  const float* prelu;   // device pointer or null
+  double alpha;         // leakyrelu
+};
+
+__device__ __forceinline__ float js_relu(float v) {
+  return v > 0.0f ? v : (v != v ? v : 0.0f);
+}
+__device__ __forceinline__ float js_relu6(float v) {
+  if (v != v) return v;
+  return v > 6.0f ? 6.0f : (v > 0.0f ? v : 0.0f);
+}
+__device__ __forceinline__ float js_elu(float v) {
+  return v >= 0.0f ? v : (float)(exp((double)v) - 1.0);
+}
+__device__ __forceinline__ float js_sigmoid(float v) {
+  return (float)(1.0 / (1.0 + exp(-(double)v)));
+}
+__device__ __forceinline__ float js_leakyrelu(float v, double alpha) {
+  return v < 0.0f ? (float)(alpha * (double)v) : v;
+}
+
+__device__ __forceinline__ float apply_act(float v, const ActParams& ap,
+                                           int channel) {
+  switch (ap.act) {
+    case TFJS_CUDA_ACT_RELU: return js_relu(v);
+    case TFJS_CUDA_ACT_RELU6: return js_relu6(v);
+    case TFJS_CUDA_ACT_PRELU: {
+      const float a = ap.prelu[ap.prelu_len == 1 ? 0 : channel];
+      return v < 0.0f ? a * v : v;
+    }
+    case TFJS_CUDA_ACT_LEAKYRELU: return js_leakyrelu(v, ap.alpha);
+    case TFJS_CUDA_ACT_SIGMOID: return js_sigmoid(v);
+    case TFJS_CUDA_ACT_ELU: return js_elu(v);
+    default: return v;
+  }
+}
+

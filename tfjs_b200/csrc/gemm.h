@@ -1,0 +1,48 @@
+// Problem description shared by the GEMM front end (matmul.cu) and its two
+// back ends: the tcgen05 TF32 kernels and the fp32 SIMT kernels.
+#pragma once
+#include "common.cuh"
+
+struct ConvGeo {
+  int batch, in_h, in_w, in_c;
+  int out_h, out_w;
+  int f_h, f_w;
+  int s_h, s_w, d_h, d_w, pad_t, pad_l;
+};
+
+struct GemmProblem {
+  // C[batch][M][N] = act(A . B + bias).  For a convolution A is the implicit
+  // im2col matrix of x (M = batch*out_h*out_w rows, K = f_h*f_w*in_c) and the
+  // GEMM batch is 1.
+  const float* a = nullptr;
+  const float* b = nullptr;
+  float* c = nullptr;
+  const float* bias = nullptr;
+  int bias_len = 0;
+  ActParams ap;
+  int M = 0, N = 0, K = 0;
+  int batch = 1, batch_a = 1, batch_b = 1;
+  bool trans_a = false, trans_b = false;
+  bool is_conv = false;
+  ConvGeo conv;
+};
+
+// B operand layouts understood by the tensor-core kernel.
+enum BLayout {
+  B_K_MAJOR = 0,   // [batch][N][ldb] with K contiguous (transposed / packed weights)
+  B_MN_MAJOR = 1   // [batch][K][ldb] with N contiguous (plain row-major [K, N])
+};
+
+struct Tf32Operands {
+  const float* a = nullptr;  // K-major A: [batch_a][M][lda] (or x for a gathered conv)
+  long long lda = 0;         // elements between consecutive rows of A
+  int a_gather = 0;          // 1: A is gathered from NHWC x by the conv geometry
+  const float* b = nullptr;
+  long long ldb = 0;         // elements between consecutive rows of the B storage
+  int b_layout = B_K_MAJOR;
+  int k_steps = 0;           // number of 32-wide K steps
+  int cin_pad = 0;           // gathered conv: per-tap channel count rounded up to 32
+};
+
+int launch_gemm_simt(tfjs_cuda_ctx* ctx, const GemmProblem& pr);
+int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operands& op);

@@ -1,0 +1,548 @@
+// TF32 GEMM and implicit-GEMM convolution on the sm_100a tensor cores.
+//
+// One persistent CTA per SM walks 128 x BN output tiles.  Warp roles:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and B tiles
+//               into 128-byte-swizzled shared-memory stages (no multicast).
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma.kind::tf32 from
+//               shared-memory descriptors into a TMEM accumulator; owns the TMEM
+//               allocation.
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (32 lanes x 32 columns per
+//               load), add the bias, apply the activation, store NHWC / row-major.
+//   warps 6-9   (convolution only) A gatherers: 16-byte cp.async copies of the
+//               im2col rows straight from the NHWC input, zero-filling taps that
+//               fall outside the image, written in the same swizzled layout TMA
+//               would produce.
+// Two TMEM accumulators alternate so the epilogue of tile i overlaps the main
+// loop of tile i+1.  Every mbarrier wait is bounded: when it gives up the kernel
+// records a code in the context's error word and drains.
+//
+// Operand formats.  A is K-major (rows of K contiguous floats).  B is either
+// K-major ([N][K]: transposed operands and packed weights) or MN-major ([K][N]
+// row-major, consumed directly through the MN-major shared-memory descriptor).
+// The tensor core reads the upper 19 bits of each fp32 word; weights are
+// rounded to TF32 when they are packed.
+#include <cuda.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "gemm.h"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;          // floats per K step = one 128-byte swizzle row
+constexpr int UMMA_K = 8;       // K of one tcgen05.mma.kind::tf32
+constexpr int A_STAGE_BYTES = BM * BK * 4;
+constexpr int GATHER_LAG = 2;   // cp.async groups in flight per gather thread
+constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+struct Tf32Args {
+  float* c;
+  const float* bias;
+  int bias_len;
+  ActParams ap;
+  int M, N;
+  int batch_a, batch_b;
+  int tiles_m, tiles_n, total_tiles;
+  int k_steps;
+  int* flag;
+  // gathered convolution
+  const float* x;
+  ConvGeo conv;
+  int chunks_per_tap;  // 32-channel chunks per filter tap
+};
+
+// ---- PTX wrappers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the phase did not complete within kWaitCycles.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t n = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++n & 0x3ff) == 0 && clock64() - t0 > kWaitCycles) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm,
+                                            uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(tm), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t adesc,
+                                            uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+      "[%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+        "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+        "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+        "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptors (128-byte swizzle, descriptor version 1).
+// K-major: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+// MN-major: 32-float column blocks 4096 bytes apart (leading offset), 8-row K
+// groups 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+  return (uint64_t)((addr >> 4) & 0x3fff) | (256ull << 16) | (64ull << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+
+template <int BN>
+struct Cfg {
+  static constexpr int B_STAGE_BYTES = BN * BK * 4;
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int SMEM_BYTES =
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+};
+
+template <int BN, int B_MN, int A_GATHER>
+__global__ void __launch_bounds__(A_GATHER ? 320 : 192, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
+                 const __grid_constant__ CUtensorMap tm_b, const Tf32Args g) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_base = smem_base;
+  const uint32_t b_base = smem_base + STAGES * A_STAGE_BYTES;
+  const uint32_t bar_base = b_base + STAGES * C::B_STAGE_BYTES;
+  // barrier layout: full[STAGES], empty[STAGES], tfull[2], tempty[2], tmem slot
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), A_GATHER ? 1 + 128 : 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile(
+        "tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+        "r"((uint32_t)C::TMEM_COLS)
+        : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  const int k_steps = g.k_steps;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer --
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x) {
+        const int nt = tile % g.tiles_n;
+        const int rest = tile / g.tiles_n;
+        const int mt = rest % g.tiles_m;
+        const int bz = rest / g.tiles_m;
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
+            atomicExch(g.flag, 1);
+            alive = false;
+            break;
+          }
+          const uint32_t fb = full_bar(stage);
+          mbar_expect_tx(fb, (A_GATHER ? 0 : A_STAGE_BYTES) + C::B_STAGE_BYTES);
+          if (!A_GATHER)
+            tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_a, fb, ks * BK, mt * BM,
+                        bz % g.batch_a);
+          const uint32_t bdst = b_base + stage * C::B_STAGE_BYTES;
+          if (!B_MN) {
+            tma_load_3d(bdst, &tm_b, fb, ks * BK, nt * BN, bz % g.batch_b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j)
+              tma_load_3d(bdst + j * 4096, &tm_b, fb, nt * BN + j * 32, ks * BK,
+                          bz % g.batch_b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      // instruction descriptor: D=f32, A=B=tf32, A K-major, B per template,
+      // N = BN, M = 128.
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) |
+                             ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), aphase ^ 1)) {
+          atomicExch(g.flag, 2);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int ks = 0; ks < k_steps; ++ks) {
+          if (!mbar_wait(full_bar(stage), phase)) {
+            atomicExch(g.flag, 3);
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = a_base + stage * A_STAGE_BYTES;
+          const uint32_t sb = b_base + stage * C::B_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = desc_k_major(sa + k * UMMA_K * 4);
+            const uint64_t bd = B_MN ? desc_mn_major(sb + k * 1024)
+                                     : desc_k_major(sb + k * UMMA_K * 4);
+            tc_mma_tf32(d_tmem, ad, bd, idesc, (ks | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (alive) tc_commit(tfull_bar(acc));
+      }
+    }
+  } else if (warp < 6) {
+    // ----------------------------------------------------------- epilogue --
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    const bool vec4 = (g.N & 3) == 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < g.total_tiles; tile += gridDim.x, ++it) {
+      const int nt = tile % g.tiles_n;
+      const int rest = tile / g.tiles_n;
+      const int mt = rest % g.tiles_m;
+      const int bz = rest / g.tiles_m;
+      const int acc = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      if (!mbar_wait(tfull_bar(acc), aphase)) {
+        if (lane == 0) atomicExch(g.flag, 4);
+        break;
+      }
+      tc_fence_after();
+      const int m = mt * BM + row_in_tile;
+      float* crow = g.c + ((long long)bz * g.M + m) * g.N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int n0 = nt * BN + c0;
+        if (n0 >= g.N) break;
+        float v[32];
+        tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), v);
+        if (m < g.M) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + j;
+            float t = v[j];
+            if (g.bias_len) t = __fadd_rn(t, g.bias[g.bias_len == 1 ? 0 : (n < g.N ? n : 0)]);
+            v[j] = apply_act(t, g.ap, n < g.N ? n : 0);
+          }
+          if (vec4) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (n0 + j < g.N)
+                *reinterpret_cast<float4*>(crow + n0 + j) =
+                    make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < g.N) crow[n0 + j] = v[j];
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+    }
+  } else if (A_GATHER) {
+    // ----------------------------------------------------- im2col gatherers --
+    const int r = threadIdx.x - 192;  // row of the A tile owned by this thread
+    const ConvGeo& cv = g.conv;
+    int stage = 0;
+    uint32_t phase = 0;
+    int sig_stage = 0;   // oldest stage whose copies are not yet published
+    int in_flight = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x) {
+      const int rest = tile / g.tiles_n;
+      const int mt = rest % g.tiles_m;
+      const int m = mt * BM + r;
+      const bool row_ok = m < g.M;
+      int ow = 0, oh = 0, b = 0;
+      if (row_ok) {
+        ow = m % cv.out_w;
+        const int t = m / cv.out_w;
+        oh = t % cv.out_h;
+        b = t / cv.out_h;
+      }
+      const int r_base = oh * cv.s_h - cv.pad_t;
+      const int c_base = ow * cv.s_w - cv.pad_l;
+      const uint32_t row_off = (uint32_t)r * 128u;
+      const uint32_t sw = (uint32_t)(r & 7);
+      for (int ks = 0; ks < k_steps; ++ks) {
+        const int tap = ks / g.chunks_per_tap;
+        const int cc = (ks - tap * g.chunks_per_tap) * BK;
+        const int fr = tap / cv.f_w, fc = tap - fr * cv.f_w;
+        const int ri = r_base + fr * cv.d_h;
+        const int ci = c_base + fc * cv.d_w;
+        const bool ok = row_ok && ri >= 0 && ri < cv.in_h && ci >= 0 && ci < cv.in_w;
+        const float* src =
+            ok ? g.x + (((long long)b * cv.in_h + ri) * cv.in_w + ci) * cv.in_c + cc : g.x;
+        if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
+          atomicExch(g.flag, 5);
+          alive = false;
+          break;
+        }
+        const uint32_t dst = a_base + stage * A_STAGE_BYTES + row_off;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t bytes = (ok && cc + j * 4 < cv.in_c) ? 16u : 0u;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                           dst + (((uint32_t)j ^ sw) << 4)),
+                       "l"(bytes ? src + j * 4 : g.x), "r"(bytes)
+                       : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (++in_flight > GATHER_LAG) {
+          asm volatile("cp.async.wait_group %0;" ::"n"(GATHER_LAG) : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive(full_bar(sig_stage));
+          if (++sig_stage == STAGES) sig_stage = 0;
+          --in_flight;
+        }
+      }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    while (in_flight > 0) {
+      mbar_arrive(full_bar(sig_stage));
+      if (++sig_stage == STAGES) sig_stage = 0;
+      --in_flight;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)C::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+          cudaSuccess &&
+      q == cudaDriverEntryPointSuccess)
+    fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+// 3-D map over [batch][rows][inner] floats; box = [1][box_rows][32].
+int make_map(tfjs_cuda_ctx* ctx, CUtensorMap* tm, const float* base, uint64_t inner,
+             uint64_t rows, uint64_t batch, uint64_t row_stride_elems,
+             uint64_t batch_stride_elems, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return ctx_fail(ctx, TFJS_CUDA_DRIVER_ERROR, "cuTensorMapEncodeTiled not found");
+  cuuint64_t dims[3] = {inner, rows, batch};
+  cuuint64_t strides[2] = {row_stride_elems * 4, batch_stride_elems * 4};
+  if (batch == 1) strides[1] = rows * row_stride_elems * 4;
+  cuuint32_t box[3] = {BK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return ctx_fail(ctx, TFJS_CUDA_DRIVER_ERROR,
+                    "cuTensorMapEncodeTiled failed (%d): inner=%llu rows=%llu batch=%llu "
+                    "row_stride=%llu",
+                    (int)r, (unsigned long long)inner, (unsigned long long)rows,
+                    (unsigned long long)batch, (unsigned long long)row_stride_elems);
+  return TFJS_CUDA_OK;
+}
+
+template <int BN, int B_MN, int A_GATHER>
+int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
+               Tf32Args& g) {
+  using C = Cfg<BN>;
+  auto kern = gemm_tf32_kernel<BN, B_MN, A_GATHER>;
+  static bool configured[64] = {false};  // per device ordinal
+  if (ctx->device >= 64 || !configured[ctx->device]) {
+    CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       C::SMEM_BYTES));
+    if (ctx->device < 64) configured[ctx->device] = true;
+  }
+  g.tiles_n = (g.N + BN - 1) / BN;
+  g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
+  const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
+  kern<<<grid, A_GATHER ? 320 : 192, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, g);
+  LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
+  return TFJS_CUDA_OK;
+}
+
+template <int B_MN, int A_GATHER>
+int launch_bn(tfjs_cuda_ctx* ctx, int bn, const CUtensorMap& a, const CUtensorMap& b,
+              Tf32Args& g) {
+  switch (bn) {
+    case 32: return launch_cfg<32, B_MN, A_GATHER>(ctx, a, b, g);
+    case 64: return launch_cfg<64, B_MN, A_GATHER>(ctx, a, b, g);
+    case 128: return launch_cfg<128, B_MN, A_GATHER>(ctx, a, b, g);
+    default: return launch_cfg<256, B_MN, A_GATHER>(ctx, a, b, g);
+  }
+}
+
+int pick_bn(int M, int N, int batch, int sm_count) {
+  // Smallest tile that covers N, but do not starve the machine: when the tile
+  // count is below the SM count a narrower tile gives more CTAs.
+  int bn = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
+  const long long tiles_m = (M + BM - 1) / BM;
+  while (bn > 64 && tiles_m * ((N + bn - 1) / bn) * batch < sm_count) bn >>= 1;
+  return bn;
+}
+
+}  // namespace
+
+int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operands& op) {
+  Tf32Args g;
+  g.c = pr.c;
+  g.bias = pr.bias;
+  g.bias_len = pr.bias ? pr.bias_len : 0;
+  g.ap = pr.ap;
+  g.M = pr.M;
+  g.N = pr.N;
+  g.batch_a = pr.batch_a;
+  g.batch_b = pr.batch_b;
+  g.tiles_m = (pr.M + BM - 1) / BM;
+  g.total_tiles = pr.batch;  // multiplied out in launch_cfg
+  g.k_steps = op.k_steps;
+  g.flag = ctx->d_flag;
+  g.x = op.a;
+  g.conv = pr.conv;
+  g.chunks_per_tap = op.cin_pad / BK;
+  const int bn = pick_bn(pr.M, pr.N, pr.batch, ctx->sm_count);
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if (op.a_gather) {
+    // A is gathered; the kernel still takes a map argument, so alias B's.
+    memset(&tm_a, 0, sizeof tm_a);
+  } else {
+    if ((rc = make_map(ctx, &tm_a, op.a, (uint64_t)pr.K, (uint64_t)pr.M,
+                       (uint64_t)pr.batch_a, (uint64_t)op.lda,
+                       (uint64_t)pr.M * op.lda, BM)))
+      return rc;
+  }
+  if (op.b_layout == B_K_MAJOR) {
+    const uint64_t kk = (uint64_t)op.k_steps * BK < (uint64_t)op.ldb
+                            ? (uint64_t)op.k_steps * BK : (uint64_t)op.ldb;
+    if ((rc = make_map(ctx, &tm_b, op.b, kk, (uint64_t)pr.N, (uint64_t)pr.batch_b,
+                       (uint64_t)op.ldb, (uint64_t)pr.N * op.ldb, (uint32_t)bn)))
+      return rc;
+    if (op.a_gather) {
+      tm_a = tm_b;
+      return launch_bn<0, 1>(ctx, bn, tm_a, tm_b, g);
+    }
+    return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, g);
+  }
+  if ((rc = make_map(ctx, &tm_b, op.b, (uint64_t)pr.N, (uint64_t)pr.K,
+                     (uint64_t)pr.batch_b, (uint64_t)op.ldb, (uint64_t)pr.K * op.ldb, 32)))
+    return rc;
+  if (op.a_gather) {
+    tm_a = tm_b;
+    return launch_bn<1, 1>(ctx, bn, tm_a, tm_b, g);
+  }
+  return launch_bn<1, 0>(ctx, bn, tm_a, tm_b, g);
+}

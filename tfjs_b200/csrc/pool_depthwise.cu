@@ -1,0 +1,275 @@
+// MaxPool / AvgPool and FusedDepthwiseConv2D: NHWC, bandwidth-bound SIMT kernels.
+// A thread owns four adjacent channels of one output pixel and moves them with
+// 128-bit loads/stores, so a warp reads and writes 512 contiguous bytes per
+// tap; overlapping taps of neighbouring pixels are served by L1/L2.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+struct Geo {
+  int batch, in_h, in_w, c;     // c = input channels
+  int out_h, out_w;
+  int f_h, f_w;                 // pool: effective window; conv: filter taps
+  int s_h, s_w, d_h, d_w, pad_t, pad_l;
+  int ch_mul;
+};
+
+// ---- pooling: tfjs-backend-cpu/src/utils/pool_utils.ts:43-84 -----------------
+// The window is clipped to the image; max starts at -inf and moves on
+// `pixel > max` (NaN is never selected); avg divides the double sum by the
+// number of in-bounds taps.
+template <bool IS_MAX, int VEC>
+__global__ void pool2d_kernel(const float* __restrict__ x, float* __restrict__ y,
+                              Geo g) {
+  const int cv = g.c / VEC;
+  const uint64_t n = (uint64_t)g.batch * g.out_h * g.out_w * cv;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    const int c = (int)(i % cv) * VEC;
+    uint64_t rem = i / cv;
+    const int ow = (int)(rem % g.out_w);
+    rem /= g.out_w;
+    const int oh = (int)(rem % g.out_h);
+    const int b = (int)(rem / g.out_h);
+    const int r0 = oh * g.s_h - g.pad_t, c0 = ow * g.s_w - g.pad_l;
+    // First in-bounds tap on the dilation grid, as `xR = xRMin; xR += dilation`
+    // does in the reference (it starts at max(0, corner), not at a grid point).
+    const int r_min = r0 > 0 ? r0 : 0, c_min = c0 > 0 ? c0 : 0;
+    const int r_max = min(g.in_h, g.f_h + r0), c_max = min(g.in_w, g.f_w + c0);
+    float mx[VEC];
+    double sum[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) { mx[v] = -INFINITY; sum[v] = 0.0; }
+    int count = 0;
+    for (int r = r_min; r < r_max; r += g.d_h) {
+      for (int cc = c_min; cc < c_max; cc += g.d_w) {
+        const float* p = x + (((uint64_t)b * g.in_h + r) * g.in_w + cc) * g.c + c;
+        float px[VEC];
+        if (VEC == 4) {
+          const float4 t = *reinterpret_cast<const float4*>(p);
+          px[0] = t.x; px[1 % VEC] = t.y; px[2 % VEC] = t.z; px[3 % VEC] = t.w;
+        } else {
+          px[0] = p[0];
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          if (IS_MAX) { if (px[v] > mx[v]) mx[v] = px[v]; }
+          else sum[v] += (double)px[v];
+        }
+        ++count;
+      }
+    }
+    float out[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v)
+      out[v] = IS_MAX ? mx[v] : (float)(sum[v] / (double)count);
+    float* q = y + (((uint64_t)b * g.out_h + oh) * g.out_w + ow) * g.c + c;
+    if (VEC == 4)
+      *reinterpret_cast<float4*>(q) = make_float4(out[0], out[1 % VEC], out[2 % VEC], out[3 % VEC]);
+    else
+      q[0] = out[0];
+  }
+}
+
+// ---- depthwise conv: tfjs-backend-cpu/src/kernels/DepthwiseConv2dNative.ts:62-99
+// Per output element the taps arrive in (wR, wC) order and every MAC rounds the
+// running value to fp32; fmaf reproduces that up to double-rounding ties.
+// Then bias (fp32 add) and the activation, as FusedDepthwiseConv2D.ts:42-60.
+template <int VEC>  // channel multiplier 1, VEC channels per thread
+__global__ void depthwise_kernel(const float* __restrict__ x,
+                                 const float* __restrict__ w,
+                                 const float* __restrict__ bias, int bias_len,
+                                 ActParams ap, float* __restrict__ y, Geo g) {
+  const int cv = g.c / VEC;
+  const uint64_t n = (uint64_t)g.batch * g.out_h * g.out_w * cv;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    const int c = (int)(i % cv) * VEC;
+    uint64_t rem = i / cv;
+    const int ow = (int)(rem % g.out_w);
+    rem /= g.out_w;
+    const int oh = (int)(rem % g.out_h);
+    const int b = (int)(rem / g.out_h);
+    const int r0 = oh * g.s_h - g.pad_t, c0 = ow * g.s_w - g.pad_l;
+    float acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] = 0.0f;
+    for (int fr = 0; fr < g.f_h; ++fr) {
+      const int r = r0 + fr * g.d_h;
+      if (r < 0 || r >= g.in_h) continue;
+      for (int fc = 0; fc < g.f_w; ++fc) {
+        const int cc = c0 + fc * g.d_w;
+        if (cc < 0 || cc >= g.in_w) continue;
+        const float* p = x + (((uint64_t)b * g.in_h + r) * g.in_w + cc) * g.c + c;
+        const float* q = w + ((uint64_t)fr * g.f_w + fc) * g.c + c;
+        if (VEC == 4) {
+          const float4 xv = *reinterpret_cast<const float4*>(p);
+          const float4 wv = __ldg(reinterpret_cast<const float4*>(q));
+          acc[0] = fmaf(xv.x, wv.x, acc[0]);
+          acc[1 % VEC] = fmaf(xv.y, wv.y, acc[1 % VEC]);
+          acc[2 % VEC] = fmaf(xv.z, wv.z, acc[2 % VEC]);
+          acc[3 % VEC] = fmaf(xv.w, wv.w, acc[3 % VEC]);
+        } else {
+          acc[0] = fmaf(p[0], __ldg(q), acc[0]);
+        }
+      }
+    }
+    float* o = y + (((uint64_t)b * g.out_h + oh) * g.out_w + ow) * g.c + c;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      float t = acc[v];
+      if (bias_len) t = __fadd_rn(t, bias[bias_len == 1 ? 0 : c + v]);
+      acc[v] = apply_act(t, ap, c + v);
+    }
+    if (VEC == 4)
+      *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+    else
+      o[0] = acc[0];
+  }
+}
+
+// General channel multiplier: one thread per output element.
+__global__ void depthwise_chmul_kernel(const float* __restrict__ x,
+                                       const float* __restrict__ w,
+                                       const float* __restrict__ bias,
+                                       int bias_len, ActParams ap,
+                                       float* __restrict__ y, Geo g) {
+  const int out_c = g.c * g.ch_mul;
+  const uint64_t n = (uint64_t)g.batch * g.out_h * g.out_w * out_c;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    const int oc = (int)(i % out_c);
+    const int d1 = oc / g.ch_mul, q = oc % g.ch_mul;
+    uint64_t rem = i / out_c;
+    const int ow = (int)(rem % g.out_w);
+    rem /= g.out_w;
+    const int oh = (int)(rem % g.out_h);
+    const int b = (int)(rem / g.out_h);
+    const int r0 = oh * g.s_h - g.pad_t, c0 = ow * g.s_w - g.pad_l;
+    float acc = 0.0f;
+    for (int fr = 0; fr < g.f_h; ++fr) {
+      const int r = r0 + fr * g.d_h;
+      if (r < 0 || r >= g.in_h) continue;
+      for (int fc = 0; fc < g.f_w; ++fc) {
+        const int cc = c0 + fc * g.d_w;
+        if (cc < 0 || cc >= g.in_w) continue;
+        acc = fmaf(x[(((uint64_t)b * g.in_h + r) * g.in_w + cc) * g.c + d1],
+                   w[(((uint64_t)fr * g.f_w + fc) * g.c + d1) * g.ch_mul + q], acc);
+      }
+    }
+    if (bias_len) acc = __fadd_rn(acc, bias[bias_len == 1 ? 0 : oc]);
+    y[i] = apply_act(acc, ap, oc);
+  }
+}
+
+int check_geo(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p, const char* who) {
+  if (!p) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "%s: null params", who);
+  if (p->batch < 0 || p->in_h < 0 || p->in_w < 0 || p->in_c < 0 || p->out_h < 0 ||
+      p->out_w < 0 || p->out_c < 0 || p->filter_h <= 0 || p->filter_w <= 0 ||
+      p->stride_h <= 0 || p->stride_w <= 0 || p->dilation_h <= 0 || p->dilation_w <= 0)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "%s: bad geometry", who);
+  return TFJS_CUDA_OK;
+}
+
+Geo make_geo(const tfjs_cuda_conv2d_params* p) {
+  Geo g;
+  g.batch = p->batch; g.in_h = p->in_h; g.in_w = p->in_w; g.c = p->in_c;
+  g.out_h = p->out_h; g.out_w = p->out_w; g.f_h = p->filter_h; g.f_w = p->filter_w;
+  g.s_h = p->stride_h; g.s_w = p->stride_w; g.d_h = p->dilation_h; g.d_w = p->dilation_w;
+  g.pad_t = p->pad_top; g.pad_l = p->pad_left; g.ch_mul = 1;
+  return g;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
+                     int32_t is_max, int32_t x_id, int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  int rc;
+  if ((rc = check_geo(ctx, p, "pool2d"))) return rc;
+  const uint64_t nx = (uint64_t)p->batch * p->in_h * p->in_w * p->in_c;
+  const uint64_t ny = (uint64_t)p->batch * p->out_h * p->out_w * p->in_c;
+  Buffer *x, *y;
+  if ((rc = ctx_get(ctx, x_id, nx * 4, "pool2d x", &x))) return rc;
+  if ((rc = ctx_get(ctx, out_id, ny * 4, "pool2d out", &y))) return rc;
+  if (ny == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  Geo g = make_geo(p);
+  const float* xp = (const float*)x->ptr;
+  float* yp = (float*)y->ptr;
+  if (g.c % 4 == 0) {
+    const unsigned grid = grid_for(ny / 4, kThreads, ctx->sm_count);
+    if (is_max) pool2d_kernel<true, 4><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, g);
+    else pool2d_kernel<false, 4><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, g);
+  } else {
+    const unsigned grid = grid_for(ny, kThreads, ctx->sm_count);
+    if (is_max) pool2d_kernel<true, 1><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, g);
+    else pool2d_kernel<false, 1><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, g);
+  }
+  LAUNCH_CHECK(ctx, "pool2d_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_fused_depthwise_conv2d(tfjs_cuda_ctx* ctx,
+                                     const tfjs_cuda_conv2d_params* p,
+                                     int32_t x_id, int32_t filter_id,
+                                     int32_t bias_id, int32_t prelu_id,
+                                     int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  int rc;
+  if ((rc = check_geo(ctx, p, "fused_depthwise_conv2d"))) return rc;
+  if (p->in_c <= 0 || p->out_c % p->in_c != 0)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG,
+                    "fused_depthwise_conv2d: out_c %d is not a multiple of in_c %d",
+                    p->out_c, p->in_c);
+  if ((p->bias_len != 0 && p->bias_len != 1 && p->bias_len != p->out_c) ||
+      (p->prelu_len != 0 && p->prelu_len != 1 && p->prelu_len != p->out_c))
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
+                    "fused_depthwise_conv2d: bias/prelu must be scalar or per channel");
+  if (p->activation == TFJS_CUDA_ACT_PRELU && (!prelu_id || !p->prelu_len))
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_depthwise_conv2d: prelu weights missing");
+  const int ch_mul = p->out_c / p->in_c;
+  const uint64_t nx = (uint64_t)p->batch * p->in_h * p->in_w * p->in_c;
+  const uint64_t nw = (uint64_t)p->filter_h * p->filter_w * p->out_c;
+  const uint64_t ny = (uint64_t)p->batch * p->out_h * p->out_w * p->out_c;
+  Buffer *x, *w, *bias = nullptr, *prelu = nullptr, *y;
+  if ((rc = ctx_get(ctx, x_id, nx * 4, "fused_depthwise_conv2d x", &x))) return rc;
+  if ((rc = ctx_get(ctx, filter_id, nw * 4, "fused_depthwise_conv2d filter", &w))) return rc;
+  if (p->bias_len && (rc = ctx_get(ctx, bias_id, (uint64_t)p->bias_len * 4, "fused_depthwise_conv2d bias", &bias))) return rc;
+  if (p->activation == TFJS_CUDA_ACT_PRELU &&
+      (rc = ctx_get(ctx, prelu_id, (uint64_t)p->prelu_len * 4, "fused_depthwise_conv2d prelu", &prelu))) return rc;
+  if ((rc = ctx_get(ctx, out_id, ny * 4, "fused_depthwise_conv2d out", &y))) return rc;
+  if (ny == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  Geo g = make_geo(p);
+  g.ch_mul = ch_mul;
+  ActParams ap;
+  ap.act = p->activation;
+  ap.prelu_len = p->prelu_len;
+  ap.prelu = prelu ? (const float*)prelu->ptr : nullptr;
+  ap.alpha = p->leakyrelu_alpha;
+  const float* bp = bias ? (const float*)bias->ptr : nullptr;
+  const int bl = bias ? p->bias_len : 0;
+  if (ch_mul == 1 && g.c % 4 == 0)
+    depthwise_kernel<4><<<grid_for(ny / 4, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+        (const float*)x->ptr, (const float*)w->ptr, bp, bl, ap, (float*)y->ptr, g);
+  else if (ch_mul == 1)
+    depthwise_kernel<1><<<grid_for(ny, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+        (const float*)x->ptr, (const float*)w->ptr, bp, bl, ap, (float*)y->ptr, g);
+  else
+    depthwise_chmul_kernel<<<grid_for(ny, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+        (const float*)x->ptr, (const float*)w->ptr, bp, bl, ap, (float*)y->ptr, g);
+  LAUNCH_CHECK(ctx, "depthwise_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+}  // extern "C"

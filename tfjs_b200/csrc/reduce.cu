@@ -1,0 +1,291 @@
+// Softmax, Sum/Mean/Max and ArgMax.  Bandwidth-bound SIMT kernels: each row is
+// read once (softmax keeps it in registers), reductions use warp shuffles.
+//
+// Accumulation is in double, as in the reference where the running sum is a JS
+// number (tfjs-backend-cpu/src/kernels/Sum.ts:67-74); with a double accumulator
+// the order of additions only matters far below fp32 resolution.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarpsPerBlock = kThreads / 32;
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Max with the reference's NaN rule (Max_impl.ts:26-36): NaN is sticky.
+__device__ __forceinline__ float nan_max(float a, float b) {
+  if (a != a) return a;
+  if (b != b) return b;
+  return a > b ? a : b;
+}
+
+__device__ __forceinline__ float warp_nan_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = nan_max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- softmax: tfjs-backend-cpu/src/kernels/Softmax.ts:50-67 -----------------
+// max -> a = fl32(x - max) -> e = fl32(exp(a)) -> s = fl32(sum_double(e)) ->
+// out = fl32(e / s).  One warp per row; up to 32 values per lane stay in
+// registers (rows up to 1024 wide); wider rows recompute e from global.
+constexpr int kRegCols = 32;
+
+__global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ y,
+                               uint64_t rows, uint32_t cols) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    const float* xr = x + r * cols;
+    float* yr = y + r * cols;
+    float m = xr[0];
+    if (cols <= 32 * kRegCols) {
+      float v[kRegCols];
+#pragma unroll
+      for (int j = 0; j < kRegCols; ++j) {
+        const uint32_t c = lane + 32 * j;
+        v[j] = c < cols ? xr[c] : -INFINITY;
+        if (c < cols) m = nan_max(m, v[j]);
+      }
+      m = warp_nan_max(m);
+      double s = 0.0;
+#pragma unroll
+      for (int j = 0; j < kRegCols; ++j) {
+        const uint32_t c = lane + 32 * j;
+        if (c < cols) {
+          v[j] = (float)exp((double)__fsub_rn(v[j], m));
+          s += (double)v[j];
+        }
+      }
+      const float sf = (float)warp_sum(s);
+#pragma unroll
+      for (int j = 0; j < kRegCols; ++j) {
+        const uint32_t c = lane + 32 * j;
+        if (c < cols) yr[c] = __fdiv_rn(v[j], sf);
+      }
+    } else {
+      for (uint32_t c = lane; c < cols; c += 32) m = nan_max(m, xr[c]);
+      m = warp_nan_max(m);
+      double s = 0.0;
+      for (uint32_t c = lane; c < cols; c += 32) {
+        const float e = (float)exp((double)__fsub_rn(xr[c], m));
+        yr[c] = e;
+        s += (double)e;
+      }
+      const float sf = (float)warp_sum(s);
+      for (uint32_t c = lane; c < cols; c += 32) yr[c] = __fdiv_rn(yr[c], sf);
+    }
+  }
+}
+
+// ---- reductions over the middle axis of [outer, reduce, inner] ----------------
+// OP 0 sum, 1 mean (each element divided by n in fp32 first, Mean.ts:37-48),
+// 2 max.
+template <int OP>
+__device__ __forceinline__ void red_init(double& acc, float& mx, float first) {
+  acc = 0.0;
+  mx = first;
+}
+
+// inner == 1: one warp per output row, lanes stride the reduced axis.
+template <int OP>
+__global__ void reduce_rows_kernel(const float* __restrict__ x,
+                                   float* __restrict__ y, uint64_t rows,
+                                   uint64_t reduce, float nf) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    const float* xr = x + r * reduce;
+    double acc = 0.0;
+    float mx = xr[0];
+    for (uint64_t j = lane; j < reduce; j += 32) {
+      const float v = xr[j];
+      if (OP == 0) acc += (double)v;
+      else if (OP == 1) acc += (double)__fdiv_rn(v, nf);
+      else mx = nan_max(mx, v);
+    }
+    if (OP == 2) {
+      mx = warp_nan_max(mx);
+      if (lane == 0) y[r] = mx;
+    } else {
+      acc = warp_sum(acc);
+      if (lane == 0) y[r] = (float)acc;
+    }
+  }
+}
+
+// inner > 1: one thread per (outer, inner) output, coalesced across inner.
+template <int OP>
+__global__ void reduce_mid_kernel(const float* __restrict__ x,
+                                  float* __restrict__ y, uint64_t outer,
+                                  uint64_t reduce, uint64_t inner, float nf) {
+  const uint64_t n = outer * inner;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    const uint64_t o = i / inner, in = i % inner;
+    const float* xp = x + o * reduce * inner + in;
+    double acc = 0.0;
+    float mx = xp[0];
+    for (uint64_t j = 0; j < reduce; ++j) {
+      const float v = xp[j * inner];
+      if (OP == 0) acc += (double)v;
+      else if (OP == 1) acc += (double)__fdiv_rn(v, nf);
+      else mx = nan_max(mx, v);
+    }
+    y[i] = OP == 2 ? mx : (float)acc;
+  }
+}
+
+// ---- argmax: tfjs-backend-cpu/src/kernels/ArgMax.ts:55-66 ---------------------
+// Sequential semantics: max starts at element 0 and moves on `value > max`, so
+// the answer is 0 when element 0 is NaN, else the first index of the largest
+// non-NaN value.
+struct Best {
+  float v;
+  int32_t i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  // NaN entries never win; ties go to the smaller index.
+  if (b.v != b.v) return a;
+  if (a.v != a.v) return b;
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+
+__global__ void argmax_rows_kernel(const float* __restrict__ x,
+                                   int32_t* __restrict__ y, uint64_t rows,
+                                   uint64_t reduce) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    const float* xr = x + r * reduce;
+    const float first = xr[0];
+    Best b;
+    b.v = NAN;
+    b.i = 0x7fffffff;
+    for (uint64_t j = lane; j < reduce; j += 32) {
+      Best c;
+      c.v = xr[j];
+      c.i = (int32_t)j;
+      b = better(b, c);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best c;
+      c.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+      c.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+      b = better(b, c);
+    }
+    if (lane == 0) y[r] = (first != first || b.v != b.v) ? 0 : b.i;
+  }
+}
+
+__global__ void argmax_mid_kernel(const float* __restrict__ x,
+                                  int32_t* __restrict__ y, uint64_t outer,
+                                  uint64_t reduce, uint64_t inner) {
+  const uint64_t n = outer * inner;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    const uint64_t o = i / inner, in = i % inner;
+    const float* xp = x + o * reduce * inner + in;
+    float mx = xp[0];
+    int32_t mi = 0;
+    for (uint64_t j = 0; j < reduce; ++j) {
+      const float v = xp[j * inner];
+      if (v > mx) { mx = v; mi = (int32_t)j; }
+    }
+    y[i] = mi;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
+                      uint64_t cols, int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  Buffer *x, *y;
+  int rc;
+  if ((rc = ctx_get(ctx, x_id, rows * cols * 4, "softmax x", &x))) return rc;
+  if ((rc = ctx_get(ctx, out_id, rows * cols * 4, "softmax out", &y))) return rc;
+  if (rows * cols == 0) return TFJS_CUDA_OK;
+  if (cols > 0xffffffffu)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "softmax: row too wide");
+  cudaSetDevice(ctx->device);
+  softmax_kernel<<<grid_for(rows * 32, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+      (const float*)x->ptr, (float*)y->ptr, rows, (uint32_t)cols);
+  LAUNCH_CHECK(ctx, "softmax_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_reduce(tfjs_cuda_ctx* ctx, int32_t op, int32_t x_id,
+                     uint64_t outer, uint64_t reduce, uint64_t inner,
+                     int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (op < 0 || op > 2) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "reduce: op %d", op);
+  Buffer *x, *y;
+  int rc;
+  if ((rc = ctx_get(ctx, x_id, outer * reduce * inner * 4, "reduce x", &x))) return rc;
+  if ((rc = ctx_get(ctx, out_id, outer * inner * 4, "reduce out", &y))) return rc;
+  if (outer * inner == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  if (reduce == 0) {
+    // Sum/Mean over nothing is 0; Max over nothing is not defined by the reference.
+    CUDA_TRY(ctx, cudaMemsetAsync(y->ptr, 0, outer * inner * 4, ctx->stream));
+    ctx_mark_written(ctx, out_id);
+    return TFJS_CUDA_OK;
+  }
+  const float nf = (float)reduce;
+  const float* xp = (const float*)x->ptr;
+  float* yp = (float*)y->ptr;
+  if (inner == 1) {
+    const unsigned grid = grid_for(outer * 32, kThreads, ctx->sm_count);
+    if (op == 0) reduce_rows_kernel<0><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, outer, reduce, nf);
+    else if (op == 1) reduce_rows_kernel<1><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, outer, reduce, nf);
+    else reduce_rows_kernel<2><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, outer, reduce, nf);
+  } else {
+    const unsigned grid = grid_for(outer * inner, 128, ctx->sm_count);
+    if (op == 0) reduce_mid_kernel<0><<<grid, 128, 0, ctx->stream>>>(xp, yp, outer, reduce, inner, nf);
+    else if (op == 1) reduce_mid_kernel<1><<<grid, 128, 0, ctx->stream>>>(xp, yp, outer, reduce, inner, nf);
+    else reduce_mid_kernel<2><<<grid, 128, 0, ctx->stream>>>(xp, yp, outer, reduce, inner, nf);
+  }
+  LAUNCH_CHECK(ctx, "reduce_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_argmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t outer,
+                     uint64_t reduce, uint64_t inner, int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  Buffer *x, *y;
+  int rc;
+  if ((rc = ctx_get(ctx, x_id, outer * reduce * inner * 4, "argmax x", &x))) return rc;
+  if ((rc = ctx_get(ctx, out_id, outer * inner * 4, "argmax out", &y))) return rc;
+  if (outer * inner == 0) return TFJS_CUDA_OK;
+  if (reduce == 0 || reduce > 0x7fffffffu)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "argmax: bad reduce size");
+  cudaSetDevice(ctx->device);
+  if (inner == 1)
+    argmax_rows_kernel<<<grid_for(outer * 32, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+        (const float*)x->ptr, (int32_t*)y->ptr, outer, reduce);
+  else
+    argmax_mid_kernel<<<grid_for(outer * inner, 128, ctx->sm_count), 128, 0, ctx->stream>>>(
+        (const float*)x->ptr, (int32_t*)y->ptr, outer, reduce, inner);
+  LAUNCH_CHECK(ctx, "argmax_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,351 @@
+// Context, device-memory pool, id -> buffer table, host<->device transfer.
+//
+// The device half of the KernelBackend storage contract
+// (tfjs-core/src/backends/backend.ts:100-156).  Ref-counting stays with the
+// host-side DataStorage, as in the reference's WASM backend where the C++ side
+// only maps tensor ids to memory (tfjs-backend-wasm/src/cc/backend.cc:124-152).
+//
+// Everything runs on ONE in-order stream: kernels, H2D, D2H and frees.  The
+// graph executor disposes an intermediate as soon as its last consumer has
+// been *enqueued* (tfjs-converter/src/executor/graph_executor.ts:382-409), so
+// frees are stream-ordered (cudaFreeAsync) and a block can be handed to a later
+// kernel without any host-side wait.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+int ctx_fail(tfjs_cuda_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->err = buf;
+  return code;
+}
+
+int ctx_check(tfjs_cuda_ctx* ctx, cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return TFJS_CUDA_OK;
+  int code = e == cudaErrorMemoryAllocation ? TFJS_CUDA_OUT_OF_MEMORY
+                                            : TFJS_CUDA_DRIVER_ERROR;
+  return ctx_fail(ctx, code, "%s: %s", what, cudaGetErrorString(e));
+}
+
+Buffer* ctx_buf(tfjs_cuda_ctx* ctx, int32_t id) {
+  if (id <= 0 || (size_t)id >= ctx->bufs.size()) return nullptr;
+  Buffer* b = &ctx->bufs[id];
+  return b->live ? b : nullptr;
+}
+
+int ctx_get(tfjs_cuda_ctx* ctx, int32_t id, uint64_t need, const char* name,
+            Buffer** out) {
+  Buffer* b = ctx_buf(ctx, id);
+  if (!b) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "%s: unknown tensor id %d",
+                          name, id);
+  if (b->bytes < need)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG,
+                    "%s: tensor id %d holds %llu bytes, kernel needs %llu", name,
+                    id, (unsigned long long)b->bytes, (unsigned long long)need);
+  *out = b;
+  return TFJS_CUDA_OK;
+}
+
+int ctx_scratch(tfjs_cuda_ctx* ctx, uint64_t bytes, void** out) {
+  if (bytes > ctx->scratch_bytes) {
+    if (ctx->scratch) CUDA_TRY(ctx, cudaFreeAsync(ctx->scratch, ctx->stream));
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    uint64_t want = bytes + (bytes >> 2);
+    CUDA_TRY(ctx, cudaMallocAsync(&ctx->scratch, want, ctx->stream));
+    ctx->scratch_bytes = want;
+  }
+  *out = ctx->scratch;
+  return TFJS_CUDA_OK;
+}
+
+void ctx_mark_written(tfjs_cuda_ctx* ctx, int32_t id) {
+  Buffer* b = ctx_buf(ctx, id);
+  if (b) {
+    b->version++;
+    b->from_host = false;
+  }
+}
+
+void ctx_drop_packed(tfjs_cuda_ctx* ctx, int32_t id) {
+  auto it = ctx->packed.find(id);
+  if (it == ctx->packed.end()) return;
+  if (it->second.ptr) cudaFreeAsync(it->second.ptr, ctx->stream);
+  ctx->packed.erase(it);
+}
+
+extern "C" {
+
+int tfjs_cuda_device_count(int* out_count) {
+  if (!out_count) return TFJS_CUDA_INVALID_ARG;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  *out_count = e == cudaSuccess ? n : 0;
+  return e == cudaSuccess ? TFJS_CUDA_OK : TFJS_CUDA_DRIVER_ERROR;
+}
+
+int tfjs_cuda_create(int device_ordinal, tfjs_cuda_ctx** out_ctx) {
+  if (!out_ctx) return TFJS_CUDA_INVALID_ARG;
+  *out_ctx = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || device_ordinal < 0 ||
+      device_ordinal >= n)
+    return TFJS_CUDA_INVALID_ARG;
+  if (cudaSetDevice(device_ordinal) != cudaSuccess)
+    return TFJS_CUDA_DRIVER_ERROR;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess)
+    return TFJS_CUDA_DRIVER_ERROR;
+  if (prop.major != 10) {
+    fprintf(stderr,
+            "tfjs_cuda: device %d is sm_%d%d; this library carries sm_100a "
+            "code only\n",
+            device_ordinal, prop.major, prop.minor);
+    return TFJS_CUDA_UNSUPPORTED;
+  }
+  tfjs_cuda_ctx* ctx = new tfjs_cuda_ctx();
+  ctx->device = device_ordinal;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->bufs.resize(1);
+  bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) ==
+            cudaSuccess;
+  ok = ok && cudaDeviceGetDefaultMemPool(&ctx->pool, device_ordinal) ==
+                 cudaSuccess;
+  if (ok) {
+    // Keep freed blocks in the pool instead of returning them to the driver.
+    uint64_t threshold = UINT64_MAX;
+    ok = cudaMemPoolSetAttribute(ctx->pool, cudaMemPoolAttrReleaseThreshold,
+                                 &threshold) == cudaSuccess;
+  }
+  ok = ok && cudaMalloc(&ctx->d_flag, sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMemset(ctx->d_flag, 0, sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMallocHost(&ctx->h_flag, sizeof(int)) == cudaSuccess;
+  ok = ok && cudaMalloc(&ctx->d_bad_index, sizeof(long long)) == cudaSuccess;
+  ok = ok && cudaMallocHost(&ctx->h_bad_index, sizeof(long long)) == cudaSuccess;
+  ok = ok && cudaEventCreate(&ctx->ev0) == cudaSuccess;
+  ok = ok && cudaEventCreate(&ctx->ev1) == cudaSuccess;
+  if (!ok) {
+    fprintf(stderr, "tfjs_cuda: context setup failed: %s\n",
+            cudaGetErrorString(cudaGetLastError()));
+    tfjs_cuda_destroy(ctx);
+    return TFJS_CUDA_DRIVER_ERROR;
+  }
+  *ctx->h_flag = 0;
+  *out_ctx = ctx;
+  return TFJS_CUDA_OK;
+}
+
+void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
+  if (!ctx) return;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  for (auto& kv : ctx->packed)
+    if (kv.second.ptr) cudaFreeAsync(kv.second.ptr, ctx->stream);
+  for (auto& b : ctx->bufs)
+    if (b.live && b.ptr) cudaFreeAsync(b.ptr, ctx->stream);
+  if (ctx->scratch) cudaFreeAsync(ctx->scratch, ctx->stream);
+  if (ctx->l2_scratch) cudaFreeAsync(ctx->l2_scratch, ctx->stream);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  if (ctx->d_flag) cudaFree(ctx->d_flag);
+  if (ctx->h_flag) cudaFreeHost(ctx->h_flag);
+  if (ctx->d_bad_index) cudaFree(ctx->d_bad_index);
+  if (ctx->h_bad_index) cudaFreeHost(ctx->h_bad_index);
+  if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+  if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+}
+
+const char* tfjs_cuda_last_error(tfjs_cuda_ctx* ctx) {
+  return ctx ? ctx->err.c_str() : "null context";
+}
+
+int tfjs_cuda_alloc(tfjs_cuda_ctx* ctx, uint64_t nbytes, int32_t* out_id) {
+  if (!ctx || !out_id) return TFJS_CUDA_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  void* p = nullptr;
+  // Round up so vectorised kernels may read a full 16-byte tail.
+  uint64_t padded = ((nbytes + 255) / 256) * 256;
+  if (padded == 0) padded = 256;
+  CUDA_TRY(ctx, cudaMallocAsync(&p, padded, ctx->stream));
+  int32_t id;
+  if (!ctx->free_ids.empty()) {
+    id = ctx->free_ids.back();
+    ctx->free_ids.pop_back();
+  } else {
+    id = (int32_t)ctx->bufs.size();
+    ctx->bufs.emplace_back();
+  }
+  Buffer& b = ctx->bufs[id];
+  b.ptr = p;
+  b.bytes = nbytes;
+  b.live = true;
+  b.from_host = false;
+  b.version++;
+  ctx->in_use += padded;
+  ctx->n_live++;
+  if (ctx->in_use > ctx->high_water) ctx->high_water = ctx->in_use;
+  *out_id = id;
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  Buffer* b = ctx_buf(ctx, id);
+  if (!b) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "free: unknown tensor id %d", id);
+  cudaSetDevice(ctx->device);
+  ctx_drop_packed(ctx, id);
+  uint64_t padded = ((b->bytes + 255) / 256) * 256;
+  if (padded == 0) padded = 256;
+  cudaError_t e = cudaFreeAsync(b->ptr, ctx->stream);
+  b->ptr = nullptr;
+  b->live = false;
+  b->bytes = 0;
+  ctx->in_use -= padded;
+  ctx->n_live--;
+  ctx->free_ids.push_back(id);
+  return ctx_check(ctx, e, "cudaFreeAsync");
+}
+
+int tfjs_cuda_write(tfjs_cuda_ctx* ctx, int32_t id, const void* host,
+                    uint64_t nbytes) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  Buffer* b;
+  int rc = ctx_get(ctx, id, nbytes, "write", &b);
+  if (rc) return rc;
+  if (nbytes == 0) return TFJS_CUDA_OK;
+  if (!host) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "write: null host pointer");
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaMemcpyAsync(b->ptr, host, nbytes, cudaMemcpyHostToDevice,
+                                ctx->stream));
+  b->version++;
+  b->from_host = true;
+  ctx_drop_packed(ctx, id);
+  return TFJS_CUDA_OK;
+}
+
+static int report_flag(tfjs_cuda_ctx* ctx) {
+  if (*ctx->h_flag != 0) {
+    int v = *ctx->h_flag;
+    *ctx->h_flag = 0;
+    cudaMemsetAsync(ctx->d_flag, 0, sizeof(int), ctx->stream);
+    return ctx_fail(ctx, TFJS_CUDA_DEVICE_TIMEOUT,
+                    "a device-side wait gave up (code %d); results of the "
+                    "affected kernel are invalid", v);
+  }
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_sync(tfjs_cuda_ctx* ctx) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_flag, ctx->d_flag, sizeof(int),
+                                cudaMemcpyDeviceToHost, ctx->stream));
+  CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return report_flag(ctx);
+}
+
+int tfjs_cuda_read_async(tfjs_cuda_ctx* ctx, int32_t id, void* host,
+                         uint64_t nbytes) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  Buffer* b;
+  int rc = ctx_get(ctx, id, nbytes, "read", &b);
+  if (rc) return rc;
+  if (nbytes == 0) return TFJS_CUDA_OK;
+  if (!host) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "read: null host pointer");
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaMemcpyAsync(host, b->ptr, nbytes, cudaMemcpyDeviceToHost,
+                                ctx->stream));
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_read(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes) {
+  int rc = tfjs_cuda_read_async(ctx, id, host, nbytes);
+  if (rc) return rc;
+  return tfjs_cuda_sync(ctx);
+}
+
+int tfjs_cuda_size_of(tfjs_cuda_ctx* ctx, int32_t id, uint64_t* out_nbytes) {
+  if (!ctx || !out_nbytes) return TFJS_CUDA_INVALID_ARG;
+  Buffer* b = ctx_buf(ctx, id);
+  if (!b) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "size_of: unknown tensor id %d", id);
+  *out_nbytes = b->bytes;
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_device_ptr(tfjs_cuda_ctx* ctx, int32_t id, void** out_ptr) {
+  if (!ctx || !out_ptr) return TFJS_CUDA_INVALID_ARG;
+  Buffer* b = ctx_buf(ctx, id);
+  if (!b) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "device_ptr: unknown tensor id %d", id);
+  *out_ptr = b->ptr;
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_memory(tfjs_cuda_ctx* ctx, uint64_t* bytes_in_use,
+                     uint64_t* bytes_reserved, uint64_t* high_water,
+                     uint64_t* num_buffers) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (bytes_in_use) *bytes_in_use = ctx->in_use;
+  if (high_water) *high_water = ctx->high_water;
+  if (num_buffers) *num_buffers = ctx->n_live;
+  if (bytes_reserved) {
+    uint64_t r = 0;
+    cudaSetDevice(ctx->device);
+    CUDA_TRY(ctx, cudaMemPoolGetAttribute(ctx->pool,
+                                          cudaMemPoolAttrReservedMemCurrent, &r));
+    *bytes_reserved = r;
+  }
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_host_alloc(tfjs_cuda_ctx* ctx, uint64_t nbytes, void** out_ptr) {
+  if (!ctx || !out_ptr) return TFJS_CUDA_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaMallocHost(out_ptr, nbytes ? nbytes : 1));
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_host_free(tfjs_cuda_ctx* ctx, void* ptr) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaFreeHost(ptr));
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_time_begin(tfjs_cuda_ctx* ctx) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_time_end(tfjs_cuda_ctx* ctx, float* out_kernel_ms) {
+  if (!ctx || !out_kernel_ms) return TFJS_CUDA_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+  CUDA_TRY(ctx, cudaEventSynchronize(ctx->ev1));
+  CUDA_TRY(ctx, cudaEventElapsedTime(out_kernel_ms, ctx->ev0, ctx->ev1));
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_set_math_mode(tfjs_cuda_ctx* ctx, int mode) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (mode != TFJS_CUDA_MATH_TF32 && mode != TFJS_CUDA_MATH_FP32)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "unknown math mode %d", mode);
+  ctx->math_mode = mode;
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_launch_count(tfjs_cuda_ctx* ctx, uint64_t* out_launches) {
+  if (!ctx || !out_launches) return TFJS_CUDA_INVALID_ARG;
+  *out_launches = ctx->launches;
+  return TFJS_CUDA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+"""Weight (de)coding for graph models.
+
+`decode_weights` is the drop-in for `io.decodeWeights`
+(tfjs-core/src/io/io_utils.ts:119-135, :185-292): GraphModel receives the io
+namespace as a constructor argument and calls `this.io.decodeWeights`
+(tfjs-converter/src/executor/graph_model.ts:104-107, :177), so a backend can
+supply one that leaves uint8 / uint16 affine-quantised weights quantised on the
+way to the GPU and dequantises them there, once, at load time.
+
+`quantize_weights` restates the converter's affine quantisation
+(tfjs-converter/python/tensorflowjs/quantization.py:93-146, :175-216) for the
+synthetic model generators; tests pin it against fixtures produced by importing
+the reference module.
+"""
+from ctypes import c_void_p
+
+import numpy as np
+
+from . import _cabi
+from .backend import NP_DTYPES, DataId, TensorInfo, _Record, size_from_shape
+
+DTYPE_VALUE_SIZE_MAP = {"float32": 4, "float16": 2, "int32": 4, "uint16": 2, "uint8": 1,
+                        "bool": 1, "complex64": 8}
+
+
+def dequantize_to_device(backend, q, scale, min_val, shape, dtype):
+    """Uploads quantised bytes and dequantises them on the device.
+    values[i] = q[i] * scale + min, rounded as io_utils.ts:221-227 (float32) or
+    :243-247 (int32, Math.round) does."""
+    q = np.ascontiguousarray(q)
+    if q.dtype not in (np.uint8, np.uint16):
+        raise ValueError("Unsupported quantization dtype %s" % q.dtype)
+    if dtype not in ("float32", "int32"):
+        raise ValueError("Unsupported quantization type %s for weight type %s." %
+                         (q.dtype, dtype))
+    n = size_from_shape(shape)
+    if q.size != n:
+        raise ValueError("dequantize: %d quantised values for shape %s" % (q.size, list(shape)))
+    q_id = backend._alloc(q.nbytes)
+    out = backend.make_output(shape, dtype)
+    try:
+        if q.nbytes:
+            backend.check(backend.lib.tfjs_cuda_write(backend.ctx, q_id,
+                                                      q.ctypes.data_as(c_void_p), q.nbytes))
+        backend.check(backend.lib.tfjs_cuda_dequantize(
+            backend.ctx, q.dtype.itemsize, _cabi.DTYPES[dtype], q_id, float(scale),
+            float(min_val), n, backend.device_id(out.dataId)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    finally:
+        backend.check(backend.lib.tfjs_cuda_free(backend.ctx, q_id))
+    return out
+
+
+def decode_weights(engine, weight_data, specs):
+    """name -> Tensor for every manifest entry, in manifest order
+    (io_utils.ts:119-135).  `weight_data` is the concatenated little-endian
+    buffer; `specs` are WeightsManifestEntry dicts (tfjs-core/src/io/types.ts:76-110)."""
+    buf = memoryview(weight_data)
+    out = {}
+    offset = 0
+    for spec in specs:
+        name, dtype, shape = spec["name"], spec["dtype"], spec["shape"]
+        size = size_from_shape(shape)
+        quant = spec.get("quantization")
+        if quant is not None:
+            qd = quant["dtype"]
+            if qd in ("uint8", "uint16"):
+                if "min" not in quant or "scale" not in quant:
+                    raise ValueError("Weight %s with quantization %s doesn't have "
+                                     "corresponding metadata min and scale." % (name, qd))
+            elif qd == "float16":
+                if dtype != "float32":
+                    raise ValueError("Weight %s is quantized with %s which only supports "
+                                     "weights of type float32 not %s." % (name, qd, dtype))
+            else:
+                raise ValueError("Weight %s has unknown quantization dtype %s. Supported "
+                                 "quantization dtypes are: 'uint8', 'uint16', and 'float16'."
+                                 % (name, qd))
+            nbytes = size * DTYPE_VALUE_SIZE_MAP[qd]
+            raw = np.frombuffer(buf[offset:offset + nbytes], dtype=np.dtype(qd))
+            offset += nbytes
+            if qd == "float16":
+                t = engine.make_tensor(raw.astype(np.float32), shape, "float32")
+            else:
+                if dtype not in ("float32", "int32"):
+                    raise ValueError("Unsupported dtype in weight '%s': %s" % (name, dtype))
+                engine.ready()
+                info = dequantize_to_device(engine.backend, raw, quant["scale"], quant["min"],
+                                            shape, dtype)
+                t = engine.make_tensor_from_info(info)
+        elif dtype == "string":
+            raise ValueError("string weights are not supported by the CUDA backend")
+        else:
+            if dtype not in ("float32", "int32", "bool"):
+                raise ValueError("Unsupported dtype in weight '%s': %s" % (name, dtype))
+            nbytes = size * DTYPE_VALUE_SIZE_MAP[dtype]
+            raw = np.frombuffer(buf[offset:offset + nbytes], dtype=NP_DTYPES[dtype])
+            offset += nbytes
+            t = engine.make_tensor(raw, shape, dtype)
+        out[name] = t
+    return out
+
+
+# ------------------------------------------------------------ converter side --
+def _affine_range(min_val, max_val, qdtype):
+    """quantization.py:175-216: nudge the range so that 0.0 maps to an integer."""
+    quant_max = np.iinfo(qdtype).max
+    scale = (max_val - min_val) / quant_max
+    if min_val <= 0 <= max_val:
+        nudged_zero = np.round((0 - min_val) / scale)
+        nudged_min = -nudged_zero * scale
+        nudged_max = quant_max * scale + nudged_min
+    else:
+        nudged_min, nudged_max = min_val, max_val
+    return scale, nudged_min, nudged_max
+
+
+def quantize_weights(data, qdtype):
+    """quantization.py:93-146 for uint8 / uint16: returns (quantised, {min, scale})."""
+    qdtype = np.dtype(qdtype).type
+    if qdtype not in (np.uint8, np.uint16):
+        raise ValueError("Invalid `quantization_dtype`: %r" % qdtype)
+    min_val = data.min().astype(np.float64)
+    max_val = data.max().astype(np.float64)
+    if min_val == max_val:
+        return np.zeros_like(data, dtype=qdtype), {"min": min_val, "scale": 1.0}
+    scale, min_val, max_val = _affine_range(min_val, max_val, qdtype)
+    q = np.round((data.clip(min_val, max_val) - min_val) / scale).astype(qdtype)
+    return q, {"min": min_val, "scale": scale}
+
+
+def encode_weights(named, quantize=None):
+    """Concatenated weight bytes plus manifest entries, in order
+    (tfjs-core/src/io/io_utils.ts:52-101 / write_weights.py).  `quantize` is None,
+    'uint8' or 'uint16' and applies to float32 tensors with more than one element."""
+    specs, chunks = [], []
+    for name, arr in named:
+        arr = np.asarray(arr)
+        if arr.dtype == np.bool_:
+            dtype, raw = "bool", arr.astype(np.uint8)
+        elif np.issubdtype(arr.dtype, np.integer):
+            dtype, raw = "int32", arr.astype(np.int32)
+        else:
+            dtype, raw = "float32", arr.astype(np.float32)
+        spec = {"name": name, "shape": [int(s) for s in arr.shape], "dtype": dtype}
+        if quantize and dtype == "float32" and arr.size > 1 and arr.ndim > 1:
+            q, meta = quantize_weights(raw, np.dtype(quantize))
+            spec["quantization"] = {"dtype": quantize, "min": float(meta["min"]),
+                                    "scale": float(meta["scale"])}
+            raw = q
+        specs.append(spec)
+        chunks.append(np.ascontiguousarray(raw).tobytes())
+    return b"".join(chunks), specs

@@ -1,0 +1,178 @@
+"""Unary and broadcasting binary kernels, FusedBatchNorm, Cast.
+
+Reference: tfjs-backend-cpu/src/utils/unary_utils.ts:34-79, binary_utils.ts:38-129,
+binary_impl.ts:25-69 and the per-op files (Add.ts, Relu.ts, Erf.ts, ...);
+BatchNorm.ts:23-90; Cast.ts:27-95.
+"""
+from .. import _cabi
+from ..backend import TensorInfo
+from ..kernel_registry import KernelConfig
+from ..util import assert_and_get_broadcast_shape, size_from_shape
+from .common import BACKEND, assert_not_complex, dev, view
+
+_I64 = _cabi.i64
+
+
+def upcast_type(a, b):
+    """tfjs-core/src/types.ts upcastType for the dtypes handled here."""
+    order = {"bool": 0, "int32": 1, "float32": 2}
+    return a if order[a] >= order[b] else b
+
+
+def cast_impl(backend, x, dtype):
+    """Cast.ts:27-95: widening casts are zero-copy in the reference; here only the
+    same-dtype and bool->bool cases share the buffer because int32 and float32
+    have different device representations."""
+    if dtype not in _cabi.DTYPES:
+        raise ValueError("Error in Cast: failed to cast %s to %s" % (x.dtype, dtype))
+    if x.dtype == dtype:
+        return view(backend, x, x.shape)
+    out = backend.make_output(x.shape, dtype)
+    try:
+        backend.check(backend.lib.tfjs_cuda_cast(
+            backend.ctx, _cabi.DTYPES[x.dtype], _cabi.DTYPES[dtype], dev(backend, x),
+            size_from_shape(x.shape), dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    return out
+
+
+def unary_impl(backend, op, x, p0=0.0, p1=0.0):
+    assert_not_complex(x, op)
+    tmp = None
+    if x.dtype != "float32":
+        tmp = cast_impl(backend, x, "float32")
+        x = tmp
+    out = backend.make_output(x.shape, "float32")
+    try:
+        backend.check(backend.lib.tfjs_cuda_unary(
+            backend.ctx, _cabi.UNARY_OPS[op], float(p0), float(p1), dev(backend, x),
+            size_from_shape(x.shape), dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    finally:
+        if tmp is not None:
+            backend.disposeData(tmp.dataId)
+    return out
+
+
+def binary_impl(backend, op, a, b, dtype=None):
+    """binary_utils.ts:38-129: operands are upcast to a common dtype first."""
+    assert_not_complex([a, b], op)
+    out_dtype = dtype or upcast_type(a.dtype, b.dtype)
+    if out_dtype == "bool":
+        out_dtype = "int32"
+    if op in ("RealDiv", "Pow", "SquaredDifference", "Prelu") and out_dtype != "float32":
+        out_dtype = "float32" if op in ("RealDiv", "Prelu") else out_dtype
+    tmp = []
+    if a.dtype != out_dtype:
+        a = cast_impl(backend, a, out_dtype)
+        tmp.append(a)
+    if b.dtype != out_dtype:
+        b = cast_impl(backend, b, out_dtype)
+        tmp.append(b)
+    out_shape = assert_and_get_broadcast_shape(a.shape, b.shape)
+    rank = len(out_shape)
+    if rank > 6:
+        raise ValueError("%s: rank %d is not supported by the CUDA backend" % (op, rank))
+    pad = lambda s: [1] * (rank - len(s)) + list(s)
+    out = backend.make_output(out_shape, out_dtype)
+    try:
+        backend.check(backend.lib.tfjs_cuda_binary(
+            backend.ctx, _cabi.BINARY_OPS[op], _cabi.DTYPES[out_dtype], rank,
+            dev(backend, a), _I64(pad(a.shape)), dev(backend, b), _I64(pad(b.shape)),
+            dev(backend, out), _I64(out_shape)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    finally:
+        for t in tmp:
+            backend.disposeData(t.dataId)
+    return out
+
+
+def apply_activation(backend, x, activation, prelu=None, alpha=None):
+    """tfjs-backend-cpu/src/utils/fused_utils.ts:29-49."""
+    if activation in (None, "linear"):
+        return view(backend, x, x.shape)
+    if activation == "relu":
+        return unary_impl(backend, "Relu", x)
+    if activation == "elu":
+        return unary_impl(backend, "Elu", x)
+    if activation == "relu6":
+        return unary_impl(backend, "Relu6", x)
+    if activation == "prelu":
+        return binary_impl(backend, "Prelu", x, prelu)
+    if activation == "leakyrelu":
+        return unary_impl(backend, "LeakyRelu", x, 0.2 if alpha is None else alpha)
+    if activation == "sigmoid":
+        return unary_impl(backend, "Sigmoid", x)
+    raise ValueError("Activation %s has not been implemented for the CUDA backend." %
+                     activation)
+
+
+def _unary_config(name, p_from_attrs=None):
+    def func(args):
+        x = args["inputs"]["x"]
+        p0, p1 = p_from_attrs(args["attrs"]) if p_from_attrs else (0.0, 0.0)
+        return unary_impl(args["backend"], name, x, p0, p1)
+    return KernelConfig(name, BACKEND, func)
+
+
+def _binary_config(name):
+    def func(args):
+        i = args["inputs"]
+        if name == "Prelu":
+            return binary_impl(args["backend"], name, i["x"], i["alpha"])
+        return binary_impl(args["backend"], name, i["a"], i["b"])
+    return KernelConfig(name, BACKEND, func)
+
+
+def relu_int_aware(name):
+    """Relu / Relu6 / Abs / Neg / Square on int32 keep int32 in the reference; the
+    device kernels are float32, so int32 goes through Maximum/Minimum instead."""
+    return _unary_config(name)
+
+
+def fused_batch_norm(args):
+    """BatchNorm.ts:23-90."""
+    i, a, backend = args["inputs"], args["attrs"], args["backend"]
+    x, mean, var = i["x"], i["mean"], i["variance"]
+    scale, offset = i.get("scale"), i.get("offset")
+    for t, nm in ((mean, "mean"), (var, "variance")):
+        if len(t.shape) != 1 and list(t.shape) != list(x.shape)[-len(t.shape):]:
+            pass  # the reference only asserts rank equality between parameters
+    eps = a.get("varianceEpsilon")
+    if eps is None:
+        eps = 0.001
+    n = size_from_shape(x.shape)
+    out = backend.make_output(x.shape, "float32")
+    try:
+        backend.check(backend.lib.tfjs_cuda_batchnorm(
+            backend.ctx, dev(backend, x), n, dev(backend, mean), size_from_shape(mean.shape),
+            dev(backend, var), size_from_shape(var.shape),
+            dev(backend, scale), size_from_shape(scale.shape) if scale is not None else 0,
+            dev(backend, offset), size_from_shape(offset.shape) if offset is not None else 0,
+            float(eps), dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    return out
+
+
+def cast(args):
+    return cast_impl(args["backend"], args["inputs"]["x"], args["attrs"]["dtype"])
+
+
+CONFIGS = (
+    [_unary_config(n) for n in ("Relu", "Relu6", "Elu", "Sigmoid", "Exp", "Sqrt", "Rsqrt",
+                                "Square", "Tanh", "Neg", "Erf", "Abs", "Log")] +
+    [_unary_config("LeakyRelu", lambda a: (a.get("alpha", 0.2), 0.0)),
+     _unary_config("ClipByValue", lambda a: (a["clipValueMin"], a["clipValueMax"]))] +
+    [_binary_config(n) for n in ("Add", "Sub", "Multiply", "RealDiv", "Maximum", "Minimum",
+                                 "Pow", "SquaredDifference", "Prelu")] +
+    [KernelConfig("FusedBatchNorm", BACKEND, fused_batch_norm),
+     KernelConfig("Cast", BACKEND, cast)]
+)

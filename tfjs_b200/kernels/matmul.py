@@ -1,0 +1,94 @@
+"""_FusedMatMul and BatchMatMul.
+
+Reference kernels: tfjs-backend-cpu/src/kernels/_FusedMatMul.ts:26-62 and
+BatchMatMul.ts:25-133 (any rank >= 2, outer dimensions broadcast, operand
+batches wrap with `bi % batchDim`).
+"""
+from ctypes import byref
+
+from .. import _cabi
+from ..kernel_registry import KernelConfig
+from ..util import assert_and_get_broadcast_shape, size_from_shape
+from .common import BACKEND, assert_not_complex, dev, per_channel_len, require_float32
+from . import elementwise
+
+
+def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activation, alpha):
+    assert_not_complex([a, b], "matMul")
+    require_float32(a, "matMul")
+    require_float32(b, "matMul")
+    a_rank, b_rank = len(a.shape), len(b.shape)
+    if a_rank < 2 or b_rank < 2:
+        raise ValueError("Error in matMul: inputs must have at least rank 2, got ranks "
+                         "%d and %d." % (a_rank, b_rank))
+    inner_a = a.shape[a_rank - 2] if transpose_a else a.shape[a_rank - 1]
+    inner_b = b.shape[b_rank - 1] if transpose_b else b.shape[b_rank - 2]
+    outer_a = a.shape[a_rank - 1] if transpose_a else a.shape[a_rank - 2]
+    outer_b = b.shape[b_rank - 2] if transpose_b else b.shape[b_rank - 1]
+    outer_dims_a, outer_dims_b = a.shape[:-2], b.shape[:-2]
+    batch_a, batch_b = size_from_shape(outer_dims_a), size_from_shape(outer_dims_b)
+    out_outer = assert_and_get_broadcast_shape(outer_dims_a, outer_dims_b)
+    out_shape = out_outer + [outer_a, outer_b]
+    if inner_a != inner_b:
+        raise ValueError(
+            "Error in matMul: inner shapes (%d) and (%d) of Tensors with shapes %s and %s "
+            "and transposeA=%s and transposeB=%s must match." %
+            (inner_a, inner_b, ",".join(map(str, a.shape)), ",".join(map(str, b.shape)),
+             str(bool(transpose_a)).lower(), str(bool(transpose_b)).lower()))
+    batch = max(batch_a, batch_b)
+    if batch_a == 0 or batch_b == 0 or batch % max(batch_a, 1) or batch % max(batch_b, 1):
+        if batch_a != 0 and batch_b != 0:
+            raise ValueError("matMul: the CUDA backend needs batch dims where one divides "
+                             "the other, got %d and %d" % (batch_a, batch_b))
+    bias_len = per_channel_len(bias, outer_b)
+    prelu_len = per_channel_len(prelu, outer_b) if activation == "prelu" else 0
+    fuse_bias = bias_len is not None
+    fuse_act = fuse_bias and (activation != "prelu" or prelu_len is not None)
+    out = backend.make_output(out_shape, "float32")
+    if size_from_shape(out_shape) and batch_a and batch_b:
+        p = _cabi.MatMulParams()
+        p.batch_a, p.batch_b = batch_a, batch_b
+        p.m, p.n, p.k = outer_a, outer_b, inner_a
+        p.transpose_a, p.transpose_b = int(bool(transpose_a)), int(bool(transpose_b))
+        p.activation = _cabi.ACTIVATIONS[activation if fuse_act else "linear"]
+        p.bias_len = bias_len if fuse_bias else 0
+        p.prelu_len = (prelu_len or 0) if fuse_act else 0
+        p.leakyrelu_alpha = 0.2 if alpha is None else float(alpha)
+        try:
+            backend.check(backend.lib.tfjs_cuda_fused_matmul(
+                backend.ctx, byref(p), dev(backend, a), dev(backend, b),
+                dev(backend, bias) if fuse_bias and bias is not None else 0,
+                dev(backend, prelu) if fuse_act and activation == "prelu" else 0,
+                dev(backend, out)))
+        except Exception:
+            backend.disposeData(out.dataId)
+            raise
+    if not fuse_bias:
+        added = elementwise.binary_impl(backend, "Add", out, bias)
+        backend.disposeData(out.dataId)
+        out = added
+    if not fuse_act:
+        act = elementwise.apply_activation(backend, out, activation, prelu, alpha)
+        backend.disposeData(out.dataId)
+        out = act
+    return out
+
+
+def fused_matmul(args):
+    i, a, b = args["inputs"], args["attrs"], args["backend"]
+    return _matmul_impl(b, i["a"], i["b"], a.get("transposeA", False),
+                        a.get("transposeB", False), i.get("bias"),
+                        i.get("preluActivationWeights"), a.get("activation") or "linear",
+                        a.get("leakyreluAlpha"))
+
+
+def batch_matmul(args):
+    i, a, b = args["inputs"], args["attrs"], args["backend"]
+    return _matmul_impl(b, i["a"], i["b"], a.get("transposeA", False),
+                        a.get("transposeB", False), None, None, "linear", None)
+
+
+CONFIGS = [
+    KernelConfig("_FusedMatMul", BACKEND, fused_matmul),
+    KernelConfig("BatchMatMul", BACKEND, batch_matmul),
+]

@@ -1,0 +1,144 @@
+"""Softmax, Sum, Mean, Max, ArgMax.
+
+Reference: tfjs-backend-cpu/src/kernels/Softmax.ts:29-77, Sum.ts:28-90,
+Mean.ts:25-53, Max.ts:28-72, ArgMax.ts:24-71.  The reference transposes the
+reduced axes innermost; here contiguous reduced axes are reduced in place over an
+[outer, reduce, inner] view and only a non-contiguous set is transposed first.
+"""
+from .. import _cabi
+from ..kernel_registry import KernelConfig
+from ..util import (compute_out_and_reduce_shapes, expand_shape_to_keep_dim,
+                    get_axes_permutation, get_inner_most_axes, parse_axis_param,
+                    size_from_shape)
+from .common import BACKEND, assert_not_complex, dev
+from . import elementwise, movement
+
+
+def _collapse(backend, x, axes):
+    """Returns (tensor, outer, reduce, inner, temporaries) with the reduced axes
+    forming one contiguous run."""
+    rank = len(x.shape)
+    axes = sorted(set(axes))
+    tmp = []
+    contiguous = all(axes[i] + 1 == axes[i + 1] for i in range(len(axes) - 1))
+    if not contiguous:
+        perm = get_axes_permutation(axes, rank)
+        x = movement.transpose_impl(backend, x, perm)
+        tmp.append(x)
+        axes = get_inner_most_axes(len(axes), rank)
+    if not axes:
+        return x, size_from_shape(x.shape), 1, 1, tmp
+    outer = size_from_shape(x.shape[:axes[0]])
+    red = size_from_shape(x.shape[axes[0]:axes[-1] + 1])
+    inner = size_from_shape(x.shape[axes[-1] + 1:])
+    return x, outer, red, inner, tmp
+
+
+def reduce_impl(backend, op, x, axis, keep_dims):
+    assert_not_complex(x, op.lower())
+    axes = parse_axis_param(axis, x.shape)
+    out_shape, _ = compute_out_and_reduce_shapes(x.shape, axes)
+    tmp = []
+    if x.dtype != "float32":
+        x = elementwise.cast_impl(backend, x, "float32")
+        tmp.append(x)
+    xt, outer, red, inner, t2 = _collapse(backend, x, axes)
+    tmp += t2
+    shape = expand_shape_to_keep_dim(out_shape, sorted(axes)) if keep_dims else out_shape
+    out = backend.make_output(shape, "float32")
+    try:
+        backend.check(backend.lib.tfjs_cuda_reduce(
+            backend.ctx, _cabi.REDUCE_OPS[op], dev(backend, xt), outer, red, inner,
+            dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    finally:
+        for t in tmp:
+            backend.disposeData(t.dataId)
+    return out
+
+
+def _sum(args):
+    a = args["attrs"]
+    x = args["inputs"]["x"]
+    out = reduce_impl(args["backend"], "Sum", x, a.get("axis"), a.get("keepDims", False))
+    if x.dtype in ("int32", "bool"):
+        # Sum.ts:57: the result dtype is upcast(x.dtype, 'int32').
+        r = elementwise.cast_impl(args["backend"], out, "int32")
+        args["backend"].disposeData(out.dataId)
+        return r
+    return out
+
+
+def _mean(args):
+    a = args["attrs"]
+    return reduce_impl(args["backend"], "Mean", args["inputs"]["x"], a.get("axis"),
+                       a.get("keepDims", False))
+
+
+def _max(args):
+    a = args["attrs"]
+    x = args["inputs"]["x"]
+    out = reduce_impl(args["backend"], "Max", x, a.get("reductionIndices"),
+                      a.get("keepDims", False))
+    if x.dtype == "int32":
+        r = elementwise.cast_impl(args["backend"], out, "int32")
+        args["backend"].disposeData(out.dataId)
+        return r
+    return out
+
+
+def _argmax(args):
+    backend, x = args["backend"], args["inputs"]["x"]
+    assert_not_complex(x, "argMax")
+    axes = parse_axis_param(args["attrs"].get("axis", 0), x.shape)[:1]
+    out_shape, _ = compute_out_and_reduce_shapes(x.shape, axes)
+    tmp = []
+    if x.dtype != "float32":
+        x = elementwise.cast_impl(backend, x, "float32")
+        tmp.append(x)
+    outer = size_from_shape(x.shape[:axes[0]])
+    red = x.shape[axes[0]]
+    inner = size_from_shape(x.shape[axes[0] + 1:])
+    out = backend.make_output(out_shape, "int32")
+    try:
+        backend.check(backend.lib.tfjs_cuda_argmax(backend.ctx, dev(backend, x), outer, red,
+                                                   inner, dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    finally:
+        for t in tmp:
+            backend.disposeData(t.dataId)
+    return out
+
+
+def _softmax(args):
+    backend, logits = args["backend"], args["inputs"]["logits"]
+    dim = args["attrs"].get("dim", -1)
+    rank = len(logits.shape)
+    if dim == -1:
+        dim = rank - 1
+    if dim != rank - 1:
+        raise ValueError("Softmax along a non-last dimension is not yet supported. "
+                         "Logits was rank %d and dim was %d" % (rank, dim))
+    cols = logits.shape[-1]
+    rows = size_from_shape(logits.shape[:-1])
+    out = backend.make_output(logits.shape, "float32")
+    try:
+        backend.check(backend.lib.tfjs_cuda_softmax(backend.ctx, dev(backend, logits), rows,
+                                                    cols, dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    return out
+
+
+CONFIGS = [
+    KernelConfig("Sum", BACKEND, _sum),
+    KernelConfig("Mean", BACKEND, _mean),
+    KernelConfig("Max", BACKEND, _max),
+    KernelConfig("ArgMax", BACKEND, _argmax),
+    KernelConfig("Softmax", BACKEND, _softmax),
+]
