@@ -150,11 +150,9 @@ def find_specs(src):
         if arrow < 0:
             continue
         name_part = inner[:arrow]
-        name = " ".join(re.findall(r"'((?:[^'\\]|\\.)*)'|\"((?:[^\"\\]|\\.)*)\"", name_part)[0]) \
-            if re.search(r"['\"]", name_part) else "?"
-        names = re.findall(r"'((?:[^'\\]|\\.)*)'", name_part.rsplit("async", 1)[0])
-        if names:
-            name = "".join(names)
+        head = name_part.rsplit("async", 1)[0]
+        names = re.findall("'([^']*)'|\"([^\"]*)\"", head)
+        name = "".join(a or b for a, b in names) or "?"
         brace = inner.find("{", arrow)
         if brace < 0:
             continue
@@ -341,6 +339,10 @@ def tr_stmt(s):
             return "%s = %s" % (lhs, tr_expr(rhs))
         name = re.match(r"[A-Za-z_]\w*", lhs).group(0)
         return "%s = %s" % (name, tr_expr(rhs))
+    m = re.match(r"^return\b\s*(.*)$", s)
+    if m:
+        e = tr_expr(m.group(1)) if m.group(1) else "None"
+        return "return __obj(%s)" % e if e.startswith("dict(") else "return %s" % e
     m = re.match(r"^expect\((.*)\)\.toEqual\((.*)\)$", s)
     if m:
         return "__expect_equal(%s, %s)" % (tr_expr(m.group(1)), tr_expr(m.group(2)))
@@ -532,6 +534,7 @@ def make_tf(rec):
     tf.zeros = lambda shape, dtype="float32": mk(np.zeros(shape), shape, dtype)
     tf.ones = lambda shape, dtype="float32": mk(np.ones(shape), shape, dtype)
     tf.fill = lambda shape, v, dtype="float32": mk(np.full(shape, v), shape, dtype)
+    tf.range = lambda a, b, step=1, dtype="float32": mk(np.arange(a, b, step), None, dtype)
 
     def fused_conv(opname):
         def f(d):
@@ -704,14 +707,38 @@ def make_tf(rec):
     return tf
 
 
+def file_helpers(src):
+    """Python source for the file-level `function name(args) {...}` helpers."""
+    out = []
+    for m in re.finditer(r"(?m)^function\s+(\w+)\s*\(([^)]*)\)\s*(?::[^{]+)?\{", src):
+        brace = m.end() - 1
+        try:
+            close = match_close(src, brace)
+            params = [re.match(r"\s*(\w+)", p).group(1) for p in m.group(2).split(",") if p.strip()]
+            body = tr_block(src[brace + 1:close], 1)
+        except (Skip, AttributeError):
+            continue
+        out.append("def %s(%s):\n%s" % (m.group(1), ", ".join(params), "\n".join(body or ["    pass"])))
+    return "\n".join(out)
+
+
 def generate_case_inputs(total_tensor, total_filter):
     """fused_conv2d_test.ts:22-35 / conv2d_test.ts helper of the same name."""
     inp = [i * 0.001 - total_tensor * 0.001 / 2 for i in range(int(total_tensor))]
     filt = [i * 0.001 * (-1 if i % 2 == 0 else 1) for i in range(int(total_filter))]
-    return {"input": inp, "filter": filt}
+    class CaseInputs(object):
+        pass
+    out = CaseInputs()
+    out.input, out.filter = inp, filt
+    return out
 
 
-def run_spec(py_lines, rec, goldens_out, meta):
+class Obj(object):
+    def __init__(self, d):
+        self.__dict__.update(d)
+
+
+def run_spec(py_lines, rec, goldens_out, meta, helpers=""):
     checks = []
 
     def close(actual, expected, eps=None):
@@ -728,7 +755,11 @@ def run_spec(py_lines, rec, goldens_out, meta):
            "__expect_equal": expect_equal, "__nan": float("nan"), "__inf": float("inf"),
            "__math": math, "__typed": lambda v: list(v) if not isinstance(v, (int, float)) else [0] * int(v),
            "__newarray": lambda n=0: [None] * int(n), "generateCaseInputs": generate_case_inputs,
-           "dict": dict, "len": len, "range": range, "int": int}
+           "dict": dict, "len": len, "range": range, "int": int,
+           "MATMUL_SHARED_DIM_THRESHOLD": 1000,  # mat_mul_test.ts:24
+           "__obj": Obj}
+    if helpers:
+        exec(helpers, env)
     exec("\n".join(py_lines), env)
     for t, expected in checks:
         if t.case is None:
@@ -771,6 +802,7 @@ def main(ref_root, out_path):
             continue
         src = strip_comments(open(path).read())
         stats = {"specs": 0, "extracted_specs": 0, "cases": 0, "skipped": {}}
+        helpers = file_helpers(src)
         for name, line, body in find_specs(src):
             stats["specs"] += 1
             before = len(goldens)
@@ -780,7 +812,8 @@ def main(ref_root, out_path):
                 if "toThrow" in body or "rejects" in body:
                     raise Skip("error-path spec")
                 py = tr_block(body)
-                run_spec(py, Recorder(), goldens, {"file": rel, "line": line, "spec": name})
+                run_spec(py, Recorder(), goldens, {"file": rel, "line": line, "spec": name},
+                         helpers)
             except Skip as e:
                 del goldens[before:]
                 key = str(e).split(":")[0][:40]
