@@ -105,6 +105,12 @@ int tfjs_cuda_host_free(tfjs_cuda_ctx* ctx, void* ptr);
 /* backend.time() (tfjs-core/src/engine.ts:1235-1240): CUDA events on the stream. */
 int tfjs_cuda_time_begin(tfjs_cuda_ctx* ctx);
 int tfjs_cuda_time_end(tfjs_cuda_ctx* ctx, float* out_kernel_ms);
+/* Per-kernel timing for tf.profile (tfjs-core/src/profiler.ts:39-79 wraps every
+ * kernel in backend.time): record numbered events on the stream, then ask for the
+ * elapsed time between two of them (blocks until the later one has happened). */
+int tfjs_cuda_event_record(tfjs_cuda_ctx* ctx, int32_t slot);
+int tfjs_cuda_event_elapsed(tfjs_cuda_ctx* ctx, int32_t slot_begin, int32_t slot_end,
+                            float* out_ms);
 int tfjs_cuda_set_math_mode(tfjs_cuda_ctx* ctx, int mode);
 /* Number of this library's kernels launched on the context so far. */
 int tfjs_cuda_launch_count(tfjs_cuda_ctx* ctx, uint64_t* out_launches);

@@ -110,6 +110,16 @@ def run_cuda(case):
         made.append(t)
         return t
 
+    def D(v):
+        """A tensor produced by a device kernel (not a host write), so that paths
+        reserved for activations, not weights, are taken."""
+        t = T(v)
+        one = T(np.ones((), np.float32))
+        out = ops.mul(t, one)
+        made.append(out)
+        return out
+
+    dev_in = set(case.get("device_inputs", ()))
     try:
         if op in ("fused_conv2d", "fused_depthwise_conv2d"):
             fn = ops.fused_conv2d if op == "fused_conv2d" else ops.fused_depthwise_conv2d
@@ -124,10 +134,11 @@ def run_cuda(case):
                      a.get("dataFormat", "NHWC"), a.get("dilations", [1, 1]) or [1, 1],
                      a.get("dimRoundingMode"))
         elif op == "mat_mul":
-            out = ops.mat_mul(T(i["a"]), T(i["b"]), a.get("transposeA", False),
-                              a.get("transposeB", False))
+            out = ops.mat_mul(T(i["a"]), (D if "b" in dev_in else T)(i["b"]),
+                              a.get("transposeA", False), a.get("transposeB", False))
         elif op == "fused_mat_mul":
-            out = ops.fused_mat_mul(T(i["a"]), T(i["b"]), a.get("transposeA", False),
+            out = ops.fused_mat_mul(T(i["a"]), (D if "b" in dev_in else T)(i["b"]),
+                                    a.get("transposeA", False),
                                     a.get("transposeB", False), T(i.get("bias")),
                                     a.get("activation", "linear") or "linear",
                                     T(i.get("preluActivationWeights")),

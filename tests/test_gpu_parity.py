@@ -143,6 +143,16 @@ def test_matmul(cuda_engine, name, mode):
     assert err <= (TF32_TOL if mode == "tf32" else FP32_TOL), (name, mode, err)
 
 
+@pytest.mark.parametrize("name", ["cfg2b", "attn_pv", "attn_qk", "bcast_b", "rank4", "tall_m",
+                                  "dense_1280_1000", "k1000_n10"])
+def test_matmul_activation_b(cuda_engine, name):
+    """B produced on the device (an activation, not a weight): the tensor-core
+    kernel streams it as stored, MN-major or K-major, instead of a packed copy."""
+    case = dict(MM_CASES[name](), device_inputs=["b"])
+    err = rel_err(opcases.run_cuda(case), opcases.run_oracle(case))
+    assert err <= TF32_TOL, (name, err)
+
+
 def test_fused_matmul_cfg2a_rows(cuda_engine):
     """BASELINE config 2a at full size on the GPU; the oracle checks a sample of
     rows (every row of the product depends on one row of A only)."""

@@ -61,6 +61,8 @@ SIGNATURES = {
     "tfjs_cuda_host_free": (c_int, [_CTX, c_void_p]),
     "tfjs_cuda_time_begin": (c_int, [_CTX]),
     "tfjs_cuda_time_end": (c_int, [_CTX, POINTER(c_float)]),
+    "tfjs_cuda_event_record": (c_int, [_CTX, c_int32]),
+    "tfjs_cuda_event_elapsed": (c_int, [_CTX, c_int32, c_int32, POINTER(c_float)]),
     "tfjs_cuda_set_math_mode": (c_int, [_CTX, c_int]),
     "tfjs_cuda_launch_count": (c_int, [_CTX, POINTER(c_uint64)]),
     "tfjs_cuda_flush_l2": (c_int, [_CTX]),

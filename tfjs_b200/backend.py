@@ -232,6 +232,15 @@ class CudaBackend(object):
         self.check(self.lib.tfjs_cuda_time_end(self.ctx, byref(ms)))
         return {"kernelMs": ms.value, "wallMs": (_time.perf_counter() - t0) * 1e3}
 
+    def event_record(self, slot):
+        self.check(self.lib.tfjs_cuda_event_record(self.ctx, int(slot)))
+
+    def event_elapsed(self, slot_begin, slot_end):
+        ms = c_float()
+        self.check(self.lib.tfjs_cuda_event_elapsed(self.ctx, int(slot_begin), int(slot_end),
+                                                    byref(ms)))
+        return ms.value
+
     def timerAvailable(self):
         return True
 

@@ -46,6 +46,7 @@ struct tfjs_cuda_ctx {
   long long* d_bad_index = nullptr;
   long long* h_bad_index = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::vector<cudaEvent_t> prof_events;  // numbered events for per-kernel timing
   void* l2_scratch = nullptr;
   uint64_t l2_scratch_bytes = 0;
   // grow-only scratch for im2col / operand transposes

@@ -8,10 +8,10 @@
 //               allocation.
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (32 lanes x 32 columns per
 //               load), add the bias, apply the activation, store NHWC / row-major.
-//   warps 6-9   (convolution only) A gatherers: 16-byte cp.async copies of the
-//               im2col rows straight from the NHWC input, zero-filling taps that
-//               fall outside the image, written in the same swizzled layout TMA
-//               would produce.
+//   warps 6-9   (convolution only) A gatherers: 16-byte loads of the im2col rows
+//               straight from the NHWC input (zeros for taps outside the image),
+//               rounded to TF32 and stored in the same swizzled layout TMA would
+//               produce.
 // Two TMEM accumulators alternate so the epilogue of tile i overlaps the main
 // loop of tile i+1.  Every mbarrier wait is bounded: when it gives up the kernel
 // records a code in the context's error word and drains.
@@ -19,10 +19,12 @@
 // Operand formats.  A is K-major (rows of K contiguous floats).  B is either
 // K-major ([N][K]: transposed operands and packed weights) or MN-major ([K][N]
 // row-major, consumed directly through the MN-major shared-memory descriptor).
-// The tensor core reads the upper 19 bits of each fp32 word; weights are
-// rounded to TF32 when they are packed.
+// The tensor core reads the upper 19 bits of each fp32 word, so every operand
+// is rounded to TF32 before it reaches shared memory: by the TMA unit (TFLOAT32
+// tensor maps), by the gather warps, or when weights are packed.
 #include <cuda.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "gemm.h"
@@ -33,7 +35,6 @@ constexpr int BM = 128;
 constexpr int BK = 32;          // floats per K step = one 128-byte swizzle row
 constexpr int UMMA_K = 8;       // K of one tcgen05.mma.kind::tf32
 constexpr int A_STAGE_BYTES = BM * BK * 4;
-constexpr int GATHER_LAG = 2;   // cp.async groups in flight per gather thread
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 struct Tf32Args {
@@ -143,11 +144,13 @@ __device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
   return (uint64_t)((addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) |
          (1ull << 46) | (2ull << 61);
 }
-// MN-major: 32-float column blocks 4096 bytes apart (leading offset), 8-row K
-// groups 1024 bytes apart (stride offset).
+// MN-major 32-bit operands use the "128-byte swizzle, 32-byte atom" layout
+// (layout type 1; TMA swizzle mode 128B_ATOM_32B): rows of 32 contiguous floats
+// along N, 4-row K groups 512 bytes apart (stride offset), 32-float column
+// blocks 4096 bytes apart (leading offset).
 __device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
-  return (uint64_t)((addr >> 4) & 0x3fff) | (256ull << 16) | (64ull << 32) |
-         (1ull << 46) | (2ull << 61);
+  return (uint64_t)((addr >> 4) & 0x3fff) | (256ull << 16) | (32ull << 32) |
+         (1ull << 46) | (1ull << 61);
 }
 
 template <int BN>
@@ -337,69 +340,83 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
   } else if (A_GATHER) {
     // ----------------------------------------------------- im2col gatherers --
-    const int r = threadIdx.x - 192;  // row of the A tile owned by this thread
+    // Thread r owns row r of every A tile.  Each K step it reads 32 channels of
+    // one filter tap (8 x 16 bytes) into registers, rounds them to TF32
+    // (nearest-even, the rounding the TMA unit applies to the other operands) and
+    // stores them in the 128-byte-swizzled layout.  The loads of step i+1 are
+    // issued before the stores of step i, so two steps are in flight per thread.
+    const int r = threadIdx.x - 192;
     const ConvGeo& cv = g.conv;
+    const uint32_t row_off = (uint32_t)r * 128u;
+    const uint32_t sw = (uint32_t)(r & 7);
+    // iterator over (tile, k step) in issue order
+    int tile = blockIdx.x, ks = 0;
+    bool row_ok = false;
+    int b = 0, r_base = 0, c_base = 0;
+    auto enter_tile = [&]() {
+      const int mt = (tile / g.tiles_n) % g.tiles_m;
+      const int m = mt * BM + r;
+      row_ok = tile < g.total_tiles && m < g.M;
+      if (row_ok) {
+        const int ow = m % cv.out_w;
+        const int t = m / cv.out_w;
+        const int oh = t % cv.out_h;
+        b = t / cv.out_h;
+        r_base = oh * cv.s_h - cv.pad_t;
+        c_base = ow * cv.s_w - cv.pad_l;
+      }
+    };
+    auto load_step = [&](float4* v) {
+      const int tap = ks / g.chunks_per_tap;
+      const int cc = (ks - tap * g.chunks_per_tap) * BK;
+      const int fr = tap / cv.f_w, fc = tap - fr * cv.f_w;
+      const int ri = r_base + fr * cv.d_h;
+      const int ci = c_base + fc * cv.d_w;
+      const bool ok = row_ok && ri >= 0 && ri < cv.in_h && ci >= 0 && ci < cv.in_w;
+      const float* src = g.x + (((long long)b * cv.in_h + ri) * cv.in_w + ci) * cv.in_c + cc;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[j] = (ok && cc + j * 4 < cv.in_c) ? __ldg(reinterpret_cast<const float4*>(src) + j)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto advance = [&]() {
+      if (++ks == k_steps) {
+        ks = 0;
+        tile += gridDim.x;
+        enter_tile();
+      }
+    };
     int stage = 0;
     uint32_t phase = 0;
-    int sig_stage = 0;   // oldest stage whose copies are not yet published
-    int in_flight = 0;
-    bool alive = true;
-    for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x) {
-      const int rest = tile / g.tiles_n;
-      const int mt = rest % g.tiles_m;
-      const int m = mt * BM + r;
-      const bool row_ok = m < g.M;
-      int ow = 0, oh = 0, b = 0;
-      if (row_ok) {
-        ow = m % cv.out_w;
-        const int t = m / cv.out_w;
-        oh = t % cv.out_h;
-        b = t / cv.out_h;
-      }
-      const int r_base = oh * cv.s_h - cv.pad_t;
-      const int c_base = ow * cv.s_w - cv.pad_l;
-      const uint32_t row_off = (uint32_t)r * 128u;
-      const uint32_t sw = (uint32_t)(r & 7);
-      for (int ks = 0; ks < k_steps; ++ks) {
-        const int tap = ks / g.chunks_per_tap;
-        const int cc = (ks - tap * g.chunks_per_tap) * BK;
-        const int fr = tap / cv.f_w, fc = tap - fr * cv.f_w;
-        const int ri = r_base + fr * cv.d_h;
-        const int ci = c_base + fc * cv.d_w;
-        const bool ok = row_ok && ri >= 0 && ri < cv.in_h && ci >= 0 && ci < cv.in_w;
-        const float* src =
-            ok ? g.x + (((long long)b * cv.in_h + ri) * cv.in_w + ci) * cv.in_c + cc : g.x;
-        if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
-          atomicExch(g.flag, 5);
-          alive = false;
-          break;
-        }
-        const uint32_t dst = a_base + stage * A_STAGE_BYTES + row_off;
+    float4 cur[8], nxt[8];
+    enter_tile();
+    if (tile < g.total_tiles) load_step(nxt);
+    while (tile < g.total_tiles) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t bytes = (ok && cc + j * 4 < cv.in_c) ? 16u : 0u;
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                           dst + (((uint32_t)j ^ sw) << 4)),
-                       "l"(bytes ? src + j * 4 : g.x), "r"(bytes)
-                       : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        if (++in_flight > GATHER_LAG) {
-          asm volatile("cp.async.wait_group %0;" ::"n"(GATHER_LAG) : "memory");
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          mbar_arrive(full_bar(sig_stage));
-          if (++sig_stage == STAGES) sig_stage = 0;
-          --in_flight;
-        }
+      for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+      advance();
+      if (tile < g.total_tiles) load_step(nxt);
+      if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
+        atomicExch(g.flag, 5);
+        break;
       }
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    while (in_flight > 0) {
-      mbar_arrive(full_bar(sig_stage));
-      if (++sig_stage == STAGES) sig_stage = 0;
-      --in_flight;
+      const uint32_t dst = a_base + stage * A_STAGE_BYTES + row_off;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t w0, w1, w2, w3;
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w0) : "f"(cur[j].x));
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w1) : "f"(cur[j].y));
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w2) : "f"(cur[j].z));
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w3) : "f"(cur[j].w));
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                         dst + (((uint32_t)j ^ sw) << 4)),
+                     "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                     : "memory");
+      }
+      // make the generic-proxy stores visible to the tensor core (async proxy)
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(full_bar(stage));
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
   }
 
@@ -435,7 +452,8 @@ EncodeTiledFn get_encode() {
 // 3-D map over [batch][rows][inner] floats; box = [1][box_rows][32].
 int make_map(tfjs_cuda_ctx* ctx, CUtensorMap* tm, const float* base, uint64_t inner,
              uint64_t rows, uint64_t batch, uint64_t row_stride_elems,
-             uint64_t batch_stride_elems, uint32_t box_rows) {
+             uint64_t batch_stride_elems, uint32_t box_rows,
+             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return ctx_fail(ctx, TFJS_CUDA_DRIVER_ERROR, "cuTensorMapEncodeTiled not found");
   cuuint64_t dims[3] = {inner, rows, batch};
@@ -443,8 +461,12 @@ int make_map(tfjs_cuda_ctx* ctx, CUtensorMap* tm, const float* base, uint64_t in
   if (batch == 1) strides[1] = rows * row_stride_elems * 4;
   cuuint32_t box[3] = {BK, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box,
-                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  // TFLOAT32 element type: the TMA unit rounds each fp32 word to TF32 (nearest
+  // even) on its way into shared memory.  With the plain FLOAT32 type the tensor
+  // core would truncate the low 13 mantissa bits, a bias toward zero that
+  // compounds layer after layer.
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, (void*)base, dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return ctx_fail(ctx, TFJS_CUDA_DRIVER_ERROR,
@@ -538,7 +560,8 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, g);
   }
   if ((rc = make_map(ctx, &tm_b, op.b, (uint64_t)pr.N, (uint64_t)pr.K,
-                     (uint64_t)pr.batch_b, (uint64_t)op.ldb, (uint64_t)pr.K * op.ldb, 32)))
+                     (uint64_t)pr.batch_b, (uint64_t)op.ldb, (uint64_t)pr.K * op.ldb, 32,
+                     CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)))
     return rc;
   if (op.a_gather) {
     tm_a = tm_b;

@@ -156,6 +156,8 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
   if (ctx->h_flag) cudaFreeHost(ctx->h_flag);
   if (ctx->d_bad_index) cudaFree(ctx->d_bad_index);
   if (ctx->h_bad_index) cudaFreeHost(ctx->h_bad_index);
+  for (cudaEvent_t e : ctx->prof_events)
+    if (e) cudaEventDestroy(e);
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -331,6 +333,31 @@ int tfjs_cuda_time_end(tfjs_cuda_ctx* ctx, float* out_kernel_ms) {
   CUDA_TRY(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
   CUDA_TRY(ctx, cudaEventSynchronize(ctx->ev1));
   CUDA_TRY(ctx, cudaEventElapsedTime(out_kernel_ms, ctx->ev0, ctx->ev1));
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_event_record(tfjs_cuda_ctx* ctx, int32_t slot) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (slot < 0 || slot > (1 << 20))
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "event_record: bad slot %d", slot);
+  cudaSetDevice(ctx->device);
+  if ((size_t)slot >= ctx->prof_events.size()) ctx->prof_events.resize(slot + 1, nullptr);
+  if (!ctx->prof_events[slot]) CUDA_TRY(ctx, cudaEventCreate(&ctx->prof_events[slot]));
+  CUDA_TRY(ctx, cudaEventRecord(ctx->prof_events[slot], ctx->stream));
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_event_elapsed(tfjs_cuda_ctx* ctx, int32_t slot_begin, int32_t slot_end,
+                            float* out_ms) {
+  if (!ctx || !out_ms) return TFJS_CUDA_INVALID_ARG;
+  const size_t n = ctx->prof_events.size();
+  if (slot_begin < 0 || slot_end < 0 || (size_t)slot_begin >= n || (size_t)slot_end >= n ||
+      !ctx->prof_events[slot_begin] || !ctx->prof_events[slot_end])
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "event_elapsed: slot was never recorded");
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaEventSynchronize(ctx->prof_events[slot_end]));
+  CUDA_TRY(ctx, cudaEventElapsedTime(out_ms, ctx->prof_events[slot_begin],
+                                     ctx->prof_events[slot_end]));
   return TFJS_CUDA_OK;
 }
 

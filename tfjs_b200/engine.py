@@ -70,6 +70,7 @@ class Engine(object):
         self.backend = None
         self.num_tensors = 0
         self.is_test = False
+        self._profile = None   # list of kernel records while tf.profile is active
 
     # ---------------------------------------------------------- backends --
     def register_backend(self, name, factory, priority=1):
@@ -161,7 +162,18 @@ class Engine(object):
                                (kernel_name, self.backend_name))
         infos = {k: (v.info() if isinstance(v, Tensor) else v) for k, v in inputs.items()}
         before = self.backend.numDataIds()
+        prof = self._profile
+        if prof is not None:
+            slot = 2 * len(prof)
+            self.backend.event_record(slot)
         out = kernel.kernelFunc({"inputs": infos, "attrs": attrs or {}, "backend": self.backend})
+        if prof is not None:
+            self.backend.event_record(slot + 1)
+            o = out if isinstance(out, (list, tuple)) else [out]
+            prof.append({"name": kernel_name, "slot": slot,
+                         "inputShapes": {k: list(v.shape) for k, v in infos.items()
+                                         if v is not None},
+                         "outputShapes": [list(t.shape) for t in o], "attrs": attrs or {}})
         outs = out if isinstance(out, (list, tuple)) else [out]
         if self.is_test:
             # engine.ts:557-588: a kernel may only add one data id per output
@@ -174,6 +186,21 @@ class Engine(object):
                                    "after running '%s'" % (self.backend_name, leaked, kernel_name))
         tensors = [self.make_tensor_from_info(o) for o in outs]
         return tensors if isinstance(out, (list, tuple)) else tensors[0]
+
+
+    def profile(self, f):
+        """tf.profile (engine.ts:976-998): runs f and returns one record per kernel
+        with its name, shapes and device time (`kernelTimeMs`, from CUDA events
+        recorded on the backend's stream around each kernel func)."""
+        self.ready()
+        self._profile = []
+        try:
+            result = f()
+        finally:
+            records, self._profile = self._profile, None
+        for rec in records:
+            rec["kernelTimeMs"] = self.backend.event_elapsed(rec["slot"], rec["slot"] + 1)
+        return {"kernels": records, "result": result}
 
 
 ENGINE = Engine()

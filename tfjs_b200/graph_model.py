@@ -1,0 +1,456 @@
+"""GraphModel / GraphExecutor for tfjs graph-model artifacts.
+
+Consumes the converter's `model.json` + weight bytes
+(tfjs-core/src/io/types.ts:49-110) and runs the node list through the 'cuda'
+backend's kernels by way of the same ops the converter's executors call.  The
+structure follows the reference: GraphModel.loadSync -> decodeWeights ->
+executor (tfjs-converter/src/executor/graph_model.ts:176-234); execute ->
+compile once per (inputs, outputs) -> node loop that stores outputs and
+disposes each intermediate right after its last consumer has been enqueued
+(graph_executor.ts:231-318, :382-409; liveness model_analysis.ts:275-335);
+per-op mapping as in operations/executors/*.ts, with attribute decoding as
+operation_mapper.ts:437-461 (strings are base64, ints are JSON strings).
+
+In a Node deployment the unmodified tfjs-converter plays this role; this module
+drives the same kernels from Python and is what the benchmark times.
+"""
+import base64
+import json
+
+import numpy as np
+
+from . import io, ops
+from .engine import ENGINE, Tensor
+
+DT_MAP = {"DT_FLOAT": "float32", "DT_INT32": "int32", "DT_BOOL": "bool", "DT_INT64": "int32",
+          1: "float32", 3: "int32", 9: "int32", 10: "bool"}
+
+
+# ---------------------------------------------------------- attribute values --
+def _b64(s):
+    try:
+        return base64.b64decode(s).decode("utf-8")
+    except Exception:
+        return s
+
+
+def attr_string(attrs, name, default=None, keep_case=False):
+    """operation_mapper.ts:437-445: base64-decoded and lower-cased."""
+    a = attrs.get(name)
+    if a is None or "s" not in a:
+        return default
+    v = _b64(a["s"])
+    return v if keep_case else v.lower()
+
+
+def attr_number(attrs, name, default=None):
+    a = attrs.get(name)
+    if a is None:
+        return default
+    if "i" in a:
+        return int(a["i"])
+    if "f" in a:
+        return float(a["f"])
+    return default
+
+
+def attr_bool(attrs, name, default=False):
+    a = attrs.get(name)
+    if a is None or "b" not in a:
+        return default
+    return bool(a["b"])
+
+
+def attr_number_list(attrs, name, default=None):
+    a = attrs.get(name)
+    if a is None or "list" not in a:
+        return default
+    lst = a["list"]
+    if lst.get("i"):
+        return [int(v) for v in lst["i"]]
+    if lst.get("f"):
+        return [float(v) for v in lst["f"]]
+    return default if default is not None else []
+
+
+def attr_string_list(attrs, name, default=None):
+    a = attrs.get(name)
+    if a is None or "list" not in a or not a["list"].get("s"):
+        return default if default is not None else []
+    return [_b64(s).lower() for s in a["list"]["s"]]
+
+
+def attr_dtype(attrs, name, default=None):
+    a = attrs.get(name)
+    if a is None or "type" not in a:
+        return default
+    t = a["type"]
+    if t not in DT_MAP:
+        raise ValueError("Unsupported dtype %s" % t)
+    return DT_MAP[t]
+
+
+def attr_shape(attrs, name):
+    a = attrs.get(name)
+    if a is None or "shape" not in a:
+        return None
+    if a["shape"].get("unknownRank"):
+        return None
+    return [int(d.get("size", -1)) for d in a["shape"].get("dim", [])]
+
+
+class Node(object):
+    __slots__ = ("name", "op", "inputs", "attrs", "children")
+
+    def __init__(self, d):
+        self.name = d["name"]
+        self.op = d["op"]
+        # control-dependency inputs ("^name") carry no tensor
+        self.inputs = [i for i in d.get("input", []) if not i.startswith("^")]
+        self.attrs = d.get("attr", {})
+        self.children = []
+
+
+def parse_node_name(name):
+    """executors/utils.ts:120-132: 'node:1' -> ('node', 1)."""
+    parts = name.split(":")
+    if len(parts) == 1:
+        return name, 0
+    return parts[0], int(parts[-1])
+
+
+# ------------------------------------------------------------- op executors --
+def _vals(t):
+    """Small parameter tensors are read on the host (executors/utils.ts:55)."""
+    return t.dataSync()
+
+
+def _pad_param(node):
+    pad = attr_string(node.attrs, "padding", "valid")
+    if pad == "explicit":
+        flat = attr_number_list(node.attrs, "explicit_paddings", [0] * 8)
+        return [[flat[2 * i], flat[2 * i + 1]] for i in range(4)]
+    return pad
+
+
+def _fused_params(node, inputs):
+    fused = attr_string_list(node.attrs, "fused_ops")
+    extra = fused[0] if len(fused) > 0 else None
+    activation = fused[1] if len(fused) > 1 else None
+    is_bias, is_prelu = extra == "biasadd", activation == "prelu"
+    num_args = attr_number(node.attrs, "num_args", 0)
+    if is_bias:
+        if is_prelu and num_args != 2:
+            raise ValueError("FusedConv2d and DepthwiseConv2d with BiasAdd and Prelu must have "
+                             "two extra arguments: bias and alpha.")
+        if not is_prelu and num_args != 1:
+            raise ValueError("FusedConv2d and DepthwiseConv2d with BiasAdd must have one extra "
+                             "argument: bias.")
+    if extra == "fusedbatchnorm":
+        raise ValueError("FusedConv2d and DepthwiseConv2d with FusedBatchNorm is not supported")
+    args = list(inputs[2:])
+    bias = args[0] if len(args) > 0 else None
+    prelu = args[1] if len(args) > 1 else None
+    if not is_bias:
+        prelu, bias = bias, None
+    return bias, prelu, activation or "linear", attr_number(node.attrs, "leakyrelu_alpha", 0.2)
+
+
+def _exec_conv(node, inp):
+    strides = attr_number_list(node.attrs, "strides", [1, 1, 1, 1])
+    dil = attr_number_list(node.attrs, "dilations", [1, 1, 1, 1])
+    fmt = attr_string(node.attrs, "data_format", "nhwc").upper()
+    pad = _pad_param(node)
+    if node.op in ("Conv2D", "DepthwiseConv2dNative", "DepthwiseConv2d"):
+        fn = ops.conv2d if node.op == "Conv2D" else ops.depthwise_conv2d
+        return fn(inp[0], inp[1], [strides[1], strides[2]], pad, fmt, [dil[1], dil[2]])
+    bias, prelu, act, alpha = _fused_params(node, inp)
+    fn = ops.fused_conv2d if node.op == "_FusedConv2D" else ops.fused_depthwise_conv2d
+    return fn(inp[0], inp[1], [strides[1], strides[2]], pad, fmt, [dil[1], dil[2]], None, bias,
+              act, prelu, alpha)
+
+
+def _exec_matmul(node, inp):
+    if node.op == "_FusedMatMul":
+        bias, prelu, act, alpha = _fused_params(node, inp)
+        return ops.fused_mat_mul(inp[0], inp[1], attr_bool(node.attrs, "transpose_a"),
+                                 attr_bool(node.attrs, "transpose_b"), bias, act, prelu, alpha)
+    if node.op == "MatMul":
+        return ops.mat_mul(inp[0], inp[1], attr_bool(node.attrs, "transpose_a"),
+                           attr_bool(node.attrs, "transpose_b"))
+    return ops.mat_mul(inp[0], inp[1], attr_bool(node.attrs, "adj_x"),
+                       attr_bool(node.attrs, "adj_y"))
+
+
+def _exec_pool(node, inp):
+    k = attr_number_list(node.attrs, "ksize", [1, 1, 1, 1])
+    s = attr_number_list(node.attrs, "strides", [1, 1, 1, 1])
+    fn = ops.max_pool if node.op == "MaxPool" else ops.avg_pool
+    return fn(inp[0], [k[1], k[2]], [s[1], s[2]], _pad_param(node))
+
+
+def _exec_reduce(node, inp):
+    axis = [int(v) for v in _vals(inp[1])]
+    keep = attr_bool(node.attrs, "keep_dims")
+    return {"Mean": ops.mean, "Sum": ops.sum, "Max": ops.max}[node.op](inp[0], axis, keep)
+
+
+_BINARY = {"Add": ops.add, "AddV2": ops.add, "BiasAdd": ops.add, "Sub": ops.sub, "Mul": ops.mul,
+           "RealDiv": ops.div, "Div": ops.div, "Maximum": ops.maximum, "Minimum": ops.minimum,
+           "Pow": ops.pow, "SquaredDifference": ops.squared_difference}
+_UNARY = {"Relu": ops.relu, "Relu6": ops.relu6, "Elu": ops.elu, "Sigmoid": ops.sigmoid,
+          "Exp": ops.exp, "Sqrt": ops.sqrt, "Rsqrt": ops.rsqrt, "Square": ops.square,
+          "Tanh": ops.tanh, "Neg": ops.neg, "Erf": ops.erf, "Abs": ops.abs, "Log": ops.log}
+
+
+def execute_op(node, inp):
+    """operations/operation_executor.ts:55-124 for the ops of the three models."""
+    op = node.op
+    if op in ("_FusedConv2D", "FusedDepthwiseConv2dNative", "Conv2D", "DepthwiseConv2dNative",
+              "DepthwiseConv2d"):
+        return _exec_conv(node, inp)
+    if op in ("_FusedMatMul", "MatMul", "BatchMatMul", "BatchMatMulV2"):
+        return _exec_matmul(node, inp)
+    if op in ("MaxPool", "AvgPool"):
+        return _exec_pool(node, inp)
+    if op in ("Mean", "Sum", "Max"):
+        return _exec_reduce(node, inp)
+    if op in _BINARY:
+        return _BINARY[op](inp[0], inp[1])
+    if op in _UNARY:
+        return _UNARY[op](inp[0])
+    if op == "LeakyRelu":
+        return ops.leaky_relu(inp[0], attr_number(node.attrs, "alpha", 0.2))
+    if op == "Prelu":
+        return ops.prelu(inp[0], inp[1])
+    if op == "ClipByValue":
+        return ops.clip_by_value(inp[0], float(_vals(inp[1])[0]), float(_vals(inp[2])[0]))
+    if op == "Softmax":
+        return ops.softmax(inp[0])
+    if op == "ArgMax":
+        return ops.arg_max(inp[0], int(_vals(inp[1])[0]))
+    if op == "GatherV2":
+        return ops.gather(inp[0], inp[1] if inp[1].dtype == "int32" else ops.cast(inp[1], "int32"),
+                          int(_vals(inp[2])[0]), attr_number(node.attrs, "batch_dims", 0))
+    if op == "Reshape":
+        return ops.reshape(inp[0], [int(v) for v in _vals(inp[1])])
+    if op == "Transpose":
+        return ops.transpose(inp[0], [int(v) for v in _vals(inp[1])])
+    if op == "ExpandDims":
+        return ops.expand_dims(inp[0], int(_vals(inp[1])[0]))
+    if op == "Squeeze":
+        dims = attr_number_list(node.attrs, "squeeze_dims", [])
+        shape = inp[0].shape
+        dims = [d % len(shape) for d in dims] if dims else [i for i, s in enumerate(shape) if s == 1]
+        return ops.reshape(inp[0], [s for i, s in enumerate(shape) if i not in dims])
+    if op == "ConcatV2":
+        return ops.concat(inp[:-1], int(_vals(inp[-1])[0]))
+    if op in ("Pad", "PadV2"):
+        p = _vals(inp[1]).reshape(-1, 2)
+        const = float(_vals(inp[2])[0]) if op == "PadV2" and len(inp) > 2 else \
+            attr_number(node.attrs, "constant_value", 0)
+        return ops.pad(inp[0], [[int(a), int(b)] for a, b in p], const)
+    if op == "Slice":
+        return ops.slice(inp[0], [int(v) for v in _vals(inp[1])], [int(v) for v in _vals(inp[2])])
+    if op == "Tile":
+        return ops.tile(inp[0], [int(v) for v in _vals(inp[1])])
+    if op == "Pack":
+        return ops.stack(inp, attr_number(node.attrs, "axis", 0))
+    if op == "Cast":
+        return ops.cast(inp[0], attr_dtype(node.attrs, "DstT", "float32"))
+    if op in ("Identity", "StopGradient", "PlaceholderWithDefault"):
+        return ops.identity(inp[0])
+    if op in ("FusedBatchNorm", "FusedBatchNormV2", "FusedBatchNormV3"):
+        return ops.batch_norm(inp[0], inp[3], inp[4], inp[2], inp[1],
+                              attr_number(node.attrs, "epsilon", 0.001))
+    raise ValueError("Node type %s is not implemented" % op)
+
+
+# ------------------------------------------------------------------- executor --
+class GraphExecutor(object):
+    def __init__(self, nodes, weight_map):
+        self.nodes = {n.name: n for n in nodes}
+        self.order_all = nodes
+        self.weight_map = weight_map      # name -> Tensor (kept for the model's lifetime)
+        self.placeholders = [n for n in nodes if n.op == "Placeholder"]
+        consumed = set()
+        for n in nodes:
+            for i in n.inputs:
+                consumed.add(parse_node_name(i)[0])
+        self.default_outputs = [n.name for n in nodes
+                                if n.name not in consumed and n.op not in ("Const", "Placeholder")]
+        self._compiled = {}
+        self.keep_intermediates = False
+        self.intermediates = {}
+
+    def _compile(self, input_names, output_names):
+        """graph_executor.ts:167-191: the nodes needed for the outputs in topological
+        order, and for every tensor the position of its last consumer."""
+        key = (tuple(sorted(input_names)), tuple(output_names))
+        if key in self._compiled:
+            return self._compiled[key]
+        needed, stack = set(), [parse_node_name(o)[0] for o in output_names]
+        while stack:
+            name = stack.pop()
+            if name in needed:
+                continue
+            if name not in self.nodes:
+                raise ValueError("The output '%s' is not found in the graph" % name)
+            needed.add(name)
+            if name in input_names:
+                continue
+            stack.extend(parse_node_name(i)[0] for i in self.nodes[name].inputs)
+        for name in needed:
+            n = self.nodes[name]
+            if n.op == "Placeholder" and name not in input_names:
+                raise ValueError("Cannot compute the outputs [%s] from the provided inputs [%s]. "
+                                 "Missing the following inputs: [%s]" %
+                                 (", ".join(output_names), ", ".join(input_names), name))
+        ordered, state = [], {}
+
+        def visit(name):
+            # iterative DFS post-order
+            st = [(name, 0)]
+            while st:
+                cur, idx = st.pop()
+                if state.get(cur) == 2:
+                    continue
+                node = self.nodes[cur]
+                ins = [] if cur in input_names else [parse_node_name(i)[0] for i in node.inputs]
+                if idx < len(ins):
+                    st.append((cur, idx + 1))
+                    if state.get(ins[idx]) is None:
+                        state[ins[idx]] = 1
+                        st.append((ins[idx], 0))
+                else:
+                    state[cur] = 2
+                    ordered.append(node)
+        for o in output_names:
+            root = parse_node_name(o)[0]
+            if state.get(root) is None:
+                state[root] = 1
+                visit(root)
+        last_use = {}
+        for pos, node in enumerate(ordered):
+            if node.name in input_names:
+                continue
+            for i in node.inputs:
+                last_use[parse_node_name(i)[0]] = pos
+        plan = (ordered, last_use)
+        self._compiled[key] = plan
+        return plan
+
+    def execute(self, inputs, outputs=None):
+        """graph_executor.ts:231-318."""
+        outputs = list(outputs) if outputs else list(self.default_outputs)
+        input_names = set(inputs)
+        for name, t in inputs.items():
+            node = self.nodes.get(name)
+            if node is None:
+                raise ValueError("The dict provided in model.execute(dict) has keys: [%s] that "
+                                 "are not part of graph" % name)
+            shape = attr_shape(node.attrs, "shape")
+            if shape is not None:
+                ok = len(shape) == len(t.shape) and all(
+                    s in (-1, d) for s, d in zip(shape, t.shape))
+                if not ok:
+                    raise ValueError("The shape of dict['%s'] provided in model.execute(dict) must "
+                                     "be [%s], but was [%s]" % (name, shape, t.shape))
+            dt = attr_dtype(node.attrs, "dtype")
+            if dt is not None and dt != t.dtype:
+                raise ValueError("The dtype of dict['%s'] provided in model.execute(dict) must be "
+                                 "%s, but was %s" % (name, dt, t.dtype))
+        ordered, last_use = self._compile(input_names, outputs)
+        out_roots = set(parse_node_name(o)[0] for o in outputs)
+        tensors = {}
+        owned = set()
+        self.intermediates = {}
+        try:
+            for pos, node in enumerate(ordered):
+                if node.name in input_names:
+                    tensors[node.name] = inputs[node.name]
+                elif node.op == "Const":
+                    tensors[node.name] = self.weight_map[node.name]
+                else:
+                    ins = [tensors[parse_node_name(i)[0]] for i in node.inputs]
+                    tensors[node.name] = execute_op(node, ins)
+                    owned.add(node.name)
+                # dispose what nobody downstream needs (graph_executor.ts:382-409)
+                if not self.keep_intermediates and node.name not in input_names:
+                    for i in node.inputs:
+                        src = parse_node_name(i)[0]
+                        if (src in owned and last_use.get(src) == pos and src not in out_roots):
+                            tensors[src].dispose()
+                            owned.discard(src)
+            result = [tensors[parse_node_name(o)[0]] for o in outputs]
+        except Exception:
+            for name in owned:
+                tensors[name].dispose()
+            raise
+        if self.keep_intermediates:
+            self.intermediates = {n: tensors[n] for n in owned}
+        else:
+            for name in list(owned):
+                if name not in out_roots:
+                    tensors[name].dispose()
+        return result
+
+
+class GraphModel(object):
+    """tfjs-converter/src/executor/graph_model.ts."""
+
+    def __init__(self, model_json, weight_data, engine=None, decode_weights=None):
+        self.engine = engine or ENGINE
+        self.artifacts = model_json if isinstance(model_json, dict) else json.loads(model_json)
+        if self.artifacts.get("format") not in (None, "graph-model"):
+            raise ValueError("not a graph-model artifact")
+        topo = self.artifacts["modelTopology"]
+        if "versions" not in topo:
+            raise ValueError("modelTopology.versions is missing")
+        self.version = "%s.%s" % (topo["versions"].get("producer"),
+                                  topo["versions"].get("minConsumer"))
+        specs = []
+        for group in self.artifacts.get("weightsManifest", []):
+            specs.extend(group["weights"])
+        decode = decode_weights or io.decode_weights
+        self.weights = decode(self.engine, weight_data, specs)
+        nodes = [Node(d) for d in topo["node"]]
+        for n in nodes:
+            if n.op == "Const" and n.name not in self.weights:
+                raise ValueError("Const node %s has no weight in the manifest" % n.name)
+        self.executor = GraphExecutor(nodes, self.weights)
+        sig = (self.artifacts.get("userDefinedMetadata") or {}).get("signature") or \
+            self.artifacts.get("signature") or {}
+        self.input_names = list((sig.get("inputs") or {}).keys()) or \
+            [n.name for n in self.executor.placeholders]
+        self.output_names = list((sig.get("outputs") or {}).keys()) or \
+            self.executor.default_outputs
+
+    @property
+    def inputs(self):
+        return [{"name": n.name, "shape": attr_shape(n.attrs, "shape"),
+                 "dtype": attr_dtype(n.attrs, "dtype")} for n in self.executor.placeholders]
+
+    def execute(self, inputs, outputs=None):
+        """graph_model.ts:507-516: inputs is a Tensor, a list, or a name->Tensor dict."""
+        if isinstance(inputs, Tensor):
+            inputs = [inputs]
+        if isinstance(inputs, (list, tuple)):
+            if len(inputs) != len(self.input_names):
+                raise ValueError("Input tensor count mismatch, the graph model has %d "
+                                 "placeholders, while there are %d input tensors." %
+                                 (len(self.input_names), len(inputs)))
+            inputs = dict(zip(self.input_names, inputs))
+        single = isinstance(outputs, str) or (outputs is None and len(self.output_names) == 1)
+        if isinstance(outputs, str):
+            outputs = [outputs]
+        res = self.executor.execute(inputs, outputs or self.output_names)
+        return res[0] if single else res
+
+    def predict(self, inputs):
+        return self.execute(inputs)
+
+    def dispose(self):
+        for t in self.weights.values():
+            t.dispose()
+        self.weights = {}
