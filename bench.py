@@ -1,0 +1,425 @@
+"""Benchmark of the tfjs 'cuda' backend on B200: GraphModel.execute throughput.
+
+    python bench.py --gpus N --steps K --warmup W [--model mobilenet_v2|resnet50|bert]
+    python bench.py --impl reference ...        # the CPU path, timed on the host cores
+
+One step = one GraphModel.execute over one batch per GPU (MobileNetV2-1.0 batch
+256, ResNet-50 batch 128 with uint8-quantised weights dequantised on the device
+at load, BERT-base encoder batch 64 x seq 128).  Weights are random-initialised
+and inputs are seeded synthetic tensors of the published shapes.  With N > 1
+every rank runs its own backend on its own GPU with its own batch (weak
+scaling, no collective on the data path); rank 0 prints one JSON line.
+
+value      device-timed throughput with the input batch resident in HBM.
+e2e        the same metric through the public API with HOST buffers: every step
+           uploads the batch from pinned memory and downloads the logits.
+roofline   for the kernel kind that takes the most device time, from CUDA events
+           recorded around every kernel on the launching stream during extra
+           profiled steps (tf.profile-style) right after the timed region.
+cpu_baseline  the CPU oracle (a C restatement of tfjs-backend-cpu) on a bounded
+           sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "mobilenet_v2": dict(batch=256, unit="images/s", metric="images/sec", out="logits",
+                         gflop=0.601548544, name="mobilenet_v2_1.0_224_b256_graphmodel"),
+    "resnet50": dict(batch=128, unit="images/s", metric="images/sec", out="logits",
+                     gflop=8.178368512, name="resnet50_v1.5_224_b128_uint8weights_graphmodel"),
+    "bert": dict(batch=64, unit="sequences/s", metric="sequences/sec", out="sequence_output",
+                 gflop=22.347251712, name="bert_base_encoder_seq128_b64_graph"),
+}
+
+
+def build_model(model, batch):
+    from tfjs_b200 import model_zoo
+    if model == "mobilenet_v2":
+        return model_zoo.mobilenet_v2(batch)
+    if model == "resnet50":
+        return model_zoo.resnet50(batch)
+    return model_zoo.bert_encoder(batch)
+
+
+def make_feeds(model, batch, seed):
+    r = np.random.default_rng(seed)
+    if model == "mobilenet_v2":
+        return {"input": r.uniform(-1, 1, (batch, 224, 224, 3)).astype(np.float32)}
+    if model == "resnet50":
+        return {"input": r.uniform(0, 1, (batch, 224, 224, 3)).astype(np.float32)}
+    return {"input_ids": r.integers(0, 30522, (batch, 128)).astype(np.int32),
+            "attention_mask": np.ones((batch, 128), np.float32)}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=float(p["hbm_gbs"]), bf16=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, source="fallback")
+
+
+class ClockSampler(object):
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(device), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = [l.strip().split(", ") for l in open(self.tmp.name) if l.strip()]
+        os.unlink(self.tmp.name)
+        sm, reasons, mx = [], set(), None
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), r[5:9]):
+                if v.strip().lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            busy = [s for s in sm if s > 0.5 * max(sm)] or sm
+            out.update(sm_mhz=float(np.median(busy)), sm_max_mhz=mx, reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------ work accounting --
+def _prod(s):
+    n = 1
+    for v in s:
+        n *= int(v)
+    return n
+
+
+def kernel_work(rec):
+    """Algorithmic (flops, bytes) of one profiled kernel call: each input and
+    output tensor is moved once; contractions count 2 flops per MAC."""
+    ins = rec["inputShapes"]
+    outs = rec["outputShapes"]
+    nbytes = 4 * (sum(_prod(s) for s in ins.values()) + sum(_prod(s) for s in outs))
+    name, flops = rec["name"], 0
+    if name in ("FusedConv2D", "Conv2D"):
+        f = ins["filter"]
+        flops = 2 * _prod(outs[0]) * f[0] * f[1] * f[2]
+    elif name in ("FusedDepthwiseConv2D", "DepthwiseConv2dNative"):
+        f = ins["filter"]
+        flops = 2 * _prod(outs[0]) * f[0] * f[1]
+    elif name in ("_FusedMatMul", "BatchMatMul"):
+        a = ins["a"]
+        k = a[-2] if rec["attrs"].get("transposeA") else a[-1]
+        flops = 2 * _prod(outs[0]) * k
+    elif name in ("Reshape", "Identity", "ExpandDims"):
+        nbytes = 0
+    return flops, nbytes
+
+
+def summarise_profile(records, steps):
+    kinds = {}
+    for rec in records:
+        flops, nbytes = kernel_work(rec)
+        k = kinds.setdefault(rec["name"], dict(launches=0, ms=0.0, flops=0, bytes=0))
+        k["launches"] += 1
+        k["ms"] += rec["kernelTimeMs"]
+        k["flops"] += flops
+        k["bytes"] += nbytes
+    total = sum(k["ms"] for k in kinds.values()) or 1.0
+    out = {}
+    for name, k in kinds.items():
+        sec = k["ms"] / 1e3 or 1e-12
+        out[name] = dict(launches_per_step=k["launches"] // steps,
+                         ms_per_step=round(k["ms"] / steps, 4), share=round(k["ms"] / total, 4),
+                         gbs=round(k["bytes"] / sec / 1e9, 1),
+                         tflops=round(k["flops"] / sec / 1e12, 2),
+                         flops_per_byte=round(k["flops"] / max(k["bytes"], 1), 1))
+    return out
+
+
+def measure_tf32_peak():
+    """cuBLAS TF32 GEMM throughput (8192^3, best of 10), the tensor roofline
+    denominator for a TF32 kernel; measured the way the bf16 figure in
+    MEASURED_PEAKS.json was.  Measurement only; not on the product path."""
+    try:
+        import torch
+        torch.backends.cuda.matmul.allow_tf32 = True
+        n = 8192
+        a = torch.randn(n, n, device="cuda")
+        b = torch.randn(n, n, device="cuda")
+        for _ in range(3):
+            a @ b
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+            e0.record()
+            a @ b
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        del a, b
+        torch.cuda.empty_cache()
+        return 2 * n ** 3 / (best / 1e3) / 1e12
+    except Exception:
+        return None
+
+
+# ------------------------------------------------------------------ reference --
+def cpu_sample(model, sample_batch, threads=None):
+    """Times the CPU oracle on `sample_batch` units of the workload."""
+    from oracle import graph_oracle, oracle as orc
+    if threads:
+        orc.set_threads(threads)
+    model_json, weights = build_model(model, sample_batch)
+    feeds = make_feeds(model, sample_batch, 1)
+    t0 = time.perf_counter()
+    graph_oracle.run(model_json, weights, feeds)
+    dt = time.perf_counter() - t0
+    return sample_batch / dt, dt, orc.max_threads()
+
+
+def run_reference(args, rank, world):
+    w = WORKLOADS[args.model]
+    if rank != 0:
+        return
+    sample = args.cpu_sample or {"mobilenet_v2": 32, "resnet50": 4, "bert": 2}[args.model]
+    for _ in range(max(args.warmup, 0) and 1):
+        cpu_sample(args.model, 1)
+    vals = []
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        v, dt, cores = cpu_sample(args.model, sample)
+        vals.append(v)
+    total = time.perf_counter() - t_all
+    value = float(np.mean(vals))
+    sample_txt = ("%d %s per step through the C restatement of tfjs-backend-cpu (same graph, "
+                  "same layer shapes), OpenMP over independent outputs" %
+                  (sample, "images" if "image" in w["unit"] else "sequences"))
+    line = {"impl": "reference", "metric": w["metric"], "value": round(value, 3),
+            "unit": w["unit"], "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(total / args.steps * 1e3, 2), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f64-math/f32-store",
+            "data": "synthetic",
+            "config": {"workload": w["name"], "batch_per_gpu": w["batch"],
+                       "sample_batch": sample},
+            "cpu_baseline": {"value": round(value, 3), "unit": w["unit"], "cores": cores,
+                             "kind": "port", "sample": sample_txt},
+            "e2e": {"value": round(value, 3), "unit": w["unit"], "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------- cuda --
+def run_cuda(args, rank, world, local_rank):
+    os.environ["TFJS_CUDA_DEVICE_ORDINAL"] = str(local_rank)
+    import tfjs_b200
+    from tfjs_b200.graph_model import GraphModel
+    eng = tfjs_b200.ENGINE
+    eng.set_backend("cuda")          # raises if the CUDA library or a GPU is missing
+    be = eng.backend
+    w = WORKLOADS[args.model]
+    batch = args.batch or w["batch"]
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("gloo", rank=rank, world_size=world)
+        dist = dist_mod
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    model_json, weights = build_model(args.model, batch)
+    gm = GraphModel(model_json, weights, eng)
+    feeds = make_feeds(args.model, batch, 1000 + rank)
+    pinned, dtypes = {}, {}
+    for k, v in feeds.items():
+        dt = "int32" if v.dtype == np.int32 else "float32"
+        p = be.pinned_empty(v.shape, dt)
+        p[...] = v
+        pinned[k], dtypes[k] = p, dt
+    resident = {k: eng.make_tensor_from_info(
+        tfjs_b200.TensorInfo(be.write_from(pinned[k], pinned[k].shape, dtypes[k]),
+                             pinned[k].shape, dtypes[k])) for k in pinned}
+    out_name = w["out"]
+
+    def step_resident():
+        y = gm.execute(resident, [out_name])[0]
+        y.dispose()
+
+    out_probe = gm.execute(resident, [out_name])[0]
+    out_shape = out_probe.shape
+    out_probe.dispose()
+    out_host = be.pinned_empty(out_shape, "float32")
+    h2d = int(sum(p.nbytes for p in pinned.values()))
+    d2h = int(out_host.nbytes)
+
+    def step_e2e():
+        ins = {k: eng.make_tensor_from_info(
+            tfjs_b200.TensorInfo(be.write_from(pinned[k], pinned[k].shape, dtypes[k]),
+                                 pinned[k].shape, dtypes[k])) for k in pinned}
+        y = gm.execute(ins, [out_name])[0]
+        be.read_into(y.dataId, out_host)     # D2H + stream sync
+        y.dispose()
+        for t in ins.values():
+            t.dispose()
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    be.sync()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    # ---- timed region: device time (CUDA events on the launching stream) ----
+    barrier()
+    be.sync()
+    launches0 = be.launch_count()
+    t_host0 = time.perf_counter()
+    be.check(be.lib.tfjs_cuda_time_begin(be.ctx))
+    for _ in range(args.steps):
+        step_resident()
+    from ctypes import byref, c_float
+    ms = c_float()
+    be.check(be.lib.tfjs_cuda_time_end(be.ctx, byref(ms)))   # records + syncs
+    be.sync()
+    host_ms = (time.perf_counter() - t_host0) * 1e3
+    barrier()
+    launches = be.launch_count() - launches0
+    dev_ms = max_over_ranks(float(ms.value))
+
+    # ---- end to end through the public API with host buffers -----------------
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    be.sync()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    be.sync()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    clocks = sampler.stop() if sampler is not None else None
+
+    # ---- per-kernel profile (rank 0) -------------------------------------------
+    line = None
+    if rank == 0:
+        prof_steps = 2
+        records = []
+        for _ in range(prof_steps):
+            records += eng.profile(step_resident)["kernels"]
+        kinds = summarise_profile(records, prof_steps)
+        top = max(kinds, key=lambda k: kinds[k]["ms_per_step"])
+        pk = peaks()
+        tk = kinds[top]
+        tensor_bound = tk["flops_per_byte"] >= 100.0
+        roof = {"kernel": top, "launches_per_step": tk["launches_per_step"],
+                "share_of_device_time": tk["share"], "traffic": None}
+        if tensor_bound:
+            tf32_peak = measure_tf32_peak()
+            peak = tf32_peak or pk["bf16"] / 2.0
+            roof.update(bound="tensor", achieved=tk["tflops"], peak=round(peak, 1),
+                        unit="TFLOP/s", frac=round(tk["tflops"] / peak, 4),
+                        peak_source=("measured in this run: torch.matmul TF32 8192^3 best of 10"
+                                     if tf32_peak else "half of the %s bf16 figure" % pk["source"]))
+        else:
+            roof.update(bound="hbm", achieved=tk["gbs"], peak=pk["hbm"], unit="GB/s",
+                        frac=round(tk["gbs"] / pk["hbm"], 4),
+                        peak_source="%s copy bandwidth" % pk["source"])
+        units = batch * world
+        value = units * args.steps / (dev_ms / 1e3)
+        line = {"metric": w["metric"], "value": round(value, 2), "unit": w["unit"],
+                "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+                "config": {"workload": w["name"], "batch_per_gpu": batch,
+                           "global_batch": units, "parallelism": "replicas x%d" % world,
+                           "l2": "activations per step are far larger than L2",
+                           "weights": "random init"},
+                "host_ms_per_step": round(host_ms / args.steps, 4),
+                "tflops": round(units * w["gflop"] / 1e3 / (dev_ms / args.steps / 1e3), 2),
+                "clocks": clocks,
+                "e2e": {"value": round(units * args.steps / e2e_s, 2), "unit": w["unit"],
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "gpu_launches": int(launches),
+                "roofline": roof,
+                "kernels": kinds}
+        if world == 1 and not args.no_cpu:
+            sample = args.cpu_sample or {"mobilenet_v2": 64, "resnet50": 8, "bert": 4}[args.model]
+            v, dt, cores = cpu_sample(args.model, sample)
+            line["cpu_baseline"] = {
+                "value": round(v, 3), "unit": w["unit"], "cores": cores, "kind": "port",
+                "sample": "%d units of the same graph through the C restatement of "
+                          "tfjs-backend-cpu in %.1f s" % (sample, dt)}
+    for t in resident.values():
+        t.dispose()
+    gm.dispose()
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--model", default="mobilenet_v2", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the workload's)")
+    ap.add_argument("--cpu-sample", type=int, default=0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_cuda(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

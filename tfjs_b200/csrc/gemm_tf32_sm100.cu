@@ -6,9 +6,10 @@
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma.kind::tf32 from
 //               shared-memory descriptors into a TMEM accumulator; owns the TMEM
 //               allocation.
-//   warps 2-5   epilogue: tcgen05.ld the accumulator (32 lanes x 32 columns per
-//               load), add the bias, apply the activation, store NHWC / row-major.
-//   warps 6-9   (convolution only) A gatherers: 16-byte loads of the im2col rows
+//   warps 2-9   epilogue: tcgen05.ld the accumulator (32 lanes x 32 columns per
+//               load), add the bias, apply the activation, stage through shared
+//               memory and store whole rows (NHWC / row-major).
+//   warps 10-13 (convolution only) A gatherers: 16-byte loads of the im2col rows
 //               straight from the NHWC input (zeros for taps outside the image),
 //               rounded to TF32 and stored in the same swizzled layout TMA would
 //               produce.
@@ -153,17 +154,78 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
          (1ull << 46) | (1ull << 61);
 }
 
+// Bias + activation on the 32 accumulator columns a thread holds, with the
+// activation resolved at compile time so the unrolled loop has no per-element
+// dispatch.
+template <int ACT>
+__device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0) {
+  const bool full = n0 + 32 <= g.N;
+  if (g.bias_len == 1) {
+    const float b = __ldg(g.bias);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], b);
+  } else if (g.bias_len > 1) {
+    if (full && (g.N & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j);
+        v[4 * j] = __fadd_rn(v[4 * j], b.x);
+        v[4 * j + 1] = __fadd_rn(v[4 * j + 1], b.y);
+        v[4 * j + 2] = __fadd_rn(v[4 * j + 2], b.z);
+        v[4 * j + 3] = __fadd_rn(v[4 * j + 3], b.w);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        v[j] = __fadd_rn(v[j], __ldg(g.bias + (n0 + j < g.N ? n0 + j : 0)));
+    }
+  }
+  if (ACT == TFJS_CUDA_ACT_LINEAR) return;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float t = v[j];
+    if (ACT == TFJS_CUDA_ACT_RELU) {
+      const float r = fmaxf(t, 0.0f);
+      v[j] = t != t ? t : r;
+    } else if (ACT == TFJS_CUDA_ACT_RELU6) {
+      const float r = fminf(fmaxf(t, 0.0f), 6.0f);
+      v[j] = t != t ? t : r;
+    } else if (ACT == TFJS_CUDA_ACT_PRELU) {
+      const float a = __ldg(g.ap.prelu + (g.ap.prelu_len == 1 ? 0 : (n0 + j < g.N ? n0 + j : 0)));
+      v[j] = t < 0.0f ? __fmul_rn(a, t) : t;
+    } else if (ACT == TFJS_CUDA_ACT_LEAKYRELU) {
+      v[j] = js_leakyrelu(t, g.ap.alpha);
+    } else if (ACT == TFJS_CUDA_ACT_SIGMOID) {
+      v[j] = js_sigmoid(t);
+    } else if (ACT == TFJS_CUDA_ACT_ELU) {
+      v[j] = js_elu(t);
+    }
+  }
+}
+
+__device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g, int n0) {
+  switch (g.ap.act) {
+    case TFJS_CUDA_ACT_RELU: chunk_math<TFJS_CUDA_ACT_RELU>(v, g, n0); break;
+    case TFJS_CUDA_ACT_RELU6: chunk_math<TFJS_CUDA_ACT_RELU6>(v, g, n0); break;
+    case TFJS_CUDA_ACT_PRELU: chunk_math<TFJS_CUDA_ACT_PRELU>(v, g, n0); break;
+    case TFJS_CUDA_ACT_LEAKYRELU: chunk_math<TFJS_CUDA_ACT_LEAKYRELU>(v, g, n0); break;
+    case TFJS_CUDA_ACT_SIGMOID: chunk_math<TFJS_CUDA_ACT_SIGMOID>(v, g, n0); break;
+    case TFJS_CUDA_ACT_ELU: chunk_math<TFJS_CUDA_ACT_ELU>(v, g, n0); break;
+    default: chunk_math<TFJS_CUDA_ACT_LINEAR>(v, g, n0); break;
+  }
+}
+
 template <int BN>
 struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
   static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int SMEM_BYTES =
-      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 8 * 4096;
 };
 
 template <int BN, int B_MN, int A_GATHER>
-__global__ void __launch_bounds__(A_GATHER ? 320 : 192, 1)
+__global__ void __launch_bounds__(A_GATHER ? 448 : 320, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_b, const Tf32Args g) {
   using C = Cfg<BN>;
@@ -179,6 +241,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t epi_base = bar_base + 256u;  // 8 x 4 KB epilogue staging tiles
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -190,7 +253,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 128);
+      mbar_init(tempty_bar(a), 256);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -288,10 +351,18 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (alive) tc_commit(tfull_bar(acc));
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 10) {
     // ----------------------------------------------------------- epilogue --
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const int row_in_tile = q * 32 + lane;
+    // Each warp owns 32 rows of the tile.  A 32-column chunk comes out of TMEM
+    // with one row per lane; it is staged through a swizzled 4 KB shared-memory
+    // tile so that the global stores run along rows: full 128-byte lines, or one
+    // contiguous run when the tile spans the whole row.
+    // Two warps share each TMEM lane quarter and take alternate chunks.
+    const int q = warp & 3;           // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2; // 0: even chunks, 1: odd chunks
+    const uint32_t stage_buf = epi_base + (uint32_t)(warp - 2) * 4096u;
+    const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
+    const uint32_t sw = (uint32_t)(lane & 7);
     const bool vec4 = (g.N & 3) == 0;
     int it = 0;
     for (int tile = blockIdx.x; tile < g.total_tiles; tile += gridDim.x, ++it) {
@@ -306,37 +377,64 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         break;
       }
       tc_fence_after();
-      const int m = mt * BM + row_in_tile;
-      float* crow = g.c + ((long long)bz * g.M + m) * g.N;
+      const int m_base = mt * BM + q * 32;
+      const int rows_valid = g.M - m_base < 32 ? g.M - m_base : 32;
+      float* cbase = g.c + ((long long)bz * g.M + m_base) * g.N;
+      bool released = false;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = half * 32; c0 < BN; c0 += 64) {
         const int n0 = nt * BN + c0;
         if (n0 >= g.N) break;
+        const int w = g.N - n0 < 32 ? g.N - n0 : 32;
         float v[32];
         tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), v);
-        if (m < g.M) {
+        if (c0 + 64 >= BN || n0 + 64 >= g.N) {
+          // last read of this accumulator by this warp: hand it back early
+          tc_fence_before();
+          mbar_arrive(tempty_bar(acc));
+          released = true;
+        }
+        chunk_math_dispatch(v, g, n0);
+        __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = n0 + j;
-            float t = v[j];
-            if (g.bias_len) t = __fadd_rn(t, g.bias[g.bias_len == 1 ? 0 : (n < g.N ? n : 0)]);
-            v[j] = apply_act(t, g.ap, n < g.N ? n : 0);
-          }
+        for (int j = 0; j < 8; ++j)
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(
+                           my_row + (((uint32_t)j ^ sw) << 4)),
+                       "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                       : "memory");
+        __syncwarp();
+        if (rows_valid > 0) {
           if (vec4) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              if (n0 + j < g.N)
-                *reinterpret_cast<float4*>(crow + n0 + j) =
-                    make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            const int qv = w >> 2;
+            const int total = rows_valid * qv;
+            for (int idx = lane; idx < total; idx += 32) {
+              const int row = idx / qv, vv = idx - row * qv;
+              float4 val;
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(val.x), "=f"(val.y), "=f"(val.z), "=f"(val.w)
+                           : "r"(stage_buf + (uint32_t)row * 128u +
+                                 (((uint32_t)vv ^ (uint32_t)(row & 7)) << 4)));
+              *reinterpret_cast<float4*>(cbase + (long long)row * g.N + n0 + vv * 4) = val;
+            }
           } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < g.N) crow[n0 + j] = v[j];
+            const int total = rows_valid * w;
+            for (int idx = lane; idx < total; idx += 32) {
+              const int row = idx / w, col = idx - row * w;
+              float val;
+              asm volatile("ld.shared.f32 %0, [%1];"
+                           : "=f"(val)
+                           : "r"(stage_buf + (uint32_t)row * 128u +
+                                 ((((uint32_t)col >> 2) ^ (uint32_t)(row & 7)) << 4) +
+                                 ((uint32_t)col & 3u) * 4u));
+              cbase[(long long)row * g.N + n0 + col] = val;
+            }
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(tempty_bar(acc));
+      if (!released) {
+        tc_fence_before();
+        mbar_arrive(tempty_bar(acc));
+      }
     }
   } else if (A_GATHER) {
     // ----------------------------------------------------- im2col gatherers --
@@ -345,7 +443,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     // (nearest-even, the rounding the TMA unit applies to the other operands) and
     // stores them in the 128-byte-swizzled layout.  The loads of step i+1 are
     // issued before the stores of step i, so two steps are in flight per thread.
-    const int r = threadIdx.x - 192;
+    const int r = threadIdx.x - 320;
     const ConvGeo& cv = g.conv;
     const uint32_t row_off = (uint32_t)r * 128u;
     const uint32_t sw = (uint32_t)(r & 7);
@@ -465,7 +563,10 @@ int make_map(tfjs_cuda_ctx* ctx, CUtensorMap* tm, const float* base, uint64_t in
   // even) on its way into shared memory.  With the plain FLOAT32 type the tensor
   // core would truncate the low 13 mantissa bits, a bias toward zero that
   // compounds layer after layer.
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 3, (void*)base, dims, strides, box,
+  static int plain = -1;
+  if (plain < 0) plain = getenv("TFJS_CUDA_TMA_FLOAT32") ? 1 : 0;  // debugging knob
+  CUresult r = enc(tm, plain ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32,
+                   3, (void*)base, dims, strides, box,
                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -491,7 +592,7 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
   g.tiles_n = (g.N + BN - 1) / BN;
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
-  kern<<<grid, A_GATHER ? 320 : 192, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, g);
+  kern<<<grid, A_GATHER ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, g);
   LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
   return TFJS_CUDA_OK;
 }
