@@ -98,6 +98,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm,
       "l"(tm), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_im2col(uint32_t dst, const CUtensorMap* tm,
+                                                uint32_t bar, int c, int w, int h, int n,
+                                                uint16_t off_w, uint16_t off_h) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
+      "l"(tm), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -224,8 +233,8 @@ struct Cfg {
       1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 8 * 4096;
 };
 
-template <int BN, int B_MN, int A_GATHER>
-__global__ void __launch_bounds__(A_GATHER ? 448 : 320, 1)
+template <int BN, int B_MN, int A_MODE>
+__global__ void __launch_bounds__(A_MODE == 1 ? 448 : 320, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_b, const Tf32Args g) {
   using C = Cfg<BN>;
@@ -248,7 +257,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), A_GATHER ? 1 + 128 : 1);
+      mbar_init(full_bar(s), A_MODE == 1 ? 1 + 128 : 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -284,6 +293,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         const int rest = tile / g.tiles_n;
         const int mt = rest % g.tiles_m;
         const int bz = rest / g.tiles_m;
+        int pix_w = 0, pix_h = 0, pix_n = 0;
+        if (A_MODE == 2) {
+          const int m0 = mt * BM;
+          const int ow = m0 % g.conv.out_w;
+          const int t = m0 / g.conv.out_w;
+          pix_w = ow * g.conv.s_w - g.conv.pad_l;
+          pix_h = (t % g.conv.out_h) * g.conv.s_h - g.conv.pad_t;
+          pix_n = t / g.conv.out_h;
+        }
         for (int ks = 0; ks < k_steps; ++ks) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
             atomicExch(g.flag, 1);
@@ -291,10 +309,19 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
             break;
           }
           const uint32_t fb = full_bar(stage);
-          mbar_expect_tx(fb, (A_GATHER ? 0 : A_STAGE_BYTES) + C::B_STAGE_BYTES);
-          if (!A_GATHER)
+          mbar_expect_tx(fb, (A_MODE == 1 ? 0 : A_STAGE_BYTES) + C::B_STAGE_BYTES);
+          if (A_MODE == 0) {
             tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_a, fb, ks * BK, mt * BM,
                         bz % g.batch_a);
+          } else if (A_MODE == 2) {
+            // im2col load: 128 consecutive output pixels starting at the tile's
+            // first one, 32 channels of filter tap (fr, fc)
+            const int tap = ks / g.chunks_per_tap;
+            const int cc = (ks - tap * g.chunks_per_tap) * BK;
+            const int fr = tap / g.conv.f_w, fc = tap - fr * g.conv.f_w;
+            tma_load_im2col(a_base + stage * A_STAGE_BYTES, &tm_a, fb, cc, pix_w, pix_h, pix_n,
+                            (uint16_t)(fc * g.conv.d_w), (uint16_t)(fr * g.conv.d_h));
+          }
           const uint32_t bdst = b_base + stage * C::B_STAGE_BYTES;
           if (!B_MN) {
             tma_load_3d(bdst, &tm_b, fb, ks * BK, nt * BN, bz % g.batch_b);
@@ -436,7 +463,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         mbar_arrive(tempty_bar(acc));
       }
     }
-  } else if (A_GATHER) {
+  } else if (A_MODE == 1) {
     // ----------------------------------------------------- im2col gatherers --
     // Thread r owns row r of every A tile.  Each K step it reads 32 channels of
     // one filter tap (8 x 16 bytes) into registers, rounds them to TF32
@@ -578,11 +605,55 @@ int make_map(tfjs_cuda_ctx* ctx, CUtensorMap* tm, const float* base, uint64_t in
   return TFJS_CUDA_OK;
 }
 
-template <int BN, int B_MN, int A_GATHER>
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// im2col map over NHWC x: dims (C, W, H, N); 32 channels x 128 pixels per load;
+// the pixel bounding box starts at -pad and ends where the last filter tap still
+// fits, and pixels are traversed with the convolution stride.
+bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv) {
+  static EncodeIm2colFn enc = nullptr;
+  if (!enc) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &p, cudaEnableDefault, &q) !=
+            cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return false;
+    enc = (EncodeIm2colFn)p;
+  }
+  const int eff_w = (cv.f_w - 1) * cv.d_w, eff_h = (cv.f_h - 1) * cv.d_h;
+  // right/bottom padding implied by the output size
+  const int pad_r = (cv.out_w - 1) * cv.s_w + eff_w + 1 - cv.in_w - cv.pad_l;
+  const int pad_b = (cv.out_h - 1) * cv.s_h + eff_h + 1 - cv.in_h - cv.pad_t;
+  int lower[2] = {-cv.pad_l, -cv.pad_t};
+  int upper[2] = {pad_r - eff_w, pad_b - eff_h};
+  // the box must yield exactly out_w x out_h base pixels
+  if ((cv.in_w + upper[0] - lower[0] - 1) / cv.s_w + 1 != cv.out_w ||
+      (cv.in_h + upper[1] - lower[1] - 1) / cv.s_h + 1 != cv.out_h)
+    return false;
+  for (int i = 0; i < 2; ++i)
+    if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return false;
+  if (eff_w > 255 || eff_h > 255 || cv.s_w > 8 || cv.s_h > 8 || (cv.in_c & 3)) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)cv.in_c, (cuuint64_t)cv.in_w, (cuuint64_t)cv.in_h,
+                        (cuuint64_t)cv.batch};
+  cuuint64_t strides[3] = {(cuuint64_t)cv.in_c * 4, (cuuint64_t)cv.in_w * cv.in_c * 4,
+                           (cuuint64_t)cv.in_h * cv.in_w * cv.in_c * 4};
+  cuuint32_t estr[4] = {1, (cuuint32_t)cv.s_w, (cuuint32_t)cv.s_h, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void*)x, dims, strides, lower,
+                   upper, BK, BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, int B_MN, int A_MODE>
 int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                Tf32Args& g) {
   using C = Cfg<BN>;
-  auto kern = gemm_tf32_kernel<BN, B_MN, A_GATHER>;
+  auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE>;
   static bool configured[64] = {false};  // per device ordinal
   if (ctx->device >= 64 || !configured[ctx->device]) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -592,19 +663,19 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
   g.tiles_n = (g.N + BN - 1) / BN;
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
-  kern<<<grid, A_GATHER ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, g);
+  kern<<<grid, A_MODE == 1 ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, g);
   LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
   return TFJS_CUDA_OK;
 }
 
-template <int B_MN, int A_GATHER>
+template <int B_MN, int A_MODE>
 int launch_bn(tfjs_cuda_ctx* ctx, int bn, const CUtensorMap& a, const CUtensorMap& b,
               Tf32Args& g) {
   switch (bn) {
-    case 32: return launch_cfg<32, B_MN, A_GATHER>(ctx, a, b, g);
-    case 64: return launch_cfg<64, B_MN, A_GATHER>(ctx, a, b, g);
-    case 128: return launch_cfg<128, B_MN, A_GATHER>(ctx, a, b, g);
-    default: return launch_cfg<256, B_MN, A_GATHER>(ctx, a, b, g);
+    case 32: return launch_cfg<32, B_MN, A_MODE>(ctx, a, b, g);
+    case 64: return launch_cfg<64, B_MN, A_MODE>(ctx, a, b, g);
+    case 128: return launch_cfg<128, B_MN, A_MODE>(ctx, a, b, g);
+    default: return launch_cfg<256, B_MN, A_MODE>(ctx, a, b, g);
   }
 }
 
@@ -639,9 +710,12 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   const int bn = pick_bn(pr.M, pr.N, pr.batch, ctx->sm_count);
   CUtensorMap tm_a, tm_b;
   int rc;
+  bool im2col = false;
   if (op.a_gather) {
-    // A is gathered; the kernel still takes a map argument, so alias B's.
+    static int no_im2col = -1;
+    if (no_im2col < 0) no_im2col = getenv("TFJS_CUDA_NO_IM2COL_TMA") ? 1 : 0;  // debugging knob
     memset(&tm_a, 0, sizeof tm_a);
+    im2col = !no_im2col && make_im2col_map(&tm_a, op.a, pr.conv);
   } else {
     if ((rc = make_map(ctx, &tm_a, op.a, (uint64_t)pr.K, (uint64_t)pr.M,
                        (uint64_t)pr.batch_a, (uint64_t)op.lda,
@@ -654,8 +728,9 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     if ((rc = make_map(ctx, &tm_b, op.b, kk, (uint64_t)pr.N, (uint64_t)pr.batch_b,
                        (uint64_t)op.ldb, (uint64_t)pr.N * op.ldb, (uint32_t)bn)))
       return rc;
+    if (im2col) return launch_bn<0, 2>(ctx, bn, tm_a, tm_b, g);
     if (op.a_gather) {
-      tm_a = tm_b;
+      tm_a = tm_b;  // unused by the gather kernel
       return launch_bn<0, 1>(ctx, bn, tm_a, tm_b, g);
     }
     return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, g);
@@ -664,9 +739,7 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
                      (uint64_t)pr.batch_b, (uint64_t)op.ldb, (uint64_t)pr.K * op.ldb, 32,
                      CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)))
     return rc;
-  if (op.a_gather) {
-    tm_a = tm_b;
-    return launch_bn<1, 1>(ctx, bn, tm_a, tm_b, g);
-  }
+  if (op.a_gather)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "convolution filters are always packed K-major");
   return launch_bn<1, 0>(ctx, bn, tm_a, tm_b, g);
 }
