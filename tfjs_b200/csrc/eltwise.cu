@@ -192,23 +192,50 @@ __global__ void binary_periodic_kernel(const float* __restrict__ full,
   }
 }
 
-template <int OP, typename T>
+// One operand is the full tensor viewed as [rows, cols]; the other has one value
+// per row (shape [..., 1], e.g. the mean / rsqrt terms of a layer norm).  cols % 4 == 0.
+template <int OP>
+__global__ void binary_rowscalar_kernel(const float* __restrict__ full,
+                                        const float* __restrict__ per_row,
+                                        float* __restrict__ o, uint64_t n, uint32_t cols,
+                                        bool swap) {
+  const uint64_t n4 = n >> 2;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const float4* f4 = reinterpret_cast<const float4*>(full);
+  float4* o4 = reinterpret_cast<float4*>(o);
+  const uint32_t c4 = cols >> 2;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 u = f4[i];
+    const float v = __ldg(per_row + i / c4);
+    float4 r;
+    r.x = swap ? binary_eval<OP>(v, u.x) : binary_eval<OP>(u.x, v);
+    r.y = swap ? binary_eval<OP>(v, u.y) : binary_eval<OP>(u.y, v);
+    r.z = swap ? binary_eval<OP>(v, u.z) : binary_eval<OP>(u.z, v);
+    r.w = swap ? binary_eval<OP>(v, u.w) : binary_eval<OP>(u.w, v);
+    o4[i] = r;
+  }
+}
+
+// I is the index type: uint32_t when every extent fits, which keeps the per-element
+// div/mod chain in 32-bit arithmetic.
+template <int OP, typename T, typename I>
 __global__ void binary_general_kernel(const T* __restrict__ a,
                                       const T* __restrict__ b, T* __restrict__ o,
                                       uint64_t n, int rank, Dims oshape,
                                       Dims astride, Dims bstride) {
-  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += stride) {
-    uint64_t rem = i;
-    long long ai = 0, bi = 0;
+  const I stride = (I)gridDim.x * blockDim.x;
+  for (I i = (I)blockIdx.x * blockDim.x + threadIdx.x; i < (I)n; i += stride) {
+    I rem = i;
+    I ai = 0, bi = 0;
     for (int d = rank - 1; d >= 0; --d) {
-      const uint64_t c = rem % (uint64_t)oshape.v[d];
-      rem /= (uint64_t)oshape.v[d];
-      ai += (long long)c * astride.v[d];
-      bi += (long long)c * bstride.v[d];
+      const I ext = (I)oshape.v[d];
+      const I q = rem / ext;
+      const I c = rem - q * ext;
+      rem = q;
+      ai += c * (I)astride.v[d];
+      bi += c * (I)bstride.v[d];
     }
-    if (sizeof(T) == 4 && ((T)0.5f != (T)0))  // float
+    if ((T)0.5f != (T)0)  // T is float
       o[i] = (T)binary_eval<OP>((float)a[ai], (float)b[bi]);
     else
       o[i] = (T)binary_eval_i32<OP>((int32_t)a[ai], (int32_t)b[bi]);
@@ -279,19 +306,19 @@ __global__ void copy_strided_kernel(const T* __restrict__ x, T* __restrict__ o,
 // ------------------------------------------------------------- transpose ----
 // Output-major traversal: writes are coalesced, reads are gathered through L2.
 // T is the moved unit (1, 4 or 16 bytes; 16 when the innermost axis stays put).
-template <typename T>
+template <typename T, typename I>
 __global__ void transpose_kernel(const T* __restrict__ x, T* __restrict__ o,
                                  uint64_t n, int rank, Dims oshape,
                                  Dims xstride_for_out) {
-  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += stride) {
-    uint64_t rem = i;
-    long long xi = 0;
+  const I stride = (I)gridDim.x * blockDim.x;
+  for (I i = (I)blockIdx.x * blockDim.x + threadIdx.x; i < (I)n; i += stride) {
+    I rem = i;
+    I xi = 0;
     for (int d = rank - 1; d >= 0; --d) {
-      const uint64_t c = rem % (uint64_t)oshape.v[d];
-      rem /= (uint64_t)oshape.v[d];
-      xi += (long long)c * xstride_for_out.v[d];
+      const I ext = (I)oshape.v[d];
+      const I q = rem / ext;
+      xi += (rem - q * ext) * (I)xstride_for_out.v[d];
+      rem = q;
     }
     o[i] = x[xi];
   }
@@ -472,7 +499,21 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
         if (s[e] != out_shape[e]) return false;
       return cnt <= 0xffffffffu;
     };
+    auto row_scalar = [&](const int64_t* s, uint64_t cnt) -> bool {
+      // s equals out_shape except for a trailing 1, and rows of 4k floats
+      if (rank < 1 || s[rank - 1] != 1 || out_shape[rank - 1] % 4 != 0 ||
+          out_shape[rank - 1] > 0xffffffffll)
+        return false;
+      for (int e = 0; e < rank - 1; ++e)
+        if (s[e] != out_shape[e]) return false;
+      return cnt * (uint64_t)out_shape[rank - 1] == n;
+    };
     if (na == n && nb == n) mode = 0;
+    else if (na == n && nb > 1 && row_scalar(b_shape, nb)) {
+      mode = 3; period = (uint32_t)out_shape[rank - 1]; swap = false;
+    } else if (nb == n && na > 1 && row_scalar(a_shape, na)) {
+      mode = 3; period = (uint32_t)out_shape[rank - 1]; swap = true;
+    }
     else if (na == n && suffix_period(b_shape, nb) && (nb == 1 || nb % 4 == 0)) {
       mode = 1; period = (uint32_t)nb; swap = false;
     } else if (nb == n && suffix_period(a_shape, na) && (na == 1 || na % 4 == 0)) {
@@ -482,6 +523,7 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
   const float* ap = (const float*)a->ptr;
   const float* bp = (const float*)b->ptr;
   float* op_ = (float*)o->ptr;
+  const bool small = n < 0x7fffffffull && na < 0x7fffffffull && nb < 0x7fffffffull;
 #define BIN_CASE(OP)                                                              \
   case OP:                                                                        \
     if (mode == 0)                                                                \
@@ -495,12 +537,20 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
       binary_periodic_kernel<OP, true>                                            \
           <<<grid_for((n + 3) / 4, kThreads, ctx->sm_count), kThreads, 0,         \
              ctx->stream>>>(bp, ap, op_, n, period);                              \
+    else if (mode == 3)                                                           \
+      binary_rowscalar_kernel<OP><<<grid_for((n + 3) / 4, kThreads, ctx->sm_count), \
+                                    kThreads, 0, ctx->stream>>>(                  \
+          swap ? bp : ap, swap ? ap : bp, op_, n, period, swap);                  \
+    else if (dtype == TFJS_CUDA_FLOAT32 && small)                                 \
+      binary_general_kernel<OP, float, uint32_t>                                  \
+          <<<grid_for(n, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(   \
+              ap, bp, op_, n, rank, os, as, bs);                                  \
     else if (dtype == TFJS_CUDA_FLOAT32)                                          \
-      binary_general_kernel<OP, float>                                            \
+      binary_general_kernel<OP, float, uint64_t>                                  \
           <<<grid_for(n, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(   \
               ap, bp, op_, n, rank, os, as, bs);                                  \
     else                                                                          \
-      binary_general_kernel<OP, int32_t>                                          \
+      binary_general_kernel<OP, int32_t, uint64_t>                                \
           <<<grid_for(n, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(   \
               (const int32_t*)a->ptr, (const int32_t*)b->ptr, (int32_t*)o->ptr,   \
               n, rank, os, as, bs);                                               \
@@ -720,20 +770,28 @@ int tfjs_cuda_transpose(tfjs_cuda_ctx* ctx, int32_t elem_bytes, int32_t rank,
       os.v[r2 - 1] /= 4;
       for (int d = 0; d < r2 - 1; ++d) xs.v[d] /= 4;
       const uint64_t n4 = n / 4;
-      transpose_kernel<uint4><<<grid_for(n4, kThreads, ctx->sm_count), kThreads, 0,
-                                ctx->stream>>>((const uint4*)x->ptr, (uint4*)o->ptr,
-                                               n4, r2, os, xs);
+      if (n < 0x7fffffffull)
+        transpose_kernel<uint4, uint32_t><<<grid_for(n4, kThreads, ctx->sm_count), kThreads, 0,
+                                            ctx->stream>>>((const uint4*)x->ptr,
+                                                           (uint4*)o->ptr, n4, r2, os, xs);
+      else
+        transpose_kernel<uint4, uint64_t><<<grid_for(n4, kThreads, ctx->sm_count), kThreads, 0,
+                                            ctx->stream>>>((const uint4*)x->ptr,
+                                                           (uint4*)o->ptr, n4, r2, os, xs);
       LAUNCH_CHECK(ctx, "transpose_kernel<uint4>");
       ctx_mark_written(ctx, out_id);
       return TFJS_CUDA_OK;
     }
   }
   const unsigned grid = grid_for(n, kThreads, ctx->sm_count);
-  if (elem_bytes == 4)
-    transpose_kernel<uint32_t><<<grid, kThreads, 0, ctx->stream>>>(
+  if (elem_bytes == 4 && n < 0x7fffffffull)
+    transpose_kernel<uint32_t, uint32_t><<<grid, kThreads, 0, ctx->stream>>>(
+        (const uint32_t*)x->ptr, (uint32_t*)o->ptr, n, r2, os, xs);
+  else if (elem_bytes == 4)
+    transpose_kernel<uint32_t, uint64_t><<<grid, kThreads, 0, ctx->stream>>>(
         (const uint32_t*)x->ptr, (uint32_t*)o->ptr, n, r2, os, xs);
   else
-    transpose_kernel<uint8_t><<<grid, kThreads, 0, ctx->stream>>>(
+    transpose_kernel<uint8_t, uint64_t><<<grid, kThreads, 0, ctx->stream>>>(
         (const uint8_t*)x->ptr, (uint8_t*)o->ptr, n, r2, os, xs);
   LAUNCH_CHECK(ctx, "transpose_kernel");
   ctx_mark_written(ctx, out_id);

@@ -132,6 +132,115 @@ __global__ void depthwise_kernel(const float* __restrict__ x,
   }
 }
 
+// 3x3, dilation 1, channel multiplier 1, C % 4 == 0 (every MobileNet layer).
+// blockIdx.y is the output row (b, oh); a thread owns 4 channels of S adjacent
+// output columns, so each input row segment is loaded once into registers and
+// reused by the S outputs, and all index arithmetic is 32-bit and per thread,
+// not per tap.  Filter taps and accumulation order are those of
+// DepthwiseConv2dNative.ts:62-99 ((wR, wC) per output element).
+template <int STRIDE, int S, int ACT>
+__global__ void __launch_bounds__(128)
+depthwise3x3_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                    const float* __restrict__ bias, int bias_len, ActParams ap,
+                    float* __restrict__ y, Geo g, int rows_total) {
+  constexpr int NC = (S - 1) * STRIDE + 3;  // input columns a strip touches
+  const int c4n = g.c >> 2;
+  const int strips = (g.out_w + S - 1) / S;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= strips * c4n) return;
+  const int c4 = t % c4n;
+  const int ow0 = (t / c4n) * S;
+  const float4* w4 = reinterpret_cast<const float4*>(w) + c4;
+  float4 wv[9];
+#pragma unroll
+  for (int k = 0; k < 9; ++k) wv[k] = __ldg(w4 + k * c4n);
+  float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (bias_len == 1) {
+    const float b0 = __ldg(bias);
+    bv = make_float4(b0, b0, b0, b0);
+  } else if (bias_len > 1) {
+    bv = __ldg(reinterpret_cast<const float4*>(bias) + c4);
+  }
+  const int c_lo = ow0 * STRIDE - g.pad_l;
+  for (int row = blockIdx.y; row < rows_total; row += gridDim.y) {
+    const int oh = row % g.out_h;
+    const int b = row / g.out_h;
+    float4 acc[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) acc[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int fr = 0; fr < 3; ++fr) {
+      const int r = oh * STRIDE - g.pad_t + fr;
+      if (r < 0 || r >= g.in_h) continue;
+      const float4* xrow =
+          reinterpret_cast<const float4*>(x) + ((size_t)b * g.in_h + r) * g.in_w * c4n + c4;
+      float4 xin[NC];
+#pragma unroll
+      for (int i = 0; i < NC; ++i) {
+        const int cc = c_lo + i;
+        xin[i] = (cc >= 0 && cc < g.in_w) ? __ldg(xrow + (size_t)cc * c4n)
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int s = 0; s < S; ++s) {
+#pragma unroll
+        for (int fc = 0; fc < 3; ++fc) {
+          // a tap outside the image is skipped by the reference; it adds 0 here
+          const float4 xv = xin[s * STRIDE + fc];
+          const float4 wk = wv[fr * 3 + fc];
+          acc[s].x = fmaf(xv.x, wk.x, acc[s].x);
+          acc[s].y = fmaf(xv.y, wk.y, acc[s].y);
+          acc[s].z = fmaf(xv.z, wk.z, acc[s].z);
+          acc[s].w = fmaf(xv.w, wk.w, acc[s].w);
+        }
+      }
+    }
+    float4* yrow = reinterpret_cast<float4*>(y) + ((size_t)row * g.out_w) * c4n + c4;
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      if (ow0 + s >= g.out_w) break;
+      float o[4] = {acc[s].x, acc[s].y, acc[s].z, acc[s].w};
+      const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float v = bias_len ? __fadd_rn(o[k], bb[k]) : o[k];
+        if (ACT == TFJS_CUDA_ACT_RELU) v = v != v ? v : fmaxf(v, 0.0f);
+        else if (ACT == TFJS_CUDA_ACT_RELU6) v = v != v ? v : fminf(fmaxf(v, 0.0f), 6.0f);
+        else if (ACT != TFJS_CUDA_ACT_LINEAR) v = apply_act(v, ap, c4 * 4 + k);
+        o[k] = v;
+      }
+      yrow[(size_t)(ow0 + s) * c4n] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+template <int STRIDE, int S>
+void launch_depthwise3x3(tfjs_cuda_ctx* ctx, const float* x, const float* w, const float* bias,
+                         int bias_len, const ActParams& ap, float* y, const Geo& g) {
+  const int c4n = g.c >> 2;
+  const int strips = (g.out_w + S - 1) / S;
+  const int rows_total = g.batch * g.out_h;
+  dim3 grid((strips * c4n + 127) / 128, rows_total < 65535 ? rows_total : 65535);
+  switch (ap.act) {
+    case TFJS_CUDA_ACT_LINEAR:
+      depthwise3x3_kernel<STRIDE, S, TFJS_CUDA_ACT_LINEAR><<<grid, 128, 0, ctx->stream>>>(
+          x, w, bias, bias_len, ap, y, g, rows_total);
+      break;
+    case TFJS_CUDA_ACT_RELU:
+      depthwise3x3_kernel<STRIDE, S, TFJS_CUDA_ACT_RELU><<<grid, 128, 0, ctx->stream>>>(
+          x, w, bias, bias_len, ap, y, g, rows_total);
+      break;
+    case TFJS_CUDA_ACT_RELU6:
+      depthwise3x3_kernel<STRIDE, S, TFJS_CUDA_ACT_RELU6><<<grid, 128, 0, ctx->stream>>>(
+          x, w, bias, bias_len, ap, y, g, rows_total);
+      break;
+    default:  // resolved per element by apply_act
+      depthwise3x3_kernel<STRIDE, S, TFJS_CUDA_ACT_ELU><<<grid, 128, 0, ctx->stream>>>(
+          x, w, bias, bias_len, ap, y, g, rows_total);
+      break;
+  }
+}
+
 // General channel multiplier: one thread per output element.
 __global__ void depthwise_chmul_kernel(const float* __restrict__ x,
                                        const float* __restrict__ w,
@@ -258,7 +367,15 @@ int tfjs_cuda_fused_depthwise_conv2d(tfjs_cuda_ctx* ctx,
   ap.alpha = p->leakyrelu_alpha;
   const float* bp = bias ? (const float*)bias->ptr : nullptr;
   const int bl = bias ? p->bias_len : 0;
-  if (ch_mul == 1 && g.c % 4 == 0)
+  const bool fast3x3 = ch_mul == 1 && g.c % 4 == 0 && g.f_h == 3 && g.f_w == 3 && g.d_h == 1 &&
+                       g.d_w == 1 && g.s_h == g.s_w && (g.s_h == 1 || g.s_h == 2);
+  if (fast3x3 && g.s_h == 1)
+    launch_depthwise3x3<1, 4>(ctx, (const float*)x->ptr, (const float*)w->ptr, bp, bl, ap,
+                              (float*)y->ptr, g);
+  else if (fast3x3)
+    launch_depthwise3x3<2, 2>(ctx, (const float*)x->ptr, (const float*)w->ptr, bp, bl, ap,
+                              (float*)y->ptr, g);
+  else if (ch_mul == 1 && g.c % 4 == 0)
     depthwise_kernel<4><<<grid_for(ny / 4, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
         (const float*)x->ptr, (const float*)w->ptr, bp, bl, ap, (float*)y->ptr, g);
   else if (ch_mul == 1)

@@ -9,7 +9,6 @@
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kWarpsPerBlock = kThreads / 32;
 
 __device__ __forceinline__ double warp_sum(double v) {
 #pragma unroll
@@ -32,10 +31,10 @@ __device__ __forceinline__ float warp_nan_max(float v) {
 
 // ---- softmax: tfjs-backend-cpu/src/kernels/Softmax.ts:50-67 -----------------
 // max -> a = fl32(x - max) -> e = fl32(exp(a)) -> s = fl32(sum_double(e)) ->
-// out = fl32(e / s).  One warp per row; up to 32 values per lane stay in
-// registers (rows up to 1024 wide); wider rows recompute e from global.
-constexpr int kRegCols = 32;
-
+// out = fl32(e / s).  One warp per row.
+// REGS values per lane stay in registers (rows up to 32*REGS wide); REGS == 0 is
+// the wide-row variant that re-reads its own output instead.
+template <int REGS>
 __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ y,
                                uint64_t rows, uint32_t cols) {
   const int lane = threadIdx.x & 31;
@@ -45,10 +44,10 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
     const float* xr = x + r * cols;
     float* yr = y + r * cols;
     float m = xr[0];
-    if (cols <= 32 * kRegCols) {
-      float v[kRegCols];
+    if (REGS > 0) {
+      float v[REGS > 0 ? REGS : 1];
 #pragma unroll
-      for (int j = 0; j < kRegCols; ++j) {
+      for (int j = 0; j < REGS; ++j) {
         const uint32_t c = lane + 32 * j;
         v[j] = c < cols ? xr[c] : -INFINITY;
         if (c < cols) m = nan_max(m, v[j]);
@@ -56,7 +55,7 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
       m = warp_nan_max(m);
       double s = 0.0;
 #pragma unroll
-      for (int j = 0; j < kRegCols; ++j) {
+      for (int j = 0; j < REGS; ++j) {
         const uint32_t c = lane + 32 * j;
         if (c < cols) {
           v[j] = (float)exp((double)__fsub_rn(v[j], m));
@@ -65,7 +64,7 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
       }
       const float sf = (float)warp_sum(s);
 #pragma unroll
-      for (int j = 0; j < kRegCols; ++j) {
+      for (int j = 0; j < REGS; ++j) {
         const uint32_t c = lane + 32 * j;
         if (c < cols) yr[c] = __fdiv_rn(v[j], sf);
       }
@@ -87,12 +86,6 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
 // ---- reductions over the middle axis of [outer, reduce, inner] ----------------
 // OP 0 sum, 1 mean (each element divided by n in fp32 first, Mean.ts:37-48),
 // 2 max.
-template <int OP>
-__device__ __forceinline__ void red_init(double& acc, float& mx, float first) {
-  acc = 0.0;
-  mx = first;
-}
-
 // inner == 1: one warp per output row, lanes stride the reduced axis.
 template <int OP>
 __global__ void reduce_rows_kernel(const float* __restrict__ x,
@@ -105,11 +98,25 @@ __global__ void reduce_rows_kernel(const float* __restrict__ x,
     const float* xr = x + r * reduce;
     double acc = 0.0;
     float mx = xr[0];
-    for (uint64_t j = lane; j < reduce; j += 32) {
-      const float v = xr[j];
-      if (OP == 0) acc += (double)v;
-      else if (OP == 1) acc += (double)__fdiv_rn(v, nf);
-      else mx = nan_max(mx, v);
+    if ((reduce & 3) == 0 && ((uintptr_t)x & 15) == 0) {
+      const float4* x4 = reinterpret_cast<const float4*>(xr);
+      for (uint32_t j = lane; j < (uint32_t)(reduce >> 2); j += 32) {
+        const float4 q = x4[j];
+        const float e[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (OP == 0) acc += (double)e[k];
+          else if (OP == 1) acc += (double)__fdiv_rn(e[k], nf);
+          else mx = nan_max(mx, e[k]);
+        }
+      }
+    } else {
+      for (uint64_t j = lane; j < reduce; j += 32) {
+        const float v = xr[j];
+        if (OP == 0) acc += (double)v;
+        else if (OP == 1) acc += (double)__fdiv_rn(v, nf);
+        else mx = nan_max(mx, v);
+      }
     }
     if (OP == 2) {
       mx = warp_nan_max(mx);
@@ -223,8 +230,19 @@ int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
   if (cols > 0xffffffffu)
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "softmax: row too wide");
   cudaSetDevice(ctx->device);
-  softmax_kernel<<<grid_for(rows * 32, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
-      (const float*)x->ptr, (float*)y->ptr, rows, (uint32_t)cols);
+  const unsigned grid = grid_for(rows * 32, kThreads, ctx->sm_count);
+  const float* xp = (const float*)x->ptr;
+  float* yp = (float*)y->ptr;
+  const uint32_t c32 = (uint32_t)cols;
+#define SOFTMAX(R) softmax_kernel<R><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32)
+  if (cols <= 32) SOFTMAX(1);
+  else if (cols <= 64) SOFTMAX(2);
+  else if (cols <= 128) SOFTMAX(4);
+  else if (cols <= 256) SOFTMAX(8);
+  else if (cols <= 512) SOFTMAX(16);
+  else if (cols <= 1024) SOFTMAX(32);
+  else SOFTMAX(0);
+#undef SOFTMAX
   LAUNCH_CHECK(ctx, "softmax_kernel");
   ctx_mark_written(ctx, out_id);
   return TFJS_CUDA_OK;
