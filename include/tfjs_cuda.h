@@ -293,6 +293,28 @@ int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_dtype_bytes,
                          int32_t to_dtype, int32_t q_id, double scale,
                          double min, uint64_t n, int32_t out_id);
 
+/* ---- tfjs_cuda_dequantize for callers that must not allocate device memory.
+ * No counterpart in the reference; it exists for hosts that load weights while
+ * device allocation is off limits -- for example an embedding application that
+ * has handed the whole GPU heap to its own arena, or a loader running while another
+ * component holds the allocator -- yet still need quantised weights expanded on the
+ * GPU.  Same arguments, same result, bit for bit, as tfjs_cuda_dequantize; `q_id`
+ * and `out_id` are the caller's existing tensors.  The one piece of scratch the
+ * kernel needs, the value lookup table, is a fixed 65536-entry (256 KiB) array
+ * compiled into the library; each GPU that loads the library carries it until the
+ * process ends.  The call performs no cudaMalloc / cudaFree and uses no pool.
+ *   - Limit: quantised types up to 2 bytes (uint8, uint16).  Anything wider would
+ *     overflow the table and is refused with TFJS_CUDA_UNSUPPORTED and a message.
+ *   - The first call on each device looks up the table's device address; make that
+ *     first call outside any stream capture.
+ *   - All calls on a GPU share the one table.  Each call rewrites every entry it
+ *     will read, so nothing carries over from earlier calls; but two calls whose
+ *     GPU work overlaps (two contexts on one device, or two host threads) would
+ *     overwrite each other's table.  Serialise them. */
+int tfjs_cuda_dequantize_static(tfjs_cuda_ctx* ctx, int32_t q_dtype_bytes,
+                                int32_t to_dtype, int32_t q_id, double scale,
+                                double min, uint64_t n, int32_t out_id);
+
 #ifdef __cplusplus
 }
 #endif

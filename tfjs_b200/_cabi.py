@@ -94,6 +94,8 @@ SIGNATURES = {
                                     c_uint64, c_double, c_int32]),
     "tfjs_cuda_dequantize": (c_int, [_CTX, c_int32, c_int32, c_int32, c_double,
                                      c_double, c_uint64, c_int32]),
+    "tfjs_cuda_dequantize_static": (c_int, [_CTX, c_int32, c_int32, c_int32, c_double,
+                                            c_double, c_uint64, c_int32]),
 }
 
 _lib = None

@@ -904,6 +904,84 @@ int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_dtype,
   return TFJS_CUDA_OK;
 }
 
+// ---- dequantisation without any allocation --------------------------------------
+// The lookup table lives in a fixed device array instead of a pool allocation.
+// 65536 entries cover the widest quantised type (uint16); 256 KiB per GPU, held
+// from library load until the process exits.
+#define TFJS_CUDA_STATIC_TABLE_ENTRIES 65536
+static __device__ __align__(256) uint32_t g_static_dequant_table[TFJS_CUDA_STATIC_TABLE_ENTRIES];
+// In host code the name above is only a handle for the symbol, not an address a
+// kernel can use; the real device address is looked up once per device.
+static uint32_t* g_static_table_addr[64];
+// Host staging for the table (no heap use on the call path).
+static uint32_t g_static_table_host[TFJS_CUDA_STATIC_TABLE_ENTRIES];
+
+int tfjs_cuda_dequantize_static(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_dtype,
+                                int32_t q_id, double scale, double min, uint64_t n,
+                                int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (q_bytes < 1)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "dequantize_static: q_dtype_bytes %d", q_bytes);
+  if (q_bytes > 2)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
+                    "dequantize_static: a %d-byte quantised type needs a lookup table larger "
+                    "than the fixed %d-entry table; the widest supported type is uint16",
+                    q_bytes, TFJS_CUDA_STATIC_TABLE_ENTRIES);
+  if (to_dtype != TFJS_CUDA_FLOAT32 && to_dtype != TFJS_CUDA_INT32)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "dequantize_static: target dtype %d", to_dtype);
+  if (ctx->device < 0 || ctx->device >= 64)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "dequantize_static: device ordinal %d",
+                    ctx->device);
+  Buffer *q, *o;
+  int rc;
+  if ((rc = ctx_get(ctx, q_id, n * q_bytes, "dequantize_static q", &q))) return rc;
+  if ((rc = ctx_get(ctx, out_id, n * 4, "dequantize_static out", &o))) return rc;
+  if (n == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  uint32_t* table = g_static_table_addr[ctx->device];
+  if (!table) {
+    // First call on this device: resolve the symbol with this device current.
+    void* addr = nullptr;
+    CUDA_TRY(ctx, cudaGetSymbolAddress(&addr, g_static_dequant_table));
+    table = g_static_table_addr[ctx->device] = (uint32_t*)addr;
+  }
+  const int entries = q_bytes == 1 ? 256 : 65536;
+  for (int v = 0; v < entries; ++v) {
+    const double d = (double)v * scale + min;
+    if (to_dtype == TFJS_CUDA_FLOAT32) {
+      const float f = (float)d;
+      memcpy(&g_static_table_host[v], &f, 4);
+    } else {
+      double r = floor(d);  // Math.round: ties toward +infinity
+      if (d - r >= 0.5) r += 1.0;
+      int32_t iv = 0;
+      if (isfinite(r)) {
+        double m = fmod(r, 4294967296.0);
+        if (m < 0) m += 4294967296.0;
+        iv = (int32_t)(uint32_t)m;
+      }
+      memcpy(&g_static_table_host[v], &iv, 4);
+    }
+  }
+  // Every entry a kernel can index is rewritten here, so nothing left over from
+  // an earlier call is ever read.  Pageable source: staged before the call returns.
+  CUDA_TRY(ctx, cudaMemcpyAsync(table, g_static_table_host, (size_t)entries * 4,
+                                cudaMemcpyHostToDevice, ctx->stream));
+  if (q_bytes == 1) {
+    dequant_u8_kernel<uint32_t><<<grid_for((n + 15) / 16, kThreads, ctx->sm_count),
+                                  kThreads, 0, ctx->stream>>>(
+        (const uint8_t*)q->ptr, (const uint32_t*)table, (uint32_t*)o->ptr, n);
+  } else {
+    dequant_u16_kernel<uint32_t><<<grid_for(n, kThreads, ctx->sm_count), kThreads, 0,
+                                   ctx->stream>>>(
+        (const uint16_t*)q->ptr, (const uint32_t*)table, (uint32_t*)o->ptr, n);
+  }
+  LAUNCH_CHECK(ctx, "dequant_kernel (static table)");
+  o->version++;           // any packed copy of the old contents is now stale
+  o->from_host = true;    // dequantised weights are constants
+  return TFJS_CUDA_OK;
+}
+
 int tfjs_cuda_flush_l2(tfjs_cuda_ctx* ctx) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
   cudaSetDevice(ctx->device);
