@@ -36,7 +36,8 @@ enum BLayout {
 struct Tf32Operands {
   const float* a = nullptr;  // K-major A: [batch_a][M][lda] (or x for a gathered conv)
   long long lda = 0;         // elements between consecutive rows of A
-  int a_gather = 0;          // 1: A is gathered from NHWC x by the conv geometry
+  int a_gather = 0;          // 1: A comes from NHWC x by the conv geometry, 32-channel chunks;
+                             // 2: same, one float at a time (channels not a multiple of 4)
   const float* b = nullptr;
   long long ldb = 0;         // elements between consecutive rows of the B storage
   int b_layout = B_K_MAJOR;

@@ -224,20 +224,24 @@ __device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g,
   }
 }
 
-template <int BN>
+constexpr int kTapTableEntries = 512;  // scalar-gather K limit (after padding to 32)
+
+template <int BN, int A_MODE = 0>
 struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  // the scalar-gather mode gives one stage up for its tap table
+  static constexpr int STAGES = (BN >= 256 ? 4 : (BN >= 128 ? 6 : 8)) - (A_MODE == 3 ? 1 : 0);
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int SMEM_BYTES =
-      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 8 * 4096;
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 8 * 4096 +
+      (A_MODE == 3 ? kTapTableEntries * 4 : 0);
 };
 
 template <int BN, int B_MN, int A_MODE>
-__global__ void __launch_bounds__(A_MODE == 1 ? 448 : 320, 1)
+__global__ void __launch_bounds__((A_MODE == 1 || A_MODE == 3) ? 448 : 320, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_b, const Tf32Args g) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, A_MODE>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -257,7 +261,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), A_MODE == 1 ? 1 + 128 : 1);
+      mbar_init(full_bar(s), (A_MODE == 1 || A_MODE == 3) ? 1 + 128 : 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -273,6 +277,21 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         "r"((uint32_t)C::TMEM_COLS)
         : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  const uint32_t tap_table = epi_base + 8u * 4096u;  // A_MODE 3 only
+  if (A_MODE == 3 && warp >= 10) {
+    // entry k: filter tap index in the top byte, element offset of (tap, channel)
+    // from the tile pixel's top-left input element in the low 24 bits
+    for (int k = threadIdx.x - 320; k < g.k_steps * BK; k += 128) {
+      uint32_t e = 0xff000000u;  // tap 255: padding beyond K, always zero
+      if (k < g.conv.f_h * g.conv.f_w * g.conv.in_c) {
+        const int tap = k / g.conv.in_c, c = k - tap * g.conv.in_c;
+        const int fr = tap / g.conv.f_w, fc = tap - fr * g.conv.f_w;
+        e = ((uint32_t)tap << 24) |
+            (uint32_t)((fr * g.conv.d_h * g.conv.in_w + fc * g.conv.d_w) * g.conv.in_c + c);
+      }
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(tap_table + 4u * k), "r"(e) : "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -309,7 +328,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
             break;
           }
           const uint32_t fb = full_bar(stage);
-          mbar_expect_tx(fb, (A_MODE == 1 ? 0 : A_STAGE_BYTES) + C::B_STAGE_BYTES);
+          mbar_expect_tx(fb, ((A_MODE == 1 || A_MODE == 3) ? 0 : A_STAGE_BYTES) + C::B_STAGE_BYTES);
           if (A_MODE == 0) {
             tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_a, fb, ks * BK, mt * BM,
                         bz % g.batch_a);
@@ -545,6 +564,75 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
   }
 
+  else if (A_MODE == 3 && warp >= 10) {
+    // ------------------------------------------- scalar im2col gatherers --
+    // For inputs whose channel count is not a multiple of 4 (the 3-channel stems).
+    // Thread r builds row r of the A tile one float at a time: k -> (tap, channel)
+    // through the tap table, taps outside the image read as zero (one validity bit
+    // per tap, computed once per tile), values rounded to TF32, stored swizzled.
+    const int r = threadIdx.x - 320;
+    const ConvGeo& cv = g.conv;
+    const uint32_t row_off = (uint32_t)r * 128u;
+    const uint32_t sw = (uint32_t)(r & 7);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x) {
+      const int mt = (tile / g.tiles_n) % g.tiles_m;
+      const int m = mt * BM + r;
+      unsigned long long mask = 0ull;
+      const float* base = g.x;
+      if (m < g.M) {
+        const int ow = m % cv.out_w;
+        const int t = m / cv.out_w;
+        const int oh = t % cv.out_h;
+        const int b = t / cv.out_h;
+        const int r0 = oh * cv.s_h - cv.pad_t, c0 = ow * cv.s_w - cv.pad_l;
+        int tap = 0;
+        for (int fr = 0; fr < cv.f_h; ++fr) {
+          const int ri = r0 + fr * cv.d_h;
+          for (int fc = 0; fc < cv.f_w; ++fc, ++tap) {
+            const int ci = c0 + fc * cv.d_w;
+            if (ri >= 0 && ri < cv.in_h && ci >= 0 && ci < cv.in_w) mask |= 1ull << tap;
+          }
+        }
+        base = g.x + (((long long)b * cv.in_h + r0) * cv.in_w + c0) * cv.in_c;
+      }
+      for (int ks = 0; ks < k_steps; ++ks) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          uint32_t e;
+          asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e) : "r"(tap_table + 4u * (ks * BK + j)));
+          const uint32_t tap = e >> 24;
+          const bool ok = tap < 64u && ((mask >> tap) & 1ull);
+          v[j] = ok ? __ldg(base + (e & 0xffffffu)) : 0.0f;
+        }
+        if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
+          atomicExch(g.flag, 6);
+          alive = false;
+          break;
+        }
+        const uint32_t dst = a_base + stage * A_STAGE_BYTES + row_off;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t w0, w1, w2, w3;
+          asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w0) : "f"(v[4 * j]));
+          asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w1) : "f"(v[4 * j + 1]));
+          asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w2) : "f"(v[4 * j + 2]));
+          asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w3) : "f"(v[4 * j + 3]));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                           dst + (((uint32_t)j ^ sw) << 4)),
+                       "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                       : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(full_bar(stage));
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -652,7 +740,7 @@ bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv) {
 template <int BN, int B_MN, int A_MODE>
 int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                Tf32Args& g) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, A_MODE>;
   auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE>;
   static bool configured[64] = {false};  // per device ordinal
   if (ctx->device >= 64 || !configured[ctx->device]) {
@@ -663,7 +751,7 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
   g.tiles_n = (g.N + BN - 1) / BN;
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
-  kern<<<grid, A_MODE == 1 ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, g);
+  kern<<<grid, (A_MODE == 1 || A_MODE == 3) ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, g);
   LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
   return TFJS_CUDA_OK;
 }
@@ -711,11 +799,13 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   CUtensorMap tm_a, tm_b;
   int rc;
   bool im2col = false;
-  if (op.a_gather) {
+  if (op.a_gather == 1) {
     static int no_im2col = -1;
     if (no_im2col < 0) no_im2col = getenv("TFJS_CUDA_NO_IM2COL_TMA") ? 1 : 0;  // debugging knob
     memset(&tm_a, 0, sizeof tm_a);
     im2col = !no_im2col && make_im2col_map(&tm_a, op.a, pr.conv);
+  } else if (op.a_gather == 2) {
+    memset(&tm_a, 0, sizeof tm_a);
   } else {
     if ((rc = make_map(ctx, &tm_a, op.a, (uint64_t)pr.K, (uint64_t)pr.M,
                        (uint64_t)pr.batch_a, (uint64_t)op.lda,
@@ -728,6 +818,10 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     if ((rc = make_map(ctx, &tm_b, op.b, kk, (uint64_t)pr.N, (uint64_t)pr.batch_b,
                        (uint64_t)op.ldb, (uint64_t)pr.N * op.ldb, (uint32_t)bn)))
       return rc;
+    if (op.a_gather == 2) {
+      tm_a = tm_b;  // unused by the gather kernel
+      return launch_bn<0, 3>(ctx, bn, tm_a, tm_b, g);
+    }
     if (im2col) return launch_bn<0, 2>(ctx, bn, tm_a, tm_b, g);
     if (op.a_gather) {
       tm_a = tm_b;  // unused by the gather kernel
