@@ -48,6 +48,7 @@ struct Tf32Args {
   int tiles_m, tiles_n, total_tiles;
   int k_steps;
   int* flag;
+  int c_tma;  // 1: the epilogue stores through the C tensor map (N % 4 == 0)
   // gathered convolution
   const float* x;
   ConvGeo conv;
@@ -240,21 +241,22 @@ struct Cfg {
 template <int BN, int B_MN, int A_MODE>
 __global__ void __launch_bounds__((A_MODE == 1 || A_MODE == 3) ? 448 : 320, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
-                 const __grid_constant__ CUtensorMap tm_b, const Tf32Args g) {
+                 const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_c, const Tf32Args g) {
   using C = Cfg<BN, A_MODE>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_base = smem_base;
   const uint32_t b_base = smem_base + STAGES * A_STAGE_BYTES;
-  const uint32_t bar_base = b_base + STAGES * C::B_STAGE_BYTES;
+  const uint32_t epi_base = b_base + STAGES * C::B_STAGE_BYTES;  // 8 x 4 KB staging tiles
+  const uint32_t bar_base = epi_base + 8u * 4096u;
   // barrier layout: full[STAGES], empty[STAGES], tfull[2], tempty[2], tmem slot
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
-  const uint32_t epi_base = bar_base + 256u;  // 8 x 4 KB epilogue staging tiles
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -278,7 +280,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  const uint32_t tap_table = epi_base + 8u * 4096u;  // A_MODE 3 only
+  const uint32_t tap_table = bar_base + 256u;  // A_MODE 3 only
   if (A_MODE == 3 && warp >= 10) {
     // entry k: filter tap index in the top byte, element offset of (tap, channel)
     // from the tile pixel's top-left input element in the low 24 bits
@@ -441,6 +443,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           released = true;
         }
         chunk_math_dispatch(v, g, n0);
+        if (g.c_tma) {
+          // the previous bulk store must have finished reading the staging tile
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        }
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -448,6 +454,20 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                            my_row + (((uint32_t)j ^ sw) << 4)),
                        "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
                        : "memory");
+        if (g.c_tma) {
+          // one bulk tensor store per 32 x 32 chunk; rows / columns beyond the
+          // tensor are clipped by the TMA unit
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0 && rows_valid > 0) {
+            asm volatile(
+                "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                ::"l"(&tm_c), "r"(stage_buf), "r"(n0), "r"(m_base), "r"(bz)
+                : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          continue;
+        }
         __syncwarp();
         if (rows_valid > 0) {
           if (vec4) {
@@ -482,6 +502,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         mbar_arrive(tempty_bar(acc));
       }
     }
+    if (g.c_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else if (A_MODE == 1) {
     // ----------------------------------------------------- im2col gatherers --
     // Thread r owns row r of every A tile.  Each K step it reads 32 channels of
@@ -739,7 +760,7 @@ bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv) {
 
 template <int BN, int B_MN, int A_MODE>
 int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
-               Tf32Args& g) {
+               const CUtensorMap& tm_c, Tf32Args& g) {
   using C = Cfg<BN, A_MODE>;
   auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE>;
   static bool configured[64] = {false};  // per device ordinal
@@ -751,19 +772,19 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
   g.tiles_n = (g.N + BN - 1) / BN;
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
-  kern<<<grid, (A_MODE == 1 || A_MODE == 3) ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, g);
+  kern<<<grid, (A_MODE == 1 || A_MODE == 3) ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, tm_c, g);
   LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
   return TFJS_CUDA_OK;
 }
 
 template <int B_MN, int A_MODE>
 int launch_bn(tfjs_cuda_ctx* ctx, int bn, const CUtensorMap& a, const CUtensorMap& b,
-              Tf32Args& g) {
+              const CUtensorMap& c, Tf32Args& g) {
   switch (bn) {
-    case 32: return launch_cfg<32, B_MN, A_MODE>(ctx, a, b, g);
-    case 64: return launch_cfg<64, B_MN, A_MODE>(ctx, a, b, g);
-    case 128: return launch_cfg<128, B_MN, A_MODE>(ctx, a, b, g);
-    default: return launch_cfg<256, B_MN, A_MODE>(ctx, a, b, g);
+    case 32: return launch_cfg<32, B_MN, A_MODE>(ctx, a, b, c, g);
+    case 64: return launch_cfg<64, B_MN, A_MODE>(ctx, a, b, c, g);
+    case 128: return launch_cfg<128, B_MN, A_MODE>(ctx, a, b, c, g);
+    default: return launch_cfg<256, B_MN, A_MODE>(ctx, a, b, c, g);
   }
 }
 
@@ -796,8 +817,23 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   g.conv = pr.conv;
   g.chunks_per_tap = op.cin_pad / BK;
   const int bn = pick_bn(pr.M, pr.N, pr.batch, ctx->sm_count);
-  CUtensorMap tm_a, tm_b;
+  CUtensorMap tm_a, tm_b, tm_c;
   int rc;
+  // output map for the epilogue's bulk stores: dims (N, M, batch), 32 x 32 boxes
+  memset(&tm_c, 0, sizeof tm_c);
+  g.c_tma = 0;
+  if ((pr.N & 3) == 0 && ((uintptr_t)pr.c & 15) == 0) {
+    EncodeTiledFn enc = get_encode();
+    cuuint64_t dims[3] = {(cuuint64_t)pr.N, (cuuint64_t)pr.M, (cuuint64_t)pr.batch};
+    cuuint64_t strides[2] = {(cuuint64_t)pr.N * 4, (cuuint64_t)pr.M * pr.N * 4};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (enc && enc(&tm_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)pr.c, dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+                   CUDA_SUCCESS)
+      g.c_tma = getenv("TFJS_CUDA_NO_TMA_STORE") ? 0 : 1;  // debugging knob
+  }
   bool im2col = false;
   if (op.a_gather == 1) {
     static int no_im2col = -1;
@@ -820,14 +856,14 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
       return rc;
     if (op.a_gather == 2) {
       tm_a = tm_b;  // unused by the gather kernel
-      return launch_bn<0, 3>(ctx, bn, tm_a, tm_b, g);
+      return launch_bn<0, 3>(ctx, bn, tm_a, tm_b, tm_c, g);
     }
-    if (im2col) return launch_bn<0, 2>(ctx, bn, tm_a, tm_b, g);
+    if (im2col) return launch_bn<0, 2>(ctx, bn, tm_a, tm_b, tm_c, g);
     if (op.a_gather) {
       tm_a = tm_b;  // unused by the gather kernel
-      return launch_bn<0, 1>(ctx, bn, tm_a, tm_b, g);
+      return launch_bn<0, 1>(ctx, bn, tm_a, tm_b, tm_c, g);
     }
-    return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, g);
+    return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, tm_c, g);
   }
   if ((rc = make_map(ctx, &tm_b, op.b, (uint64_t)pr.N, (uint64_t)pr.K,
                      (uint64_t)pr.batch_b, (uint64_t)op.ldb, (uint64_t)pr.K * op.ldb, 32,
@@ -835,5 +871,5 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     return rc;
   if (op.a_gather)
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "convolution filters are always packed K-major");
-  return launch_bn<1, 0>(ctx, bn, tm_a, tm_b, g);
+  return launch_bn<1, 0>(ctx, bn, tm_a, tm_b, tm_c, g);
 }
