@@ -251,23 +251,10 @@ def run_cuda(args, rank, world, local_rank):
     w = WORKLOADS[args.model]
     batch = args.batch or w["batch"]
 
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist_mod.init_process_group("gloo", rank=rank, world_size=world)
-        dist = dist_mod
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-
-    def max_over_ranks(x):
-        if dist is None:
-            return x
-        import torch
-        t = torch.tensor([x], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
+    from tfjs_b200.replicas import ReplicaGroup
+    group = ReplicaGroup(rank, world)
+    barrier = group.barrier
+    max_over_ranks = group.max_over_ranks
 
     model_json, weights = build_model(args.model, batch)
     gm = GraphModel(model_json, weights, eng)
@@ -394,9 +381,7 @@ def run_cuda(args, rank, world, local_rank):
     gm.dispose()
     if rank == 0:
         print(json.dumps(line))
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    group.close()
 
 
 def main():

@@ -1,0 +1,73 @@
+"""Batch-sharded replicas: one process per GPU, no collective on the data path.
+
+tfjs has no distributed runtime; its Engine is a per-process singleton with one
+active backend (tfjs-core/src/engine.ts:168-186), so several GPUs means several
+processes (or Node workers), each with its own backend instance bound to one
+device, each taking a contiguous slice of the batch; results are gathered on the
+host.  This module holds that host logic: rank discovery from the torchrun
+environment, the batch split, and the host-side barrier / max / gather used for
+timing and for collecting outputs.  The process group is gloo (CPU): nothing
+crosses NVLink and NCCL is not involved.
+"""
+import os
+
+import numpy as np
+
+
+def shard_range(total, world, rank):
+    """Contiguous ceil(total / world) slices; trailing ranks may get fewer (or no)
+    units."""
+    per = -(-total // world)
+    lo = min(rank * per, total)
+    return lo, min(lo + per, total)
+
+
+class ReplicaGroup(object):
+    def __init__(self, rank=None, world=None):
+        self.rank = int(os.environ.get("RANK", "0")) if rank is None else rank
+        self.world = int(os.environ.get("WORLD_SIZE", "1")) if world is None else world
+        self.local_rank = int(os.environ.get("LOCAL_RANK", str(self.rank)))
+        self._dist = None
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29511")
+            import torch.distributed as dist
+            if not dist.is_initialized():
+                dist.init_process_group("gloo", rank=self.rank, world_size=self.world)
+            self._dist = dist
+
+    def barrier(self):
+        if self._dist is not None:
+            self._dist.barrier()
+
+    def max_over_ranks(self, value):
+        if self._dist is None:
+            return float(value)
+        import torch
+        t = torch.tensor([float(value)], dtype=torch.float64)
+        self._dist.all_reduce(t, op=self._dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def sum_over_ranks(self, value):
+        if self._dist is None:
+            return float(value)
+        import torch
+        t = torch.tensor([float(value)], dtype=torch.float64)
+        self._dist.all_reduce(t, op=self._dist.ReduceOp.SUM)
+        return float(t[0])
+
+    def gather_to_root(self, array):
+        """Concatenates per-rank host arrays along axis 0 on rank 0 (None elsewhere)."""
+        if self._dist is None:
+            return np.asarray(array)
+        parts = [None] * self.world if self.rank == 0 else None
+        self._dist.gather_object(np.asarray(array), parts, dst=0)
+        if self.rank != 0:
+            return None
+        return np.concatenate([p for p in parts if p.shape[0] > 0], axis=0)
+
+    def close(self):
+        if self._dist is not None and self._dist.is_initialized():
+            self._dist.barrier()
+            self._dist.destroy_process_group()
+            self._dist = None
