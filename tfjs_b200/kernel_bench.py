@@ -1,0 +1,55 @@
+"""Per-kernel micro-benchmark of the 'cuda' backend: times one op through the public
+op front end with CUDA events on the backend's stream.
+
+    python -m tfjs_b200.kernel_bench <case> [iterations]
+
+cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072),
+pw_<hw>_<cin>_<cout>_<batch> (1x1 conv), c3_<hw>_<cin>_<cout>_<batch>_<stride> (3x3
+conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<batch>_<stride>
+(3x3 depthwise).  Prints ms, TFLOP/s and algorithmic GB/s (each tensor moved once).
+"""
+import sys
+
+import numpy as np
+
+import tfjs_b200
+from tfjs_b200 import ops
+
+eng=tfjs_b200.ENGINE; eng.set_backend('cuda'); be=eng.backend
+case=sys.argv[1]; iters=int(sys.argv[2]) if len(sys.argv)>2 else 3
+r=np.random.default_rng(0)
+def timeit(f, n):
+    for _ in range(2): f().dispose()
+    be.sync()
+    t=be.time(lambda: [f().dispose() for _ in range(n)])
+    return t['kernelMs']/n
+if case=='mm2a':
+    a=ops.tensor(r.standard_normal((4096,1024)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((1024,4096)).astype(np.float32)/32)
+    bias=ops.tensor(r.standard_normal(4096).astype(np.float32))
+    f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'relu6'); fl=2*4096*4096*1024; by=4*(4096*1024*2+4096*4096)
+elif case=='ffn':
+    a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
+    bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
+    f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'linear'); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
+elif case.startswith('pw'):   # pointwise conv: pw_<hw>_<cin>_<cout>_<batch>
+    _,hw,ci,co,bt=case.split('_'); hw,ci,co,bt=int(hw),int(ci),int(co),int(bt)
+    x=ops.tensor(r.standard_normal((bt,hw,hw,ci)).astype(np.float32)); w=ops.tensor(r.standard_normal((1,1,ci,co)).astype(np.float32)/8)
+    bias=ops.tensor(r.standard_normal(co).astype(np.float32))
+    f=lambda: ops.fused_conv2d(x,w,1,'same','NHWC',[1,1],None,bias,'relu6'); fl=2*bt*hw*hw*ci*co; by=4*(bt*hw*hw*(ci+co)+ci*co)
+elif case.startswith('c3'):   # 3x3 conv: c3_<hw>_<cin>_<cout>_<batch>_<stride>
+    _,hw,ci,co,bt,st=case.split('_'); hw,ci,co,bt,st=int(hw),int(ci),int(co),int(bt),int(st)
+    x=ops.tensor(r.standard_normal((bt,hw,hw,ci)).astype(np.float32)); w=ops.tensor(r.standard_normal((3,3,ci,co)).astype(np.float32)/24)
+    bias=ops.tensor(r.standard_normal(co).astype(np.float32))
+    f=lambda: ops.fused_conv2d(x,w,st,'same','NHWC',[1,1],None,bias,'relu'); ho=(hw+st-1)//st; fl=2*bt*ho*ho*9*ci*co; by=4*(bt*hw*hw*ci+bt*ho*ho*co+9*ci*co)
+elif case.startswith('stem'):   # stem_<hw>_<k>_<cout>_<batch>_<stride>
+    _,hw,k,co,bt,st=case.split('_'); hw,k,co,bt,st=int(hw),int(k),int(co),int(bt),int(st)
+    x=ops.tensor(r.standard_normal((bt,hw,hw,3)).astype(np.float32)); w=ops.tensor(r.standard_normal((k,k,3,co)).astype(np.float32)/8)
+    bias=ops.tensor(r.standard_normal(co).astype(np.float32))
+    f=lambda: ops.fused_conv2d(x,w,st,'same','NHWC',[1,1],None,bias,'relu6'); ho=(hw+st-1)//st; fl=2*bt*ho*ho*k*k*3*co; by=4*(bt*hw*hw*3+bt*ho*ho*co)
+elif case.startswith('dw'):   # depthwise: dw_<hw>_<c>_<batch>_<stride>
+    _,hw,c,bt,st=case.split('_'); hw,c,bt,st=int(hw),int(c),int(bt),int(st)
+    x=ops.tensor(r.standard_normal((bt,hw,hw,c)).astype(np.float32)); w=ops.tensor(r.standard_normal((3,3,c,1)).astype(np.float32)/3)
+    bias=ops.tensor(r.standard_normal(c).astype(np.float32))
+    f=lambda: ops.fused_depthwise_conv2d(x,w,st,'same','NHWC',[1,1],None,bias,'relu6'); ho=(hw+st-1)//st; fl=2*bt*ho*ho*9*c; by=4*(bt*hw*hw*c+bt*ho*ho*c)
+ms=timeit(f,iters)
+print('%s: %.4f ms  %.1f TFLOP/s  %.1f GB/s (algorithmic)'%(case,ms,fl/ms/1e9,by/ms/1e6))
