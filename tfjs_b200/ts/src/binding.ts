@@ -1,0 +1,101 @@
+/**
+ * Typed view of the N-API addon (binding/tfjs_cuda_binding.cc), one function per
+ * entry point of include/tfjs_cuda.h.
+ */
+// tslint:disable-next-line:no-require-imports
+const addon = require('../build/Release/tfjs_cuda_binding.node');
+
+export type Ctx = unknown;
+
+export interface CudaBinding {
+  create(deviceOrdinal: number): Ctx;
+  alloc(ctx: Ctx, nbytes: number): number;
+  free(ctx: Ctx, id: number): void;
+  write(ctx: Ctx, id: number, data: ArrayBufferView, nbytes: number): void;
+  read(ctx: Ctx, id: number, out: ArrayBufferView, nbytes: number): void;
+  sync(ctx: Ctx): void;
+  memory(ctx: Ctx): {numBytesInGPU: number, numBytesInGPUAllocated: number,
+                     poolHighWater: number, numDeviceBuffers: number};
+  timeBegin(ctx: Ctx): void;
+  timeEnd(ctx: Ctx): number;
+  setMathMode(ctx: Ctx, mode: number): void;
+  fusedConv2d(ctx: Ctx, params: ArrayBuffer, x: number, filter: number, bias: number,
+              prelu: number, out: number): void;
+  fusedDepthwiseConv2d(ctx: Ctx, params: ArrayBuffer, x: number, filter: number, bias: number,
+                       prelu: number, out: number): void;
+  fusedMatMul(ctx: Ctx, params: ArrayBuffer, a: number, b: number, bias: number, prelu: number,
+              out: number): void;
+  pool2d(ctx: Ctx, params: ArrayBuffer, isMax: number, x: number, out: number): void;
+  binary(ctx: Ctx, op: number, dtype: number, rank: number, a: number, aShape: BigInt64Array,
+         b: number, bShape: BigInt64Array, out: number, outShape: BigInt64Array): void;
+  unary(ctx: Ctx, op: number, p0: number, p1: number, x: number, n: number, out: number): void;
+  softmax(ctx: Ctx, x: number, rows: number, cols: number, out: number): void;
+  reduce(ctx: Ctx, op: number, x: number, outer: number, reduce: number, inner: number,
+         out: number): void;
+  argMax(ctx: Ctx, x: number, outer: number, reduce: number, inner: number, out: number): void;
+  transpose(ctx: Ctx, elemBytes: number, rank: number, x: number, xShape: BigInt64Array,
+            perm: Int32Array, out: number): void;
+  gather(ctx: Ctx, elemBytes: number, x: number, indices: number, batch: number, outer: number,
+         dim: number, slice: number, nIdx: number, out: number, check: number): number;
+  cast(ctx: Ctx, from: number, to: number, x: number, n: number, out: number): void;
+  copyStrided(ctx: Ctx, elemBytes: number, rank: number, extent: BigInt64Array, x: number,
+              xOff: number, xStrides: BigInt64Array, xWrap: BigInt64Array, out: number,
+              oOff: number, oStrides: BigInt64Array): void;
+  fill(ctx: Ctx, elemBytes: number, bits: number, out: number, n: number): void;
+  batchNorm(ctx: Ctx, x: number, n: number, mean: number, nMean: number, variance: number,
+            nVar: number, scale: number, nScale: number, offset: number, nOffset: number,
+            eps: number, out: number): void;
+  dequantize(ctx: Ctx, qBytes: number, toDtype: number, q: number, scale: number, min: number,
+             n: number, out: number): void;
+  dequantizeStatic(ctx: Ctx, qBytes: number, toDtype: number, q: number, scale: number,
+                   min: number, n: number, out: number): void;
+}
+
+export const binding = addon as CudaBinding;
+
+/** Enum values of include/tfjs_cuda.h. */
+export const ACTIVATION: {[name: string]: number} =
+    {linear: 0, relu: 1, relu6: 2, prelu: 3, leakyrelu: 4, sigmoid: 5, elu: 6};
+export const DTYPE: {[name: string]: number} = {float32: 0, int32: 1, bool: 2};
+export const BINARY_OP = {Add: 0, Sub: 1, Multiply: 2, RealDiv: 3, Maximum: 4, Minimum: 5, Pow: 6,
+                          SquaredDifference: 7, Prelu: 8};
+export const UNARY_OP = {Relu: 0, Relu6: 1, Elu: 2, Sigmoid: 3, LeakyRelu: 4, Exp: 5, Sqrt: 6,
+                         Rsqrt: 7, Square: 8, Tanh: 9, Neg: 10, ClipByValue: 11, Erf: 12, Abs: 13,
+                         Log: 14};
+export const REDUCE_OP = {Sum: 0, Mean: 1, Max: 2};
+
+/** tfjs_cuda_conv2d_params: 18 int32 fields, 4 bytes of padding, one double. */
+export function packConvParams(
+    ci: {batchSize: number, inHeight: number, inWidth: number, inChannels: number,
+         outHeight: number, outWidth: number, outChannels: number, filterHeight: number,
+         filterWidth: number, strideHeight: number, strideWidth: number, dilationHeight: number,
+         dilationWidth: number, padInfo: {top: number, left: number}},
+    activation: number, biasLen: number, preluLen: number, leakyreluAlpha = 0.2,
+    effective = false, effFilter?: [number, number]): ArrayBuffer {
+  const buf = new ArrayBuffer(80);
+  const v = new DataView(buf);
+  const f = effective && effFilter ? effFilter : [ci.filterHeight, ci.filterWidth];
+  [ci.batchSize, ci.inHeight, ci.inWidth, ci.inChannels, ci.outHeight, ci.outWidth,
+   ci.outChannels, f[0], f[1], ci.strideHeight, ci.strideWidth, ci.dilationHeight,
+   ci.dilationWidth, ci.padInfo.top, ci.padInfo.left, activation, biasLen, preluLen]
+      .forEach((x, i) => v.setInt32(4 * i, x, true));
+  v.setFloat64(72, leakyreluAlpha, true);
+  return buf;
+}
+
+/** tfjs_cuda_matmul_params: 10 int32 fields then one double. */
+export function packMatMulParams(
+    batchA: number, batchB: number, m: number, n: number, k: number, transposeA: boolean,
+    transposeB: boolean, activation: number, biasLen: number, preluLen: number,
+    leakyreluAlpha = 0.2): ArrayBuffer {
+  const buf = new ArrayBuffer(48);
+  const v = new DataView(buf);
+  [batchA, batchB, m, n, k, transposeA ? 1 : 0, transposeB ? 1 : 0, activation, biasLen, preluLen]
+      .forEach((x, i) => v.setInt32(4 * i, x, true));
+  v.setFloat64(40, leakyreluAlpha, true);
+  return buf;
+}
+
+export function i64(values: number[]): BigInt64Array {
+  return BigInt64Array.from((values.length ? values : [0]).map(x => BigInt(x)));
+}

@@ -1,0 +1,63 @@
+/** _FusedMatMul and BatchMatMul.  Python twin: tfjs_b200/kernels/matmul.py. */
+import {_FusedMatMul, BatchMatMul, broadcast_util, KernelConfig, KernelFunc, TensorInfo,
+        util} from '@tensorflow/tfjs-core';
+
+import {CudaBackend} from '../backend_cuda';
+import {ACTIVATION, binding, packMatMulParams} from '../binding';
+import {perChannelLen} from './conv';
+import {applyActivation, binaryImpl} from './elementwise';
+
+function matMulImpl(
+    backend: CudaBackend, a: TensorInfo, b: TensorInfo, transposeA: boolean, transposeB: boolean,
+    bias?: TensorInfo, prelu?: TensorInfo, activation = 'linear', alpha = 0.2): TensorInfo {
+  const ar = a.shape.length, br = b.shape.length;
+  const innerA = transposeA ? a.shape[ar - 2] : a.shape[ar - 1];
+  const innerB = transposeB ? b.shape[br - 1] : b.shape[br - 2];
+  const outerA = transposeA ? a.shape[ar - 1] : a.shape[ar - 2];
+  const outerB = transposeB ? b.shape[br - 2] : b.shape[br - 1];
+  util.assert(innerA === innerB, () =>
+      `Error in matMul: inner shapes (${innerA}) and (${innerB}) of Tensors with shapes ` +
+      `${a.shape} and ${b.shape} and transposeA=${transposeA} and transposeB=${transposeB} must match.`);
+  const batchA = util.sizeFromShape(a.shape.slice(0, -2));
+  const batchB = util.sizeFromShape(b.shape.slice(0, -2));
+  const outShape = broadcast_util.assertAndGetBroadcastShape(a.shape.slice(0, -2), b.shape.slice(0, -2))
+                       .concat([outerA, outerB]);
+  const biasLen = perChannelLen(bias, outerB);
+  const preluLen = activation === 'prelu' ? perChannelLen(prelu, outerB) : 0;
+  const fuseBias = biasLen != null;
+  const fuseAct = fuseBias && (activation !== 'prelu' || preluLen != null);
+  let out = backend.makeOutput(outShape, 'float32');
+  if (util.sizeFromShape(outShape) > 0) {
+    binding.fusedMatMul(
+        backend.ctx,
+        packMatMulParams(batchA, batchB, outerA, outerB, innerA, transposeA, transposeB,
+                         ACTIVATION[fuseAct ? activation : 'linear'], fuseBias ? biasLen : 0,
+                         fuseAct ? (preluLen ?? 0) : 0, alpha),
+        backend.deviceId(a), backend.deviceId(b), fuseBias ? backend.deviceId(bias) : 0,
+        fuseAct && activation === 'prelu' ? backend.deviceId(prelu) : 0, backend.deviceId(out));
+  }
+  if (!fuseBias) {
+    const added = binaryImpl(backend, 'Add', out, bias);
+    backend.disposeData(out.dataId);
+    out = added;
+  }
+  if (!fuseAct) {
+    const act = applyActivation(backend, out, activation, prelu, alpha);
+    backend.disposeData(out.dataId);
+    out = act;
+  }
+  return out;
+}
+
+type Args = {inputs: {[k: string]: TensorInfo}, attrs: {[k: string]: unknown}, backend: CudaBackend};
+
+export const matMulConfigs: KernelConfig[] = [
+  {kernelName: _FusedMatMul, backendName: 'cuda',
+   kernelFunc: (({inputs, attrs, backend}: Args) => matMulImpl(
+       backend, inputs['a'], inputs['b'], !!attrs['transposeA'], !!attrs['transposeB'], inputs['bias'],
+       inputs['preluActivationWeights'], (attrs['activation'] as string) ?? 'linear',
+       (attrs['leakyreluAlpha'] as number) ?? 0.2)) as unknown as KernelFunc},
+  {kernelName: BatchMatMul, backendName: 'cuda',
+   kernelFunc: (({inputs, attrs, backend}: Args) => matMulImpl(
+       backend, inputs['a'], inputs['b'], !!attrs['transposeA'], !!attrs['transposeB'])) as unknown as KernelFunc},
+];

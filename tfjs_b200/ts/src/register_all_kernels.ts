@@ -1,0 +1,11 @@
+/** Registers every kernel of the 'cuda' backend (cf. tfjs-backend-cpu/src/register_all_kernels.ts). */
+import {registerKernel} from '@tensorflow/tfjs-core';
+
+import {convConfigs} from './kernels/conv';
+import {elementwiseConfigs} from './kernels/elementwise';
+import {matMulConfigs} from './kernels/matmul';
+import {otherConfigs} from './kernels/pool_reduce_movement';
+
+for (const config of [...convConfigs, ...matMulConfigs, ...elementwiseConfigs, ...otherConfigs]) {
+  registerKernel(config);
+}
