@@ -86,6 +86,11 @@ int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id);
  * bytes untouched until the next blocking call. */
 int tfjs_cuda_write(tfjs_cuda_ctx* ctx, int32_t id, const void* host,
                     uint64_t nbytes);
+/* alloc + write in one call, on a separate copy stream: the transfer overlaps kernels
+ * already queued on the compute stream, and the first kernel that consumes the new
+ * tensor waits for it.  `host` should be pinned and must stay untouched until the
+ * tensor has been consumed or a blocking call returns. */
+int tfjs_cuda_upload(tfjs_cuda_ctx* ctx, const void* host, uint64_t nbytes, int32_t* out_id);
 /* backend.readSync(): D2H then stream sync; reports a pending device timeout. */
 int tfjs_cuda_read(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes);
 /* Queue a D2H copy without waiting (pair with tfjs_cuda_sync). */

@@ -463,3 +463,28 @@ def test_reshape_is_zero_copy(cuda_engine):
 def test_missing_kernel_is_an_error(cuda_engine):
     with pytest.raises(RuntimeError, match="not registered for backend 'cuda'"):
         cuda_engine.run_kernel("NonMaxSuppressionV5", {}, {})
+
+
+def test_overlapped_upload(cuda_engine):
+    """tfjs_cuda_upload: copy-stream transfer; the first consumer waits for it."""
+    from tfjs_b200 import ops
+    from tfjs_b200.backend import TensorInfo
+    b = cuda_engine.backend
+    r = rng(30)
+    big = b.pinned_empty((512, 1024), "float32")
+    big[...] = r.standard_normal((512, 1024)).astype(np.float32)
+    for _ in range(3):
+        # keep the compute stream busy, then upload and consume right away
+        busy = ops.tensor(np.ones((2048, 2048), np.float32))
+        prod = ops.mat_mul(busy, busy)
+        did = b.write_from(big, big.shape, "float32")
+        t = cuda_engine.make_tensor_from_info(TensorInfo(did, big.shape, "float32"))
+        doubled = ops.add(t, t)
+        assert np.array_equal(doubled.arraySync(), big * 2)
+        assert np.array_equal(t.dataSync().reshape(big.shape), big)
+        for x in (busy, prod, t, doubled):
+            x.dispose()
+    # an uploaded tensor that is never consumed can still be freed
+    did = b.write_from(big, big.shape, "float32")
+    assert b.disposeData(did) is True
+    b.sync()

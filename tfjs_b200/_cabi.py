@@ -51,6 +51,7 @@ SIGNATURES = {
     "tfjs_cuda_alloc": (c_int, [_CTX, c_uint64, POINTER(c_int32)]),
     "tfjs_cuda_free": (c_int, [_CTX, c_int32]),
     "tfjs_cuda_write": (c_int, [_CTX, c_int32, c_void_p, c_uint64]),
+    "tfjs_cuda_upload": (c_int, [_CTX, c_void_p, c_uint64, POINTER(c_int32)]),
     "tfjs_cuda_read": (c_int, [_CTX, c_int32, c_void_p, c_uint64]),
     "tfjs_cuda_read_async": (c_int, [_CTX, c_int32, c_void_p, c_uint64]),
     "tfjs_cuda_sync": (c_int, [_CTX]),

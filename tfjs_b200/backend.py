@@ -277,11 +277,11 @@ class CudaBackend(object):
         n = size_from_shape(shape)
         nbytes = n * np.dtype(NP_DTYPES[dtype]).itemsize
         dataId = DataId()
-        rec = _Record(self._alloc(nbytes), nbytes, dtype, 1, None)
-        if nbytes:
-            self.check(self.lib.tfjs_cuda_write(self.ctx, rec.dev,
-                                                host_array.ctypes.data_as(c_void_p), nbytes))
-        self.data[dataId] = rec
+        dev = c_int32()
+        # copy-stream upload: overlaps whatever is already queued on the compute stream
+        self.check(self.lib.tfjs_cuda_upload(self.ctx, host_array.ctypes.data_as(c_void_p),
+                                             nbytes, byref(dev)))
+        self.data[dataId] = _Record(dev.value, nbytes, dtype, 1, None)
         return dataId
 
     def dispose(self):

@@ -17,6 +17,7 @@ struct Buffer {
   bool live = false;
   bool from_host = false;  // last filled by write()/dequantize(): weight-like
   uint32_t version = 0;    // bumped whenever the contents are (re)written
+  cudaEvent_t ready = nullptr;  // set while an upload on the copy stream is pending
 };
 
 // A filter repacked for the tensor-core kernels: [rows = out channels][k_pad]
@@ -33,6 +34,8 @@ struct tfjs_cuda_ctx {
   int device = 0;
   int sm_count = 148;
   cudaStream_t stream = nullptr;
+  cudaStream_t copy_stream = nullptr;       // uploads that overlap compute
+  std::vector<cudaEvent_t> event_pool;      // recycled upload-completion events
   cudaMemPool_t pool = nullptr;
   std::vector<Buffer> bufs;  // index = id; slot 0 unused
   std::vector<int32_t> free_ids;

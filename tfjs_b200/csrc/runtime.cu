@@ -48,6 +48,12 @@ int ctx_get(tfjs_cuda_ctx* ctx, int32_t id, uint64_t need, const char* name,
     return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG,
                     "%s: tensor id %d holds %llu bytes, kernel needs %llu", name,
                     id, (unsigned long long)b->bytes, (unsigned long long)need);
+  if (b->ready) {
+    // first use after an overlapped upload: order the compute stream behind the copy
+    cudaStreamWaitEvent(ctx->stream, b->ready, 0);
+    ctx->event_pool.push_back(b->ready);
+    b->ready = nullptr;
+  }
   *out = b;
   return TFJS_CUDA_OK;
 }
@@ -115,6 +121,7 @@ int tfjs_cuda_create(int device_ordinal, tfjs_cuda_ctx** out_ctx) {
   ctx->bufs.resize(1);
   bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) ==
             cudaSuccess;
+  ok = ok && cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking) == cudaSuccess;
   ok = ok && cudaDeviceGetDefaultMemPool(&ctx->pool, device_ordinal) ==
                  cudaSuccess;
   if (ok) {
@@ -158,6 +165,13 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
   if (ctx->h_bad_index) cudaFreeHost(ctx->h_bad_index);
   for (cudaEvent_t e : ctx->prof_events)
     if (e) cudaEventDestroy(e);
+  for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
+  for (auto& b : ctx->bufs)
+    if (b.ready) cudaEventDestroy(b.ready);
+  if (ctx->copy_stream) {
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamDestroy(ctx->copy_stream);
+  }
   if (ctx->ev0) cudaEventDestroy(ctx->ev0);
   if (ctx->ev1) cudaEventDestroy(ctx->ev1);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -203,6 +217,11 @@ int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id) {
   if (!b) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "free: unknown tensor id %d", id);
   cudaSetDevice(ctx->device);
   ctx_drop_packed(ctx, id);
+  if (b->ready) {  // never used since its upload: still order the free behind the copy
+    cudaStreamWaitEvent(ctx->stream, b->ready, 0);
+    ctx->event_pool.push_back(b->ready);
+    b->ready = nullptr;
+  }
   uint64_t padded = ((b->bytes + 255) / 256) * 256;
   if (padded == 0) padded = 256;
   cudaError_t e = cudaFreeAsync(b->ptr, ctx->stream);
@@ -229,6 +248,48 @@ int tfjs_cuda_write(tfjs_cuda_ctx* ctx, int32_t id, const void* host,
   b->version++;
   b->from_host = true;
   ctx_drop_packed(ctx, id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_upload(tfjs_cuda_ctx* ctx, const void* host, uint64_t nbytes, int32_t* out_id) {
+  if (!ctx || !out_id) return TFJS_CUDA_INVALID_ARG;
+  if (nbytes && !host) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "upload: null host pointer");
+  cudaSetDevice(ctx->device);
+  void* p = nullptr;
+  uint64_t padded = ((nbytes + 255) / 256) * 256;
+  if (padded == 0) padded = 256;
+  // Allocated and filled on the copy stream, so the transfer does not queue behind
+  // kernels already launched on the compute stream.
+  CUDA_TRY(ctx, cudaMallocAsync(&p, padded, ctx->copy_stream));
+  if (nbytes)
+    CUDA_TRY(ctx, cudaMemcpyAsync(p, host, nbytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+  cudaEvent_t ev = nullptr;
+  if (!ctx->event_pool.empty()) {
+    ev = ctx->event_pool.back();
+    ctx->event_pool.pop_back();
+  } else {
+    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  }
+  CUDA_TRY(ctx, cudaEventRecord(ev, ctx->copy_stream));
+  int32_t id;
+  if (!ctx->free_ids.empty()) {
+    id = ctx->free_ids.back();
+    ctx->free_ids.pop_back();
+  } else {
+    id = (int32_t)ctx->bufs.size();
+    ctx->bufs.emplace_back();
+  }
+  Buffer& b = ctx->bufs[id];
+  b.ptr = p;
+  b.bytes = nbytes;
+  b.live = true;
+  b.from_host = true;
+  b.version++;
+  b.ready = ev;
+  ctx->in_use += padded;
+  ctx->n_live++;
+  if (ctx->in_use > ctx->high_water) ctx->high_water = ctx->in_use;
+  *out_id = id;
   return TFJS_CUDA_OK;
 }
 
