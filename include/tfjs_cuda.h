@@ -104,6 +104,8 @@ int tfjs_cuda_device_ptr(tfjs_cuda_ctx* ctx, int32_t id, void** out_ptr);
 int tfjs_cuda_memory(tfjs_cuda_ctx* ctx, uint64_t* bytes_in_use,
                      uint64_t* bytes_reserved, uint64_t* high_water,
                      uint64_t* num_buffers);
+/* Returns cached and pooled free blocks to the driver (blocks until the stream is idle). */
+int tfjs_cuda_trim(tfjs_cuda_ctx* ctx);
 /* Pinned host buffers for write/read staging. */
 int tfjs_cuda_host_alloc(tfjs_cuda_ctx* ctx, uint64_t nbytes, void** out_ptr);
 int tfjs_cuda_host_free(tfjs_cuda_ctx* ctx, void* ptr);

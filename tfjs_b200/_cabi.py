@@ -58,6 +58,7 @@ SIGNATURES = {
     "tfjs_cuda_size_of": (c_int, [_CTX, c_int32, POINTER(c_uint64)]),
     "tfjs_cuda_device_ptr": (c_int, [_CTX, c_int32, POINTER(c_void_p)]),
     "tfjs_cuda_memory": (c_int, [_CTX] + [POINTER(c_uint64)] * 4),
+    "tfjs_cuda_trim": (c_int, [_CTX]),
     "tfjs_cuda_host_alloc": (c_int, [_CTX, c_uint64, POINTER(c_void_p)]),
     "tfjs_cuda_host_free": (c_int, [_CTX, c_void_p]),
     "tfjs_cuda_time_begin": (c_int, [_CTX]),

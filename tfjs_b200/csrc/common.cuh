@@ -36,6 +36,13 @@ struct tfjs_cuda_ctx {
   cudaStream_t stream = nullptr;
   cudaStream_t copy_stream = nullptr;       // uploads that overlap compute
   std::vector<cudaEvent_t> event_pool;      // recycled upload-completion events
+  // Exact-size cache of freed blocks.  A graph model asks for the same sizes every
+  // step; handing a freed block straight to the next request of that size keeps the
+  // driver's allocator (and its occasional re-mapping of large blocks) off the step.
+  // Safe without fences because every cached block is reused on the same in-order
+  // compute stream that last touched it.
+  std::unordered_map<uint64_t, std::vector<void*>> block_cache;
+  uint64_t cached_bytes = 0;
   cudaMemPool_t pool = nullptr;
   std::vector<Buffer> bufs;  // index = id; slot 0 unused
   std::vector<int32_t> free_ids;

@@ -595,62 +595,80 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     const ConvGeo& cv = g.conv;
     const uint32_t row_off = (uint32_t)r * 128u;
     const uint32_t sw = (uint32_t)(r & 7);
-    int stage = 0;
-    uint32_t phase = 0;
-    bool alive = true;
-    for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x) {
+    // iterator over (tile, k step); the loads of step i+1 are issued before the
+    // stores of step i so two steps are in flight per thread
+    int tile = blockIdx.x, ks = 0;
+    unsigned long long mask = 0ull;
+    const float* base = g.x;
+    auto enter_tile = [&]() {
+      mask = 0ull;
+      base = g.x;
+      if (tile >= g.total_tiles) return;
       const int mt = (tile / g.tiles_n) % g.tiles_m;
       const int m = mt * BM + r;
-      unsigned long long mask = 0ull;
-      const float* base = g.x;
-      if (m < g.M) {
-        const int ow = m % cv.out_w;
-        const int t = m / cv.out_w;
-        const int oh = t % cv.out_h;
-        const int b = t / cv.out_h;
-        const int r0 = oh * cv.s_h - cv.pad_t, c0 = ow * cv.s_w - cv.pad_l;
-        int tap = 0;
-        for (int fr = 0; fr < cv.f_h; ++fr) {
-          const int ri = r0 + fr * cv.d_h;
-          for (int fc = 0; fc < cv.f_w; ++fc, ++tap) {
-            const int ci = c0 + fc * cv.d_w;
-            if (ri >= 0 && ri < cv.in_h && ci >= 0 && ci < cv.in_w) mask |= 1ull << tap;
-          }
+      if (m >= g.M) return;
+      const int ow = m % cv.out_w;
+      const int t = m / cv.out_w;
+      const int oh = t % cv.out_h;
+      const int b = t / cv.out_h;
+      const int r0 = oh * cv.s_h - cv.pad_t, c0 = ow * cv.s_w - cv.pad_l;
+      int tap = 0;
+      for (int fr = 0; fr < cv.f_h; ++fr) {
+        const int ri = r0 + fr * cv.d_h;
+        for (int fc = 0; fc < cv.f_w; ++fc, ++tap) {
+          const int ci = c0 + fc * cv.d_w;
+          if (ri >= 0 && ri < cv.in_h && ci >= 0 && ci < cv.in_w) mask |= 1ull << tap;
         }
-        base = g.x + (((long long)b * cv.in_h + r0) * cv.in_w + c0) * cv.in_c;
       }
-      for (int ks = 0; ks < k_steps; ++ks) {
-        float v[32];
+      base = g.x + (((long long)b * cv.in_h + r0) * cv.in_w + c0) * cv.in_c;
+    };
+    auto load_step = [&](float* v) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          uint32_t e;
-          asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e) : "r"(tap_table + 4u * (ks * BK + j)));
-          const uint32_t tap = e >> 24;
-          const bool ok = tap < 64u && ((mask >> tap) & 1ull);
-          v[j] = ok ? __ldg(base + (e & 0xffffffu)) : 0.0f;
-        }
-        if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
-          atomicExch(g.flag, 6);
-          alive = false;
-          break;
-        }
-        const uint32_t dst = a_base + stage * A_STAGE_BYTES + row_off;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint32_t w0, w1, w2, w3;
-          asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w0) : "f"(v[4 * j]));
-          asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w1) : "f"(v[4 * j + 1]));
-          asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w2) : "f"(v[4 * j + 2]));
-          asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w3) : "f"(v[4 * j + 3]));
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
-                           dst + (((uint32_t)j ^ sw) << 4)),
-                       "r"(w0), "r"(w1), "r"(w2), "r"(w3)
-                       : "memory");
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(full_bar(stage));
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      for (int j = 0; j < 32; ++j) {
+        uint32_t e;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e) : "r"(tap_table + 4u * (ks * BK + j)));
+        const uint32_t tap = e >> 24;
+        const bool ok = tap < 64u && ((mask >> tap) & 1ull);
+        v[j] = ok ? __ldg(base + (e & 0xffffffu)) : 0.0f;
       }
+    };
+    auto advance = [&]() {
+      if (++ks == k_steps) {
+        ks = 0;
+        tile += gridDim.x;
+        enter_tile();
+      }
+    };
+    int stage = 0;
+    uint32_t phase = 0;
+    float cur[32], nxt[32];
+    enter_tile();
+    if (tile < g.total_tiles) load_step(nxt);
+    while (tile < g.total_tiles) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) cur[j] = nxt[j];
+      advance();
+      if (tile < g.total_tiles) load_step(nxt);
+      if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
+        atomicExch(g.flag, 6);
+        break;
+      }
+      const uint32_t dst = a_base + stage * A_STAGE_BYTES + row_off;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t w0, w1, w2, w3;
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w0) : "f"(cur[4 * j]));
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w1) : "f"(cur[4 * j + 1]));
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w2) : "f"(cur[4 * j + 2]));
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w3) : "f"(cur[4 * j + 3]));
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                         dst + (((uint32_t)j ^ sw) << 4)),
+                     "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                     : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(full_bar(stage));
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
   }
 

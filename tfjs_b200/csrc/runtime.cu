@@ -86,6 +86,38 @@ void ctx_drop_packed(tfjs_cuda_ctx* ctx, int32_t id) {
   ctx->packed.erase(it);
 }
 
+static void cache_flush(tfjs_cuda_ctx* ctx) {
+  for (auto& kv : ctx->block_cache)
+    for (void* p : kv.second) cudaFreeAsync(p, ctx->stream);
+  ctx->block_cache.clear();
+  ctx->cached_bytes = 0;
+}
+
+// Pool allocation for tensors: exact-size cache first, then the stream-ordered pool;
+// on failure the cache is returned to the pool and the request retried once.
+static cudaError_t block_alloc(tfjs_cuda_ctx* ctx, uint64_t padded, void** out) {
+  auto it = ctx->block_cache.find(padded);
+  if (it != ctx->block_cache.end() && !it->second.empty()) {
+    *out = it->second.back();
+    it->second.pop_back();
+    ctx->cached_bytes -= padded;
+    return cudaSuccess;
+  }
+  cudaError_t e = cudaMallocAsync(out, padded, ctx->stream);
+  if (e == cudaErrorMemoryAllocation && ctx->cached_bytes) {
+    cudaGetLastError();
+    cache_flush(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    e = cudaMallocAsync(out, padded, ctx->stream);
+  }
+  return e;
+}
+
+static void block_free(tfjs_cuda_ctx* ctx, void* p, uint64_t padded) {
+  ctx->block_cache[padded].push_back(p);
+  ctx->cached_bytes += padded;
+}
+
 extern "C" {
 
 int tfjs_cuda_device_count(int* out_count) {
@@ -156,6 +188,7 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
     if (kv.second.ptr) cudaFreeAsync(kv.second.ptr, ctx->stream);
   for (auto& b : ctx->bufs)
     if (b.live && b.ptr) cudaFreeAsync(b.ptr, ctx->stream);
+  cache_flush(ctx);
   if (ctx->scratch) cudaFreeAsync(ctx->scratch, ctx->stream);
   if (ctx->l2_scratch) cudaFreeAsync(ctx->l2_scratch, ctx->stream);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
@@ -189,7 +222,7 @@ int tfjs_cuda_alloc(tfjs_cuda_ctx* ctx, uint64_t nbytes, int32_t* out_id) {
   // Round up so vectorised kernels may read a full 16-byte tail.
   uint64_t padded = ((nbytes + 255) / 256) * 256;
   if (padded == 0) padded = 256;
-  CUDA_TRY(ctx, cudaMallocAsync(&p, padded, ctx->stream));
+  CUDA_TRY(ctx, block_alloc(ctx, padded, &p));
   int32_t id;
   if (!ctx->free_ids.empty()) {
     id = ctx->free_ids.back();
@@ -224,14 +257,14 @@ int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id) {
   }
   uint64_t padded = ((b->bytes + 255) / 256) * 256;
   if (padded == 0) padded = 256;
-  cudaError_t e = cudaFreeAsync(b->ptr, ctx->stream);
+  block_free(ctx, b->ptr, padded);
   b->ptr = nullptr;
   b->live = false;
   b->bytes = 0;
   ctx->in_use -= padded;
   ctx->n_live--;
   ctx->free_ids.push_back(id);
-  return ctx_check(ctx, e, "cudaFreeAsync");
+  return TFJS_CUDA_OK;
 }
 
 int tfjs_cuda_write(tfjs_cuda_ctx* ctx, int32_t id, const void* host,
@@ -364,6 +397,15 @@ int tfjs_cuda_memory(tfjs_cuda_ctx* ctx, uint64_t* bytes_in_use,
                                           cudaMemPoolAttrReservedMemCurrent, &r));
     *bytes_reserved = r;
   }
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_trim(tfjs_cuda_ctx* ctx) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  cache_flush(ctx);
+  CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  CUDA_TRY(ctx, cudaMemPoolTrimTo(ctx->pool, 0));
   return TFJS_CUDA_OK;
 }
 
