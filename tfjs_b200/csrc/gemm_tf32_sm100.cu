@@ -29,6 +29,7 @@
 
 #include "common.cuh"
 #include "gemm.h"
+#include "ptx.cuh"
 
 namespace {
 
@@ -36,7 +37,6 @@ constexpr int BM = 128;
 constexpr int BK = 32;          // floats per K step = one 128-byte swizzle row
 constexpr int UMMA_K = 8;       // K of one tcgen05.mma.kind::tf32
 constexpr int A_STAGE_BYTES = BM * BK * 4;
-constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 struct Tf32Args {
   float* c;
@@ -55,42 +55,6 @@ struct Tf32Args {
   int chunks_per_tap;  // 32-channel chunks per filter tap
 };
 
-// ---- PTX wrappers ------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the phase did not complete within kWaitCycles.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t n = 0;
-  while (!mbar_try(bar, parity)) {
-    if ((++n & 0x3ff) == 0 && clock64() - t0 > kWaitCycles) return false;
-  }
-  return true;
-}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm,
                                             uint32_t bar, int x, int y, int z) {
   asm volatile(
@@ -683,24 +647,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
 }
 
 // ---- host side ---------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
-          cudaSuccess &&
-      q == cudaDriverEntryPointSuccess)
-    fn = (EncodeTiledFn)p;
-  return fn;
-}
-
 // 3-D map over [batch][rows][inner] floats; box = [1][box_rows][32].
 int make_map(tfjs_cuda_ctx* ctx, CUtensorMap* tm, const float* base, uint64_t inner,
              uint64_t rows, uint64_t batch, uint64_t row_stride_elems,

@@ -2,7 +2,10 @@
 // A thread owns four adjacent channels of one output pixel and moves them with
 // 128-bit loads/stores, so a warp reads and writes 512 contiguous bytes per
 // tap; overlapping taps of neighbouring pixels are served by L1/L2.
+#include <stdlib.h>
+
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace {
 
@@ -241,6 +244,195 @@ void launch_depthwise3x3(tfjs_cuda_ctx* ctx, const float* x, const float* w, con
   }
 }
 
+// ---- 3x3 depthwise through TMA-staged input tiles -------------------------------
+// A CTA walks (image, output tile, 32-channel chunk) work items.  The input patch
+// of a tile (with its one-pixel halo; zero outside the image, which is what
+// skipping those taps amounts to) arrives in shared memory by one 4-D TMA load;
+// two buffers alternate so the load of the next tile overlaps the arithmetic of
+// the current one.  A thread owns 4 channels of S adjacent output columns.
+template <int STRIDE, int TW_>
+struct DwTile {
+  static constexpr int TW = TW_;                      // output tile width (16 or 14)
+  static constexpr int TH = STRIDE == 1 ? 8 : 4;      // output tile height
+  static constexpr int S = (STRIDE == 1 && TW_ == 16) ? 4 : 2;  // outputs per strip
+  static constexpr int NSTRIPS = (TW / S) * TH;       // strips per tile, 32 per pass
+  static constexpr int IW = (TW - 1) * STRIDE + 3;    // input patch
+  static constexpr int IH = (TH - 1) * STRIDE + 3;
+  static constexpr int BUF_BYTES = IW * IH * 128;
+  static constexpr int SMEM_BYTES = 2 * BUF_BYTES + 128 + 64;
+};
+
+struct DwTiles {
+  int tiles_w, tiles_h, chunks, total;
+};
+
+template <int STRIDE, int TW_, int ACT>
+__global__ void __launch_bounds__(256, 2)
+depthwise3x3_tma_kernel(const __grid_constant__ CUtensorMap tm_x, const float* __restrict__ w,
+                        const float* __restrict__ bias, int bias_len, ActParams ap,
+                        float* __restrict__ y, Geo g, DwTiles tl, int* flag) {
+  using T = DwTile<STRIDE, TW_>;
+  constexpr int NC = (T::S - 1) * STRIDE + 3;
+  extern __shared__ uint8_t dw_smem_raw[];
+  const uint32_t base = (smem_u32(dw_smem_raw) + 127u) & ~127u;
+  const uint32_t bar0 = base + 2 * T::BUF_BYTES;
+  const int tid = threadIdx.x;
+  const int c4 = tid & 7;
+  constexpr int strips_per_row = T::TW / T::S;
+
+  if (tid == 0) {
+    mbar_init(bar0, 1);
+    mbar_init(bar0 + 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto decode = [&](int item, int& n, int& th, int& tw, int& cc) {
+    cc = item % tl.chunks;
+    int rest = item / tl.chunks;
+    tw = rest % tl.tiles_w;
+    rest /= tl.tiles_w;
+    th = rest % tl.tiles_h;
+    n = rest / tl.tiles_h;
+  };
+  auto issue = [&](int item, int buf) {
+    int n, th, tw, cc;
+    decode(item, n, th, tw, cc);
+    const uint32_t bar = bar0 + 8 * buf;
+    mbar_expect_tx(bar, T::BUF_BYTES);
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(base + buf * T::BUF_BYTES),
+        "l"(&tm_x), "r"(bar), "r"(cc * 32), "r"(tw * T::TW * STRIDE - g.pad_l),
+        "r"(th * T::TH * STRIDE - g.pad_t), "r"(n)
+        : "memory");
+  };
+
+  int item = blockIdx.x;
+  if (tid == 0 && item < tl.total) issue(item, 0);
+  uint32_t phase[2] = {0, 0};
+  int buf = 0;
+  for (; item < tl.total; item += gridDim.x, buf ^= 1) {
+    const int next = item + gridDim.x;
+    // every thread finished reading buffer buf^1 at the barrier that ended the
+    // previous iteration, so it can be refilled now
+    if (tid == 0 && next < tl.total) issue(next, buf ^ 1);
+    int n, th, tw, cc;
+    decode(item, n, th, tw, cc);
+    const int c = cc * 32 + c4 * 4;
+    const bool c_ok = c < g.c;
+    float4 wv[9];
+    float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c_ok) {
+#pragma unroll
+      for (int k = 0; k < 9; ++k) wv[k] = __ldg(reinterpret_cast<const float4*>(w + k * g.c + c));
+      if (bias_len == 1) {
+        const float b0 = __ldg(bias);
+        bv = make_float4(b0, b0, b0, b0);
+      } else if (bias_len > 1) {
+        bv = __ldg(reinterpret_cast<const float4*>(bias + c));
+      }
+    }
+    if (!mbar_wait(bar0 + 8 * buf, phase[buf])) {
+      if (tid == 0) atomicExch(flag, 7);
+      break;
+    }
+    phase[buf] ^= 1;
+    for (int strip = tid >> 3; strip < T::NSTRIPS; strip += 32) {
+    const int sr = strip / strips_per_row;        // row inside the tile
+    const int sc = (strip % strips_per_row) * T::S;
+    const int oh = th * T::TH + sr;
+    const int ow0 = tw * T::TW + sc;
+    if (c_ok && oh < g.out_h && ow0 < g.out_w) {
+      float4 acc[T::S];
+#pragma unroll
+      for (int s = 0; s < T::S; ++s) acc[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const uint32_t tile = base + buf * T::BUF_BYTES + (uint32_t)c4 * 16u;
+#pragma unroll
+      for (int fr = 0; fr < 3; ++fr) {
+        const uint32_t row = tile + (uint32_t)((sr * STRIDE + fr) * T::IW + sc * STRIDE) * 128u;
+        float4 xin[NC];
+#pragma unroll
+        for (int i = 0; i < NC; ++i)
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(xin[i].x), "=f"(xin[i].y), "=f"(xin[i].z), "=f"(xin[i].w)
+                       : "r"(row + (uint32_t)i * 128u));
+#pragma unroll
+        for (int s = 0; s < T::S; ++s) {
+#pragma unroll
+          for (int fc = 0; fc < 3; ++fc) {
+            const float4 xv = xin[s * STRIDE + fc];
+            const float4 wk = wv[fr * 3 + fc];
+            acc[s].x = fmaf(xv.x, wk.x, acc[s].x);
+            acc[s].y = fmaf(xv.y, wk.y, acc[s].y);
+            acc[s].z = fmaf(xv.z, wk.z, acc[s].z);
+            acc[s].w = fmaf(xv.w, wk.w, acc[s].w);
+          }
+        }
+      }
+      float* yrow = y + (((size_t)n * g.out_h + oh) * g.out_w + ow0) * g.c + c;
+#pragma unroll
+      for (int s = 0; s < T::S; ++s) {
+        if (ow0 + s >= g.out_w) break;
+        float o[4] = {acc[s].x, acc[s].y, acc[s].z, acc[s].w};
+        const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float v = bias_len ? __fadd_rn(o[k], bb[k]) : o[k];
+          if (ACT == TFJS_CUDA_ACT_RELU) v = v != v ? v : fmaxf(v, 0.0f);
+          else if (ACT == TFJS_CUDA_ACT_RELU6) v = v != v ? v : fminf(fmaxf(v, 0.0f), 6.0f);
+          else if (ACT != TFJS_CUDA_ACT_LINEAR) v = apply_act(v, ap, c + k);
+          o[k] = v;
+        }
+        *reinterpret_cast<float4*>(yrow + (size_t)s * g.c) = make_float4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    }
+    __syncthreads();
+  }
+}
+
+template <int STRIDE, int TW_>
+int launch_depthwise3x3_tma(tfjs_cuda_ctx* ctx, const float* x, const float* w, const float* bias,
+                            int bias_len, const ActParams& ap, float* y, const Geo& g) {
+  using T = DwTile<STRIDE, TW_>;
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  CUtensorMap tm;
+  cuuint64_t dims[4] = {(cuuint64_t)g.c, (cuuint64_t)g.in_w, (cuuint64_t)g.in_h, (cuuint64_t)g.batch};
+  cuuint64_t strides[3] = {(cuuint64_t)g.c * 4, (cuuint64_t)g.in_w * g.c * 4,
+                           (cuuint64_t)g.in_h * g.in_w * g.c * 4};
+  cuuint32_t box[4] = {32, T::IW, T::IH, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (enc(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)x, dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return -1;
+  DwTiles tl;
+  tl.tiles_w = (g.out_w + T::TW - 1) / T::TW;
+  tl.tiles_h = (g.out_h + T::TH - 1) / T::TH;
+  tl.chunks = (g.c + 31) / 32;
+  const long long total = (long long)g.batch * tl.tiles_h * tl.tiles_w * tl.chunks;
+  if (total > 0x7fffffffLL) return -1;
+  tl.total = (int)total;
+  const int grid = tl.total < ctx->sm_count * 2 ? tl.total : ctx->sm_count * 2;
+#define DW_TMA(ACT)                                                                          \
+  {                                                                                          \
+    auto kern = depthwise3x3_tma_kernel<STRIDE, TW_, ACT>;                                        \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);  \
+    kern<<<grid, 256, T::SMEM_BYTES, ctx->stream>>>(tm, w, bias, bias_len, ap, y, g, tl,     \
+                                                    ctx->d_flag);                            \
+  }
+  switch (ap.act) {
+    case TFJS_CUDA_ACT_LINEAR: DW_TMA(TFJS_CUDA_ACT_LINEAR) break;
+    case TFJS_CUDA_ACT_RELU: DW_TMA(TFJS_CUDA_ACT_RELU) break;
+    case TFJS_CUDA_ACT_RELU6: DW_TMA(TFJS_CUDA_ACT_RELU6) break;
+    default: DW_TMA(TFJS_CUDA_ACT_ELU) break;
+  }
+#undef DW_TMA
+  return 0;
+}
+
 // General channel multiplier: one thread per output element.
 __global__ void depthwise_chmul_kernel(const float* __restrict__ x,
                                        const float* __restrict__ w,
@@ -369,7 +561,24 @@ int tfjs_cuda_fused_depthwise_conv2d(tfjs_cuda_ctx* ctx,
   const int bl = bias ? p->bias_len : 0;
   const bool fast3x3 = ch_mul == 1 && g.c % 4 == 0 && g.f_h == 3 && g.f_w == 3 && g.d_h == 1 &&
                        g.d_w == 1 && g.s_h == g.s_w && (g.s_h == 1 || g.s_h == 2);
-  if (fast3x3 && g.s_h == 1)
+  static int no_tma = -1;
+  if (no_tma < 0) no_tma = getenv("TFJS_CUDA_NO_DW_TMA") ? 1 : 0;  // debugging knob
+  // 16-wide tiles measured faster than 14-wide ones even on 56 / 28 / 14 wide maps;
+  // maps narrower than 12 keep the register-strip kernel
+  const int tw = g.out_w >= 12 ? 16 : 0;
+  int launched = -1;
+  if (fast3x3 && !no_tma && tw) {
+    const float* xp = (const float*)x->ptr;
+    const float* wp = (const float*)w->ptr;
+    float* yp = (float*)y->ptr;
+    if (g.s_h == 1 && tw == 16) launched = launch_depthwise3x3_tma<1, 16>(ctx, xp, wp, bp, bl, ap, yp, g);
+    else if (g.s_h == 1) launched = launch_depthwise3x3_tma<1, 14>(ctx, xp, wp, bp, bl, ap, yp, g);
+    else if (tw == 16) launched = launch_depthwise3x3_tma<2, 16>(ctx, xp, wp, bp, bl, ap, yp, g);
+    else launched = launch_depthwise3x3_tma<2, 14>(ctx, xp, wp, bp, bl, ap, yp, g);
+  }
+  if (launched == 0) {
+    // launched
+  } else if (fast3x3 && g.s_h == 1)
     launch_depthwise3x3<1, 4>(ctx, (const float*)x->ptr, (const float*)w->ptr, bp, bl, ap,
                               (float*)y->ptr, g);
   else if (fast3x3)
