@@ -195,10 +195,14 @@ template <int BN, int A_MODE = 0>
 struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
   // the scalar-gather mode gives one stage up for its tap table
-  static constexpr int STAGES = (BN >= 256 ? 4 : (BN >= 128 ? 6 : 8)) - (A_MODE == 3 ? 1 : 0);
+  static constexpr int STAGES =
+      (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 6 : 8))) - (A_MODE == 3 ? 1 : 0);
+  // staging tiles per epilogue warp: two below BN = 256 (bandwidth-bound shapes), so
+  // a warp fills one while the TMA unit still drains the other
+  static constexpr int EPI_BUFS = BN >= 256 ? 1 : 2;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int SMEM_BYTES =
-      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 8 * 4096 +
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 8 * EPI_BUFS * 4096 +
       (A_MODE == 3 ? kTapTableEntries * 4 : 0);
 };
 
@@ -213,8 +217,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_base = smem_base;
   const uint32_t b_base = smem_base + STAGES * A_STAGE_BYTES;
-  const uint32_t epi_base = b_base + STAGES * C::B_STAGE_BYTES;  // 8 x 4 KB staging tiles
-  const uint32_t bar_base = epi_base + 8u * 4096u;
+  const uint32_t epi_base = b_base + STAGES * C::B_STAGE_BYTES;  // 4 KB staging tiles
+  const uint32_t bar_base = epi_base + 8u * C::EPI_BUFS * 4096u;
   // barrier layout: full[STAGES], empty[STAGES], tfull[2], tempty[2], tmem slot
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
@@ -232,7 +236,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 256);
+      mbar_init(tempty_bar(a), BN == 32 ? 128 : 256);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -369,11 +373,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     // with one row per lane; it is staged through a swizzled 4 KB shared-memory
     // tile so that the global stores run along rows: full 128-byte lines, or one
     // contiguous run when the tile spans the whole row.
-    // Two warps share each TMEM lane quarter and take alternate chunks.
+    // Two warps share each TMEM lane quarter and take alternate chunks (alternate
+    // tiles when a tile is a single chunk wide).
     const int q = warp & 3;           // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2; // 0: even chunks, 1: odd chunks
-    const uint32_t stage_buf = epi_base + (uint32_t)(warp - 2) * 4096u;
-    const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
+    const uint32_t stage_base = epi_base + (uint32_t)(warp - 2) * (C::EPI_BUFS * 4096u);
+    uint32_t ebuf = 0;
     const uint32_t sw = (uint32_t)(lane & 7);
     const bool vec4 = (g.N & 3) == 0;
     int it = 0;
@@ -384,6 +389,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int bz = rest / g.tiles_m;
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
+      if (BN == 32 && (it & 1) != half) continue;  // the other warp of the pair takes it
       if (!mbar_wait(tfull_bar(acc), aphase)) {
         if (lane == 0) atomicExch(g.flag, 4);
         break;
@@ -394,7 +400,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       float* cbase = g.c + ((long long)bz * g.M + m_base) * g.N;
       bool released = false;
 #pragma unroll 1
-      for (int c0 = half * 32; c0 < BN; c0 += 64) {
+      for (int c0 = BN == 32 ? 0 : half * 32; c0 < BN; c0 += 64) {
         const int n0 = nt * BN + c0;
         if (n0 >= g.N) break;
         const int w = g.N - n0 < 32 ? g.N - n0 : 32;
@@ -407,9 +413,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           released = true;
         }
         chunk_math_dispatch(v, g, n0);
+        const uint32_t stage_buf = stage_base + ebuf * 4096u;
+        const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
+        if (C::EPI_BUFS == 2) ebuf ^= 1;
         if (g.c_tma) {
-          // the previous bulk store must have finished reading the staging tile
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          // the bulk store that last used this staging tile must have finished reading it
+          if (lane == 0) {
+            if (C::EPI_BUFS == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
         }
         __syncwarp();
 #pragma unroll
@@ -590,7 +602,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         uint32_t e;
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e) : "r"(tap_table + 4u * (ks * BK + j)));
+        // not volatile: the table is constant after set-up, let the loads be scheduled freely
+        asm("ld.shared.b32 %0, [%1];" : "=r"(e) : "r"(tap_table + 4u * (ks * BK + j)));
         const uint32_t tap = e >> 24;
         const bool ok = tap < 64u && ((mask >> tap) & 1ull);
         v[j] = ok ? __ldg(base + (e & 0xffffffu)) : 0.0f;
