@@ -128,8 +128,18 @@ def _prod(s):
 def kernel_work(rec):
     """Algorithmic (flops, bytes) of one profiled kernel call: each input and
     output tensor is moved once; contractions count 2 flops per MAC."""
-    ins = rec["inputShapes"]
     outs = rec["outputShapes"]
+    if rec.get("parts"):
+        # one launch that covers several kernels (a convolution with the Add / Relu
+        # that followed it folded in): the operands of each part are read once, the
+        # final result is written once, intermediate results never reach memory
+        flops = nbytes = 0
+        for part in rec["parts"]:
+            f, _ = kernel_work(dict(part, parts=None))
+            flops += f
+            nbytes += 4 * sum(_prod(s) for s in part["inputShapes"].values())
+        return flops, nbytes + 4 * sum(_prod(s) for s in outs)
+    ins = rec["inputShapes"]
     nbytes = 4 * (sum(_prod(s) for s in ins.values()) + sum(_prod(s) for s in outs))
     name, flops = rec["name"], 0
     if name in ("FusedConv2D", "Conv2D"):
@@ -150,6 +160,8 @@ def kernel_work(rec):
 def summarise_profile(records, steps):
     kinds = {}
     for rec in records:
+        if rec.get("deferred"):
+            continue  # launched later, inside the record that lists it under `parts`
         flops, nbytes = kernel_work(rec)
         k = kinds.setdefault(rec["name"], dict(launches=0, ms=0.0, flops=0, bytes=0))
         k["launches"] += 1

@@ -144,6 +144,17 @@ int tfjs_cuda_fused_conv2d(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
                            int32_t x_id, int32_t filter_id, int32_t bias_id,
                            int32_t prelu_id, int32_t out_id);
 
+/* FusedConv2D whose epilogue also absorbs the two kernels that follow it in a residual
+ * block, Add (tfjs-backend-cpu/src/kernels/Add.ts:23-30) and Relu / Relu6 (Relu.ts:22):
+ *   out = post_activation(residual + act(conv(x, filter) + bias))
+ * with each step rounded to fp32 as the separate kernels would.  The host layer uses it
+ * when a FusedConv2D result is consumed only by such an Add (+ Relu); `residual` has the
+ * output's shape; post_activation is LINEAR, RELU or RELU6. */
+int tfjs_cuda_fused_conv2d_residual(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
+                                    int32_t x_id, int32_t filter_id, int32_t bias_id,
+                                    int32_t prelu_id, int32_t residual_id,
+                                    int32_t post_activation, int32_t out_id);
+
 /* ---- FusedDepthwiseConv2D / DepthwiseConv2dNative:
  * tfjs-backend-cpu/src/kernels/FusedDepthwiseConv2D.ts:25-61,
  * DepthwiseConv2dNative.ts:23-102; attrs kernel_names.ts:1033-1048.  out_c is
@@ -201,6 +212,11 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
                      int32_t a_id, const int64_t* a_shape, int32_t b_id,
                      const int64_t* b_shape, int32_t out_id,
                      const int64_t* out_shape);
+
+/* Add of two equal-shape float32 tensors fused with a following Relu / Relu6 (or none):
+ * out = activation(a + b).  Add.ts:23-30 then Relu.ts:22 / Relu6.ts:22-23. */
+int tfjs_cuda_add_activation(tfjs_cuda_ctx* ctx, int32_t activation, int32_t a_id,
+                             int32_t b_id, uint64_t n, int32_t out_id);
 
 /* ---- unary kernels: tfjs-backend-cpu/src/utils/unary_impl.ts:25-36 with Relu.ts,
  * Relu6.ts, Elu.ts, Sigmoid.ts, LeakyRelu.ts, Exp.ts, Sqrt.ts, Rsqrt.ts, Square.ts,

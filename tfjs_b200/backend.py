@@ -15,8 +15,20 @@ when a kernel first consumes them.  The graph executor reads axis / shape / perm
 Const tensors with dataSync() inside its node loop
 (tfjs-converter/src/operations/executors/utils.ts:55); with this rule those
 reads never touch the CUDA stream.
+
+Deferred launches.  A FusedConv2D with a linear activation and a same-shape float32
+Add return a tensor whose launch is pending; it is launched when the tensor is first
+read or consumed by another kernel.  An Add that consumes a pending convolution, and a
+Relu / Relu6 that consumes either, fold into the producer's epilogue instead
+(`tfjs_cuda_fused_conv2d_residual`, `tfjs_cuda_add_activation`), which removes the
+separate Add and Relu passes of a residual block.  Every step still rounds to fp32
+in the order of the separate kernels, so results do not change.  The WebGL backend
+defers work behind the same KernelBackend contract (uploads and packing happen on
+first use, tfjs-backend-webgl/src/backend_webgl.ts uploadToGPU).  Set
+TFJS_CUDA_NO_LAZY_FUSION=1 to launch every kernel eagerly.
 """
 import ctypes
+import os
 import time as _time
 from ctypes import byref, c_float, c_int32, c_uint64, c_void_p
 
@@ -63,14 +75,62 @@ class TensorInfo(object):
 
 
 class _Record(object):
-    __slots__ = ("dev", "nbytes", "dtype", "ref", "host")
+    __slots__ = ("dev", "nbytes", "dtype", "ref", "host", "pending", "held")
 
     def __init__(self, dev, nbytes, dtype, ref, host):
-        self.dev = dev        # device buffer id, 0 = not uploaded yet
+        self.dev = dev        # device buffer id, 0 = not uploaded / not launched yet
         self.nbytes = nbytes
         self.dtype = dtype
         self.ref = ref
         self.host = host      # numpy copy for small host-written tensors
+        self.pending = None   # PendingConv / PendingAdd until the launch happens
+        self.held = 0         # how many of `ref` belong to pending launches
+
+
+class PendingConv(object):
+    """A FusedConv2D (bias fused, linear activation) not launched yet, optionally with
+    the operand of the Add that consumed it."""
+    __slots__ = ("params", "x", "filt", "bias", "residual", "desc")
+
+    def __init__(self, params, x, filt, bias, residual, desc):
+        self.params, self.x, self.filt, self.bias = params, x, filt, bias
+        self.residual = residual
+        self.desc = desc      # profile records of the kernels folded into this launch
+
+    def deps(self):
+        return [d for d in (self.x, self.filt, self.bias, self.residual) if d is not None]
+
+    def launch(self, backend, out_dev, post_act):
+        lib, p = backend.lib, self.params
+        bias = backend.device_id(self.bias) if self.bias is not None else 0
+        if self.residual is None:
+            if post_act != "linear":
+                p = _cabi.Conv2DParams.from_buffer_copy(p)
+                p.activation = _cabi.ACTIVATIONS[post_act]
+            backend.check(lib.tfjs_cuda_fused_conv2d(
+                backend.ctx, byref(p), backend.device_id(self.x), backend.device_id(self.filt),
+                bias, 0, out_dev))
+        else:
+            backend.check(lib.tfjs_cuda_fused_conv2d_residual(
+                backend.ctx, byref(p), backend.device_id(self.x), backend.device_id(self.filt),
+                bias, 0, backend.device_id(self.residual), _cabi.ACTIVATIONS[post_act],
+                out_dev))
+
+
+class PendingAdd(object):
+    """A same-shape float32 Add not launched yet."""
+    __slots__ = ("a", "b", "n", "desc")
+
+    def __init__(self, a, b, n, desc):
+        self.a, self.b, self.n, self.desc = a, b, n, desc
+
+    def deps(self):
+        return [self.a, self.b]
+
+    def launch(self, backend, out_dev, post_act):
+        backend.check(backend.lib.tfjs_cuda_add_activation(
+            backend.ctx, _cabi.ACTIVATIONS[post_act], backend.device_id(self.a),
+            backend.device_id(self.b), self.n, out_dev))
 
 
 def size_from_shape(shape):
@@ -94,6 +154,9 @@ class CudaBackend(object):
         self.device_ordinal = device_ordinal
         self.data = {}        # DataId -> _Record
         self._pinned = []
+        self._hidden = 0      # records kept alive only by pending launches
+        self.lazy_fusion = os.environ.get("TFJS_CUDA_NO_LAZY_FUSION", "0") in ("", "0")
+        self.profiler = None  # the engine, while it profiles (told about deferred launches)
 
     # ------------------------------------------------------------ plumbing --
     def check(self, rc):
@@ -149,10 +212,81 @@ class CudaBackend(object):
         self.data[dataId] = _Record(self._alloc(nbytes), nbytes, dtype, 1, None)
         return TensorInfo(dataId, shape, dtype)
 
+    # ---------------------------------------------------- deferred launches --
+    def _adjust(self, rec, dref, dheld):
+        """Change a record's reference counts, tracking whether only pending launches
+        keep it alive (such records are not reported by numDataIds)."""
+        was = rec.held > 0 and rec.ref <= rec.held
+        rec.ref += dref
+        rec.held += dheld
+        now = rec.held > 0 and rec.ref <= rec.held
+        if was != now:
+            self._hidden += 1 if now else -1
+
+    def defer(self, shape, dtype, pending):
+        """Output tensor of a kernel whose launch is deferred; the inputs stay alive
+        until the launch happened or the output was disposed."""
+        nbytes = size_from_shape(shape) * np.dtype(NP_DTYPES[dtype]).itemsize
+        dataId = DataId()
+        rec = _Record(0, nbytes, dtype, 1, None)
+        rec.pending = pending
+        for d in pending.deps():
+            self._adjust(self.data[d], 1, 1)
+        self.data[dataId] = rec
+        return TensorInfo(dataId, shape, dtype)
+
+    def pending_of(self, dataId):
+        return self.data[dataId].pending
+
+    def _release(self, pending):
+        for d in pending.deps():
+            rec = self.data[d]
+            self._adjust(rec, -1, -1)
+            if rec.ref <= 0:
+                self._drop(d, rec)
+
+    def _launch(self, pending, dev, post_act, fold_into_caller):
+        if self.profiler is None:
+            return pending.launch(self, dev, post_act)
+        # operands that are themselves pending launch first, as records of their own
+        for d in pending.deps():
+            self.device_id(d)
+        return self.profiler.deferred_launch(
+            pending.desc, lambda: pending.launch(self, dev, post_act), fold_into_caller)
+
+    def _resolve(self, rec):
+        pending = rec.pending
+        dev = self._alloc(rec.nbytes)
+        try:
+            self._launch(pending, dev, "linear", False)
+        except Exception:
+            self.lib.tfjs_cuda_free(self.ctx, dev)
+            raise
+        rec.dev = dev
+        rec.pending = None
+        self._release(pending)
+
+    def launch_pending(self, info, post_act):
+        """Launch the pending producer of `info` with `post_act` (relu / relu6) folded
+        into its epilogue and return the activated tensor.  `info` itself stays
+        pending: if another kernel consumes it later it is launched again, without
+        the activation."""
+        pending = self.data[info.dataId].pending
+        out = self.make_output(info.shape, "float32")
+        try:
+            self._launch(pending, self.data[out.dataId].dev, post_act, True)
+        except Exception:
+            self.disposeData(out.dataId)
+            raise
+        return out
+
     def device_id(self, dataId):
-        """Device buffer id of a tensor, uploading a host-resident one first."""
+        """Device buffer id of a tensor; launches a pending producer or uploads a
+        host-resident tensor first."""
         rec = self.data[dataId]
-        if rec.dev == 0:
+        if rec.pending is not None:
+            self._resolve(rec)
+        elif rec.dev == 0:
             rec.dev = self._alloc(rec.nbytes)
             if rec.nbytes:
                 self.check(self.lib.tfjs_cuda_write(
@@ -166,6 +300,8 @@ class CudaBackend(object):
     def readSync(self, dataId):
         """backend_cpu.ts:129-144: the only blocking call besides time()."""
         rec = self.data[dataId]
+        if rec.pending is not None:
+            self._resolve(rec)
         if rec.host is not None:
             out = rec.host.copy()
         else:
@@ -181,6 +317,8 @@ class CudaBackend(object):
     def read_into(self, dataId, host_array):
         """readSync into caller-provided (ideally pinned) memory."""
         rec = self.data[dataId]
+        if rec.pending is not None:
+            self._resolve(rec)
         if rec.host is not None:
             host_array.reshape(-1)[:] = rec.host
             return
@@ -192,28 +330,36 @@ class CudaBackend(object):
         rec = self.data.get(dataId)
         if rec is None:
             return False
-        rec.ref -= 1
-        if not force and rec.ref > 0:
+        self._adjust(rec, -1, 0)
+        if rec.ref > 0 and (not force or rec.held > 0):
             return False
+        self._drop(dataId, rec)
+        return True
+
+    def _drop(self, dataId, rec):
+        if rec.held > 0 and rec.ref <= rec.held:
+            self._hidden -= 1
+        del self.data[dataId]
         if rec.dev:
             self.check(self.lib.tfjs_cuda_free(self.ctx, rec.dev))
-        del self.data[dataId]
-        return True
+        if rec.pending is not None:
+            pending, rec.pending = rec.pending, None
+            self._release(pending)
 
     def refCount(self, dataId):
         rec = self.data.get(dataId)
-        return rec.ref if rec is not None else 0
+        return rec.ref - rec.held if rec is not None else 0
 
     def incRef(self, dataId):
-        self.data[dataId].ref += 1
+        self._adjust(self.data[dataId], 1, 0)
 
     def decRef(self, dataId):
         rec = self.data.get(dataId)
         if rec is not None:
-            rec.ref -= 1
+            self._adjust(rec, -1, 0)
 
     def numDataIds(self):
-        return len(self.data)
+        return len(self.data) - self._hidden
 
     def memory(self):
         """tfjs-core/src/engine.ts:959-974 merges this into tf.memory()."""

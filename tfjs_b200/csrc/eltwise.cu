@@ -157,6 +157,28 @@ __global__ void binary_same_kernel(const float* __restrict__ a,
     o[i] = binary_eval<OP>(a[i], b[i]);
 }
 
+// out = act(a + b) for equal shapes: the residual Add followed by Relu of a
+// bottleneck block, in one pass (3 tensor transfers instead of 5).
+template <int ACT>
+__global__ void add_act_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                               float* __restrict__ o, uint64_t n) {
+  const uint64_t n4 = n >> 2;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const float4* a4 = reinterpret_cast<const float4*>(a);
+  const float4* b4 = reinterpret_cast<const float4*>(b);
+  float4* o4 = reinterpret_cast<float4*>(o);
+  auto f = [](float x, float y) {
+    const float s = __fadd_rn(x, y);
+    return ACT == TFJS_CUDA_ACT_RELU ? js_relu(s) : (ACT == TFJS_CUDA_ACT_RELU6 ? js_relu6(s) : s);
+  };
+  for (uint64_t i = tid; i < n4; i += stride) {
+    const float4 u = a4[i], v = b4[i];
+    o4[i] = make_float4(f(u.x, v.x), f(u.y, v.y), f(u.z, v.z), f(u.w, v.w));
+  }
+  for (uint64_t i = (n4 << 2) + tid; i < n; i += stride) o[i] = f(a[i], b[i]);
+}
+
 // One operand is the full tensor, the other repeats with period `period`
 // (bias over the innermost axis, or a scalar when period == 1).  period % 4 == 0
 // or period == 1.  SWAP: the periodic operand is the left one.
@@ -564,6 +586,34 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
   }
 #undef BIN_CASE
   LAUNCH_CHECK(ctx, "binary_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_add_activation(tfjs_cuda_ctx* ctx, int32_t activation, int32_t a_id,
+                             int32_t b_id, uint64_t n, int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (activation != TFJS_CUDA_ACT_LINEAR && activation != TFJS_CUDA_ACT_RELU &&
+      activation != TFJS_CUDA_ACT_RELU6)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "add_activation: activation %d", activation);
+  Buffer *a, *b, *o;
+  int rc;
+  if ((rc = ctx_get(ctx, a_id, n * 4, "add_activation a", &a))) return rc;
+  if ((rc = ctx_get(ctx, b_id, n * 4, "add_activation b", &b))) return rc;
+  if ((rc = ctx_get(ctx, out_id, n * 4, "add_activation out", &o))) return rc;
+  if (n == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  const unsigned grid = grid_for((n + 3) / 4, kThreads, ctx->sm_count);
+  const float* ap = (const float*)a->ptr;
+  const float* bp = (const float*)b->ptr;
+  float* op = (float*)o->ptr;
+  if (activation == TFJS_CUDA_ACT_RELU)
+    add_act_kernel<TFJS_CUDA_ACT_RELU><<<grid, kThreads, 0, ctx->stream>>>(ap, bp, op, n);
+  else if (activation == TFJS_CUDA_ACT_RELU6)
+    add_act_kernel<TFJS_CUDA_ACT_RELU6><<<grid, kThreads, 0, ctx->stream>>>(ap, bp, op, n);
+  else
+    add_act_kernel<TFJS_CUDA_ACT_LINEAR><<<grid, kThreads, 0, ctx->stream>>>(ap, bp, op, n);
+  LAUNCH_CHECK(ctx, "add_act_kernel");
   ctx_mark_written(ctx, out_id);
   return TFJS_CUDA_OK;
 }

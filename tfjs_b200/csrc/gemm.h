@@ -25,6 +25,10 @@ struct GemmProblem {
   bool trans_a = false, trans_b = false;
   bool is_conv = false;
   ConvGeo conv;
+  // optional second stage of the epilogue: out = post_act(act(A.B + bias) + residual),
+  // residual shaped like the output (the bottleneck shortcut of a residual network)
+  const float* residual = nullptr;
+  int post_act = 0;  // TFJS_CUDA_ACT_LINEAR or TFJS_CUDA_ACT_RELU / RELU6
 };
 
 // B operand layouts understood by the tensor-core kernel.

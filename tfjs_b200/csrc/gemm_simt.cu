@@ -26,6 +26,8 @@ struct SimtGemmArgs {
   long long a_row_stride, a_k_stride;  // matmul A addressing
   long long b_k_stride, b_n_stride;
   ConvGeo conv;                        // used when IS_CONV
+  const float* residual;
+  int post_act;
 };
 
 template <bool IS_CONV>
@@ -103,7 +105,13 @@ gemm_simt_kernel(SimtGemmArgs g) {
       if (n >= g.N) continue;
       float v = acc[i][j];
       if (g.bias_len) v = __fadd_rn(v, g.bias[g.bias_len == 1 ? 0 : n]);
-      c[(long long)m * g.N + n] = apply_act(v, g.ap, n);
+      v = apply_act(v, g.ap, n);
+      if (g.residual) {
+        v = __fadd_rn(g.residual[(long long)bz * g.M * g.N + (long long)m * g.N + n], v);
+        if (g.post_act == TFJS_CUDA_ACT_RELU) v = js_relu(v);
+        else if (g.post_act == TFJS_CUDA_ACT_RELU6) v = js_relu6(v);
+      }
+      c[(long long)m * g.N + n] = v;
     }
   }
 }
@@ -124,6 +132,8 @@ int launch_gemm_simt(tfjs_cuda_ctx* ctx, const GemmProblem& pr) {
   g.b_k_stride = pr.trans_b ? 1 : pr.N;
   g.b_n_stride = pr.trans_b ? pr.K : 1;
   g.conv = pr.conv;
+  g.residual = pr.residual;
+  g.post_act = pr.post_act;
   if (pr.batch > 65535)
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "matmul: batch %d too large for the fp32 path", pr.batch);
   dim3 grid((pr.M + BM - 1) / BM, (pr.N + BN - 1) / BN, pr.batch);

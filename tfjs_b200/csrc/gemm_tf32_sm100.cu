@@ -49,6 +49,8 @@ struct Tf32Args {
   int k_steps;
   int* flag;
   int c_tma;  // 1: the epilogue stores through the C tensor map (N % 4 == 0)
+  const float* residual;  // optional: out = post_act(act(acc + bias) + residual)
+  int post_act;
   // gathered convolution
   const float* x;
   ConvGeo conv;
@@ -191,27 +193,33 @@ __device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g,
 
 constexpr int kTapTableEntries = 512;  // scalar-gather K limit (after padding to 32)
 
-template <int BN, int A_MODE = 0>
+constexpr int kBarrierBytes = 384;  // pipeline barriers, TMEM slot, residual barriers
+
+// RES: the epilogue adds a residual tile that the TMA unit prefetches into the
+// staging tile of the next chunk (two staging tiles per warp, and at BN = 256 one
+// pipeline stage fewer to make room for them).
+template <int BN, int A_MODE = 0, int RES = 0>
 struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
   // the scalar-gather mode gives one stage up for its tap table
-  static constexpr int STAGES =
-      (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 6 : 8))) - (A_MODE == 3 ? 1 : 0);
+  static constexpr int STAGES = (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 6 : 8))) -
+                                (A_MODE == 3 ? 1 : 0) - (RES && BN >= 256 ? 1 : 0);
   // staging tiles per epilogue warp: two below BN = 256 (bandwidth-bound shapes), so
   // a warp fills one while the TMA unit still drains the other
-  static constexpr int EPI_BUFS = BN >= 256 ? 1 : 2;
+  static constexpr int EPI_BUFS = (BN >= 256 && !RES) ? 1 : 2;
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int SMEM_BYTES =
-      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + 8 * EPI_BUFS * 4096 +
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + kBarrierBytes + 8 * EPI_BUFS * 4096 +
       (A_MODE == 3 ? kTapTableEntries * 4 : 0);
 };
 
-template <int BN, int B_MN, int A_MODE>
+template <int BN, int B_MN, int A_MODE, int RES>
 __global__ void __launch_bounds__((A_MODE == 1 || A_MODE == 3) ? 448 : 320, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_b,
-                 const __grid_constant__ CUtensorMap tm_c, const Tf32Args g) {
-  using C = Cfg<BN, A_MODE>;
+                 const __grid_constant__ CUtensorMap tm_c,
+                 const __grid_constant__ CUtensorMap tm_r, const Tf32Args g) {
+  using C = Cfg<BN, A_MODE, RES>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -225,6 +233,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  // residual prefetch barriers: one per epilogue warp and staging tile
+  auto res_bar = [&](int w, uint32_t b) { return bar_base + 256u + 8u * (2u * w + b); };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -238,6 +248,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), BN == 32 ? 128 : 256);
     }
+    if (RES)
+      for (int w = 0; w < 8; ++w) {
+        mbar_init(res_bar(w, 0), 1);
+        mbar_init(res_bar(w, 1), 1);
+      }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -248,7 +263,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  const uint32_t tap_table = bar_base + 256u;  // A_MODE 3 only
+  const uint32_t tap_table = bar_base + (uint32_t)kBarrierBytes;  // A_MODE 3 only
   if (A_MODE == 3 && warp >= 10) {
     // entry k: filter tap index in the top byte, element offset of (tap, channel)
     // from the tile pixel's top-left input element in the low 24 bits
@@ -381,6 +396,35 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     uint32_t ebuf = 0;
     const uint32_t sw = (uint32_t)(lane & 7);
     const bool vec4 = (g.N & 3) == 0;
+    // Residual prefetch (RES): a cursor runs one chunk ahead of the loop below over
+    // the same (tile, chunk) sequence; lane 0 asks the TMA unit for the residual
+    // 32 x 32 tile of that chunk, into the staging tile the chunk will use.
+    const int first_c0 = BN == 32 ? 0 : half * 32;
+    int p_tile = blockIdx.x, p_it = 0, p_c0 = first_c0;
+    uint32_t rphase = 0;       // bit b: parity the next wait on res_bar(b) uses
+    bool res_issued = false;   // a load into the current staging tile is in flight
+    auto prefetch_residual = [&](uint32_t b) -> bool {
+      while (p_tile < g.total_tiles) {
+        const int n0 = (p_tile % g.tiles_n) * BN + p_c0;
+        if (!(BN == 32 && (p_it & 1) != half) && p_c0 < BN && n0 < g.N) {
+          const int rest = p_tile / g.tiles_n;
+          const int m_base = (rest % g.tiles_m) * BM + q * 32;
+          p_c0 += 64;
+          if (m_base >= g.M) return false;  // rows beyond the tensor: nothing to add
+          if (lane == 0) {
+            const uint32_t bar = res_bar(warp - 2, b);
+            mbar_expect_tx(bar, 4096u);
+            tma_load_3d(stage_base + b * 4096u, &tm_r, bar, n0, m_base, rest / g.tiles_m);
+          }
+          return true;
+        }
+        p_tile += gridDim.x;
+        ++p_it;
+        p_c0 = first_c0;
+      }
+      return false;
+    };
+    if (RES) res_issued = prefetch_residual(0);
     int it = 0;
     for (int tile = blockIdx.x; tile < g.total_tiles; tile += gridDim.x, ++it) {
       const int nt = tile % g.tiles_n;
@@ -392,12 +436,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (BN == 32 && (it & 1) != half) continue;  // the other warp of the pair takes it
       if (!mbar_wait(tfull_bar(acc), aphase)) {
         if (lane == 0) atomicExch(g.flag, 4);
+        // let the residual load in flight land before this CTA's shared memory goes
+        if (RES && res_issued) mbar_wait(res_bar(warp - 2, ebuf), (rphase >> ebuf) & 1u);
+        res_issued = false;
         break;
       }
       tc_fence_after();
       const int m_base = mt * BM + q * 32;
       const int rows_valid = g.M - m_base < 32 ? g.M - m_base : 32;
       float* cbase = g.c + ((long long)bz * g.M + m_base) * g.N;
+      const float* rbase = g.residual + ((long long)bz * g.M + m_base) * g.N;
       bool released = false;
 #pragma unroll 1
       for (int c0 = BN == 32 ? 0 : half * 32; c0 < BN; c0 += 64) {
@@ -415,6 +463,57 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         chunk_math_dispatch(v, g, n0);
         const uint32_t stage_buf = stage_base + ebuf * 4096u;
         const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
+        if (RES) {
+          // out = post(residual + act(acc + bias)): the residual tile sits in this
+          // chunk's staging tile in the layout the result is staged in, so each lane
+          // reads the 16-byte pieces it is about to overwrite.
+          if (res_issued) {
+            const bool ok = mbar_wait(res_bar(warp - 2, ebuf), (rphase >> ebuf) & 1u);
+            rphase ^= 1u << ebuf;
+            if (!ok && lane == 0) atomicExch(g.flag, 5);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 rs;
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(rs.x), "=f"(rs.y), "=f"(rs.z), "=f"(rs.w)
+                           : "r"(my_row + (((uint32_t)j ^ sw) << 4)));
+              v[4 * j] = __fadd_rn(rs.x, v[4 * j]);
+              v[4 * j + 1] = __fadd_rn(rs.y, v[4 * j + 1]);
+              v[4 * j + 2] = __fadd_rn(rs.z, v[4 * j + 2]);
+              v[4 * j + 3] = __fadd_rn(rs.w, v[4 * j + 3]);
+            }
+            if (g.post_act == TFJS_CUDA_ACT_RELU) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = js_relu(v[j]);
+            } else if (g.post_act == TFJS_CUDA_ACT_RELU6) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = js_relu6(v[j]);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(
+                             my_row + (((uint32_t)j ^ sw) << 4)),
+                         "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                         : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (rows_valid > 0) {
+              asm volatile(
+                  "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                  ::"l"(&tm_c), "r"(stage_buf), "r"(n0), "r"(m_base), "r"(bz)
+                  : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            // the other staging tile is free once the store before this one has read it
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          }
+          __syncwarp();  // no lane writes that tile before lane 0 has seen it free
+          ebuf ^= 1;
+          res_issued = prefetch_residual(ebuf);
+          continue;
+        }
         if (C::EPI_BUFS == 2) ebuf ^= 1;
         if (g.c_tma) {
           // the bulk store that last used this staging tile must have finished reading it
@@ -450,13 +549,32 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
             const int qv = w >> 2;
             const int total = rows_valid * qv;
             for (int idx = lane; idx < total; idx += 32) {
-              const int row = idx / qv, vv = idx - row * qv;
+              int row, vv;
+              if (qv == 8) { row = idx >> 3; vv = idx & 7; }
+              else { row = idx / qv; vv = idx - row * qv; }
               float4 val;
               asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                            : "=f"(val.x), "=f"(val.y), "=f"(val.z), "=f"(val.w)
                            : "r"(stage_buf + (uint32_t)row * 128u +
                                  (((uint32_t)vv ^ (uint32_t)(row & 7)) << 4)));
-              *reinterpret_cast<float4*>(cbase + (long long)row * g.N + n0 + vv * 4) = val;
+              const long long off = (long long)row * g.N + n0 + vv * 4;
+              if (g.residual) {
+                // residual tile read along rows, like the stores: a + b in the order
+                // of the reference's Add(shortcut, branch), then the trailing Relu
+                const float4 rs = __ldg(reinterpret_cast<const float4*>(rbase + off));
+                val.x = __fadd_rn(rs.x, val.x);
+                val.y = __fadd_rn(rs.y, val.y);
+                val.z = __fadd_rn(rs.z, val.z);
+                val.w = __fadd_rn(rs.w, val.w);
+                if (g.post_act == TFJS_CUDA_ACT_RELU) {
+                  val.x = js_relu(val.x); val.y = js_relu(val.y);
+                  val.z = js_relu(val.z); val.w = js_relu(val.w);
+                } else if (g.post_act == TFJS_CUDA_ACT_RELU6) {
+                  val.x = js_relu6(val.x); val.y = js_relu6(val.y);
+                  val.z = js_relu6(val.z); val.w = js_relu6(val.w);
+                }
+              }
+              *reinterpret_cast<float4*>(cbase + off) = val;
             }
           } else {
             const int total = rows_valid * w;
@@ -468,7 +586,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                            : "r"(stage_buf + (uint32_t)row * 128u +
                                  ((((uint32_t)col >> 2) ^ (uint32_t)(row & 7)) << 4) +
                                  ((uint32_t)col & 3u) * 4u));
-              cbase[(long long)row * g.N + n0 + col] = val;
+              const long long off = (long long)row * g.N + n0 + col;
+              if (g.residual) {
+                val = __fadd_rn(__ldg(rbase + off), val);
+                if (g.post_act == TFJS_CUDA_ACT_RELU) val = js_relu(val);
+                else if (g.post_act == TFJS_CUDA_ACT_RELU6) val = js_relu6(val);
+              }
+              cbase[off] = val;
             }
           }
         }
@@ -735,11 +859,11 @@ bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv) {
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, int B_MN, int A_MODE>
+template <int BN, int B_MN, int A_MODE, int RES = 0>
 int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
-               const CUtensorMap& tm_c, Tf32Args& g) {
-  using C = Cfg<BN, A_MODE>;
-  auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE>;
+               const CUtensorMap& tm_c, const CUtensorMap& tm_r, Tf32Args& g) {
+  using C = Cfg<BN, A_MODE, RES>;
+  auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE, RES>;
   static bool configured[64] = {false};  // per device ordinal
   if (ctx->device >= 64 || !configured[ctx->device]) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -749,19 +873,19 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
   g.tiles_n = (g.N + BN - 1) / BN;
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
-  kern<<<grid, (A_MODE == 1 || A_MODE == 3) ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, tm_c, g);
+  kern<<<grid, (A_MODE == 1 || A_MODE == 3) ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, tm_c, tm_r, g);
   LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
   return TFJS_CUDA_OK;
 }
 
-template <int B_MN, int A_MODE>
+template <int B_MN, int A_MODE, int RES = 0>
 int launch_bn(tfjs_cuda_ctx* ctx, int bn, const CUtensorMap& a, const CUtensorMap& b,
-              const CUtensorMap& c, Tf32Args& g) {
+              const CUtensorMap& c, const CUtensorMap& r, Tf32Args& g) {
   switch (bn) {
-    case 32: return launch_cfg<32, B_MN, A_MODE>(ctx, a, b, c, g);
-    case 64: return launch_cfg<64, B_MN, A_MODE>(ctx, a, b, c, g);
-    case 128: return launch_cfg<128, B_MN, A_MODE>(ctx, a, b, c, g);
-    default: return launch_cfg<256, B_MN, A_MODE>(ctx, a, b, c, g);
+    case 32: return launch_cfg<32, B_MN, A_MODE, RES>(ctx, a, b, c, r, g);
+    case 64: return launch_cfg<64, B_MN, A_MODE, RES>(ctx, a, b, c, r, g);
+    case 128: return launch_cfg<128, B_MN, A_MODE, RES>(ctx, a, b, c, r, g);
+    default: return launch_cfg<256, B_MN, A_MODE, RES>(ctx, a, b, c, r, g);
   }
 }
 
@@ -794,22 +918,37 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   g.conv = pr.conv;
   g.chunks_per_tap = op.cin_pad / BK;
   const int bn = pick_bn(pr.M, pr.N, pr.batch, ctx->sm_count);
-  CUtensorMap tm_a, tm_b, tm_c;
+  CUtensorMap tm_a, tm_b, tm_c, tm_r;
   int rc;
-  // output map for the epilogue's bulk stores: dims (N, M, batch), 32 x 32 boxes
+  // output map for the epilogue's bulk stores, and the same view of the residual for
+  // its prefetches: dims (N, M, batch), 32 x 32 boxes
   memset(&tm_c, 0, sizeof tm_c);
+  memset(&tm_r, 0, sizeof tm_r);
   g.c_tma = 0;
-  if ((pr.N & 3) == 0 && ((uintptr_t)pr.c & 15) == 0) {
+  g.residual = pr.residual;
+  g.post_act = pr.post_act;
+  bool res_tma = false;
+  if ((pr.N & 3) == 0 && ((uintptr_t)pr.c & 15) == 0 && ((uintptr_t)pr.residual & 15) == 0) {
     EncodeTiledFn enc = get_encode();
     cuuint64_t dims[3] = {(cuuint64_t)pr.N, (cuuint64_t)pr.M, (cuuint64_t)pr.batch};
     cuuint64_t strides[2] = {(cuuint64_t)pr.N * 4, (cuuint64_t)pr.M * pr.N * 4};
     cuuint32_t box[3] = {32, 32, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    if (enc && enc(&tm_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)pr.c, dims, strides, box,
-                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
-                   CUDA_SUCCESS)
-      g.c_tma = getenv("TFJS_CUDA_NO_TMA_STORE") ? 0 : 1;  // debugging knob
+    auto encode = [&](CUtensorMap* tm, const void* base, CUtensorMapL2promotion l2) {
+      return enc && enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, l2,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    static int no_tma_store = -1;
+    if (no_tma_store < 0) no_tma_store = getenv("TFJS_CUDA_NO_TMA_STORE") ? 1 : 0;  // debugging knob
+    const bool ok = !no_tma_store && encode(&tm_c, pr.c, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    if (!pr.residual) {
+      g.c_tma = ok ? 1 : 0;
+    } else if (ok && op.b_layout == B_K_MAJOR && (op.a_gather == 0 || op.a_gather == 1) &&
+               encode(&tm_r, pr.residual, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
+      // the residual epilogue exists for the TMA-fed A operand modes
+      res_tma = true;
+    }
   }
   bool im2col = false;
   if (op.a_gather == 1) {
@@ -833,14 +972,24 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
       return rc;
     if (op.a_gather == 2) {
       tm_a = tm_b;  // unused by the gather kernel
-      return launch_bn<0, 3>(ctx, bn, tm_a, tm_b, tm_c, g);
+      return launch_bn<0, 3>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }
-    if (im2col) return launch_bn<0, 2>(ctx, bn, tm_a, tm_b, tm_c, g);
+    if (im2col) {
+      if (res_tma) {
+        g.c_tma = 1;
+        return launch_bn<0, 2, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
+      }
+      return launch_bn<0, 2>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
+    }
     if (op.a_gather) {
       tm_a = tm_b;  // unused by the gather kernel
-      return launch_bn<0, 1>(ctx, bn, tm_a, tm_b, tm_c, g);
+      return launch_bn<0, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }
-    return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, tm_c, g);
+    if (res_tma) {
+      g.c_tma = 1;
+      return launch_bn<0, 0, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
+    }
+    return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
   }
   if ((rc = make_map(ctx, &tm_b, op.b, (uint64_t)pr.N, (uint64_t)pr.K,
                      (uint64_t)pr.batch_b, (uint64_t)op.ldb, (uint64_t)pr.K * op.ldb, 32,
@@ -848,5 +997,5 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     return rc;
   if (op.a_gather)
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "convolution filters are always packed K-major");
-  return launch_bn<1, 0>(ctx, bn, tm_a, tm_b, tm_c, g);
+  return launch_bn<1, 0>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
 }

@@ -209,9 +209,9 @@ int tfjs_cuda_fused_matmul(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
   return rc;
 }
 
-int tfjs_cuda_fused_conv2d(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
-                           int32_t x_id, int32_t filter_id, int32_t bias_id,
-                           int32_t prelu_id, int32_t out_id) {
+static int conv2d_impl(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p, int32_t x_id,
+                       int32_t filter_id, int32_t bias_id, int32_t prelu_id,
+                       int32_t residual_id, int32_t post_activation, int32_t out_id) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
   if (!p) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_conv2d: null params");
   if (p->batch < 0 || p->in_h < 0 || p->in_w < 0 || p->in_c < 0 || p->out_h < 0 ||
@@ -234,6 +234,17 @@ int tfjs_cuda_fused_conv2d(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
   if (p->bias_len && (rc = ctx_get(ctx, bias_id, (uint64_t)p->bias_len * 4, "fused_conv2d bias", &bias))) return rc;
   if ((rc = ctx_get(ctx, out_id, M64 * p->out_c * 4, "fused_conv2d out", &out))) return rc;
   GemmProblem pr;
+  if (residual_id) {
+    Buffer* res;
+    if ((rc = ctx_get(ctx, residual_id, M64 * p->out_c * 4, "fused_conv2d residual", &res)))
+      return rc;
+    if (post_activation != TFJS_CUDA_ACT_LINEAR && post_activation != TFJS_CUDA_ACT_RELU &&
+        post_activation != TFJS_CUDA_ACT_RELU6)
+      return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
+                      "fused_conv2d_residual: post activation must be linear, relu or relu6");
+    pr.residual = (const float*)res->ptr;
+    pr.post_act = post_activation;
+  }
   if ((rc = fill_act(ctx, p->activation, p->prelu_len, prelu_id, p->leakyrelu_alpha,
                      p->out_c, "fused_conv2d", &pr.ap)))
     return rc;
@@ -308,6 +319,22 @@ int tfjs_cuda_fused_conv2d(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
   rc = launch_gemm_simt(ctx, pr);
   if (rc == TFJS_CUDA_OK) ctx_mark_written(ctx, out_id);
   return rc;
+}
+
+int tfjs_cuda_fused_conv2d(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
+                           int32_t x_id, int32_t filter_id, int32_t bias_id,
+                           int32_t prelu_id, int32_t out_id) {
+  return conv2d_impl(ctx, p, x_id, filter_id, bias_id, prelu_id, 0, TFJS_CUDA_ACT_LINEAR, out_id);
+}
+
+int tfjs_cuda_fused_conv2d_residual(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p,
+                                    int32_t x_id, int32_t filter_id, int32_t bias_id,
+                                    int32_t prelu_id, int32_t residual_id,
+                                    int32_t post_activation, int32_t out_id) {
+  if (ctx && !residual_id)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_conv2d_residual: residual tensor missing");
+  return conv2d_impl(ctx, p, x_id, filter_id, bias_id, prelu_id, residual_id, post_activation,
+                     out_id);
 }
 
 }  // extern "C"

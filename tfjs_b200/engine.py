@@ -71,6 +71,8 @@ class Engine(object):
         self.num_tensors = 0
         self.is_test = False
         self._profile = None   # list of kernel records while tf.profile is active
+        self._prof_stack = []  # records of the kernel funcs being executed
+        self._prof_next_slot = 0
 
     # ---------------------------------------------------------- backends --
     def register_backend(self, name, factory, priority=1):
@@ -164,16 +166,21 @@ class Engine(object):
         before = self.backend.numDataIds()
         prof = self._profile
         if prof is not None:
-            slot = 2 * len(prof)
-            self.backend.event_record(slot)
+            rec = {"name": kernel_name, "slot": self._take_slots(),
+                   "inputShapes": {k: list(v.shape) for k, v in infos.items() if v is not None},
+                   "attrs": attrs or {}, "parts": [], "nested": []}
+            self._prof_stack.append(rec)
+            self.backend.event_record(rec["slot"])
         out = kernel.kernelFunc({"inputs": infos, "attrs": attrs or {}, "backend": self.backend})
         if prof is not None:
-            self.backend.event_record(slot + 1)
+            self.backend.event_record(rec["slot"] + 1)
+            self._prof_stack.pop()
             o = out if isinstance(out, (list, tuple)) else [out]
-            prof.append({"name": kernel_name, "slot": slot,
-                         "inputShapes": {k: list(v.shape) for k, v in infos.items()
-                                         if v is not None},
-                         "outputShapes": [list(t.shape) for t in o], "attrs": attrs or {}})
+            rec["outputShapes"] = [list(t.shape) for t in o]
+            # a kernel whose launch was deferred shows up later, as `parts` of the
+            # record in which it was launched
+            rec["deferred"] = any(self.backend.pending_of(t.dataId) is not None for t in o)
+            prof.append(rec)
         outs = out if isinstance(out, (list, tuple)) else [out]
         if self.is_test:
             # engine.ts:557-588: a kernel may only add one data id per output
@@ -188,18 +195,53 @@ class Engine(object):
         return tensors if isinstance(out, (list, tuple)) else tensors[0]
 
 
+    def _take_slots(self):
+        slot = self._prof_next_slot
+        self._prof_next_slot += 2
+        return slot
+
+    def deferred_launch(self, descs, launch, fold_into_caller):
+        """Called by the backend while profiling when it launches deferred kernels
+        (`descs`: their would-be records).  A launch folded into the calling kernel
+        (an activation joining its producer) becomes part of the caller's record;
+        a launch that merely had to happen first gets a record of its own and its
+        time is taken out of the caller's."""
+        if fold_into_caller and self._prof_stack:
+            self._prof_stack[-1]["parts"] = list(descs)
+            self._prof_stack[-1]["folded"] = True
+            return launch()
+        rec = {"name": "+".join(d["name"] for d in descs), "slot": self._take_slots(),
+               "inputShapes": {}, "outputShapes": descs[-1]["outputShapes"], "attrs": {},
+               "parts": list(descs), "nested": [], "deferred": False}
+        self.backend.event_record(rec["slot"])
+        result = launch()
+        self.backend.event_record(rec["slot"] + 1)
+        if self._prof_stack:
+            self._prof_stack[-1]["nested"].append(rec["slot"])
+        self._profile.append(rec)
+        return result
+
     def profile(self, f):
         """tf.profile (engine.ts:976-998): runs f and returns one record per kernel
         with its name, shapes and device time (`kernelTimeMs`, from CUDA events
         recorded on the backend's stream around each kernel func)."""
         self.ready()
         self._profile = []
+        self._prof_stack = []
+        self._prof_next_slot = 0
+        self.backend.profiler = self
         try:
             result = f()
         finally:
             records, self._profile = self._profile, None
+            self.backend.profiler = None
         for rec in records:
-            rec["kernelTimeMs"] = self.backend.event_elapsed(rec["slot"], rec["slot"] + 1)
+            ms = self.backend.event_elapsed(rec["slot"], rec["slot"] + 1)
+            for slot in rec["nested"]:
+                ms -= self.backend.event_elapsed(slot, slot + 1)
+            rec["kernelTimeMs"] = max(ms, 0.0)
+            if rec.get("folded"):
+                rec["name"] = "+".join([d["name"] for d in rec["parts"]] + [rec["name"]])
         return {"kernels": records, "result": result}
 
 

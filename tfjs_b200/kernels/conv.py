@@ -9,6 +9,8 @@ WASM backend does before calling into C
 from ctypes import byref
 
 from .. import _cabi, conv_util
+from ..backend import PendingConv
+from ..util import size_from_shape
 from ..kernel_registry import KernelConfig
 from .common import BACKEND, assert_not_complex, dev, per_channel_len, require_float32
 from . import elementwise, movement
@@ -86,6 +88,15 @@ def _conv_impl(backend, x, filt, bias, prelu, attrs, activation, depthwise):
                          "in the CUDA backend" % name)
     p = _params(ci, activation if fuse_act else "linear", bias_len if fuse_bias else 0,
                 (prelu_len or 0) if fuse_act else 0, alpha, depthwise)
+    if (backend.lazy_fusion and not depthwise and not nchw and fuse_bias and
+            activation == "linear" and size_from_shape(ci.outShape) > 0):
+        # Deferred: a following Add and / or Relu folds into this launch's epilogue.
+        desc = {"name": "FusedConv2D",
+                "inputShapes": dict([("x", list(x.shape)), ("filter", list(filt.shape))] +
+                                    ([("bias", list(bias.shape))] if bias is not None else [])),
+                "outputShapes": [list(ci.outShape)], "attrs": {}}
+        return backend.defer(ci.outShape, "float32", PendingConv(
+            p, x.dataId, filt.dataId, bias.dataId if bias is not None else None, None, [desc]))
     out = backend.make_output(ci.outShape, "float32")
     fn = (backend.lib.tfjs_cuda_fused_depthwise_conv2d if depthwise
           else backend.lib.tfjs_cuda_fused_conv2d)

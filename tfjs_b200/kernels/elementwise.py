@@ -5,7 +5,7 @@ binary_impl.ts:25-69 and the per-op files (Add.ts, Relu.ts, Erf.ts, ...);
 BatchNorm.ts:23-90; Cast.ts:27-95.
 """
 from .. import _cabi
-from ..backend import TensorInfo
+from ..backend import PendingAdd, PendingConv, TensorInfo
 from ..kernel_registry import KernelConfig
 from ..util import assert_and_get_broadcast_shape, size_from_shape
 from .common import BACKEND, assert_not_complex, dev, view
@@ -113,11 +113,36 @@ def apply_activation(backend, x, activation, prelu=None, alpha=None):
                      activation)
 
 
+def deferred_add(backend, a, b):
+    """Add of two equal-shape float32 tensors as a deferred launch: folded into the
+    epilogue of a pending convolution when one operand is one, else a pending
+    add that a following Relu / Relu6 can join.  None when the operands do not
+    qualify."""
+    if not (backend.lazy_fusion and a.dtype == "float32" and b.dtype == "float32" and
+            list(a.shape) == list(b.shape) and size_from_shape(a.shape) > 0):
+        return None
+    desc = {"name": "Add", "inputShapes": {"b": list(b.shape)},
+            "outputShapes": [list(a.shape)], "attrs": {}}
+    for conv, other in ((a, b), (b, a)):
+        pend = backend.pending_of(conv.dataId)
+        if isinstance(pend, PendingConv) and pend.residual is None:
+            return backend.defer(a.shape, "float32", PendingConv(
+                pend.params, pend.x, pend.filt, pend.bias, other.dataId, pend.desc + [desc]))
+    desc["inputShapes"]["a"] = list(a.shape)
+    return backend.defer(a.shape, "float32",
+                         PendingAdd(a.dataId, b.dataId, size_from_shape(a.shape), [desc]))
+
+
 def _unary_config(name, p_from_attrs=None):
+    post_act = {"Relu": "relu", "Relu6": "relu6"}.get(name)
+
     def func(args):
         x = args["inputs"]["x"]
+        backend = args["backend"]
+        if post_act and x.dtype == "float32" and backend.pending_of(x.dataId) is not None:
+            return backend.launch_pending(x, post_act)
         p0, p1 = p_from_attrs(args["attrs"]) if p_from_attrs else (0.0, 0.0)
-        return unary_impl(args["backend"], name, x, p0, p1)
+        return unary_impl(backend, name, x, p0, p1)
     return KernelConfig(name, BACKEND, func)
 
 
@@ -126,6 +151,10 @@ def _binary_config(name):
         i = args["inputs"]
         if name == "Prelu":
             return binary_impl(args["backend"], name, i["x"], i["alpha"])
+        if name == "Add":
+            out = deferred_add(args["backend"], i["a"], i["b"])
+            if out is not None:
+                return out
         return binary_impl(args["backend"], name, i["a"], i["b"])
     return KernelConfig(name, BACKEND, func)
 

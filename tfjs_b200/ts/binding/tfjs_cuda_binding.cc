@@ -119,6 +119,15 @@ napi_value FusedConv2D(napi_env env, napi_callback_info info) {
   auto* p = static_cast<tfjs_cuda_conv2d_params*>(a.buffer(1));
   return check(env, a.ctx(0), tfjs_cuda_fused_conv2d(a.ctx(0), p, a.i32(2), a.i32(3), a.i32(4), a.i32(5), a.i32(6)));
 }
+napi_value FusedConv2DResidual(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  auto* p = static_cast<tfjs_cuda_conv2d_params*>(a.buffer(1));
+  return check(env, a.ctx(0), tfjs_cuda_fused_conv2d_residual(a.ctx(0), p, a.i32(2), a.i32(3), a.i32(4), a.i32(5), a.i32(6), a.i32(7), a.i32(8)));
+}
+napi_value AddActivation(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  return check(env, a.ctx(0), tfjs_cuda_add_activation(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.u64(4), a.i32(5)));
+}
 napi_value FusedDepthwiseConv2D(napi_env env, napi_callback_info info) {
   Args a(env, info);
   auto* p = static_cast<tfjs_cuda_conv2d_params*>(a.buffer(1));
@@ -200,6 +209,7 @@ napi_value Init(napi_env env, napi_value exports) {
       {"create", Create}, {"alloc", Alloc}, {"free", Free}, {"write", Write}, {"read", Read},
       {"sync", Sync}, {"memory", Memory}, {"timeBegin", TimeBegin}, {"timeEnd", TimeEnd},
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},
+      {"fusedConv2dResidual", FusedConv2DResidual}, {"addActivation", AddActivation},
       {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul},
       {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax},
       {"reduce", Reduce}, {"argMax", ArgMax}, {"transpose", Transpose}, {"gather", Gather},

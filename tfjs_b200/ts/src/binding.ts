@@ -21,6 +21,11 @@ export interface CudaBinding {
   setMathMode(ctx: Ctx, mode: number): void;
   fusedConv2d(ctx: Ctx, params: ArrayBuffer, x: number, filter: number, bias: number,
               prelu: number, out: number): void;
+  fusedConv2dResidual(ctx: Ctx, params: ArrayBuffer, x: number, filter: number, bias: number,
+                      prelu: number, residual: number, postActivation: number,
+                      out: number): void;
+  addActivation(ctx: Ctx, activation: number, a: number, b: number, n: number,
+                out: number): void;
   fusedDepthwiseConv2d(ctx: Ctx, params: ArrayBuffer, x: number, filter: number, bias: number,
                        prelu: number, out: number): void;
   fusedMatMul(ctx: Ctx, params: ArrayBuffer, a: number, b: number, bias: number, prelu: number,
