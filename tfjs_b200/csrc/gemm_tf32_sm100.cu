@@ -210,7 +210,7 @@ struct Cfg {
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int SMEM_BYTES =
       1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + kBarrierBytes + 8 * EPI_BUFS * 4096 +
-      (A_MODE == 3 ? kTapTableEntries * 4 : 0);
+      (A_MODE == 3 ? kTapTableEntries * 4 + 4 * 512 : 0);  // tap table + 4 row tables
 };
 
 template <int BN, int B_MN, int A_MODE, int RES>
@@ -688,49 +688,61 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   else if (A_MODE == 3 && warp >= 10) {
     // ------------------------------------------- scalar im2col gatherers --
     // For inputs whose channel count is not a multiple of 4 (the 3-channel stems).
-    // Thread r builds row r of the A tile one float at a time: k -> (tap, channel)
-    // through the tap table, taps outside the image read as zero (one validity bit
-    // per tap, computed once per tile), values rounded to TF32, stored swizzled.
-    const int r = threadIdx.x - 320;
+    // Warp gw builds rows 32 gw .. 32 gw + 31 of the A tile.  Within a K step lane l
+    // owns column l: consecutive lanes read consecutive (tap, channel) elements of one
+    // pixel's patch, which are contiguous in memory along a filter row, and write one
+    // 128-byte row of the tile without bank conflicts.  k -> (tap, channel, offset)
+    // comes from the tap table, the geometry of the warp's 32 rows from a small
+    // per-warp table rebuilt at every tile; taps outside the image read as zero and
+    // values are rounded to TF32.
+    const int gw = warp - 10;
     const ConvGeo& cv = g.conv;
-    const uint32_t row_off = (uint32_t)r * 128u;
-    const uint32_t sw = (uint32_t)(r & 7);
-    // iterator over (tile, k step); the loads of step i+1 are issued before the
-    // stores of step i so two steps are in flight per thread
+    const uint32_t row_tab = tap_table + (uint32_t)kTapTableEntries * 4u + (uint32_t)gw * 512u;
+    const uint32_t kpos = ((uint32_t)lane & 3u) * 4u;
+    const uint32_t kchunk = (uint32_t)lane >> 2;
     int tile = blockIdx.x, ks = 0;
-    unsigned long long mask = 0ull;
-    const float* base = g.x;
     auto enter_tile = [&]() {
-      mask = 0ull;
-      base = g.x;
-      if (tile >= g.total_tiles) return;
-      const int mt = (tile / g.tiles_n) % g.tiles_m;
-      const int m = mt * BM + r;
-      if (m >= g.M) return;
-      const int ow = m % cv.out_w;
-      const int t = m / cv.out_w;
-      const int oh = t % cv.out_h;
-      const int b = t / cv.out_h;
-      const int r0 = oh * cv.s_h - cv.pad_t, c0 = ow * cv.s_w - cv.pad_l;
-      int tap = 0;
-      for (int fr = 0; fr < cv.f_h; ++fr) {
-        const int ri = r0 + fr * cv.d_h;
-        for (int fc = 0; fc < cv.f_w; ++fc, ++tap) {
-          const int ci = c0 + fc * cv.d_w;
-          if (ri >= 0 && ri < cv.in_h && ci >= 0 && ci < cv.in_w) mask |= 1ull << tap;
+      long long base = 0;
+      int r0 = -(1 << 28), c0 = 0;  // rows beyond M fail every bounds test
+      if (tile < g.total_tiles) {
+        const int mt = (tile / g.tiles_n) % g.tiles_m;
+        const int m = mt * BM + gw * 32 + lane;
+        if (m < g.M) {
+          const int ow = m % cv.out_w;
+          const int t = m / cv.out_w;
+          const int oh = t % cv.out_h;
+          const int b = t / cv.out_h;
+          r0 = oh * cv.s_h - cv.pad_t;
+          c0 = ow * cv.s_w - cv.pad_l;
+          base = (((long long)b * cv.in_h + r0) * cv.in_w + c0) * cv.in_c;
         }
       }
-      base = g.x + (((long long)b * cv.in_h + r0) * cv.in_w + c0) * cv.in_c;
+      __syncwarp();  // every lane is done with the previous tile's table
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_tab + (uint32_t)lane * 16u),
+                   "r"((uint32_t)(unsigned long long)base),
+                   "r"((uint32_t)((unsigned long long)base >> 32)), "r"(r0), "r"(c0)
+                   : "memory");
+      __syncwarp();
     };
     auto load_step = [&](float* v) {
+      uint32_t e;
+      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e) : "r"(tap_table + 4u * (ks * BK + lane)));
+      const int tap = (int)(e >> 24);
+      const bool kval = tap != 255;
+      const int fr = tap / cv.f_w, fc = tap - fr * cv.f_w;
+      const int dr = fr * cv.d_h, dc = fc * cv.d_w;
+      const float* src = g.x + (e & 0xffffffu);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        uint32_t e;
-        // not volatile: the table is constant after set-up, let the loads be scheduled freely
-        asm("ld.shared.b32 %0, [%1];" : "=r"(e) : "r"(tap_table + 4u * (ks * BK + j)));
-        const uint32_t tap = e >> 24;
-        const bool ok = tap < 64u && ((mask >> tap) & 1ull);
-        v[j] = ok ? __ldg(base + (e & 0xffffffu)) : 0.0f;
+      for (int i = 0; i < 32; ++i) {
+        uint32_t lo, hi;
+        int r0, c0;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(lo), "=r"(hi), "=r"(r0), "=r"(c0)
+                     : "r"(row_tab + (uint32_t)i * 16u));
+        const long long base = (long long)(((unsigned long long)hi << 32) | lo);
+        const bool ok = kval && (unsigned)(r0 + dr) < (unsigned)cv.in_h &&
+                        (unsigned)(c0 + dc) < (unsigned)cv.in_w;
+        v[i] = ok ? __ldg(src + base) : 0.0f;
       }
     };
     auto advance = [&]() {
@@ -749,22 +761,20 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
 #pragma unroll
       for (int j = 0; j < 32; ++j) cur[j] = nxt[j];
       advance();
+      // the loads of step i+1 are issued before the stores of step i
       if (tile < g.total_tiles) load_step(nxt);
       if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
         atomicExch(g.flag, 6);
         break;
       }
-      const uint32_t dst = a_base + stage * A_STAGE_BYTES + row_off;
+      const uint32_t dst = a_base + stage * A_STAGE_BYTES + (uint32_t)gw * 4096u + kpos;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint32_t w0, w1, w2, w3;
-        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w0) : "f"(cur[4 * j]));
-        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w1) : "f"(cur[4 * j + 1]));
-        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w2) : "f"(cur[4 * j + 2]));
-        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w3) : "f"(cur[4 * j + 3]));
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
-                         dst + (((uint32_t)j ^ sw) << 4)),
-                     "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+      for (int i = 0; i < 32; ++i) {
+        uint32_t w;
+        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w) : "f"(cur[i]));
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(
+                         dst + (uint32_t)i * 128u + ((kchunk ^ (uint32_t)(i & 7)) << 4)),
+                     "r"(w)
                      : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
