@@ -42,12 +42,21 @@ struct Tf32Operands {
   long long lda = 0;         // elements between consecutive rows of A
   int a_gather = 0;          // 1: A comes from NHWC x by the conv geometry, 32-channel chunks;
                              // 2: same, one float at a time (channels not a multiple of 4)
+                             // 3: same, image rows staged in shared memory
   const float* b = nullptr;
   long long ldb = 0;         // elements between consecutive rows of the B storage
   int b_layout = B_K_MAJOR;
   int k_steps = 0;           // number of 32-wide K steps
   int cin_pad = 0;           // gathered conv: per-tap channel count rounded up to 32
 };
+
+// Shared-memory plan of the staged-row gather (a_gather 3); tf32_patch_plan returns
+// false when the shape cannot use it.
+struct PatchPlan {
+  int bytes, pitch, ml, rows;  // per buffer; floats between rows; left margin; rows held
+  int bufs;                    // buffers that fit (2 to 4)
+};
+bool tf32_patch_plan(const ConvGeo& cv, int M, int N, int sm_count, PatchPlan* plan);
 
 int launch_gemm_simt(tfjs_cuda_ctx* ctx, const GemmProblem& pr);
 int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operands& op);

@@ -51,6 +51,12 @@ struct Tf32Args {
   int c_tma;  // 1: the epilogue stores through the C tensor map (N % 4 == 0)
   const float* residual;  // optional: out = post_act(act(acc + bias) + residual)
   int post_act;
+  int patch_cap;          // staged-row gather: bytes per patch buffer, 0 = off
+  int patch_pitch;        // floats between patch rows (left margin + image row + right margin)
+  int patch_ml;           // floats of left margin
+  int patch_rows;         // image rows a buffer holds; row `patch_rows` stays zero
+  int patch_bufs;         // patch buffers (2 to 4); tiles are staged patch_bufs - 1 ahead
+  uint32_t ow_mul, ow_shr, oh_mul, oh_shr;  // division by out_w / out_h as multiply-shift
   // gathered convolution
   const float* x;
   ConvGeo conv;
@@ -191,9 +197,23 @@ __device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g,
   }
 }
 
+// n / d for 0 <= n < 2^31 as umulhi(n, mul) >> shr (mul = ceil(2^(32+shr) / d)).
+__device__ __forceinline__ int fast_div(int n, uint32_t mul, uint32_t shr) {
+  return mul ? (int)(__umulhi((uint32_t)n, mul) >> shr) : n;
+}
+inline void fast_div_setup(int d, uint32_t* mul, uint32_t* shr) {
+  if (d <= 1) { *mul = 0; *shr = 0; return; }
+  int lg = 0;
+  while ((1ll << lg) < d) ++lg;
+  const int p = 31 + lg;
+  *mul = (uint32_t)(((1ull << p) + (uint64_t)d - 1) / (uint64_t)d);
+  *shr = (uint32_t)(p - 32);
+}
+
 constexpr int kTapTableEntries = 512;  // scalar-gather K limit (after padding to 32)
 
-constexpr int kBarrierBytes = 384;  // pipeline barriers, TMEM slot, residual barriers
+constexpr int kMaxSmemBytes = 232448;  // 227 KB per CTA
+constexpr int kBarrierBytes = 512;  // pipeline barriers, TMEM slot, residual barriers
 
 // RES: the epilogue adds a residual tile that the TMA unit prefetches into the
 // staging tile of the next chunk (two staging tiles per warp, and at BN = 256 one
@@ -201,13 +221,20 @@ constexpr int kBarrierBytes = 384;  // pipeline barriers, TMEM slot, residual ba
 template <int BN, int A_MODE = 0, int RES = 0>
 struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
-  // the scalar-gather mode gives one stage up for its tap table
-  static constexpr int STAGES = (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 6 : 8))) -
-                                (A_MODE == 3 ? 1 : 0) - (RES && BN >= 256 ? 1 : 0);
+  // the scalar-gather mode runs three stages: its shared memory goes to the tap and
+  // row tables and to the two staged input patches
+  static constexpr int STAGES =
+      A_MODE == 3 ? (BN == 32 ? 5 : (BN == 64 ? 4 : 3))
+                  : (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 6 : 8))) -
+                        (RES && BN >= 256 ? 1 : 0);
   // staging tiles per epilogue warp: two below BN = 256 (bandwidth-bound shapes), so
   // a warp fills one while the TMA unit still drains the other
-  static constexpr int EPI_BUFS = (BN >= 256 && !RES) ? 1 : 2;
-  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int EPI_BUFS = ((BN >= 256 && !RES) || A_MODE == 3) ? 1 : 2;
+  // TMEM accumulator stages.  A tile's accumulator is handed back and forth through
+  // two barriers whose wake-ups cost more than a short tile's MMAs, so narrow tiles
+  // (few K steps in practice) keep more tiles in flight: 256 columns at BN <= 128.
+  static constexpr int ACC_STAGES = BN >= 256 ? 2 : 256 / BN;
+  static constexpr int TMEM_COLS = ACC_STAGES * BN;
   static constexpr int SMEM_BYTES =
       1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + kBarrierBytes + 8 * EPI_BUFS * 4096 +
       (A_MODE == 3 ? kTapTableEntries * 4 + 4 * 512 : 0);  // tap table + 4 row tables
@@ -227,32 +254,36 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t b_base = smem_base + STAGES * A_STAGE_BYTES;
   const uint32_t epi_base = b_base + STAGES * C::B_STAGE_BYTES;  // 4 KB staging tiles
   const uint32_t bar_base = epi_base + 8u * C::EPI_BUFS * 4096u;
-  // barrier layout: full[STAGES], empty[STAGES], tfull[2], tempty[2], tmem slot
+  // barrier layout: full[STAGES], empty[STAGES], tfull[ACC], tempty[ACC], tmem slot
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  constexpr int ACC = C::ACC_STAGES;
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + ACC + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 2 * ACC);
   // residual prefetch barriers: one per epilogue warp and staging tile
-  auto res_bar = [&](int w, uint32_t b) { return bar_base + 256u + 8u * (2u * w + b); };
+  auto res_bar = [&](int w, uint32_t b) { return bar_base + 320u + 8u * (2u * w + b); };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), (A_MODE == 1 || A_MODE == 3) ? 1 + 128 : 1);
+      mbar_init(full_bar(s), (A_MODE == 1 || A_MODE == 3) ? 1 + 4 : 1);  // producer + 4 gather warps
       mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < ACC; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), BN == 32 ? 128 : 256);
+      mbar_init(tempty_bar(a), BN == 32 ? 4 : 8);  // one arrival per epilogue warp
     }
     if (RES)
       for (int w = 0; w < 8; ++w) {
         mbar_init(res_bar(w, 0), 1);
         mbar_init(res_bar(w, 1), 1);
       }
+    if (A_MODE == 3) {  // "patch landed" barriers (this mode has no residual epilogue)
+      for (int b = 0; b < 4; ++b) mbar_init(res_bar(b >> 1, b & 1), 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -265,14 +296,24 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
   const uint32_t tap_table = bar_base + (uint32_t)kBarrierBytes;  // A_MODE 3 only
   if (A_MODE == 3 && warp >= 10) {
-    // entry k: filter tap index in the top byte, element offset of (tap, channel)
-    // from the tile pixel's top-left input element in the low 24 bits
+    // entry k: filter row and column of the tap in the top byte (4 bits each, 0xff =
+    // padding beyond K), element offset of (tap, channel) from the tile pixel's top-left
+    // input element in the low 24 bits
     for (int k = threadIdx.x - 320; k < g.k_steps * BK; k += 128) {
-      uint32_t e = 0xff000000u;  // tap 255: padding beyond K, always zero
-      if (k < g.conv.f_h * g.conv.f_w * g.conv.in_c) {
+      uint32_t e = 0xff000000u;  // padding beyond K, always zero
+      if (g.patch_cap > 0) {
+        // staged-row mode: filter row in the top byte (31 = padding), offset of the
+        // element from the row's window start inside the patch in the low 24 bits
+        const int fwc = g.conv.f_w * g.conv.in_c;
+        e = 31u << 24;
+        if (k < g.conv.f_h * fwc) {
+          const int fr = k / fwc;
+          e = ((uint32_t)fr << 24) | (uint32_t)(fr * g.conv.d_h * g.patch_pitch + (k - fr * fwc));
+        }
+      } else if (k < g.conv.f_h * g.conv.f_w * g.conv.in_c) {
         const int tap = k / g.conv.in_c, c = k - tap * g.conv.in_c;
         const int fr = tap / g.conv.f_w, fc = tap - fr * g.conv.f_w;
-        e = ((uint32_t)tap << 24) |
+        e = ((uint32_t)fr << 28) | ((uint32_t)fc << 24) |
             (uint32_t)((fr * g.conv.d_h * g.conv.in_w + fc * g.conv.d_w) * g.conv.in_c + c);
       }
       asm volatile("st.shared.b32 [%0], %1;" ::"r"(tap_table + 4u * k), "r"(e) : "memory");
@@ -352,8 +393,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       int it = 0;
       bool alive = true;
       for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x, ++it) {
-        const int acc = it & 1;
-        const uint32_t aphase = (it >> 1) & 1;
+        const int acc = it % ACC;
+        const uint32_t aphase = (it / ACC) & 1;
         if (!mbar_wait(tempty_bar(acc), aphase ^ 1)) {
           atomicExch(g.flag, 2);
           break;
@@ -431,8 +472,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int rest = tile / g.tiles_n;
       const int mt = rest % g.tiles_m;
       const int bz = rest / g.tiles_m;
-      const int acc = it & 1;
-      const uint32_t aphase = (it >> 1) & 1;
+      const int acc = it % ACC;
+      const uint32_t aphase = (it / ACC) & 1;
       if (BN == 32 && (it & 1) != half) continue;  // the other warp of the pair takes it
       if (!mbar_wait(tfull_bar(acc), aphase)) {
         if (lane == 0) atomicExch(g.flag, 4);
@@ -457,7 +498,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (c0 + 64 >= BN || n0 + 64 >= g.N) {
           // last read of this accumulator by this warp: hand it back early
           tc_fence_before();
-          mbar_arrive(tempty_bar(acc));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(acc));
           released = true;
         }
         chunk_math_dispatch(v, g, n0);
@@ -599,7 +641,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       if (!released) {
         tc_fence_before();
-        mbar_arrive(tempty_bar(acc));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
       }
     }
     if (g.c_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -623,10 +666,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int m = mt * BM + r;
       row_ok = tile < g.total_tiles && m < g.M;
       if (row_ok) {
-        const int ow = m % cv.out_w;
-        const int t = m / cv.out_w;
-        const int oh = t % cv.out_h;
-        b = t / cv.out_h;
+        const int t = fast_div(m, g.ow_mul, g.ow_shr);
+        const int ow = m - t * cv.out_w;
+        b = fast_div(t, g.oh_mul, g.oh_shr);
+        const int oh = t - b * cv.out_h;
         r_base = oh * cv.s_h - cv.pad_t;
         c_base = ow * cv.s_w - cv.pad_l;
       }
@@ -680,7 +723,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
       // make the generic-proxy stores visible to the tensor core (async proxy)
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(full_bar(stage));
+      __syncwarp();  // every lane fenced its stores
+      if (lane == 0) mbar_arrive(full_bar(stage));
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
   }
@@ -708,10 +752,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         const int mt = (tile / g.tiles_n) % g.tiles_m;
         const int m = mt * BM + gw * 32 + lane;
         if (m < g.M) {
-          const int ow = m % cv.out_w;
-          const int t = m / cv.out_w;
-          const int oh = t % cv.out_h;
-          const int b = t / cv.out_h;
+          const int t = fast_div(m, g.ow_mul, g.ow_shr);
+          const int ow = m - t * cv.out_w;
+          const int b = fast_div(t, g.oh_mul, g.oh_shr);
+          const int oh = t - b * cv.out_h;
           r0 = oh * cv.s_h - cv.pad_t;
           c0 = ow * cv.s_w - cv.pad_l;
           base = (((long long)b * cv.in_h + r0) * cv.in_w + c0) * cv.in_c;
@@ -724,13 +768,181 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                    : "memory");
       __syncwarp();
     };
+    if (g.patch_cap > 0) {
+      // Staged rows.  The input rows a tile touches are whole image rows; bulk copies
+      // bring them into a shared-memory patch (two buffers: the rows of the next tile
+      // travel while this tile is expanded) whose rows carry zeroed margins for the
+      // horizontal padding, plus one all-zero row that stands in for rows above or
+      // below the image.  K is the filter in storage order (row, column, channel), so a
+      // thread (one tile row) copies runs of filter_w * in_c contiguous floats: one
+      // scalar load per element, one 16-byte store per four, no per-element bounds
+      // test.
+      const uint32_t patch_base = tap_table + (uint32_t)kTapTableEntries * 4u + 4u * 512u;
+      const int rowlen = cv.in_w * cv.in_c;  // floats per image row
+      const int pitch = g.patch_pitch;
+      const int fwc = cv.f_w * cv.in_c;
+      const int nb = g.patch_bufs;
+      const int total_rows = cv.batch * cv.in_h;
+      const int zero_off = g.patch_rows * pitch;
+      {
+        const uint32_t z = 0u;
+        for (uint32_t o = (uint32_t)(threadIdx.x - 320) * 16u;
+             o < (uint32_t)nb * (uint32_t)g.patch_cap;
+             o += 128u * 16u)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(patch_base + o), "r"(z)
+                       : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      // first global image row (b * in_h + r) and row count of a tile's patch
+      auto patch_rows = [&](int t, int* r_lo) -> int {
+        const int mt = (t / g.tiles_n) % g.tiles_m;
+        const int m0 = mt * BM;
+        const int m1 = (m0 + BM - 1 < g.M ? m0 + BM - 1 : g.M - 1);
+        const int t0 = fast_div(m0, g.ow_mul, g.ow_shr);  // (b, oh) flattened
+        const int t1 = fast_div(m1, g.ow_mul, g.ow_shr);
+        const int b0 = fast_div(t0, g.oh_mul, g.oh_shr), b1 = fast_div(t1, g.oh_mul, g.oh_shr);
+        const int lo = b0 * cv.in_h + (t0 - b0 * cv.out_h) * cv.s_h - cv.pad_t;
+        const int hi = b1 * cv.in_h + (t1 - b1 * cv.out_h) * cv.s_h - cv.pad_t +
+                       (cv.f_h - 1) * cv.d_h;
+        const int a = lo < 0 ? 0 : lo;
+        const int b = hi > total_rows - 1 ? total_rows - 1 : hi;
+        *r_lo = a;
+        int n = b - a + 1;
+        if (n < 0) n = 0;
+        if (n > g.patch_rows) {  // the host's sizing guarantees this never holds
+          atomicExch(g.flag, 7);
+          n = g.patch_rows;
+        }
+        return n;
+      };
+      auto issue_patch = [&](int t, uint32_t buf) {  // the first gather warp, all lanes
+        const uint32_t bar = res_bar(buf >> 1, buf & 1u);
+        int r_lo;
+        const int n = patch_rows(t, &r_lo);
+        if (lane == 0) {
+          if (n <= 0) mbar_arrive(bar);
+          else mbar_expect_tx(bar, (uint32_t)n * (uint32_t)rowlen * 4u);
+        }
+        __syncwarp();
+        // one bulk copy per image row, spread over the lanes
+        const uint32_t dst0 = patch_base + buf * (uint32_t)g.patch_cap + (uint32_t)g.patch_ml * 4u;
+        for (int r = lane; r < n; r += 32)
+          asm volatile(
+              "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+              ::"r"(dst0 + (uint32_t)(r * pitch) * 4u),
+              "l"(g.x + (long long)(r_lo + r) * rowlen), "r"((uint32_t)rowlen * 4u), "r"(bar)
+              : "memory");
+      };
+      const bool leader = gw == 0;
+      if (leader)
+        for (int j = 0; j < nb - 1; ++j)
+          if (tile + j * (int)gridDim.x < g.total_tiles) issue_patch(tile + j * gridDim.x, j);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      const uint32_t smem0 = smem_u32(smem_raw);
+      const uint32_t my_row = (uint32_t)(gw * 32 + lane) * 128u;
+      const uint32_t sw = (uint32_t)lane & 7u;
+      for (int t = 0; tile < g.total_tiles && alive; tile += gridDim.x, ++t) {
+        const uint32_t buf = (uint32_t)(t % nb);
+        // every gather thread is done with the buffer of tile t - 1: refill it with the
+        // patch of tile t + nb - 1
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (leader && tile + (nb - 1) * (int)gridDim.x < g.total_tiles)
+          issue_patch(tile + (nb - 1) * gridDim.x, (uint32_t)((t + nb - 1) % nb));
+        // this thread's tile row: where its window starts inside the patch
+        int pbase = 0, r0 = -(1 << 28);
+        {
+          int r_lo;
+          patch_rows(tile, &r_lo);
+          const int mt = (tile / g.tiles_n) % g.tiles_m;
+          const int m = mt * BM + gw * 32 + lane;
+          if (m < g.M) {
+            const int tt = fast_div(m, g.ow_mul, g.ow_shr);
+            const int ow = m - tt * cv.out_w;
+            const int b = fast_div(tt, g.oh_mul, g.oh_shr);
+            const int oh = tt - b * cv.out_h;
+            r0 = oh * cv.s_h - cv.pad_t;
+            pbase = (b * cv.in_h + r0 - r_lo) * pitch + g.patch_ml +
+                    (ow * cv.s_w - cv.pad_l) * cv.in_c;
+          }
+        }
+        if (!mbar_wait(res_bar(buf >> 1, buf & 1u), (uint32_t)(t / nb) & 1u)) {
+          atomicExch(g.flag, 8);
+          alive = false;
+          break;
+        }
+        // plain shared-memory loads (not asm) so the compiler may batch them
+        const float* pf = reinterpret_cast<const float*>(
+            smem_raw + (patch_base + buf * (uint32_t)g.patch_cap - smem0));
+        // filter rows of this thread's window that lie inside the image
+        uint32_t vmask = 0;
+        for (int fr = 0; fr < cv.f_h; ++fr)
+          if ((unsigned)(r0 + fr * cv.d_h) < (unsigned)cv.in_h) vmask |= 1u << fr;
+        const bool interior = __all_sync(0xffffffffu, vmask == (1u << cv.f_h) - 1u);
+        const uint4* tp = reinterpret_cast<const uint4*>(smem_raw + (tap_table - smem0));
+        const int k_real = cv.f_h * fwc;
+        for (ks = 0; ks < k_steps; ++ks) {
+          float v[32];
+          if (interior && (ks + 1) * BK <= k_real) {
+            // every element of this step exists for every row of the warp
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              const uint4 t4 = tp[ks * 8 + q4];
+              v[4 * q4] = pf[pbase + (int)(t4.x & 0xffffffu)];
+              v[4 * q4 + 1] = pf[pbase + (int)(t4.y & 0xffffffu)];
+              v[4 * q4 + 2] = pf[pbase + (int)(t4.z & 0xffffffu)];
+              v[4 * q4 + 3] = pf[pbase + (int)(t4.w & 0xffffffu)];
+            }
+          } else {
+            // rows above / below the image and the padding beyond K read the zero row
+            auto pick = [&](uint32_t e) -> float {
+              const bool ok = (vmask >> (e >> 24)) & 1u;
+              return pf[ok ? pbase + (int)(e & 0xffffffu) : zero_off];
+            };
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              const uint4 t4 = tp[ks * 8 + q4];
+              v[4 * q4] = pick(t4.x);
+              v[4 * q4 + 1] = pick(t4.y);
+              v[4 * q4 + 2] = pick(t4.z);
+              v[4 * q4 + 3] = pick(t4.w);
+            }
+          }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
+            atomicExch(g.flag, 6);
+            alive = false;
+            break;
+          }
+          const uint32_t dst = a_base + stage * A_STAGE_BYTES + my_row;
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8) {
+            uint32_t w0, w1, w2, w3;
+            asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w0) : "f"(v[4 * c8]));
+            asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w1) : "f"(v[4 * c8 + 1]));
+            asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w2) : "f"(v[4 * c8 + 2]));
+            asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(w3) : "f"(v[4 * c8 + 3]));
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                             dst + (((uint32_t)c8 ^ sw) << 4)),
+                         "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                         : "memory");
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();  // every lane fenced its stores
+          if (lane == 0) mbar_arrive(full_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      // patches may still be in flight after an early exit: let them land
+      if (!alive && leader && lane == 0)
+        for (int b = 0; b < nb; ++b) mbar_wait(res_bar(b >> 1, b & 1), 0);
+    } else {
     auto load_step = [&](float* v) {
       uint32_t e;
       asm volatile("ld.shared.b32 %0, [%1];" : "=r"(e) : "r"(tap_table + 4u * (ks * BK + lane)));
-      const int tap = (int)(e >> 24);
-      const bool kval = tap != 255;
-      const int fr = tap / cv.f_w, fc = tap - fr * cv.f_w;
-      const int dr = fr * cv.d_h, dc = fc * cv.d_w;
+      const bool kval = (e >> 24) != 0xffu;
+      const int dr = (int)(e >> 28) * cv.d_h, dc = (int)((e >> 24) & 15u) * cv.d_w;
       const float* src = g.x + (e & 0xffffffu);
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
@@ -778,9 +990,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                      : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(full_bar(stage));
+      __syncwarp();  // every lane fenced its stores
+      if (lane == 0) mbar_arrive(full_bar(stage));
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
+    }  // register-held gather
   }
 
   tc_fence_before();
@@ -875,15 +1089,20 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
   using C = Cfg<BN, A_MODE, RES>;
   auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE, RES>;
   static bool configured[64] = {false};  // per device ordinal
+  // the scalar-gather mode adds its two input patches to the fixed layout
+  int smem = C::SMEM_BYTES;
+  if (A_MODE == 3) {
+    smem += g.patch_bufs * g.patch_cap;
+  }
   if (ctx->device >= 64 || !configured[ctx->device]) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       C::SMEM_BYTES));
+                                       A_MODE == 3 ? kMaxSmemBytes : C::SMEM_BYTES));
     if (ctx->device < 64) configured[ctx->device] = true;
   }
   g.tiles_n = (g.N + BN - 1) / BN;
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
-  kern<<<grid, (A_MODE == 1 || A_MODE == 3) ? 448 : 320, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, tm_c, tm_r, g);
+  kern<<<grid, (A_MODE == 1 || A_MODE == 3) ? 448 : 320, smem, ctx->stream>>>(tm_a, tm_b, tm_c, tm_r, g);
   LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
   return TFJS_CUDA_OK;
 }
@@ -908,7 +1127,43 @@ int pick_bn(int M, int N, int batch, int sm_count) {
   return bn;
 }
 
+constexpr int smem_base_mode3(int bn) {
+  return bn == 32 ? Cfg<32, 3>::SMEM_BYTES
+                  : (bn == 64 ? Cfg<64, 3>::SMEM_BYTES
+                              : (bn == 128 ? Cfg<128, 3>::SMEM_BYTES : Cfg<256, 3>::SMEM_BYTES));
+}
+
 }  // namespace
+
+bool tf32_patch_plan(const ConvGeo& cv, int M, int N, int sm_count, PatchPlan* plan) {
+  static int off = -1;
+  if (off < 0) off = getenv("TFJS_CUDA_NO_PATCH_GATHER") ? 1 : 0;  // debugging knob
+  const long long rowlen = (long long)cv.in_w * cv.in_c;
+  if (off || cv.d_w != 1 || cv.f_h > 15 || (rowlen & 3) || rowlen * 4 > (1 << 20)) return false;
+  // margins: the window of the first / last output column reaches this far outside
+  const int ml = (cv.pad_l * cv.in_c + 3) & ~3;
+  long long over = (long long)(cv.out_w - 1) * cv.s_w - cv.pad_l + cv.f_w - cv.in_w;
+  if (over < 0) over = 0;
+  const long long mr = (over * cv.in_c + 3) & ~3ll;
+  const long long pitch = ml + rowlen + mr;
+  // upper bound of the image rows one 128-pixel tile touches: q output rows, at most
+  // `step` global rows apart (the stride, or the jump to the next image)
+  const long long q = (BM - 1) / cv.out_w + 2;
+  const long long jump = (long long)cv.in_h - (long long)(cv.out_h - 1) * cv.s_h;
+  const long long step = jump > cv.s_h ? jump : cv.s_h;
+  long long rows = (q - 1) * step + (long long)(cv.f_h - 1) * cv.d_h + 1;
+  if (rows > (long long)cv.batch * cv.in_h) rows = (long long)cv.batch * cv.in_h;
+  const long long bytes = (((rows + 1) * pitch * 4) + 127) & ~127ll;
+  const int bn = pick_bn(M, N, 1, sm_count);
+  long long bufs = (kMaxSmemBytes - smem_base_mode3(bn)) / bytes;
+  if (bufs < 2) return false;
+  plan->bufs = bufs > 4 ? 4 : (int)bufs;
+  plan->bytes = (int)bytes;
+  plan->pitch = (int)pitch;
+  plan->ml = ml;
+  plan->rows = (int)rows;
+  return true;
+}
 
 int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operands& op) {
   Tf32Args g;
@@ -937,6 +1192,19 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   g.c_tma = 0;
   g.residual = pr.residual;
   g.post_act = pr.post_act;
+  g.patch_cap = g.patch_pitch = g.patch_ml = g.patch_rows = g.patch_bufs = 0;
+  fast_div_setup(op.a_gather ? pr.conv.out_w : 1, &g.ow_mul, &g.ow_shr);
+  fast_div_setup(op.a_gather ? pr.conv.out_h : 1, &g.oh_mul, &g.oh_shr);
+  if (op.a_gather == 3) {
+    PatchPlan plan;
+    if (!tf32_patch_plan(pr.conv, pr.M, pr.N, ctx->sm_count, &plan) || ((uintptr_t)op.a & 15))
+      return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "staged-row gather planned for a shape it cannot take");
+    g.patch_cap = plan.bytes;
+    g.patch_pitch = plan.pitch;
+    g.patch_ml = plan.ml;
+    g.patch_rows = plan.rows;
+    g.patch_bufs = plan.bufs;
+  }
   bool res_tma = false;
   if ((pr.N & 3) == 0 && ((uintptr_t)pr.c & 15) == 0 && ((uintptr_t)pr.residual & 15) == 0) {
     EncodeTiledFn enc = get_encode();
@@ -966,7 +1234,7 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     if (no_im2col < 0) no_im2col = getenv("TFJS_CUDA_NO_IM2COL_TMA") ? 1 : 0;  // debugging knob
     memset(&tm_a, 0, sizeof tm_a);
     im2col = !no_im2col && make_im2col_map(&tm_a, op.a, pr.conv);
-  } else if (op.a_gather == 2) {
+  } else if (op.a_gather >= 2) {
     memset(&tm_a, 0, sizeof tm_a);
   } else {
     if ((rc = make_map(ctx, &tm_a, op.a, (uint64_t)pr.K, (uint64_t)pr.M,
@@ -980,7 +1248,7 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     if ((rc = make_map(ctx, &tm_b, op.b, kk, (uint64_t)pr.N, (uint64_t)pr.batch_b,
                        (uint64_t)op.ldb, (uint64_t)pr.N * op.ldb, (uint32_t)bn)))
       return rc;
-    if (op.a_gather == 2) {
+    if (op.a_gather >= 2) {
       tm_a = tm_b;  // unused by the gather kernel
       return launch_bn<0, 3>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }

@@ -285,7 +285,17 @@ static int conv2d_impl(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p, int
       op.a = pr.a; op.a_gather = 1; op.cin_pad = cin_pad;
       op.b = packed; op.ldb = (long long)taps * cin_pad; op.b_layout = B_K_MAJOR;
       op.k_steps = taps * (cin_pad / 32);
-    } else if (taps <= 64 && ((int)K64 + 31) / 32 * 32 <= 512 &&
+    } else if (PatchPlan plan; ((int)K64 + 31) / 32 * 32 <= 512 &&
+                               tf32_patch_plan(cv, pr.M, pr.N, ctx->sm_count, &plan)) {
+      // few input channels (image stems), image rows staged in shared memory; K is
+      // padded to a multiple of 32 in the packed filter
+      const int k_pad = ((int)K64 + 31) / 32 * 32;
+      if ((rc = get_packed(ctx, filter_id, w, 1, p->out_c, 1, (int)K64, k_pad, 0, &packed)))
+        return rc;
+      op.a = pr.a; op.a_gather = 3;
+      op.b = packed; op.ldb = k_pad; op.b_layout = B_K_MAJOR;
+      op.k_steps = k_pad / 32;
+    } else if (p->filter_h <= 15 && p->filter_w <= 15 && ((int)K64 + 31) / 32 * 32 <= 512 &&
                (uint64_t)((p->filter_h - 1) * p->dilation_h * p->in_w +
                           (p->filter_w - 1) * p->dilation_w + 1) * p->in_c < (1u << 24)) {
       // few input channels (image stems): the gather warps assemble the im2col rows
