@@ -298,20 +298,29 @@ def run_cuda(args, rank, world, local_rank):
             tfjs_b200.TensorInfo(be.write_from(pinned[k], pinned[k].shape, dtypes[k]),
                                  pinned[k].shape, dtypes[k])) for k in pinned}
 
+    out_hosts = [out_host, be.pinned_empty(out_shape, "float32")]
+
     def run_e2e(steps):
-        """Each step uploads its batch from pinned host memory, executes, and downloads
-        the result.  The upload of batch i+1 is issued (copy stream) while batch i is
-        still executing, which is what an application loop naturally does because
-        launches return immediately."""
+        """Each step uploads its batch from pinned host memory (copy stream), executes,
+        and downloads the result with tensor.data() into pinned memory.  The loop is the
+        one an application writes with promises: the upload and the launches of batch
+        i+1 are issued before the result of batch i is awaited, so the GPU never waits
+        for the host to enqueue a step.  Every result is awaited inside the timed
+        region."""
         nxt = upload_inputs()
+        prev = None
         for i in range(steps):
             ins = nxt
             y = gm.execute(ins, [out_name])[0]
-            nxt = upload_inputs() if i + 1 < steps else None
-            be.read_into(y.dataId, out_host)     # D2H + stream sync
-            y.dispose()
             for t in ins.values():
-                t.dispose()
+                t.dispose()                      # stream-ordered: after the step's kernels
+            pending = y.data(into=out_hosts[i & 1])      # D2H queued behind the step
+            y.dispose()
+            nxt = upload_inputs() if i + 1 < steps else None
+            if prev is not None:
+                prev.wait()
+            prev = pending
+        prev.wait()
 
     for _ in range(max(args.warmup, 3)):
         step_resident()

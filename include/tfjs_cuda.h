@@ -96,6 +96,14 @@ int tfjs_cuda_read(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes);
 /* Queue a D2H copy without waiting (pair with tfjs_cuda_sync). */
 int tfjs_cuda_read_async(tfjs_cuda_ctx* ctx, int32_t id, void* host,
                          uint64_t nbytes);
+/* backend.read(dataId): Promise (tfjs-core/src/backends/backend.ts:104): read_begin queues
+ * the D2H copy behind the kernels already launched and returns a ticket at once;
+ * read_wait blocks until that copy has landed (and reports a pending device timeout).
+ * The caller keeps `host` (ideally pinned) alive and untouched in between; a ticket is
+ * collected exactly once. */
+int tfjs_cuda_read_begin(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes,
+                         int32_t* out_ticket);
+int tfjs_cuda_read_wait(tfjs_cuda_ctx* ctx, int32_t ticket);
 int tfjs_cuda_sync(tfjs_cuda_ctx* ctx);
 int tfjs_cuda_size_of(tfjs_cuda_ctx* ctx, int32_t id, uint64_t* out_nbytes);
 /* Raw device address of a tensor, for interop (profilers, other libraries). */

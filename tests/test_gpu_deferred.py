@@ -292,3 +292,30 @@ def test_residual_entry_point_rejects_bad_arguments(cuda_engine):
         t.dispose()
     backend.disposeData(out.dataId)
     backend.disposeData(small.dataId)
+
+
+def test_async_read_overlaps_later_launches(cuda_engine):
+    """tensor.data() returns at once; kernels launched afterwards do not disturb the
+    bytes it delivers, tickets are collected once, and a small host-resident tensor
+    resolves without touching the device."""
+    from tfjs_b200 import ops as tf
+    backend = cuda_engine.backend
+    r = np.random.default_rng(61)
+    a = r.standard_normal(1 << 20).astype(np.float32)
+    at = tf.tensor(a)
+    y = tf.mul(at, at)
+    host = backend.pinned_empty([1 << 20], "float32")
+    pending = y.data(into=host)
+    z = tf.add(y, at)                 # launched while the copy is outstanding
+    z2 = tf.relu(z)
+    got = pending.wait()
+    assert got is host or np.shares_memory(got, host)
+    assert np.array_equal(got, a * a)
+    assert np.array_equal(pending.wait(), a * a)      # a second wait is a no-op
+    assert np.array_equal(z2.dataSync(), np.maximum(a * a + a, 0))
+    small = tf.tensor(np.arange(4, dtype=np.float32))
+    assert np.array_equal(small.data().wait(), np.arange(4, dtype=np.float32))
+    rc = backend.lib.tfjs_cuda_read_wait(backend.ctx, 12345)
+    assert rc == 1
+    for t in (at, y, z, z2, small):
+        t.dispose()

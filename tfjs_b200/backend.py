@@ -133,6 +133,20 @@ class PendingAdd(object):
             backend.device_id(self.b), self.n, out_dev))
 
 
+class PendingRead(object):
+    """Result of CudaBackend.read: the Promise of backend.read in tfjs."""
+    __slots__ = ("backend", "ticket", "values", "dtype")
+
+    def __init__(self, backend, ticket, values, dtype):
+        self.backend, self.ticket, self.values, self.dtype = backend, ticket, values, dtype
+
+    def wait(self):
+        if self.ticket:
+            ticket, self.ticket = self.ticket, 0
+            self.backend.check(self.backend.lib.tfjs_cuda_read_wait(self.backend.ctx, ticket))
+        return self.values.astype(np.bool_) if self.dtype == "bool" else self.values
+
+
 def size_from_shape(shape):
     n = 1
     for s in shape:
@@ -311,8 +325,27 @@ class CudaBackend(object):
                                                out.ctypes.data_as(c_void_p), rec.nbytes))
         return out.astype(np.bool_) if rec.dtype == "bool" else out
 
-    def read(self, dataId):
-        return self.readSync(dataId)
+    def read(self, dataId, into=None):
+        """backend.read(dataId): Promise (backend.ts:104).  Queues the device-to-host
+        copy behind the kernels launched so far and returns a PendingRead at once;
+        `.wait()` blocks until the bytes are there.  `into` is an optional (ideally
+        pinned) numpy array that receives them."""
+        rec = self.data[dataId]
+        if rec.pending is not None:
+            self._resolve(rec)
+        npdt = NP_DTYPES[rec.dtype]
+        if rec.host is not None:
+            if into is None:
+                into = rec.host.copy()
+            else:
+                into.reshape(-1)[:] = rec.host
+            return PendingRead(self, 0, into, rec.dtype)
+        if into is None:
+            into = np.empty(rec.nbytes // np.dtype(npdt).itemsize, npdt)
+        ticket = c_int32()
+        self.check(self.lib.tfjs_cuda_read_begin(self.ctx, rec.dev, into.ctypes.data_as(c_void_p),
+                                                 rec.nbytes, byref(ticket)))
+        return PendingRead(self, ticket.value, into, rec.dtype)
 
     def read_into(self, dataId, host_array):
         """readSync into caller-provided (ideally pinned) memory."""

@@ -18,6 +18,16 @@ struct Buffer {
   bool from_host = false;  // last filled by write()/dequantize(): weight-like
   uint32_t version = 0;    // bumped whenever the contents are (re)written
   cudaEvent_t ready = nullptr;  // set while an upload on the copy stream is pending
+  bool uploaded = false;        // block came from tfjs_cuda_upload: recycled for uploads
+};
+
+// A block released by an uploaded tensor, kept for the next upload of that size: the
+// copy stream waits for `released` (the compute stream's position when the tensor was
+// freed) instead of the compute stream's tail.
+struct UploadBlock {
+  void* ptr;
+  uint64_t bytes;
+  cudaEvent_t released;
 };
 
 // A filter repacked for the tensor-core kernels: [rows = out channels][k_pad]
@@ -43,6 +53,7 @@ struct tfjs_cuda_ctx {
   // compute stream that last touched it.
   std::unordered_map<uint64_t, std::vector<void*>> block_cache;
   uint64_t cached_bytes = 0;
+  std::vector<UploadBlock> upload_cache;  // oldest first
   cudaMemPool_t pool = nullptr;
   std::vector<Buffer> bufs;  // index = id; slot 0 unused
   std::vector<int32_t> free_ids;
@@ -57,6 +68,8 @@ struct tfjs_cuda_ctx {
   long long* h_bad_index = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::vector<cudaEvent_t> prof_events;  // numbered events for per-kernel timing
+  std::vector<cudaEvent_t> read_events;  // tickets of tfjs_cuda_read_begin (index + 1)
+  std::vector<int> read_free;            // ticket slots free for reuse
   void* l2_scratch = nullptr;
   uint64_t l2_scratch_bytes = 0;
   // grow-only scratch for im2col / operand transposes

@@ -141,7 +141,20 @@ __global__ void reduce_mid_kernel(const float* __restrict__ x,
     const float* xp = x + o * reduce * inner + in;
     double acc = 0.0;
     float mx = xp[0];
-    for (uint64_t j = 0; j < reduce; ++j) {
+    // eight independent loads in flight per thread; the accumulation order stays j = 0, 1, ...
+    uint64_t j = 0;
+    for (; j + 8 <= reduce; j += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldg(xp + (j + u) * inner);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (OP == 0) acc += (double)v[u];
+        else if (OP == 1) acc += (double)__fdiv_rn(v[u], nf);
+        else mx = nan_max(mx, v[u]);
+      }
+    }
+    for (; j < reduce; ++j) {
       const float v = xp[j * inner];
       if (OP == 0) acc += (double)v;
       else if (OP == 1) acc += (double)__fdiv_rn(v, nf);

@@ -90,6 +90,12 @@ static void cache_flush(tfjs_cuda_ctx* ctx) {
   for (auto& kv : ctx->block_cache)
     for (void* p : kv.second) cudaFreeAsync(p, ctx->stream);
   ctx->block_cache.clear();
+  for (UploadBlock& u : ctx->upload_cache) {
+    cudaStreamWaitEvent(ctx->stream, u.released, 0);
+    cudaFreeAsync(u.ptr, ctx->stream);
+    ctx->event_pool.push_back(u.released);
+  }
+  ctx->upload_cache.clear();
   ctx->cached_bytes = 0;
 }
 
@@ -199,6 +205,7 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
   for (cudaEvent_t e : ctx->prof_events)
     if (e) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
+  for (cudaEvent_t e : ctx->read_events) cudaEventDestroy(e);
   for (auto& b : ctx->bufs)
     if (b.ready) cudaEventDestroy(b.ready);
   if (ctx->copy_stream) {
@@ -257,7 +264,25 @@ int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id) {
   }
   uint64_t padded = ((b->bytes + 255) / 256) * 256;
   if (padded == 0) padded = 256;
-  block_free(ctx, b->ptr, padded);
+  cudaEvent_t rel = nullptr;
+  if (b->uploaded) {
+    if (!ctx->event_pool.empty()) {
+      rel = ctx->event_pool.back();
+      ctx->event_pool.pop_back();
+    } else if (cudaEventCreateWithFlags(&rel, cudaEventDisableTiming) != cudaSuccess) {
+      rel = nullptr;
+    }
+  }
+  if (rel && cudaEventRecord(rel, ctx->stream) == cudaSuccess) {
+    // every kernel that reads the tensor has been launched: the block may be refilled by
+    // the copy stream once the compute stream gets here
+    ctx->upload_cache.push_back(UploadBlock{b->ptr, padded, rel});
+    ctx->cached_bytes += padded;
+  } else {
+    if (rel) ctx->event_pool.push_back(rel);
+    block_free(ctx, b->ptr, padded);
+  }
+  b->uploaded = false;
   b->ptr = nullptr;
   b->live = false;
   b->bytes = 0;
@@ -291,9 +316,32 @@ int tfjs_cuda_upload(tfjs_cuda_ctx* ctx, const void* host, uint64_t nbytes, int3
   void* p = nullptr;
   uint64_t padded = ((nbytes + 255) / 256) * 256;
   if (padded == 0) padded = 256;
-  // Allocated and filled on the copy stream, so the transfer does not queue behind
-  // kernels already launched on the compute stream.
-  CUDA_TRY(ctx, cudaMallocAsync(&p, padded, ctx->copy_stream));
+  // Filled on the copy stream, so the transfer does not queue behind kernels already
+  // launched on the compute stream.  The block is the one an earlier upload of this size
+  // released longest ago, else a fresh one.
+  // Prefer a block whose last reader has already finished; while fewer than two blocks of
+  // this size wait for their readers, take a fresh one rather than stall the transfer.
+  int same = 0, pick = -1;
+  for (size_t i = 0; i < ctx->upload_cache.size(); ++i) {
+    if (ctx->upload_cache[i].bytes != padded) continue;
+    ++same;
+    if (cudaEventQuery(ctx->upload_cache[i].released) == cudaSuccess) {
+      pick = (int)i;
+      break;
+    }
+    if (pick < 0) pick = (int)i;  // oldest, if nothing has finished
+  }
+  cudaGetLastError();  // cudaErrorNotReady from the queries is not an error
+  if (pick >= 0 && (same >= 2 || cudaEventQuery(ctx->upload_cache[pick].released) == cudaSuccess)) {
+    UploadBlock u = ctx->upload_cache[pick];
+    ctx->upload_cache.erase(ctx->upload_cache.begin() + pick);
+    ctx->cached_bytes -= padded;
+    CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_stream, u.released, 0));
+    ctx->event_pool.push_back(u.released);
+    p = u.ptr;
+  }
+  cudaGetLastError();
+  if (!p) CUDA_TRY(ctx, cudaMallocAsync(&p, padded, ctx->copy_stream));
   if (nbytes)
     CUDA_TRY(ctx, cudaMemcpyAsync(p, host, nbytes, cudaMemcpyHostToDevice, ctx->copy_stream));
   cudaEvent_t ev = nullptr;
@@ -319,6 +367,7 @@ int tfjs_cuda_upload(tfjs_cuda_ctx* ctx, const void* host, uint64_t nbytes, int3
   b.from_host = true;
   b.version++;
   b.ready = ev;
+  b.uploaded = true;
   ctx->in_use += padded;
   ctx->n_live++;
   if (ctx->in_use > ctx->high_water) ctx->high_water = ctx->in_use;
@@ -359,6 +408,45 @@ int tfjs_cuda_read_async(tfjs_cuda_ctx* ctx, int32_t id, void* host,
   CUDA_TRY(ctx, cudaMemcpyAsync(host, b->ptr, nbytes, cudaMemcpyDeviceToHost,
                                 ctx->stream));
   return TFJS_CUDA_OK;
+}
+
+// backend.read(): the D2H copy and an event are queued behind the kernels already on
+// the stream; the host keeps launching and collects the bytes with read_wait.
+int tfjs_cuda_read_begin(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes,
+                         int32_t* out_ticket) {
+  if (!ctx || !out_ticket) return TFJS_CUDA_INVALID_ARG;
+  *out_ticket = 0;
+  int rc = tfjs_cuda_read_async(ctx, id, host, nbytes);
+  if (rc) return rc;
+  // the device error word travels with every read, as it does with a blocking one
+  CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_flag, ctx->d_flag, sizeof(int),
+                                cudaMemcpyDeviceToHost, ctx->stream));
+  int slot;
+  if (!ctx->read_free.empty()) {
+    slot = ctx->read_free.back();
+    ctx->read_free.pop_back();
+  } else {
+    cudaEvent_t ev;
+    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    ctx->read_events.push_back(ev);
+    slot = (int)ctx->read_events.size() - 1;
+  }
+  CUDA_TRY(ctx, cudaEventRecord(ctx->read_events[slot], ctx->stream));
+  *out_ticket = slot + 1;
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_read_wait(tfjs_cuda_ctx* ctx, int32_t ticket) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  const int slot = ticket - 1;
+  if (slot < 0 || (size_t)slot >= ctx->read_events.size())
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "read_wait: unknown ticket %d", ticket);
+  for (int f : ctx->read_free)
+    if (f == slot) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "read_wait: ticket %d already collected", ticket);
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaEventSynchronize(ctx->read_events[slot]));
+  ctx->read_free.push_back(slot);
+  return report_flag(ctx);
 }
 
 int tfjs_cuda_read(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes) {

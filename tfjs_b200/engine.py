@@ -41,8 +41,12 @@ class Tensor(object):
         self._check()
         return self._engine.backend.readSync(self.dataId)
 
-    def data(self):
-        return self.dataSync()
+    def data(self, into=None):
+        """tensor.data(): Promise (tensor.ts:322-336 -> backend.read).  Returns a
+        PendingRead; `.wait()` yields the values.  Kernels launched after this call
+        run while the copy is outstanding."""
+        self._check()
+        return self._engine.backend.read(self.dataId, into)
 
     def arraySync(self):
         return self.dataSync().reshape(self.shape)

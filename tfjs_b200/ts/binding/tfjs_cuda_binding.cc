@@ -109,6 +109,16 @@ napi_value TimeEnd(napi_env env, napi_callback_info info) {
   check(env, a.ctx(0), tfjs_cuda_time_end(a.ctx(0), &ms));
   return num(env, ms);
 }
+napi_value ReadBegin(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  int32_t ticket = 0;
+  napi_value bad = check(env, a.ctx(0), tfjs_cuda_read_begin(a.ctx(0), a.i32(1), a.buffer(2), a.u64(3), &ticket));
+  (void)bad;
+  return num(env, ticket);
+}
+napi_value ReadWait(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_read_wait(a.ctx(0), a.i32(1)));
+}
 napi_value SetMathMode(napi_env env, napi_callback_info info) {
   Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_set_math_mode(a.ctx(0), a.i32(1)));
 }
@@ -207,7 +217,7 @@ napi_value DequantizeStatic(napi_env env, napi_callback_info info) {
 napi_value Init(napi_env env, napi_value exports) {
   struct { const char* name; napi_callback fn; } table[] = {
       {"create", Create}, {"alloc", Alloc}, {"free", Free}, {"write", Write}, {"read", Read},
-      {"sync", Sync}, {"memory", Memory}, {"timeBegin", TimeBegin}, {"timeEnd", TimeEnd},
+      {"readBegin", ReadBegin}, {"readWait", ReadWait}, {"sync", Sync}, {"memory", Memory}, {"timeBegin", TimeBegin}, {"timeEnd", TimeEnd},
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},
       {"fusedConv2dResidual", FusedConv2DResidual}, {"addActivation", AddActivation},
       {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul},

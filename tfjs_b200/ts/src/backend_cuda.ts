@@ -86,8 +86,16 @@ export class CudaBackend extends KernelBackend {
     return out;
   }
 
-  override async read(dataId: object): Promise<backend_util.BackendValues> {
-    return this.readSync(dataId);
+  /** The copy is queued behind the kernels launched so far; the promise resolves on a
+   *  later turn of the event loop, so code between `data()` and `await` keeps launching. */
+  override read(dataId: object): Promise<backend_util.BackendValues> {
+    const r = this.data.get(dataId);
+    if (r.host != null) return Promise.resolve(r.host.slice());
+    const out = util.getTypedArrayFromDType(r.dtype as 'float32', r.nbytes / bytesPerElement(r.dtype));
+    const ticket = binding.readBegin(this.ctx, r.id, out, r.nbytes);
+    return new Promise((resolve, reject) => setImmediate(() => {
+      try { binding.readWait(this.ctx, ticket); resolve(out); } catch (e) { reject(e); }
+    }));
   }
 
   override disposeData(dataId: object, force = false): boolean {

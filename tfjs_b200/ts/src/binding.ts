@@ -13,6 +13,8 @@ export interface CudaBinding {
   free(ctx: Ctx, id: number): void;
   write(ctx: Ctx, id: number, data: ArrayBufferView, nbytes: number): void;
   read(ctx: Ctx, id: number, out: ArrayBufferView, nbytes: number): void;
+  readBegin(ctx: Ctx, id: number, out: ArrayBufferView, nbytes: number): number;
+  readWait(ctx: Ctx, ticket: number): void;
   sync(ctx: Ctx): void;
   memory(ctx: Ctx): {numBytesInGPU: number, numBytesInGPUAllocated: number,
                      poolHighWater: number, numDeviceBuffers: number};
