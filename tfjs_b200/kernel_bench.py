@@ -6,7 +6,9 @@ op front end with CUDA events on the backend's stream.
 cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072),
 pw_<hw>_<cin>_<cout>_<batch> (1x1 conv), c3_<hw>_<cin>_<cout>_<batch>_<stride> (3x3
 conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<batch>_<stride>
-(3x3 depthwise).  Prints ms, TFLOP/s and algorithmic GB/s (each tensor moved once).
+(3x3 depthwise), res_<hw>_<cin>_<cout>_<batch> (1x1 conv + bias, Add of a shortcut, Relu:
+one launch through the deferred-launch path).  Prints ms, TFLOP/s and algorithmic GB/s
+(each tensor moved once).
 """
 import sys
 
@@ -31,6 +33,14 @@ elif case=='ffn':
     a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
     bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
     f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'linear'); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
+elif case.startswith('res'):   # residual block exit: res_<hw>_<cin>_<cout>_<batch>
+    _,hw,ci,co,bt=case.split('_'); hw,ci,co,bt=int(hw),int(ci),int(co),int(bt)
+    x=ops.tensor(r.standard_normal((bt,hw,hw,ci)).astype(np.float32)); w=ops.tensor(r.standard_normal((1,1,ci,co)).astype(np.float32)/8)
+    bias=ops.tensor(r.standard_normal(co).astype(np.float32)); sc=ops.tensor(r.standard_normal((bt,hw,hw,co)).astype(np.float32))
+    def f():
+        y=ops.fused_conv2d(x,w,1,'same','NHWC',[1,1],None,bias,'linear'); s=ops.add(y,sc); o=ops.relu(s)
+        y.dispose(); s.dispose(); return o
+    fl=2*bt*hw*hw*ci*co; by=4*(bt*hw*hw*(ci+2*co)+ci*co)
 elif case.startswith('pw'):   # pointwise conv: pw_<hw>_<cin>_<cout>_<batch>
     _,hw,ci,co,bt=case.split('_'); hw,ci,co,bt=int(hw),int(ci),int(co),int(bt)
     x=ops.tensor(r.standard_normal((bt,hw,hw,ci)).astype(np.float32)); w=ops.tensor(r.standard_normal((1,1,ci,co)).astype(np.float32)/8)
