@@ -232,12 +232,14 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     sample = args.cpu_sample or {"mobilenet_v2": 32, "resnet50": 4, "bert": 2}[args.model]
+    # torchrun exports OMP_NUM_THREADS=1; the reference arm uses every host core
+    threads = os.cpu_count() or 1
     for _ in range(max(args.warmup, 0) and 1):
-        cpu_sample(args.model, 1)
+        cpu_sample(args.model, 1, threads=threads)
     vals = []
     t_all = time.perf_counter()
     for _ in range(args.steps):
-        v, dt, cores, _ = cpu_sample(args.model, sample)
+        v, dt, cores, _ = cpu_sample(args.model, sample, threads=threads)
         vals.append(v)
     total = time.perf_counter() - t_all
     value = float(np.mean(vals))
