@@ -277,7 +277,9 @@ def run_cuda(args, rank, world, local_rank):
     max_over_ranks = group.max_over_ranks
 
     model_json, weights = build_model(args.model, batch)
-    gm = GraphModel(model_json, weights, eng)
+    # whole-step replay: the second warm-up step is captured into a CUDA graph and every
+    # later step is one graph launch (the per-kernel profile below runs eagerly)
+    gm = GraphModel(model_json, weights, eng, replay=not args.no_replay)
     feeds = make_feeds(args.model, batch, 1000 + rank)
     pinned, dtypes = {}, {}
     for k, v in feeds.items():
@@ -397,6 +399,7 @@ def run_cuda(args, rank, world, local_rank):
                 "config": {"workload": w["name"], "batch_per_gpu": batch,
                            "global_batch": units, "parallelism": "replicas x%d" % world,
                            "l2": "activations per step are far larger than L2",
+                           "step_replay": bool(gm.replay),
                            "weights": "random init"},
                 "host_ms_per_step": round(host_ms / args.steps, 4),
                 "tflops": round(units * w["gflop"] / 1e3 / (dev_ms / args.steps / 1e3), 2),
@@ -431,6 +434,8 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the workload's)")
     ap.add_argument("--cpu-sample", type=int, default=0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-replay", action="store_true",
+                    help="launch every kernel from the host at every step")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

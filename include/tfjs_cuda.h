@@ -163,6 +163,29 @@ int tfjs_cuda_fused_conv2d_residual(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_p
                                     int32_t prelu_id, int32_t residual_id,
                                     int32_t post_activation, int32_t out_id);
 
+/* ---- whole-step capture and replay ----------------------------------------------------
+ * The graph executor launches the same kernels with the same shapes at every
+ * GraphModel.execute (tfjs-converter/src/executor/graph_executor.ts:228-310).  Between
+ * capture_begin and capture_end every kernel call on this context is recorded into a
+ * CUDA graph instead of being run, and tensors allocated in between live in an arena of
+ * `arena_bytes` that belongs to the graph; graph_launch then replays the whole step with
+ * one call.  Tensors that exist before the capture (weights, the step's input buffers)
+ * are referenced by address, so a replay reads whatever they hold at that time
+ * (tfjs_cuda_copy refills the input buffers).  Calls that move data to or from the host,
+ * wait, or need new pool memory are refused during a capture (TFJS_CUDA_UNSUPPORTED) and
+ * make capture_end discard it; the host layer then keeps running that model eagerly.
+ * Tensors created during a capture that are still alive at capture_end (the step's
+ * outputs) stay valid until graph_destroy and are rewritten by every replay. */
+int tfjs_cuda_capture_begin(tfjs_cuda_ctx* ctx, uint64_t arena_bytes);
+int tfjs_cuda_capture_end(tfjs_cuda_ctx* ctx, int abandon, int32_t* out_graph);
+int tfjs_cuda_graph_launch(tfjs_cuda_ctx* ctx, int32_t graph);
+int tfjs_cuda_graph_destroy(tfjs_cuda_ctx* ctx, int32_t graph);
+/* Device-to-device copy of the first nbytes of src into dst, in stream order. */
+int tfjs_cuda_copy(tfjs_cuda_ctx* ctx, int32_t src_id, int32_t dst_id, uint64_t nbytes);
+/* Restart the high-water mark of tfjs_cuda_memory at the bytes in use now (sizes the arena
+ * of a capture from an eager step). */
+int tfjs_cuda_high_water_reset(tfjs_cuda_ctx* ctx);
+
 /* ---- FusedDepthwiseConv2D / DepthwiseConv2dNative:
  * tfjs-backend-cpu/src/kernels/FusedDepthwiseConv2D.ts:25-61,
  * DepthwiseConv2dNative.ts:23-102; attrs kernel_names.ts:1033-1048.  out_c is

@@ -69,6 +69,12 @@ SIGNATURES = {
     "tfjs_cuda_launch_count": (c_int, [_CTX, POINTER(c_uint64)]),
     "tfjs_cuda_flush_l2": (c_int, [_CTX]),
     "tfjs_cuda_fused_conv2d": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 5),
+    "tfjs_cuda_capture_begin": (c_int, [_CTX, c_uint64]),
+    "tfjs_cuda_capture_end": (c_int, [_CTX, c_int, POINTER(c_int32)]),
+    "tfjs_cuda_graph_launch": (c_int, [_CTX, c_int32]),
+    "tfjs_cuda_graph_destroy": (c_int, [_CTX, c_int32]),
+    "tfjs_cuda_copy": (c_int, [_CTX, c_int32, c_int32, c_uint64]),
+    "tfjs_cuda_high_water_reset": (c_int, [_CTX]),
     "tfjs_cuda_read_begin": (c_int, [_CTX, c_int32, c_void_p, c_uint64, POINTER(c_int32)]),
     "tfjs_cuda_read_wait": (c_int, [_CTX, c_int32]),
     "tfjs_cuda_fused_conv2d_residual": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 7),

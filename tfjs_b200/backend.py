@@ -431,6 +431,32 @@ class CudaBackend(object):
         self.check(self.lib.tfjs_cuda_set_math_mode(
             self.ctx, {"tf32": _cabi.MATH_TF32, "fp32": _cabi.MATH_FP32}[mode]))
 
+    # ------------------------------------------------ whole-step capture / replay --
+    def high_water_reset(self):
+        self.check(self.lib.tfjs_cuda_high_water_reset(self.ctx))
+
+    def copy(self, src_dataId, dst_dataId):
+        """Device-to-device copy of a whole tensor, in stream order."""
+        nbytes = self.data[src_dataId].nbytes
+        self.check(self.lib.tfjs_cuda_copy(self.ctx, self.device_id(src_dataId),
+                                           self.device_id(dst_dataId), nbytes))
+
+    def capture_begin(self, arena_bytes):
+        self.check(self.lib.tfjs_cuda_capture_begin(self.ctx, int(arena_bytes)))
+
+    def capture_end(self, abandon=False):
+        """Graph id of the captured step; raises CudaError (UNSUPPORTED) when the capture
+        had to be discarded."""
+        graph = c_int32()
+        self.check(self.lib.tfjs_cuda_capture_end(self.ctx, 1 if abandon else 0, byref(graph)))
+        return graph.value
+
+    def graph_launch(self, graph):
+        self.check(self.lib.tfjs_cuda_graph_launch(self.ctx, int(graph)))
+
+    def graph_destroy(self, graph):
+        self.check(self.lib.tfjs_cuda_graph_destroy(self.ctx, int(graph)))
+
     def launch_count(self):
         v = c_uint64()
         self.check(self.lib.tfjs_cuda_launch_count(self.ctx, byref(v)))

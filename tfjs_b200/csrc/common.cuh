@@ -19,6 +19,19 @@ struct Buffer {
   uint32_t version = 0;    // bumped whenever the contents are (re)written
   cudaEvent_t ready = nullptr;  // set while an upload on the copy stream is pending
   bool uploaded = false;        // block came from tfjs_cuda_upload: recycled for uploads
+  bool in_arena = false;        // lives in the arena of a captured graph
+};
+
+// A captured step (tfjs_cuda_capture_begin .. _end): the instantiated graph and the
+// arena its intermediate and output tensors live in.
+struct ReplayGraph {
+  cudaGraphExec_t exec = nullptr;
+  void* arena = nullptr;
+  uint64_t arena_bytes = 0;
+  uint64_t launches = 0;  // kernels per replay
+};
+struct ArenaSpan {
+  uint64_t off, size;
 };
 
 // A block released by an uploaded tensor, kept for the next upload of that size: the
@@ -54,6 +67,14 @@ struct tfjs_cuda_ctx {
   std::unordered_map<uint64_t, std::vector<void*>> block_cache;
   uint64_t cached_bytes = 0;
   std::vector<UploadBlock> upload_cache;  // oldest first
+  // stream capture of a whole step
+  bool capturing = false;
+  bool capture_failed = false;
+  void* arena = nullptr;
+  uint64_t arena_bytes = 0;
+  std::vector<ArenaSpan> arena_free;  // sorted by offset, coalesced
+  uint64_t capture_launches0 = 0;
+  std::vector<ReplayGraph> graphs;    // index + 1 = graph id
   cudaMemPool_t pool = nullptr;
   std::vector<Buffer> bufs;  // index = id; slot 0 unused
   std::vector<int32_t> free_ids;
@@ -91,6 +112,18 @@ void ctx_drop_packed(tfjs_cuda_ctx* ctx, int32_t id);
   do {                                                        \
     int _rc = ctx_check((ctx), (expr), #expr);                \
     if (_rc != TFJS_CUDA_OK) return _rc;                      \
+  } while (0)
+
+// Entry points that cannot be part of a captured step (host transfers, waits, new
+// pool allocations) refuse and mark the capture as failed; the host layer then runs
+// that model eagerly.
+#define NOT_WHILE_CAPTURING(ctx, what)                                                    \
+  do {                                                                                    \
+    if ((ctx)->capturing) {                                                               \
+      (ctx)->capture_failed = true;                                                       \
+      return ctx_fail((ctx), TFJS_CUDA_UNSUPPORTED,                                       \
+                      what " cannot be part of a captured step");                         \
+    }                                                                                     \
   } while (0)
 
 #define LAUNCH_CHECK(ctx, name)                               \

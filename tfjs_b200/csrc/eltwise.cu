@@ -884,6 +884,11 @@ int tfjs_cuda_gather(tfjs_cuda_ctx* ctx, int32_t elem_bytes, int32_t x_id,
   }
   LAUNCH_CHECK(ctx, "gather_kernel");
   ctx_mark_written(ctx, out_id);
+  if (check_indices && ctx->capturing) {
+    // a captured step cannot stop for the answer: the kernel writes zeros for a bad index
+    // (as it always does) and replays do not raise the reference's error for it
+    return TFJS_CUDA_OK;
+  }
   if (check_indices) {
     CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_bad_index, ctx->d_bad_index, sizeof(long long),
                                   cudaMemcpyDeviceToHost, ctx->stream));
@@ -902,6 +907,7 @@ int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_dtype,
                          int32_t q_id, double scale, double min, uint64_t n,
                          int32_t out_id) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "dequantising weights");
   if (q_bytes != 1 && q_bytes != 2)
     return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "dequantize: q_dtype_bytes %d", q_bytes);
   if (to_dtype != TFJS_CUDA_FLOAT32 && to_dtype != TFJS_CUDA_INT32)
@@ -970,6 +976,7 @@ int tfjs_cuda_dequantize_static(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_
                                 int32_t q_id, double scale, double min, uint64_t n,
                                 int32_t out_id) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "dequantising weights");
   if (q_bytes < 1)
     return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "dequantize_static: q_dtype_bytes %d", q_bytes);
   if (q_bytes > 2)
@@ -1034,6 +1041,7 @@ int tfjs_cuda_dequantize_static(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_
 
 int tfjs_cuda_flush_l2(tfjs_cuda_ctx* ctx) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "flushing L2");
   cudaSetDevice(ctx->device);
   const uint64_t bytes = 256ull << 20;
   if (!ctx->l2_scratch) {

@@ -83,6 +83,7 @@ int get_packed(tfjs_cuda_ctx* ctx, int32_t id, Buffer* src, int batch, int N, in
     *out = it->second.ptr;
     return TFJS_CUDA_OK;
   }
+  NOT_WHILE_CAPTURING(ctx, "packing a weight tensor");
   ctx_drop_packed(ctx, id);
   PackedWeight pw;
   const uint64_t total = (uint64_t)batch * N * taps * cin_pad;

@@ -49,6 +49,7 @@ int ctx_get(tfjs_cuda_ctx* ctx, int32_t id, uint64_t need, const char* name,
                     "%s: tensor id %d holds %llu bytes, kernel needs %llu", name,
                     id, (unsigned long long)b->bytes, (unsigned long long)need);
   if (b->ready) {
+    NOT_WHILE_CAPTURING(ctx, "a tensor whose upload is still pending");
     // first use after an overlapped upload: order the compute stream behind the copy
     cudaStreamWaitEvent(ctx->stream, b->ready, 0);
     ctx->event_pool.push_back(b->ready);
@@ -60,6 +61,7 @@ int ctx_get(tfjs_cuda_ctx* ctx, int32_t id, uint64_t need, const char* name,
 
 int ctx_scratch(tfjs_cuda_ctx* ctx, uint64_t bytes, void** out) {
   if (bytes > ctx->scratch_bytes) {
+    NOT_WHILE_CAPTURING(ctx, "growing the scratch buffer");
     if (ctx->scratch) CUDA_TRY(ctx, cudaFreeAsync(ctx->scratch, ctx->stream));
     ctx->scratch = nullptr;
     ctx->scratch_bytes = 0;
@@ -101,6 +103,38 @@ static void cache_flush(tfjs_cuda_ctx* ctx) {
 
 // Pool allocation for tensors: exact-size cache first, then the stream-ordered pool;
 // on failure the cache is returned to the pool and the request retried once.
+// First-fit allocator over the arena of the step being captured.  The captured step is
+// one chain of graph nodes in launch order, so a span freed by the host may be handed
+// to a later node straight away, exactly like the stream-ordered blocks outside capture.
+static bool arena_alloc(tfjs_cuda_ctx* ctx, uint64_t padded, void** out) {
+  for (size_t i = 0; i < ctx->arena_free.size(); ++i) {
+    ArenaSpan& f = ctx->arena_free[i];
+    if (f.size < padded) continue;
+    *out = (char*)ctx->arena + f.off;
+    f.off += padded;
+    f.size -= padded;
+    if (f.size == 0) ctx->arena_free.erase(ctx->arena_free.begin() + i);
+    return true;
+  }
+  return false;
+}
+
+static void arena_release(tfjs_cuda_ctx* ctx, void* p, uint64_t padded) {
+  const uint64_t off = (uint64_t)((char*)p - (char*)ctx->arena);
+  size_t i = 0;
+  while (i < ctx->arena_free.size() && ctx->arena_free[i].off < off) ++i;
+  ctx->arena_free.insert(ctx->arena_free.begin() + i, ArenaSpan{off, padded});
+  if (i + 1 < ctx->arena_free.size() &&
+      ctx->arena_free[i].off + ctx->arena_free[i].size == ctx->arena_free[i + 1].off) {
+    ctx->arena_free[i].size += ctx->arena_free[i + 1].size;
+    ctx->arena_free.erase(ctx->arena_free.begin() + i + 1);
+  }
+  if (i > 0 && ctx->arena_free[i - 1].off + ctx->arena_free[i - 1].size == ctx->arena_free[i].off) {
+    ctx->arena_free[i - 1].size += ctx->arena_free[i].size;
+    ctx->arena_free.erase(ctx->arena_free.begin() + i);
+  }
+}
+
 static cudaError_t block_alloc(tfjs_cuda_ctx* ctx, uint64_t padded, void** out) {
   auto it = ctx->block_cache.find(padded);
   if (it != ctx->block_cache.end() && !it->second.empty()) {
@@ -206,6 +240,11 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
     if (e) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->read_events) cudaEventDestroy(e);
+  for (ReplayGraph& g : ctx->graphs)
+    if (g.exec) {
+      cudaGraphExecDestroy(g.exec);
+      cudaFree(g.arena);
+    }
   for (auto& b : ctx->bufs)
     if (b.ready) cudaEventDestroy(b.ready);
   if (ctx->copy_stream) {
@@ -229,7 +268,17 @@ int tfjs_cuda_alloc(tfjs_cuda_ctx* ctx, uint64_t nbytes, int32_t* out_id) {
   // Round up so vectorised kernels may read a full 16-byte tail.
   uint64_t padded = ((nbytes + 255) / 256) * 256;
   if (padded == 0) padded = 256;
-  CUDA_TRY(ctx, block_alloc(ctx, padded, &p));
+  const bool in_arena = ctx->capturing;
+  if (in_arena) {
+    if (!arena_alloc(ctx, padded, &p)) {
+      ctx->capture_failed = true;
+      return ctx_fail(ctx, TFJS_CUDA_OUT_OF_MEMORY,
+                      "the arena of the step being captured is full (%llu bytes)",
+                      (unsigned long long)ctx->arena_bytes);
+    }
+  } else {
+    CUDA_TRY(ctx, block_alloc(ctx, padded, &p));
+  }
   int32_t id;
   if (!ctx->free_ids.empty()) {
     id = ctx->free_ids.back();
@@ -243,6 +292,7 @@ int tfjs_cuda_alloc(tfjs_cuda_ctx* ctx, uint64_t nbytes, int32_t* out_id) {
   b.bytes = nbytes;
   b.live = true;
   b.from_host = false;
+  b.in_arena = in_arena;
   b.version++;
   ctx->in_use += padded;
   ctx->n_live++;
@@ -256,6 +306,8 @@ int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id) {
   Buffer* b = ctx_buf(ctx, id);
   if (!b) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "free: unknown tensor id %d", id);
   cudaSetDevice(ctx->device);
+  if (ctx->capturing && (b->ready || ctx->packed.count(id)))
+    NOT_WHILE_CAPTURING(ctx, "freeing a weight or a tensor whose upload is pending");
   ctx_drop_packed(ctx, id);
   if (b->ready) {  // never used since its upload: still order the free behind the copy
     cudaStreamWaitEvent(ctx->stream, b->ready, 0);
@@ -265,7 +317,20 @@ int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id) {
   uint64_t padded = ((b->bytes + 255) / 256) * 256;
   if (padded == 0) padded = 256;
   cudaEvent_t rel = nullptr;
-  if (b->uploaded) {
+  if (b->in_arena) {
+    // inside the capture the span goes back to the arena; afterwards (an output of a
+    // captured step) the memory belongs to the graph and only the id is retired
+    if (ctx->capturing) arena_release(ctx, b->ptr, padded);
+    b->in_arena = false;
+    b->ptr = nullptr;
+    b->live = false;
+    b->bytes = 0;
+    ctx->in_use -= padded;
+    ctx->n_live--;
+    ctx->free_ids.push_back(id);
+    return TFJS_CUDA_OK;
+  }
+  if (b->uploaded && !ctx->capturing) {
     if (!ctx->event_pool.empty()) {
       rel = ctx->event_pool.back();
       ctx->event_pool.pop_back();
@@ -295,6 +360,7 @@ int tfjs_cuda_free(tfjs_cuda_ctx* ctx, int32_t id) {
 int tfjs_cuda_write(tfjs_cuda_ctx* ctx, int32_t id, const void* host,
                     uint64_t nbytes) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "a host-to-device write");
   Buffer* b;
   int rc = ctx_get(ctx, id, nbytes, "write", &b);
   if (rc) return rc;
@@ -311,6 +377,7 @@ int tfjs_cuda_write(tfjs_cuda_ctx* ctx, int32_t id, const void* host,
 
 int tfjs_cuda_upload(tfjs_cuda_ctx* ctx, const void* host, uint64_t nbytes, int32_t* out_id) {
   if (!ctx || !out_id) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "a host-to-device upload");
   if (nbytes && !host) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "upload: null host pointer");
   cudaSetDevice(ctx->device);
   void* p = nullptr;
@@ -389,6 +456,7 @@ static int report_flag(tfjs_cuda_ctx* ctx) {
 
 int tfjs_cuda_sync(tfjs_cuda_ctx* ctx) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "a stream synchronisation");
   cudaSetDevice(ctx->device);
   CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_flag, ctx->d_flag, sizeof(int),
                                 cudaMemcpyDeviceToHost, ctx->stream));
@@ -399,6 +467,7 @@ int tfjs_cuda_sync(tfjs_cuda_ctx* ctx) {
 int tfjs_cuda_read_async(tfjs_cuda_ctx* ctx, int32_t id, void* host,
                          uint64_t nbytes) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "a device-to-host read");
   Buffer* b;
   int rc = ctx_get(ctx, id, nbytes, "read", &b);
   if (rc) return rc;
@@ -490,6 +559,7 @@ int tfjs_cuda_memory(tfjs_cuda_ctx* ctx, uint64_t* bytes_in_use,
 
 int tfjs_cuda_trim(tfjs_cuda_ctx* ctx) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "trimming the pool");
   cudaSetDevice(ctx->device);
   cache_flush(ctx);
   CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
@@ -513,6 +583,7 @@ int tfjs_cuda_host_free(tfjs_cuda_ctx* ctx, void* ptr) {
 
 int tfjs_cuda_time_begin(tfjs_cuda_ctx* ctx) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "timing");
   cudaSetDevice(ctx->device);
   CUDA_TRY(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
   return TFJS_CUDA_OK;
@@ -520,6 +591,7 @@ int tfjs_cuda_time_begin(tfjs_cuda_ctx* ctx) {
 
 int tfjs_cuda_time_end(tfjs_cuda_ctx* ctx, float* out_kernel_ms) {
   if (!ctx || !out_kernel_ms) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "timing");
   cudaSetDevice(ctx->device);
   CUDA_TRY(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
   CUDA_TRY(ctx, cudaEventSynchronize(ctx->ev1));
@@ -529,6 +601,7 @@ int tfjs_cuda_time_end(tfjs_cuda_ctx* ctx, float* out_kernel_ms) {
 
 int tfjs_cuda_event_record(tfjs_cuda_ctx* ctx, int32_t slot) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "recording a timing event");
   if (slot < 0 || slot > (1 << 20))
     return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "event_record: bad slot %d", slot);
   cudaSetDevice(ctx->device);
@@ -549,6 +622,128 @@ int tfjs_cuda_event_elapsed(tfjs_cuda_ctx* ctx, int32_t slot_begin, int32_t slot
   CUDA_TRY(ctx, cudaEventSynchronize(ctx->prof_events[slot_end]));
   CUDA_TRY(ctx, cudaEventElapsedTime(out_ms, ctx->prof_events[slot_begin],
                                      ctx->prof_events[slot_end]));
+  return TFJS_CUDA_OK;
+}
+
+// ---- whole-step capture and replay -----------------------------------------------------
+int tfjs_cuda_high_water_reset(tfjs_cuda_ctx* ctx) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  ctx->high_water = ctx->in_use;
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_copy(tfjs_cuda_ctx* ctx, int32_t src_id, int32_t dst_id, uint64_t nbytes) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  Buffer *src, *dst;
+  int rc;
+  if ((rc = ctx_get(ctx, src_id, nbytes, "copy src", &src))) return rc;
+  if ((rc = ctx_get(ctx, dst_id, nbytes, "copy dst", &dst))) return rc;
+  if (nbytes == 0 || src->ptr == dst->ptr) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaMemcpyAsync(dst->ptr, src->ptr, nbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  dst->version++;
+  dst->from_host = false;
+  ctx_drop_packed(ctx, dst_id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_capture_begin(tfjs_cuda_ctx* ctx, uint64_t arena_bytes) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (ctx->capturing) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "capture_begin: already capturing");
+  cudaSetDevice(ctx->device);
+  arena_bytes = ((arena_bytes + 255) / 256) * 256;
+  if (arena_bytes == 0) arena_bytes = 256;
+  void* arena = nullptr;
+  CUDA_TRY(ctx, cudaMallocAsync(&arena, arena_bytes, ctx->stream));
+  // nothing of the capture may depend on work that is still in flight
+  CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  CUDA_TRY(ctx, cudaStreamSynchronize(ctx->copy_stream));
+  cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) {
+    cudaFreeAsync(arena, ctx->stream);
+    return ctx_check(ctx, e, "cudaStreamBeginCapture");
+  }
+  ctx->arena = arena;
+  ctx->arena_bytes = arena_bytes;
+  ctx->arena_free.assign(1, ArenaSpan{0, arena_bytes});
+  ctx->capturing = true;
+  ctx->capture_failed = false;
+  ctx->capture_launches0 = ctx->launches;
+  return TFJS_CUDA_OK;
+}
+
+// Ends the capture.  abandon != 0, a refused call during the capture or a failed
+// instantiation discard it (TFJS_CUDA_UNSUPPORTED); the tensors created during the
+// capture are then invalid and must only be freed.
+int tfjs_cuda_capture_end(tfjs_cuda_ctx* ctx, int abandon, int32_t* out_graph) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (out_graph) *out_graph = 0;
+  if (!ctx->capturing) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "capture_end: not capturing");
+  cudaSetDevice(ctx->device);
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+  ctx->capturing = false;
+  const uint64_t launches = ctx->launches - ctx->capture_launches0;
+  ctx->launches = ctx->capture_launches0;  // nothing ran yet
+  cudaGraphExec_t exec = nullptr;
+  const bool keep = e == cudaSuccess && graph && !abandon && !ctx->capture_failed && out_graph;
+  if (keep) e = cudaGraphInstantiate(&exec, graph, 0);
+  if (graph) cudaGraphDestroy(graph);
+  if (!keep || e != cudaSuccess || !exec) {
+    cudaGetLastError();
+    cudaFreeAsync(ctx->arena, ctx->stream);
+    ctx->arena = nullptr;
+    ctx->arena_free.clear();
+    if (e != cudaSuccess) return ctx_check(ctx, e, "ending the capture");
+    std::string why = ctx->err;
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "capture discarded%s%s",
+                    ctx->capture_failed ? ": " : "", ctx->capture_failed ? why.c_str() : "");
+  }
+  ReplayGraph g;
+  g.exec = exec;
+  g.arena = ctx->arena;
+  g.arena_bytes = ctx->arena_bytes;
+  g.launches = launches;
+  ctx->arena = nullptr;
+  ctx->arena_free.clear();
+  int slot = -1;
+  for (size_t i = 0; i < ctx->graphs.size(); ++i)
+    if (!ctx->graphs[i].exec) { slot = (int)i; break; }
+  if (slot < 0) {
+    ctx->graphs.emplace_back();
+    slot = (int)ctx->graphs.size() - 1;
+  }
+  ctx->graphs[slot] = g;
+  *out_graph = slot + 1;
+  return TFJS_CUDA_OK;
+}
+
+static ReplayGraph* graph_of(tfjs_cuda_ctx* ctx, int32_t id) {
+  if (id <= 0 || (size_t)id > ctx->graphs.size() || !ctx->graphs[id - 1].exec) return nullptr;
+  return &ctx->graphs[id - 1];
+}
+
+int tfjs_cuda_graph_launch(tfjs_cuda_ctx* ctx, int32_t graph) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "launching a captured step");
+  ReplayGraph* g = graph_of(ctx, graph);
+  if (!g) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "graph_launch: unknown graph %d", graph);
+  cudaSetDevice(ctx->device);
+  CUDA_TRY(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+  ctx->launches += g->launches;
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_graph_destroy(tfjs_cuda_ctx* ctx, int32_t graph) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  ReplayGraph* g = graph_of(ctx, graph);
+  if (!g) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "graph_destroy: unknown graph %d", graph);
+  cudaSetDevice(ctx->device);
+  // the arena goes back to the pool behind the replays already queued
+  cudaFreeAsync(g->arena, ctx->stream);
+  cudaStreamSynchronize(ctx->stream);
+  cudaGraphExecDestroy(g->exec);
+  *g = ReplayGraph();
   return TFJS_CUDA_OK;
 }
 

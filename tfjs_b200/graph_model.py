@@ -16,6 +16,7 @@ drives the same kernels from Python and is what the benchmark times.
 """
 import base64
 import json
+import os
 
 import numpy as np
 
@@ -399,8 +400,13 @@ class GraphExecutor(object):
 class GraphModel(object):
     """tfjs-converter/src/executor/graph_model.ts."""
 
-    def __init__(self, model_json, weight_data, engine=None, decode_weights=None):
+    def __init__(self, model_json, weight_data, engine=None, decode_weights=None, replay=None):
         self.engine = engine or ENGINE
+        # Whole-step replay: after one eager execute per (input shapes, outputs) signature
+        # the step is captured into a CUDA graph and later executes are one launch.
+        self.replay = (os.environ.get("TFJS_CUDA_GRAPH_REPLAY", "0") not in ("", "0")
+                       if replay is None else bool(replay))
+        self._replays = {}
         self.artifacts = model_json if isinstance(model_json, dict) else json.loads(model_json)
         if self.artifacts.get("format") not in (None, "graph-model"):
             raise ValueError("not a graph-model artifact")
@@ -444,13 +450,92 @@ class GraphModel(object):
         single = isinstance(outputs, str) or (outputs is None and len(self.output_names) == 1)
         if isinstance(outputs, str):
             outputs = [outputs]
-        res = self.executor.execute(inputs, outputs or self.output_names)
+        outputs = outputs or self.output_names
+        if self.replay and self.engine._profile is None and not self.executor.keep_intermediates:
+            res = self._execute_replayed(inputs, list(outputs))
+        else:
+            res = self.executor.execute(inputs, outputs)
         return res[0] if single else res
+
+    # ------------------------------------------------------------ step replay --
+    def _execute_replayed(self, inputs, outputs):
+        """First call per signature: eager, measuring the step's peak memory.  Second:
+        the executor runs once more under stream capture (nothing executes; every kernel
+        call is recorded, intermediates live in an arena owned by the graph).  From then
+        on: copy the inputs into the captured input buffers, launch the graph, copy the
+        outputs out.  A step that cannot be captured (a kernel that needs the host)
+        stays eager."""
+        from ._cabi import CudaError
+        be = self.engine.backend
+        key = (tuple(sorted((n, tuple(t.shape), t.dtype) for n, t in inputs.items())),
+               tuple(outputs))
+        st = self._replays.get(key)
+        if st is None:
+            be.high_water_reset()
+            before = be.memory()["numBytesInGPU"]
+            res = self.executor.execute(inputs, outputs)
+            for t in res:
+                be.device_id(t.dataId)          # launch anything still pending
+            peak = be.memory()["poolHighWater"] - before
+            self._replays[key] = {"state": "warm", "peak": max(int(peak), 0)}
+            return res
+        if st["state"] == "warm":
+            try:
+                self._capture(st, inputs, outputs)
+                st["state"] = "ready"
+            except CudaError as e:
+                st["state"] = "eager"
+                st["why"] = str(e)
+        if st["state"] != "ready":
+            return self.executor.execute(inputs, outputs)
+        for name, t in inputs.items():
+            be.copy(t.dataId, st["fixed"][name].dataId)
+        be.graph_launch(st["graph"])
+        res = []
+        for o in st["outs"]:
+            fresh = be.make_output(o.shape, o.dtype)
+            be.copy(o.dataId, fresh.dataId)
+            res.append(self.engine.make_tensor_from_info(fresh))
+        return res
+
+    def _capture(self, st, inputs, outputs):
+        be, eng = self.engine.backend, self.engine
+        fixed = {}
+        for name, t in inputs.items():
+            info = be.make_output(t.shape, t.dtype)
+            fixed[name] = eng.make_tensor_from_info(info)
+            be.copy(t.dataId, info.dataId)
+        outs = None
+        be.capture_begin(int(st["peak"] * 1.25) + (4 << 20))
+        try:
+            outs = self.executor.execute(fixed, outputs)
+            for t in outs:
+                be.device_id(t.dataId)
+            st["graph"] = be.capture_end(False)
+        except Exception:
+            try:
+                be.capture_end(True)
+            except Exception:
+                pass
+            for t in (outs or []):
+                t.dispose()
+            for t in fixed.values():
+                t.dispose()
+            raise
+        st["fixed"], st["outs"] = fixed, outs
 
     def predict(self, inputs):
         return self.execute(inputs)
 
     def dispose(self):
+        for st in self._replays.values():
+            if st.get("state") == "ready":
+                for t in st["outs"]:
+                    t.dispose()
+                for t in st["fixed"].values():
+                    t.dispose()
+                self.engine.backend.graph_destroy(st["graph"])
+        self._replays = {}
         for t in self.weights.values():
             t.dispose()
         self.weights = {}

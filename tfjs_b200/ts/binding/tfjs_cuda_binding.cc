@@ -119,6 +119,27 @@ napi_value ReadBegin(napi_env env, napi_callback_info info) {
 napi_value ReadWait(napi_env env, napi_callback_info info) {
   Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_read_wait(a.ctx(0), a.i32(1)));
 }
+napi_value CaptureBegin(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_capture_begin(a.ctx(0), a.u64(1)));
+}
+napi_value CaptureEnd(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  int32_t graph = 0;
+  check(env, a.ctx(0), tfjs_cuda_capture_end(a.ctx(0), a.i32(1), &graph));
+  return num(env, graph);
+}
+napi_value GraphLaunch(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_graph_launch(a.ctx(0), a.i32(1)));
+}
+napi_value GraphDestroy(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_graph_destroy(a.ctx(0), a.i32(1)));
+}
+napi_value Copy(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_copy(a.ctx(0), a.i32(1), a.i32(2), a.u64(3)));
+}
+napi_value HighWaterReset(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_high_water_reset(a.ctx(0)));
+}
 napi_value SetMathMode(napi_env env, napi_callback_info info) {
   Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_set_math_mode(a.ctx(0), a.i32(1)));
 }
@@ -217,6 +238,8 @@ napi_value DequantizeStatic(napi_env env, napi_callback_info info) {
 napi_value Init(napi_env env, napi_value exports) {
   struct { const char* name; napi_callback fn; } table[] = {
       {"create", Create}, {"alloc", Alloc}, {"free", Free}, {"write", Write}, {"read", Read},
+      {"captureBegin", CaptureBegin}, {"captureEnd", CaptureEnd}, {"graphLaunch", GraphLaunch},
+      {"graphDestroy", GraphDestroy}, {"copy", Copy}, {"highWaterReset", HighWaterReset},
       {"readBegin", ReadBegin}, {"readWait", ReadWait}, {"sync", Sync}, {"memory", Memory}, {"timeBegin", TimeBegin}, {"timeEnd", TimeEnd},
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},
       {"fusedConv2dResidual", FusedConv2DResidual}, {"addActivation", AddActivation},

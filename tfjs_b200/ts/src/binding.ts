@@ -13,6 +13,12 @@ export interface CudaBinding {
   free(ctx: Ctx, id: number): void;
   write(ctx: Ctx, id: number, data: ArrayBufferView, nbytes: number): void;
   read(ctx: Ctx, id: number, out: ArrayBufferView, nbytes: number): void;
+  captureBegin(ctx: Ctx, arenaBytes: number): void;
+  captureEnd(ctx: Ctx, abandon: number): number;
+  graphLaunch(ctx: Ctx, graph: number): void;
+  graphDestroy(ctx: Ctx, graph: number): void;
+  copy(ctx: Ctx, src: number, dst: number, nbytes: number): void;
+  highWaterReset(ctx: Ctx): void;
   readBegin(ctx: Ctx, id: number, out: ArrayBufferView, nbytes: number): number;
   readWait(ctx: Ctx, ticket: number): void;
   sync(ctx: Ctx): void;
