@@ -139,28 +139,20 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
 // Bias + activation on the 32 accumulator columns a thread holds, with the
 // activation resolved at compile time so the unrolled loop has no per-element
 // dispatch.
+// The bias of column n0 + lane, fetched by each lane ahead of the accumulator (0 when the
+// kernel has no bias or the column lies beyond N).
+__device__ __forceinline__ float chunk_bias(const Tf32Args& g, int n0, int lane) {
+  if (g.bias_len == 0) return 0.0f;
+  if (g.bias_len == 1) return __ldg(g.bias);
+  return n0 + lane < g.N ? __ldg(g.bias + n0 + lane) : 0.0f;
+}
+
 template <int ACT>
-__device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0) {
-  const bool full = n0 + 32 <= g.N;
-  if (g.bias_len == 1) {
-    const float b = __ldg(g.bias);
+__device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, float bj) {
+  if (g.bias_len != 0) {
+    // lane j holds the bias of column n0 + j; every thread owns a row of 32 columns
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], b);
-  } else if (g.bias_len > 1) {
-    if (full && (g.N & 3) == 0) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 b = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j);
-        v[4 * j] = __fadd_rn(v[4 * j], b.x);
-        v[4 * j + 1] = __fadd_rn(v[4 * j + 1], b.y);
-        v[4 * j + 2] = __fadd_rn(v[4 * j + 2], b.z);
-        v[4 * j + 3] = __fadd_rn(v[4 * j + 3], b.w);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        v[j] = __fadd_rn(v[j], __ldg(g.bias + (n0 + j < g.N ? n0 + j : 0)));
-    }
+    for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __shfl_sync(0xffffffffu, bj, j));
   }
   if (ACT == TFJS_CUDA_ACT_LINEAR) return;
 #pragma unroll
@@ -185,15 +177,16 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0) 
   }
 }
 
-__device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g, int n0) {
+__device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g, int n0,
+                                                    float bj) {
   switch (g.ap.act) {
-    case TFJS_CUDA_ACT_RELU: chunk_math<TFJS_CUDA_ACT_RELU>(v, g, n0); break;
-    case TFJS_CUDA_ACT_RELU6: chunk_math<TFJS_CUDA_ACT_RELU6>(v, g, n0); break;
-    case TFJS_CUDA_ACT_PRELU: chunk_math<TFJS_CUDA_ACT_PRELU>(v, g, n0); break;
-    case TFJS_CUDA_ACT_LEAKYRELU: chunk_math<TFJS_CUDA_ACT_LEAKYRELU>(v, g, n0); break;
-    case TFJS_CUDA_ACT_SIGMOID: chunk_math<TFJS_CUDA_ACT_SIGMOID>(v, g, n0); break;
-    case TFJS_CUDA_ACT_ELU: chunk_math<TFJS_CUDA_ACT_ELU>(v, g, n0); break;
-    default: chunk_math<TFJS_CUDA_ACT_LINEAR>(v, g, n0); break;
+    case TFJS_CUDA_ACT_RELU: chunk_math<TFJS_CUDA_ACT_RELU>(v, g, n0, bj); break;
+    case TFJS_CUDA_ACT_RELU6: chunk_math<TFJS_CUDA_ACT_RELU6>(v, g, n0, bj); break;
+    case TFJS_CUDA_ACT_PRELU: chunk_math<TFJS_CUDA_ACT_PRELU>(v, g, n0, bj); break;
+    case TFJS_CUDA_ACT_LEAKYRELU: chunk_math<TFJS_CUDA_ACT_LEAKYRELU>(v, g, n0, bj); break;
+    case TFJS_CUDA_ACT_SIGMOID: chunk_math<TFJS_CUDA_ACT_SIGMOID>(v, g, n0, bj); break;
+    case TFJS_CUDA_ACT_ELU: chunk_math<TFJS_CUDA_ACT_ELU>(v, g, n0, bj); break;
+    default: chunk_math<TFJS_CUDA_ACT_LINEAR>(v, g, n0, bj); break;
   }
 }
 
@@ -475,6 +468,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int acc = it % ACC;
       const uint32_t aphase = (it / ACC) & 1;
       if (BN == 32 && (it & 1) != half) continue;  // the other warp of the pair takes it
+      // the first chunk's bias travels while the tile's MMAs finish
+      float bj = chunk_bias(g, nt * BN + (BN == 32 ? 0 : half * 32), lane);
       if (!mbar_wait(tfull_bar(acc), aphase)) {
         if (lane == 0) atomicExch(g.flag, 4);
         // let the residual load in flight land before this CTA's shared memory goes
@@ -502,7 +497,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           if (lane == 0) mbar_arrive(tempty_bar(acc));
           released = true;
         }
-        chunk_math_dispatch(v, g, n0);
+        chunk_math_dispatch(v, g, n0, bj);
+        if (c0 + 64 < BN) bj = chunk_bias(g, n0 + 64, lane);  // next chunk's, ahead of its use
         const uint32_t stage_buf = stage_base + ebuf * 4096u;
         const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
         if (RES) {
