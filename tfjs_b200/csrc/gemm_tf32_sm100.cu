@@ -438,6 +438,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     uint32_t rphase = 0;       // bit b: parity the next wait on res_bar(b) uses
     bool res_issued = false;   // a load into the current staging tile is in flight
     auto prefetch_residual = [&](uint32_t b) -> bool {
+      if (!g.residual) return false;  // this instantiation also serves as the two-buffer epilogue
       while (p_tile < g.total_tiles) {
         const int n0 = (p_tile % g.tiles_n) * BN + p_c0;
         if (!(BN == 32 && (p_it & 1) != half) && p_c0 < BN && n0 < g.N) {
