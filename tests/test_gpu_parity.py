@@ -271,7 +271,12 @@ def test_leakyrelu_clip(cuda_engine):
 
 
 BIN_SHAPES = [((4, 56, 56, 64), (4, 56, 56, 64)), ((8, 49, 320), (320,)), ((320,), (8, 49, 320)),
-              ((7, 5, 3), (1,)), ((3, 1, 5), (1, 4, 1)), ((2, 3, 4, 5), (4, 1)), ((6,), ())]
+              ((7, 5, 3), (1,)), ((3, 1, 5), (1, 4, 1)), ((2, 3, 4, 5), (4, 1)), ((6,), ()),
+              # attention mask against scores: equal on the outer and inner axes, 1 in between
+              ((4, 12, 128, 128), (4, 1, 1, 128)), ((3, 1, 1, 64), (3, 5, 7, 64)),
+              ((2, 6, 8), (2, 1, 8)), ((5, 3, 2, 4, 12), (5, 3, 1, 1, 12)),
+              # periods that do not divide the grid stride
+              ((1000, 772), (772,)), ((33, 7, 20), (7, 20))]
 
 
 @pytest.mark.parametrize("op", ["add", "sub", "mul", "div", "maximum", "minimum",

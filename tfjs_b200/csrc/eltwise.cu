@@ -191,26 +191,54 @@ __global__ void binary_periodic_kernel(const float* __restrict__ full,
   const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
   const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const float4* f4 = reinterpret_cast<const float4*>(full);
+  const float4* p4 = reinterpret_cast<const float4*>(per);
   float4* o4 = reinterpret_cast<float4*>(o);
   const float s = per[0];
+  // position inside the period in float4 units, advanced without a division per element
+  const uint32_t per4 = period == 1 ? 1u : period >> 2;
+  const uint32_t step = (uint32_t)(stride % per4);
+  uint32_t r = (uint32_t)(tid % per4);
   for (uint64_t i = tid; i < n4; i += stride) {
     const float4 u = f4[i];
-    float4 v;
-    if (period == 1) {
-      v = make_float4(s, s, s, s);
-    } else {
-      v = *reinterpret_cast<const float4*>(per + ((i << 2) % period));
-    }
-    float4 r;
-    r.x = SWAP ? binary_eval<OP>(v.x, u.x) : binary_eval<OP>(u.x, v.x);
-    r.y = SWAP ? binary_eval<OP>(v.y, u.y) : binary_eval<OP>(u.y, v.y);
-    r.z = SWAP ? binary_eval<OP>(v.z, u.z) : binary_eval<OP>(u.z, v.z);
-    r.w = SWAP ? binary_eval<OP>(v.w, u.w) : binary_eval<OP>(u.w, v.w);
-    o4[i] = r;
+    const float4 v = period == 1 ? make_float4(s, s, s, s) : __ldg(p4 + r);
+    r += step;
+    if (r >= per4) r -= per4;
+    float4 q;
+    q.x = SWAP ? binary_eval<OP>(v.x, u.x) : binary_eval<OP>(u.x, v.x);
+    q.y = SWAP ? binary_eval<OP>(v.y, u.y) : binary_eval<OP>(u.y, v.y);
+    q.z = SWAP ? binary_eval<OP>(v.z, u.z) : binary_eval<OP>(u.z, v.z);
+    q.w = SWAP ? binary_eval<OP>(v.w, u.w) : binary_eval<OP>(u.w, v.w);
+    o4[i] = q;
   }
   for (uint64_t i = (n4 << 2) + tid; i < n; i += stride) {
     const float v = per[period == 1 ? 0 : i % period];
     o[i] = SWAP ? binary_eval<OP>(v, full[i]) : binary_eval<OP>(full[i], v);
+  }
+}
+
+// out[o][m][i] = full[o][m][i] op small[o][i]: the small operand equals the output shape on
+// a leading and a trailing group of axes and is 1 in between (an attention mask
+// [B,1,1,S] against scores [B,H,S,S]).  inner % 4 == 0; sizes in float4 units fit 32 bits.
+template <int OP, bool SWAP>
+__global__ void binary_batched_periodic_kernel(const float* __restrict__ full,
+                                               const float* __restrict__ small_op,
+                                               float* __restrict__ o, uint32_t n4,
+                                               uint32_t inner4, uint32_t mid_inner4) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  const float4* f4 = reinterpret_cast<const float4*>(full);
+  const float4* s4 = reinterpret_cast<const float4*>(small_op);
+  float4* o4 = reinterpret_cast<float4*>(o);
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const uint32_t outer = i / mid_inner4;
+    const uint32_t in4 = (i - outer * mid_inner4) % inner4;
+    const float4 u = f4[i];
+    const float4 v = __ldg(s4 + outer * inner4 + in4);
+    float4 q;
+    q.x = SWAP ? binary_eval<OP>(v.x, u.x) : binary_eval<OP>(u.x, v.x);
+    q.y = SWAP ? binary_eval<OP>(v.y, u.y) : binary_eval<OP>(u.y, v.y);
+    q.z = SWAP ? binary_eval<OP>(v.z, u.z) : binary_eval<OP>(u.z, v.z);
+    q.w = SWAP ? binary_eval<OP>(v.w, u.w) : binary_eval<OP>(u.w, v.w);
+    o4[i] = q;
   }
 }
 
@@ -510,7 +538,7 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
   cudaSetDevice(ctx->device);
   // Classify: same-size, or one side periodic over a suffix of the out shape.
   int mode = 2;  // general
-  uint32_t period = 0;
+  uint32_t period = 0, bp_inner4 = 0, bp_mid_inner4 = 0;
   bool swap = false;
   if (dtype == TFJS_CUDA_FLOAT32) {
     auto suffix_period = [&](const int64_t* s, uint64_t cnt) -> bool {
@@ -530,11 +558,34 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
         if (s[e] != out_shape[e]) return false;
       return cnt * (uint64_t)out_shape[rank - 1] == n;
     };
+    auto batched_period = [&](const int64_t* sh) -> bool {
+      // equal to out_shape on axes [0, p) and [q, rank), 1 on [p, q), with 0 < p < q < rank
+      int p = 0;
+      while (p < rank && sh[p] == out_shape[p]) ++p;
+      int q = p;
+      while (q < rank && sh[q] == 1) ++q;
+      if (p == 0 || q == p || q == rank) return false;
+      uint64_t inner = 1, mid = 1;
+      for (int e = q; e < rank; ++e) {
+        if (sh[e] != out_shape[e]) return false;
+        inner *= (uint64_t)out_shape[e];
+      }
+      for (int e = p; e < q; ++e) mid *= (uint64_t)out_shape[e];
+      if (inner % 4 != 0 || mid < 2 || n / 4 > 0xffffffffull) return false;
+      bp_inner4 = (uint32_t)(inner / 4);
+      bp_mid_inner4 = (uint32_t)(mid * inner / 4);
+      return true;
+    };
     if (na == n && nb == n) mode = 0;
     else if (na == n && nb > 1 && row_scalar(b_shape, nb)) {
       mode = 3; period = (uint32_t)out_shape[rank - 1]; swap = false;
     } else if (nb == n && na > 1 && row_scalar(a_shape, na)) {
       mode = 3; period = (uint32_t)out_shape[rank - 1]; swap = true;
+    }
+    else if (na == n && nb > 1 && batched_period(b_shape)) {
+      mode = 4; swap = false;
+    } else if (nb == n && na > 1 && batched_period(a_shape)) {
+      mode = 4; swap = true;
     }
     else if (na == n && suffix_period(b_shape, nb) && (nb == 1 || nb % 4 == 0)) {
       mode = 1; period = (uint32_t)nb; swap = false;
@@ -559,6 +610,14 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
       binary_periodic_kernel<OP, true>                                            \
           <<<grid_for((n + 3) / 4, kThreads, ctx->sm_count), kThreads, 0,         \
              ctx->stream>>>(bp, ap, op_, n, period);                              \
+    else if (mode == 4 && !swap)                                                  \
+      binary_batched_periodic_kernel<OP, false>                                   \
+          <<<grid_for(n / 4, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>( \
+              ap, bp, op_, (uint32_t)(n / 4), bp_inner4, bp_mid_inner4);           \
+    else if (mode == 4)                                                           \
+      binary_batched_periodic_kernel<OP, true>                                    \
+          <<<grid_for(n / 4, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>( \
+              bp, ap, op_, (uint32_t)(n / 4), bp_inner4, bp_mid_inner4);           \
     else if (mode == 3)                                                           \
       binary_rowscalar_kernel<OP><<<grid_for((n + 3) / 4, kThreads, ctx->sm_count), \
                                     kThreads, 0, ctx->stream>>>(                  \
