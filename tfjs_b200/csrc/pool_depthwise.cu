@@ -321,11 +321,18 @@ depthwise3x3_tma_kernel(const __grid_constant__ CUtensorMap tm_x, const float* _
     decode(item, n, th, tw, cc);
     const int c = cc * 32 + c4 * 4;
     const bool c_ok = c < g.c;
-    float4 wv[9];
+    // Arithmetic on packed pairs (fma.rn.f32x2: two independent fp32 FMAs per
+    // instruction, each rounded like the scalar one): a float4 of channels is two
+    // 64-bit registers.
+    unsigned long long wv[9][2];
     float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c_ok) {
 #pragma unroll
-      for (int k = 0; k < 9; ++k) wv[k] = __ldg(reinterpret_cast<const float4*>(w + k * g.c + c));
+      for (int k = 0; k < 9; ++k) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(w + k * g.c + c));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(wv[k][0]) : "f"(t.x), "f"(t.y));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(wv[k][1]) : "f"(t.z), "f"(t.w));
+      }
       if (bias_len == 1) {
         const float b0 = __ldg(bias);
         bv = make_float4(b0, b0, b0, b0);
@@ -344,29 +351,27 @@ depthwise3x3_tma_kernel(const __grid_constant__ CUtensorMap tm_x, const float* _
     const int oh = th * T::TH + sr;
     const int ow0 = tw * T::TW + sc;
     if (c_ok && oh < g.out_h && ow0 < g.out_w) {
-      float4 acc[T::S];
+      unsigned long long acc[T::S][2];
 #pragma unroll
-      for (int s = 0; s < T::S; ++s) acc[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < T::S; ++s) acc[s][0] = acc[s][1] = 0ull;
       const uint32_t tile = base + buf * T::BUF_BYTES + (uint32_t)c4 * 16u;
 #pragma unroll
       for (int fr = 0; fr < 3; ++fr) {
         const uint32_t row = tile + (uint32_t)((sr * STRIDE + fr) * T::IW + sc * STRIDE) * 128u;
-        float4 xin[NC];
+        unsigned long long xin[NC][2];
 #pragma unroll
         for (int i = 0; i < NC; ++i)
-          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                       : "=f"(xin[i].x), "=f"(xin[i].y), "=f"(xin[i].z), "=f"(xin[i].w)
+          asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];"
+                       : "=l"(xin[i][0]), "=l"(xin[i][1])
                        : "r"(row + (uint32_t)i * 128u));
 #pragma unroll
         for (int s = 0; s < T::S; ++s) {
 #pragma unroll
           for (int fc = 0; fc < 3; ++fc) {
-            const float4 xv = xin[s * STRIDE + fc];
-            const float4 wk = wv[fr * 3 + fc];
-            acc[s].x = fmaf(xv.x, wk.x, acc[s].x);
-            acc[s].y = fmaf(xv.y, wk.y, acc[s].y);
-            acc[s].z = fmaf(xv.z, wk.z, acc[s].z);
-            acc[s].w = fmaf(xv.w, wk.w, acc[s].w);
+            asm("fma.rn.f32x2 %0, %1, %2, %0;"
+                : "+l"(acc[s][0]) : "l"(xin[s * STRIDE + fc][0]), "l"(wv[fr * 3 + fc][0]));
+            asm("fma.rn.f32x2 %0, %1, %2, %0;"
+                : "+l"(acc[s][1]) : "l"(xin[s * STRIDE + fc][1]), "l"(wv[fr * 3 + fc][1]));
           }
         }
       }
@@ -374,14 +379,22 @@ depthwise3x3_tma_kernel(const __grid_constant__ CUtensorMap tm_x, const float* _
 #pragma unroll
       for (int s = 0; s < T::S; ++s) {
         if (ow0 + s >= g.out_w) break;
-        float o[4] = {acc[s].x, acc[s].y, acc[s].z, acc[s].w};
+        float o[4];
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(o[0]), "=f"(o[1]) : "l"(acc[s][0]));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(o[2]), "=f"(o[3]) : "l"(acc[s][1]));
         const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           float v = bias_len ? __fadd_rn(o[k], bb[k]) : o[k];
-          if (ACT == TFJS_CUDA_ACT_RELU) v = v != v ? v : fmaxf(v, 0.0f);
-          else if (ACT == TFJS_CUDA_ACT_RELU6) v = v != v ? v : fminf(fmaxf(v, 0.0f), 6.0f);
-          else if (ACT != TFJS_CUDA_ACT_LINEAR) v = apply_act(v, ap, c + k);
+          // max.NaN / min.NaN keep a NaN input, as Math.max / Math.min do
+          if (ACT == TFJS_CUDA_ACT_RELU) {
+            asm("max.NaN.f32 %0, %0, 0f00000000;" : "+f"(v));
+          } else if (ACT == TFJS_CUDA_ACT_RELU6) {
+            asm("max.NaN.f32 %0, %0, 0f00000000;" : "+f"(v));
+            asm("min.NaN.f32 %0, %0, 0f40C00000;" : "+f"(v));
+          } else if (ACT != TFJS_CUDA_ACT_LINEAR) {
+            v = apply_act(v, ap, c + k);
+          }
           o[k] = v;
         }
         *reinterpret_cast<float4*>(yrow + (size_t)s * g.c) = make_float4(o[0], o[1], o[2], o[3]);

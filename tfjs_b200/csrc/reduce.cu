@@ -100,14 +100,25 @@ __global__ void reduce_rows_kernel(const float* __restrict__ x,
     float mx = xr[0];
     if ((reduce & 3) == 0 && ((uintptr_t)x & 15) == 0) {
       const float4* x4 = reinterpret_cast<const float4*>(xr);
-      for (uint32_t j = lane; j < (uint32_t)(reduce >> 2); j += 32) {
-        const float4 q = x4[j];
-        const float e[4] = {q.x, q.y, q.z, q.w};
+      const uint32_t n4 = (uint32_t)(reduce >> 2);
+      // eight 16-byte loads in flight per lane (1024 floats of the row per round)
+      for (uint32_t j0 = 0; j0 < n4; j0 += 256) {
+        float4 q[8];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (OP == 0) acc += (double)e[k];
-          else if (OP == 1) acc += (double)__fdiv_rn(e[k], nf);
-          else mx = nan_max(mx, e[k]);
+        for (int u = 0; u < 8; ++u) {
+          const uint32_t j = j0 + u * 32 + lane;
+          q[u] = j < n4 ? __ldg(x4 + j) : make_float4(xr[0], xr[0], xr[0], xr[0]);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (j0 + u * 32 + lane >= n4) continue;
+          const float e[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (OP == 0) acc += (double)e[k];
+            else if (OP == 1) acc += (double)__fdiv_rn(e[k], nf);
+            else mx = nan_max(mx, e[k]);
+          }
         }
       }
     } else {
