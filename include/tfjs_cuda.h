@@ -347,6 +347,12 @@ int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_dtype_bytes,
                          int32_t to_dtype, int32_t q_id, double scale,
                          double min, uint64_t n, int32_t out_id);
 
+/* Weights stored as float16 ('float16' quantization of a float32 weight,
+ * tfjs-core/src/io/io_utils.ts:228-231, decoder :720-741): exact widening of n half-precision
+ * values (raw uint16 bits in q) to float32, on the device, so such weights cross PCIe at two
+ * bytes per value. */
+int tfjs_cuda_decode_float16(tfjs_cuda_ctx* ctx, int32_t q_id, uint64_t n, int32_t out_id);
+
 /* ---- tfjs_cuda_dequantize for callers that must not allocate device memory.
  * No counterpart in the reference; it exists for hosts that load weights while
  * device allocation is off limits -- for example an embedding application that

@@ -422,3 +422,32 @@ def dequantize(q, scale, min_val, dtype="float32"):
     fn(_ptr(q), is_u16, ctypes.c_double(scale), ctypes.c_double(min_val),
        _ptr(out), ctypes.c_long(q.size))
     return out
+
+
+def decode_float16(q):
+    """tfjs-core/src/io/io_utils.ts:720-741 (getFloat16Decoder) with the tables of
+    :645-713: the table method of van der Zijp, "Fast Half Float Conversions" - a 2048-entry
+    mantissa table (entries 1..1023 are the normalised subnormals, 1024..2047 the plain
+    mantissas), a 64-entry exponent table and a 64-entry offset table indexed by the
+    sign+exponent bits.  Returns float32 of the same shape as the uint16 input."""
+    q = np.ascontiguousarray(q).view(np.uint16)
+    mant = np.zeros(2048, np.uint64)
+    for i in range(1, 1024):
+        m, e = i << 13, 0
+        while not (m & 0x00800000):
+            e -= 0x00800000
+            m <<= 1
+        mant[i] = ((m & ~0x00800000) | ((e + 0x38800000) & 0xffffffff)) & 0xffffffff
+    for i in range(1024, 2048):
+        mant[i] = 0x38000000 + ((i - 1024) << 13)
+    expo = np.zeros(64, np.uint64)
+    expo[31], expo[32], expo[63] = 0x47800000, 0x80000000, 0xc7800000
+    for i in range(1, 31):
+        expo[i] = i << 23
+    for i in range(33, 63):
+        expo[i] = 0x80000000 + ((i - 32) << 23)
+    off = np.full(64, 1024, np.int64)
+    off[0] = off[32] = 0
+    hi = (q >> 10).astype(np.int64)
+    bits = (mant[off[hi] + (q & 0x3ff).astype(np.int64)] + expo[hi]) & 0xffffffff
+    return bits.astype(np.uint32).view(np.float32).reshape(q.shape)

@@ -493,3 +493,26 @@ def test_overlapped_upload(cuda_engine):
     did = b.write_from(big, big.shape, "float32")
     assert b.disposeData(did) is True
     b.sync()
+
+
+def test_float16_weights_decode_on_device_bit_exact(cuda_engine):
+    """Every half-precision bit pattern (NaN payloads included) and a ragged length,
+    through decode_weights with a 'float16' quantised manifest entry."""
+    from tfjs_b200 import io
+    every = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    r = rng(77)
+    ragged = r.integers(0, 65536, 1003).astype(np.uint16)
+    specs = [{"name": "every", "dtype": "float32", "shape": [256, 256],
+              "quantization": {"dtype": "float16"}},
+             {"name": "ragged", "dtype": "float32", "shape": [1003],
+              "quantization": {"dtype": "float16"}},
+             {"name": "empty", "dtype": "float32", "shape": [0],
+              "quantization": {"dtype": "float16"}}]
+    tensors = io.decode_weights(cuda_engine, every.tobytes() + ragged.tobytes(), specs)
+    for name, src in (("every", every), ("ragged", ragged)):
+        got = tensors[name].dataSync()
+        ref = orc.decode_float16(src)
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), name
+    assert tensors["empty"].shape == [0]
+    for t in tensors.values():
+        t.dispose()

@@ -79,3 +79,29 @@ def test_js_numerics_details():
     assert orc.pool2d(x, "avg", 2, 1, "same")[0, 2, 2, 0] == 8.0
     with pytest.raises(ValueError):
         orc.gather(np.zeros((3, 2), np.float32), np.array([3], np.int32))
+
+
+def test_float16_decoder_known_answers_and_every_bit_pattern():
+    """io_utils_test.ts:601-616 and :711-778 (NaN, infinities, signed zeros, 0.25 / 0.5 /
+    0.75 / 0.333), then all 65536 patterns against numpy's IEEE widening."""
+    f = orc.decode_float16(np.array([13312, 14336, 14848], np.uint16))
+    assert np.array_equal(f, np.float32([0.25, 0.5, 0.75]))
+    assert np.isnan(orc.decode_float16(np.array([0x7e00], np.uint16))[0])
+    inf = orc.decode_float16(np.array([0x7c00, 0xfc00], np.uint16))
+    assert inf[0] == np.inf and inf[1] == -np.inf
+    z = orc.decode_float16(np.array([0x0000, 0x8000], np.uint16))
+    assert np.array_equal(z.view(np.uint32), np.array([0, 0x80000000], np.uint32))
+    assert orc.decode_float16(np.array([0xfbff + 1], np.uint16))[0] == -np.inf
+    assert orc.decode_float16(np.array([0x7bff + 1], np.uint16))[0] == np.inf
+    v = orc.decode_float16(np.array([0x3400, 0x3800, 0x3a00, 0x3555], np.uint16))
+    assert np.allclose(v, [0.25, 0.5, 0.75, 0.333], atol=5e-3)
+    every = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    got = orc.decode_float16(every)
+    want = every.view(np.float16).astype(np.float32)
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got), nan)
+    assert np.array_equal(got[~nan].view(np.uint32), want[~nan].view(np.uint32))
+    # a NaN keeps its payload in the upper mantissa bits
+    m = (every[nan].astype(np.uint32) & 0x3ff) << 13
+    s = (every[nan].astype(np.uint32) & 0x8000) << 16
+    assert np.array_equal(got[nan].view(np.uint32), s | 0x7f800000 | m)

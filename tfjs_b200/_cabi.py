@@ -69,6 +69,7 @@ SIGNATURES = {
     "tfjs_cuda_launch_count": (c_int, [_CTX, POINTER(c_uint64)]),
     "tfjs_cuda_flush_l2": (c_int, [_CTX]),
     "tfjs_cuda_fused_conv2d": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 5),
+    "tfjs_cuda_decode_float16": (c_int, [_CTX, c_int32, c_uint64, c_int32]),
     "tfjs_cuda_capture_begin": (c_int, [_CTX, c_uint64]),
     "tfjs_cuda_capture_end": (c_int, [_CTX, c_int, POINTER(c_int32)]),
     "tfjs_cuda_graph_launch": (c_int, [_CTX, c_int32]),

@@ -1019,6 +1019,65 @@ int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_dtype,
   return TFJS_CUDA_OK;
 }
 
+// ---- float16-stored weights: exact widening to float32 ------------------------------
+// tfjs-core/src/io/io_utils.ts:228-231 decodes 'float16' quantised weights with the
+// table method of van der Zijp ("Fast Half Float Conversions"), which is the exact IEEE
+// widening: subnormals are normalised, infinities stay, a NaN keeps its payload in the
+// upper mantissa bits.  Done here with integer arithmetic, eight values per thread.
+__device__ __forceinline__ uint32_t half_bits_to_float_bits(uint32_t h) {
+  const uint32_t sign = (h & 0x8000u) << 16;
+  const uint32_t e = (h >> 10) & 31u;
+  uint32_t m = h & 0x3ffu;
+  if (e == 0) {
+    if (m == 0) return sign;
+    const int shift = __clz(m) - 21;  // bring the leading one to bit 10
+    m = (m << shift) & 0x3ffu;
+    return sign | ((uint32_t)(113 - shift) << 23) | (m << 13);
+  }
+  if (e == 31) return sign | 0x7f800000u | (m << 13);
+  return sign | ((e + 112u) << 23) | (m << 13);
+}
+
+__global__ void decode_f16_kernel(const uint16_t* __restrict__ q, uint32_t* __restrict__ o,
+                                  uint64_t n) {
+  const uint64_t n8 = n >> 3;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint4* q8 = reinterpret_cast<const uint4*>(q);
+  uint4* o4 = reinterpret_cast<uint4*>(o);
+  for (uint64_t i = tid; i < n8; i += stride) {
+    const uint4 v = __ldg(q8 + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t r[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      r[2 * k] = half_bits_to_float_bits(w[k] & 0xffffu);
+      r[2 * k + 1] = half_bits_to_float_bits(w[k] >> 16);
+    }
+    o4[2 * i] = make_uint4(r[0], r[1], r[2], r[3]);
+    o4[2 * i + 1] = make_uint4(r[4], r[5], r[6], r[7]);
+  }
+  for (uint64_t i = (n8 << 3) + tid; i < n; i += stride) o[i] = half_bits_to_float_bits(q[i]);
+}
+
+int tfjs_cuda_decode_float16(tfjs_cuda_ctx* ctx, int32_t q_id, uint64_t n, int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  Buffer *q, *o;
+  int rc;
+  if ((rc = ctx_get(ctx, q_id, n * 2, "decode_float16 q", &q))) return rc;
+  if ((rc = ctx_get(ctx, out_id, n * 4, "decode_float16 out", &o))) return rc;
+  if (n == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  decode_f16_kernel<<<grid_for((n + 7) / 8, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+      (const uint16_t*)q->ptr, (uint32_t*)o->ptr, n);
+  LAUNCH_CHECK(ctx, "decode_f16_kernel");
+  Buffer* ob = ctx_buf(ctx, out_id);
+  ob->version++;
+  ob->from_host = true;  // decoded weights are constants
+  ctx_drop_packed(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
 // ---- dequantisation without any allocation --------------------------------------
 // The lookup table lives in a fixed device array instead of a pool allocation.
 // 65536 entries cover the widest quantised type (uint16); 256 KiB per GPU, held

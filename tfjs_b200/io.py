@@ -53,6 +53,28 @@ def dequantize_to_device(backend, q, scale, min_val, shape, dtype):
     return out
 
 
+def decode_float16_to_device(backend, q, shape):
+    """Upload raw float16 bits (uint16) and widen them to float32 on the device
+    (io_utils.ts:228-231 with the decoder of :720-741)."""
+    q = np.ascontiguousarray(q).view(np.uint16).reshape(-1)
+    n = int(q.size)
+    out = backend.make_output(shape, "float32")
+    if n == 0:
+        return out
+    qid = backend._alloc(n * 2)
+    try:
+        backend.check(backend.lib.tfjs_cuda_write(backend.ctx, qid, q.ctypes.data_as(c_void_p),
+                                                  n * 2))
+        backend.check(backend.lib.tfjs_cuda_decode_float16(backend.ctx, qid, n,
+                                                           backend.device_id(out.dataId)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    finally:
+        backend.check(backend.lib.tfjs_cuda_free(backend.ctx, qid))
+    return out
+
+
 def decode_weights(engine, weight_data, specs):
     """name -> Tensor for every manifest entry, in manifest order
     (io_utils.ts:119-135).  `weight_data` is the concatenated little-endian
@@ -82,7 +104,9 @@ def decode_weights(engine, weight_data, specs):
             raw = np.frombuffer(buf[offset:offset + nbytes], dtype=np.dtype(qd))
             offset += nbytes
             if qd == "float16":
-                t = engine.make_tensor(raw.astype(np.float32), shape, "float32")
+                engine.ready()
+                t = engine.make_tensor_from_info(decode_float16_to_device(engine.backend, raw,
+                                                                          shape))
             else:
                 if dtype not in ("float32", "int32"):
                     raise ValueError("Unsupported dtype in weight '%s': %s" % (name, dtype))

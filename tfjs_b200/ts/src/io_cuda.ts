@@ -36,8 +36,18 @@ function decodeWeights(weightData: io.WeightData, specs: io.WeightsManifestEntry
       binding.free(backend.ctx, qId);
       out[spec.name] = engine().makeTensorFromTensorInfo(info) as Tensor;
       offset += nbytes;
+    } else if (q != null && q.dtype === 'float16' && spec.dtype === 'float32') {
+      // half-precision storage: upload the raw bits, widen on the device
+      const nbytes = size * 2;
+      const qId = binding.alloc(backend.ctx, nbytes);
+      binding.write(backend.ctx, qId, new Uint8Array(buffer, offset, nbytes), nbytes);
+      const info = backend.makeOutput(spec.shape, 'float32');
+      binding.decodeFloat16(backend.ctx, qId, size, backend.deviceId(info));
+      binding.free(backend.ctx, qId);
+      out[spec.name] = engine().makeTensorFromTensorInfo(info) as Tensor;
+      offset += nbytes;
     } else {
-      // float16 and unquantised entries: the stock decoder, one entry at a time
+      // unquantised entries: the stock decoder, one entry at a time
       const bytes = size * (q != null ? 2 : (spec.dtype === 'bool' ? 1 : 4));
       Object.assign(out, io.decodeWeights(buffer.slice(offset, offset + bytes), [spec]));
       offset += bytes;
