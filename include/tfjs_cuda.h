@@ -274,6 +274,59 @@ enum tfjs_cuda_unary_op {
 int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int32_t op, double p0, double p1,
                     int32_t x_id, uint64_t n, int32_t out_id);
 
+/* ---- chains of elementwise kernels in one pass ---------------------------------------
+ * A program is a short list of the unary / binary kernels above applied to float32 values:
+ * the graph models decompose LayerNorm, GELU and scaling into such chains (e.g.
+ * Mul, Erf, Add, Mul, Mul), each of which the reference runs as one pass over memory
+ * (unary_impl.ts:25-36, binary_impl.ts:25-69).  The fused kernel reads every input once,
+ * evaluates the ops per element in order, rounding every intermediate result to fp32
+ * exactly like the separate kernels, and writes the last result: same bits, one pass.
+ *
+ * Value slots: 0 .. n_inputs-1 are the inputs, n_inputs + j is the result of op j.  Each
+ * input is addressed relative to the OUTPUT's flat index i (cols = the output's innermost
+ * extent): FULL in[i]; PERIODIC in[i % period] (a trailing-axes broadcast such as a bias);
+ * ROW in[i / cols] (shape = output shape with the last axis 1); SCALAR in[0]; BATCHED
+ * in[(i / aux) * period + i % period] (equal to the output on leading and trailing axes, 1 in
+ * between: period = product of the trailing axes, aux = period * product of the middle ones).
+ * binary ops use opcode = tfjs_cuda_binary_op, unary ops opcode = 32 + tfjs_cuda_unary_op
+ * with operand a only and parameters p0, p1. */
+enum tfjs_cuda_ew_input_mode {
+  TFJS_CUDA_EW_FULL = 0,
+  TFJS_CUDA_EW_PERIODIC = 1,
+  TFJS_CUDA_EW_ROW = 2,
+  TFJS_CUDA_EW_SCALAR = 3,
+  TFJS_CUDA_EW_BATCHED = 4
+};
+#define TFJS_CUDA_EW_MAX_INPUTS 8
+#define TFJS_CUDA_EW_MAX_OPS 24
+#define TFJS_CUDA_EW_UNARY 32
+typedef struct tfjs_cuda_ew_op {
+  int16_t opcode;
+  uint8_t a, b; /* value slots */
+  float p0, p1;
+} tfjs_cuda_ew_op;
+typedef struct tfjs_cuda_ew_program {
+  int32_t n_inputs, n_ops;
+  uint64_t n;    /* output elements */
+  uint32_t cols; /* output's innermost extent (ROW inputs), >= 1 */
+  uint32_t reserved;
+  int32_t input_id[TFJS_CUDA_EW_MAX_INPUTS];
+  int32_t input_mode[TFJS_CUDA_EW_MAX_INPUTS];
+  uint32_t input_period[TFJS_CUDA_EW_MAX_INPUTS]; /* PERIODIC: elements of the input */
+  uint32_t input_aux[TFJS_CUDA_EW_MAX_INPUTS];    /* BATCHED: see above */
+  tfjs_cuda_ew_op ops[TFJS_CUDA_EW_MAX_OPS];
+} tfjs_cuda_ew_program;
+int tfjs_cuda_fused_elementwise(tfjs_cuda_ctx* ctx, const tfjs_cuda_ew_program* prog,
+                                int32_t out_id);
+/* The library carries straight-line kernels for the chains graph models contain (LayerNorm
+ * tail in its two usual decompositions, erf-GELU, x * a + b, a + b + c); any other program
+ * runs through an interpreter kernel that is slower than the separate kernels for short
+ * chains.  *out_yes = 1 when `prog` (ops and operand slots; sizes and ids are ignored)
+ * matches a catalogued chain, so a host layer can keep launching the separate kernels
+ * otherwise. */
+int tfjs_cuda_fused_elementwise_catalogued(tfjs_cuda_ctx* ctx, const tfjs_cuda_ew_program* prog,
+                                           int32_t* out_yes);
+
 /* ---- Softmax over the last axis: tfjs-backend-cpu/src/kernels/Softmax.ts:29-77. */
 int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
                       uint64_t cols, int32_t out_id);

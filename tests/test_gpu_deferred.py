@@ -248,6 +248,7 @@ def test_profile_names_folded_launches(cuda_engine):
         r = tf.relu(s)
         y2 = tf.fused_conv2d(xt, ft, 1, "same", bias=bt)
         m = tf.mul(y2, sc)
+        m.dataSync()                  # launches the convolution, then the multiply
         for t in (y, s, y2):
             t.dispose()
         return r, m
@@ -319,3 +320,135 @@ def test_async_read_overlaps_later_launches(cuda_engine):
     assert rc == 1
     for t in (at, y, z, z2, small):
         t.dispose()
+
+
+# ------------------------------------------------------ elementwise chains --
+def _chain_cases():
+    r = np.random.default_rng(5)
+    R, C = 96, 772
+    x = r.standard_normal((R, C)).astype(np.float32)
+    mean = r.standard_normal((R, 1)).astype(np.float32)
+    var = (r.random((R, 1)) + 0.1).astype(np.float32)
+    gamma = r.standard_normal(C).astype(np.float32)
+    beta = r.standard_normal(C).astype(np.float32)
+    eps = np.float32(1e-12)
+
+    def layer_norm_tail(tf, t):
+        # the graph models' decomposed LayerNorm after the two Mean kernels
+        inv = tf.rsqrt(tf.add(t["var"], t["eps"]))
+        scale = tf.mul(inv, t["gamma"])
+        return tf.add(tf.mul(t["x"], scale), tf.sub(t["beta"], tf.mul(t["mean"], scale)))
+
+    def layer_norm_tail_simple(tf, t):
+        # ((x - mean) * rstd) * gamma + beta, the form the converter leaves for tf.nn.moments
+        norm = tf.mul(tf.sub(t["x"], t["mean"]), t["var"])
+        return tf.add(tf.mul(norm, t["gamma"]), t["beta"])
+
+    def gelu(tf, t):
+        inner = tf.add(tf.erf(tf.mul(t["x"], t["c"])), t["one"])
+        return tf.mul(tf.mul(t["x"], t["half"]), inner)
+
+    def masked_scores(tf, t):
+        return tf.add(tf.mul(t["s"], t["scale"]), t["mask"])
+
+    def ragged(tf, t):        # sizes that are no multiples of 4: the scalar kernel
+        return tf.relu(tf.sub(tf.square(t["p"]), tf.maximum(t["q"], t["row"])))
+
+    def general_broadcast(tf, t):   # [3,1,5] op [1,4,1]: no addressing mode fits
+        return tf.tanh(tf.add(tf.mul(t["u"], t["v"]), t["u"]))
+
+    def long_chain(tf, t):    # more ops than one program holds
+        y = t["x"]
+        for i in range(40):
+            y = tf.add(tf.mul(y, t["half"]), t["gamma"]) if i % 2 else tf.sub(y, t["beta"])
+        return y
+
+    def reused(tf, t):        # an intermediate with two consumers
+        a = tf.exp(tf.mul(t["x"], t["half"]))
+        return tf.div(tf.sub(a, t["one"]), tf.add(a, t["one"]))
+
+    return {
+        "layer_norm_tail": (layer_norm_tail, dict(x=x, mean=mean, var=var, gamma=gamma,
+                                                  beta=beta, eps=eps)),
+        "layer_norm_tail_simple": (layer_norm_tail_simple, dict(x=x, mean=mean, var=var,
+                                                                gamma=gamma, beta=beta)),
+        "gelu": (gelu, dict(x=x, c=np.float32(0.7071067811865476), one=np.float32(1),
+                            half=np.float32(0.5))),
+        "masked_scores": (masked_scores, dict(
+            s=r.standard_normal((3, 4, 16, 32)).astype(np.float32), scale=np.float32(0.125),
+            mask=r.standard_normal((3, 1, 1, 32)).astype(np.float32))),
+        "ragged": (ragged, dict(p=r.standard_normal((7, 13)).astype(np.float32),
+                                q=r.standard_normal((7, 13)).astype(np.float32),
+                                row=r.standard_normal((7, 1)).astype(np.float32))),
+        "general_broadcast": (general_broadcast, dict(
+            u=r.standard_normal((3, 1, 5)).astype(np.float32),
+            v=r.standard_normal((1, 4, 1)).astype(np.float32))),
+        "long_chain": (long_chain, dict(x=x, half=np.float32(0.5), gamma=gamma, beta=beta)),
+        "reused": (reused, dict(x=x, half=np.float32(0.5), one=np.float32(1))),
+    }
+
+
+class _OracleOps(object):
+    """The op front ends evaluated by the CPU oracle on numpy arrays."""
+    def __getattr__(self, name):
+        binary = {"add": "add", "sub": "sub", "mul": "mul", "div": "div", "maximum": "maximum"}
+        if name in binary:
+            return lambda a, b: orc.binary(binary[name], a, b)
+        return lambda a: orc.unary(name, a)
+
+
+@pytest.mark.parametrize("name", sorted(_chain_cases()))
+def test_elementwise_chain_matches_separate_kernels_and_oracle(cuda_engine, name):
+    from tfjs_b200 import ops as tf
+    fn, arrays = _chain_cases()[name]
+    backend = cuda_engine.backend
+    outs, launches = {}, {}
+    for lazy in (True, False):
+        backend.lazy_fusion = lazy
+        try:
+            tensors = {k: tf.tensor(v) for k, v in arrays.items()}
+            before_t = cuda_engine.memory()["numTensors"]
+            n0 = backend.launch_count()
+            y = fn(tf, tensors)
+            outs[lazy] = y.dataSync().reshape(y.shape)
+            launches[lazy] = backend.launch_count() - n0
+            y.dispose()
+            for t in tensors.values():
+                t.dispose()
+        finally:
+            backend.lazy_fusion = True
+    assert np.array_equal(outs[True].view(np.uint32), outs[False].view(np.uint32)), name
+    assert launches[True] <= launches[False]
+    if name in ("layer_norm_tail", "layer_norm_tail_simple", "gelu", "masked_scores"):
+        # chains the library has straight-line kernels for
+        assert launches[True] < launches[False], (name, launches)
+    ref = fn(_OracleOps(), arrays)
+    ok = np.isfinite(ref)
+    assert np.array_equal(np.isnan(outs[True]), np.isnan(ref))
+    scale = max(float(np.max(np.abs(ref[ok]))), 1e-30)
+    assert float(np.max(np.abs(outs[True][ok] - ref[ok]))) <= 1e-6 * scale, name
+
+
+def test_fused_elementwise_rejects_malformed_programs(cuda_engine):
+    from tfjs_b200 import _cabi
+    backend = cuda_engine.backend
+    out = backend.make_output([64], "float32")
+    src = backend.make_output([64], "float32")
+    prog = _cabi.EwProgram()
+    prog.n_inputs, prog.n_ops, prog.n, prog.cols = 1, 1, 64, 64
+    prog.input_id[0] = backend.device_id(src.dataId)
+    prog.input_mode[0] = _cabi.EW_FULL
+    prog.ops[0].opcode, prog.ops[0].a, prog.ops[0].b = 0, 0, 3        # operand slot 3 does not exist
+    call = lambda: backend.lib.tfjs_cuda_fused_elementwise(
+        backend.ctx, ctypes.byref(prog), backend.device_id(out.dataId))
+    assert call() == 1
+    prog.ops[0].b = 0
+    prog.ops[0].opcode = 6                                            # Pow is not fusable
+    assert call() == 1
+    prog.ops[0].opcode = 0
+    prog.input_mode[0], prog.input_period[0] = _cabi.EW_PERIODIC, 48   # 48 does not divide 64
+    assert call() == 1
+    prog.n_ops = 25
+    assert call() == 1
+    backend.disposeData(out.dataId)
+    backend.disposeData(src.dataId)

@@ -34,6 +34,23 @@ class Conv2DParams(Structure):
             ("leakyrelu_alpha", c_double)]
 
 
+EW_MAX_INPUTS, EW_MAX_OPS, EW_UNARY = 8, 24, 32
+EW_FULL, EW_PERIODIC, EW_ROW, EW_SCALAR, EW_BATCHED = 0, 1, 2, 3, 4
+
+
+class EwOp(Structure):
+    _fields_ = [("opcode", ctypes.c_int16), ("a", ctypes.c_uint8), ("b", ctypes.c_uint8),
+                ("p0", c_float), ("p1", c_float)]
+
+
+class EwProgram(Structure):
+    _fields_ = [("n_inputs", c_int32), ("n_ops", c_int32), ("n", c_uint64),
+                ("cols", c_uint32), ("reserved", c_uint32),
+                ("input_id", c_int32 * EW_MAX_INPUTS), ("input_mode", c_int32 * EW_MAX_INPUTS),
+                ("input_period", c_uint32 * EW_MAX_INPUTS),
+                ("input_aux", c_uint32 * EW_MAX_INPUTS), ("ops", EwOp * EW_MAX_OPS)]
+
+
 class MatMulParams(Structure):
     _fields_ = [(n, c_int32) for n in (
         "batch_a", "batch_b", "m", "n", "k", "transpose_a", "transpose_b",
@@ -69,6 +86,9 @@ SIGNATURES = {
     "tfjs_cuda_launch_count": (c_int, [_CTX, POINTER(c_uint64)]),
     "tfjs_cuda_flush_l2": (c_int, [_CTX]),
     "tfjs_cuda_fused_conv2d": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 5),
+    "tfjs_cuda_fused_elementwise": (c_int, [_CTX, POINTER(EwProgram), c_int32]),
+    "tfjs_cuda_fused_elementwise_catalogued": (c_int, [_CTX, POINTER(EwProgram),
+                                                       POINTER(c_int32)]),
     "tfjs_cuda_decode_float16": (c_int, [_CTX, c_int32, c_uint64, c_int32]),
     "tfjs_cuda_capture_begin": (c_int, [_CTX, c_uint64]),
     "tfjs_cuda_capture_end": (c_int, [_CTX, c_int, POINTER(c_int32)]),

@@ -16,12 +16,13 @@ Const tensors with dataSync() inside its node loop
 (tfjs-converter/src/operations/executors/utils.ts:55); with this rule those
 reads never touch the CUDA stream.
 
-Deferred launches.  A FusedConv2D with a linear activation and a same-shape float32
-Add return a tensor whose launch is pending; it is launched when the tensor is first
-read or consumed by another kernel.  An Add that consumes a pending convolution, and a
-Relu / Relu6 that consumes either, fold into the producer's epilogue instead
-(`tfjs_cuda_fused_conv2d_residual`, `tfjs_cuda_add_activation`), which removes the
-separate Add and Relu passes of a residual block.  Every step still rounds to fp32
+Deferred launches.  A FusedConv2D with a linear activation and the float32 unary / binary
+elementwise kernels return a tensor whose launch is pending; it is launched when the
+tensor is first read or consumed by another kind of kernel.  An Add that consumes a
+pending convolution, and a Relu / Relu6 that consumes that, fold into the convolution's
+epilogue (`tfjs_cuda_fused_conv2d_residual`), which removes the separate Add and Relu
+passes of a residual block; chains of elementwise kernels (the decomposed LayerNorm and
+GELU of a transformer graph) become one `tfjs_cuda_fused_elementwise` pass.  Every step still rounds to fp32
 in the order of the separate kernels, so results do not change.  The WebGL backend
 defers work behind the same KernelBackend contract (uploads and packing happen on
 first use, tfjs-backend-webgl/src/backend_webgl.ts uploadToGPU).  Set
@@ -117,20 +118,182 @@ class PendingConv(object):
                 out_dev))
 
 
-class PendingAdd(object):
-    """A same-shape float32 Add not launched yet."""
-    __slots__ = ("a", "b", "n", "desc")
+class PendingEw(object):
+    """A chain of float32 elementwise kernels not launched yet.
 
-    def __init__(self, a, b, n, desc):
-        self.a, self.b, self.n, self.desc = a, b, n, desc
+    `leaves` are the tensors the chain reads (dataIds, with their shapes); `ops` are
+    (opcode, a, b, p0, p1, out_shape, a_shape, b_shape) in execution order, operands being
+    ("in", k) for leaf k or ("op", j) for the result of op j; the last op's result is
+    the tensor.  Opcodes are the C ABI's: binary op numbers, or 32 + unary op number."""
+    __slots__ = ("leaves", "leaf_shapes", "ops", "shape", "desc", "consumed", "top")
+
+    def __init__(self, leaves, leaf_shapes, ops, shape, desc, top):
+        self.leaves, self.leaf_shapes, self.ops = leaves, leaf_shapes, ops
+        self.shape, self.desc = [int(v) for v in shape], desc
+        self.consumed = 0   # how many later chains took a copy of this one
+        # the kernel call that created this tensor: (opcode, a dataId, a shape, b dataId or
+        # None, b shape).  A chain the library has no fused kernel for is launched as this
+        # one kernel on its operand tensors, which launches their chains the same way, so
+        # nothing is ever computed twice.
+        self.top = top
 
     def deps(self):
-        return [self.a, self.b]
+        out = list(self.leaves)
+        for d in (self.top[1], self.top[3]):
+            if d is not None and d not in out:
+                out.append(d)
+        return out
+
+    def cheap(self):
+        """True when every leaf is smaller than the result (broadcast scalars, rows and
+        biases only): recomputing such a chain inside each consumer costs no memory pass."""
+        n = size_from_shape(self.shape)
+        return len(self.ops) <= 2 and all(size_from_shape(s) < n for s in self.leaf_shapes)
+
+    # ------------------------------------------------------------- launching --
+    def _leaf_mode(self, shape):
+        """(mode, period, aux) of a leaf relative to the result's flat index, or None."""
+        out = self.shape
+        n, m = size_from_shape(out), size_from_shape(shape)
+        rank = len(out)
+        sh = [1] * (rank - len(shape)) + [int(v) for v in shape]
+        if len(sh) != rank:
+            return None
+        if m == 1:
+            return (_cabi.EW_SCALAR, 1, 0)
+        if m == n:
+            return (_cabi.EW_FULL, 0, 0)
+        d = 0
+        while d < rank and sh[d] == 1:
+            d += 1
+        if sh[d:] == out[d:]:
+            return (_cabi.EW_PERIODIC, m, 0)
+        if rank >= 1 and sh[-1] == 1 and sh[:-1] == out[:-1]:
+            return (_cabi.EW_ROW, 0, 0)
+        p = 0
+        while p < rank and sh[p] == out[p]:
+            p += 1
+        q = p
+        while q < rank and sh[q] == 1:
+            q += 1
+        if 0 < p < q < rank and sh[q:] == out[q:]:
+            inner = size_from_shape(out[q:])
+            return (_cabi.EW_BATCHED, inner, inner * size_from_shape(out[p:q]))
+        return None
 
     def launch(self, backend, out_dev, post_act):
-        backend.check(backend.lib.tfjs_cuda_add_activation(
-            backend.ctx, _cabi.ACTIVATIONS[post_act], backend.device_id(self.a),
-            backend.device_id(self.b), self.n, out_dev))
+        assert post_act == "linear"
+        ops = self.ops
+        n = size_from_shape(self.shape)
+        modes = [self._leaf_mode(s) for s in self.leaf_shapes]
+        if len(ops) == 1 or n >= (1 << 31) or any(m is None for m in modes):
+            return self._launch_top(backend, out_dev)
+        # Add (+ Relu / Relu6) of two full tensors has a kernel of its own
+        if (len(self.leaves) == 2 and all(m[0] == _cabi.EW_FULL for m in modes) and
+                ops[0][0] == _cabi.BINARY_OPS["Add"] and
+                {ops[0][1], ops[0][2]} == {("in", 0), ("in", 1)} and len(ops) == 2 and
+                ops[1][0] in (_cabi.EW_UNARY + _cabi.UNARY_OPS["Relu"],
+                              _cabi.EW_UNARY + _cabi.UNARY_OPS["Relu6"])):
+            act = "relu" if ops[1][0] == _cabi.EW_UNARY + _cabi.UNARY_OPS["Relu"] else "relu6"
+            return backend.check(backend.lib.tfjs_cuda_add_activation(
+                backend.ctx, _cabi.ACTIVATIONS[act], backend.device_id(self.leaves[0]),
+                backend.device_id(self.leaves[1]), n, out_dev))
+        # canonical order (commutative operands sorted by structure, ops in evaluation
+        # order from the result, leaves numbered by first use), then the library's
+        # catalogue of straight-line chain kernels; other chains run kernel by kernel
+        c_ops, leaf_order = _canonical_program(ops, [m[0] for m in modes])
+        prog = _cabi.EwProgram()
+        prog.n_inputs, prog.n_ops, prog.n = len(leaf_order), len(c_ops), n
+        prog.cols = max(int(self.shape[-1]) if self.shape else 1, 1)
+        slot = lambda ref: ref[1] if ref[0] == "in" else len(leaf_order) + ref[1]
+        for j, (code, a, b) in enumerate(c_ops):
+            prog.ops[j].opcode, prog.ops[j].a, prog.ops[j].b = code, slot(a), slot(b)
+        signature = tuple((code, slot(a), slot(b)) for code, a, b in c_ops)
+        known = backend.ew_catalogue.get(signature)
+        if known is None:
+            yes = c_int32()
+            backend.check(backend.lib.tfjs_cuda_fused_elementwise_catalogued(
+                backend.ctx, byref(prog), byref(yes)))
+            known = backend.ew_catalogue[signature] = bool(yes.value)
+        if not known:
+            return self._launch_top(backend, out_dev)
+        for k, leaf in enumerate(leaf_order):
+            prog.input_id[k] = backend.device_id(self.leaves[leaf])
+            prog.input_mode[k], prog.input_period[k], prog.input_aux[k] = modes[leaf]
+        backend.check(backend.lib.tfjs_cuda_fused_elementwise(backend.ctx, byref(prog), out_dev))
+
+    def _launch_top(self, backend, out_dev):
+        """The separate kernel of the call that made this tensor, on its operand tensors
+        (whose own pending launches happen first)."""
+        code, a, a_shape, b, b_shape = self.top
+        lib = backend.lib
+        # this launch covers the last kernel of the chain only (what the profile records)
+        ins = {"a" if b is not None else "x": list(a_shape)}
+        if b is not None:
+            ins["b"] = list(b_shape)
+        self.desc[:] = [dict(self.desc[-1], inputShapes=ins)]
+        if code >= _cabi.EW_UNARY:
+            return backend.check(lib.tfjs_cuda_unary(
+                backend.ctx, code - _cabi.EW_UNARY, 0.0, 0.0, backend.device_id(a),
+                size_from_shape(self.shape), out_dev))
+        rank = len(self.shape)
+        pad = lambda sh: _cabi.i64([1] * (rank - len(sh)) + [int(v) for v in sh])
+        backend.check(lib.tfjs_cuda_binary(
+            backend.ctx, code, _cabi.DTYPES["float32"], rank, backend.device_id(a), pad(a_shape),
+            backend.device_id(b), pad(b_shape), out_dev, _cabi.i64(self.shape)))
+
+
+_EW_COMMUTATIVE = frozenset(_cabi.BINARY_OPS[n] for n in
+                            ("Add", "Multiply", "Maximum", "Minimum", "SquaredDifference"))
+
+
+def _canonical_program(ops, leaf_modes):
+    """(ops, leaf order) of an elementwise chain in canonical form: operands of
+    commutative ops ordered by a structural key, ops emitted in evaluation order from the
+    result, leaves numbered by first use, a value used twice emitted once.  ops in and
+    out are (opcode, a, b, ...) with operand references ("in", k) / ("op", j)."""
+    keys = {}
+
+    def key(ref):
+        k = keys.get(ref)
+        if k is None:
+            if ref[0] == "in":
+                k = "L%d" % leaf_modes[ref[1]]
+            else:
+                code, a, b = ops[ref[1]][:3]
+                if code >= _cabi.EW_UNARY:
+                    k = "(%d %s)" % (code, key(a))
+                else:
+                    ka, kb = key(a), key(b)
+                    if code in _EW_COMMUTATIVE and kb < ka:
+                        ka, kb = kb, ka
+                    k = "(%d %s %s)" % (code, ka, kb)
+            keys[ref] = k
+        return k
+
+    out, leaf_order, done = [], [], {}
+
+    def emit(ref):
+        r = done.get(ref)
+        if r is None:
+            if ref[0] == "in":
+                leaf_order.append(ref[1])
+                r = ("in", len(leaf_order) - 1)
+            else:
+                code, a, b = ops[ref[1]][:3]
+                if code >= _cabi.EW_UNARY:
+                    ra = rb = emit(a)
+                else:
+                    if code in _EW_COMMUTATIVE and key(b) < key(a):
+                        a, b = b, a
+                    ra, rb = emit(a), emit(b)
+                out.append((code, ra, rb))
+                r = ("op", len(out) - 1)
+            done[ref] = r
+        return r
+
+    emit(("op", len(ops) - 1))
+    return out, leaf_order
 
 
 class PendingRead(object):
@@ -171,6 +334,7 @@ class CudaBackend(object):
         self._hidden = 0      # records kept alive only by pending launches
         self.lazy_fusion = os.environ.get("TFJS_CUDA_NO_LAZY_FUSION", "0") in ("", "0")
         self.profiler = None  # the engine, while it profiles (told about deferred launches)
+        self.ew_catalogue = {}  # chain signature -> the library has a kernel for it
 
     # ------------------------------------------------------------ plumbing --
     def check(self, rc):
@@ -262,9 +426,7 @@ class CudaBackend(object):
     def _launch(self, pending, dev, post_act, fold_into_caller):
         if self.profiler is None:
             return pending.launch(self, dev, post_act)
-        # operands that are themselves pending launch first, as records of their own
-        for d in pending.deps():
-            self.device_id(d)
+        # operands that are themselves pending launch inside, as records of their own
         return self.profiler.deferred_launch(
             pending.desc, lambda: pending.launch(self, dev, post_act), fold_into_caller)
 

@@ -179,6 +179,141 @@ __global__ void add_act_kernel(const float* __restrict__ a, const float* __restr
   for (uint64_t i = (n4 << 2) + tid; i < n; i += stride) o[i] = f(a[i], b[i]);
 }
 
+// ---- chains of elementwise ops in one pass -------------------------------------------
+// Interpreter over a small program (tfjs_cuda_ew_program): a thread owns V consecutive
+// output elements, keeps every value slot in a per-thread array and evaluates the ops in
+// order with the same device functions as the separate kernels, so every intermediate is
+// rounded to fp32 exactly as if it had been written to memory.
+struct EwArgs {
+  int n_inputs, n_ops;
+  uint64_t n;
+  uint32_t cols;
+  const float* in[TFJS_CUDA_EW_MAX_INPUTS];
+  int mode[TFJS_CUDA_EW_MAX_INPUTS];
+  uint32_t period[TFJS_CUDA_EW_MAX_INPUTS];
+  uint32_t aux[TFJS_CUDA_EW_MAX_INPUTS];
+  // divisions by cols / period / aux as multiply-shift, valid for indices below 2^31
+  // (the launcher sends larger tensors through the separate kernels)
+  uint32_t cols_mul, cols_shr;
+  uint32_t period_mul[TFJS_CUDA_EW_MAX_INPUTS], period_shr[TFJS_CUDA_EW_MAX_INPUTS];
+  uint32_t aux_mul[TFJS_CUDA_EW_MAX_INPUTS], aux_shr[TFJS_CUDA_EW_MAX_INPUTS];
+  tfjs_cuda_ew_op ops[TFJS_CUDA_EW_MAX_OPS];
+  float* out;
+};
+
+// n / d for 0 <= n < 2^31 as umulhi(n, mul) >> shr, mul = ceil(2^(32 + shr) / d); mul = 0: d = 1.
+__device__ __forceinline__ uint32_t ew_div(uint32_t n, uint32_t mul, uint32_t shr) {
+  return mul ? __umulhi(n, mul) >> shr : n;
+}
+static void ew_div_setup(uint32_t d, uint32_t* mul, uint32_t* shr) {
+  if (d <= 1) { *mul = 0; *shr = 0; return; }
+  int lg = 0;
+  while ((1ull << lg) < d) ++lg;
+  const int p = 31 + lg;
+  *mul = (uint32_t)(((1ull << p) + d - 1) / d);
+  *shr = (uint32_t)(p - 32);
+}
+
+// Address of input k for the thread whose first element is e0.
+__device__ __forceinline__ const float* ew_input_ptr(const EwArgs& g, int k, uint32_t e0) {
+  const float* src = g.in[k];
+  const int mode = g.mode[k];
+  if (mode == TFJS_CUDA_EW_FULL) return src + e0;
+  if (mode == TFJS_CUDA_EW_PERIODIC)
+    return src + (e0 - ew_div(e0, g.period_mul[k], g.period_shr[k]) * g.period[k]);
+  if (mode == TFJS_CUDA_EW_ROW) return src + ew_div(e0, g.cols_mul, g.cols_shr);
+  if (mode == TFJS_CUDA_EW_BATCHED)
+    return src + ew_div(e0, g.aux_mul[k], g.aux_shr[k]) * g.period[k] +
+           (e0 - ew_div(e0, g.period_mul[k], g.period_shr[k]) * g.period[k]);
+  return src;
+}
+
+// One decode per op: the switch is outside the loop over the thread's V elements.
+template <int V>
+__device__ __forceinline__ void ew_eval(int code, const float* a, const float* b, float* r) {
+#define EW_BIN(OP)                                                    \
+  case OP:                                                            \
+    _Pragma("unroll") for (int t = 0; t < V; ++t) r[t] = binary_eval<OP>(a[t], b[t]); \
+    break;
+#define EW_UN(OP)                                                     \
+  case TFJS_CUDA_EW_UNARY + OP:                                       \
+    _Pragma("unroll") for (int t = 0; t < V; ++t) r[t] = unary_eval<OP>(a[t], 0.0, 0.0); \
+    break;
+  switch (code) {
+    EW_BIN(TFJS_CUDA_ADD)
+    EW_BIN(TFJS_CUDA_SUB)
+    EW_BIN(TFJS_CUDA_MUL)
+    EW_BIN(TFJS_CUDA_DIV)
+    EW_BIN(TFJS_CUDA_MAXIMUM)
+    EW_BIN(TFJS_CUDA_MINIMUM)
+    EW_BIN(TFJS_CUDA_SQUARED_DIFFERENCE)
+    EW_UN(TFJS_CUDA_RELU)
+    EW_UN(TFJS_CUDA_RELU6)
+    EW_UN(TFJS_CUDA_ELU)
+    EW_UN(TFJS_CUDA_SIGMOID)
+    EW_UN(TFJS_CUDA_EXP)
+    EW_UN(TFJS_CUDA_SQRT)
+    EW_UN(TFJS_CUDA_RSQRT)
+    EW_UN(TFJS_CUDA_TANH)
+    EW_UN(TFJS_CUDA_NEG)
+    EW_UN(TFJS_CUDA_ERF)
+    EW_UN(TFJS_CUDA_ABS)
+    EW_UN(TFJS_CUDA_LOG)
+    case TFJS_CUDA_EW_UNARY + TFJS_CUDA_SQUARE:
+#pragma unroll
+      for (int t = 0; t < V; ++t) r[t] = __fmul_rn(a[t], a[t]);
+      break;
+    default:
+#pragma unroll
+      for (int t = 0; t < V; ++t) r[t] = a[t];
+      break;
+  }
+#undef EW_BIN
+#undef EW_UN
+}
+
+// V = 4: n, cols and every period are multiples of 4 (or the period is 1) and every pointer
+// is 16-byte aligned; V = 1 otherwise.  Indices fit 32 bits (checked by the launcher).
+template <int V>
+__global__ void __launch_bounds__(256)
+fused_elementwise_kernel(const __grid_constant__ EwArgs g) {
+  const uint32_t nv = (uint32_t)(g.n / V);
+  const uint32_t stride = gridDim.x * blockDim.x;
+  constexpr int kSlots = TFJS_CUDA_EW_MAX_INPUTS + TFJS_CUDA_EW_MAX_OPS;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    float vals[kSlots][V];
+    const uint32_t e0 = i * V;  // first element of this thread
+    for (int k = 0; k < g.n_inputs; ++k) {
+      const float* src = ew_input_ptr(g, k, e0);
+      const int mode = g.mode[k];
+      if (mode == TFJS_CUDA_EW_ROW || mode == TFJS_CUDA_EW_SCALAR) {
+        const float sv = __ldg(src);
+#pragma unroll
+        for (int t = 0; t < V; ++t) vals[k][t] = sv;
+      } else if (V == 4) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(src));
+        vals[k][0] = q.x; vals[k][1 % V] = q.y; vals[k][2 % V] = q.z; vals[k][3 % V] = q.w;
+      } else {
+        vals[k][0] = __ldg(src);
+      }
+    }
+    for (int j = 0; j < g.n_ops; ++j) {
+      const tfjs_cuda_ew_op op = g.ops[j];
+      float r[V];
+      ew_eval<V>(op.opcode, vals[op.a], vals[op.b], r);
+#pragma unroll
+      for (int t = 0; t < V; ++t) vals[g.n_inputs + j][t] = r[t];
+    }
+    const int last = g.n_inputs + g.n_ops - 1;
+    if (V == 4) {
+      *reinterpret_cast<float4*>(g.out + e0) =
+          make_float4(vals[last][0], vals[last][1 % V], vals[last][2 % V], vals[last][3 % V]);
+    } else {
+      g.out[e0] = vals[last][0];
+    }
+  }
+}
+
 // One operand is the full tensor, the other repeats with period `period`
 // (bias over the innermost axis, or a scalar when period == 1).  period % 4 == 0
 // or period == 1.  SWAP: the periodic operand is the left one.
@@ -474,6 +609,141 @@ static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 }  // namespace
 
+// ---- catalogued chains: straight-line kernels ------------------------------------------
+// The chains the graph models actually contain are compiled ahead of time: the program is
+// a compile-time constant, so the loop over ops unrolls, every value slot is a register and
+// each op is the inlined device function of the separate kernel.  A program matches an
+// entry when its ops and operand slots are identical (the host layer brings programs into
+// a canonical order first); input addressing modes stay run-time values.
+struct StaticOp {
+  int code, a, b;
+};
+#define EW_B(OP, A, B) StaticOp{TFJS_CUDA_##OP, A, B}
+#define EW_U(OP, A) StaticOp{TFJS_CUDA_EW_UNARY + TFJS_CUDA_##OP, A, A}
+// slots: inputs first, then one per op
+struct ProgLayerNormTail {  // ((x - mean) * rstd) * gamma + beta
+  static constexpr int n_in = 5, n_ops = 4;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[4] = {EW_B(SUB, 0, 1), EW_B(MUL, 5, 2), EW_B(MUL, 6, 3),
+                               EW_B(ADD, 7, 4)};
+    return t[j];
+  }
+};
+struct ProgLayerNormTailBn {  // x * (rstd * gamma) + (beta - mean * (rstd * gamma))
+  static constexpr int n_in = 5, n_ops = 6;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[6] = {EW_B(MUL, 1, 2), EW_B(MUL, 5, 3), EW_B(SUB, 0, 6),
+                                      EW_B(MUL, 1, 2), EW_B(MUL, 8, 4), EW_B(ADD, 7, 9)};
+    return t[j];
+  }
+};
+struct ProgGeluErf {  // (x * 0.5) * (erf(x * c) + 1)
+  static constexpr int n_in = 4, n_ops = 5;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[5] = {EW_B(MUL, 0, 1), EW_U(ERF, 4), EW_B(ADD, 5, 2),
+                                      EW_B(MUL, 0, 3), EW_B(MUL, 6, 7)};
+    return t[j];
+  }
+};
+struct ProgGeluErfDiv {  // (x * 0.5) * (erf(x / c) + 1)
+  static constexpr int n_in = 4, n_ops = 5;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[5] = {EW_B(DIV, 0, 1), EW_U(ERF, 4), EW_B(ADD, 5, 2),
+                                      EW_B(MUL, 0, 3), EW_B(MUL, 6, 7)};
+    return t[j];
+  }
+};
+struct ProgScaleShift {  // x * a + b (attention scores * scale + mask, affine maps)
+  static constexpr int n_in = 3, n_ops = 2;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[2] = {EW_B(MUL, 0, 1), EW_B(ADD, 3, 2)};
+    return t[j];
+  }
+};
+struct ProgAddAdd {  // (a + b) + c (residual + bias)
+  static constexpr int n_in = 3, n_ops = 2;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[2] = {EW_B(ADD, 0, 1), EW_B(ADD, 3, 2)};
+    return t[j];
+  }
+};
+#undef EW_B
+#undef EW_U
+
+template <class P, int V>
+__global__ void __launch_bounds__(256)
+fused_elementwise_static_kernel(const __grid_constant__ EwArgs g) {
+  const uint32_t nv = (uint32_t)(g.n / V);
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    const uint32_t e0 = i * V;
+    float vals[P::n_in + P::n_ops][V];
+#pragma unroll
+    for (int k = 0; k < P::n_in; ++k) {
+      const float* src = ew_input_ptr(g, k, e0);
+      const int mode = g.mode[k];
+      if (mode == TFJS_CUDA_EW_ROW || mode == TFJS_CUDA_EW_SCALAR) {
+        const float sv = __ldg(src);
+#pragma unroll
+        for (int t = 0; t < V; ++t) vals[k][t] = sv;
+      } else if (V == 4) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(src));
+        vals[k][0] = q.x; vals[k][1 % V] = q.y; vals[k][2 % V] = q.z; vals[k][3 % V] = q.w;
+      } else {
+        vals[k][0] = __ldg(src);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < P::n_ops; ++j)
+      ew_eval<V>(P::op(j).code, vals[P::op(j).a], vals[P::op(j).b], vals[P::n_in + j]);
+    constexpr int last = P::n_in + P::n_ops - 1;
+    if (V == 4) {
+      *reinterpret_cast<float4*>(g.out + e0) =
+          make_float4(vals[last][0], vals[last][1 % V], vals[last][2 % V], vals[last][3 % V]);
+    } else {
+      g.out[e0] = vals[last][0];
+    }
+  }
+}
+
+template <class P>
+static bool ew_matches(const EwArgs& g) {
+  if (g.n_inputs != P::n_in || g.n_ops != P::n_ops) return false;
+  for (int j = 0; j < P::n_ops; ++j)
+    if (g.ops[j].opcode != P::op(j).code || g.ops[j].a != P::op(j).a ||
+        g.ops[j].b != P::op(j).b)
+      return false;
+  return true;
+}
+
+template <class P>
+static void ew_launch_static(tfjs_cuda_ctx* ctx, const EwArgs& g, bool vec) {
+  if (vec)
+    fused_elementwise_static_kernel<P, 4><<<grid_for(g.n / 4, kThreads, ctx->sm_count), kThreads,
+                                            0, ctx->stream>>>(g);
+  else
+    fused_elementwise_static_kernel<P, 1><<<grid_for(g.n, kThreads, ctx->sm_count), kThreads, 0,
+                                            ctx->stream>>>(g);
+}
+
+// Launches the catalogue entry that matches g (dry_run: only reports whether one does).
+static bool ew_launch_catalogued(tfjs_cuda_ctx* ctx, const EwArgs& g, bool vec,
+                                 bool dry_run = false) {
+#define EW_TRY(P)                                  \
+  if (ew_matches<P>(g)) {                          \
+    if (!dry_run) ew_launch_static<P>(ctx, g, vec); \
+    return true;                                   \
+  }
+  EW_TRY(ProgLayerNormTail)
+  EW_TRY(ProgLayerNormTailBn)
+  EW_TRY(ProgGeluErf)
+  EW_TRY(ProgGeluErfDiv)
+  EW_TRY(ProgScaleShift)
+  EW_TRY(ProgAddAdd)
+#undef EW_TRY
+  return false;
+}
+
 extern "C" {
 
 int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int32_t op, double p0, double p1,
@@ -646,6 +916,113 @@ int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int32_t op, int32_t dtype, int32_t rank
 #undef BIN_CASE
   LAUNCH_CHECK(ctx, "binary_kernel");
   ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_fused_elementwise(tfjs_cuda_ctx* ctx, const tfjs_cuda_ew_program* p,
+                                int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (!p || p->n_inputs < 1 || p->n_inputs > TFJS_CUDA_EW_MAX_INPUTS || p->n_ops < 1 ||
+      p->n_ops > TFJS_CUDA_EW_MAX_OPS || p->cols < 1)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_elementwise: bad program header");
+  if (p->n >= (1ull << 31))
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "fused_elementwise: 2^31 elements or more");
+  EwArgs g;
+  memset(&g, 0, sizeof g);
+  g.n_inputs = p->n_inputs;
+  g.n_ops = p->n_ops;
+  g.n = p->n;
+  g.cols = p->cols;
+  ew_div_setup(g.cols, &g.cols_mul, &g.cols_shr);
+  bool vec = (p->n % 4) == 0 && (p->cols % 4) == 0;
+  int rc;
+  for (int k = 0; k < p->n_inputs; ++k) {
+    uint64_t need;
+    const int mode = p->input_mode[k];
+    if (mode == TFJS_CUDA_EW_FULL) need = p->n;
+    else if (mode == TFJS_CUDA_EW_PERIODIC) {
+      need = p->input_period[k];
+      if (need == 0 || p->n % need != 0)
+        return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG,
+                        "fused_elementwise: period %u of input %d does not divide the output",
+                        p->input_period[k], k);
+      if (need % 4 != 0) vec = false;
+    } else if (mode == TFJS_CUDA_EW_ROW) {
+      if (p->n % p->cols != 0)
+        return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_elementwise: cols does not divide n");
+      need = p->n / p->cols;
+    } else if (mode == TFJS_CUDA_EW_SCALAR) need = 1;
+    else if (mode == TFJS_CUDA_EW_BATCHED) {
+      const uint64_t per = p->input_period[k], aux = p->input_aux[k];
+      if (per == 0 || aux == 0 || aux % per != 0 || p->n % aux != 0)
+        return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG,
+                        "fused_elementwise: batched input %d has period %u, aux %u", k,
+                        p->input_period[k], p->input_aux[k]);
+      need = p->n / aux * per;
+      if (per % 4 != 0) vec = false;
+    }
+    else return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_elementwise: input mode %d", mode);
+    Buffer* b;
+    if ((rc = ctx_get(ctx, p->input_id[k], need * 4, "fused_elementwise input", &b))) return rc;
+    g.in[k] = (const float*)b->ptr;
+    g.mode[k] = mode;
+    g.period[k] = p->input_period[k];
+    g.aux[k] = p->input_aux[k];
+    ew_div_setup(g.period[k], &g.period_mul[k], &g.period_shr[k]);
+    ew_div_setup(g.aux[k], &g.aux_mul[k], &g.aux_shr[k]);
+    if (!aligned16(b->ptr)) vec = false;
+  }
+  for (int j = 0; j < p->n_ops; ++j) {
+    const tfjs_cuda_ew_op& op = p->ops[j];
+    const int limit = p->n_inputs + j;  // an op reads inputs and earlier results only
+    const bool unary = op.opcode >= TFJS_CUDA_EW_UNARY;
+    const int code = unary ? op.opcode - TFJS_CUDA_EW_UNARY : op.opcode;
+    const bool known = unary ? (code >= TFJS_CUDA_RELU && code <= TFJS_CUDA_LOG &&
+                                code != TFJS_CUDA_LEAKYRELU && code != TFJS_CUDA_CLIP)
+                             : (code >= TFJS_CUDA_ADD && code <= TFJS_CUDA_SQUARED_DIFFERENCE &&
+                                code != TFJS_CUDA_POW);
+    if (!known || op.a >= limit || (!unary && op.b >= limit))
+      return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_elementwise: op %d is malformed", j);
+    g.ops[j] = op;
+    if (unary) g.ops[j].b = op.a;
+  }
+  Buffer* o;
+  if ((rc = ctx_get(ctx, out_id, p->n * 4, "fused_elementwise out", &o))) return rc;
+  if (p->n == 0) return TFJS_CUDA_OK;
+  g.out = (float*)o->ptr;
+  if (!aligned16(o->ptr)) vec = false;
+  cudaSetDevice(ctx->device);
+  if (!ew_launch_catalogued(ctx, g, vec)) {
+    // not in the catalogue: the interpreter (slower than the separate kernels for short
+    // chains; the host layer asks tfjs_cuda_fused_elementwise_catalogued first)
+    if (vec)
+      fused_elementwise_kernel<4><<<grid_for(p->n / 4, kThreads, ctx->sm_count), kThreads, 0,
+                                    ctx->stream>>>(g);
+    else
+      fused_elementwise_kernel<1><<<grid_for(p->n, kThreads, ctx->sm_count), kThreads, 0,
+                                    ctx->stream>>>(g);
+  }
+  LAUNCH_CHECK(ctx, "fused_elementwise_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_fused_elementwise_catalogued(tfjs_cuda_ctx* ctx, const tfjs_cuda_ew_program* p,
+                                           int32_t* out_yes) {
+  if (!ctx || !p || !out_yes) return TFJS_CUDA_INVALID_ARG;
+  *out_yes = 0;
+  if (p->n_inputs < 1 || p->n_inputs > TFJS_CUDA_EW_MAX_INPUTS || p->n_ops < 1 ||
+      p->n_ops > TFJS_CUDA_EW_MAX_OPS)
+    return TFJS_CUDA_OK;
+  EwArgs g;
+  memset(&g, 0, sizeof g);
+  g.n_inputs = p->n_inputs;
+  g.n_ops = p->n_ops;
+  for (int j = 0; j < p->n_ops; ++j) {
+    g.ops[j] = p->ops[j];
+    if (g.ops[j].opcode >= TFJS_CUDA_EW_UNARY) g.ops[j].b = g.ops[j].a;
+  }
+  *out_yes = ew_launch_catalogued(ctx, g, true, true) ? 1 : 0;
   return TFJS_CUDA_OK;
 }
 

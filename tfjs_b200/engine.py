@@ -214,12 +214,19 @@ class Engine(object):
             self._prof_stack[-1]["parts"] = list(descs)
             self._prof_stack[-1]["folded"] = True
             return launch()
-        rec = {"name": "+".join(d["name"] for d in descs), "slot": self._take_slots(),
-               "inputShapes": {}, "outputShapes": descs[-1]["outputShapes"], "attrs": {},
-               "parts": list(descs), "nested": [], "deferred": False}
+        rec = {"slot": self._take_slots(), "inputShapes": {}, "attrs": {}, "nested": [],
+               "deferred": False}
         self.backend.event_record(rec["slot"])
-        result = launch()
+        self._prof_stack.append(rec)      # launches of pending operands nest under this one
+        try:
+            result = launch()
+        finally:
+            self._prof_stack.pop()
         self.backend.event_record(rec["slot"] + 1)
+        # a launch may narrow `descs` to what it really covered (a chain that ran as its
+        # last kernel only), so the record is named afterwards
+        rec.update(name="+".join(d["name"] for d in descs), parts=list(descs),
+                   outputShapes=descs[-1]["outputShapes"])
         if self._prof_stack:
             self._prof_stack[-1]["nested"].append(rec["slot"])
         self._profile.append(rec)

@@ -5,7 +5,7 @@ binary_impl.ts:25-69 and the per-op files (Add.ts, Relu.ts, Erf.ts, ...);
 BatchNorm.ts:23-90; Cast.ts:27-95.
 """
 from .. import _cabi
-from ..backend import PendingAdd, PendingConv, TensorInfo
+from ..backend import PendingConv, PendingEw, TensorInfo
 from ..kernel_registry import KernelConfig
 from ..util import assert_and_get_broadcast_shape, size_from_shape
 from .common import BACKEND, assert_not_complex, dev, view
@@ -113,24 +113,70 @@ def apply_activation(backend, x, activation, prelu=None, alpha=None):
                      activation)
 
 
-def deferred_add(backend, a, b):
-    """Add of two equal-shape float32 tensors as a deferred launch: folded into the
-    epilogue of a pending convolution when one operand is one, else a pending
-    add that a following Relu / Relu6 can join.  None when the operands do not
-    qualify."""
-    if not (backend.lazy_fusion and a.dtype == "float32" and b.dtype == "float32" and
-            list(a.shape) == list(b.shape) and size_from_shape(a.shape) > 0):
+# ---------------------------------------------------------- deferred launches --
+EW_BINARY = ("Add", "Sub", "Multiply", "RealDiv", "Maximum", "Minimum", "SquaredDifference")
+EW_UNARY = ("Relu", "Relu6", "Elu", "Sigmoid", "Exp", "Sqrt", "Rsqrt", "Square", "Tanh", "Neg",
+            "Erf", "Abs", "Log")
+
+
+def _ew_operand(backend, info, leaves, leaf_shapes, ops, out_n, budget):
+    """Reference to `info` inside the chain being built: a copy of its own pending
+    chain when it has the result's size and has not been copied before (or is cheap to
+    recompute), else a leaf."""
+    pend = backend.pending_of(info.dataId)
+    if (isinstance(pend, PendingEw) and size_from_shape(pend.shape) == out_n and
+            (pend.consumed == 0 or pend.cheap()) and
+            len(ops) + len(pend.ops) <= budget and
+            len(set(leaves) | set(pend.leaves)) <= _cabi.EW_MAX_INPUTS):
+        remap = []
+        for leaf, shape in zip(pend.leaves, pend.leaf_shapes):
+            if leaf not in leaves:
+                leaves.append(leaf)
+                leaf_shapes.append(shape)
+            remap.append(leaves.index(leaf))
+        base = len(ops)
+        ref = lambda r: ("in", remap[r[1]]) if r[0] == "in" else ("op", base + r[1])
+        for op in pend.ops:
+            ops.append((op[0], ref(op[1]), ref(op[2])))
+        pend.consumed += 1
+        return ("op", len(ops) - 1), pend.desc
+    if info.dataId not in leaves:
+        leaves.append(info.dataId)
+        leaf_shapes.append(list(info.shape))
+    return ("in", leaves.index(info.dataId)), None
+
+
+def deferred_elementwise(backend, name, a, b=None):
+    """The float32 kernel `name` as a deferred launch joined to the pending chains of its
+    operands; None when it has to run at once (other dtypes, empty or oversized tensors)."""
+    if not backend.lazy_fusion or a.dtype != "float32" or (b is not None and b.dtype != "float32"):
         return None
-    desc = {"name": "Add", "inputShapes": {"b": list(b.shape)},
-            "outputShapes": [list(a.shape)], "attrs": {}}
-    for conv, other in ((a, b), (b, a)):
-        pend = backend.pending_of(conv.dataId)
-        if isinstance(pend, PendingConv) and pend.residual is None:
-            return backend.defer(a.shape, "float32", PendingConv(
-                pend.params, pend.x, pend.filt, pend.bias, other.dataId, pend.desc + [desc]))
-    desc["inputShapes"]["a"] = list(a.shape)
-    return backend.defer(a.shape, "float32",
-                         PendingAdd(a.dataId, b.dataId, size_from_shape(a.shape), [desc]))
+    out_shape = list(a.shape) if b is None else assert_and_get_broadcast_shape(a.shape, b.shape)
+    n = size_from_shape(out_shape)
+    if n == 0 or len(out_shape) > 6:
+        return None
+    leaves, leaf_shapes, ops, descs = [], [], [], []
+    budget = _cabi.EW_MAX_OPS - 2          # room for this op and a folded activation
+    ra, da = _ew_operand(backend, a, leaves, leaf_shapes, ops, n, budget)
+    rb, db = (ra, None) if b is None else _ew_operand(backend, b, leaves, leaf_shapes, ops, n,
+                                                        budget)
+    if len(leaves) > _cabi.EW_MAX_INPUTS:
+        return None
+    code = _cabi.BINARY_OPS[name] if b is not None else _cabi.EW_UNARY + _cabi.UNARY_OPS[name]
+    ops.append((code, ra, rb))
+    for d in (da, db):
+        if d:
+            descs.extend(d)
+    ins = {}
+    if ra[0] == "in":
+        ins["a" if b is not None else "x"] = list(a.shape)
+    if b is not None and rb[0] == "in" and rb != ra:
+        ins["b"] = list(b.shape)
+    descs.append({"name": name, "inputShapes": ins, "outputShapes": [out_shape], "attrs": {}})
+    top = (code, a.dataId, list(a.shape), b.dataId if b is not None else None,
+           list(b.shape) if b is not None else None)
+    return backend.defer(out_shape, "float32",
+                         PendingEw(leaves, leaf_shapes, ops, out_shape, descs, top))
 
 
 def _unary_config(name, p_from_attrs=None):
@@ -139,23 +185,46 @@ def _unary_config(name, p_from_attrs=None):
     def func(args):
         x = args["inputs"]["x"]
         backend = args["backend"]
-        if post_act and x.dtype == "float32" and backend.pending_of(x.dataId) is not None:
-            return backend.launch_pending(x, post_act)
+        if x.dtype == "float32" and backend.lazy_fusion:
+            if post_act and isinstance(backend.pending_of(x.dataId), PendingConv):
+                return backend.launch_pending(x, post_act)
+            if name in EW_UNARY:
+                out = deferred_elementwise(backend, name, x)
+                if out is not None:
+                    return out
         p0, p1 = p_from_attrs(args["attrs"]) if p_from_attrs else (0.0, 0.0)
         return unary_impl(backend, name, x, p0, p1)
     return KernelConfig(name, BACKEND, func)
 
 
+def _conv_residual(backend, a, b):
+    """Add of a pending convolution and an equal-shape float32 tensor: the convolution with
+    the other operand as its residual, still pending."""
+    if not (a.dtype == "float32" and b.dtype == "float32" and list(a.shape) == list(b.shape)):
+        return None
+    desc = {"name": "Add", "inputShapes": {"b": list(b.shape)},
+            "outputShapes": [list(a.shape)], "attrs": {}}
+    for conv, other in ((a, b), (b, a)):
+        pend = backend.pending_of(conv.dataId)
+        if isinstance(pend, PendingConv) and pend.residual is None:
+            return backend.defer(a.shape, "float32", PendingConv(
+                pend.params, pend.x, pend.filt, pend.bias, other.dataId, pend.desc + [desc]))
+    return None
+
+
 def _binary_config(name):
     def func(args):
         i = args["inputs"]
+        backend = args["backend"]
         if name == "Prelu":
-            return binary_impl(args["backend"], name, i["x"], i["alpha"])
-        if name == "Add":
-            out = deferred_add(args["backend"], i["a"], i["b"])
+            return binary_impl(backend, name, i["x"], i["alpha"])
+        if backend.lazy_fusion:
+            out = _conv_residual(backend, i["a"], i["b"]) if name == "Add" else None
+            if out is None and name in EW_BINARY:
+                out = deferred_elementwise(backend, name, i["a"], i["b"])
             if out is not None:
                 return out
-        return binary_impl(args["backend"], name, i["a"], i["b"])
+        return binary_impl(backend, name, i["a"], i["b"])
     return KernelConfig(name, BACKEND, func)
 
 

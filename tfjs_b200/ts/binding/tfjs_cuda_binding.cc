@@ -119,6 +119,11 @@ napi_value ReadBegin(napi_env env, napi_callback_info info) {
 napi_value ReadWait(napi_env env, napi_callback_info info) {
   Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_read_wait(a.ctx(0), a.i32(1)));
 }
+napi_value FusedElementwise(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  auto* p = static_cast<tfjs_cuda_ew_program*>(a.buffer(1));   // packed program struct
+  return check(env, a.ctx(0), tfjs_cuda_fused_elementwise(a.ctx(0), p, a.i32(2)));
+}
 napi_value DecodeFloat16(napi_env env, napi_callback_info info) {
   Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_decode_float16(a.ctx(0), a.i32(1), a.u64(2), a.i32(3)));
 }
@@ -241,7 +246,7 @@ napi_value DequantizeStatic(napi_env env, napi_callback_info info) {
 napi_value Init(napi_env env, napi_value exports) {
   struct { const char* name; napi_callback fn; } table[] = {
       {"create", Create}, {"alloc", Alloc}, {"free", Free}, {"write", Write}, {"read", Read},
-      {"decodeFloat16", DecodeFloat16}, {"captureBegin", CaptureBegin}, {"captureEnd", CaptureEnd}, {"graphLaunch", GraphLaunch},
+      {"fusedElementwise", FusedElementwise}, {"decodeFloat16", DecodeFloat16}, {"captureBegin", CaptureBegin}, {"captureEnd", CaptureEnd}, {"graphLaunch", GraphLaunch},
       {"graphDestroy", GraphDestroy}, {"copy", Copy}, {"highWaterReset", HighWaterReset},
       {"readBegin", ReadBegin}, {"readWait", ReadWait}, {"sync", Sync}, {"memory", Memory}, {"timeBegin", TimeBegin}, {"timeEnd", TimeEnd},
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},

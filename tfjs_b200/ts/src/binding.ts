@@ -13,6 +13,7 @@ export interface CudaBinding {
   free(ctx: Ctx, id: number): void;
   write(ctx: Ctx, id: number, data: ArrayBufferView, nbytes: number): void;
   read(ctx: Ctx, id: number, out: ArrayBufferView, nbytes: number): void;
+  fusedElementwise(ctx: Ctx, program: ArrayBuffer, out: number): void;
   decodeFloat16(ctx: Ctx, q: number, n: number, out: number): void;
   captureBegin(ctx: Ctx, arenaBytes: number): void;
   captureEnd(ctx: Ctx, abandon: number): number;
