@@ -7,8 +7,10 @@ cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072),
 pw_<hw>_<cin>_<cout>_<batch> (1x1 conv), c3_<hw>_<cin>_<cout>_<batch>_<stride> (3x3
 conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<batch>_<stride>
 (3x3 depthwise), res_<hw>_<cin>_<cout>_<batch> (1x1 conv + bias, Add of a shortcut, Relu:
-one launch through the deferred-launch path).  Prints ms, TFLOP/s and algorithmic GB/s
-(each tensor moved once).
+one launch through the deferred-launch path), gelu_<rows>_<cols> (x * 0.5 * (1 + erf(x /
+sqrt 2)): five elementwise kernels, one catalogued chain launch), ln_<rows>_<cols> (LayerNorm
+tail ((x - mean) * rstd) * gamma + beta: four kernels, one chain launch).  Prints ms, TFLOP/s
+and algorithmic GB/s (each tensor moved once).
 """
 import sys
 
@@ -33,6 +35,26 @@ elif case=='ffn':
     a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
     bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
     f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'linear'); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
+elif case.startswith('gelu'):   # gelu_<rows>_<cols>
+    _,rows,cols=case.split('_'); rows,cols=int(rows),int(cols)
+    x=ops.tensor(r.standard_normal((rows,cols)).astype(np.float32))
+    c=ops.tensor(np.float32(1/np.sqrt(2))); one=ops.tensor(np.float32(1)); half=ops.tensor(np.float32(0.5))
+    def f():
+        a=ops.mul(x,c); b=ops.erf(a); i=ops.add(b,one); d=ops.mul(x,half); y=ops.mul(d,i)
+        be.device_id(y.dataId)
+        for t in (a,b,i,d): t.dispose()
+        return y
+    fl=0; by=8*rows*cols
+elif case.startswith('ln'):   # ln_<rows>_<cols>
+    _,rows,cols=case.split('_'); rows,cols=int(rows),int(cols)
+    x=ops.tensor(r.standard_normal((rows,cols)).astype(np.float32)); mean=ops.tensor(r.standard_normal((rows,1)).astype(np.float32))
+    rstd=ops.tensor((r.random((rows,1))+0.5).astype(np.float32)); gamma=ops.tensor(r.standard_normal(cols).astype(np.float32)); beta=ops.tensor(r.standard_normal(cols).astype(np.float32))
+    def f():
+        a=ops.sub(x,mean); b=ops.mul(a,rstd); c2=ops.mul(b,gamma); y=ops.add(c2,beta)
+        be.device_id(y.dataId)
+        for t in (a,b,c2): t.dispose()
+        return y
+    fl=0; by=8*rows*cols
 elif case.startswith('res'):   # residual block exit: res_<hw>_<cin>_<cout>_<batch>
     _,hw,ci,co,bt=case.split('_'); hw,ci,co,bt=int(hw),int(ci),int(co),int(bt)
     x=ops.tensor(r.standard_normal((bt,hw,hw,ci)).astype(np.float32)); w=ops.tensor(r.standard_normal((1,1,ci,co)).astype(np.float32)/8)
