@@ -452,3 +452,19 @@ def test_fused_elementwise_rejects_malformed_programs(cuda_engine):
     assert call() == 1
     backend.disposeData(out.dataId)
     backend.disposeData(src.dataId)
+
+
+def test_very_long_unread_chain_does_not_recurse_deeply(cuda_engine):
+    """3000 dependent elementwise kernels with no read in between."""
+    from tfjs_b200 import ops as tf
+    x = tf.tensor(np.full(4096, 1.0, np.float32))
+    one = tf.tensor(np.float32(1.0))
+    y = x
+    for _ in range(3000):
+        z = tf.add(y, one)
+        if y is not x:
+            y.dispose()
+        y = z
+    assert np.array_equal(y.dataSync(), np.full(4096, 3001.0, np.float32))
+    for t in (x, one, y):
+        t.dispose()

@@ -122,12 +122,15 @@ class PendingEw(object):
     """A chain of float32 elementwise kernels not launched yet.
 
     `leaves` are the tensors the chain reads (dataIds, with their shapes); `ops` are
-    (opcode, a, b, p0, p1, out_shape, a_shape, b_shape) in execution order, operands being
-    ("in", k) for leaf k or ("op", j) for the result of op j; the last op's result is
-    the tensor.  Opcodes are the C ABI's: binary op numbers, or 32 + unary op number."""
-    __slots__ = ("leaves", "leaf_shapes", "ops", "shape", "desc", "consumed", "top")
+    (opcode, a, b) in execution order, operands being ("in", k) for leaf k or ("op", j)
+    for the result of op j; the last op's result is the tensor.  Opcodes are the C ABI's:
+    binary op numbers, or 32 + unary op number.  `depth` counts the pending tensors
+    stacked below this one (bounded by the kernel funcs, since launching walks them
+    recursively)."""
+    __slots__ = ("leaves", "leaf_shapes", "ops", "shape", "desc", "consumed", "top", "depth")
 
-    def __init__(self, leaves, leaf_shapes, ops, shape, desc, top):
+    def __init__(self, leaves, leaf_shapes, ops, shape, desc, top, depth=1):
+        self.depth = depth
         self.leaves, self.leaf_shapes, self.ops = leaves, leaf_shapes, ops
         self.shape, self.desc = [int(v) for v in shape], desc
         self.consumed = 0   # how many later chains took a copy of this one

@@ -155,8 +155,18 @@ def deferred_elementwise(backend, name, a, b=None):
     n = size_from_shape(out_shape)
     if n == 0 or len(out_shape) > 6:
         return None
+    # launching a pending tensor walks its pending operands recursively: keep that shallow
+    depth = 1
+    for t in (a, b):
+        if t is not None:
+            pend = backend.pending_of(t.dataId)
+            if isinstance(pend, PendingEw):
+                if pend.depth >= 32:
+                    backend.device_id(t.dataId)
+                else:
+                    depth = max(depth, pend.depth + 1)
     leaves, leaf_shapes, ops, descs = [], [], [], []
-    budget = _cabi.EW_MAX_OPS - 2          # room for this op and a folded activation
+    budget = _cabi.EW_MAX_OPS - 2
     ra, da = _ew_operand(backend, a, leaves, leaf_shapes, ops, n, budget)
     rb, db = (ra, None) if b is None else _ew_operand(backend, b, leaves, leaf_shapes, ops, n,
                                                         budget)
@@ -176,7 +186,7 @@ def deferred_elementwise(backend, name, a, b=None):
     top = (code, a.dataId, list(a.shape), b.dataId if b is not None else None,
            list(b.shape) if b is not None else None)
     return backend.defer(out_shape, "float32",
-                         PendingEw(leaves, leaf_shapes, ops, out_shape, descs, top))
+                         PendingEw(leaves, leaf_shapes, ops, out_shape, descs, top, depth))
 
 
 def _unary_config(name, p_from_attrs=None):
