@@ -1,0 +1,106 @@
+"""Host-side logic that needs no GPU: canonical form of elementwise chains, the chain
+catalogue query of the library, leaf addressing modes, batch sharding."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from tfjs_b200 import _cabi
+from tfjs_b200.backend import PendingEw, _canonical_program
+
+ADD, SUB, MUL, DIV = (_cabi.BINARY_OPS[n] for n in ("Add", "Sub", "Multiply", "RealDiv"))
+ERF = _cabi.EW_UNARY + _cabi.UNARY_OPS["Erf"]
+RELU = _cabi.EW_UNARY + _cabi.UNARY_OPS["Relu"]
+FULL, PER, ROW, SCAL, BAT = (_cabi.EW_FULL, _cabi.EW_PERIODIC, _cabi.EW_ROW, _cabi.EW_SCALAR,
+                             _cabi.EW_BATCHED)
+
+
+def _signature(ops, modes):
+    c_ops, order = _canonical_program(ops, modes)
+    slot = lambda r: r[1] if r[0] == "in" else len(order) + r[1]
+    return [(code, slot(a), slot(b)) for code, a, b in c_ops], [modes[k] for k in order]
+
+
+def _gelu(order):
+    """x * 0.5 * (1 + erf(x * c)) written with the operands of every commutative op in the
+    given order; leaves: 0 x, 1 half, 2 c, 3 one."""
+    sw = (lambda a, b: (b, a)) if order else (lambda a, b: (a, b))
+    return [(MUL,) + sw(("in", 0), ("in", 1)), (MUL,) + sw(("in", 0), ("in", 2)),
+            (ERF, ("op", 1), ("op", 1)), (ADD,) + sw(("op", 2), ("in", 3)),
+            (MUL,) + sw(("op", 0), ("op", 3))]
+
+
+def test_canonical_program_ignores_operand_order_of_commutative_ops():
+    a = _signature(_gelu(False), [FULL, SCAL, SCAL, SCAL])
+    b = _signature(_gelu(True), [FULL, SCAL, SCAL, SCAL])
+    assert a == b
+    assert a[0] == [(MUL, 0, 1), (ERF, 4, 4), (ADD, 5, 2), (MUL, 0, 3), (MUL, 6, 7)]
+    # Sub is not commutative: its operand order survives
+    s1 = _signature([(SUB, ("in", 0), ("in", 1))], [FULL, ROW])
+    s2 = _signature([(SUB, ("in", 1), ("in", 0))], [FULL, ROW])
+    assert s1[0] == [(SUB, 0, 1)] and s2[0] == [(SUB, 0, 1)] and s1[1] != s2[1]
+
+
+def test_canonical_program_emits_a_shared_value_once():
+    # (a + b) used twice: relu(s) * s
+    ops = [(ADD, ("in", 0), ("in", 1)), (RELU, ("op", 0), ("op", 0)), (MUL, ("op", 1), ("op", 0))]
+    sig, _ = _signature(ops, [FULL, FULL])
+    assert len(sig) == 3 and sum(1 for code, _, _ in sig if code == ADD) == 1
+
+
+CHAINS = {
+    "layer_norm_tail": ([(SUB, ("in", 0), ("in", 1)), (MUL, ("op", 0), ("in", 2)),
+                         (MUL, ("op", 1), ("in", 3)), (ADD, ("op", 2), ("in", 4))],
+                        [FULL, ROW, ROW, PER, PER], True),
+    "layer_norm_tail_bn": ([(MUL, ("in", 1), ("in", 2)), (MUL, ("in", 0), ("op", 0)),
+                            (MUL, ("in", 1), ("in", 2)), (MUL, ("in", 4), ("op", 2)),
+                            (SUB, ("in", 3), ("op", 3)), (ADD, ("op", 1), ("op", 4))],
+                           [FULL, ROW, PER, PER, ROW], True),
+    "gelu_mul": (_gelu(False), [FULL, SCAL, SCAL, SCAL], True),
+    "gelu_div": ([(MUL, ("in", 0), ("in", 1)), (DIV, ("in", 0), ("in", 2)),
+                  (ERF, ("op", 1), ("op", 1)), (ADD, ("op", 2), ("in", 3)),
+                  (MUL, ("op", 0), ("op", 3))], [FULL, SCAL, SCAL, SCAL], True),
+    "scale_mask": ([(MUL, ("in", 0), ("in", 1)), (ADD, ("op", 0), ("in", 2))],
+                   [FULL, SCAL, BAT], True),
+    "add_add": ([(ADD, ("in", 0), ("in", 1)), (ADD, ("op", 0), ("in", 2))],
+                [FULL, FULL, PER], True),
+    "not_catalogued": ([(SUB, ("in", 0), ("in", 1)), (RELU, ("op", 0), ("op", 0))],
+                       [FULL, FULL], False),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CHAINS))
+def test_library_catalogue_knows_the_chains_of_the_graph_models(name):
+    """The canonical programs the host layer builds for the decomposed LayerNorm, GELU and
+    score scaling are the ones the library has straight-line kernels for (the query needs
+    no GPU and no context state)."""
+    ops, modes, expected = CHAINS[name]
+    sig, _ = _signature(ops, modes)
+    prog = _cabi.EwProgram()
+    prog.n_inputs, prog.n_ops = len(modes), len(sig)
+    for j, (code, a, b) in enumerate(sig):
+        prog.ops[j].opcode, prog.ops[j].a, prog.ops[j].b = code, a, b
+    lib = _cabi.load()
+    yes = ctypes.c_int32(-1)
+    # the query reads the program only; a dummy non-null context pointer is never followed
+    dummy = ctypes.create_string_buffer(8)
+    rc = lib.tfjs_cuda_fused_elementwise_catalogued(ctypes.cast(dummy, ctypes.c_void_p),
+                                                    ctypes.byref(prog), ctypes.byref(yes))
+    assert rc == _cabi.OK
+    assert bool(yes.value) == expected
+
+
+def test_leaf_addressing_modes():
+    p = PendingEw([], [], [], [4, 12, 16, 32], [], (ADD, None, [1], None, [1]))
+    assert p._leaf_mode([4, 12, 16, 32])[0] == FULL
+    assert p._leaf_mode([1])[0] == SCAL and p._leaf_mode([])[0] == SCAL
+    assert p._leaf_mode([32]) == (PER, 32, 0)
+    assert p._leaf_mode([16, 32]) == (PER, 512, 0)
+    assert p._leaf_mode([4, 12, 16, 1])[0] == ROW
+    assert p._leaf_mode([4, 1, 1, 32]) == (BAT, 32, 12 * 16 * 32)
+    assert p._leaf_mode([4, 1, 16, 32]) == (BAT, 512, 12 * 512)
+    assert p._leaf_mode([4, 12, 1, 32]) == (BAT, 32, 16 * 32)
+    assert p._leaf_mode([1, 12, 1, 32]) is None          # two separate broadcast gaps
+    assert p._leaf_mode([1, 12, 1, 1]) is None
+    q = PendingEw([], [], [], [8, 1], [], (ADD, None, [1], None, [1]))
+    assert q._leaf_mode([8, 1])[0] == FULL and q._leaf_mode([1])[0] == SCAL

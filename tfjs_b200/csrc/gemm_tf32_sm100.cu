@@ -206,47 +206,56 @@ inline void fast_div_setup(int d, uint32_t* mul, uint32_t* shr) {
 constexpr int kTapTableEntries = 512;  // scalar-gather K limit (after padding to 32)
 
 constexpr int kMaxSmemBytes = 232448;  // 227 KB per CTA
-constexpr int kBarrierBytes = 512;  // pipeline barriers, TMEM slot, residual barriers
+constexpr int kBarrierBytes = 640;  // pipeline barriers, TMEM slot, residual barriers
 
 // RES: the epilogue adds a residual tile that the TMA unit prefetches into the
 // staging tile of the next chunk (two staging tiles per warp, and at BN = 256 one
 // pipeline stage fewer to make room for them).
-template <int BN, int A_MODE = 0, int RES = 0>
+template <int BN, int A_MODE = 0, int RES = 0, int EW = 8>
 struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
   // the scalar-gather mode runs three stages: its shared memory goes to the tap and
-  // row tables and to the two staged input patches
+  // row tables and to the two staged input patches; sixteen epilogue warps (EW = 16,
+  // short-K launches) take one stage at BN = 256 for their staging tiles
   static constexpr int STAGES =
       A_MODE == 3 ? (BN == 32 ? 5 : (BN == 64 ? 4 : 3))
                   : (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 6 : 8))) -
-                        (RES && BN >= 256 ? 1 : 0);
+                        ((RES || EW == 16) && BN >= 256 ? 1 : 0);
   // staging tiles per epilogue warp: two below BN = 256 (bandwidth-bound shapes), so
-  // a warp fills one while the TMA unit still drains the other
-  static constexpr int EPI_BUFS = ((BN >= 256 && !RES) || A_MODE == 3) ? 1 : 2;
+  // a warp fills one while the TMA unit still drains the other; one with sixteen warps
+  static constexpr int EPI_BUFS = (((BN >= 256 && !RES) || A_MODE == 3) || EW == 16) ? 1 : 2;
   // TMEM accumulator stages.  A tile's accumulator is handed back and forth through
   // two barriers whose wake-ups cost more than a short tile's MMAs, so narrow tiles
   // (few K steps in practice) keep more tiles in flight: 256 columns at BN <= 128.
   static constexpr int ACC_STAGES = BN >= 256 ? 2 : 256 / BN;
   static constexpr int TMEM_COLS = ACC_STAGES * BN;
+  // epilogue work split: P warps per TMEM lane quarter, C 32-column chunks per tile
+  static constexpr int EPI_P = EW / 4, EPI_C = BN / 32;
+  static constexpr int EPI_G = EPI_C >= EPI_P ? 1 : EPI_P / EPI_C;  // tiles alternate over G groups
+  static constexpr int EPI_STEP = (EPI_C >= EPI_P ? EPI_P : EPI_C) * 32;
+  static constexpr int EPI_ARRIVALS = 4 * (EPI_C >= EPI_P ? EPI_P : EPI_C);
+  static constexpr int THREADS = 64 + EW * 32 + ((A_MODE == 1 || A_MODE == 3) ? 128 : 0);
   static constexpr int SMEM_BYTES =
-      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + kBarrierBytes + 8 * EPI_BUFS * 4096 +
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + kBarrierBytes + EW * EPI_BUFS * 4096 +
       (A_MODE == 3 ? kTapTableEntries * 4 + 4 * 512 : 0);  // tap table + 4 row tables
 };
 
-template <int BN, int B_MN, int A_MODE, int RES>
-__global__ void __launch_bounds__((A_MODE == 1 || A_MODE == 3) ? 448 : 320, 1)
+template <int BN, int B_MN, int A_MODE, int RES, int EW = 8>
+__global__ void __launch_bounds__((Cfg<BN, A_MODE, RES, EW>::THREADS), 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_c,
                  const __grid_constant__ CUtensorMap tm_r, const Tf32Args g) {
-  using C = Cfg<BN, A_MODE, RES>;
+  using C = Cfg<BN, A_MODE, RES, EW>;
   constexpr int STAGES = C::STAGES;
+  constexpr int kGatherWarp0 = 2 + EW;          // first gather warp (A_MODE 1 and 3)
+  constexpr int kGatherThread0 = 64 + EW * 32;  // its first thread
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_base = smem_base;
   const uint32_t b_base = smem_base + STAGES * A_STAGE_BYTES;
   const uint32_t epi_base = b_base + STAGES * C::B_STAGE_BYTES;  // 4 KB staging tiles
-  const uint32_t bar_base = epi_base + 8u * C::EPI_BUFS * 4096u;
+  const uint32_t bar_base = epi_base + (uint32_t)EW * C::EPI_BUFS * 4096u;
   // barrier layout: full[STAGES], empty[STAGES], tfull[ACC], tempty[ACC], tmem slot
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
@@ -255,7 +264,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + ACC + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 2 * ACC);
   // residual prefetch barriers: one per epilogue warp and staging tile
-  auto res_bar = [&](int w, uint32_t b) { return bar_base + 320u + 8u * (2u * w + b); };
+  auto res_bar = [&](int w, uint32_t b) { return bar_base + 320u + 8u * (2u * w + b); };  // up to 32
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -267,10 +276,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
     for (int a = 0; a < ACC; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), BN == 32 ? 4 : 8);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), C::EPI_ARRIVALS);  // one arrival per epilogue warp of a tile
     }
     if (RES)
-      for (int w = 0; w < 8; ++w) {
+      for (int w = 0; w < EW; ++w) {
         mbar_init(res_bar(w, 0), 1);
         mbar_init(res_bar(w, 1), 1);
       }
@@ -288,11 +297,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   const uint32_t tap_table = bar_base + (uint32_t)kBarrierBytes;  // A_MODE 3 only
-  if (A_MODE == 3 && warp >= 10) {
+  if (A_MODE == 3 && warp >= kGatherWarp0) {
     // entry k: filter row and column of the tap in the top byte (4 bits each, 0xff =
     // padding beyond K), element offset of (tap, channel) from the tile pixel's top-left
     // input element in the low 24 bits
-    for (int k = threadIdx.x - 320; k < g.k_steps * BK; k += 128) {
+    for (int k = threadIdx.x - kGatherThread0; k < g.k_steps * BK; k += 128) {
       uint32_t e = 0xff000000u;  // padding beyond K, always zero
       if (g.patch_cap > 0) {
         // staged-row mode: filter row in the top byte (31 = padding), offset of the
@@ -416,16 +425,19 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         if (alive) tc_commit(tfull_bar(acc));
       }
     }
-  } else if (warp < 10) {
+  } else if (warp < kGatherWarp0) {
     // ----------------------------------------------------------- epilogue --
     // Each warp owns 32 rows of the tile.  A 32-column chunk comes out of TMEM
     // with one row per lane; it is staged through a swizzled 4 KB shared-memory
     // tile so that the global stores run along rows: full 128-byte lines, or one
     // contiguous run when the tile spans the whole row.
-    // Two warps share each TMEM lane quarter and take alternate chunks (alternate
-    // tiles when a tile is a single chunk wide).
-    const int q = warp & 3;           // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2; // 0: even chunks, 1: odd chunks
+    // EW / 4 warps share each TMEM lane quarter and take the chunks of a tile in turn
+    // (tiles in turn when a tile has fewer chunks than that).
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int part = (warp - 2) >> 2;  // which of the quarter's warps this is
+    constexpr int kChunk0Mod = C::EPI_C >= C::EPI_P ? C::EPI_P : C::EPI_C;
+    const int my_c0 = (part % kChunk0Mod) * 32;       // first chunk this warp takes
+    const int my_group = part / kChunk0Mod;           // tiles with it % EPI_G == my_group
     const uint32_t stage_base = epi_base + (uint32_t)(warp - 2) * (C::EPI_BUFS * 4096u);
     uint32_t ebuf = 0;
     const uint32_t sw = (uint32_t)(lane & 7);
@@ -433,7 +445,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     // Residual prefetch (RES): a cursor runs one chunk ahead of the loop below over
     // the same (tile, chunk) sequence; lane 0 asks the TMA unit for the residual
     // 32 x 32 tile of that chunk, into the staging tile the chunk will use.
-    const int first_c0 = BN == 32 ? 0 : half * 32;
+    const int first_c0 = my_c0;
     int p_tile = blockIdx.x, p_it = 0, p_c0 = first_c0;
     uint32_t rphase = 0;       // bit b: parity the next wait on res_bar(b) uses
     bool res_issued = false;   // a load into the current staging tile is in flight
@@ -441,10 +453,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       if (!g.residual) return false;  // this instantiation also serves as the two-buffer epilogue
       while (p_tile < g.total_tiles) {
         const int n0 = (p_tile % g.tiles_n) * BN + p_c0;
-        if (!(BN == 32 && (p_it & 1) != half) && p_c0 < BN && n0 < g.N) {
+        if (!(C::EPI_G > 1 && (p_it % C::EPI_G) != my_group) && p_c0 < BN && n0 < g.N) {
           const int rest = p_tile / g.tiles_n;
           const int m_base = (rest % g.tiles_m) * BM + q * 32;
-          p_c0 += 64;
+          p_c0 += C::EPI_STEP;
           if (m_base >= g.M) return false;  // rows beyond the tensor: nothing to add
           if (lane == 0) {
             const uint32_t bar = res_bar(warp - 2, b);
@@ -468,9 +480,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int bz = rest / g.tiles_m;
       const int acc = it % ACC;
       const uint32_t aphase = (it / ACC) & 1;
-      if (BN == 32 && (it & 1) != half) continue;  // the other warp of the pair takes it
+      if (C::EPI_G > 1 && (it % C::EPI_G) != my_group) continue;  // another warp's tile
       // the first chunk's bias travels while the tile's MMAs finish
-      float bj = chunk_bias(g, nt * BN + (BN == 32 ? 0 : half * 32), lane);
+      float bj = chunk_bias(g, nt * BN + my_c0, lane);
       if (!mbar_wait(tfull_bar(acc), aphase)) {
         if (lane == 0) atomicExch(g.flag, 4);
         // let the residual load in flight land before this CTA's shared memory goes
@@ -485,13 +497,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       const float* rbase = g.residual + ((long long)bz * g.M + m_base) * g.N;
       bool released = false;
 #pragma unroll 1
-      for (int c0 = BN == 32 ? 0 : half * 32; c0 < BN; c0 += 64) {
+      for (int c0 = my_c0; c0 < BN; c0 += C::EPI_STEP) {
         const int n0 = nt * BN + c0;
         if (n0 >= g.N) break;
         const int w = g.N - n0 < 32 ? g.N - n0 : 32;
         float v[32];
         tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), v);
-        if (c0 + 64 >= BN || n0 + 64 >= g.N) {
+        if (c0 + C::EPI_STEP >= BN || n0 + C::EPI_STEP >= g.N) {
           // last read of this accumulator by this warp: hand it back early
           tc_fence_before();
           __syncwarp();
@@ -499,7 +511,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           released = true;
         }
         chunk_math_dispatch(v, g, n0, bj);
-        if (c0 + 64 < BN) bj = chunk_bias(g, n0 + 64, lane);  // next chunk's, ahead of its use
+        if (c0 + C::EPI_STEP < BN) bj = chunk_bias(g, n0 + C::EPI_STEP, lane);  // next chunk's
         const uint32_t stage_buf = stage_base + ebuf * 4096u;
         const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
         if (RES) {
@@ -650,7 +662,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     // (nearest-even, the rounding the TMA unit applies to the other operands) and
     // stores them in the 128-byte-swizzled layout.  The loads of step i+1 are
     // issued before the stores of step i, so two steps are in flight per thread.
-    const int r = threadIdx.x - 320;
+    const int r = threadIdx.x - kGatherThread0;
     const ConvGeo& cv = g.conv;
     const uint32_t row_off = (uint32_t)r * 128u;
     const uint32_t sw = (uint32_t)(r & 7);
@@ -726,7 +738,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     }
   }
 
-  else if (A_MODE == 3 && warp >= 10) {
+  else if (A_MODE == 3 && warp >= kGatherWarp0) {
     // ------------------------------------------- scalar im2col gatherers --
     // For inputs whose channel count is not a multiple of 4 (the 3-channel stems).
     // Warp gw builds rows 32 gw .. 32 gw + 31 of the A tile.  Within a K step lane l
@@ -736,7 +748,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     // comes from the tap table, the geometry of the warp's 32 rows from a small
     // per-warp table rebuilt at every tile; taps outside the image read as zero and
     // values are rounded to TF32.
-    const int gw = warp - 10;
+    const int gw = warp - kGatherWarp0;
     const ConvGeo& cv = g.conv;
     const uint32_t row_tab = tap_table + (uint32_t)kTapTableEntries * 4u + (uint32_t)gw * 512u;
     const uint32_t kpos = ((uint32_t)lane & 3u) * 4u;
@@ -783,7 +795,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       const int zero_off = g.patch_rows * pitch;
       {
         const uint32_t z = 0u;
-        for (uint32_t o = (uint32_t)(threadIdx.x - 320) * 16u;
+        for (uint32_t o = (uint32_t)(threadIdx.x - kGatherThread0) * 16u;
              o < (uint32_t)nb * (uint32_t)g.patch_cap;
              o += 128u * 16u)
           asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(patch_base + o), "r"(z)
@@ -1080,11 +1092,11 @@ bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv) {
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, int B_MN, int A_MODE, int RES = 0>
+template <int BN, int B_MN, int A_MODE, int RES = 0, int EW = 8>
 int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                const CUtensorMap& tm_c, const CUtensorMap& tm_r, Tf32Args& g) {
-  using C = Cfg<BN, A_MODE, RES>;
-  auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE, RES>;
+  using C = Cfg<BN, A_MODE, RES, EW>;
+  auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE, RES, EW>;
   static bool configured[64] = {false};  // per device ordinal
   // the scalar-gather mode adds its two input patches to the fixed layout
   int smem = C::SMEM_BYTES;
@@ -1099,19 +1111,19 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
   g.tiles_n = (g.N + BN - 1) / BN;
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
-  kern<<<grid, (A_MODE == 1 || A_MODE == 3) ? 448 : 320, smem, ctx->stream>>>(tm_a, tm_b, tm_c, tm_r, g);
+  kern<<<grid, C::THREADS, smem, ctx->stream>>>(tm_a, tm_b, tm_c, tm_r, g);
   LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
   return TFJS_CUDA_OK;
 }
 
-template <int B_MN, int A_MODE, int RES = 0>
+template <int B_MN, int A_MODE, int RES = 0, int EW = 8>
 int launch_bn(tfjs_cuda_ctx* ctx, int bn, const CUtensorMap& a, const CUtensorMap& b,
               const CUtensorMap& c, const CUtensorMap& r, Tf32Args& g) {
   switch (bn) {
-    case 32: return launch_cfg<32, B_MN, A_MODE, RES>(ctx, a, b, c, r, g);
-    case 64: return launch_cfg<64, B_MN, A_MODE, RES>(ctx, a, b, c, r, g);
-    case 128: return launch_cfg<128, B_MN, A_MODE, RES>(ctx, a, b, c, r, g);
-    default: return launch_cfg<256, B_MN, A_MODE, RES>(ctx, a, b, c, r, g);
+    case 32: return launch_cfg<32, B_MN, A_MODE, RES, EW>(ctx, a, b, c, r, g);
+    case 64: return launch_cfg<64, B_MN, A_MODE, RES, EW>(ctx, a, b, c, r, g);
+    case 128: return launch_cfg<128, B_MN, A_MODE, RES, EW>(ctx, a, b, c, r, g);
+    default: return launch_cfg<256, B_MN, A_MODE, RES, EW>(ctx, a, b, c, r, g);
   }
 }
 
@@ -1249,11 +1261,18 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
       tm_a = tm_b;  // unused by the gather kernel
       return launch_bn<0, 3>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }
+    // Few K steps per tile: the kernel is a stream of epilogues, whose per-chunk chain
+    // (TMEM load, bias / activation, staging, bulk store) is latency-bound with two warps
+    // per TMEM lane quarter; these launches run four.
+    static int no_ew16 = -1;
+    if (no_ew16 < 0) no_ew16 = getenv("TFJS_CUDA_NO_WIDE_EPILOGUE") ? 1 : 0;  // debugging knob
+    const bool wide = !no_ew16 && !pr.residual && op.k_steps <= 4;
     if (im2col) {
       if (res_tma) {
         g.c_tma = 1;
         return launch_bn<0, 2, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
       }
+      if (wide) return launch_bn<0, 2, 0, 16>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
       return launch_bn<0, 2>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }
     if (op.a_gather) {
@@ -1264,6 +1283,7 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
       g.c_tma = 1;
       return launch_bn<0, 0, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }
+    if (wide) return launch_bn<0, 0, 0, 16>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
   }
   if ((rc = make_map(ctx, &tm_b, op.b, (uint64_t)pr.N, (uint64_t)pr.K,
