@@ -1264,9 +1264,9 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     // Few K steps per tile: the kernel is a stream of epilogues, whose per-chunk chain
     // (TMEM load, bias / activation, staging, bulk store) is latency-bound with two warps
     // per TMEM lane quarter; these launches run four.
-    static int no_ew16 = -1;
-    if (no_ew16 < 0) no_ew16 = getenv("TFJS_CUDA_NO_WIDE_EPILOGUE") ? 1 : 0;  // debugging knob
-    const bool wide = !no_ew16 && !pr.residual && op.k_steps <= 4;
+    static int ew16 = -1;
+    if (ew16 < 0) ew16 = getenv("TFJS_CUDA_WIDE_EPILOGUE") ? 1 : 0;  // opt-in knob
+    const bool wide = ew16 && !pr.residual && op.k_steps <= 4;
     if (im2col) {
       if (res_tma) {
         g.c_tma = 1;
