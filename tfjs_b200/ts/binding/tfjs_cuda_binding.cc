@@ -124,6 +124,13 @@ napi_value FusedElementwise(napi_env env, napi_callback_info info) {
   auto* p = static_cast<tfjs_cuda_ew_program*>(a.buffer(1));   // packed program struct
   return check(env, a.ctx(0), tfjs_cuda_fused_elementwise(a.ctx(0), p, a.i32(2)));
 }
+napi_value FusedElementwiseCatalogued(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  auto* p = static_cast<tfjs_cuda_ew_program*>(a.buffer(1));
+  int32_t yes = 0;
+  check(env, a.ctx(0), tfjs_cuda_fused_elementwise_catalogued(a.ctx(0), p, &yes));
+  return num(env, yes);
+}
 napi_value DecodeFloat16(napi_env env, napi_callback_info info) {
   Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_decode_float16(a.ctx(0), a.i32(1), a.u64(2), a.i32(3)));
 }
@@ -246,7 +253,8 @@ napi_value DequantizeStatic(napi_env env, napi_callback_info info) {
 napi_value Init(napi_env env, napi_value exports) {
   struct { const char* name; napi_callback fn; } table[] = {
       {"create", Create}, {"alloc", Alloc}, {"free", Free}, {"write", Write}, {"read", Read},
-      {"fusedElementwise", FusedElementwise}, {"decodeFloat16", DecodeFloat16}, {"captureBegin", CaptureBegin}, {"captureEnd", CaptureEnd}, {"graphLaunch", GraphLaunch},
+      {"fusedElementwise", FusedElementwise},
+      {"fusedElementwiseCatalogued", FusedElementwiseCatalogued}, {"decodeFloat16", DecodeFloat16}, {"captureBegin", CaptureBegin}, {"captureEnd", CaptureEnd}, {"graphLaunch", GraphLaunch},
       {"graphDestroy", GraphDestroy}, {"copy", Copy}, {"highWaterReset", HighWaterReset},
       {"readBegin", ReadBegin}, {"readWait", ReadWait}, {"sync", Sync}, {"memory", Memory}, {"timeBegin", TimeBegin}, {"timeEnd", TimeEnd},
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},

@@ -14,6 +14,7 @@ export interface CudaBinding {
   write(ctx: Ctx, id: number, data: ArrayBufferView, nbytes: number): void;
   read(ctx: Ctx, id: number, out: ArrayBufferView, nbytes: number): void;
   fusedElementwise(ctx: Ctx, program: ArrayBuffer, out: number): void;
+  fusedElementwiseCatalogued(ctx: Ctx, program: ArrayBuffer): number;
   decodeFloat16(ctx: Ctx, q: number, n: number, out: number): void;
   captureBegin(ctx: Ctx, arenaBytes: number): void;
   captureEnd(ctx: Ctx, abandon: number): number;
