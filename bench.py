@@ -10,12 +10,17 @@ and inputs are seeded synthetic tensors of the published shapes.  With N > 1
 every rank runs its own backend on its own GPU with its own batch (weak
 scaling, no collective on the data path); rank 0 prints one JSON line.
 
-value      device-timed throughput with the input batch resident in HBM.
+value      device-timed throughput with the input batch resident in HBM.  The timed
+           steps are replays of the step captured during warm-up (GraphModel's
+           whole-step replay; --no-replay launches every kernel from the host).
 e2e        the same metric through the public API with HOST buffers: every step
-           uploads the batch from pinned memory and downloads the logits.
+           uploads the batch from pinned memory (copy stream) and downloads the
+           logits with tensor.data(); batch i+1 is uploaded and launched before the
+           result of batch i is awaited, every result is awaited in the timed region.
 roofline   for the kernel kind that takes the most device time, from CUDA events
            recorded around every kernel on the launching stream during extra
-           profiled steps (tf.profile-style) right after the timed region.
+           eagerly launched steps (tf.profile-style) right after the timed region;
+           HBM-bound kinds also carry the fraction of the nominal 8 TB/s.
 cpu_baseline  the CPU oracle (a C restatement of tfjs-backend-cpu) on a bounded
            sample of the same workload.
 """
@@ -394,7 +399,8 @@ def run_cuda(args, rank, world, local_rank):
         else:
             roof.update(bound="hbm", achieved=tk["gbs"], peak=pk["hbm"], unit="GB/s",
                         frac=round(tk["gbs"] / pk["hbm"], 4),
-                        peak_source="%s copy bandwidth" % pk["source"])
+                        peak_source="%s copy bandwidth" % pk["source"],
+                        frac_of_nominal_8tbs=round(tk["gbs"] / 8000.0, 4))
         units = batch * world
         value = units * args.steps / (dev_ms / 1e3)
         line = {"metric": w["metric"], "value": round(value, 2), "unit": w["unit"],
