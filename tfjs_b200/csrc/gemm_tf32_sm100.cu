@@ -1264,9 +1264,11 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     // Few K steps per tile: the kernel is a stream of epilogues, whose per-chunk chain
     // (TMEM load, bias / activation, staging, bulk store) is latency-bound with two warps
     // per TMEM lane quarter; these launches run four.
-    static int ew16 = -1;
-    if (ew16 < 0) ew16 = getenv("TFJS_CUDA_WIDE_EPILOGUE") ? 1 : 0;  // opt-in knob
-    const bool wide = ew16 && !pr.residual && op.k_steps <= 4;
+    static int wide_k = -1;  // widest K (in 32-float steps) that takes the 16-warp epilogue
+    if (wide_k < 0)
+      wide_k = getenv("TFJS_CUDA_WIDE_EPILOGUE_KSTEPS") ? atoi(getenv("TFJS_CUDA_WIDE_EPILOGUE_KSTEPS"))
+                                                        : 8;  // tuning knob, 0 switches it off
+    const bool wide = !pr.residual && op.k_steps <= wide_k;
     if (im2col) {
       if (res_tma) {
         g.c_tma = 1;
