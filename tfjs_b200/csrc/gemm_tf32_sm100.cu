@@ -214,16 +214,20 @@ constexpr int kBarrierBytes = 640;  // pipeline barriers, TMEM slot, residual ba
 template <int BN, int A_MODE = 0, int RES = 0, int EW = 8>
 struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 4;
-  // the scalar-gather mode runs three stages: its shared memory goes to the tap and
-  // row tables and to the two staged input patches; sixteen epilogue warps (EW = 16,
-  // short-K launches) take one stage at BN = 256 for their staging tiles
+  // staging tiles per epilogue warp: two (a warp fills one while the TMA unit still
+  // drains the other, and the residual epilogue prefetches into the other one), one at
+  // BN = 256 without residual, in the scalar-gather mode and with sixteen warps
+  static constexpr int EPI_BUFS =
+      RES ? 2 : (((BN >= 256 || A_MODE == 3) || EW == 16) ? 1 : 2);
+  // pipeline stages: as many as fit beside the staging tiles, up to 4 / 5 / 6 / 8 by tile
+  // width; the scalar-gather mode keeps room for its tables and the staged input rows
+  static constexpr int STAGES_WANTED = BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 6 : 8));
+  static constexpr int STAGES_FIT =
+      (kMaxSmemBytes - 1024 - kBarrierBytes - EW * EPI_BUFS * 4096) /
+      (A_STAGE_BYTES + B_STAGE_BYTES);
   static constexpr int STAGES =
       A_MODE == 3 ? (BN == 32 ? 5 : (BN == 64 ? 4 : 3))
-                  : (BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 6 : 8))) -
-                        ((RES || EW == 16) && BN >= 256 ? 1 : 0);
-  // staging tiles per epilogue warp: two below BN = 256 (bandwidth-bound shapes), so
-  // a warp fills one while the TMA unit still drains the other; one with sixteen warps
-  static constexpr int EPI_BUFS = (((BN >= 256 && !RES) || A_MODE == 3) || EW == 16) ? 1 : 2;
+                  : (STAGES_FIT < STAGES_WANTED ? STAGES_FIT : STAGES_WANTED);
   // TMEM accumulator stages.  A tile's accumulator is handed back and forth through
   // two barriers whose wake-ups cost more than a short tile's MMAs, so narrow tiles
   // (few K steps in practice) keep more tiles in flight: 256 columns at BN <= 128.
@@ -1269,9 +1273,15 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
       wide_k = getenv("TFJS_CUDA_WIDE_EPILOGUE_KSTEPS") ? atoi(getenv("TFJS_CUDA_WIDE_EPILOGUE_KSTEPS"))
                                                         : 8;  // tuning knob, 0 switches it off
     const bool wide = !pr.residual && op.k_steps <= wide_k;
+    static int wide_res_k = -1;  // the same bound for the residual epilogue
+    if (wide_res_k < 0)
+      wide_res_k = getenv("TFJS_CUDA_WIDE_RESIDUAL_KSTEPS")
+                       ? atoi(getenv("TFJS_CUDA_WIDE_RESIDUAL_KSTEPS")) : 8;  // tuning knob
     if (im2col) {
       if (res_tma) {
         g.c_tma = 1;
+        if (op.k_steps <= wide_res_k)
+          return launch_bn<0, 2, 1, 16>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
         return launch_bn<0, 2, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
       }
       if (wide) return launch_bn<0, 2, 0, 16>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
@@ -1283,6 +1293,8 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     }
     if (res_tma) {
       g.c_tma = 1;
+      if (op.k_steps <= wide_res_k)
+        return launch_bn<0, 0, 1, 16>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
       return launch_bn<0, 0, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }
     if (wide) return launch_bn<0, 0, 0, 16>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
