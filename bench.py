@@ -268,6 +268,8 @@ def run_reference(args, rank, world):
 # ----------------------------------------------------------------------- cuda --
 def run_cuda(args, rank, world, local_rank):
     os.environ["TFJS_CUDA_DEVICE_ORDINAL"] = str(local_rank)
+    from tfjs_b200.replicas import bind_to_gpu_cpus
+    near_cpus = bind_to_gpu_cpus(local_rank) if world > 1 else None
     import tfjs_b200
     from tfjs_b200.graph_model import GraphModel
     eng = tfjs_b200.ENGINE
@@ -411,6 +413,7 @@ def run_cuda(args, rank, world, local_rank):
                            "global_batch": units, "parallelism": "replicas x%d" % world,
                            "l2": "activations per step are far larger than L2",
                            "step_replay": bool(gm.replay),
+                           "cpu_binding": ("GPU-local cores" if near_cpus else "none"),
                            "weights": "random init"},
                 "host_ms_per_step": round(host_ms / args.steps, 4),
                 "tflops": round(units * w["gflop"] / 1e3 / (dev_ms / args.steps / 1e3), 2),

@@ -22,6 +22,31 @@ def shard_range(total, world, rank):
     return lo, min(lo + per, total)
 
 
+def bind_to_gpu_cpus(device_ordinal):
+    """Pins this process to the CPU cores that share a NUMA node with its GPU, before any
+    pinned host memory is allocated, so that a replica's staging buffers and its
+    host-to-device copies stay on the GPU's own socket (with eight replicas on a
+    two-socket host, half of them would otherwise cross the inter-socket link).  Uses
+    NVML's read-only affinity query; returns the chosen cores, or None when NVML or the
+    query is unavailable or none of those cores is usable by this process (a container
+    confined to one socket)."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(int(device_ordinal))
+        allowed = os.sched_getaffinity(0)
+        words = (max(allowed) // 64) + 1
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        near = set(i * 64 + b for i, w in enumerate(mask) for b in range(64) if (w >> b) & 1)
+        cores = sorted(near & allowed)
+        if not cores:
+            return None
+        os.sched_setaffinity(0, cores)
+        return cores
+    except Exception:
+        return None
+
+
 class ReplicaGroup(object):
     def __init__(self, rank=None, world=None):
         self.rank = int(os.environ.get("RANK", "0")) if rank is None else rank
