@@ -69,6 +69,11 @@ CONV_CASES = {
     "prelu_scalar_nobias": lambda: conv_case(14, (1, 8, 8, 32), (3, 3, 32, 32), bias=False, act="prelu", prelu="scalar"),
     "wide_cout256": lambda: conv_case(15, (2, 14, 14, 256), (3, 3, 256, 256)),
     "cin5_simt_route": lambda: conv_case(16, (1, 9, 9, 5), (2, 2, 5, 7), pad="valid"),
+    # long K, <= 128 output channels: the form with the pixels on the MMA's N axis
+    "narrow_1x1_k416_cout100": lambda: conv_case(17, (3, 10, 11, 416), (1, 1, 416, 100), act="linear"),
+    "narrow_3x3_cout96_ragged": lambda: conv_case(18, (3, 21, 23, 64), (3, 3, 64, 96), act="relu6"),
+    "narrow_dilated_nobias": lambda: conv_case(19, (1, 20, 20, 64), (3, 3, 64, 32), dilations=2, bias=False, act="sigmoid"),
+    "narrow_s2_valid_cout4": lambda: conv_case(20, (2, 15, 15, 128), (3, 3, 128, 4), strides=2, pad="valid"),
 }
 
 

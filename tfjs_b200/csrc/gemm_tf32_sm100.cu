@@ -13,6 +13,10 @@
 //               straight from the NHWC input (zeros for taps outside the image),
 //               rounded to TF32 and stored in the same swizzled layout TMA would
 //               produce.
+// Convolutions with at most 128 output channels and a long K run with the operands
+// swapped (A_MODE 4 / 5): the packed filter is the MMA's 128-row operand and 256
+// output pixels its N axis, because a tcgen05.mma takes the same time at N = 64 as
+// at N = 256; the epilogue transposes the [channel][pixel] accumulator while staging.
 // Two TMEM accumulators alternate so the epilogue of tile i overlaps the main
 // loop of tile i+1.  Every mbarrier wait is bounded: when it gives up the kernel
 // records a code in the context's error word and drains.
@@ -148,8 +152,9 @@ __device__ __forceinline__ float chunk_bias(const Tf32Args& g, int n0, int lane)
 }
 
 template <int ACT>
-__device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, float bj) {
-  if (g.bias_len != 0) {
+__device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, float bj,
+                                           bool skip_bias = false) {
+  if (g.bias_len != 0 && !skip_bias) {
     // lane j holds the bias of column n0 + j; every thread owns a row of 32 columns
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __shfl_sync(0xffffffffu, bj, j));
@@ -178,15 +183,15 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, 
 }
 
 __device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g, int n0,
-                                                    float bj) {
+                                                    float bj, bool skip_bias = false) {
   switch (g.ap.act) {
-    case TFJS_CUDA_ACT_RELU: chunk_math<TFJS_CUDA_ACT_RELU>(v, g, n0, bj); break;
-    case TFJS_CUDA_ACT_RELU6: chunk_math<TFJS_CUDA_ACT_RELU6>(v, g, n0, bj); break;
-    case TFJS_CUDA_ACT_PRELU: chunk_math<TFJS_CUDA_ACT_PRELU>(v, g, n0, bj); break;
-    case TFJS_CUDA_ACT_LEAKYRELU: chunk_math<TFJS_CUDA_ACT_LEAKYRELU>(v, g, n0, bj); break;
-    case TFJS_CUDA_ACT_SIGMOID: chunk_math<TFJS_CUDA_ACT_SIGMOID>(v, g, n0, bj); break;
-    case TFJS_CUDA_ACT_ELU: chunk_math<TFJS_CUDA_ACT_ELU>(v, g, n0, bj); break;
-    default: chunk_math<TFJS_CUDA_ACT_LINEAR>(v, g, n0, bj); break;
+    case TFJS_CUDA_ACT_RELU: chunk_math<TFJS_CUDA_ACT_RELU>(v, g, n0, bj, skip_bias); break;
+    case TFJS_CUDA_ACT_RELU6: chunk_math<TFJS_CUDA_ACT_RELU6>(v, g, n0, bj, skip_bias); break;
+    case TFJS_CUDA_ACT_PRELU: chunk_math<TFJS_CUDA_ACT_PRELU>(v, g, n0, bj, skip_bias); break;
+    case TFJS_CUDA_ACT_LEAKYRELU: chunk_math<TFJS_CUDA_ACT_LEAKYRELU>(v, g, n0, bj, skip_bias); break;
+    case TFJS_CUDA_ACT_SIGMOID: chunk_math<TFJS_CUDA_ACT_SIGMOID>(v, g, n0, bj, skip_bias); break;
+    case TFJS_CUDA_ACT_ELU: chunk_math<TFJS_CUDA_ACT_ELU>(v, g, n0, bj, skip_bias); break;
+    default: chunk_math<TFJS_CUDA_ACT_LINEAR>(v, g, n0, bj, skip_bias); break;
   }
 }
 
@@ -252,6 +257,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_r, const Tf32Args g) {
   using C = Cfg<BN, A_MODE, RES, EW>;
   constexpr int STAGES = C::STAGES;
+  // A_MODE 4 / 5: operands swapped for narrow outputs (N <= 128).  A tcgen05.mma takes the
+  // same time whatever its N, so the weights become the 128-row operand and 256 output
+  // pixels the N axis: half the MMAs per pixel.  The accumulator is then [channel][pixel]
+  // and the epilogue transposes it back while staging.  LOAD is how the pixel operand is
+  // fetched (0 tiled TMA, 2 TMA im2col), as in modes 0 and 2.
+  constexpr bool SWAP = A_MODE >= 4;
+  constexpr int LOAD = SWAP ? (A_MODE == 4 ? 0 : 2) : A_MODE;
+  constexpr int kTileRows = SWAP ? 256 : BM;    // output pixels (GEMM rows) per tile
+  static_assert(!SWAP || (BN == 256 && !RES && !B_MN), "swapped operands: 256-pixel tiles only");
   constexpr int kGatherWarp0 = 2 + EW;          // first gather warp (A_MODE 1 and 3)
   constexpr int kGatherThread0 = 64 + EW * 32;  // its first thread
   extern __shared__ uint8_t smem_raw[];
@@ -345,8 +359,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         const int mt = rest % g.tiles_m;
         const int bz = rest / g.tiles_m;
         int pix_w = 0, pix_h = 0, pix_n = 0;
-        if (A_MODE == 2) {
-          const int m0 = mt * BM;
+        if (LOAD == 2) {
+          const int m0 = mt * kTileRows;
           const int ow = m0 % g.conv.out_w;
           const int t = m0 / g.conv.out_w;
           pix_w = ow * g.conv.s_w - g.conv.pad_l;
@@ -361,6 +375,23 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
           const uint32_t fb = full_bar(stage);
           mbar_expect_tx(fb, ((A_MODE == 1 || A_MODE == 3) ? 0 : A_STAGE_BYTES) + C::B_STAGE_BYTES);
+          if (SWAP) {
+            // weights (all N <= 128 rows, zero-filled beyond) into the 128-row operand
+            // slot, 256 pixels into the wide one
+            tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_b, fb, ks * BK, 0, bz % g.batch_b);
+            const uint32_t pdst = b_base + stage * C::B_STAGE_BYTES;
+            if (LOAD == 0) {
+              tma_load_3d(pdst, &tm_a, fb, ks * BK, mt * kTileRows, bz % g.batch_a);
+            } else {
+              const int tap = ks / g.chunks_per_tap;
+              const int cc = (ks - tap * g.chunks_per_tap) * BK;
+              const int fr = tap / g.conv.f_w, fc = tap - fr * g.conv.f_w;
+              tma_load_im2col(pdst, &tm_a, fb, cc, pix_w, pix_h, pix_n,
+                              (uint16_t)(fc * g.conv.d_w), (uint16_t)(fr * g.conv.d_h));
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (A_MODE == 0) {
             tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_a, fb, ks * BK, mt * BM,
                         bz % g.batch_a);
@@ -439,6 +470,66 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
     // (tiles in turn when a tile has fewer chunks than that).
     const int q = warp & 3;            // TMEM lane quarter this warp may read
     const int part = (warp - 2) >> 2;  // which of the quarter's warps this is
+    if (SWAP) {
+      // Accumulator rows are output channels (lane = channel 32 q + lane), columns are
+      // the tile's 256 pixels.  A chunk is 32 pixels x 32 channels: the lane adds its
+      // channel's bias, applies the activation and writes its 32 values down a column of
+      // the staging tile, which is then a [pixel][channel] box for the bulk store.
+      const int ch0 = q * 32;
+      const bool ch_ok = ch0 < g.N;
+      float bch = 0.0f;
+      if (ch_ok && g.bias_len == 1) bch = __ldg(g.bias);
+      else if (ch_ok && g.bias_len > 1 && ch0 + lane < g.N) bch = __ldg(g.bias + ch0 + lane);
+      const uint32_t stage_buf = epi_base + (uint32_t)(warp - 2) * (C::EPI_BUFS * 4096u);
+      const uint32_t col = (((uint32_t)lane >> 2)), word = ((uint32_t)lane & 3u) * 4u;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < g.total_tiles; tile += gridDim.x, ++it) {
+        const int rest = tile / g.tiles_n;
+        const int mt = rest % g.tiles_m;
+        const int bz = rest / g.tiles_m;
+        const int acc = it % ACC;
+        const uint32_t aphase = (it / ACC) & 1;
+        if (!mbar_wait(tfull_bar(acc), aphase)) {
+          if (lane == 0) atomicExch(g.flag, 4);
+          break;
+        }
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = part * 32; c0 < 256; c0 += C::EPI_P * 32) {
+          const int m0 = mt * 256 + c0;
+          if (!ch_ok || m0 >= g.M) continue;
+          float v[32];
+          tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), v);
+          if (g.bias_len != 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], bch);
+          }
+          chunk_math_dispatch(v, g, 0, 0.0f, true);
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(
+                             stage_buf + (uint32_t)j * 128u + ((col ^ (uint32_t)(j & 7)) << 4) + word),
+                         "f"(v[j])
+                         : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile(
+                "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                ::"l"(&tm_c), "r"(stage_buf), "r"(ch0), "r"(m0), "r"(bz)
+                : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        // every chunk of this tile has left TMEM
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+      }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    } else {
     constexpr int kChunk0Mod = C::EPI_C >= C::EPI_P ? C::EPI_P : C::EPI_C;
     const int my_c0 = (part % kChunk0Mod) * 32;       // first chunk this warp takes
     const int my_group = part / kChunk0Mod;           // tiles with it % EPI_G == my_group
@@ -659,6 +750,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       }
     }
     if (g.c_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }  // !SWAP
   } else if (A_MODE == 1) {
     // ----------------------------------------------------- im2col gatherers --
     // Thread r owns row r of every A tile.  Each K step it reads 32 channels of
@@ -1061,7 +1153,7 @@ typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 // im2col map over NHWC x: dims (C, W, H, N); 32 channels x 128 pixels per load;
 // the pixel bounding box starts at -pad and ends where the last filter tap still
 // fits, and pixels are traversed with the convolution stride.
-bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv) {
+bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv, int pixels = BM) {
   static EncodeIm2colFn enc = nullptr;
   if (!enc) {
     void* p = nullptr;
@@ -1090,7 +1182,7 @@ bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv) {
                            (cuuint64_t)cv.in_h * cv.in_w * cv.in_c * 4};
   cuuint32_t estr[4] = {1, (cuuint32_t)cv.s_w, (cuuint32_t)cv.s_h, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void*)x, dims, strides, lower,
-                   upper, BK, BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   upper, BK, (cuuint32_t)pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -1242,9 +1334,40 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     }
   }
   bool im2col = false;
+  static int no_im2col = -1;
+  if (no_im2col < 0) no_im2col = getenv("TFJS_CUDA_NO_IM2COL_TMA") ? 1 : 0;  // debugging knob
+  // Narrow outputs with a long K: a tcgen05.mma takes the same time for 64 output
+  // columns as for 256, so put the pixels on the instruction's N axis (256 per tile)
+  // and the <= 128 output channels on its 128 rows.
+  // Measured on 3x3 convolutions at batch 128: 64 -> 64 at 56x56 153 -> 95 us, 128 -> 128 at
+  // 28x28 88 -> 56 us; with fewer than about 12 K steps the epilogue dominates and the two
+  // forms tie.
+  static int swap_k = -1;  // fewest K steps that take the swapped form; 0 switches it off
+  if (swap_k < 0)
+    swap_k = getenv("TFJS_CUDA_SWAP_AB_KSTEPS") ? atoi(getenv("TFJS_CUDA_SWAP_AB_KSTEPS")) : 12;
+  if (swap_k > 0 && op.k_steps >= swap_k && op.b_layout == B_K_MAJOR && pr.N <= 128 &&
+      g.c_tma && !pr.residual && pr.ap.act != TFJS_CUDA_ACT_PRELU &&
+      (op.a_gather == 0 || (op.a_gather == 1 && !no_im2col))) {
+    memset(&tm_a, 0, sizeof tm_a);
+    bool ok;
+    if (op.a_gather == 1) {
+      ok = make_im2col_map(&tm_a, op.a, pr.conv, 256);
+    } else {
+      ok = make_map(ctx, &tm_a, op.a, (uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.batch_a,
+                    (uint64_t)op.lda, (uint64_t)pr.M * op.lda, 256) == TFJS_CUDA_OK;
+    }
+    if (ok) {
+      const uint64_t kk = (uint64_t)op.k_steps * BK < (uint64_t)op.ldb
+                              ? (uint64_t)op.k_steps * BK : (uint64_t)op.ldb;
+      if ((rc = make_map(ctx, &tm_b, op.b, kk, (uint64_t)pr.N, (uint64_t)pr.batch_b,
+                         (uint64_t)op.ldb, (uint64_t)pr.N * op.ldb, (uint32_t)BM)))
+        return rc;
+      g.tiles_m = (pr.M + 255) / 256;
+      if (op.a_gather == 1) return launch_cfg<256, 0, 5>(ctx, tm_a, tm_b, tm_c, tm_r, g);
+      return launch_cfg<256, 0, 4>(ctx, tm_a, tm_b, tm_c, tm_r, g);
+    }
+  }
   if (op.a_gather == 1) {
-    static int no_im2col = -1;
-    if (no_im2col < 0) no_im2col = getenv("TFJS_CUDA_NO_IM2COL_TMA") ? 1 : 0;  // debugging knob
     memset(&tm_a, 0, sizeof tm_a);
     im2col = !no_im2col && make_im2col_map(&tm_a, op.a, pr.conv);
   } else if (op.a_gather >= 2) {
