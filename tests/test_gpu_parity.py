@@ -268,6 +268,27 @@ def test_unary(cuda_engine, op):
         assert np.max(np.abs(got[ok] - ref[ok]) / np.maximum(np.abs(ref[ok]), 1e-30)) <= 2.5e-7
 
 
+@pytest.mark.parametrize("op", ["erf", "exp", "sigmoid"])
+def test_unary_wide_range(cuda_engine, op):
+    """Magnitudes from 1e-9 to beyond the range where exp over- or underflows: the device
+    evaluates erf and exp with a shortened double sequence except near zero (erf) and
+    beyond +-700 (exp)."""
+    r = rng(55)
+    mag = 10.0 ** r.uniform(-9, 1.6 if op == "erf" else 2.0, 200000)
+    x = f32(mag * np.where(r.random(200000) < 0.5, -1.0, 1.0))
+    x[:8] = [np.nan, 0.0, -0.0, np.inf, -np.inf, 2.0 ** -13, -2.0 ** -13, 88.0]
+    case = {"op": op, "inputs": {"x": x}}
+    with np.errstate(over="ignore"):
+        got, ref = opcases.run_cuda(case), opcases.run_oracle(case)
+    assert np.array_equal(np.isnan(got), np.isnan(ref))
+    assert np.array_equal(np.isinf(got), np.isinf(ref))
+    ok = np.isfinite(ref)
+    assert np.array_equal(np.signbit(got[ok]), np.signbit(ref[ok]))
+    assert np.max(np.abs(got[ok] - ref[ok]) / np.maximum(np.abs(ref[ok]), 1e-37)) <= 2.5e-7
+    # the shortened sequence changes the rounding of very few results
+    assert np.mean(got[ok] != ref[ok]) < 1e-3
+
+
 def test_leakyrelu_clip(cuda_engine):
     x = f32(rng(6).standard_normal(5000) * 4)
     for case in ({"op": "leaky_relu", "inputs": {"x": x}, "attrs": {"alpha": 0.2}},

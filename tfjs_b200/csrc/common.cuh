@@ -155,6 +155,93 @@ struct ActParams {
   double alpha;         // leakyrelu
 };
 
+// exp(x) in double for results that are rounded to fp32 afterwards.  The library's exp
+// costs about twice the instructions for its last few bits; this one is good to ~2^-47
+// relative (Cody-Waite reduction by ln 2, Taylor series to r^11 on |r| <= ln 2 / 2), which
+// changes the fp32 rounding of about one result in 2^22.  Arguments beyond +-700 (and
+// NaN) take the library path.
+__device__ __forceinline__ double exp_fast(double x) {
+  if (!(fabs(x) <= 700.0)) return exp(x);
+  const double kMagic = 6755399441055744.0;  // 1.5 * 2^52: adding it rounds to an integer
+  const double t = fma(x, 1.4426950408889634074, kMagic);
+  const int n = __double2loint(t);
+  const double nd = t - kMagic;
+  double r = fma(nd, -6.93147180369123816490e-01, x);
+  r = fma(nd, -1.90821492927058770002e-10, r);
+  double p = 2.50521083854417187751e-08;          // 1/11!
+  p = fma(p, r, 2.75573192239858906526e-07);      // 1/10!
+  p = fma(p, r, 2.75573192239858906526e-06);      // 1/9!
+  p = fma(p, r, 2.48015873015873015873e-05);      // 1/8!
+  p = fma(p, r, 1.98412698412698412698e-04);      // 1/7!
+  p = fma(p, r, 1.38888888888888888889e-03);      // 1/6!
+  p = fma(p, r, 8.33333333333333333333e-03);      // 1/5!
+  p = fma(p, r, 4.16666666666666666667e-02);      // 1/4!
+  p = fma(p, r, 1.66666666666666666667e-01);      // 1/3!
+  p = fma(p, r, 0.5);
+  p = fma(p, r, 1.0);
+  p = fma(p, r, 1.0);
+  // p in [0.70, 1.42], |n| <= 1010: scaling by 2^n is an add to the exponent field
+  return __hiloint2double(__double2hiint(p) + (n << 20), __double2loint(p));
+}
+
+// erf as the reference evaluates it (tfjs-core/src/ops/erf_util.ts:18-23,
+// tfjs-backend-cpu/src/kernels/Erf.ts:31-39): Abramowitz-Stegun 7.1.26 in double, rounded
+// to fp32 once.  js_erf_exact is that sequence operation by operation.  1 - poly(t) * t *
+// exp(-v^2) cancels for small v, so the short form (approximate reciprocal with one Newton
+// step, exp_fast; relative error ~2^-45) serves 2^-13 <= |x| <= 26, where it leaves the
+// fp32 result within one part in 2^30 of the exact sequence; it has no branches, and
+// reports arguments outside that range (zero, NaN and infinity among them) through `slow`
+// for the caller to redo.
+__device__ __forceinline__ float js_erf_exact(float x) {
+  const double p = 0.3275911, a1 = 0.254829592, a2 = -0.284496736,
+               a3 = 1.421413741, a4 = -1.453152027, a5 = 1.061405429;
+  const double xd = (double)x;
+  const double v = fabs(xd);
+  const double sign = xd > 0.0 ? 1.0 : (xd < 0.0 ? -1.0 : xd);
+  // every product and sum rounded on its own, as JavaScript does (no contraction to
+  // FMA): near zero the result is the 1e-9 left over by the cancellation
+  const double t = 1.0 / __dadd_rn(1.0, __dmul_rn(p, v));
+  double q = __dadd_rn(__dmul_rn(a5, t), a4);
+  q = __dadd_rn(__dmul_rn(q, t), a3);
+  q = __dadd_rn(__dmul_rn(q, t), a2);
+  q = __dadd_rn(__dmul_rn(q, t), a1);
+  q = __dmul_rn(__dmul_rn(q, t), exp(-__dmul_rn(v, v)));
+  return (float)__dmul_rn(sign, __dadd_rn(1.0, -q));
+}
+__device__ __forceinline__ float js_erf_short(float x, bool& slow) {
+  const double p = 0.3275911, a1 = 0.254829592, a2 = -0.284496736,
+               a3 = 1.421413741, a4 = -1.453152027, a5 = 1.061405429;
+  const float ax = fabsf(x);
+  slow |= !(ax >= 0x1p-13f && ax <= 26.0f);
+  const double v = (double)fminf(ax, 26.0f);  // keeps -v^2 inside exp_fast's short range
+  const double d = fma(p, v, 1.0);
+  double t;
+  asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(t) : "d"(d));  // good to ~2^-23
+  t = fma(fma(-d, t, 1.0), t, t);
+  double q = fma(a5, t, a4);
+  q = fma(q, t, a3);
+  q = fma(q, t, a2);
+  q = fma(q, t, a1);
+  q *= t;
+  return copysignf((float)fma(-q, exp_fast(-v * v), 1.0), x);
+}
+// V values at once: the short form for all, the exact one again if any asked for it.
+template <int V>
+__device__ __forceinline__ void js_erf_vec(const float* a, float* r) {
+  bool slow = false;
+#pragma unroll
+  for (int t = 0; t < V; ++t) r[t] = js_erf_short(a[t], slow);
+  if (slow) {
+#pragma unroll  // (a rolled loop would index a[] and r[] and push them out of registers)
+    for (int t = 0; t < V; ++t) r[t] = js_erf_exact(a[t]);
+  }
+}
+__device__ __forceinline__ float js_erf(float x) {
+  float r;
+  js_erf_vec<1>(&x, &r);
+  return r;
+}
+
 __device__ __forceinline__ float js_relu(float v) {
   return v > 0.0f ? v : (v != v ? v : 0.0f);
 }
@@ -166,7 +253,7 @@ __device__ __forceinline__ float js_elu(float v) {
   return v >= 0.0f ? v : (float)(exp((double)v) - 1.0);
 }
 __device__ __forceinline__ float js_sigmoid(float v) {
-  return (float)(1.0 / (1.0 + exp(-(double)v)));
+  return (float)(1.0 / (1.0 + exp_fast(-(double)v)));
 }
 __device__ __forceinline__ float js_leakyrelu(float v, double alpha) {
   return v < 0.0f ? (float)(alpha * (double)v) : v;

@@ -26,7 +26,7 @@ __device__ __forceinline__ float unary_eval(float x, double p0, double p1) {
   if (OP == TFJS_CUDA_ELU) return js_elu(x);
   if (OP == TFJS_CUDA_SIGMOID) return js_sigmoid(x);
   if (OP == TFJS_CUDA_LEAKYRELU) return js_leakyrelu(x, p0);
-  if (OP == TFJS_CUDA_EXP) return (float)exp((double)x);
+  if (OP == TFJS_CUDA_EXP) return (float)exp_fast((double)x);
   if (OP == TFJS_CUDA_SQRT) return sqrtf(x);
   if (OP == TFJS_CUDA_RSQRT) return (float)(1.0 / sqrt((double)x));
   if (OP == TFJS_CUDA_SQUARE) return x * x;
@@ -36,18 +36,7 @@ __device__ __forceinline__ float unary_eval(float x, double p0, double p1) {
     const double v = (double)x;
     return (float)(v > p1 ? p1 : (v < p0 ? p0 : v));
   }
-  if (OP == TFJS_CUDA_ERF) {
-    // Abramowitz-Stegun 7.1.26 with the reference's constants
-    // (tfjs-core/src/ops/erf_util.ts:18-23; tfjs-backend-cpu/src/kernels/Erf.ts:31-39).
-    const double p = 0.3275911, a1 = 0.254829592, a2 = -0.284496736,
-                 a3 = 1.421413741, a4 = -1.453152027, a5 = 1.061405429;
-    const double xd = (double)x;
-    const double sign = xd > 0.0 ? 1.0 : (xd < 0.0 ? -1.0 : xd);
-    const double v = fabs(xd);
-    const double t = 1.0 / (1.0 + p * v);
-    return (float)(sign * (1.0 - (((((a5 * t + a4) * t) + a3) * t + a2) * t + a1) *
-                                     t * exp(-v * v)));
-  }
+  if (OP == TFJS_CUDA_ERF) return js_erf(x);
   if (OP == TFJS_CUDA_ABS) return fabsf(x);
   if (OP == TFJS_CUDA_LOG) return (float)log((double)x);
   return x;
@@ -63,6 +52,13 @@ __global__ void unary_kernel(const float* __restrict__ x, float* __restrict__ y,
   float4* y4 = reinterpret_cast<float4*>(y);
   for (uint64_t i = tid; i < n4; i += stride) {
     float4 v = x4[i];
+    if (OP == TFJS_CUDA_ERF) {
+      const float in[4] = {v.x, v.y, v.z, v.w};
+      float out[4];
+      js_erf_vec<4>(in, out);
+      y4[i] = make_float4(out[0], out[1], out[2], out[3]);
+      continue;
+    }
     v.x = unary_eval<OP>(v.x, p0, p1);
     v.y = unary_eval<OP>(v.y, p0, p1);
     v.z = unary_eval<OP>(v.z, p0, p1);
@@ -256,9 +252,11 @@ __device__ __forceinline__ void ew_eval(int code, const float* a, const float* b
     EW_UN(TFJS_CUDA_RSQRT)
     EW_UN(TFJS_CUDA_TANH)
     EW_UN(TFJS_CUDA_NEG)
-    EW_UN(TFJS_CUDA_ERF)
     EW_UN(TFJS_CUDA_ABS)
     EW_UN(TFJS_CUDA_LOG)
+    case TFJS_CUDA_EW_UNARY + TFJS_CUDA_ERF:
+      js_erf_vec<V>(a, r);
+      break;
     case TFJS_CUDA_EW_UNARY + TFJS_CUDA_SQUARE:
 #pragma unroll
       for (int t = 0; t < V; ++t) r[t] = __fmul_rn(a[t], a[t]);
@@ -670,16 +668,39 @@ struct ProgAddAdd {  // (a + b) + c (residual + bias)
 #undef EW_B
 #undef EW_U
 
-template <class P, int V>
+// SIMPLE: every input is either a full tensor or a scalar; the scalars are fetched once,
+// ahead of the loop, and no index arithmetic is left in it.
+template <class P, int V, bool SIMPLE>
 __global__ void __launch_bounds__(256)
 fused_elementwise_static_kernel(const __grid_constant__ EwArgs g) {
   const uint32_t nv = (uint32_t)(g.n / V);
   const uint32_t stride = gridDim.x * blockDim.x;
+  float scalar[P::n_in];
+  bool is_scalar[P::n_in];
+  if (SIMPLE) {
+#pragma unroll
+    for (int k = 0; k < P::n_in; ++k) {
+      is_scalar[k] = g.mode[k] == TFJS_CUDA_EW_SCALAR;
+      scalar[k] = is_scalar[k] ? __ldg(g.in[k]) : 0.0f;
+    }
+  }
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
     const uint32_t e0 = i * V;
     float vals[P::n_in + P::n_ops][V];
 #pragma unroll
     for (int k = 0; k < P::n_in; ++k) {
+      if (SIMPLE) {
+        if (is_scalar[k]) {
+#pragma unroll
+          for (int t = 0; t < V; ++t) vals[k][t] = scalar[k];
+        } else if (V == 4) {
+          const float4 q = __ldg(reinterpret_cast<const float4*>(g.in[k] + e0));
+          vals[k][0] = q.x; vals[k][1 % V] = q.y; vals[k][2 % V] = q.z; vals[k][3 % V] = q.w;
+        } else {
+          vals[k][0] = __ldg(g.in[k] + e0);
+        }
+        continue;
+      }
       const float* src = ew_input_ptr(g, k, e0);
       const int mode = g.mode[k];
       if (mode == TFJS_CUDA_EW_ROW || mode == TFJS_CUDA_EW_SCALAR) {
@@ -718,12 +739,16 @@ static bool ew_matches(const EwArgs& g) {
 
 template <class P>
 static void ew_launch_static(tfjs_cuda_ctx* ctx, const EwArgs& g, bool vec) {
-  if (vec)
-    fused_elementwise_static_kernel<P, 4><<<grid_for(g.n / 4, kThreads, ctx->sm_count), kThreads,
-                                            0, ctx->stream>>>(g);
+  bool simple = true;
+  for (int k = 0; k < g.n_inputs; ++k)
+    simple = simple && (g.mode[k] == TFJS_CUDA_EW_FULL || g.mode[k] == TFJS_CUDA_EW_SCALAR);
+  const unsigned grid = grid_for(vec ? g.n / 4 : g.n, kThreads, ctx->sm_count);
+  if (vec && simple)
+    fused_elementwise_static_kernel<P, 4, true><<<grid, kThreads, 0, ctx->stream>>>(g);
+  else if (vec)
+    fused_elementwise_static_kernel<P, 4, false><<<grid, kThreads, 0, ctx->stream>>>(g);
   else
-    fused_elementwise_static_kernel<P, 1><<<grid_for(g.n, kThreads, ctx->sm_count), kThreads, 0,
-                                            ctx->stream>>>(g);
+    fused_elementwise_static_kernel<P, 1, false><<<grid, kThreads, 0, ctx->stream>>>(g);
 }
 
 // Launches the catalogue entry that matches g (dry_run: only reports whether one does).

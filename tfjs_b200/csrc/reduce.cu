@@ -58,7 +58,7 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
       for (int j = 0; j < REGS; ++j) {
         const uint32_t c = lane + 32 * j;
         if (c < cols) {
-          v[j] = (float)exp((double)__fsub_rn(v[j], m));
+          v[j] = (float)exp_fast((double)__fsub_rn(v[j], m));
           s += (double)v[j];
         }
       }
@@ -73,7 +73,7 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
       m = warp_nan_max(m);
       double s = 0.0;
       for (uint32_t c = lane; c < cols; c += 32) {
-        const float e = (float)exp((double)__fsub_rn(xr[c], m));
+        const float e = (float)exp_fast((double)__fsub_rn(xr[c], m));
         yr[c] = e;
         s += (double)e;
       }
