@@ -1223,11 +1223,29 @@ int launch_bn(tfjs_cuda_ctx* ctx, int bn, const CUtensorMap& a, const CUtensorMa
   }
 }
 
-int pick_bn(int M, int N, int batch, int sm_count) {
+int pick_bn(int M, int N, int batch, int sm_count, int k_steps = 0) {
   // Smallest tile that covers N, but do not starve the machine: when the tile
   // count is below the SM count a narrower tile gives more CTAs.
   int bn = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
   const long long tiles_m = (M + BM - 1) / BM;
+  if (k_steps >= 16 && bn > 64) {
+    // Long K: a K step costs nearly the same whatever the tile's width (measured 0.41 /
+    // 0.45 / 0.49 us at 64 / 128 / 256 columns), so halving the tile to fill idle SMs
+    // only pays if it saves a wave.  Cost = waves x main loop of a tile + one exposed
+    // epilogue (1.3 us per 32-column chunk, two warps per TMEM lane quarter).
+    int best = bn;
+    double best_cost = 1e30;
+    for (int c = bn; c >= 64; c >>= 1) {
+      const long long tiles = tiles_m * ((N + c - 1) / c) * batch;
+      const long long waves = (tiles + sm_count - 1) / sm_count;
+      const double step = c >= 256 ? 0.49 : (c >= 128 ? 0.45 : 0.41);
+      const double epi = 1.3 * (c / 64);
+      const double main_loop = k_steps * step > epi ? k_steps * step : epi;
+      const double cost = waves * main_loop + epi;
+      if (cost < best_cost) { best_cost = cost; best = c; }
+    }
+    return best;
+  }
   while (bn > 64 && tiles_m * ((N + bn - 1) / bn) * batch < sm_count) bn >>= 1;
   return bn;
 }
@@ -1287,7 +1305,7 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   g.x = op.a;
   g.conv = pr.conv;
   g.chunks_per_tap = op.cin_pad / BK;
-  const int bn = pick_bn(pr.M, pr.N, pr.batch, ctx->sm_count);
+  const int bn = pick_bn(pr.M, pr.N, pr.batch, ctx->sm_count, op.k_steps);
   CUtensorMap tm_a, tm_b, tm_c, tm_r;
   int rc;
   // output map for the epilogue's bulk stores, and the same view of the residual for
