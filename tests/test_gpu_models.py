@@ -140,3 +140,60 @@ def test_no_data_id_leak_across_executes(cuda_engine):
         base = n
     x.dispose()
     gm.dispose()
+
+
+# ------------------------------------------------- plan rewrite: layer normalisation --
+@pytest.mark.parametrize("shape", [(64, 128, 768), (5, 7, 100), (3, 1024), (9, 4), (2, 3, 6),
+                                   (4, 2048)])
+def test_fused_layer_norm_has_the_bits_of_the_separate_kernels(cuda_engine, shape):
+    """One launch against the nine kernels it replaces; shapes the kernel does not take
+    (a row that is not a multiple of 4, or beyond 1024) run the separate kernels."""
+    from tfjs_b200 import graph_model, ops
+    r = np.random.default_rng(sum(shape))
+    x = ops.tensor((r.standard_normal(shape) * 3 + 0.5).astype(np.float32))
+    gamma = ops.tensor(r.standard_normal(shape[-1]).astype(np.float32))
+    beta = ops.tensor(r.standard_normal(shape[-1]).astype(np.float32))
+    eps = np.float32(1e-12)
+    node = graph_model.Node({"name": "ln", "op": "_FusedLayerNorm", "input": ["x", "g", "b"],
+                             "attr": {"epsilon": {"f": float(eps)}}})
+    got_t = graph_model.execute_op(node, [x, gamma, beta])
+    got = got_t.arraySync()
+    mean = ops.mean(x, [-1], True)
+    sq = ops.squared_difference(x, mean)
+    var = ops.mean(sq, [-1], True)
+    e = ops.tensor(eps)
+    ve = ops.add(var, e)
+    rs = ops.rsqrt(ve)
+    sub = ops.sub(x, mean)
+    norm = ops.mul(sub, rs)
+    ng = ops.mul(norm, gamma)
+    ref_t = ops.add(ng, beta)
+    ref = ref_t.arraySync()
+    for t in (got_t, mean, sq, var, e, ve, rs, sub, norm, ng, ref_t, x, gamma, beta):
+        t.dispose()
+    assert got.shape == ref.shape
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+
+
+def test_bert_with_fused_layer_norms_matches_the_stored_graph(cuda_engine):
+    model_json, weights = model_zoo.bert_encoder(2, layers=2)
+    r = np.random.default_rng(3)
+    feeds = {"input_ids": r.integers(0, 30522, (2, 128)).astype(np.int32),
+             "attention_mask": np.ones((2, 128), np.float32)}
+    outs = []
+    be = cuda_engine.backend
+    for fuse in (True, False):
+        gm = GraphModel(model_json, weights, cuda_engine, replay=False)
+        gm.executor.fuse = fuse
+        ins = {k: cuda_engine.make_tensor(v, list(v.shape), "int32" if v.dtype == np.int32
+                                          else "float32") for k, v in feeds.items()}
+        before = be.numDataIds()
+        y = gm.execute(ins, ["sequence_output"])[0]
+        outs.append(y.arraySync())
+        assert gm.executor.fused_subgraphs == (5 if fuse else 0)
+        y.dispose()
+        assert be.numDataIds() == before
+        for t in ins.values():
+            t.dispose()
+        gm.dispose()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))

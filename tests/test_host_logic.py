@@ -104,3 +104,66 @@ def test_leaf_addressing_modes():
     assert p._leaf_mode([1, 12, 1, 1]) is None
     q = PendingEw([], [], [], [8, 1], [], (ADD, None, [1], None, [1]))
     assert q._leaf_mode([8, 1])[0] == FULL and q._leaf_mode([1])[0] == SCAL
+
+
+# ------------------------------------------------ plan rewrite: layer normalisation --
+def _bert_plan():
+    import bench
+    from tfjs_b200 import graph_model as G
+    mj, wt = bench.build_model("bert", 2)
+    consts, off = {}, 0
+    for group in mj["weightsManifest"]:
+        for spec in group["weights"]:
+            assert "quantization" not in spec
+            n = int(np.prod(spec["shape"])) if spec["shape"] else 1
+            consts[spec["name"]] = np.frombuffer(
+                wt, dtype=np.dtype(spec["dtype"]), count=n, offset=off).reshape(spec["shape"])
+            off += n * 4
+    nodes = [G.Node(d) for d in mj["modelTopology"]["node"]]
+    return G, nodes, consts
+
+
+def _fuse(G, nodes, consts, protected=()):
+    return G.fuse_layer_norms(nodes, lambda n: n in consts, lambda n: consts[n].reshape(-1),
+                              lambda n: list(consts[n].shape), protected)
+
+
+def test_layer_norm_subgraphs_of_bert_are_replaced():
+    G, nodes, consts = _bert_plan()
+    new, n = _fuse(G, nodes, consts)
+    assert n == 25                         # embeddings + 2 per encoder layer
+    assert len(new) == len(nodes) - 8 * n  # nine nodes become one
+    fused = [x for x in new if x.op == "_FusedLayerNorm"]
+    assert len(fused) == n
+    names = set(x.name for x in new)
+    for f in fused:
+        assert len(f.inputs) == 3 and abs(G.attr_number(f.attrs, "epsilon") - 1e-12) < 1e-18
+        assert all(G.parse_node_name(i)[0] in names for i in f.inputs)
+    # still topologically ordered
+    pos = {x.name: i for i, x in enumerate(new)}
+    for x in new:
+        for i in x.inputs:
+            assert pos[G.parse_node_name(i)[0]] < pos[x.name]
+    assert not any(x.op in ("SquaredDifference", "Rsqrt") for x in new)
+
+
+def test_layer_norm_is_left_alone_when_an_intermediate_is_wanted():
+    G, nodes, consts = _bert_plan()
+    rs = [x for x in nodes if x.op == "Rsqrt"]
+    new, n = _fuse(G, nodes, consts, protected=[rs[3].name])
+    assert n == 24 and any(x.name == rs[3].name for x in new)
+    # a second consumer of the variance keeps that subgraph too
+    var = next(x for x in nodes if x.name == G.parse_node_name(
+        next(y for y in nodes if y.name == G.parse_node_name(rs[0].inputs[0])[0]).inputs[0])[0])
+    extra = G.Node({"name": "tap", "op": "Identity", "input": [var.name]})
+    new, n = _fuse(G, nodes + [extra], consts)
+    assert n == 24
+
+
+def test_layer_norm_match_needs_the_last_axis_and_keep_dims():
+    G, nodes, consts = _bert_plan()
+    mean = next(x for x in nodes if x.op == "Mean")
+    consts2 = dict(consts)
+    consts2[G.parse_node_name(mean.inputs[1])[0]] = np.array([1], np.int32)
+    _, n = _fuse(G, nodes, consts2)
+    assert n < 25

@@ -83,6 +83,72 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
   }
 }
 
+// ---- layer normalisation over the last axis, as the converter leaves it in a graph:
+//   mean = Mean(x); var = Mean(SquaredDifference(x, mean)); rs = Rsqrt(var + eps);
+//   y = ((x - mean) * rs) * gamma + beta
+// Nine kernels of the reference (Mean.ts, SquaredDifference.ts, Add.ts, Rsqrt.ts, Sub.ts,
+// Multiply.ts) in one pass: a warp keeps its row in registers and performs the same
+// fp32 operations in the same order (every intermediate rounded to fp32, the two sums
+// accumulated in double over fl32(element / n), lanes striding 16-byte pieces as the
+// Mean kernel does), so the result carries the bits of the separate kernels.
+// NV = 16-byte pieces per lane (rows up to 128 * NV floats).
+template <int NV>
+__global__ void layer_norm_rows_kernel(const float* __restrict__ x,
+                                       const float* __restrict__ gamma,
+                                       const float* __restrict__ beta, float* __restrict__ y,
+                                       uint64_t rows, uint32_t cols, float nf, float eps) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  const uint32_t n4 = cols >> 2;
+  const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  const float4* b4 = reinterpret_cast<const float4*>(beta);
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    const float4* x4 = reinterpret_cast<const float4*>(x + r * cols);
+    float4* y4 = reinterpret_cast<float4*>(y + r * cols);
+    float v[NV][4];
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      const uint32_t j = u * 32 + lane;
+      const float4 q = j < n4 ? __ldg(x4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[u][0] = q.x; v[u][1] = q.y; v[u][2] = q.z; v[u][3] = q.w;
+    }
+    double acc = 0.0;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      if (u * 32 + lane >= n4) continue;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc += (double)__fdiv_rn(v[u][k], nf);
+    }
+    const float mean = (float)warp_sum(acc);
+    acc = 0.0;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      if (u * 32 + lane >= n4) continue;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        // SquaredDifference.ts: the difference and its square in double, stored as fp32
+        const double d = (double)v[u][k] - (double)mean;
+        acc += (double)__fdiv_rn((float)(d * d), nf);
+      }
+    }
+    const float var = (float)warp_sum(acc);
+    const float rs = (float)(1.0 / sqrt((double)__fadd_rn(var, eps)));
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      const uint32_t j = u * 32 + lane;
+      if (j >= n4) continue;
+      const float4 g = __ldg(g4 + j), b = __ldg(b4 + j);
+      const float gg[4] = {g.x, g.y, g.z, g.w}, bb[4] = {b.x, b.y, b.z, b.w};
+      float o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        o[k] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[u][k], mean), rs), gg[k]), bb[k]);
+      y4[j] = make_float4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 // ---- reductions over the middle axis of [outer, reduce, inner] ----------------
 // OP 0 sum, 1 mean (each element divided by n in fp32 first, Mean.ts:37-48),
 // 2 max.
@@ -268,6 +334,37 @@ int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
   else SOFTMAX(0);
 #undef SOFTMAX
   LAUNCH_CHECK(ctx, "softmax_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_layer_norm(tfjs_cuda_ctx* ctx, int32_t x_id, int32_t gamma_id, int32_t beta_id,
+                         uint64_t rows, uint64_t cols, float epsilon, int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  Buffer *x, *g, *b, *y;
+  int rc;
+  if ((rc = ctx_get(ctx, x_id, rows * cols * 4, "layer norm x", &x))) return rc;
+  if ((rc = ctx_get(ctx, gamma_id, cols * 4, "layer norm gamma", &g))) return rc;
+  if ((rc = ctx_get(ctx, beta_id, cols * 4, "layer norm beta", &b))) return rc;
+  if ((rc = ctx_get(ctx, out_id, rows * cols * 4, "layer norm out", &y))) return rc;
+  if (rows * cols == 0) return TFJS_CUDA_OK;
+  if ((cols & 3) || cols > 1024 || (((uintptr_t)x->ptr | (uintptr_t)g->ptr | (uintptr_t)b->ptr |
+                                      (uintptr_t)y->ptr) & 15))
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
+                    "layer norm: rows of a multiple of 4 up to 1024 floats, 16-byte aligned");
+  cudaSetDevice(ctx->device);
+  const unsigned grid = grid_for(rows * 32, kThreads, ctx->sm_count);
+#define LNORM(NV)                                                                          \
+  layer_norm_rows_kernel<NV><<<grid, kThreads, 0, ctx->stream>>>(                          \
+      (const float*)x->ptr, (const float*)g->ptr, (const float*)b->ptr, (float*)y->ptr,    \
+      rows, (uint32_t)cols, (float)cols, epsilon)
+  if (cols <= 128) LNORM(1);
+  else if (cols <= 256) LNORM(2);
+  else if (cols <= 512) LNORM(4);
+  else if (cols <= 768) LNORM(6);
+  else LNORM(8);
+#undef LNORM
+  LAUNCH_CHECK(ctx, "layer_norm_rows_kernel");
   ctx_mark_written(ctx, out_id);
   return TFJS_CUDA_OK;
 }

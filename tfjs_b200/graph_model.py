@@ -261,10 +261,143 @@ def execute_op(node, inp):
         return ops.cast(inp[0], attr_dtype(node.attrs, "DstT", "float32"))
     if op in ("Identity", "StopGradient", "PlaceholderWithDefault"):
         return ops.identity(inp[0])
+    if op == "_FusedLayerNorm":
+        return _exec_layer_norm(node, inp)
     if op in ("FusedBatchNorm", "FusedBatchNormV2", "FusedBatchNormV3"):
         return ops.batch_norm(inp[0], inp[3], inp[4], inp[2], inp[1],
                               attr_number(node.attrs, "epsilon", 0.001))
     raise ValueError("Node type %s is not implemented" % op)
+
+
+# ------------------------------------------------------------- plan rewrites --
+def _exec_layer_norm(node, inp):
+    x, gamma, beta = inp
+    eps = attr_number(node.attrs, "epsilon")
+    from .kernels.reduce import layer_norm_supported
+    if x.dtype == "float32" and layer_norm_supported(x.shape, gamma.shape, beta.shape):
+        return ops.fused_layer_norm(x, gamma, beta, eps)
+    # shapes the one-launch kernel does not take: the matched subgraph, op by op
+    tmp = []
+
+    def keep(t):
+        tmp.append(t)
+        return t
+    try:
+        mean = keep(ops.mean(x, [-1], True))
+        var = keep(ops.mean(keep(ops.squared_difference(x, mean)), [-1], True))
+        e = keep(ops.tensor(np.float32(eps)))
+        rs = keep(ops.rsqrt(keep(ops.add(var, e))))
+        norm = keep(ops.mul(keep(ops.sub(x, mean)), rs))
+        return ops.add(keep(ops.mul(norm, gamma)), beta)
+    finally:
+        for t in tmp:
+            t.dispose()
+
+
+def fuse_layer_norms(ordered, is_const, const_value, const_shape, protected=()):
+    """Plan rewrite in the spirit of the converter's graph fusions (FusedConv2D, _FusedMatMul
+    are made the same way at conversion time): the subgraph a converted model holds for a
+    layer normalisation over the last axis,
+
+        mean = Mean(x, [-1], keep_dims); var = Mean(SquaredDifference(x, mean), [-1], keep_dims)
+        out = AddV2(Mul(Mul(Sub(x, mean), Rsqrt(AddV2(var, eps))), gamma), beta)
+
+    becomes one `_FusedLayerNorm(x, gamma, beta; epsilon)` node that keeps the name of `out`.
+    Only when every intermediate is consumed inside the subgraph and none is in `protected`
+    (requested outputs, fed inputs).  `ordered` is a topologically sorted node list;
+    is_const(name), const_value(name) -> flat numpy array, const_shape(name) -> list.
+    Returns the new list and the number of subgraphs replaced."""
+    by_name = {n.name: n for n in ordered}
+    consumers = {}
+    for n in ordered:
+        for i in n.inputs:
+            consumers.setdefault(parse_node_name(i)[0], []).append(n.name)
+    protected = set(protected)
+
+    def node(inp, op=None):
+        name, idx = parse_node_name(inp)
+        n = by_name.get(name)
+        if n is None or idx != 0 or (op is not None and n.op not in op):
+            return None
+        return n
+
+    def split(n, want_a, want_b):
+        """The two inputs of a commutative node as (a, b) with a matching want_a."""
+        if len(n.inputs) != 2:
+            return None
+        for a, b in ((n.inputs[0], n.inputs[1]), (n.inputs[1], n.inputs[0])):
+            if want_a(a) and want_b(b):
+                return a, b
+        return None
+
+    def const(inp):
+        name, idx = parse_node_name(inp)
+        return idx == 0 and name in by_name and by_name[name].op == "Const" and is_const(name)
+
+    def last_axis_mean(n):
+        if n is None or n.op != "Mean" or len(n.inputs) != 2 or not attr_bool(n.attrs, "keep_dims"):
+            return False
+        if not const(n.inputs[1]):
+            return False
+        axes = [int(v) for v in const_value(parse_node_name(n.inputs[1])[0])]
+        return axes == [-1]
+
+    def only(name, users):
+        return sorted(consumers.get(name, [])) == sorted(users) and name not in protected
+
+    ADD = ("Add", "AddV2")
+    removed, replaced = set(), {}
+    for out in ordered:
+        if out.op not in ADD:
+            continue
+        ab = split(out, lambda i: node(i, ("Mul",)) is not None, const)
+        if not ab:
+            continue
+        m2, beta = node(ab[0]), ab[1]
+        ab = split(m2, lambda i: node(i, ("Mul",)) is not None, const)
+        if not ab:
+            continue
+        norm, gamma = node(ab[0]), ab[1]
+        ab = split(norm, lambda i: node(i, ("Sub",)) is not None,
+                   lambda i: node(i, ("Rsqrt",)) is not None)
+        if not ab:
+            continue
+        sub, rs = node(ab[0]), node(ab[1])
+        if len(sub.inputs) != 2:
+            continue
+        x_in, mean = sub.inputs[0], node(sub.inputs[1])
+        if not last_axis_mean(mean) or mean.inputs[0] != x_in:
+            continue
+        add = node(rs.inputs[0], ADD)
+        if add is None:
+            continue
+        ab = split(add, lambda i: last_axis_mean(node(i)), const)
+        if not ab:
+            continue
+        var, eps = node(ab[0]), ab[1]
+        sq = node(var.inputs[0], ("SquaredDifference",))
+        if sq is None or sorted(sq.inputs) != sorted([x_in, mean.name]):
+            continue
+        eps_v = const_value(parse_node_name(eps)[0])
+        g_shape = list(const_shape(parse_node_name(gamma)[0]))
+        b_shape = list(const_shape(parse_node_name(beta)[0]))
+        if len(eps_v) != 1 or len(g_shape) != 1 or g_shape != b_shape:
+            continue
+        inner = (mean, sq, var, add, rs, sub, norm, m2)
+        if len(set(n.name for n in inner)) != len(inner) or any(n.name in removed for n in inner):
+            continue
+        if not (only(mean.name, [sq.name, sub.name]) and only(sq.name, [var.name]) and
+                only(var.name, [add.name]) and only(add.name, [rs.name]) and
+                only(rs.name, [norm.name]) and only(sub.name, [norm.name]) and
+                only(norm.name, [m2.name]) and only(m2.name, [out.name])):
+            continue
+        removed.update(n.name for n in inner)
+        replaced[out.name] = Node({"name": out.name, "op": "_FusedLayerNorm",
+                                   "input": [x_in, gamma, beta],
+                                   "attr": {"epsilon": {"f": float(np.float32(eps_v[0]))}}})
+    if not replaced:
+        return list(ordered), 0
+    return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
 
 
 # ------------------------------------------------------------------- executor --
@@ -281,13 +414,17 @@ class GraphExecutor(object):
         self.default_outputs = [n.name for n in nodes
                                 if n.name not in consumed and n.op not in ("Const", "Placeholder")]
         self._compiled = {}
+        # plan rewrites (fuse_layer_norms); TFJS_CUDA_NO_GRAPH_FUSION=1 runs the graph as stored
+        self.fuse = os.environ.get("TFJS_CUDA_NO_GRAPH_FUSION", "0") in ("", "0")
+        self.fused_subgraphs = 0
         self.keep_intermediates = False
         self.intermediates = {}
 
     def _compile(self, input_names, output_names):
         """graph_executor.ts:167-191: the nodes needed for the outputs in topological
         order, and for every tensor the position of its last consumer."""
-        key = (tuple(sorted(input_names)), tuple(output_names))
+        fuse = self.fuse and not self.keep_intermediates
+        key = (tuple(sorted(input_names)), tuple(output_names), fuse)
         if key in self._compiled:
             return self._compiled[key]
         needed, stack = set(), [parse_node_name(o)[0] for o in output_names]
@@ -331,6 +468,13 @@ class GraphExecutor(object):
             if state.get(root) is None:
                 state[root] = 1
                 visit(root)
+        if fuse:
+            ordered, n = fuse_layer_norms(
+                ordered, lambda name: name in self.weight_map,
+                lambda name: np.asarray(_vals(self.weight_map[name])).reshape(-1),
+                lambda name: self.weight_map[name].shape,
+                protected=set(input_names) | set(parse_node_name(o)[0] for o in output_names))
+            self.fused_subgraphs = n
         last_use = {}
         for pos, node in enumerate(ordered):
             if node.name in input_names:

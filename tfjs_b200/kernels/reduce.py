@@ -5,6 +5,8 @@ Mean.ts:25-53, Max.ts:28-72, ArgMax.ts:24-71.  The reference transposes the
 reduced axes innermost; here contiguous reduced axes are reduced in place over an
 [outer, reduce, inner] view and only a non-contiguous set is transposed first.
 """
+import numpy as np
+
 from .. import _cabi
 from ..kernel_registry import KernelConfig
 from ..util import (compute_out_and_reduce_shapes, expand_shape_to_keep_dim,
@@ -135,10 +137,44 @@ def _softmax(args):
     return out
 
 
+def layer_norm_supported(x_shape, gamma_shape, beta_shape):
+    """Shapes the one-launch layer normalisation takes: rows of a multiple of 4 up to 1024
+    floats, gamma and beta one value per column."""
+    if not x_shape:
+        return False
+    cols = x_shape[-1]
+    return (cols % 4 == 0 and 0 < cols <= 1024 and size_from_shape(gamma_shape) == cols and
+            size_from_shape(beta_shape) == cols and
+            (not gamma_shape or gamma_shape[-1] == cols) and
+            (not beta_shape or beta_shape[-1] == cols))
+
+
+def _fused_layer_norm(args):
+    """((x - mean) * rsqrt(var + epsilon)) * gamma + beta over the last axis, the subgraph
+    the graph executor matches (graph_model.fuse_layer_norms), in one launch."""
+    backend, inp = args["backend"], args["inputs"]
+    x, gamma, beta = inp["x"], inp["gamma"], inp["beta"]
+    if not layer_norm_supported(x.shape, gamma.shape, beta.shape):
+        raise ValueError("_FusedLayerNorm: unsupported shapes %s %s %s" %
+                         (x.shape, gamma.shape, beta.shape))
+    cols = x.shape[-1]
+    rows = size_from_shape(x.shape[:-1])
+    out = backend.make_output(x.shape, "float32")
+    try:
+        backend.check(backend.lib.tfjs_cuda_layer_norm(
+            backend.ctx, dev(backend, x), dev(backend, gamma), dev(backend, beta), rows, cols,
+            float(np.float32(args["attrs"]["epsilon"])), dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    return out
+
+
 CONFIGS = [
     KernelConfig("Sum", BACKEND, _sum),
     KernelConfig("Mean", BACKEND, _mean),
     KernelConfig("Max", BACKEND, _max),
     KernelConfig("ArgMax", BACKEND, _argmax),
     KernelConfig("Softmax", BACKEND, _softmax),
+    KernelConfig("_FusedLayerNorm", BACKEND, _fused_layer_norm),
 ]

@@ -288,6 +288,14 @@ def softmax(logits, dim=-1):
     return _run("Softmax", {"logits": logits}, {"dim": dim})
 
 
+def fused_layer_norm(x, gamma, beta, epsilon):
+    """Layer normalisation over the last axis in the decomposed form of a converted graph,
+    as one kernel of the 'cuda' backend (no counterpart among the reference's ops; the
+    graph executor substitutes it for the matched subgraph)."""
+    return _run("_FusedLayerNorm", {"x": x, "gamma": gamma, "beta": beta},
+                {"epsilon": float(epsilon)})
+
+
 def sum(x, axis=None, keepDims=False):
     return _run("Sum", {"x": x}, {"axis": axis, "keepDims": keepDims})
 

@@ -203,6 +203,11 @@ napi_value Softmax(napi_env env, napi_callback_info info) {
   Args a(env, info);
   return check(env, a.ctx(0), tfjs_cuda_softmax(a.ctx(0), a.i32(1), a.u64(2), a.u64(3), a.i32(4)));
 }
+napi_value LayerNorm(napi_env env, napi_callback_info info) {
+  Args a(env, info);  // ctx, xId, gammaId, betaId, rows, cols, epsilon, outId
+  return check(env, a.ctx(0), tfjs_cuda_layer_norm(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.u64(4), a.u64(5),
+                                                   static_cast<float>(a.f64(6)), a.i32(7)));
+}
 napi_value Reduce(napi_env env, napi_callback_info info) {
   Args a(env, info);
   return check(env, a.ctx(0), tfjs_cuda_reduce(a.ctx(0), a.i32(1), a.i32(2), a.u64(3), a.u64(4), a.u64(5), a.i32(6)));
@@ -260,7 +265,7 @@ napi_value Init(napi_env env, napi_value exports) {
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},
       {"fusedConv2dResidual", FusedConv2DResidual}, {"addActivation", AddActivation},
       {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul},
-      {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax},
+      {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm},
       {"reduce", Reduce}, {"argMax", ArgMax}, {"transpose", Transpose}, {"gather", Gather},
       {"cast", Cast}, {"copyStrided", CopyStrided}, {"fill", Fill}, {"batchNorm", BatchNorm},
       {"dequantize", Dequantize}, {"dequantizeStatic", DequantizeStatic}};
