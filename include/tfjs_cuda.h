@@ -333,14 +333,17 @@ int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
 
 /* ---- Layer normalisation over the last axis of a [rows, cols] view, in the decomposed
  * form a converted graph holds: y = ((x - mean) * rsqrt(var + epsilon)) * gamma + beta with
- * mean = Mean(x), var = Mean(SquaredDifference(x, mean)).  One launch for the nine kernels
+ * mean = Mean(x), var = Mean(SquaredDifference(x, mean)).  One launch for the nine (ten with the residual Add) kernels
  * (tfjs-backend-cpu/src/kernels/Mean.ts:25-53, SquaredDifference.ts, Add.ts, Rsqrt.ts,
  * Sub.ts, Multiply.ts) with every intermediate rounded as those kernels round it.  gamma and
- * beta hold cols floats.  cols must be a multiple of 4 and at most 1024 (UNSUPPORTED
+ * beta hold cols floats.  residual_id != 0: the normalised tensor is Add(x, residual) (the
+ * residual connection in front of the normalisation; Add.ts), never written to memory.
+ * cols must be a multiple of 4 and at most 1024 (UNSUPPORTED
  * otherwise: the host then runs the separate kernels).  No counterpart in the reference's
  * kernel set; the graph executor substitutes it for the matched subgraph. */
-int tfjs_cuda_layer_norm(tfjs_cuda_ctx* ctx, int32_t x_id, int32_t gamma_id, int32_t beta_id,
-                         uint64_t rows, uint64_t cols, float epsilon, int32_t out_id);
+int tfjs_cuda_layer_norm(tfjs_cuda_ctx* ctx, int32_t x_id, int32_t residual_id, int32_t gamma_id,
+                         int32_t beta_id, uint64_t rows, uint64_t cols, float epsilon,
+                         int32_t out_id);
 
 /* ---- Sum / Mean / Max over the middle axis of an [outer, reduce, inner] view:
  * tfjs-backend-cpu/src/kernels/Sum.ts:28-90, Mean.ts:25-53, Max.ts:28-72.  The

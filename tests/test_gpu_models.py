@@ -143,21 +143,32 @@ def test_no_data_id_leak_across_executes(cuda_engine):
 
 
 # ------------------------------------------------- plan rewrite: layer normalisation --
+@pytest.mark.parametrize("residual", [None, "same", "broadcast"])
 @pytest.mark.parametrize("shape", [(64, 128, 768), (5, 7, 100), (3, 1024), (9, 4), (2, 3, 6),
                                    (4, 2048)])
-def test_fused_layer_norm_has_the_bits_of_the_separate_kernels(cuda_engine, shape):
+def test_fused_layer_norm_has_the_bits_of_the_separate_kernels(cuda_engine, shape, residual):
     """One launch against the nine kernels it replaces; shapes the kernel does not take
     (a row that is not a multiple of 4, or beyond 1024) run the separate kernels."""
     from tfjs_b200 import graph_model, ops
     r = np.random.default_rng(sum(shape))
     x = ops.tensor((r.standard_normal(shape) * 3 + 0.5).astype(np.float32))
+    extra = []
+    if residual is not None:
+        rshape = shape if residual == "same" else (1,) + tuple(shape[1:])
+        extra = [ops.tensor(r.standard_normal(rshape).astype(np.float32))]
     gamma = ops.tensor(r.standard_normal(shape[-1]).astype(np.float32))
     beta = ops.tensor(r.standard_normal(shape[-1]).astype(np.float32))
     eps = np.float32(1e-12)
-    node = graph_model.Node({"name": "ln", "op": "_FusedLayerNorm", "input": ["x", "g", "b"],
-                             "attr": {"epsilon": {"f": float(eps)}}})
-    got_t = graph_model.execute_op(node, [x, gamma, beta])
+    attrs = {"epsilon": {"f": float(eps)}}
+    if extra:
+        attrs["residual"] = {"b": True}
+    node = graph_model.Node({"name": "ln", "op": "_FusedLayerNorm",
+                             "input": ["x"] + ["r"] * len(extra) + ["g", "b"], "attr": attrs})
+    got_t = graph_model.execute_op(node, [x] + extra + [gamma, beta])
     got = got_t.arraySync()
+    if extra:
+        extra.append(x)
+        x = ops.add(x, extra[0])
     mean = ops.mean(x, [-1], True)
     sq = ops.squared_difference(x, mean)
     var = ops.mean(sq, [-1], True)
@@ -169,7 +180,7 @@ def test_fused_layer_norm_has_the_bits_of_the_separate_kernels(cuda_engine, shap
     ng = ops.mul(norm, gamma)
     ref_t = ops.add(ng, beta)
     ref = ref_t.arraySync()
-    for t in (got_t, mean, sq, var, e, ve, rs, sub, norm, ng, ref_t, x, gamma, beta):
+    for t in [got_t, mean, sq, var, e, ve, rs, sub, norm, ng, ref_t, x, gamma, beta] + extra:
         t.dispose()
     assert got.shape == ref.shape
     assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))

@@ -132,12 +132,15 @@ def test_layer_norm_subgraphs_of_bert_are_replaced():
     G, nodes, consts = _bert_plan()
     new, n = _fuse(G, nodes, consts)
     assert n == 25                         # embeddings + 2 per encoder layer
-    assert len(new) == len(nodes) - 8 * n  # nine nodes become one
+    # nine nodes become one, and the Add in front of each (24 residual connections and
+    # the sum of the two embeddings) is absorbed
+    assert len(new) == len(nodes) - 9 * n
     fused = [x for x in new if x.op == "_FusedLayerNorm"]
     assert len(fused) == n
     names = set(x.name for x in new)
     for f in fused:
-        assert len(f.inputs) == 3 and abs(G.attr_number(f.attrs, "epsilon") - 1e-12) < 1e-18
+        assert len(f.inputs) == 4 and G.attr_bool(f.attrs, "residual")
+        assert abs(G.attr_number(f.attrs, "epsilon") - 1e-12) < 1e-18
         assert all(G.parse_node_name(i)[0] in names for i in f.inputs)
     # still topologically ordered
     pos = {x.name: i for i, x in enumerate(new)}
@@ -145,6 +148,13 @@ def test_layer_norm_subgraphs_of_bert_are_replaced():
         for i in x.inputs:
             assert pos[G.parse_node_name(i)[0]] < pos[x.name]
     assert not any(x.op in ("SquaredDifference", "Rsqrt") for x in new)
+    # a residual sum that something else reads as well stays a node of its own
+    res_sum = next(x for x in nodes if x.op == "AddV2" and x.name not in names and
+                   x.inputs == fused[-1].inputs[:2])
+    tap = G.Node({"name": "tap", "op": "Identity", "input": [res_sum.name]})
+    new2, n2 = _fuse(G, nodes + [tap], consts)
+    assert n2 == 25 and any(x.name == res_sum.name for x in new2)
+    assert sum(1 for x in new2 if x.op == "_FusedLayerNorm" and len(x.inputs) == 3) == 1
 
 
 def test_layer_norm_is_left_alone_when_an_intermediate_is_wanted():

@@ -91,9 +91,12 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
 // fp32 operations in the same order (every intermediate rounded to fp32, the two sums
 // accumulated in double over fl32(element / n), lanes striding 16-byte pieces as the
 // Mean kernel does), so the result carries the bits of the separate kernels.
-// NV = 16-byte pieces per lane (rows up to 128 * NV floats).
+// NV = 16-byte pieces per lane (rows up to 128 * NV floats).  With `res` the normalised
+// tensor is Add(x, res) (the residual connection in front of the normalisation), formed
+// in registers.
 template <int NV>
 __global__ void layer_norm_rows_kernel(const float* __restrict__ x,
+                                       const float* __restrict__ res,
                                        const float* __restrict__ gamma,
                                        const float* __restrict__ beta, float* __restrict__ y,
                                        uint64_t rows, uint32_t cols, float nf, float eps) {
@@ -112,6 +115,11 @@ __global__ void layer_norm_rows_kernel(const float* __restrict__ x,
       const uint32_t j = u * 32 + lane;
       const float4 q = j < n4 ? __ldg(x4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
       v[u][0] = q.x; v[u][1] = q.y; v[u][2] = q.z; v[u][3] = q.w;
+      if (res != nullptr && j < n4) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(res + r * cols) + j);
+        v[u][0] = __fadd_rn(v[u][0], t.x); v[u][1] = __fadd_rn(v[u][1], t.y);
+        v[u][2] = __fadd_rn(v[u][2], t.z); v[u][3] = __fadd_rn(v[u][3], t.w);
+      }
     }
     double acc = 0.0;
 #pragma unroll
@@ -338,25 +346,31 @@ int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
   return TFJS_CUDA_OK;
 }
 
-int tfjs_cuda_layer_norm(tfjs_cuda_ctx* ctx, int32_t x_id, int32_t gamma_id, int32_t beta_id,
-                         uint64_t rows, uint64_t cols, float epsilon, int32_t out_id) {
+int tfjs_cuda_layer_norm(tfjs_cuda_ctx* ctx, int32_t x_id, int32_t residual_id, int32_t gamma_id,
+                         int32_t beta_id, uint64_t rows, uint64_t cols, float epsilon,
+                         int32_t out_id) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
-  Buffer *x, *g, *b, *y;
+  Buffer *x, *g, *b, *y, *res = nullptr;
   int rc;
   if ((rc = ctx_get(ctx, x_id, rows * cols * 4, "layer norm x", &x))) return rc;
+  if (residual_id != 0 &&
+      (rc = ctx_get(ctx, residual_id, rows * cols * 4, "layer norm residual", &res)))
+    return rc;
   if ((rc = ctx_get(ctx, gamma_id, cols * 4, "layer norm gamma", &g))) return rc;
   if ((rc = ctx_get(ctx, beta_id, cols * 4, "layer norm beta", &b))) return rc;
   if ((rc = ctx_get(ctx, out_id, rows * cols * 4, "layer norm out", &y))) return rc;
   if (rows * cols == 0) return TFJS_CUDA_OK;
-  if ((cols & 3) || cols > 1024 || (((uintptr_t)x->ptr | (uintptr_t)g->ptr | (uintptr_t)b->ptr |
-                                      (uintptr_t)y->ptr) & 15))
+  if ((cols & 3) || cols > 1024 ||
+      (((uintptr_t)x->ptr | (uintptr_t)g->ptr | (uintptr_t)b->ptr | (uintptr_t)y->ptr |
+        (uintptr_t)(res ? res->ptr : nullptr)) & 15))
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
                     "layer norm: rows of a multiple of 4 up to 1024 floats, 16-byte aligned");
   cudaSetDevice(ctx->device);
   const unsigned grid = grid_for(rows * 32, kThreads, ctx->sm_count);
 #define LNORM(NV)                                                                          \
   layer_norm_rows_kernel<NV><<<grid, kThreads, 0, ctx->stream>>>(                          \
-      (const float*)x->ptr, (const float*)g->ptr, (const float*)b->ptr, (float*)y->ptr,    \
+      (const float*)x->ptr, res ? (const float*)res->ptr : nullptr, (const float*)g->ptr,  \
+      (const float*)b->ptr, (float*)y->ptr,                                                \
       rows, (uint32_t)cols, (float)cols, epsilon)
   if (cols <= 128) LNORM(1);
   else if (cols <= 256) LNORM(2);

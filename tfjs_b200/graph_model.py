@@ -271,18 +271,27 @@ def execute_op(node, inp):
 
 # ------------------------------------------------------------- plan rewrites --
 def _exec_layer_norm(node, inp):
-    x, gamma, beta = inp
     eps = attr_number(node.attrs, "epsilon")
     from .kernels.reduce import layer_norm_supported
-    if x.dtype == "float32" and layer_norm_supported(x.shape, gamma.shape, beta.shape):
-        return ops.fused_layer_norm(x, gamma, beta, eps)
-    # shapes the one-launch kernel does not take: the matched subgraph, op by op
     tmp = []
 
     def keep(t):
         tmp.append(t)
         return t
     try:
+        if attr_bool(node.attrs, "residual"):
+            # the normalised tensor is Add(a, b), absorbed when both have its shape
+            a, b, gamma, beta = inp
+            if (a.dtype == "float32" and b.dtype == "float32" and
+                    list(a.shape) == list(b.shape) and
+                    layer_norm_supported(a.shape, gamma.shape, beta.shape)):
+                return ops.fused_layer_norm(a, gamma, beta, eps, residual=b)
+            x = keep(ops.add(a, b))
+        else:
+            x, gamma, beta = inp
+        if x.dtype == "float32" and layer_norm_supported(x.shape, gamma.shape, beta.shape):
+            return ops.fused_layer_norm(x, gamma, beta, eps)
+        # shapes the one-launch kernel does not take: the matched subgraph, op by op
         mean = keep(ops.mean(x, [-1], True))
         var = keep(ops.mean(keep(ops.squared_difference(x, mean)), [-1], True))
         e = keep(ops.tensor(np.float32(eps)))
@@ -304,7 +313,9 @@ def fuse_layer_norms(ordered, is_const, const_value, const_shape, protected=()):
 
     becomes one `_FusedLayerNorm(x, gamma, beta; epsilon)` node that keeps the name of `out`.
     Only when every intermediate is consumed inside the subgraph and none is in `protected`
-    (requested outputs, fed inputs).  `ordered` is a topologically sorted node list;
+    (requested outputs, fed inputs).  When x itself is an Add / AddV2 that nothing else
+    consumes (the residual connection in front of the normalisation), it is absorbed too:
+    `_FusedLayerNorm(a, b, gamma, beta; epsilon, residual)`.  `ordered` is a topologically sorted node list;
     is_const(name), const_value(name) -> flat numpy array, const_shape(name) -> list.
     Returns the new list and the number of subgraphs replaced."""
     by_name = {n.name: n for n in ordered}
@@ -392,9 +403,16 @@ def fuse_layer_norms(ordered, is_const, const_value, const_shape, protected=()):
                 only(norm.name, [m2.name]) and only(m2.name, [out.name])):
             continue
         removed.update(n.name for n in inner)
-        replaced[out.name] = Node({"name": out.name, "op": "_FusedLayerNorm",
-                                   "input": [x_in, gamma, beta],
-                                   "attr": {"epsilon": {"f": float(np.float32(eps_v[0]))}}})
+        attrs = {"epsilon": {"f": float(np.float32(eps_v[0]))}}
+        ins = [x_in, gamma, beta]
+        xn = node(x_in, ADD)
+        if (xn is not None and len(xn.inputs) == 2 and xn.name not in removed and
+                only(xn.name, [mean.name, sq.name, sub.name])):
+            removed.add(xn.name)
+            ins = [xn.inputs[0], xn.inputs[1], gamma, beta]
+            attrs["residual"] = {"b": True}
+        replaced[out.name] = Node({"name": out.name, "op": "_FusedLayerNorm", "input": ins,
+                                   "attr": attrs})
     if not replaced:
         return list(ordered), 0
     return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)

@@ -151,9 +151,15 @@ def layer_norm_supported(x_shape, gamma_shape, beta_shape):
 
 def _fused_layer_norm(args):
     """((x - mean) * rsqrt(var + epsilon)) * gamma + beta over the last axis, the subgraph
-    the graph executor matches (graph_model.fuse_layer_norms), in one launch."""
+    the graph executor matches (graph_model.fuse_layer_norms), in one launch; with
+    `residual`, of Add(x, residual)."""
     backend, inp = args["backend"], args["inputs"]
     x, gamma, beta = inp["x"], inp["gamma"], inp["beta"]
+    residual = inp.get("residual")
+    if residual is not None and (list(residual.shape) != list(x.shape) or
+                                 residual.dtype != "float32"):
+        raise ValueError("_FusedLayerNorm: residual %s does not have the shape of x %s" %
+                         (residual.shape, x.shape))
     if not layer_norm_supported(x.shape, gamma.shape, beta.shape):
         raise ValueError("_FusedLayerNorm: unsupported shapes %s %s %s" %
                          (x.shape, gamma.shape, beta.shape))
@@ -162,7 +168,8 @@ def _fused_layer_norm(args):
     out = backend.make_output(x.shape, "float32")
     try:
         backend.check(backend.lib.tfjs_cuda_layer_norm(
-            backend.ctx, dev(backend, x), dev(backend, gamma), dev(backend, beta), rows, cols,
+            backend.ctx, dev(backend, x), dev(backend, residual), dev(backend, gamma),
+            dev(backend, beta), rows, cols,
             float(np.float32(args["attrs"]["epsilon"])), dev(backend, out)))
     except Exception:
         backend.disposeData(out.dataId)

@@ -288,11 +288,11 @@ def softmax(logits, dim=-1):
     return _run("Softmax", {"logits": logits}, {"dim": dim})
 
 
-def fused_layer_norm(x, gamma, beta, epsilon):
+def fused_layer_norm(x, gamma, beta, epsilon, residual=None):
     """Layer normalisation over the last axis in the decomposed form of a converted graph,
     as one kernel of the 'cuda' backend (no counterpart among the reference's ops; the
     graph executor substitutes it for the matched subgraph)."""
-    return _run("_FusedLayerNorm", {"x": x, "gamma": gamma, "beta": beta},
+    return _run("_FusedLayerNorm", {"x": x, "gamma": gamma, "beta": beta, "residual": residual},
                 {"epsilon": float(epsilon)})
 
 

@@ -204,9 +204,9 @@ napi_value Softmax(napi_env env, napi_callback_info info) {
   return check(env, a.ctx(0), tfjs_cuda_softmax(a.ctx(0), a.i32(1), a.u64(2), a.u64(3), a.i32(4)));
 }
 napi_value LayerNorm(napi_env env, napi_callback_info info) {
-  Args a(env, info);  // ctx, xId, gammaId, betaId, rows, cols, epsilon, outId
-  return check(env, a.ctx(0), tfjs_cuda_layer_norm(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.u64(4), a.u64(5),
-                                                   static_cast<float>(a.f64(6)), a.i32(7)));
+  Args a(env, info);  // ctx, xId, residualId (0: none), gammaId, betaId, rows, cols, epsilon, outId
+  return check(env, a.ctx(0), tfjs_cuda_layer_norm(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.i32(4), a.u64(5),
+                                                   a.u64(6), static_cast<float>(a.f64(7)), a.i32(8)));
 }
 napi_value Reduce(napi_env env, napi_callback_info info) {
   Args a(env, info);
