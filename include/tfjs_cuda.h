@@ -216,6 +216,23 @@ int tfjs_cuda_fused_matmul(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
                            int32_t a_id, int32_t b_id, int32_t bias_id,
                            int32_t prelu_id, int32_t out_id);
 
+/* The same product stored through the permutation that splits or merges attention heads, so
+ * that the Reshape + Transpose([0, 2, 1, 3]) around a multi-head attention
+ * (tfjs-backend-cpu/src/kernels/Transpose.ts, one pass over the tensor each) cost nothing:
+ *   TFJS_CUDA_HEADS_SPLIT  batch 1, M = B*S, N = H*D: the [B, S, H, D] view of the result is
+ *                          written as [B, H, S, D]; rows_or_heads = S, head_dim = D.
+ *   TFJS_CUDA_HEADS_MERGE  batch B*H, M = S, N = D: the [B, H, S, D] result is written as
+ *                          [B, S, H, D]; rows_or_heads = H, head_dim = D.
+ * The values are those of tfjs_cuda_fused_matmul; only their places differ.  S and D must
+ * be multiples of 32 and the tensor-core path must apply (TF32 math mode, K % 4 == 0, a not
+ * transposed); otherwise TFJS_CUDA_UNSUPPORTED, nothing is written, and the host runs the
+ * plain product and the Transpose kernel. */
+enum tfjs_cuda_heads_layout { TFJS_CUDA_HEADS_SPLIT = 1, TFJS_CUDA_HEADS_MERGE = 2 };
+int tfjs_cuda_fused_matmul_heads(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
+                                 int32_t a_id, int32_t b_id, int32_t bias_id, int32_t prelu_id,
+                                 int32_t layout, int32_t rows_or_heads, int32_t head_dim,
+                                 int32_t out_id);
+
 /* ---- MaxPool / AvgPool: tfjs-backend-cpu/src/kernels/MaxPool.ts:24-55,
  * AvgPool.ts:24-55, utils/pool_utils.ts:20-87; attrs kernel_names.ts:83-90,
  * :517-524.  Geometry from computePool2DInfo (conv_util.ts:119-140); filter_h/w

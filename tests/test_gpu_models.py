@@ -208,3 +208,74 @@ def test_bert_with_fused_layer_norms_matches_the_stored_graph(cuda_engine):
             t.dispose()
         gm.dispose()
     assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
+# ---------------------------------------------------- plan rewrite: attention heads --
+@pytest.mark.parametrize("heads", [(2, 128, 12, 64), (3, 64, 4, 32), (1, 96, 2, 160),
+                                   (2, 50, 3, 64), (2, 64, 3, 48)])
+def test_matmul_heads_store_has_the_bits_of_matmul_then_transpose(cuda_engine, heads):
+    """Split and merge through the permuted store against product + Reshape + Transpose; the
+    last two shapes (S or D not a multiple of 32) are declined by the library and take the
+    three ops inside the executor."""
+    from tfjs_b200 import graph_model, ops
+    import base64
+    B, S, H, D = heads
+    r = np.random.default_rng(B * 1000 + S)
+    enc = lambda t: {"s": base64.b64encode(t.encode()).decode()}
+    ints = lambda v: {"list": {"i": [str(x) for x in v]}}
+    # split: [B*S, K] x [K, H*D] + bias -> [B, H, S, D]
+    K = 96
+    a = ops.tensor(r.standard_normal((B * S, K)).astype(np.float32))
+    w = ops.tensor((r.standard_normal((K, H * D)) / 8).astype(np.float32))
+    bias = ops.tensor(r.standard_normal(H * D).astype(np.float32))
+    attrs = {"transpose_a": {"b": False}, "transpose_b": {"b": False}, "num_args": {"i": "1"},
+             "fused_ops": {"list": {"s": [base64.b64encode(b"BiasAdd").decode()]}},
+             "_layout": enc("split"), "_op": enc("_FusedMatMul"), "_dims": ints([B, S, H, D])}
+    node = graph_model.Node({"name": "q", "op": "_MatMulHeads", "input": ["a", "w", "b"],
+                             "attr": attrs})
+    got_t = graph_model.execute_op(node, [a, w, bias])
+    y = ops.fused_mat_mul(a, w, False, False, bias, "linear")
+    y4 = ops.reshape(y, [B, S, H, D])
+    ref_t = ops.transpose(y4, [0, 2, 1, 3])
+    got, ref = got_t.arraySync(), ref_t.arraySync()
+    assert got.shape == (B, H, S, D)
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    # merge: [B, H, S, S] x [B, H, S, D] -> [B, S, H, D] -> [B*S, H*D]
+    p = ops.tensor(r.random((B, H, S, S)).astype(np.float32))
+    attrs = {"adj_x": {"b": False}, "adj_y": {"b": False}, "_layout": enc("merge"),
+             "_op": enc("BatchMatMulV2"), "_dims": ints([B * S, H * D])}
+    node = graph_model.Node({"name": "c", "op": "_MatMulHeads", "input": ["p", "v"],
+                             "attr": attrs})
+    got2_t = graph_model.execute_op(node, [p, ref_t])
+    c = ops.mat_mul(p, ref_t)
+    ct = ops.transpose(c, [0, 2, 1, 3])
+    ref2_t = ops.reshape(ct, [B * S, H * D])
+    got2, ref2 = got2_t.arraySync(), ref2_t.arraySync()
+    assert got2.shape == (B * S, H * D)
+    assert np.array_equal(got2.view(np.uint32), ref2.view(np.uint32))
+    for t in (a, w, bias, got_t, y, y4, ref_t, p, got2_t, c, ct, ref2_t):
+        t.dispose()
+
+
+def test_bert_with_folded_head_transposes_matches_the_stored_graph(cuda_engine):
+    model_json, weights = model_zoo.bert_encoder(2, layers=2)
+    r = np.random.default_rng(4)
+    feeds = {"input_ids": r.integers(0, 30522, (2, 128)).astype(np.int32),
+             "attention_mask": np.ones((2, 128), np.float32)}
+    outs, launches = [], []
+    be = cuda_engine.backend
+    for fuse in (True, False):
+        gm = GraphModel(model_json, weights, cuda_engine, replay=False)
+        gm.executor.fuse = fuse
+        ins = {k: cuda_engine.make_tensor(v, list(v.shape), "int32" if v.dtype == np.int32
+                                          else "float32") for k, v in feeds.items()}
+        before = be.numDataIds()
+        y = gm.execute(ins, ["sequence_output"])[0]
+        outs.append(y.arraySync())
+        assert gm.executor.fused_heads == (8 if fuse else 0)
+        y.dispose()
+        assert be.numDataIds() == before
+        for t in ins.values():
+            t.dispose()
+        gm.dispose()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))

@@ -177,3 +177,42 @@ def test_layer_norm_match_needs_the_last_axis_and_keep_dims():
     consts2[G.parse_node_name(mean.inputs[1])[0]] = np.array([1], np.int32)
     _, n = _fuse(G, nodes, consts2)
     assert n < 25
+
+
+# ---------------------------------------------------- plan rewrite: attention heads --
+def test_heads_split_and_merge_of_bert_become_store_orders():
+    G, nodes, consts = _bert_plan()
+    new, n = G.fuse_attention_heads(nodes, lambda x: x in consts, lambda x: consts[x].reshape(-1))
+    assert n == 12 * 4                       # Q, K, V splits and one merge per layer
+    assert len(new) == len(nodes) - 2 * n    # Reshape + Transpose folded into each product
+    assert not any(x.op == "Transpose" for x in new)
+    fused = [x for x in new if x.op == "_MatMulHeads"]
+    kinds = [G.attr_string(x.attrs, "_layout") for x in fused]
+    assert kinds.count("split") == 36 and kinds.count("merge") == 12
+    for x in fused:
+        inner = G.attr_string(x.attrs, "_op", keep_case=True)
+        dims = G.attr_number_list(x.attrs, "_dims")
+        if G.attr_string(x.attrs, "_layout") == "split":
+            assert inner == "_FusedMatMul" and dims == [2, 128, 12, 64] and len(x.inputs) == 3
+        else:
+            assert inner == "BatchMatMulV2" and dims == [256, 768] and len(x.inputs) == 2
+    pos = {x.name: i for i, x in enumerate(new)}
+    for x in new:
+        for i in x.inputs:
+            assert pos[G.parse_node_name(i)[0]] < pos[x.name]
+    # both rewrites together, as the executor applies them
+    both, k = _fuse(G, new, consts)
+    assert k == 25
+
+
+def test_heads_rewrite_keeps_a_product_that_is_read_elsewhere():
+    G, nodes, consts = _bert_plan()
+    t = next(x for x in nodes if x.op == "Transpose")
+    r = next(x for x in nodes if x.name == G.parse_node_name(t.inputs[0])[0])
+    tap = G.Node({"name": "tap", "op": "Identity", "input": [r.inputs[0]]})
+    new, n = G.fuse_attention_heads(nodes + [tap], lambda x: x in consts,
+                                    lambda x: consts[x].reshape(-1))
+    assert n == 47 and any(x.name == t.name and x.op == "Transpose" for x in new)
+    _, n = G.fuse_attention_heads(nodes, lambda x: x in consts, lambda x: consts[x].reshape(-1),
+                                  protected=[r.name])
+    assert n == 47

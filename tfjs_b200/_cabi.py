@@ -14,6 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtfjs_cuda.so")
 
 OK = 0
+UNSUPPORTED = 5
 ACTIVATIONS = dict(linear=0, relu=1, relu6=2, prelu=3, leakyrelu=4, sigmoid=5,
                    elu=6)
 DTYPES = dict(float32=0, int32=1, bool=2)
@@ -102,6 +103,7 @@ SIGNATURES = {
     "tfjs_cuda_add_activation": (c_int, [_CTX, c_int32, c_int32, c_int32, c_uint64, c_int32]),
     "tfjs_cuda_fused_depthwise_conv2d": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 5),
     "tfjs_cuda_fused_matmul": (c_int, [_CTX, POINTER(MatMulParams)] + [c_int32] * 5),
+    "tfjs_cuda_fused_matmul_heads": (c_int, [_CTX, POINTER(MatMulParams)] + [c_int32] * 8),
     "tfjs_cuda_pool2d": (c_int, [_CTX, POINTER(Conv2DParams), c_int32, c_int32, c_int32]),
     "tfjs_cuda_binary": (c_int, [_CTX, c_int32, c_int32, c_int32, c_int32, _I64P,
                                  c_int32, _I64P, c_int32, _I64P]),
@@ -152,6 +154,9 @@ def load():
         fn.argtypes = args
     _lib = lib
     return lib
+
+
+HEADS_SPLIT, HEADS_MERGE = 1, 2
 
 
 class CudaError(RuntimeError):

@@ -29,6 +29,13 @@ struct GemmProblem {
   // residual shaped like the output (the bottleneck shortcut of a residual network)
   const float* residual = nullptr;
   int post_act = 0;  // TFJS_CUDA_ACT_LINEAR or TFJS_CUDA_ACT_RELU / RELU6
+  // optional permuted store for attention heads (tensor-core kernels only):
+  //   1  batch == 1, M = B*perm_p, N = H*perm_d: the [B, S, H, D] view of the result is
+  //      written as [B, H, S, D] (the heads split of a projection, S = perm_p, D = perm_d)
+  //   2  batch = B*perm_p, N = perm_d: the [B, H, S, D] result is written as [B, S, H, D]
+  //      (the heads merged back, H = perm_p, S = M, D = perm_d)
+  int out_perm = 0;
+  int perm_p = 0, perm_d = 0;
 };
 
 // B operand layouts understood by the tensor-core kernel.

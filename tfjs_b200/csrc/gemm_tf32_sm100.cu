@@ -55,6 +55,7 @@ struct Tf32Args {
   int c_tma;  // 1: the epilogue stores through the C tensor map (N % 4 == 0)
   const float* residual;  // optional: out = post_act(act(acc + bias) + residual)
   int post_act;
+  int out_perm, perm_p, perm_d;  // heads-permuted store through a 4-D C map (GemmProblem)
   int patch_cap;          // staged-row gather: bytes per patch buffer, 0 = off
   int patch_pitch;        // floats between patch rows (left margin + image row + right margin)
   int patch_ml;           // floats of left margin
@@ -681,10 +682,27 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0 && rows_valid > 0) {
-            asm volatile(
-                "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                ::"l"(&tm_c), "r"(stage_buf), "r"(n0), "r"(m_base), "r"(bz)
-                : "memory");
+            if (g.out_perm == 0) {
+              asm volatile(
+                  "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                  ::"l"(&tm_c), "r"(stage_buf), "r"(n0), "r"(m_base), "r"(bz)
+                  : "memory");
+            } else {
+              // 4-D map over the permuted result: (d, s, h, b) for the heads split,
+              // (d, h, s, b) for the merge; the 32 x 32 tile is a box of it either way
+              int c0, c1, c2, c3;
+              if (g.out_perm == 1) {
+                c2 = n0 / g.perm_d; c0 = n0 - c2 * g.perm_d;
+                c3 = m_base / g.perm_p; c1 = m_base - c3 * g.perm_p;
+              } else {
+                c0 = n0; c2 = m_base;
+                c3 = bz / g.perm_p; c1 = bz - c3 * g.perm_p;
+              }
+              asm volatile(
+                  "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                  ::"l"(&tm_c), "r"(stage_buf), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                  : "memory");
+            }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
           continue;
@@ -1329,6 +1347,43 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     g.patch_bufs = plan.bufs;
   }
   bool res_tma = false;
+  g.out_perm = pr.out_perm;
+  g.perm_p = pr.perm_p;
+  g.perm_d = pr.perm_d;
+  if (pr.out_perm != 0) {
+    // every 32 x 32 store tile must be one box of the permuted tensor
+    const int S = pr.out_perm == 1 ? pr.perm_p : pr.M, D = pr.perm_d;
+    const bool shape_ok =
+        pr.out_perm == 1 ? (pr.batch == 1 && pr.perm_p > 0 && D > 0 && pr.M % pr.perm_p == 0 &&
+                            pr.N % D == 0)
+                         : (pr.out_perm == 2 && pr.perm_p > 0 && pr.batch % pr.perm_p == 0 &&
+                            D == pr.N);
+    if (!shape_ok || (S & 31) || (D & 31) || ((uintptr_t)pr.c & 15) || pr.residual)
+      return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
+                      "heads-permuted store: sequence and head sizes must be multiples of 32");
+    EncodeTiledFn enc = get_encode();
+    const cuuint64_t B = pr.out_perm == 1 ? pr.M / pr.perm_p : pr.batch / pr.perm_p;
+    const cuuint64_t H = pr.out_perm == 1 ? pr.N / D : pr.perm_p;
+    cuuint64_t dims[4], strides[3];
+    cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+    dims[0] = D; dims[3] = B;
+    if (pr.out_perm == 1) {  // physical [B, H, S, D]
+      dims[1] = S; dims[2] = H;
+      strides[0] = (cuuint64_t)D * 4; strides[1] = (cuuint64_t)S * D * 4;
+      box[0] = 32; box[1] = 32; box[2] = 1; box[3] = 1;
+    } else {                 // physical [B, S, H, D]
+      dims[1] = H; dims[2] = S;
+      strides[0] = (cuuint64_t)D * 4; strides[1] = (cuuint64_t)H * D * 4;
+      box[0] = 32; box[1] = 1; box[2] = 32; box[3] = 1;
+    }
+    strides[2] = (cuuint64_t)H * S * D * 4;
+    if (!enc || enc(&tm_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)pr.c, dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "heads-permuted store: tensor map refused");
+    g.c_tma = 1;
+  } else
   if ((pr.N & 3) == 0 && ((uintptr_t)pr.c & 15) == 0 && ((uintptr_t)pr.residual & 15) == 0) {
     EncodeTiledFn enc = get_encode();
     cuuint64_t dims[3] = {(cuuint64_t)pr.N, (cuuint64_t)pr.M, (cuuint64_t)pr.batch};
@@ -1364,7 +1419,7 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   if (swap_k < 0)
     swap_k = getenv("TFJS_CUDA_SWAP_AB_KSTEPS") ? atoi(getenv("TFJS_CUDA_SWAP_AB_KSTEPS")) : 12;
   if (swap_k > 0 && op.k_steps >= swap_k && op.b_layout == B_K_MAJOR && pr.N <= 128 &&
-      g.c_tma && !pr.residual && pr.ap.act != TFJS_CUDA_ACT_PRELU &&
+      g.c_tma && !pr.residual && pr.out_perm == 0 && pr.ap.act != TFJS_CUDA_ACT_PRELU &&
       (op.a_gather == 0 || (op.a_gather == 1 && !no_im2col))) {
     memset(&tm_a, 0, sizeof tm_a);
     bool ok;

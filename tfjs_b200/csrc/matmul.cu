@@ -133,9 +133,9 @@ int fill_act(tfjs_cuda_ctx* ctx, int activation, int prelu_len, int32_t prelu_id
 
 extern "C" {
 
-int tfjs_cuda_fused_matmul(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
-                           int32_t a_id, int32_t b_id, int32_t bias_id,
-                           int32_t prelu_id, int32_t out_id) {
+static int matmul_impl(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p, int32_t a_id,
+                       int32_t b_id, int32_t bias_id, int32_t prelu_id, int32_t out_perm,
+                       int32_t perm_p, int32_t perm_d, int32_t out_id) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
   if (!p) return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_matmul: null params");
   if (p->batch_a <= 0 || p->batch_b <= 0 || p->m < 0 || p->n < 0 || p->k < 0)
@@ -170,6 +170,9 @@ int tfjs_cuda_fused_matmul(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
   pr.trans_a = p->transpose_a != 0;
   pr.trans_b = p->transpose_b != 0;
   pr.is_conv = false;
+  pr.out_perm = out_perm;
+  pr.perm_p = perm_p;
+  pr.perm_d = perm_d;
 
   const bool tc_ok = ctx->math_mode == TFJS_CUDA_MATH_TF32 && p->k > 0 && (p->k % 4) == 0 &&
                      !pr.trans_a;
@@ -205,9 +208,31 @@ int tfjs_cuda_fused_matmul(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
       return rc;
     }
   }
+  if (out_perm != 0)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
+                    "fused_matmul_heads: only the tensor-core path stores permuted results");
   rc = launch_gemm_simt(ctx, pr);
   if (rc == TFJS_CUDA_OK) ctx_mark_written(ctx, out_id);
   return rc;
+}
+
+int tfjs_cuda_fused_matmul(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
+                           int32_t a_id, int32_t b_id, int32_t bias_id,
+                           int32_t prelu_id, int32_t out_id) {
+  return matmul_impl(ctx, p, a_id, b_id, bias_id, prelu_id, 0, 0, 0, out_id);
+}
+
+int tfjs_cuda_fused_matmul_heads(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
+                                 int32_t a_id, int32_t b_id, int32_t bias_id, int32_t prelu_id,
+                                 int32_t layout, int32_t rows_or_heads, int32_t head_dim,
+                                 int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (layout != TFJS_CUDA_HEADS_SPLIT && layout != TFJS_CUDA_HEADS_MERGE)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_matmul_heads: unknown layout %d", layout);
+  if (rows_or_heads <= 0 || head_dim <= 0)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_matmul_heads: bad sizes");
+  return matmul_impl(ctx, p, a_id, b_id, bias_id, prelu_id, layout, rows_or_heads, head_dim,
+                     out_id);
 }
 
 static int conv2d_impl(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p, int32_t x_id,

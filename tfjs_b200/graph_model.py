@@ -263,6 +263,8 @@ def execute_op(node, inp):
         return ops.identity(inp[0])
     if op == "_FusedLayerNorm":
         return _exec_layer_norm(node, inp)
+    if op == "_MatMulHeads":
+        return _exec_matmul_heads(node, inp)
     if op in ("FusedBatchNorm", "FusedBatchNormV2", "FusedBatchNormV3"):
         return ops.batch_norm(inp[0], inp[3], inp[4], inp[2], inp[1],
                               attr_number(node.attrs, "epsilon", 0.001))
@@ -418,6 +420,137 @@ def fuse_layer_norms(ordered, is_const, const_value, const_shape, protected=()):
     return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
 
 
+_HEADS_REFUSED = set()   # (layout, operand shapes) the library has declined once
+
+
+def _exec_matmul_heads(node, inp):
+    """matMul + Reshape + Transpose([0, 2, 1, 3]) (heads split) or matMul + Transpose +
+    Reshape (heads merged) as one product stored in the permuted order; the three ops one
+    after the other when the library declines the shape."""
+    from ._cabi import CudaError, UNSUPPORTED
+    layout = attr_string(node.attrs, "_layout")
+    inner_op = attr_string(node.attrs, "_op", keep_case=True)
+    dims = attr_number_list(node.attrs, "_dims")      # the Reshape's target shape
+    inner = Node({"name": node.name, "op": inner_op, "input": [], "attr": node.attrs})
+    a, b = inp[0], inp[1]
+    if inner_op == "_FusedMatMul":
+        bias, prelu, act, alpha = _fused_params(inner, inp)
+        ta, tb = attr_bool(node.attrs, "transpose_a"), attr_bool(node.attrs, "transpose_b")
+    else:
+        bias = prelu = alpha = None
+        act = "linear"
+        key = ("adj_x", "adj_y") if inner_op.startswith("BatchMatMul") else \
+            ("transpose_a", "transpose_b")
+        ta, tb = attr_bool(node.attrs, key[0]), attr_bool(node.attrs, key[1])
+    if layout == "split":
+        heads = dims if len(dims) == 4 and all(d > 0 for d in dims) else None
+    else:
+        # the product is [B, H, S, D]; the Reshape flattens its transpose [B, S, H, D]
+        heads = None
+        if len(a.shape) == 4 and len(b.shape) == 4:
+            B, H = a.shape[0], a.shape[1]
+            S = a.shape[2] if not ta else a.shape[3]
+            D = b.shape[3] if not tb else b.shape[2]
+            heads = [B, S, H, D]
+    sig = (layout, tuple(a.shape), tuple(b.shape), ta, tb)
+    if heads is not None and sig not in _HEADS_REFUSED:
+        try:
+            y = ops.mat_mul_heads(a, b, layout, heads, ta, tb, bias, act, prelu, alpha)
+            if layout == "split":
+                return y
+            out = ops.reshape(y, dims)
+            y.dispose()
+            return out
+        except CudaError as e:
+            if e.code != UNSUPPORTED:
+                raise
+            _HEADS_REFUSED.add(sig)
+    y = execute_op(inner, inp)
+    try:
+        if layout == "split":
+            r = ops.reshape(y, dims)
+            try:
+                return ops.transpose(r, [0, 2, 1, 3])
+            finally:
+                r.dispose()
+        t = ops.transpose(y, [0, 2, 1, 3])
+        try:
+            return ops.reshape(t, dims)
+        finally:
+            t.dispose()
+    finally:
+        y.dispose()
+
+
+def fuse_attention_heads(ordered, is_const, const_value, protected=()):
+    """Plan rewrite: the Reshape + Transpose([0, 2, 1, 3]) that splits a projection into
+    attention heads, and the Transpose + Reshape that merges them again, become the store
+    order of the product in front of them:
+
+        Transpose(Reshape(matMul(a, b ...), [B, S, H, D]), [0, 2, 1, 3])  -> `_MatMulHeads` split
+        Reshape(Transpose(batchMatMul(a, b), [0, 2, 1, 3]), shape)        -> `_MatMulHeads` merge
+
+    when the intermediate tensors have no other consumer and are not in `protected`.  The
+    new node keeps the name of the last node of the pattern and the attributes of the
+    product."""
+    by_name = {n.name: n for n in ordered}
+    consumers = {}
+    for n in ordered:
+        for i in n.inputs:
+            consumers.setdefault(parse_node_name(i)[0], []).append(n.name)
+    protected = set(protected)
+    MATMULS = ("_FusedMatMul", "MatMul", "BatchMatMul", "BatchMatMulV2")
+
+    def node(inp, op):
+        name, idx = parse_node_name(inp)
+        n = by_name.get(name)
+        return n if n is not None and idx == 0 and n.op in op else None
+
+    def const_ints(inp):
+        name, idx = parse_node_name(inp)
+        if idx != 0 or name not in by_name or by_name[name].op != "Const" or not is_const(name):
+            return None
+        return [int(v) for v in const_value(name)]
+
+    def only(n, user):
+        return consumers.get(n.name, []) == [user.name] and n.name not in protected
+
+    removed, replaced = set(), {}
+    for last in ordered:
+        if last.op == "Transpose" and len(last.inputs) == 2:            # heads split
+            r = node(last.inputs[0], ("Reshape",))
+            mm = node(r.inputs[0], MATMULS) if r is not None and len(r.inputs) == 2 else None
+            if mm is None or const_ints(last.inputs[1]) != [0, 2, 1, 3]:
+                continue
+            dims = const_ints(r.inputs[1])
+            layout = "split"
+            mid = r
+        elif last.op == "Reshape" and len(last.inputs) == 2:            # heads merge
+            t = node(last.inputs[0], ("Transpose",))
+            mm = node(t.inputs[0], MATMULS) if t is not None and len(t.inputs) == 2 else None
+            if mm is None or const_ints(t.inputs[1]) != [0, 2, 1, 3]:
+                continue
+            dims = const_ints(last.inputs[1])
+            layout = "merge"
+            mid = t
+        else:
+            continue
+        if dims is None or any(d <= 0 for d in dims) or (layout == "split" and len(dims) != 4):
+            continue
+        if mm.name in removed or not only(mm, mid) or not only(mid, last):
+            continue
+        removed.update((mm.name, mid.name))
+        attrs = dict(mm.attrs)
+        attrs["_layout"] = {"s": base64.b64encode(layout.encode()).decode()}
+        attrs["_op"] = {"s": base64.b64encode(mm.op.encode()).decode()}
+        attrs["_dims"] = {"list": {"i": [str(d) for d in dims]}}
+        replaced[last.name] = Node({"name": last.name, "op": "_MatMulHeads",
+                                    "input": list(mm.inputs), "attr": attrs})
+    if not replaced:
+        return list(ordered), 0
+    return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
+
+
 # ------------------------------------------------------------------- executor --
 class GraphExecutor(object):
     def __init__(self, nodes, weight_map):
@@ -435,6 +568,7 @@ class GraphExecutor(object):
         # plan rewrites (fuse_layer_norms); TFJS_CUDA_NO_GRAPH_FUSION=1 runs the graph as stored
         self.fuse = os.environ.get("TFJS_CUDA_NO_GRAPH_FUSION", "0") in ("", "0")
         self.fused_subgraphs = 0
+        self.fused_heads = 0
         self.keep_intermediates = False
         self.intermediates = {}
 
@@ -492,7 +626,12 @@ class GraphExecutor(object):
                 lambda name: np.asarray(_vals(self.weight_map[name])).reshape(-1),
                 lambda name: self.weight_map[name].shape,
                 protected=set(input_names) | set(parse_node_name(o)[0] for o in output_names))
+            ordered, k = fuse_attention_heads(
+                ordered, lambda name: name in self.weight_map,
+                lambda name: np.asarray(_vals(self.weight_map[name])).reshape(-1),
+                protected=set(input_names) | set(parse_node_name(o)[0] for o in output_names))
             self.fused_subgraphs = n
+            self.fused_heads = k
         last_use = {}
         for pos, node in enumerate(ordered):
             if node.name in input_names:

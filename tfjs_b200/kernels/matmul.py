@@ -13,7 +13,11 @@ from .common import BACKEND, assert_not_complex, dev, per_channel_len, require_f
 from . import elementwise
 
 
-def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activation, alpha):
+def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activation, alpha,
+                 heads=None):
+    """heads: None, or (layout, rows_or_heads, head_dim, out_shape) for the product stored
+    through the heads permutation (tfjs_cuda_fused_matmul_heads); bias and activation must
+    then be fusable, and a refusal by the library propagates as CudaError(UNSUPPORTED)."""
     assert_not_complex([a, b], "matMul")
     require_float32(a, "matMul")
     require_float32(b, "matMul")
@@ -44,7 +48,9 @@ def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activatio
     prelu_len = per_channel_len(prelu, outer_b) if activation == "prelu" else 0
     fuse_bias = bias_len is not None
     fuse_act = fuse_bias and (activation != "prelu" or prelu_len is not None)
-    out = backend.make_output(out_shape, "float32")
+    if heads is not None and not (fuse_bias and fuse_act and size_from_shape(out_shape)):
+        raise _cabi.CudaError(_cabi.UNSUPPORTED, "matMul heads: bias / activation not fusable")
+    out = backend.make_output(out_shape if heads is None else heads[3], "float32")
     if size_from_shape(out_shape) and batch_a and batch_b:
         p = _cabi.MatMulParams()
         p.batch_a, p.batch_b = batch_a, batch_b
@@ -55,11 +61,16 @@ def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activatio
         p.prelu_len = (prelu_len or 0) if fuse_act else 0
         p.leakyrelu_alpha = 0.2 if alpha is None else float(alpha)
         try:
-            backend.check(backend.lib.tfjs_cuda_fused_matmul(
-                backend.ctx, byref(p), dev(backend, a), dev(backend, b),
-                dev(backend, bias) if fuse_bias and bias is not None else 0,
-                dev(backend, prelu) if fuse_act and activation == "prelu" else 0,
-                dev(backend, out)))
+            bias_id = dev(backend, bias) if fuse_bias and bias is not None else 0
+            prelu_id = dev(backend, prelu) if fuse_act and activation == "prelu" else 0
+            if heads is None:
+                backend.check(backend.lib.tfjs_cuda_fused_matmul(
+                    backend.ctx, byref(p), dev(backend, a), dev(backend, b), bias_id, prelu_id,
+                    dev(backend, out)))
+            else:
+                backend.check(backend.lib.tfjs_cuda_fused_matmul_heads(
+                    backend.ctx, byref(p), dev(backend, a), dev(backend, b), bias_id, prelu_id,
+                    heads[0], heads[1], heads[2], dev(backend, out)))
         except Exception:
             backend.disposeData(out.dataId)
             raise
@@ -88,7 +99,34 @@ def batch_matmul(args):
                         a.get("transposeB", False), None, None, "linear", None)
 
 
+def matmul_heads(args):
+    """The product of _FusedMatMul / BatchMatMul written through the permutation that splits
+    or merges attention heads (what Reshape + Transpose([0, 2, 1, 3]) would do in a pass of
+    its own).  attrs.layout "split": a [.., M, K] x b [K, N] with M = B*S, N = H*D gives
+    [B, H, S, D]; "merge": a [B, H, S, K] x b [B, H, K, D] gives [B, S, H, D];
+    attrs.heads = [B, S, H, D]."""
+    i, at, backend = args["inputs"], args["attrs"], args["backend"]
+    a, b = i["a"], i["b"]
+    B, S, H, D = [int(v) for v in at["heads"]]
+    ta, tb = at.get("transposeA", False), at.get("transposeB", False)
+    m = a.shape[-1] if ta else a.shape[-2]
+    n = b.shape[-2] if tb else b.shape[-1]
+    batch = size_from_shape(a.shape[:-2])
+    if at["layout"] == "split":
+        ok = batch == 1 and size_from_shape(b.shape[:-2]) == 1 and m == B * S and n == H * D
+        heads = (_cabi.HEADS_SPLIT, S, D, [B, H, S, D])
+    else:
+        ok = (list(a.shape[:-2]) == [B, H] and list(b.shape[:-2]) == [B, H] and m == S and n == D)
+        heads = (_cabi.HEADS_MERGE, H, D, [B, S, H, D])
+    if not ok:
+        raise _cabi.CudaError(_cabi.UNSUPPORTED, "matMul heads: operand shapes %s %s do not "
+                              "give heads %s" % (a.shape, b.shape, [B, S, H, D]))
+    return _matmul_impl(backend, a, b, ta, tb, i.get("bias"), i.get("preluActivationWeights"),
+                        at.get("activation") or "linear", at.get("leakyreluAlpha"), heads)
+
+
 CONFIGS = [
+    KernelConfig("_MatMulHeads", BACKEND, matmul_heads),
     KernelConfig("_FusedMatMul", BACKEND, fused_matmul),
     KernelConfig("BatchMatMul", BACKEND, batch_matmul),
 ]

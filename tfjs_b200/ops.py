@@ -157,6 +157,19 @@ def mat_mul(a, b, transposeA=False, transposeB=False):
                 {"transposeA": transposeA, "transposeB": transposeB})
 
 
+def mat_mul_heads(a, b, layout, heads, transposeA=False, transposeB=False, bias=None,
+                  activation="linear", preluActivationWeights=None, leakyreluAlpha=0.2):
+    """matMul whose result is stored with attention heads split ("split": [B*S, H*D] product
+    written as [B, H, S, D]) or merged ("merge": [B, H, S, D] product written as
+    [B, S, H, D]); heads = [B, S, H, D].  A kernel of the 'cuda' backend with no counterpart
+    among the reference's ops (the graph executor substitutes it for matMul + reshape +
+    transpose); raises CudaError(UNSUPPORTED) for shapes it does not take."""
+    return _run("_MatMulHeads", {"a": a, "b": b, "bias": bias,
+                                 "preluActivationWeights": preluActivationWeights},
+                {"transposeA": transposeA, "transposeB": transposeB, "activation": activation,
+                 "leakyreluAlpha": leakyreluAlpha, "layout": layout, "heads": list(heads)})
+
+
 def fused_mat_mul(a, b, transposeA=False, transposeB=False, bias=None, activation="linear",
                   preluActivationWeights=None, leakyreluAlpha=0.2):
     """tfjs-core/src/ops/fused/mat_mul.ts: operands are reshaped to rank 3 first

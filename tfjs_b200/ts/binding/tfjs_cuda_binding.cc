@@ -184,6 +184,12 @@ napi_value FusedMatMul(napi_env env, napi_callback_info info) {
   auto* p = static_cast<tfjs_cuda_matmul_params*>(a.buffer(1));
   return check(env, a.ctx(0), tfjs_cuda_fused_matmul(a.ctx(0), p, a.i32(2), a.i32(3), a.i32(4), a.i32(5), a.i32(6)));
 }
+napi_value FusedMatMulHeads(napi_env env, napi_callback_info info) {
+  Args a(env, info);  // ctx, params, aId, bId, biasId, preluId, layout, rowsOrHeads, headDim, outId
+  auto* p = static_cast<tfjs_cuda_matmul_params*>(a.buffer(1));
+  return check(env, a.ctx(0), tfjs_cuda_fused_matmul_heads(a.ctx(0), p, a.i32(2), a.i32(3), a.i32(4), a.i32(5),
+                                                           a.i32(6), a.i32(7), a.i32(8), a.i32(9)));
+}
 napi_value Pool2D(napi_env env, napi_callback_info info) {
   Args a(env, info);
   auto* p = static_cast<tfjs_cuda_conv2d_params*>(a.buffer(1));
@@ -264,7 +270,7 @@ napi_value Init(napi_env env, napi_value exports) {
       {"readBegin", ReadBegin}, {"readWait", ReadWait}, {"sync", Sync}, {"memory", Memory}, {"timeBegin", TimeBegin}, {"timeEnd", TimeEnd},
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},
       {"fusedConv2dResidual", FusedConv2DResidual}, {"addActivation", AddActivation},
-      {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul},
+      {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul}, {"fusedMatMulHeads", FusedMatMulHeads},
       {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm},
       {"reduce", Reduce}, {"argMax", ArgMax}, {"transpose", Transpose}, {"gather", Gather},
       {"cast", Cast}, {"copyStrided", CopyStrided}, {"fill", Fill}, {"batchNorm", BatchNorm},

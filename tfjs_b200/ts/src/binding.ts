@@ -41,6 +41,9 @@ export interface CudaBinding {
                        prelu: number, out: number): void;
   fusedMatMul(ctx: Ctx, params: ArrayBuffer, a: number, b: number, bias: number, prelu: number,
               out: number): void;
+  fusedMatMulHeads(ctx: Ctx, params: ArrayBuffer, a: number, b: number, bias: number,
+                   prelu: number, layout: number, rowsOrHeads: number, headDim: number,
+                   out: number): void;
   pool2d(ctx: Ctx, params: ArrayBuffer, isMax: number, x: number, out: number): void;
   binary(ctx: Ctx, op: number, dtype: number, rank: number, a: number, aShape: BigInt64Array,
          b: number, bShape: BigInt64Array, out: number, outShape: BigInt64Array): void;
