@@ -348,6 +348,16 @@ int tfjs_cuda_fused_elementwise_catalogued(tfjs_cuda_ctx* ctx, const tfjs_cuda_e
 int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
                       uint64_t cols, int32_t out_id);
 
+/* Softmax of fl32(fl32(x * scale) + mask): the Multiply.ts (by a scalar) and Add.ts kernels
+ * that scale and mask attention scores, applied on the way into the softmax with the same
+ * fp32 roundings.  has_scale = 0 skips the product; mask_id = 0 the sum.  The mask holds
+ * ceil(rows / rows_per_mask) rows of cols floats; row r of x uses mask row r / rows_per_mask
+ * (rows_per_mask = heads * queries for a [batch, 1, 1, keys] mask, 1 for a mask shaped like
+ * x, rows for a single row). */
+int tfjs_cuda_softmax_scaled_masked(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
+                                    uint64_t cols, int32_t has_scale, float scale,
+                                    int32_t mask_id, uint64_t rows_per_mask, int32_t out_id);
+
 /* ---- Layer normalisation over the last axis of a [rows, cols] view, in the decomposed
  * form a converted graph holds: y = ((x - mean) * rsqrt(var + epsilon)) * gamma + beta with
  * mean = Mean(x), var = Mean(SquaredDifference(x, mean)).  One launch for the nine (ten with the residual Add) kernels

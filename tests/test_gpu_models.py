@@ -273,9 +273,39 @@ def test_bert_with_folded_head_transposes_matches_the_stored_graph(cuda_engine):
         y = gm.execute(ins, ["sequence_output"])[0]
         outs.append(y.arraySync())
         assert gm.executor.fused_heads == (8 if fuse else 0)
+        assert gm.executor.fused_softmaxes == (2 if fuse else 0)
         y.dispose()
         assert be.numDataIds() == before
         for t in ins.values():
             t.dispose()
         gm.dispose()
     assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
+# ------------------------------------------------- plan rewrite: softmax of scores --
+@pytest.mark.parametrize("case", [((4, 6, 64, 128), (4, 1, 1, 128), 0.125),
+                                  ((4, 6, 64, 128), (4, 6, 64, 128), 0.5),
+                                  ((3, 5, 40), (40,), 0.3), ((2, 3, 8, 2000), (2, 1, 1, 2000), 2.0),
+                                  ((4, 6, 64, 128), None, 0.125),
+                                  ((4, 6, 16, 32), (1, 6, 1, 32), 0.125)])
+def test_scaled_masked_softmax_has_the_bits_of_the_separate_kernels(cuda_engine, case):
+    """The last case's mask does not broadcast over whole rows: the executor runs the three
+    kernels."""
+    from tfjs_b200 import graph_model, ops
+    xs, ms, scale = case
+    r = np.random.default_rng(len(xs) * 100 + xs[-1])
+    x = ops.tensor((r.standard_normal(xs) * 4).astype(np.float32))
+    mask = None if ms is None else ops.tensor(
+        np.where(r.random(ms) < 0.2, -10000.0, 0.0).astype(np.float32))
+    node = graph_model.Node({"name": "p", "op": "_SoftmaxScaledMasked",
+                             "input": ["x"] + (["m"] if ms else []),
+                             "attr": {"_scale": {"f": float(np.float32(scale))}}})
+    got_t = graph_model.execute_op(node, [x] + ([mask] if ms else []))
+    c = ops.tensor(np.float32(scale))
+    s1 = ops.mul(x, c)
+    s2 = ops.add(s1, mask) if ms else ops.identity(s1)
+    ref_t = ops.softmax(s2)
+    got, ref = got_t.arraySync(), ref_t.arraySync()
+    for t in [x, got_t, c, s1, s2, ref_t] + ([mask] if ms else []):
+        t.dispose()
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))

@@ -216,3 +216,31 @@ def test_heads_rewrite_keeps_a_product_that_is_read_elsewhere():
     _, n = G.fuse_attention_heads(nodes, lambda x: x in consts, lambda x: consts[x].reshape(-1),
                                   protected=[r.name])
     assert n == 47
+
+
+# ------------------------------------------------- plan rewrite: softmax of scores --
+def test_scaled_masked_softmax_of_bert_is_one_node():
+    G, nodes, consts = _bert_plan()
+    new, n = G.fuse_softmax_inputs(nodes, lambda x: x in consts, lambda x: consts[x].reshape(-1))
+    assert n == 12 and len(new) == len(nodes) - 2 * n
+    for x in new:
+        if x.op == "_SoftmaxScaledMasked":
+            assert len(x.inputs) == 2
+            assert abs(G.attr_number(x.attrs, "_scale") - float(np.float32(0.125))) < 1e-12
+    sm = next(x for x in nodes if x.op == "Softmax")
+    _, n = G.fuse_softmax_inputs(nodes, lambda x: x in consts, lambda x: consts[x].reshape(-1),
+                                 protected=[G.parse_node_name(sm.inputs[0])[0]])
+    assert n == 11
+
+
+def test_softmax_mask_rows():
+    from tfjs_b200.kernels.reduce import softmax_mask_rows as f
+    assert f([64, 12, 128, 128], [64, 1, 1, 128]) == 12 * 128
+    assert f([64, 12, 128, 128], [64, 12, 128, 128]) == 1
+    assert f([64, 12, 128, 128], [128]) == 64 * 12 * 128
+    assert f([64, 12, 128, 128], [1, 1, 1, 128]) == 64 * 12 * 128
+    assert f([64, 12, 128, 128], [64, 12, 1, 128]) == 128
+    assert f([64, 12, 128, 128], [1, 12, 1, 128]) is None
+    assert f([64, 12, 128, 128], [64, 1, 128, 128]) is None
+    assert f([64, 12, 128, 128], [64, 1, 1, 1]) is None
+    assert f([5, 7], [7]) == 5 and f([7], [7]) == 1

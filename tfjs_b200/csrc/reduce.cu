@@ -34,22 +34,39 @@ __device__ __forceinline__ float warp_nan_max(float v) {
 // out = fl32(e / s).  One warp per row.
 // REGS values per lane stay in registers (rows up to 32*REGS wide); REGS == 0 is
 // the wide-row variant that re-reads its own output instead.
+// Optional prologue (the scaled, masked scores of an attention layer): logit =
+// fl32(fl32(x * scale) + mask[row / rows_per_mask][col]), the Multiply.ts and Add.ts
+// kernels in front of the softmax, formed on the way in.
+struct SoftmaxPrologue {
+  int has_scale;
+  float scale;
+  const float* mask;        // null: none
+  uint64_t rows_per_mask;   // consecutive rows that share one mask row
+};
+__device__ __forceinline__ float softmax_logit(const SoftmaxPrologue& pg, const float* mrow,
+                                               float v, uint32_t c) {
+  if (pg.has_scale) v = __fmul_rn(v, pg.scale);
+  if (mrow) v = __fadd_rn(v, __ldg(mrow + c));
+  return v;
+}
+
 template <int REGS>
 __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ y,
-                               uint64_t rows, uint32_t cols) {
+                               uint64_t rows, uint32_t cols, SoftmaxPrologue pg) {
   const int lane = threadIdx.x & 31;
   const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
   for (uint64_t r = warp; r < rows; r += nwarps) {
     const float* xr = x + r * cols;
     float* yr = y + r * cols;
-    float m = xr[0];
+    const float* mrow = pg.mask ? pg.mask + (r / pg.rows_per_mask) * cols : nullptr;
+    float m = softmax_logit(pg, mrow, xr[0], 0);
     if (REGS > 0) {
       float v[REGS > 0 ? REGS : 1];
 #pragma unroll
       for (int j = 0; j < REGS; ++j) {
         const uint32_t c = lane + 32 * j;
-        v[j] = c < cols ? xr[c] : -INFINITY;
+        v[j] = c < cols ? softmax_logit(pg, mrow, xr[c], c) : -INFINITY;
         if (c < cols) m = nan_max(m, v[j]);
       }
       m = warp_nan_max(m);
@@ -69,11 +86,11 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
         if (c < cols) yr[c] = __fdiv_rn(v[j], sf);
       }
     } else {
-      for (uint32_t c = lane; c < cols; c += 32) m = nan_max(m, xr[c]);
+      for (uint32_t c = lane; c < cols; c += 32) m = nan_max(m, softmax_logit(pg, mrow, xr[c], c));
       m = warp_nan_max(m);
       double s = 0.0;
       for (uint32_t c = lane; c < cols; c += 32) {
-        const float e = (float)exp_fast((double)__fsub_rn(xr[c], m));
+        const float e = (float)exp_fast((double)__fsub_rn(softmax_logit(pg, mrow, xr[c], c), m));
         yr[c] = e;
         s += (double)e;
       }
@@ -317,13 +334,25 @@ __global__ void argmax_mid_kernel(const float* __restrict__ x,
 
 extern "C" {
 
-int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
-                      uint64_t cols, int32_t out_id) {
+static int softmax_impl(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows, uint64_t cols,
+                        int32_t has_scale, float scale, int32_t mask_id,
+                        uint64_t rows_per_mask, int32_t out_id) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
-  Buffer *x, *y;
+  Buffer *x, *y, *mask = nullptr;
   int rc;
   if ((rc = ctx_get(ctx, x_id, rows * cols * 4, "softmax x", &x))) return rc;
   if ((rc = ctx_get(ctx, out_id, rows * cols * 4, "softmax out", &y))) return rc;
+  if (mask_id != 0) {
+    if (rows_per_mask == 0)
+      return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "softmax: rows_per_mask must be positive");
+    const uint64_t mask_rows = rows ? (rows - 1) / rows_per_mask + 1 : 0;
+    if ((rc = ctx_get(ctx, mask_id, mask_rows * cols * 4, "softmax mask", &mask))) return rc;
+  }
+  SoftmaxPrologue pg;
+  pg.has_scale = has_scale;
+  pg.scale = scale;
+  pg.mask = mask ? (const float*)mask->ptr : nullptr;
+  pg.rows_per_mask = rows_per_mask ? rows_per_mask : 1;
   if (rows * cols == 0) return TFJS_CUDA_OK;
   if (cols > 0xffffffffu)
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "softmax: row too wide");
@@ -332,7 +361,7 @@ int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
   const float* xp = (const float*)x->ptr;
   float* yp = (float*)y->ptr;
   const uint32_t c32 = (uint32_t)cols;
-#define SOFTMAX(R) softmax_kernel<R><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32)
+#define SOFTMAX(R) softmax_kernel<R><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32, pg)
   if (cols <= 32) SOFTMAX(1);
   else if (cols <= 64) SOFTMAX(2);
   else if (cols <= 128) SOFTMAX(4);
@@ -344,6 +373,17 @@ int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
   LAUNCH_CHECK(ctx, "softmax_kernel");
   ctx_mark_written(ctx, out_id);
   return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_softmax(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
+                      uint64_t cols, int32_t out_id) {
+  return softmax_impl(ctx, x_id, rows, cols, 0, 1.0f, 0, 1, out_id);
+}
+
+int tfjs_cuda_softmax_scaled_masked(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows,
+                                    uint64_t cols, int32_t has_scale, float scale,
+                                    int32_t mask_id, uint64_t rows_per_mask, int32_t out_id) {
+  return softmax_impl(ctx, x_id, rows, cols, has_scale, scale, mask_id, rows_per_mask, out_id);
 }
 
 int tfjs_cuda_layer_norm(tfjs_cuda_ctx* ctx, int32_t x_id, int32_t residual_id, int32_t gamma_id,

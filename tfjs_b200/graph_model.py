@@ -265,6 +265,8 @@ def execute_op(node, inp):
         return _exec_layer_norm(node, inp)
     if op == "_MatMulHeads":
         return _exec_matmul_heads(node, inp)
+    if op == "_SoftmaxScaledMasked":
+        return _exec_softmax_fused(node, inp)
     if op in ("FusedBatchNorm", "FusedBatchNormV2", "FusedBatchNormV3"):
         return ops.batch_norm(inp[0], inp[3], inp[4], inp[2], inp[1],
                               attr_number(node.attrs, "epsilon", 0.001))
@@ -420,6 +422,95 @@ def fuse_layer_norms(ordered, is_const, const_value, const_shape, protected=()):
     return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
 
 
+def _exec_softmax_fused(node, inp):
+    from .kernels.reduce import softmax_mask_rows
+    scale = attr_number(node.attrs, "_scale")
+    x = inp[0]
+    mask = inp[1] if len(inp) > 1 else None
+    if x.dtype == "float32" and len(x.shape) >= 1 and (
+            mask is None or (mask.dtype == "float32" and
+                             softmax_mask_rows(x.shape, mask.shape) is not None)):
+        return ops.softmax_scaled_masked(x, scale, mask)
+    tmp = []
+    try:
+        if scale is not None:
+            c = ops.tensor(np.float32(scale))
+            tmp.append(c)
+            x = ops.mul(x, c)
+            tmp.append(x)
+        if mask is not None:
+            x = ops.add(x, mask)
+            tmp.append(x)
+        return ops.softmax(x)
+    finally:
+        for t in tmp:
+            t.dispose()
+
+
+def fuse_softmax_inputs(ordered, is_const, const_value, protected=()):
+    """Plan rewrite: Softmax(AddV2(Mul(s, c), mask)) and Softmax(Mul(s, c)) with c a scalar
+    constant (attention scores scaled by 1 / sqrt(d) and masked) become one
+    `_SoftmaxScaledMasked(s[, mask]; scale)` node named like the Softmax, when the
+    intermediate tensors have no other consumer and are not in `protected`."""
+    by_name = {n.name: n for n in ordered}
+    consumers = {}
+    for n in ordered:
+        for i in n.inputs:
+            consumers.setdefault(parse_node_name(i)[0], []).append(n.name)
+    protected = set(protected)
+
+    def node(inp, op):
+        name, idx = parse_node_name(inp)
+        n = by_name.get(name)
+        return n if n is not None and idx == 0 and n.op in op else None
+
+    def scalar_const(inp):
+        name, idx = parse_node_name(inp)
+        if idx != 0 or name not in by_name or by_name[name].op != "Const" or not is_const(name):
+            return None
+        v = const_value(name)
+        return float(np.float32(v[0])) if len(v) == 1 else None
+
+    def scaled(inp):
+        """(scores input, scale, Mul node) when inp is Mul(scores, scalar const)."""
+        m = node(inp, ("Mul",))
+        if m is None or len(m.inputs) != 2:
+            return None
+        for a, b in ((m.inputs[0], m.inputs[1]), (m.inputs[1], m.inputs[0])):
+            c = scalar_const(b)
+            if c is not None and scalar_const(a) is None:
+                return a, c, m
+        return None
+
+    def only(n, user):
+        return consumers.get(n.name, []) == [user.name] and n.name not in protected
+
+    removed, replaced = set(), {}
+    for sm in ordered:
+        if sm.op != "Softmax" or len(sm.inputs) != 1:
+            continue
+        ins, scale, gone = None, None, []
+        add = node(sm.inputs[0], ("Add", "AddV2"))
+        if add is not None and len(add.inputs) == 2 and only(add, sm):
+            for a, b in ((add.inputs[0], add.inputs[1]), (add.inputs[1], add.inputs[0])):
+                sc = scaled(a)
+                if sc is not None and only(sc[2], add):
+                    ins, scale, gone = [sc[0], b], sc[1], [add, sc[2]]
+                    break
+        else:
+            sc = scaled(sm.inputs[0])
+            if sc is not None and only(sc[2], sm):
+                ins, scale, gone = [sc[0]], sc[1], [sc[2]]
+        if ins is None:
+            continue
+        removed.update(n.name for n in gone)
+        replaced[sm.name] = Node({"name": sm.name, "op": "_SoftmaxScaledMasked", "input": ins,
+                                  "attr": {"_scale": {"f": scale}}})
+    if not replaced:
+        return list(ordered), 0
+    return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
+
+
 _HEADS_REFUSED = set()   # (layout, operand shapes) the library has declined once
 
 
@@ -566,9 +657,13 @@ class GraphExecutor(object):
                                 if n.name not in consumed and n.op not in ("Const", "Placeholder")]
         self._compiled = {}
         # plan rewrites (fuse_layer_norms); TFJS_CUDA_NO_GRAPH_FUSION=1 runs the graph as stored
-        self.fuse = os.environ.get("TFJS_CUDA_NO_GRAPH_FUSION", "0") in ("", "0")
+        off = os.environ.get("TFJS_CUDA_NO_GRAPH_FUSION", "0")
+        self.fuse = off in ("", "0") or off not in ("1", "all")
+        # ...=layernorm,heads,softmax switches single rewrites off
+        self.fuse_skip = set(off.split(",")) if self.fuse else set()
         self.fused_subgraphs = 0
         self.fused_heads = 0
+        self.fused_softmaxes = 0
         self.keep_intermediates = False
         self.intermediates = {}
 
@@ -621,17 +716,24 @@ class GraphExecutor(object):
                 state[root] = 1
                 visit(root)
         if fuse:
+            n = k = j = 0
+            prot = set(input_names) | set(parse_node_name(o)[0] for o in output_names)
+            consts = (lambda name: name in self.weight_map,
+                      lambda name: np.asarray(_vals(self.weight_map[name])).reshape(-1))
+        if fuse and "layernorm" not in self.fuse_skip:
             ordered, n = fuse_layer_norms(
                 ordered, lambda name: name in self.weight_map,
                 lambda name: np.asarray(_vals(self.weight_map[name])).reshape(-1),
                 lambda name: self.weight_map[name].shape,
                 protected=set(input_names) | set(parse_node_name(o)[0] for o in output_names))
-            ordered, k = fuse_attention_heads(
-                ordered, lambda name: name in self.weight_map,
-                lambda name: np.asarray(_vals(self.weight_map[name])).reshape(-1),
-                protected=set(input_names) | set(parse_node_name(o)[0] for o in output_names))
+        if fuse and "heads" not in self.fuse_skip:
+            ordered, k = fuse_attention_heads(ordered, consts[0], consts[1], protected=prot)
+        if fuse and "softmax" not in self.fuse_skip:
+            ordered, j = fuse_softmax_inputs(ordered, consts[0], consts[1], protected=prot)
+        if fuse:
             self.fused_subgraphs = n
             self.fused_heads = k
+            self.fused_softmaxes = j
         last_use = {}
         for pos, node in enumerate(ordered):
             if node.name in input_names:

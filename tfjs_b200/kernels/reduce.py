@@ -137,6 +137,48 @@ def _softmax(args):
     return out
 
 
+def softmax_mask_rows(x_shape, mask_shape):
+    """rows_per_mask for a mask that broadcasts against x over whole rows: the mask equals x
+    on the last axis and on a (possibly empty) run of leading axes and is 1 in between.
+    None when it broadcasts any other way."""
+    rank = len(x_shape)
+    m = [1] * (rank - len(mask_shape)) + list(mask_shape)
+    if len(m) != rank or rank == 0 or m[-1] != x_shape[-1]:
+        return None
+    lead = 0
+    while lead < rank - 1 and m[lead] == x_shape[lead]:
+        lead += 1
+    if any(d != 1 for d in m[lead:rank - 1]):
+        return None
+    return max(size_from_shape(list(x_shape[lead:rank - 1])), 1)
+
+
+def _softmax_scaled_masked(args):
+    """softmax(x * scale + mask) over the last axis in one launch (the scaled, masked scores
+    of an attention layer; graph_model.fuse_softmax_inputs)."""
+    backend, inp, at = args["backend"], args["inputs"], args["attrs"]
+    x, mask = inp["logits"], inp.get("mask")
+    scale = at.get("scale")
+    cols = x.shape[-1]
+    rows = size_from_shape(x.shape[:-1])
+    rpm = 1
+    if mask is not None:
+        rpm = softmax_mask_rows(x.shape, mask.shape)
+        if rpm is None or mask.dtype != "float32":
+            raise ValueError("_SoftmaxScaledMasked: mask %s does not broadcast over rows of %s"
+                             % (mask.shape, x.shape))
+    out = backend.make_output(x.shape, "float32")
+    try:
+        backend.check(backend.lib.tfjs_cuda_softmax_scaled_masked(
+            backend.ctx, dev(backend, x), rows, cols, int(scale is not None),
+            float(np.float32(scale if scale is not None else 1.0)), dev(backend, mask), rpm,
+            dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    return out
+
+
 def layer_norm_supported(x_shape, gamma_shape, beta_shape):
     """Shapes the one-launch layer normalisation takes: rows of a multiple of 4 up to 1024
     floats, gamma and beta one value per column."""
@@ -184,4 +226,5 @@ CONFIGS = [
     KernelConfig("ArgMax", BACKEND, _argmax),
     KernelConfig("Softmax", BACKEND, _softmax),
     KernelConfig("_FusedLayerNorm", BACKEND, _fused_layer_norm),
+    KernelConfig("_SoftmaxScaledMasked", BACKEND, _softmax_scaled_masked),
 ]

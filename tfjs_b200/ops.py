@@ -301,6 +301,13 @@ def softmax(logits, dim=-1):
     return _run("Softmax", {"logits": logits}, {"dim": dim})
 
 
+def softmax_scaled_masked(logits, scale=None, mask=None):
+    """softmax(logits * scale + mask) over the last axis as one kernel of the 'cuda' backend
+    (the graph executor substitutes it for Mul + AddV2 + Softmax); the mask must broadcast
+    over whole rows."""
+    return _run("_SoftmaxScaledMasked", {"logits": logits, "mask": mask}, {"scale": scale})
+
+
 def fused_layer_norm(x, gamma, beta, epsilon, residual=None):
     """Layer normalisation over the last axis in the decomposed form of a converted graph,
     as one kernel of the 'cuda' backend (no counterpart among the reference's ops; the

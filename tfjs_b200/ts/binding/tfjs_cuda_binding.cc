@@ -209,6 +209,11 @@ napi_value Softmax(napi_env env, napi_callback_info info) {
   Args a(env, info);
   return check(env, a.ctx(0), tfjs_cuda_softmax(a.ctx(0), a.i32(1), a.u64(2), a.u64(3), a.i32(4)));
 }
+napi_value SoftmaxScaledMasked(napi_env env, napi_callback_info info) {
+  Args a(env, info);  // ctx, xId, rows, cols, hasScale, scale, maskId, rowsPerMask, outId
+  return check(env, a.ctx(0), tfjs_cuda_softmax_scaled_masked(a.ctx(0), a.i32(1), a.u64(2), a.u64(3), a.i32(4),
+                                                              static_cast<float>(a.f64(5)), a.i32(6), a.u64(7), a.i32(8)));
+}
 napi_value LayerNorm(napi_env env, napi_callback_info info) {
   Args a(env, info);  // ctx, xId, residualId (0: none), gammaId, betaId, rows, cols, epsilon, outId
   return check(env, a.ctx(0), tfjs_cuda_layer_norm(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.i32(4), a.u64(5),
@@ -271,7 +276,7 @@ napi_value Init(napi_env env, napi_value exports) {
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},
       {"fusedConv2dResidual", FusedConv2DResidual}, {"addActivation", AddActivation},
       {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul}, {"fusedMatMulHeads", FusedMatMulHeads},
-      {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm},
+      {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm}, {"softmaxScaledMasked", SoftmaxScaledMasked},
       {"reduce", Reduce}, {"argMax", ArgMax}, {"transpose", Transpose}, {"gather", Gather},
       {"cast", Cast}, {"copyStrided", CopyStrided}, {"fill", Fill}, {"batchNorm", BatchNorm},
       {"dequantize", Dequantize}, {"dequantizeStatic", DequantizeStatic}};

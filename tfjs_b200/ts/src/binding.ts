@@ -49,6 +49,8 @@ export interface CudaBinding {
          b: number, bShape: BigInt64Array, out: number, outShape: BigInt64Array): void;
   unary(ctx: Ctx, op: number, p0: number, p1: number, x: number, n: number, out: number): void;
   softmax(ctx: Ctx, x: number, rows: number, cols: number, out: number): void;
+  softmaxScaledMasked(ctx: Ctx, x: number, rows: number, cols: number, hasScale: number,
+                      scale: number, mask: number, rowsPerMask: number, out: number): void;
   layerNorm(ctx: Ctx, x: number, residual: number, gamma: number, beta: number, rows: number,
             cols: number, epsilon: number, out: number): void;
   reduce(ctx: Ctx, op: number, x: number, outer: number, reduce: number, inner: number,
