@@ -93,6 +93,9 @@ struct tfjs_cuda_ctx {
   std::vector<int> read_free;            // ticket slots free for reuse
   void* l2_scratch = nullptr;
   uint64_t l2_scratch_bytes = 0;
+  // workspace of the GEMM's K-split tail: partial accumulator tiles and their flags
+  void* sk_ws = nullptr;
+  unsigned* sk_flags = nullptr;
   // grow-only scratch for im2col / operand transposes
   void* scratch = nullptr;
   uint64_t scratch_bytes = 0;

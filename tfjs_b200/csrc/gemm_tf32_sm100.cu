@@ -56,6 +56,11 @@ struct Tf32Args {
   const float* residual;  // optional: out = post_act(act(acc + bias) + residual)
   int post_act;
   int out_perm, perm_p, perm_d;  // heads-permuted store through a 4-D C map (GemmProblem)
+  // K-split of the last, partial wave (SK instantiations): the last sk_tiles tiles are cut
+  // along K into one contiguous share per CTA; partial accumulators travel through sk_ws
+  int sk_tiles;
+  float* sk_ws;         // [CTA][epilogue warp][chunk][32 columns][32 rows] fp32
+  unsigned* sk_flags;   // [CTA][epilogue warp]: 1 while that warp's partial waits to be read
   int patch_cap;          // staged-row gather: bytes per patch buffer, 0 = off
   int patch_pitch;        // floats between patch rows (left margin + image row + right margin)
   int patch_ml;           // floats of left margin
@@ -214,6 +219,56 @@ constexpr int kTapTableEntries = 512;  // scalar-gather K limit (after padding t
 constexpr int kMaxSmemBytes = 232448;  // 227 KB per CTA
 constexpr int kBarrierBytes = 640;  // pipeline barriers, TMEM slot, residual barriers
 
+// The work items of a CTA, in the order every warp role walks them.  Plain: the tiles
+// blockIdx.x, + gridDim.x, ... each over all K steps.  With a K-split tail: the tiles of
+// the full waves first, then this CTA's contiguous share [u, u1) of the K steps of the
+// last sk_tiles tiles (units = sk_tiles * k_steps, split evenly over the CTAs), which
+// touches one to a few tiles: possibly the tail of a tile another CTA started, whole
+// tiles, and the head of a tile that later CTAs finish.
+struct WorkIter {
+  int idx, n_dp, stride, first, k_steps, sk_base;
+  long long u, u1;
+  __device__ __forceinline__ void init(const Tf32Args& g, bool sk) {
+    idx = 0;
+    stride = (int)gridDim.x;
+    first = (int)blockIdx.x;
+    k_steps = g.k_steps;
+    u = u1 = 0;
+    sk_base = 0;
+    if (!sk || g.sk_tiles == 0) {
+      const int t = g.total_tiles - first;
+      n_dp = t > 0 ? (t + stride - 1) / stride : 0;
+    } else {
+      sk_base = g.total_tiles - g.sk_tiles;  // a multiple of the grid
+      n_dp = sk_base / stride;
+      const long long T = (long long)g.sk_tiles * k_steps;
+      u = T * first / stride;
+      u1 = T * (first + 1) / stride;
+    }
+  }
+  // false when the CTA has no more work; `it` of the item is idx - 1 afterwards
+  __device__ __forceinline__ bool next(int& tile, int& ks0, int& ks1) {
+    if (idx < n_dp) {
+      tile = first + idx * stride;
+      ks0 = 0;
+      ks1 = k_steps;
+      ++idx;
+      return true;
+    }
+    if (u < u1) {
+      const int sk = (int)(u / k_steps);
+      ks0 = (int)(u - (long long)sk * k_steps);
+      const long long left = u1 - u;
+      ks1 = left < (long long)(k_steps - ks0) ? ks0 + (int)left : k_steps;
+      tile = sk_base + sk;
+      u += ks1 - ks0;
+      ++idx;
+      return true;
+    }
+    return false;
+  }
+};
+
 // RES: the epilogue adds a residual tile that the TMA unit prefetches into the
 // staging tile of the next chunk (two staging tiles per warp, and at BN = 256 one
 // pipeline stage fewer to make room for them).
@@ -250,7 +305,7 @@ struct Cfg {
       (A_MODE == 3 ? kTapTableEntries * 4 + 4 * 512 : 0);  // tap table + 4 row tables
 };
 
-template <int BN, int B_MN, int A_MODE, int RES, int EW = 8>
+template <int BN, int B_MN, int A_MODE, int RES, int EW = 8, int SK = 0>
 __global__ void __launch_bounds__((Cfg<BN, A_MODE, RES, EW>::THREADS), 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_b,
@@ -267,6 +322,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   constexpr int LOAD = SWAP ? (A_MODE == 4 ? 0 : 2) : A_MODE;
   constexpr int kTileRows = SWAP ? 256 : BM;    // output pixels (GEMM rows) per tile
   static_assert(!SWAP || (BN == 256 && !RES && !B_MN), "swapped operands: 256-pixel tiles only");
+  static_assert(!SK || (BN == 256 && !RES && !SWAP && EW == 8 && (A_MODE == 0 || A_MODE == 2)),
+                "K-split tail: plain 128 x 256 tiles only");
   constexpr int kGatherWarp0 = 2 + EW;          // first gather warp (A_MODE 1 and 3)
   constexpr int kGatherThread0 = 64 + EW * 32;  // its first thread
   extern __shared__ uint8_t smem_raw[];
@@ -354,7 +411,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x) {
+      WorkIter wi;
+      wi.init(g, SK != 0);
+      int tile, ks0, ks1;
+      while (alive && wi.next(tile, ks0, ks1)) {
         const int nt = tile % g.tiles_n;
         const int rest = tile / g.tiles_n;
         const int mt = rest % g.tiles_m;
@@ -368,7 +428,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           pix_h = (t % g.conv.out_h) * g.conv.s_h - g.conv.pad_t;
           pix_n = t / g.conv.out_h;
         }
-        for (int ks = 0; ks < k_steps; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
             atomicExch(g.flag, 1);
             alive = false;
@@ -428,9 +488,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
                              ((uint32_t)(BM >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
-      int it = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < g.total_tiles && alive; tile += gridDim.x, ++it) {
+      WorkIter wi;
+      wi.init(g, SK != 0);
+      int tile, ks0, ks1;
+      while (alive && wi.next(tile, ks0, ks1)) {
+        const int it = wi.idx - 1;
         const int acc = it % ACC;
         const uint32_t aphase = (it / ACC) & 1;
         if (!mbar_wait(tempty_bar(acc), aphase ^ 1)) {
@@ -439,7 +502,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int ks = 0; ks < k_steps; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(full_bar(stage), phase)) {
             atomicExch(g.flag, 3);
             alive = false;
@@ -453,7 +516,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
             const uint64_t ad = desc_k_major(sa + k * UMMA_K * 4);
             const uint64_t bd = B_MN ? desc_mn_major(sb + k * 1024)
                                      : desc_k_major(sb + k * UMMA_K * 4);
-            tc_mma_tf32(d_tmem, ad, bd, idesc, (ks | k) != 0 ? 1u : 0u);
+            tc_mma_tf32(d_tmem, ad, bd, idesc, ((ks - ks0) | k) != 0 ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -568,8 +631,26 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       return false;
     };
     if (RES) res_issued = prefetch_residual(0);
-    int it = 0;
-    for (int tile = blockIdx.x; tile < g.total_tiles; tile += gridDim.x, ++it) {
+    WorkIter wi;
+    wi.init(g, SK != 0);
+    int tile, ks0, ks1;
+    while (wi.next(tile, ks0, ks1)) {
+      const int it = wi.idx - 1;
+      // K-split tail: `sk_tail` items hold the later K steps of a tile another CTA
+      // started: the raw accumulator goes to the workspace.  `sk_head` items hold the
+      // first K steps of a tile that the following CTAs finish: their partial sums are
+      // added, in CTA order, before bias and activation.
+      const bool sk_tail = SK && ks0 > 0;
+      const bool sk_head = SK && ks0 == 0 && ks1 < g.k_steps;
+      constexpr int kSkChunks = C::EPI_C / C::EPI_P;  // chunks a warp handles per tile
+      int peer0 = 0, peer1 = 0;                        // CTAs [peer0, peer1) finish this tile
+      if (sk_head) {
+        const long long T = (long long)g.sk_tiles * g.k_steps;
+        const long long tile_end = (long long)(tile - wi.sk_base + 1) * g.k_steps;
+        peer0 = (int)blockIdx.x + 1;
+        peer1 = peer0;
+        while (peer1 < (int)gridDim.x && T * peer1 / (long long)gridDim.x < tile_end) ++peer1;
+      }
       const int nt = tile % g.tiles_n;
       const int rest = tile / g.tiles_n;
       const int mt = rest % g.tiles_m;
@@ -587,6 +668,26 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         break;
       }
       tc_fence_after();
+      if (SK && sk_head) {
+        // the part of each peer's partial tile that the same warp of that CTA wrote is
+        // complete once its flag is up (bounded wait; code 7 on giving up)
+        if (lane == 0) {
+          for (int p = peer0; p < peer1; ++p) {
+            const unsigned* f = g.sk_flags + p * EW + (warp - 2);
+            const long long t0 = clock64();
+            unsigned seen, n = 0;
+            for (;;) {
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+              if (seen != 0) break;
+              if ((++n & 0xff) == 0 && clock64() - t0 > kWaitCycles) {
+                atomicExch(g.flag, 7);
+                break;
+              }
+            }
+          }
+        }
+        __syncwarp();
+      }
       const int m_base = mt * BM + q * 32;
       const int rows_valid = g.M - m_base < 32 ? g.M - m_base : 32;
       float* cbase = g.c + ((long long)bz * g.M + m_base) * g.N;
@@ -605,6 +706,22 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           __syncwarp();
           if (lane == 0) mbar_arrive(tempty_bar(acc));
           released = true;
+        }
+        if (SK && (sk_tail || sk_head)) {
+          const int ci = (c0 - my_c0) / C::EPI_STEP;
+          if (sk_tail) {
+            float* dst = g.sk_ws +
+                         (((size_t)blockIdx.x * EW + (warp - 2)) * kSkChunks + ci) * 1024 + lane;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) __stcg(dst + j * 32, v[j]);
+            continue;
+          }
+          for (int p = peer0; p < peer1; ++p) {
+            const float* src =
+                g.sk_ws + (((size_t)p * EW + (warp - 2)) * kSkChunks + ci) * 1024 + lane;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __ldcg(src + j * 32));
+          }
         }
         chunk_math_dispatch(v, g, n0, bj);
         if (c0 + C::EPI_STEP < BN) bj = chunk_bias(g, n0 + C::EPI_STEP, lane);  // next chunk's
@@ -765,6 +882,22 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(acc));
+      }
+      if (SK && sk_tail) {
+        // publish this warp's part of the partial tile
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          unsigned* f = g.sk_flags + (size_t)blockIdx.x * EW + (warp - 2);
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(f), "r"(1u) : "memory");
+        }
+      }
+      if (SK && sk_head) {
+        // every chunk of the peers' partials has been read: lower their flags for the
+        // next launch
+        __syncwarp();
+        if (lane == 0)
+          for (int p = peer0; p < peer1; ++p) g.sk_flags[p * EW + (warp - 2)] = 0u;
       }
     }
     if (g.c_tma && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -1206,11 +1339,11 @@ bool make_im2col_map(CUtensorMap* tm, const float* x, const ConvGeo& cv, int pix
   return r == CUDA_SUCCESS;
 }
 
-template <int BN, int B_MN, int A_MODE, int RES = 0, int EW = 8>
+template <int BN, int B_MN, int A_MODE, int RES = 0, int EW = 8, int SK = 0>
 int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                const CUtensorMap& tm_c, const CUtensorMap& tm_r, Tf32Args& g) {
   using C = Cfg<BN, A_MODE, RES, EW>;
-  auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE, RES, EW>;
+  auto kern = gemm_tf32_kernel<BN, B_MN, A_MODE, RES, EW, SK>;
   static bool configured[64] = {false};  // per device ordinal
   // the scalar-gather mode adds its two input patches to the fixed layout
   int smem = C::SMEM_BYTES;
@@ -1224,7 +1357,14 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
   }
   g.tiles_n = (g.N + BN - 1) / BN;
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
-  const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
+  int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
+  if (SK) {
+    // the caller has checked that the split pays and that the workspace exists
+    grid = ctx->sm_count;
+    g.sk_tiles = g.total_tiles % grid;
+    g.sk_ws = (float*)ctx->sk_ws;
+    g.sk_flags = ctx->sk_flags;
+  }
   kern<<<grid, C::THREADS, smem, ctx->stream>>>(tm_a, tm_b, tm_c, tm_r, g);
   LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
   return TFJS_CUDA_OK;
@@ -1266,6 +1406,43 @@ int pick_bn(int M, int N, int batch, int sm_count, int k_steps = 0) {
   }
   while (bn > 64 && tiles_m * ((N + bn - 1) / bn) * batch < sm_count) bn >>= 1;
   return bn;
+}
+
+// K-split of the last wave: worth it when the partial wave leaves most SMs idle for a long
+// main loop.  Costs in K steps: plain = waves x k_steps; split = full waves x k_steps + the
+// even share of the rest + the exchange of partial tiles through L2 (`overhead`, measured).
+// Also makes sure the workspace exists (never allocated while a step is being captured).
+bool use_k_split(tfjs_cuda_ctx* ctx, int total_tiles, int k_steps) {
+  // Measured: the exchange costs about as much as 20 K steps (peers store 128 KB each after
+  // their last MMA, the owner then reads up to four of them before its ordinary epilogue), so
+  // only long main loops gain: [8192, 3072] x [3072, 768] 82 -> 74 us, 3x3 256ch @14x14 b128
+  // 66 -> 61 us, 3x3 512ch @7x7 63 -> 57 us; with K = 768 the split loses and stays off.
+  static int overhead = -2;  // K steps; negative switches the split off
+  if (overhead == -2)
+    overhead = getenv("TFJS_CUDA_KSPLIT_OVERHEAD") ? atoi(getenv("TFJS_CUDA_KSPLIT_OVERHEAD")) : 24;
+  const int grid = ctx->sm_count;
+  const int rest = total_tiles % grid;
+  if (overhead < 0 || rest == 0 || grid > 512) return false;
+  const long long full = total_tiles / grid;
+  const long long share = ((long long)rest * k_steps + grid - 1) / grid;
+  if (share < 4) return false;
+  const long long plain = (full + 1) * k_steps;
+  const long long split = full * k_steps + share + overhead;
+  if (split * 10 > plain * 9) return false;
+  if (!ctx->sk_ws) {
+    if (ctx->capturing) return false;
+    const size_t ws = (size_t)grid * 8 * 4 * 4096;  // CTA x warp x chunk x 32 x 32 floats
+    if (cudaMalloc(&ctx->sk_ws, ws) != cudaSuccess) { ctx->sk_ws = nullptr; cudaGetLastError(); return false; }
+    if (cudaMalloc((void**)&ctx->sk_flags, 4096 * sizeof(unsigned)) != cudaSuccess) {
+      cudaFree(ctx->sk_ws);
+      ctx->sk_ws = nullptr;
+      ctx->sk_flags = nullptr;
+      cudaGetLastError();
+      return false;
+    }
+    cudaMemsetAsync(ctx->sk_flags, 0, 4096 * sizeof(unsigned), ctx->stream);
+  }
+  return true;
 }
 
 constexpr int smem_base_mode3(int bn) {
@@ -1347,6 +1524,9 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     g.patch_bufs = plan.bufs;
   }
   bool res_tma = false;
+  g.sk_tiles = 0;
+  g.sk_ws = nullptr;
+  g.sk_flags = nullptr;
   g.out_perm = pr.out_perm;
   g.perm_p = pr.perm_p;
   g.perm_d = pr.perm_d;
@@ -1481,6 +1661,8 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
         return launch_bn<0, 2, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
       }
       if (wide) return launch_bn<0, 2, 0, 16>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
+      if (bn == 256 && use_k_split(ctx, g.tiles_m * ((pr.N + 255) / 256) * pr.batch, op.k_steps))
+        return launch_cfg<256, 0, 2, 0, 8, 1>(ctx, tm_a, tm_b, tm_c, tm_r, g);
       return launch_bn<0, 2>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }
     if (op.a_gather) {
@@ -1494,6 +1676,8 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
       return launch_bn<0, 0, 1>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
     }
     if (wide) return launch_bn<0, 0, 0, 16>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
+    if (bn == 256 && use_k_split(ctx, g.tiles_m * ((pr.N + 255) / 256) * pr.batch, op.k_steps))
+      return launch_cfg<256, 0, 0, 0, 8, 1>(ctx, tm_a, tm_b, tm_c, tm_r, g);
     return launch_bn<0, 0>(ctx, bn, tm_a, tm_b, tm_c, tm_r, g);
   }
   if ((rc = make_map(ctx, &tm_b, op.b, (uint64_t)pr.N, (uint64_t)pr.K,

@@ -232,6 +232,8 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
   if (ctx->scratch) cudaFreeAsync(ctx->scratch, ctx->stream);
   if (ctx->l2_scratch) cudaFreeAsync(ctx->l2_scratch, ctx->stream);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  if (ctx->sk_ws) cudaFree(ctx->sk_ws);
+  if (ctx->sk_flags) cudaFree(ctx->sk_flags);
   if (ctx->d_flag) cudaFree(ctx->d_flag);
   if (ctx->h_flag) cudaFreeHost(ctx->h_flag);
   if (ctx->d_bad_index) cudaFree(ctx->d_bad_index);
@@ -447,6 +449,8 @@ static int report_flag(tfjs_cuda_ctx* ctx) {
     int v = *ctx->h_flag;
     *ctx->h_flag = 0;
     cudaMemsetAsync(ctx->d_flag, 0, sizeof(int), ctx->stream);
+    // a K-split GEMM that gave up may have left partial-tile flags raised
+    if (ctx->sk_flags) cudaMemsetAsync(ctx->sk_flags, 0, 4096 * sizeof(unsigned), ctx->stream);
     return ctx_fail(ctx, TFJS_CUDA_DEVICE_TIMEOUT,
                     "a device-side wait gave up (code %d); results of the "
                     "affected kernel are invalid", v);

@@ -4,6 +4,7 @@ op front end with CUDA events on the backend's stream.
     python -m tfjs_b200.kernel_bench <case> [iterations]
 
 cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072),
+mm_<m>_<k>_<n> (fused matMul + bias),
 pw_<hw>_<cin>_<cout>_<batch> (1x1 conv), c3_<hw>_<cin>_<cout>_<batch>_<stride> (3x3
 conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<batch>_<stride>
 (3x3 depthwise), res_<hw>_<cin>_<cout>_<batch> (1x1 conv + bias, Add of a shortcut, Relu:
@@ -35,6 +36,11 @@ elif case=='ffn':
     a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
     bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
     f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'linear'); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
+elif case.startswith('mm_'):   # mm_<m>_<k>_<n>: fused matMul + bias
+    _,m,k,n=case.split('_'); m,k,n=int(m),int(k),int(n)
+    a=ops.tensor(r.standard_normal((m,k)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((k,n)).astype(np.float32)/32)
+    bias=ops.tensor(r.standard_normal(n).astype(np.float32))
+    f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'linear'); fl=2*m*n*k; by=4*(m*k+k*n+m*n)
 elif case.startswith('gelu'):   # gelu_<rows>_<cols>
     _,rows,cols=case.split('_'); rows,cols=int(rows),int(cols)
     x=ops.tensor(r.standard_normal((rows,cols)).astype(np.float32))
