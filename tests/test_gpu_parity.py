@@ -69,6 +69,8 @@ CONV_CASES = {
     "prelu_scalar_nobias": lambda: conv_case(14, (1, 8, 8, 32), (3, 3, 32, 32), bias=False, act="prelu", prelu="scalar"),
     "wide_cout256": lambda: conv_case(15, (2, 14, 14, 256), (3, 3, 256, 256)),
     "cin5_simt_route": lambda: conv_case(16, (1, 9, 9, 5), (2, 2, 5, 7), pad="valid"),
+    # 14 tiles of 144 K steps (ResNet conv5 at a small batch): K-split over all SMs
+    "k_split_conv5": lambda: conv_case(21, (16, 7, 7, 512), (3, 3, 512, 512)),
     # long K, <= 128 output channels: the form with the pixels on the MMA's N axis
     "narrow_1x1_k416_cout100": lambda: conv_case(17, (3, 10, 11, 416), (1, 1, 416, 100), act="linear"),
     "narrow_3x3_cout96_ragged": lambda: conv_case(18, (3, 21, 23, 64), (3, 3, 64, 96), act="relu6"),
@@ -131,6 +133,11 @@ MM_CASES = {
     "k_not_mult4": lambda: mm_case(10, (37, 13), (13, 29), bias=True, act="elu"),
     "k1000_n10": lambda: mm_case(11, (130, 1000), (1000, 10), bias=True, act="sigmoid"),
     "tall_m": lambda: mm_case(12, (3000, 64), (64, 96), act="relu"),
+    # 10 tiles with 128 K steps each: the K steps are shared out over all SMs and every
+    # tile is summed from the partial tiles of about 15 CTAs
+    "k_split_long_k": lambda: mm_case(13, (640, 4096), (4096, 512), bias=True, act="relu"),
+    # one full wave of tiles and a remainder of 30 whose K steps are split (178 tiles)
+    "k_split_tail_wave": lambda: mm_case(14, (11392, 1536), (1536, 512), bias=True),
 }
 
 
@@ -175,6 +182,13 @@ def test_fused_matmul_cfg2a_rows(cuda_engine):
     # weights were packed once; a second call reuses the packed copy
     got2 = opcases.run_cuda(case)
     assert np.array_equal(got, got2)
+
+
+def test_k_split_matmul_is_deterministic(cuda_engine):
+    """Partial tiles are added in CTA order, so two launches give the same bits."""
+    case = MM_CASES["k_split_long_k"]()
+    a, b = opcases.run_cuda(case), opcases.run_cuda(case)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
 
 
 def test_matmul_nan_propagates(cuda_engine):
