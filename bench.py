@@ -153,7 +153,7 @@ def kernel_work(rec):
     elif name in ("FusedDepthwiseConv2D", "DepthwiseConv2dNative"):
         f = ins["filter"]
         flops = 2 * _prod(outs[0]) * f[0] * f[1]
-    elif name in ("_FusedMatMul", "BatchMatMul"):
+    elif name in ("_FusedMatMul", "BatchMatMul", "_MatMulHeads"):
         a = ins["a"]
         k = a[-2] if rec["attrs"].get("transposeA") else a[-1]
         flops = 2 * _prod(outs[0]) * k

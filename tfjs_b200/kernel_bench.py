@@ -10,7 +10,8 @@ conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<bat
 (3x3 depthwise), res_<hw>_<cin>_<cout>_<batch> (1x1 conv + bias, Add of a shortcut, Relu:
 one launch through the deferred-launch path), gelu_<rows>_<cols> (x * 0.5 * (1 + erf(x /
 sqrt 2)): five elementwise kernels, one catalogued chain launch), ln_<rows>_<cols> (LayerNorm
-tail ((x - mean) * rstd) * gamma + beta: four kernels, one chain launch).  Prints ms, TFLOP/s
+tail ((x - mean) * rstd) * gamma + beta: four kernels, one chain launch), lnf_<rows>_<cols>
+(residual Add + the whole layer normalisation: ten kernels of the reference, one launch).  Prints ms, TFLOP/s
 and algorithmic GB/s (each tensor moved once).
 """
 import sys
@@ -51,6 +52,11 @@ elif case.startswith('gelu'):   # gelu_<rows>_<cols>
         for t in (a,b,i,d): t.dispose()
         return y
     fl=0; by=8*rows*cols
+elif case.startswith('lnf'):   # lnf_<rows>_<cols>: residual Add + layer normalisation, one kernel
+    _,rows,cols=case.split('_'); rows,cols=int(rows),int(cols)
+    x=ops.tensor(r.standard_normal((rows,cols)).astype(np.float32)); res=ops.tensor(r.standard_normal((rows,cols)).astype(np.float32))
+    gamma=ops.tensor(r.standard_normal(cols).astype(np.float32)); beta=ops.tensor(r.standard_normal(cols).astype(np.float32))
+    f=lambda: ops.fused_layer_norm(x,gamma,beta,1e-12,residual=res); fl=0; by=12*rows*cols
 elif case.startswith('ln'):   # ln_<rows>_<cols>
     _,rows,cols=case.split('_'); rows,cols=int(rows),int(cols)
     x=ops.tensor(r.standard_normal((rows,cols)).astype(np.float32)); mean=ops.tensor(r.standard_normal((rows,1)).astype(np.float32))
