@@ -56,36 +56,62 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
   const int lane = threadIdx.x & 31;
   const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
-  for (uint64_t r = warp; r < rows; r += nwarps) {
-    const float* xr = x + r * cols;
-    float* yr = y + r * cols;
-    const float* mrow = pg.mask ? pg.mask + (r / pg.rows_per_mask) * cols : nullptr;
-    float m = softmax_logit(pg, mrow, xr[0], 0);
-    if (REGS > 0) {
-      float v[REGS > 0 ? REGS : 1];
+  if (REGS > 0) {
+    // The row a warp handles next is fetched while it works on the current one: a row is a
+    // chain of load -> max -> exp -> sum -> divide -> store, and without the prefetch the
+    // warps sit in the load at the head of every row.
+    constexpr int R = REGS > 0 ? REGS : 1;
+    float nx[R], nm[R];
+    auto fetch = [&](uint64_t row) {
+      const float* xr = x + row * cols;
+      const float* mr = pg.mask ? pg.mask + (row / pg.rows_per_mask) * cols : nullptr;
 #pragma unroll
-      for (int j = 0; j < REGS; ++j) {
+      for (int j = 0; j < R; ++j) {
         const uint32_t c = lane + 32 * j;
-        v[j] = c < cols ? softmax_logit(pg, mrow, xr[c], c) : -INFINITY;
-        if (c < cols) m = nan_max(m, v[j]);
+        nx[j] = c < cols ? xr[c] : 0.0f;
+        nm[j] = (mr != nullptr && c < cols) ? __ldg(mr + c) : 0.0f;
       }
+    };
+    if (warp < rows) fetch(warp);
+    for (uint64_t r = warp; r < rows; r += nwarps) {
+      float* yr = y + r * cols;
+      float v[R];
+#pragma unroll
+      for (int j = 0; j < R; ++j) {
+        float t = nx[j];
+        if (pg.has_scale) t = __fmul_rn(t, pg.scale);
+        if (pg.mask) t = __fadd_rn(t, nm[j]);
+        v[j] = lane + 32 * j < cols ? t : -INFINITY;
+      }
+      if (r + nwarps < rows) fetch(r + nwarps);
+      float m = __shfl_sync(0xffffffffu, v[0], 0);  // column 0 exists in every row
+#pragma unroll
+      for (int j = 0; j < R; ++j)
+        if (lane + 32 * j < cols) m = nan_max(m, v[j]);
       m = warp_nan_max(m);
       double s = 0.0;
 #pragma unroll
-      for (int j = 0; j < REGS; ++j) {
-        const uint32_t c = lane + 32 * j;
-        if (c < cols) {
+      for (int j = 0; j < R; ++j) {
+        if (lane + 32 * j < cols) {
           v[j] = (float)exp_fast((double)__fsub_rn(v[j], m));
           s += (double)v[j];
         }
       }
       const float sf = (float)warp_sum(s);
 #pragma unroll
-      for (int j = 0; j < REGS; ++j) {
+      for (int j = 0; j < R; ++j) {
         const uint32_t c = lane + 32 * j;
         if (c < cols) yr[c] = __fdiv_rn(v[j], sf);
       }
-    } else {
+    }
+    return;
+  }
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    const float* xr = x + r * cols;
+    float* yr = y + r * cols;
+    const float* mrow = pg.mask ? pg.mask + (r / pg.rows_per_mask) * cols : nullptr;
+    float m = softmax_logit(pg, mrow, xr[0], 0);
+    {
       for (uint32_t c = lane; c < cols; c += 32) m = nan_max(m, softmax_logit(pg, mrow, xr[c], c));
       m = warp_nan_max(m);
       double s = 0.0;
