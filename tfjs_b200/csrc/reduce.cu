@@ -64,7 +64,11 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
     float nx[R], nm[R];
     auto fetch = [&](uint64_t row) {
       const float* xr = x + row * cols;
-      const float* mr = pg.mask ? pg.mask + (row / pg.rows_per_mask) * cols : nullptr;
+      // (a 64-bit division costs more than the rest of the row's bookkeeping)
+      const uint64_t mrow_idx = (row | pg.rows_per_mask) >> 32
+                                    ? row / pg.rows_per_mask
+                                    : (uint64_t)((uint32_t)row / (uint32_t)pg.rows_per_mask);
+      const float* mr = pg.mask ? pg.mask + mrow_idx * cols : nullptr;
 #pragma unroll
       for (int j = 0; j < R; ++j) {
         const uint32_t c = lane + 32 * j;

@@ -11,7 +11,8 @@ conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<bat
 one launch through the deferred-launch path), gelu_<rows>_<cols> (x * 0.5 * (1 + erf(x /
 sqrt 2)): five elementwise kernels, one catalogued chain launch), ln_<rows>_<cols> (LayerNorm
 tail ((x - mean) * rstd) * gamma + beta: four kernels, one chain launch), lnf_<rows>_<cols>
-(residual Add + the whole layer normalisation: ten kernels of the reference, one launch).  Prints ms, TFLOP/s
+(residual Add + the whole layer normalisation: ten kernels of the reference, one launch),
+sm_<rows>_<cols> (softmax of scaled, masked attention scores, rows a multiple of 1536).  Prints ms, TFLOP/s
 and algorithmic GB/s (each tensor moved once).
 """
 import sys
@@ -52,6 +53,10 @@ elif case.startswith('gelu'):   # gelu_<rows>_<cols>
         for t in (a,b,i,d): t.dispose()
         return y
     fl=0; by=8*rows*cols
+elif case.startswith('sm_'):   # sm_<rows>_<cols>: softmax(x * 0.125 + mask) with a [rows/1536, 1, 1, cols] mask
+    _,rows,cols=case.split('_'); rows,cols=int(rows),int(cols)
+    x=ops.tensor(r.standard_normal((rows//1536,12,128,cols)).astype(np.float32)); mask=ops.tensor(np.zeros((rows//1536,1,1,cols),np.float32))
+    f=lambda: ops.softmax_scaled_masked(x,0.125,mask); fl=0; by=8*rows*cols
 elif case.startswith('lnf'):   # lnf_<rows>_<cols>: residual Add + layer normalisation, one kernel
     _,rows,cols=case.split('_'); rows,cols=int(rows),int(cols)
     x=ops.tensor(r.standard_normal((rows,cols)).astype(np.float32)); res=ops.tensor(r.standard_normal((rows,cols)).astype(np.float32))
