@@ -51,7 +51,13 @@ enum tfjs_cuda_activation {
   TFJS_CUDA_ACT_PRELU = 3,
   TFJS_CUDA_ACT_LEAKYRELU = 4,
   TFJS_CUDA_ACT_SIGMOID = 5,
-  TFJS_CUDA_ACT_ELU = 6
+  TFJS_CUDA_ACT_ELU = 6,
+  /* tfjs_cuda_fused_matmul only: the erf form of GELU as a converted graph spells it,
+   * out = (h * gelu_half) * (erf(h * gelu_scale) + gelu_one)  (or erf(h / gelu_scale)
+   * when gelu_divide), each product and sum rounded to fp32 as the separate Multiply.ts /
+   * RealDiv.ts / Erf.ts / Add.ts kernels round them.  The graph executor substitutes it for
+   * the five nodes after a dense layer. */
+  TFJS_CUDA_ACT_GELU_ERF = 7
 };
 
 /* tfjs-backend-wasm/src/cc/backend.h:33-40 (DType); bool is one byte. */
@@ -210,6 +216,9 @@ typedef struct tfjs_cuda_matmul_params {
   int32_t activation;
   int32_t bias_len, prelu_len;
   double leakyrelu_alpha;
+  /* constants of TFJS_CUDA_ACT_GELU_ERF (ignored otherwise) */
+  float gelu_scale, gelu_half, gelu_one;
+  int32_t gelu_divide;
 } tfjs_cuda_matmul_params;
 
 int tfjs_cuda_fused_matmul(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,

@@ -274,6 +274,7 @@ def test_bert_with_folded_head_transposes_matches_the_stored_graph(cuda_engine):
         outs.append(y.arraySync())
         assert gm.executor.fused_heads == (8 if fuse else 0)
         assert gm.executor.fused_softmaxes == (2 if fuse else 0)
+        assert gm.executor.fused_gelus == 0   # opt-in (slower than the chain kernel)
         y.dispose()
         assert be.numDataIds() == before
         for t in ins.values():
@@ -307,5 +308,39 @@ def test_scaled_masked_softmax_has_the_bits_of_the_separate_kernels(cuda_engine,
     ref_t = ops.softmax(s2)
     got, ref = got_t.arraySync(), ref_t.arraySync()
     for t in [x, got_t, c, s1, s2, ref_t] + ([mask] if ms else []):
+        t.dispose()
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+
+
+# ------------------------------------------------------ plan rewrite: erf GELU --
+@pytest.mark.parametrize("mode", ["tf32", "fp32"])
+@pytest.mark.parametrize("divide", [False, True])
+def test_gelu_epilogue_has_the_bits_of_the_five_kernels(cuda_engine, mode, divide):
+    from tfjs_b200 import graph_model, ops
+    import base64
+    r = np.random.default_rng(11)
+    a = ops.tensor(r.standard_normal((300, 96)).astype(np.float32))
+    w = ops.tensor((r.standard_normal((96, 200)) / 4).astype(np.float32))
+    bias = ops.tensor(r.standard_normal(200).astype(np.float32))
+    c = float(np.float32(np.sqrt(2.0))) if divide else float(np.float32(1 / np.sqrt(2.0)))
+    attrs = {"transpose_a": {"b": False}, "transpose_b": {"b": False}, "num_args": {"i": "1"},
+             "fused_ops": {"list": {"s": [base64.b64encode(b"BiasAdd").decode()]}},
+             "_gelu": {"list": {"f": [c, 0.5, 1.0, 1.0 if divide else 0.0]}}}
+    node = graph_model.Node({"name": "h", "op": "_FusedMatMulGelu", "input": ["a", "w", "b"],
+                             "attr": attrs})
+    cuda_engine.backend.set_math_mode(mode)
+    try:
+        got_t = graph_model.execute_op(node, [a, w, bias])
+        h = ops.fused_mat_mul(a, w, False, False, bias, "linear")
+        ct, half, one = ops.tensor(np.float32(c)), ops.tensor(np.float32(0.5)), ops.tensor(np.float32(1))
+        s = ops.div(h, ct) if divide else ops.mul(h, ct)
+        e = ops.erf(s)
+        e1 = ops.add(e, one)
+        m = ops.mul(h, half)
+        ref_t = ops.mul(m, e1)
+        got, ref = got_t.arraySync(), ref_t.arraySync()
+    finally:
+        cuda_engine.backend.set_math_mode("tf32")
+    for t in (a, w, bias, got_t, h, ct, half, one, s, e, e1, m, ref_t):
         t.dispose()
     assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))

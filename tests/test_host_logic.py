@@ -244,3 +244,24 @@ def test_softmax_mask_rows():
     assert f([64, 12, 128, 128], [64, 1, 128, 128]) is None
     assert f([64, 12, 128, 128], [64, 1, 1, 1]) is None
     assert f([5, 7], [7]) == 5 and f([7], [7]) == 1
+
+
+# ------------------------------------------------------ plan rewrite: erf GELU --
+def test_erf_gelu_after_a_dense_layer_becomes_its_epilogue():
+    G, nodes, consts = _bert_plan()
+    new, n = G.fuse_gelu_into_matmul(nodes, lambda x: x in consts, lambda x: consts[x].reshape(-1))
+    assert n == 12 and len(new) == len(nodes) - 5 * n
+    assert not any(x.op == "Erf" for x in new)
+    for x in new:
+        if x.op == "_FusedMatMulGelu":
+            p = G.attr_number_list(x.attrs, "_gelu")
+            assert len(x.inputs) == 3
+            assert p == [float(np.float32(1 / np.sqrt(2.0))), 0.5, 1.0, 0.0]
+    # the dense output read by something else keeps the five nodes
+    erf = next(x for x in nodes if x.op == "Erf")
+    mul = next(x for x in nodes if x.name == G.parse_node_name(erf.inputs[0])[0])
+    h = next(i for i in mul.inputs if G.parse_node_name(i)[0] not in consts)
+    tap = G.Node({"name": "tap", "op": "Identity", "input": [h]})
+    _, n = G.fuse_gelu_into_matmul(nodes + [tap], lambda x: x in consts,
+                                   lambda x: consts[x].reshape(-1))
+    assert n == 11

@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libtfjs_cuda.so")
 OK = 0
 UNSUPPORTED = 5
 ACTIVATIONS = dict(linear=0, relu=1, relu6=2, prelu=3, leakyrelu=4, sigmoid=5,
-                   elu=6)
+                   elu=6, gelu_erf=7)
 DTYPES = dict(float32=0, int32=1, bool=2)
 BINARY_OPS = dict(Add=0, Sub=1, Multiply=2, RealDiv=3, Maximum=4, Minimum=5,
                   Pow=6, SquaredDifference=7, Prelu=8)
@@ -55,7 +55,9 @@ class EwProgram(Structure):
 class MatMulParams(Structure):
     _fields_ = [(n, c_int32) for n in (
         "batch_a", "batch_b", "m", "n", "k", "transpose_a", "transpose_b",
-        "activation", "bias_len", "prelu_len")] + [("leakyrelu_alpha", c_double)]
+        "activation", "bias_len", "prelu_len")] + [
+            ("leakyrelu_alpha", c_double), ("gelu_scale", c_float), ("gelu_half", c_float),
+            ("gelu_one", c_float), ("gelu_divide", c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/tfjs_cuda.h declares.

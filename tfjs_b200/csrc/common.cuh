@@ -156,6 +156,8 @@ struct ActParams {
   int prelu_len;        // 0, 1, or channel count
   const float* prelu;   // device pointer or null
   double alpha;         // leakyrelu
+  float gelu_scale, gelu_half, gelu_one;  // TFJS_CUDA_ACT_GELU_ERF
+  int gelu_divide;
 };
 
 // exp(x) in double for results that are rounded to fp32 afterwards.  The library's exp
@@ -262,6 +264,13 @@ __device__ __forceinline__ float js_leakyrelu(float v, double alpha) {
   return v < 0.0f ? (float)(alpha * (double)v) : v;
 }
 
+// (h * half) * (erf(h * scale) + one) with every step rounded to fp32: the five
+// elementwise kernels a converted graph runs after a dense layer for the erf GELU.
+__device__ __forceinline__ float js_gelu_erf(float h, const ActParams& ap) {
+  const float a = ap.gelu_divide ? __fdiv_rn(h, ap.gelu_scale) : __fmul_rn(h, ap.gelu_scale);
+  return __fmul_rn(__fmul_rn(h, ap.gelu_half), __fadd_rn(js_erf(a), ap.gelu_one));
+}
+
 __device__ __forceinline__ float apply_act(float v, const ActParams& ap,
                                            int channel) {
   switch (ap.act) {
@@ -274,6 +283,7 @@ __device__ __forceinline__ float apply_act(float v, const ActParams& ap,
     case TFJS_CUDA_ACT_LEAKYRELU: return js_leakyrelu(v, ap.alpha);
     case TFJS_CUDA_ACT_SIGMOID: return js_sigmoid(v);
     case TFJS_CUDA_ACT_ELU: return js_elu(v);
+    case TFJS_CUDA_ACT_GELU_ERF: return js_gelu_erf(v, ap);
     default: return v;
   }
 }

@@ -166,6 +166,24 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, 
     for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __shfl_sync(0xffffffffu, bj, j));
   }
   if (ACT == TFJS_CUDA_ACT_LINEAR) return;
+  if (ACT == TFJS_CUDA_ACT_GELU_ERF) {
+    // four independent erf evaluations at a time: each is a chain of ~40 dependent
+    // double operations, and the two epilogue warps of a scheduler have nothing else
+    // to fill its slots with
+#pragma unroll
+    for (int j0 = 0; j0 < 32; j0 += 4) {
+      float a[4], e[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        a[u] = g.ap.gelu_divide ? __fdiv_rn(v[j0 + u], g.ap.gelu_scale)
+                                : __fmul_rn(v[j0 + u], g.ap.gelu_scale);
+      js_erf_vec<4>(a, e);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        v[j0 + u] = __fmul_rn(__fmul_rn(v[j0 + u], g.ap.gelu_half), __fadd_rn(e[u], g.ap.gelu_one));
+    }
+    return;
+  }
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
     const float t = v[j];
@@ -197,6 +215,7 @@ __device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g,
     case TFJS_CUDA_ACT_LEAKYRELU: chunk_math<TFJS_CUDA_ACT_LEAKYRELU>(v, g, n0, bj, skip_bias); break;
     case TFJS_CUDA_ACT_SIGMOID: chunk_math<TFJS_CUDA_ACT_SIGMOID>(v, g, n0, bj, skip_bias); break;
     case TFJS_CUDA_ACT_ELU: chunk_math<TFJS_CUDA_ACT_ELU>(v, g, n0, bj, skip_bias); break;
+    case TFJS_CUDA_ACT_GELU_ERF: chunk_math<TFJS_CUDA_ACT_GELU_ERF>(v, g, n0, bj, skip_bias); break;
     default: chunk_math<TFJS_CUDA_ACT_LINEAR>(v, g, n0, bj, skip_bias); break;
   }
 }

@@ -113,6 +113,8 @@ int fill_act(tfjs_cuda_ctx* ctx, int activation, int prelu_len, int32_t prelu_id
   if (activation < TFJS_CUDA_ACT_LINEAR || activation > TFJS_CUDA_ACT_ELU)
     return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "%s: unknown activation %d", who, activation);
   ap->act = activation;
+  ap->gelu_scale = ap->gelu_half = ap->gelu_one = 0.0f;
+  ap->gelu_divide = 0;
   ap->prelu_len = 0;
   ap->prelu = nullptr;
   ap->alpha = alpha;
@@ -155,9 +157,17 @@ static int matmul_impl(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p, int
   if (p->bias_len && (rc = ctx_get(ctx, bias_id, (uint64_t)p->bias_len * 4, "fused_matmul bias", &bias))) return rc;
   if ((rc = ctx_get(ctx, out_id, (uint64_t)batch * p->m * p->n * 4, "fused_matmul out", &out))) return rc;
   GemmProblem pr;
-  if ((rc = fill_act(ctx, p->activation, p->prelu_len, prelu_id, p->leakyrelu_alpha, p->n,
-                     "fused_matmul", &pr.ap)))
+  const bool gelu = p->activation == TFJS_CUDA_ACT_GELU_ERF;
+  if ((rc = fill_act(ctx, gelu ? TFJS_CUDA_ACT_LINEAR : p->activation, p->prelu_len, prelu_id,
+                     p->leakyrelu_alpha, p->n, "fused_matmul", &pr.ap)))
     return rc;
+  if (gelu) {
+    pr.ap.act = TFJS_CUDA_ACT_GELU_ERF;
+    pr.ap.gelu_scale = p->gelu_scale;
+    pr.ap.gelu_half = p->gelu_half;
+    pr.ap.gelu_one = p->gelu_one;
+    pr.ap.gelu_divide = p->gelu_divide != 0;
+  }
   if ((uint64_t)batch * p->m * p->n == 0) return TFJS_CUDA_OK;
   cudaSetDevice(ctx->device);
   pr.a = (const float*)a->ptr;

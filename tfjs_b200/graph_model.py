@@ -267,6 +267,8 @@ def execute_op(node, inp):
         return _exec_matmul_heads(node, inp)
     if op == "_SoftmaxScaledMasked":
         return _exec_softmax_fused(node, inp)
+    if op == "_FusedMatMulGelu":
+        return _exec_matmul_gelu(node, inp)
     if op in ("FusedBatchNorm", "FusedBatchNormV2", "FusedBatchNormV3"):
         return ops.batch_norm(inp[0], inp[3], inp[4], inp[2], inp[1],
                               attr_number(node.attrs, "epsilon", 0.001))
@@ -417,6 +419,117 @@ def fuse_layer_norms(ordered, is_const, const_value, const_shape, protected=()):
             attrs["residual"] = {"b": True}
         replaced[out.name] = Node({"name": out.name, "op": "_FusedLayerNorm", "input": ins,
                                    "attr": attrs})
+    if not replaced:
+        return list(ordered), 0
+    return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
+
+
+def _exec_matmul_gelu(node, inp):
+    """_FusedMatMul whose epilogue is the erf GELU the five following nodes spelled out."""
+    bias, prelu, act, alpha = _fused_params(node, inp)
+    p = attr_number_list(node.attrs, "_gelu")
+    ta, tb = attr_bool(node.attrs, "transpose_a"), attr_bool(node.attrs, "transpose_b")
+    from ._cabi import CudaError, UNSUPPORTED
+    if act == "linear" and bias is not None:
+        try:
+            return ops.fused_mat_mul(inp[0], inp[1], ta, tb, bias, "gelu_erf", None, alpha,
+                                     geluParams=p)
+        except CudaError as e:
+            if e.code != UNSUPPORTED:
+                raise
+    h = ops.fused_mat_mul(inp[0], inp[1], ta, tb, bias, act, prelu, alpha)
+    tmp = [h]
+    try:
+        c, half, one = [ops.tensor(np.float32(v)) for v in p[:3]]
+        tmp += [c, half, one]
+        a = ops.div(h, c) if p[3] else ops.mul(h, c)
+        tmp.append(a)
+        e = ops.erf(a)
+        tmp.append(e)
+        s1 = ops.add(e, one)
+        tmp.append(s1)
+        m = ops.mul(h, half)
+        tmp.append(m)
+        return ops.mul(m, s1)
+    finally:
+        for t in tmp:
+            t.dispose()
+
+
+def fuse_gelu_into_matmul(ordered, is_const, const_value, protected=()):
+    """Plan rewrite: h = _FusedMatMul(a, b, bias) (no activation) followed by the erf GELU a
+    converted graph spells as Mul(Mul(h, half), AddV2(Erf(Mul(h, scale)), one)) (or
+    Erf(RealDiv(h, scale))), with scalar constants and h consumed by those two products
+    only, becomes that `_FusedMatMul` with the GELU as its epilogue (node op
+    `_FusedMatMulGelu`, named like the final Mul).  The epilogue performs the same fp32
+    operations on the same h, so the bits do not change."""
+    by_name = {n.name: n for n in ordered}
+    consumers = {}
+    for n in ordered:
+        for i in n.inputs:
+            consumers.setdefault(parse_node_name(i)[0], []).append(n.name)
+    protected = set(protected)
+
+    def node(inp, op):
+        name, idx = parse_node_name(inp)
+        n = by_name.get(name)
+        return n if n is not None and idx == 0 and n.op in op else None
+
+    def scalar_const(inp):
+        name, idx = parse_node_name(inp)
+        if idx != 0 or name not in by_name or by_name[name].op != "Const" or not is_const(name):
+            return None
+        v = const_value(name)
+        return float(np.float32(v[0])) if len(v) == 1 else None
+
+    def with_const(n, commutative=True):
+        """(other input, constant) of a two-input node one of whose inputs is a scalar const."""
+        if n is None or len(n.inputs) != 2:
+            return None
+        pairs = [(n.inputs[0], n.inputs[1])] + ([(n.inputs[1], n.inputs[0])] if commutative else [])
+        for a, b in pairs:
+            c = scalar_const(b)
+            if c is not None and scalar_const(a) is None:
+                return a, c
+        return None
+
+    def users(name):
+        return sorted(consumers.get(name, []))
+
+    removed, replaced = set(), {}
+    for out in ordered:
+        if out.op != "Mul" or len(out.inputs) != 2:
+            continue
+        for mi, ai in ((out.inputs[0], out.inputs[1]), (out.inputs[1], out.inputs[0])):
+            m2, add = node(mi, ("Mul",)), node(ai, ("Add", "AddV2"))
+            hm = with_const(m2)
+            ea = with_const(add)
+            if hm is None or ea is None:
+                continue
+            erf = node(ea[0], ("Erf",))
+            if erf is None:
+                continue
+            inner = node(erf.inputs[0], ("Mul", "RealDiv", "Div"))
+            hs = with_const(inner, commutative=inner is not None and inner.op == "Mul")
+            if hs is None or hs[0] != hm[0]:
+                continue
+            mm = node(hm[0], ("_FusedMatMul",))
+            if mm is None or mm.name in removed:
+                continue
+            fused = attr_string_list(mm.attrs, "fused_ops", [])
+            if [f.lower() for f in fused] != ["biasadd"] or attr_number(mm.attrs, "num_args", 0) != 1:
+                continue
+            gone = [mm, m2, add, erf, inner]
+            if (users(mm.name) != sorted([m2.name, inner.name]) or users(m2.name) != [out.name] or
+                    users(add.name) != [out.name] or users(erf.name) != [add.name] or
+                    users(inner.name) != [erf.name] or any(n.name in protected for n in gone)):
+                continue
+            removed.update(n.name for n in gone)
+            attrs = dict(mm.attrs)
+            attrs["_gelu"] = {"list": {"f": [hs[1], hm[1], ea[1], 1.0 if inner.op != "Mul" else 0.0]}}
+            replaced[out.name] = Node({"name": out.name, "op": "_FusedMatMulGelu",
+                                       "input": list(mm.inputs), "attr": attrs})
+            break
     if not replaced:
         return list(ordered), 0
     return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
@@ -664,6 +777,7 @@ class GraphExecutor(object):
         self.fused_subgraphs = 0
         self.fused_heads = 0
         self.fused_softmaxes = 0
+        self.fused_gelus = 0
         self.keep_intermediates = False
         self.intermediates = {}
 
@@ -728,6 +842,13 @@ class GraphExecutor(object):
                 protected=set(input_names) | set(parse_node_name(o)[0] for o in output_names))
         if fuse and "heads" not in self.fuse_skip:
             ordered, k = fuse_attention_heads(ordered, consts[0], consts[1], protected=prot)
+        # Off unless TFJS_CUDA_FUSE_GELU=1: measured on BERT-base, the erf GELU as a GEMM
+        # epilogue is five times slower than the separate chain kernel (its double-precision
+        # chains need the whole SM's warps; the epilogue has eight), 8.5 against 5.4 ms per step.
+        if fuse and "gelu" not in self.fuse_skip and \
+                os.environ.get("TFJS_CUDA_FUSE_GELU", "0") not in ("", "0"):
+            ordered, self.fused_gelus = fuse_gelu_into_matmul(ordered, consts[0], consts[1],
+                                                              protected=prot)
         if fuse and "softmax" not in self.fuse_skip:
             ordered, j = fuse_softmax_inputs(ordered, consts[0], consts[1], protected=prot)
         if fuse:

@@ -6,6 +6,8 @@ batches wrap with `bi % batchDim`).
 """
 from ctypes import byref
 
+import numpy as np
+
 from .. import _cabi
 from ..kernel_registry import KernelConfig
 from ..util import assert_and_get_broadcast_shape, size_from_shape
@@ -14,7 +16,7 @@ from . import elementwise
 
 
 def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activation, alpha,
-                 heads=None):
+                 heads=None, gelu=None):
     """heads: None, or (layout, rows_or_heads, head_dim, out_shape) for the product stored
     through the heads permutation (tfjs_cuda_fused_matmul_heads); bias and activation must
     then be fusable, and a refusal by the library propagates as CudaError(UNSUPPORTED)."""
@@ -48,6 +50,9 @@ def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activatio
     prelu_len = per_channel_len(prelu, outer_b) if activation == "prelu" else 0
     fuse_bias = bias_len is not None
     fuse_act = fuse_bias and (activation != "prelu" or prelu_len is not None)
+    if activation == "gelu_erf" and not (fuse_act and gelu is not None):
+        # only exists as a fused epilogue (graph_model.fuse_gelu_into_matmul)
+        raise _cabi.CudaError(_cabi.UNSUPPORTED, "matMul: gelu_erf needs a fusable bias")
     if heads is not None and not (fuse_bias and fuse_act and size_from_shape(out_shape)):
         raise _cabi.CudaError(_cabi.UNSUPPORTED, "matMul heads: bias / activation not fusable")
     out = backend.make_output(out_shape if heads is None else heads[3], "float32")
@@ -60,6 +65,9 @@ def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activatio
         p.bias_len = bias_len if fuse_bias else 0
         p.prelu_len = (prelu_len or 0) if fuse_act else 0
         p.leakyrelu_alpha = 0.2 if alpha is None else float(alpha)
+        if activation == "gelu_erf":
+            p.gelu_scale, p.gelu_half, p.gelu_one = [float(np.float32(v)) for v in gelu[:3]]
+            p.gelu_divide = int(bool(gelu[3]))
         try:
             bias_id = dev(backend, bias) if fuse_bias and bias is not None else 0
             prelu_id = dev(backend, prelu) if fuse_act and activation == "prelu" else 0
@@ -90,7 +98,7 @@ def fused_matmul(args):
     return _matmul_impl(b, i["a"], i["b"], a.get("transposeA", False),
                         a.get("transposeB", False), i.get("bias"),
                         i.get("preluActivationWeights"), a.get("activation") or "linear",
-                        a.get("leakyreluAlpha"))
+                        a.get("leakyreluAlpha"), gelu=a.get("geluParams"))
 
 
 def batch_matmul(args):

@@ -171,9 +171,12 @@ def mat_mul_heads(a, b, layout, heads, transposeA=False, transposeB=False, bias=
 
 
 def fused_mat_mul(a, b, transposeA=False, transposeB=False, bias=None, activation="linear",
-                  preluActivationWeights=None, leakyreluAlpha=0.2):
+                  preluActivationWeights=None, leakyreluAlpha=0.2, geluParams=None):
     """tfjs-core/src/ops/fused/mat_mul.ts: operands are reshaped to rank 3 first
-    (:117-122) and the result is reshaped back."""
+    (:117-122) and the result is reshaped back.  activation "gelu_erf" with geluParams =
+    [scale, half, one, divide] exists on the 'cuda' backend only: (h * half) * (erf(h * scale)
+    + one) as the epilogue (the graph executor substitutes it for the five nodes of an erf
+    GELU after a dense layer)."""
     inner_a = a.shape[a.rank - 2] if transposeA else a.shape[a.rank - 1]
     inner_b = b.shape[b.rank - 1] if transposeB else b.shape[b.rank - 2]
     outer_a = a.shape[a.rank - 1] if transposeA else a.shape[a.rank - 2]
@@ -196,7 +199,8 @@ def fused_mat_mul(a, b, transposeA=False, transposeB=False, bias=None, activatio
                    {"a": a3, "b": b3, "bias": bias,
                     "preluActivationWeights": preluActivationWeights},
                    {"transposeA": transposeA, "transposeB": transposeB,
-                    "activation": activation, "leakyreluAlpha": leakyreluAlpha})
+                    "activation": activation, "leakyreluAlpha": leakyreluAlpha,
+                    "geluParams": geluParams})
     finally:
         a3.dispose()
         b3.dispose()
