@@ -106,16 +106,23 @@ export function packConvParams(
   return buf;
 }
 
-/** tfjs_cuda_matmul_params: 10 int32 fields then one double. */
+/** tfjs_cuda_matmul_params: 10 int32 fields, one double, then the constants of the
+ * erf-GELU epilogue (three floats and an int32; zero unless activation is GELU_ERF). */
 export function packMatMulParams(
     batchA: number, batchB: number, m: number, n: number, k: number, transposeA: boolean,
     transposeB: boolean, activation: number, biasLen: number, preluLen: number,
-    leakyreluAlpha = 0.2): ArrayBuffer {
-  const buf = new ArrayBuffer(48);
+    leakyreluAlpha = 0.2, gelu?: [number, number, number, boolean]): ArrayBuffer {
+  const buf = new ArrayBuffer(64);
   const v = new DataView(buf);
   [batchA, batchB, m, n, k, transposeA ? 1 : 0, transposeB ? 1 : 0, activation, biasLen, preluLen]
       .forEach((x, i) => v.setInt32(4 * i, x, true));
   v.setFloat64(40, leakyreluAlpha, true);
+  if (gelu) {
+    v.setFloat32(48, gelu[0], true);
+    v.setFloat32(52, gelu[1], true);
+    v.setFloat32(56, gelu[2], true);
+    v.setInt32(60, gelu[3] ? 1 : 0, true);
+  }
   return buf;
 }
 
