@@ -69,6 +69,11 @@ CONV_CASES = {
     "prelu_scalar_nobias": lambda: conv_case(14, (1, 8, 8, 32), (3, 3, 32, 32), bias=False, act="prelu", prelu="scalar"),
     "wide_cout256": lambda: conv_case(15, (2, 14, 14, 256), (3, 3, 256, 256)),
     "cin5_simt_route": lambda: conv_case(16, (1, 9, 9, 5), (2, 2, 5, 7), pad="valid"),
+    # 3 x 3 on a 3-channel image: the fp32 SIMT stem kernel (both math modes)
+    "stem_3x3_s1_cout8_valid": lambda: conv_case(22, (2, 19, 23, 3), (3, 3, 3, 8), pad="valid", act="linear"),
+    "stem_3x3_s2_cout64_prelu": lambda: conv_case(23, (1, 30, 30, 3), (3, 3, 3, 64), strides=2, act="prelu", prelu="channel"),
+    "stem_3x3_s2_224_cout32": lambda: conv_case(24, (1, 224, 224, 3), (3, 3, 3, 32), strides=2, act="relu6"),
+    "stem_3x3_s1_explicit_pad_cout16": lambda: conv_case(25, (2, 9, 70, 3), (3, 3, 3, 16), pad=[[0, 0], [2, 1], [0, 3], [0, 0]], bias=False, act="sigmoid"),
     # 14 tiles of 144 K steps (ResNet conv5 at a small batch): K-split over all SMs
     "k_split_conv5": lambda: conv_case(21, (16, 7, 7, 512), (3, 3, 512, 512)),
     # long K, <= 128 output channels: the form with the pixels on the MMA's N axis
