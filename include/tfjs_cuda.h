@@ -181,7 +181,13 @@ int tfjs_cuda_fused_conv2d_residual(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_p
  * wait, or need new pool memory are refused during a capture (TFJS_CUDA_UNSUPPORTED) and
  * make capture_end discard it; the host layer then keeps running that model eagerly.
  * Tensors created during a capture that are still alive at capture_end (the step's
- * outputs) stay valid until graph_destroy and are rewritten by every replay. */
+ * outputs) stay valid until graph_destroy and are rewritten by every replay.
+ * Two kinds of memory outside the arena are also referenced by address: the library's
+ * repacked copy of each weight the step reads, and its scratch buffer (explicit im2col of
+ * unusual convolutions).  If, after the capture, such a weight is freed or rewritten, or an
+ * eager call makes the scratch buffer grow, the graph is stale: graph_launch returns
+ * TFJS_CUDA_UNSUPPORTED without launching anything and the host captures the step again
+ * (or runs it eagerly). */
 int tfjs_cuda_capture_begin(tfjs_cuda_ctx* ctx, uint64_t arena_bytes);
 int tfjs_cuda_capture_end(tfjs_cuda_ctx* ctx, int abandon, int32_t* out_graph);
 int tfjs_cuda_graph_launch(tfjs_cuda_ctx* ctx, int32_t graph);
@@ -472,8 +478,13 @@ int tfjs_cuda_decode_float16(tfjs_cuda_ctx* ctx, int32_t q_id, uint64_t n, int32
  *     first call outside any stream capture.
  *   - All calls on a GPU share the one table.  Each call rewrites every entry it
  *     will read, so nothing carries over from earlier calls; but two calls whose
- *     GPU work overlaps (two contexts on one device, or two host threads) would
- *     overwrite each other's table.  Serialise them. */
+ *     GPU work overlaps (two contexts on one device, each with its own stream) would
+ *     overwrite each other's table.  Serialise them, e.g. sync the first context
+ *     before the second one calls.
+ *   - The table is built on the host in one fixed array shared by the whole process
+ *     (all GPUs).  The library takes a lock around filling it and handing it to the
+ *     driver, so host threads may call concurrently for different GPUs; they simply
+ *     take turns for those few microseconds. */
 int tfjs_cuda_dequantize_static(tfjs_cuda_ctx* ctx, int32_t q_dtype_bytes,
                                 int32_t to_dtype, int32_t q_id, double scale,
                                 double min, uint64_t n, int32_t out_id);

@@ -1,7 +1,7 @@
 """Per-kernel micro-benchmark of the 'cuda' backend: times one op through the public
 op front end with CUDA events on the backend's stream.
 
-    python -m tfjs_b200.kernel_bench <case> [iterations]
+    python kernel_bench.py <case> [iterations]
 
 cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072),
 mm_<m>_<k>_<n> (fused matMul + bias),

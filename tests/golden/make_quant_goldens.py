@@ -1,6 +1,6 @@
 """Generates quantisation fixtures by importing the reference's own module.
 
-    python tests/golden/make_quant_goldens.py /root/reference tests/golden/quant_goldens.npz
+    python tests/golden/make_quant_goldens.py <tfjs checkout> tests/golden/quant_goldens.npz
 
 tfjs-converter/python/tensorflowjs/quantization.py needs only numpy, so it is
 loaded straight from the reference checkout (the `tensorflowjs` package itself
@@ -57,5 +57,7 @@ def main(ref_root, out_path):
 
 if __name__ == "__main__":
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference",
+    if len(sys.argv) < 2:
+        sys.exit("usage: %s <path to a tensorflow/tfjs checkout> [output file]" % sys.argv[0])
+    main(sys.argv[1],
          sys.argv[2] if len(sys.argv) > 2 else os.path.join(root, "tests/golden/quant_goldens.npz"))

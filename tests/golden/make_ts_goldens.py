@@ -2,7 +2,7 @@
 
 Run in the container that has the reference checkout:
 
-    python tests/golden/make_ts_goldens.py /root/reference tests/golden/ts_goldens.json
+    python tests/golden/make_ts_goldens.py <tfjs checkout> tests/golden/ts_goldens.json
 
 The reference's op tests (tfjs-core/src/ops/**/*_test.ts) hold inputs and
 expected outputs inline.  Node is not available, so this script translates each
@@ -52,7 +52,6 @@ TEST_FILES = [
     "tfjs-core/src/ops/elu_test.ts",
     "tfjs-core/src/ops/sigmoid_test.ts",
     "tfjs-core/src/ops/leaky_relu_test.ts",
-    "tfjs-core/src/ops/prelu_test.ts",
     "tfjs-core/src/ops/erf_test.ts",
     "tfjs-core/src/ops/exp_test.ts",
     "tfjs-core/src/ops/sqrt_test.ts",
@@ -63,6 +62,22 @@ TEST_FILES = [
     "tfjs-core/src/ops/batchnorm_test.ts",
     "tfjs-core/src/ops/clip_by_value_test.ts",
     "tfjs-core/src/ops/tile_test.ts",
+    "tfjs-core/src/ops/binary_ops_test.ts",
+    "tfjs-core/src/ops/arithmetic_test.ts",
+    "tfjs-core/src/ops/sub_test.ts",
+    "tfjs-core/src/ops/neg_test.ts",
+    "tfjs-core/src/ops/abs_test.ts",
+    "tfjs-core/src/ops/log_test.ts",
+    "tfjs-core/src/ops/concat_test.ts",
+    "tfjs-core/src/ops/slice_test.ts",
+    "tfjs-core/src/ops/slice1d_test.ts",
+    "tfjs-core/src/ops/slice2d_test.ts",
+    "tfjs-core/src/ops/slice3d_test.ts",
+    "tfjs-core/src/ops/slice4d_test.ts",
+    "tfjs-core/src/ops/pad_test.ts",
+    "tfjs-core/src/ops/stack_test.ts",
+    "tfjs-core/src/ops/expand_dims_test.ts",
+    "tfjs-core/src/tensor_test.ts",
 ]
 
 
@@ -157,7 +172,35 @@ def find_specs(src):
         if brace < 0:
             continue
         close = match_close(inner, brace)
-        yield name.strip(), src.count("\n", 0, m.start()) + 1, inner[brace + 1:close]
+        yield name.strip(), src.count("\n", 0, m.start()) + 1, inner[brace + 1:close], m.start()
+
+
+def find_setups(src):
+    """(span start, span end, body) of every `beforeEach(() => {...})`, the span being the
+    describe block that holds it: its statements run before each spec of that block."""
+    spans = []
+    for m in re.finditer(r"\b(?:describeWithFlags|describe)\(", src):
+        try:
+            spans.append((m.start(), match_close(src, m.end() - 1)))
+        except Skip:
+            continue
+    out = []
+    for m in re.finditer(r"\bbeforeEach\(", src):
+        try:
+            end = match_close(src, m.end() - 1)
+            inner = src[m.end():end]
+            arrow = inner.find("=>")
+            brace = inner.find("{", arrow)
+            if arrow < 0 or brace < 0:
+                continue
+            body = inner[brace + 1:match_close(inner, brace)]
+        except Skip:
+            continue
+        holders = [sp for sp in spans if sp[0] < m.start() < sp[1]]
+        if holders:
+            a, b = max(holders, key=lambda sp: sp[0])     # innermost
+            out.append((a, b, body))
+    return out
 
 
 def strip_as_casts(e):
@@ -243,6 +286,7 @@ def tr_expr(e):
     e = re.sub(r"\bawait\s+", "", e)
     e = re.sub(r"\bnew\s+(Float32Array|Int32Array|Uint8Array)\s*\(", "__typed(", e)
     e = re.sub(r"\bnew\s+Array\s*\(", "__newarray(", e)
+    e = re.sub(r"\bArray\.from\(", "__arrayfrom(", e)
     e = e.replace("tf.test_util.", "")
     e = e.replace("===", "==").replace("!==", "!=")
     e = re.sub(r"&&", " and ", e)
@@ -351,6 +395,10 @@ def tr_stmt(s):
         return "__expect_equal(%s, %s)" % (tr_expr(m.group(1)), tr_expr(m.group(2)))
     if s.startswith("expect("):
         raise Skip("expect form")
+    m = re.match(r"^(\w+)\[([^\]]+)\]\s*=(?!=)\s*(.*)$", s)
+    if m and not s.startswith("expectArrays"):
+        # a JavaScript array grows when an index beyond its end is assigned
+        return "__setidx(%s, %s, %s)" % (m.group(1), tr_expr(m.group(2)), tr_expr(m.group(3)))
     m = re.match(r"^(\w[\w.\[\]]*)\s*(\+|-|\*)?=\s*(.*)$", s)
     if m and not s.startswith("expectArrays"):
         return "%s %s= %s" % (tr_expr(m.group(1)), m.group(2) or "", tr_expr(m.group(3)))
@@ -426,19 +474,77 @@ class FT(object):
         return Data(self)
 
     def array(self):
-        raise Skip("array()")
+        return self.value.tolist()
+
+    def arraySync(self):
+        return self.value.tolist()
+
+    def buffer(self):
+        return Buf(self.value)
+
+    def bufferSync(self):
+        return Buf(self.value)
 
     def reshape(self, shape):
-        return FT(self.value.reshape(shape), self.dtype, None)
+        # a view of an op result still checks that op: the expected values are compared
+        # flat, and the case keeps the op's own output shape
+        out = FT(self.value.reshape(shape), self.dtype, self.case)
+        out.op_shape = getattr(self, "op_shape", list(self.value.shape))
+        if getattr(self, "squeeze0", False):
+            out.squeeze0 = True
+        return out
 
     def as1D(self):
+        return self.reshape([-1])
+
+    def as2D(self, a, b):
+        return self.reshape([a, b])
+
+    def as3D(self, a, b, c):
+        return self.reshape([a, b, c])
+
+    def as4D(self, a, b, c, d):
+        return self.reshape([a, b, c, d])
+
+    def flatten(self):
         return self.reshape([-1])
 
     def dispose(self):
         pass
 
     def clone(self):
-        raise Skip("clone")
+        return FT(self.value.copy(), self.dtype, None)
+
+    def toInt(self):
+        return self.tf.cast(self, "int32")
+
+    def toFloat(self):
+        return self.tf.cast(self, "float32")
+
+    def toBool(self):
+        return self.tf.cast(self, "bool")
+
+    def asType(self, dtype):
+        return self.tf.cast(self, dtype)
+
+    def __getattr__(self, name):
+        # chained form a.op(b, ...) of tf.op(a, b, ...)
+        if name.startswith("__") or name in ("tf", "squeeze0", "op_shape"):
+            raise AttributeError(name)
+        fn = getattr(self.tf, name, None)
+        if fn is None:
+            raise Skip("chained %s" % name)
+        return lambda *args, **kw: fn(self, *args, **kw)
+
+
+class Buf(object):
+    """TensorBuffer stand-in (tfjs-core/src/tensor.ts TensorBuffer.get)."""
+
+    def __init__(self, value):
+        self.value = value
+
+    def get(self, *idx):
+        return float(self.value[tuple(int(i) for i in idx)]) if idx else float(self.value)
 
 
 class Data(object):
@@ -704,6 +810,88 @@ def make_tf(rec):
                                      "scale": scale is not None and as_ft(scale) or None},
                       {"varianceEpsilon": varianceEpsilon})
     tf.batchNorm = tf.batchNorm2d = tf.batchNorm3d = tf.batchNorm4d = batchnorm
+
+    tf.pow = binary("pow")
+    real_div = binary("div")
+
+    def div(a, b):
+        a, b = as_ft(a), as_ft(b)
+        if a.dtype == "int32" and b.dtype == "int32":
+            raise Skip("int32 div is the FloorDiv kernel")      # tfjs-core/src/ops/div.ts:55-57
+        return real_div(a, b)
+    tf.div = div
+
+    def dot(t1, t2):
+        """tfjs-core/src/ops/dot.ts:45-72: vectors become 1 x n / n x 1 matrices."""
+        t1, t2 = as_ft(t1), as_ft(t2)
+        if t1.rank == 1 and t2.rank == 1:
+            return matmul(t1.reshape([1, -1]), t2.reshape([-1, 1])).reshape([])
+        if t1.rank == 1 and t2.rank == 2:
+            return matmul(t1.reshape([1, -1]), t2).reshape([-1])
+        if t1.rank == 2 and t2.rank == 1:
+            return matmul(t1, t2.reshape([-1, 1])).reshape([-1])
+        return matmul(t1, t2)
+    tf.dot = dot
+    tf.outerProduct = lambda v1, v2: matmul(as_ft(v1).reshape([-1, 1]), as_ft(v2).reshape([1, -1]))
+
+    def cast(x, dtype):
+        x = as_ft(x)
+        if dtype not in ("float32", "int32", "bool"):
+            raise Skip("dtype %s" % dtype)
+        return rec.op("cast", {"x": x}, {"dtype": dtype}, dtype)
+    tf.cast = cast
+
+    def same_dtype(ts):
+        ts = [as_ft(t) for t in ts]
+        if len(set(t.dtype for t in ts)) != 1:
+            raise Skip("mixed dtype")
+        return ts
+
+    def chained_list(tensors, rest):
+        """a.concat(b, axis) / a.stack(b, axis): (tensor list, axis)."""
+        if isinstance(tensors, FT):
+            other = rest[0] if rest else []
+            tensors = [tensors] + (list(other) if isinstance(other, (list, tuple)) else [other])
+            rest = rest[1:]
+        return tensors, (rest[0] if rest else 0)
+
+    def concat(tensors, *rest, **kw):
+        tensors, axis = chained_list(tensors, rest)
+        axis = kw.get("axis", axis)
+        ts = same_dtype(tensors)
+        return rec.op("concat", {"tensors": ts}, {"axis": axis}, ts[0].dtype)
+    tf.concat = tf.concat1d = tf.concat2d = tf.concat3d = tf.concat4d = concat
+
+    def stack(tensors, *rest, **kw):
+        tensors, axis = chained_list(tensors, rest)
+        axis = kw.get("axis", axis)
+        ts = same_dtype(tensors)
+        return rec.op("stack", {"tensors": ts}, {"axis": axis}, ts[0].dtype)
+    tf.stack = stack
+
+    def expand_dims(x, axis=0):
+        x = as_ft(x)
+        return rec.op("expand_dims", {"x": x}, {"axis": axis}, x.dtype)
+    tf.expandDims = expand_dims
+
+    def slice_(x, begin, size=None):
+        x = as_ft(x)
+        return rec.op("slice", {"x": x}, {"begin": begin, "size": size}, x.dtype)
+    tf.slice = tf.slice1d = tf.slice2d = tf.slice3d = tf.slice4d = slice_
+
+    def pad(x, paddings, constantValue=0):
+        x = as_ft(x)
+        if x.rank == 1 and paddings and not isinstance(paddings[0], (list, tuple)):
+            paddings = [paddings]      # pad1d takes one [before, after] pair
+        return rec.op("pad", {"x": x}, {"paddings": [list(p) for p in paddings],
+                                        "constantValue": constantValue}, x.dtype)
+    tf.pad = tf.pad1d = tf.pad2d = tf.pad3d = tf.pad4d = pad
+
+    tf.memory = lambda: Obj({"numTensors": 0, "numDataBuffers": 0, "numBytes": 0})
+    tf.engine = lambda: Obj({"backend": Obj({"numDataIds": lambda: 0})})
+    tf.dispose = lambda *a: None
+    tf.backend = lambda: Obj({"floatPrecision": lambda: 32})
+    FT.tf = tf
     return tf
 
 
@@ -733,6 +921,24 @@ def generate_case_inputs(total_tensor, total_filter):
     return out
 
 
+def optimal_window(n):
+    if n <= 30:
+        return n
+    a = int(math.floor(math.sqrt(n)))
+    while a < n:
+        if n % a == 0:
+            return a
+        a += 1
+    return n
+
+
+def set_index(lst, i, v):
+    i = int(i)
+    if i >= len(lst):
+        lst.extend([None] * (i + 1 - len(lst)))
+    lst[i] = v
+
+
 class Obj(object):
     def __init__(self, d):
         self.__dict__.update(d)
@@ -757,17 +963,26 @@ def run_spec(py_lines, rec, goldens_out, meta, helpers=""):
            "__newarray": lambda n=0: [None] * int(n), "generateCaseInputs": generate_case_inputs,
            "dict": dict, "len": len, "range": range, "int": int,
            "MATMUL_SHARED_DIM_THRESHOLD": 1000,  # mat_mul_test.ts:24
-           "__obj": Obj}
+           "__obj": Obj, "__setidx": set_index,
+           # tfjs-core/src/util_base.ts tanh (Math.tanh with the overflow guards)
+           "util": Obj({"tanh": math.tanh}),
+           # reduce_util.ts:24-38 with nearestDivisor of util_base.ts
+           "reduce_util": Obj({"PARALLELIZE_THRESHOLD": 30,
+                               "computeOptimalWindowSize": optimal_window}),
+           "env": Obj({"backendName": "cpu"}), "__arrayfrom": lambda v: v,
+           "backend": lambda: Obj({"floatPrecision": lambda: 32})}
     if helpers:
         exec(helpers, env)
-    exec("\n".join(py_lines), env)
+    # the spec body runs as a function so that an early `return` is legal
+    exec("def __spec():\n" + "\n".join("    " + ln for ln in (py_lines or ["pass"])) +
+         "\n__spec()\n", env)
     for t, expected in checks:
         if t.case is None:
             continue
         case = t.case
         goldens_out.append(dict(meta, op=case["op"], inputs=case["inputs"], attrs=case["attrs"],
                                 input_dtypes=case["input_dtypes"], expected=expected,
-                                expected_shape=list(t.value.shape),
+                                expected_shape=list(getattr(t, "op_shape", t.value.shape)),
                                 squeeze0=bool(getattr(t, "squeeze0", False))))
 
 
@@ -803,8 +1018,10 @@ def main(ref_root, out_path):
         src = strip_comments(open(path).read())
         stats = {"specs": 0, "extracted_specs": 0, "cases": 0, "skipped": {}}
         helpers = file_helpers(src)
-        for name, line, body in find_specs(src):
+        setups = find_setups(src)
+        for name, line, body, pos in find_specs(src):
             stats["specs"] += 1
+            body = "".join(b + ";\n" for a, e, b in sorted(setups) if a < pos < e) + body
             before = len(goldens)
             try:
                 if re.search(r"\btf\.(grad|grads|valueAndGrad|customGrad|complex|browser)\b", body):
@@ -822,6 +1039,13 @@ def main(ref_root, out_path):
             except Exception as e:  # translation gap: count it, keep going
                 del goldens[before:]
                 key = "translator: %s" % type(e).__name__
+                msg = str(e)
+                if isinstance(e, ValueError) and "could not convert string" in msg:
+                    key = "string tensor"
+                elif isinstance(e, AttributeError) and "'NS' object has no attribute" in msg:
+                    key = "op outside the hot path"   # tf.mod, tf.atan2, tf.squeeze ...
+                elif isinstance(e, NameError) and "encodeString" in msg:
+                    key = "string tensor"
                 stats["skipped"][key] = stats["skipped"].get(key, 0) + 1
                 continue
             if len(goldens) > before:
@@ -848,5 +1072,7 @@ def main(ref_root, out_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference",
+    if len(sys.argv) < 2:
+        sys.exit("usage: %s <path to a tensorflow/tfjs checkout> [output file]" % sys.argv[0])
+    main(sys.argv[1],
          sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "tests", "golden", "ts_goldens.json"))

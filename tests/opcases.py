@@ -90,6 +90,10 @@ def run_oracle(case):
         return np.pad(np.asarray(i["x"]), a["paddings"], constant_values=a.get("constantValue", 0))
     if op == "tile":
         return np.tile(np.asarray(i["x"]), a["reps"])
+    if op == "stack":
+        return np.stack([np.asarray(t) for t in i["tensors"]], a.get("axis", 0))
+    if op == "expand_dims":
+        return np.expand_dims(np.asarray(i["x"]), a.get("axis", 0))
     raise NotImplementedError(op)
 
 
@@ -180,6 +184,10 @@ def run_cuda(case):
             out = ops.pad(T(i["x"]), a["paddings"], a.get("constantValue", 0))
         elif op == "tile":
             out = ops.tile(T(i["x"]), a["reps"])
+        elif op == "stack":
+            out = ops.stack([T(t) for t in i["tensors"]], a.get("axis", 0))
+        elif op == "expand_dims":
+            out = ops.expand_dims(T(i["x"]), a.get("axis", 0))
         else:
             raise NotImplementedError(op)
         res = out.arraySync()

@@ -121,3 +121,66 @@ def test_uncapturable_model_stays_eager(cuda_engine, monkeypatch):
     assert st["state"] == "eager" and "captured step" in st["why"]
     gm.dispose()
     ref.dispose()
+
+
+def _im2col_model(batch, seed=5):
+    """One convolution whose channel count (6) and reduction length (11 * 11 * 6 = 726) send
+    it down the explicit im2col path, which writes the context's scratch buffer, followed by
+    a 3x3 convolution with a packed weight."""
+    g = model_zoo.GraphBuilder(seed)
+    r = g.rng
+    x = g.placeholder("input", [batch, 24, 24, 6])
+    y = g.conv(x, (r.standard_normal((11, 11, 6, 8)) / 27).astype(np.float32),
+               r.standard_normal(8).astype(np.float32), 1, "relu")
+    y = g.conv(y, (r.standard_normal((3, 3, 8, 64)) / 8).astype(np.float32),
+               r.standard_normal(64).astype(np.float32), 1, None, name="out")
+    return g.artifacts(["input"], [y])
+
+
+def test_stale_graph_is_refused_and_captured_again(cuda_engine):
+    """A captured step carries the addresses of the scratch buffer and of the packed weight
+    copies.  When an eager call makes the scratch buffer grow, or a weight is rewritten, the
+    library refuses the old graph; GraphModel runs that step eagerly and captures again."""
+    from tfjs_b200 import ops as tf
+    be = cuda_engine.backend
+    model_json, weights = _im2col_model(2)
+    fast = GraphModel(model_json, weights, cuda_engine, replay=True)
+    eager = GraphModel(model_json, weights, cuda_engine, replay=False)
+
+    def step(seed):
+        x = np.random.default_rng(seed).standard_normal((2, 24, 24, 6)).astype(np.float32)
+        t = cuda_engine.make_tensor(x)
+        got, want = fast.execute(t, ["out"])[0], eager.execute(t, ["out"])[0]
+        a, b = got.dataSync(), want.dataSync()
+        for v in (t, got, want):
+            v.dispose()
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), seed
+        return list(fast._replays.values())[0]
+
+    assert [step(s)["state"] for s in range(3)] == ["warm", "ready", "ready"]
+    graph = list(fast._replays.values())[0]["graph"]
+    # a larger convolution of the same kind, eagerly: the scratch buffer is re-allocated
+    r = np.random.default_rng(9)
+    big = tf.tensor(r.standard_normal((16, 40, 40, 6)).astype(np.float32))
+    f = tf.tensor((r.standard_normal((11, 11, 6, 8)) / 27).astype(np.float32))
+    y = tf.conv2d(big, f, [1, 1], "same")
+    y.dataSync()
+    for t in (big, f, y):
+        t.dispose()
+    assert be.lib.tfjs_cuda_graph_launch(be.ctx, graph) == 5        # TFJS_CUDA_UNSUPPORTED
+    assert b"stale" in be.lib.tfjs_cuda_last_error(be.ctx)
+    st = step(3)
+    assert st["state"] == "warm" and st["recaptures"] == 1
+    assert [step(s)["state"] for s in (4, 5)] == ["ready", "ready"]
+    # rewriting a weight drops its packed copy: stale again, and the new values are used
+    name = [n for n, t in fast.weights.items() if t.shape == [3, 3, 8, 64]][0]
+    new = np.random.default_rng(10).standard_normal((3, 3, 8, 64)).astype(np.float32)
+    for gm in (fast, eager):
+        dev = be.device_id(gm.weights[name].dataId)
+        be.check(be.lib.tfjs_cuda_write(be.ctx, dev, new.ctypes.data_as(ctypes.c_void_p),
+                                        new.nbytes))
+    st = step(6)
+    assert st["state"] == "warm" and st["recaptures"] == 2
+    assert step(7)["state"] == "ready"
+    fast.dispose()
+    eager.dispose()

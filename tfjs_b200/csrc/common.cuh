@@ -29,6 +29,12 @@ struct ReplayGraph {
   void* arena = nullptr;
   uint64_t arena_bytes = 0;
   uint64_t launches = 0;  // kernels per replay
+  // Memory outside the arena whose address the recorded kernels carry: the packed copies
+  // of these weight ids and, if uses_scratch, the context's scratch buffer.  When one of
+  // them is freed or re-allocated the graph is stale and graph_launch refuses it.
+  std::vector<int32_t> packed_ids;
+  bool uses_scratch = false;
+  bool stale = false;
 };
 struct ArenaSpan {
   uint64_t off, size;
@@ -74,6 +80,8 @@ struct tfjs_cuda_ctx {
   uint64_t arena_bytes = 0;
   std::vector<ArenaSpan> arena_free;  // sorted by offset, coalesced
   uint64_t capture_launches0 = 0;
+  std::vector<int32_t> capture_packed;  // weight ids whose packed copy the capture reads
+  bool capture_scratch = false;         // the capture reads or writes ctx->scratch
   std::vector<ReplayGraph> graphs;    // index + 1 = graph id
   cudaMemPool_t pool = nullptr;
   std::vector<Buffer> bufs;  // index = id; slot 0 unused
@@ -90,6 +98,7 @@ struct tfjs_cuda_ctx {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::vector<cudaEvent_t> prof_events;  // numbered events for per-kernel timing
   std::vector<cudaEvent_t> read_events;  // tickets of tfjs_cuda_read_begin (index + 1)
+  std::vector<int*> read_flags;          // one pinned copy of the device error word per ticket
   std::vector<int> read_free;            // ticket slots free for reuse
   void* l2_scratch = nullptr;
   uint64_t l2_scratch_bytes = 0;
@@ -110,6 +119,8 @@ int ctx_get(tfjs_cuda_ctx* ctx, int32_t id, uint64_t need, const char* name,
 int ctx_scratch(tfjs_cuda_ctx* ctx, uint64_t bytes, void** out);
 void ctx_mark_written(tfjs_cuda_ctx* ctx, int32_t id);
 void ctx_drop_packed(tfjs_cuda_ctx* ctx, int32_t id);
+// Marks captured steps that read the packed copy of weight `id` as stale (no memory call).
+void ctx_packed_contents_changed(tfjs_cuda_ctx* ctx, int32_t id);
 
 #define CUDA_TRY(ctx, expr)                                   \
   do {                                                        \

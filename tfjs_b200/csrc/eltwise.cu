@@ -5,6 +5,7 @@
 // All are SIMT kernels with grid-stride loops over 128-bit vectors where the
 // layout allows; grids are capped at a multiple of the SM count.
 #include "common.cuh"
+#include <mutex>
 
 namespace {
 
@@ -1489,8 +1490,13 @@ static __device__ __align__(256) uint32_t g_static_dequant_table[TFJS_CUDA_STATI
 // In host code the name above is only a handle for the symbol, not an address a
 // kernel can use; the real device address is looked up once per device.
 static uint32_t* g_static_table_addr[64];
-// Host staging for the table (no heap use on the call path).
+// Host staging for the table (no heap use on the call path).  One array for the whole
+// process, so host threads that dequantise at the same time (on the same GPU or on
+// different ones) take turns filling it: the lock is held from the fill until the copy
+// out of it has been staged by the driver, which is before cudaMemcpyAsync returns for a
+// pageable source.
 static uint32_t g_static_table_host[TFJS_CUDA_STATIC_TABLE_ENTRIES];
+static std::mutex g_static_table_lock;
 
 int tfjs_cuda_dequantize_static(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_dtype,
                                 int32_t q_id, double scale, double min, uint64_t n,
@@ -1515,6 +1521,7 @@ int tfjs_cuda_dequantize_static(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_
   if ((rc = ctx_get(ctx, out_id, n * 4, "dequantize_static out", &o))) return rc;
   if (n == 0) return TFJS_CUDA_OK;
   cudaSetDevice(ctx->device);
+  std::lock_guard<std::mutex> hold(g_static_table_lock);
   uint32_t* table = g_static_table_addr[ctx->device];
   if (!table) {
     // First call on this device: resolve the symbol with this device current.
@@ -1556,6 +1563,7 @@ int tfjs_cuda_dequantize_static(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_
   LAUNCH_CHECK(ctx, "dequant_kernel (static table)");
   o->version++;           // any packed copy of the old contents is now stale
   o->from_host = true;    // dequantised weights are constants
+  ctx_packed_contents_changed(ctx, out_id);  // so are captured steps that read that copy
   return TFJS_CUDA_OK;
 }
 

@@ -80,6 +80,7 @@ int get_packed(tfjs_cuda_ctx* ctx, int32_t id, Buffer* src, int batch, int N, in
   auto it = ctx->packed.find(id);
   if (it != ctx->packed.end() && it->second.version == src->version &&
       it->second.layout == layout && it->second.rows == N) {
+    if (ctx->capturing) ctx->capture_packed.push_back(id);
     *out = it->second.ptr;
     return TFJS_CUDA_OK;
   }

@@ -62,6 +62,9 @@ int ctx_get(tfjs_cuda_ctx* ctx, int32_t id, uint64_t need, const char* name,
 int ctx_scratch(tfjs_cuda_ctx* ctx, uint64_t bytes, void** out) {
   if (bytes > ctx->scratch_bytes) {
     NOT_WHILE_CAPTURING(ctx, "growing the scratch buffer");
+    // captured steps that use the scratch buffer carry its old address
+    for (ReplayGraph& g : ctx->graphs)
+      if (g.exec && g.uses_scratch) g.stale = true;
     if (ctx->scratch) CUDA_TRY(ctx, cudaFreeAsync(ctx->scratch, ctx->stream));
     ctx->scratch = nullptr;
     ctx->scratch_bytes = 0;
@@ -69,6 +72,7 @@ int ctx_scratch(tfjs_cuda_ctx* ctx, uint64_t bytes, void** out) {
     CUDA_TRY(ctx, cudaMallocAsync(&ctx->scratch, want, ctx->stream));
     ctx->scratch_bytes = want;
   }
+  if (ctx->capturing) ctx->capture_scratch = true;
   *out = ctx->scratch;
   return TFJS_CUDA_OK;
 }
@@ -81,9 +85,18 @@ void ctx_mark_written(tfjs_cuda_ctx* ctx, int32_t id) {
   }
 }
 
+void ctx_packed_contents_changed(tfjs_cuda_ctx* ctx, int32_t id) {
+  for (ReplayGraph& g : ctx->graphs)
+    if (g.exec)
+      for (int32_t w : g.packed_ids)
+        if (w == id) g.stale = true;
+}
+
 void ctx_drop_packed(tfjs_cuda_ctx* ctx, int32_t id) {
   auto it = ctx->packed.find(id);
   if (it == ctx->packed.end()) return;
+  // captured steps that read this packed copy carry its address
+  ctx_packed_contents_changed(ctx, id);
   if (it->second.ptr) cudaFreeAsync(it->second.ptr, ctx->stream);
   ctx->packed.erase(it);
 }
@@ -242,6 +255,7 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
     if (e) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->read_events) cudaEventDestroy(e);
+  for (int* w : ctx->read_flags) cudaFreeHost(w);
   for (ReplayGraph& g : ctx->graphs)
     if (g.exec) {
       cudaGraphExecDestroy(g.exec);
@@ -410,7 +424,17 @@ int tfjs_cuda_upload(tfjs_cuda_ctx* ctx, const void* host, uint64_t nbytes, int3
     p = u.ptr;
   }
   cudaGetLastError();
-  if (!p) CUDA_TRY(ctx, cudaMallocAsync(&p, padded, ctx->copy_stream));
+  if (!p) {
+    cudaError_t e = cudaMallocAsync(&p, padded, ctx->copy_stream);
+    if (e == cudaErrorMemoryAllocation && ctx->cached_bytes) {
+      // the context itself may hold the memory: hand the cached blocks back and retry once
+      cudaGetLastError();
+      cache_flush(ctx);
+      cudaStreamSynchronize(ctx->stream);
+      e = cudaMallocAsync(&p, padded, ctx->copy_stream);
+    }
+    CUDA_TRY(ctx, e);
+  }
   if (nbytes)
     CUDA_TRY(ctx, cudaMemcpyAsync(p, host, nbytes, cudaMemcpyHostToDevice, ctx->copy_stream));
   cudaEvent_t ev = nullptr;
@@ -444,11 +468,21 @@ int tfjs_cuda_upload(tfjs_cuda_ctx* ctx, const void* host, uint64_t nbytes, int3
   return TFJS_CUDA_OK;
 }
 
-static int report_flag(tfjs_cuda_ctx* ctx) {
-  if (*ctx->h_flag != 0) {
-    int v = *ctx->h_flag;
-    *ctx->h_flag = 0;
-    cudaMemsetAsync(ctx->d_flag, 0, sizeof(int), ctx->stream);
+// The device error word is copied to a pinned word of the caller's (the context's for a
+// blocking sync, the ticket's for an asynchronous read) and cleared right behind the copy
+// in stream order, so each device-side timeout is seen by exactly one copy and reported
+// exactly once, by the wait that collects that copy.
+static int fetch_flag(tfjs_cuda_ctx* ctx, int* host_word) {
+  CUDA_TRY(ctx, cudaMemcpyAsync(host_word, ctx->d_flag, sizeof(int), cudaMemcpyDeviceToHost,
+                                ctx->stream));
+  CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_flag, 0, sizeof(int), ctx->stream));
+  return TFJS_CUDA_OK;
+}
+
+static int report_flag(tfjs_cuda_ctx* ctx, int* host_word) {
+  if (*host_word != 0) {
+    int v = *host_word;
+    *host_word = 0;
     // a K-split GEMM that gave up may have left partial-tile flags raised
     if (ctx->sk_flags) cudaMemsetAsync(ctx->sk_flags, 0, 4096 * sizeof(unsigned), ctx->stream);
     return ctx_fail(ctx, TFJS_CUDA_DEVICE_TIMEOUT,
@@ -462,10 +496,10 @@ int tfjs_cuda_sync(tfjs_cuda_ctx* ctx) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
   NOT_WHILE_CAPTURING(ctx, "a stream synchronisation");
   cudaSetDevice(ctx->device);
-  CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_flag, ctx->d_flag, sizeof(int),
-                                cudaMemcpyDeviceToHost, ctx->stream));
+  int rc = fetch_flag(ctx, ctx->h_flag);
+  if (rc) return rc;
   CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-  return report_flag(ctx);
+  return report_flag(ctx, ctx->h_flag);
 }
 
 int tfjs_cuda_read_async(tfjs_cuda_ctx* ctx, int32_t id, void* host,
@@ -491,20 +525,33 @@ int tfjs_cuda_read_begin(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nb
   *out_ticket = 0;
   int rc = tfjs_cuda_read_async(ctx, id, host, nbytes);
   if (rc) return rc;
-  // the device error word travels with every read, as it does with a blocking one
-  CUDA_TRY(ctx, cudaMemcpyAsync(ctx->h_flag, ctx->d_flag, sizeof(int),
-                                cudaMemcpyDeviceToHost, ctx->stream));
   int slot;
   if (!ctx->read_free.empty()) {
     slot = ctx->read_free.back();
     ctx->read_free.pop_back();
   } else {
     cudaEvent_t ev;
-    CUDA_TRY(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    int* word = nullptr;
+    CUDA_TRY(ctx, cudaMallocHost((void**)&word, sizeof(int)));
+    *word = 0;
+    cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+      cudaFreeHost(word);
+      return ctx_check(ctx, e, "cudaEventCreateWithFlags");
+    }
     ctx->read_events.push_back(ev);
+    ctx->read_flags.push_back(word);
     slot = (int)ctx->read_events.size() - 1;
   }
-  CUDA_TRY(ctx, cudaEventRecord(ctx->read_events[slot], ctx->stream));
+  // the device error word travels with every read, as it does with a blocking one, into
+  // a pinned word that belongs to this ticket
+  rc = fetch_flag(ctx, ctx->read_flags[slot]);
+  if (rc == TFJS_CUDA_OK) rc = ctx_check(ctx, cudaEventRecord(ctx->read_events[slot], ctx->stream),
+                                         "cudaEventRecord");
+  if (rc) {
+    ctx->read_free.push_back(slot);
+    return rc;
+  }
   *out_ticket = slot + 1;
   return TFJS_CUDA_OK;
 }
@@ -519,7 +566,7 @@ int tfjs_cuda_read_wait(tfjs_cuda_ctx* ctx, int32_t ticket) {
   cudaSetDevice(ctx->device);
   CUDA_TRY(ctx, cudaEventSynchronize(ctx->read_events[slot]));
   ctx->read_free.push_back(slot);
-  return report_flag(ctx);
+  return report_flag(ctx, ctx->read_flags[slot]);
 }
 
 int tfjs_cuda_read(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes) {
@@ -673,6 +720,8 @@ int tfjs_cuda_capture_begin(tfjs_cuda_ctx* ctx, uint64_t arena_bytes) {
   ctx->capturing = true;
   ctx->capture_failed = false;
   ctx->capture_launches0 = ctx->launches;
+  ctx->capture_packed.clear();
+  ctx->capture_scratch = false;
   return TFJS_CUDA_OK;
 }
 
@@ -708,6 +757,8 @@ int tfjs_cuda_capture_end(tfjs_cuda_ctx* ctx, int abandon, int32_t* out_graph) {
   g.arena = ctx->arena;
   g.arena_bytes = ctx->arena_bytes;
   g.launches = launches;
+  g.packed_ids.swap(ctx->capture_packed);
+  g.uses_scratch = ctx->capture_scratch;
   ctx->arena = nullptr;
   ctx->arena_free.clear();
   int slot = -1;
@@ -732,6 +783,11 @@ int tfjs_cuda_graph_launch(tfjs_cuda_ctx* ctx, int32_t graph) {
   NOT_WHILE_CAPTURING(ctx, "launching a captured step");
   ReplayGraph* g = graph_of(ctx, graph);
   if (!g) return ctx_fail(ctx, TFJS_CUDA_UNKNOWN_ID, "graph_launch: unknown graph %d", graph);
+  if (g->stale)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
+                    "graph_launch: graph %d is stale (a packed weight or the scratch buffer its "
+                    "kernels address was freed or re-allocated after the capture); capture the "
+                    "step again", graph);
   cudaSetDevice(ctx->device);
   CUDA_TRY(ctx, cudaGraphLaunch(g->exec, ctx->stream));
   ctx->launches += g->launches;

@@ -989,7 +989,7 @@ class GraphModel(object):
         on: copy the inputs into the captured input buffers, launch the graph, copy the
         outputs out.  A step that cannot be captured (a kernel that needs the host)
         stays eager."""
-        from ._cabi import CudaError
+        from ._cabi import CudaError, UNSUPPORTED
         be = self.engine.backend
         key = (tuple(sorted((n, tuple(t.shape), t.dtype) for n, t in inputs.items())),
                tuple(outputs))
@@ -1014,7 +1014,27 @@ class GraphModel(object):
             return self.executor.execute(inputs, outputs)
         for name, t in inputs.items():
             be.copy(t.dataId, st["fixed"][name].dataId)
-        be.graph_launch(st["graph"])
+        try:
+            be.graph_launch(st["graph"])
+        except CudaError as e:
+            if e.code != UNSUPPORTED:
+                raise
+            # the graph went stale (a weight it reads was freed or rewritten, or the
+            # library's scratch buffer moved): drop it, run this step eagerly, and let the
+            # next execute of this signature capture again
+            self._drop_replay(st)
+            again = st.get("recaptures", 0) + 1
+            st.clear()
+            # a step that keeps going stale is not worth capturing
+            st.update(state="warm" if again <= 3 else "eager", peak=0, recaptures=again,
+                      why="captured step went stale %d times" % again)
+            be.high_water_reset()
+            before = be.memory()["numBytesInGPU"]
+            res = self.executor.execute(inputs, outputs)
+            for t in res:
+                be.device_id(t.dataId)
+            st["peak"] = max(int(be.memory()["poolHighWater"] - before), 0)
+            return res
         res = []
         for o in st["outs"]:
             fresh = be.make_output(o.shape, o.dtype)
@@ -1051,14 +1071,17 @@ class GraphModel(object):
     def predict(self, inputs):
         return self.execute(inputs)
 
+    def _drop_replay(self, st):
+        if st.get("state") == "ready":
+            for t in st["outs"]:
+                t.dispose()
+            for t in st["fixed"].values():
+                t.dispose()
+            self.engine.backend.graph_destroy(st["graph"])
+
     def dispose(self):
         for st in self._replays.values():
-            if st.get("state") == "ready":
-                for t in st["outs"]:
-                    t.dispose()
-                for t in st["fixed"].values():
-                    t.dispose()
-                self.engine.backend.graph_destroy(st["graph"])
+            self._drop_replay(st)
         self._replays = {}
         for t in self.weights.values():
             t.dispose()
