@@ -116,20 +116,26 @@ static void cache_flush(tfjs_cuda_ctx* ctx) {
 
 // Pool allocation for tensors: exact-size cache first, then the stream-ordered pool;
 // on failure the cache is returned to the pool and the request retried once.
-// First-fit allocator over the arena of the step being captured.  The captured step is
+// Best-fit allocator over the arena of the step being captured.  The captured step is
 // one chain of graph nodes in launch order, so a span freed by the host may be handed
 // to a later node straight away, exactly like the stream-ordered blocks outside capture.
 static bool arena_alloc(tfjs_cuda_ctx* ctx, uint64_t padded, void** out) {
+  // best fit: the smallest free span that holds the request (a model's steps ask for a few
+  // distinct sizes over and over, so an exact-size hole is usually there to be found)
+  int best = -1;
   for (size_t i = 0; i < ctx->arena_free.size(); ++i) {
-    ArenaSpan& f = ctx->arena_free[i];
+    const ArenaSpan& f = ctx->arena_free[i];
     if (f.size < padded) continue;
-    *out = (char*)ctx->arena + f.off;
-    f.off += padded;
-    f.size -= padded;
-    if (f.size == 0) ctx->arena_free.erase(ctx->arena_free.begin() + i);
-    return true;
+    if (best < 0 || f.size < ctx->arena_free[best].size) best = (int)i;
+    if (f.size == padded) break;
   }
-  return false;
+  if (best < 0) return false;
+  ArenaSpan& f = ctx->arena_free[best];
+  *out = (char*)ctx->arena + f.off;
+  f.off += padded;
+  f.size -= padded;
+  if (f.size == 0) ctx->arena_free.erase(ctx->arena_free.begin() + best);
+  return true;
 }
 
 static void arena_release(tfjs_cuda_ctx* ctx, void* p, uint64_t padded) {

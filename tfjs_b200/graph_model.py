@@ -1008,7 +1008,13 @@ class GraphModel(object):
                 self._capture(st, inputs, outputs)
                 st["state"] = "ready"
             except CudaError as e:
-                st["state"] = "eager"
+                if "arena" in str(e) and st.get("arena_retries", 0) < 2:
+                    # the arena (sized from the eager step's peak) fragmented: this step runs
+                    # eagerly and the next one captures with more room
+                    st["arena_retries"] = st.get("arena_retries", 0) + 1
+                    st["peak"] = int(st["peak"] * 1.6) + (64 << 20)
+                else:
+                    st["state"] = "eager"
                 st["why"] = str(e)
         if st["state"] != "ready":
             return self.executor.execute(inputs, outputs)

@@ -47,6 +47,38 @@ def bind_to_gpu_cpus(device_ordinal):
         return None
 
 
+def sharded_execute(engine, build_model, feeds, output, group, replay=False):
+    """One model call on a batch split over the group's replicas, the way the path is
+    meant to span GPUs: rank r takes the contiguous ceil(B / world) slice
+    `shard_range(B, world, r)` of every input (axis 0), builds the model for that many
+    units (`build_model(units) -> (model_json, weight_bytes)`; every replica holds its own
+    copy of the weights), executes it on its own backend, reads the result back and rank 0
+    concatenates the slices in rank order (None on the other ranks).  No device-to-device
+    traffic: each Engine has one backend, and tensors move between backends through the
+    host (tfjs-core/src/engine.ts:424-439)."""
+    from .graph_model import GraphModel
+    total = int(next(iter(feeds.values())).shape[0])
+    lo, hi = shard_range(total, group.world, group.rank)
+    if hi == lo:
+        return group.gather_to_root(np.zeros((0,), np.float32))
+    model_json, weights = build_model(hi - lo)
+    gm = GraphModel(model_json, weights, engine, replay=replay)
+    ins = {}
+    try:
+        for name, v in feeds.items():
+            part = np.ascontiguousarray(v[lo:hi])
+            ins[name] = engine.make_tensor(part, list(part.shape),
+                                           "int32" if part.dtype == np.int32 else "float32")
+        y = gm.execute(ins, [output])[0]
+        local = y.arraySync()
+        y.dispose()
+    finally:
+        for t in ins.values():
+            t.dispose()
+        gm.dispose()
+    return group.gather_to_root(local)
+
+
 class ReplicaGroup(object):
     def __init__(self, rank=None, world=None):
         self.rank = int(os.environ.get("RANK", "0")) if rank is None else rank
