@@ -435,6 +435,14 @@ NCU_TRAFFIC = {
         ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 25, 5180641536),
     "mobilenet_v2_1.0_224_b256_graphmodel/FusedDepthwiseConv2D":
         ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 17, 6286064640),
+    "resnet50_v1.5_224_b128_uint8weights_graphmodel/FusedConv2D":
+        ("profiles/bench_dram_traffic_resnet50_b128.md", 37, 6562264832),
+    "resnet50_v1.5_224_b128_uint8weights_graphmodel/FusedConv2D+Add+Relu":
+        ("profiles/bench_dram_traffic_resnet50_b128.md", 16, 6475964416),
+    "bert_base_encoder_seq128_b64_graph/_FusedMatMul":
+        ("profiles/bench_dram_traffic_bert_base_b64.md", 36, 3173843968),
+    "bert_base_encoder_seq128_b64_graph/_MatMulHeads":
+        ("profiles/bench_dram_traffic_bert_base_b64.md", 48, 1899865856),
 }
 
 

@@ -270,38 +270,75 @@ EXACT_UNARY = ["relu", "relu6", "sqrt", "square", "neg", "abs"]
 DOUBLE_UNARY = ["elu", "sigmoid", "exp", "rsqrt", "tanh", "erf", "log"]
 
 
+def _in_mode(engine, mode, case):
+    """Runs a case with the backend in math mode 'fp32' (the reference's double-precision
+    evaluation order, fp32 store) or 'tf32' (the default: fp32 evaluations of exp / erf /
+    tanh and an fp32 softmax sum)."""
+    engine.backend.set_math_mode(mode)
+    try:
+        return opcases.run_cuda(case)
+    finally:
+        engine.backend.set_math_mode("tf32")
+
+
+# Bounds of the default mode's fp32 evaluations against the double-precision oracle: a few
+# units in the last place for exp / sigmoid / tanh / elu; erf is the reference's polynomial
+# in fp32, whose cancellation near zero leaves an absolute error.
+FP32_EVAL_REL = 6e-7
+FP32_ERF_ABS = 5e-7
+
+
+@pytest.mark.parametrize("mode", ["fp32", "tf32"])
 @pytest.mark.parametrize("op", EXACT_UNARY + DOUBLE_UNARY)
-def test_unary(cuda_engine, op):
+def test_unary(cuda_engine, op, mode):
     x = f32(rng(5).standard_normal(100003) * 3)
     if op in ("sqrt", "rsqrt", "log"):
         x = np.abs(x) + 1e-3
     x[:4] = [np.nan, 0.0, -0.0, np.inf]
     case = {"op": op, "inputs": {"x": x}}
-    got, ref = opcases.run_cuda(case), opcases.run_oracle(case)
+    got, ref = _in_mode(cuda_engine, mode, case), opcases.run_oracle(case)
     if op in EXACT_UNARY:
         assert np.array_equal(got, ref, equal_nan=True)
     else:
         ok = np.isfinite(ref)
         assert np.array_equal(np.isnan(got), np.isnan(ref))
-        # device and host libm may differ in the last bit of the double result
-        assert np.max(np.abs(got[ok] - ref[ok]) / np.maximum(np.abs(ref[ok]), 1e-30)) <= 2.5e-7
+        if mode == "tf32" and op == "erf":
+            assert np.max(np.abs(got[ok] - ref[ok])) <= FP32_ERF_ABS
+            return
+        # fp32 mode: device and host libm may differ in the last bit of the double result
+        bound = 2.5e-7 if mode == "fp32" else FP32_EVAL_REL
+        assert np.max(np.abs(got[ok] - ref[ok]) / np.maximum(np.abs(ref[ok]), 1e-30)) <= bound
 
 
+@pytest.mark.parametrize("mode", ["fp32", "tf32"])
 @pytest.mark.parametrize("op", ["erf", "exp", "sigmoid"])
-def test_unary_wide_range(cuda_engine, op):
-    """Magnitudes from 1e-9 to beyond the range where exp over- or underflows: the device
-    evaluates erf and exp with a shortened double sequence except near zero (erf) and
-    beyond +-700 (exp)."""
+def test_unary_wide_range(cuda_engine, op, mode):
+    """Magnitudes from 1e-9 to beyond the range where exp over- or underflows.  fp32 mode:
+    the device evaluates erf and exp with a shortened double sequence except near zero
+    (erf) and beyond +-700 (exp).  tf32 mode: fp32 evaluations; results below the smallest
+    normal fp32 number may flush to zero."""
     r = rng(55)
     mag = 10.0 ** r.uniform(-9, 1.6 if op == "erf" else 2.0, 200000)
     x = f32(mag * np.where(r.random(200000) < 0.5, -1.0, 1.0))
     x[:8] = [np.nan, 0.0, -0.0, np.inf, -np.inf, 2.0 ** -13, -2.0 ** -13, 88.0]
     case = {"op": op, "inputs": {"x": x}}
     with np.errstate(over="ignore"):
-        got, ref = opcases.run_cuda(case), opcases.run_oracle(case)
+        got, ref = _in_mode(cuda_engine, mode, case), opcases.run_oracle(case)
     assert np.array_equal(np.isnan(got), np.isnan(ref))
-    assert np.array_equal(np.isinf(got), np.isinf(ref))
     ok = np.isfinite(ref)
+    if mode == "tf32":
+        err = np.abs(got[ok].astype(np.float64) - ref[ok])
+        if op == "erf":
+            assert np.max(err) <= FP32_ERF_ABS
+            assert np.array_equal(np.signbit(got[ok]), np.signbit(ref[ok]))
+        else:
+            # relative, with an absolute floor at the fp32 normal limit; an overflow to
+            # infinity may come one ulp of the argument early or late
+            assert np.max(err[np.isfinite(got[ok])] /
+                          (np.abs(ref[ok][np.isfinite(got[ok])]) + 2e-38)) <= FP32_EVAL_REL
+            assert np.all(np.abs(ref[ok][np.isinf(got[ok])]) > 3e38)
+        return
+    assert np.array_equal(np.isinf(got), np.isinf(ref))
     assert np.array_equal(np.signbit(got[ok]), np.signbit(ref[ok]))
     assert np.max(np.abs(got[ok] - ref[ok]) / np.maximum(np.abs(ref[ok]), 1e-37)) <= 2.5e-7
     # the shortened sequence changes the rounding of very few results
@@ -366,11 +403,14 @@ def test_prelu_and_batchnorm(cuda_engine):
 
 # --------------------------------------------------------------- reductions --
 @pytest.mark.parametrize("shape", [(64, 12, 16, 128), (70, 1000), (3, 2500), (5, 1)])
-def test_softmax(cuda_engine, shape):
+@pytest.mark.parametrize("mode", ["fp32", "tf32"])
+def test_softmax(cuda_engine, shape, mode):
     x = f32(rng(10).standard_normal(shape) * 4)
     case = {"op": "softmax", "inputs": {"logits": x}}
-    got, ref = opcases.run_cuda(case), opcases.run_oracle(case)
-    assert np.max(np.abs(got - ref)) <= 1.5e-7, np.max(np.abs(got - ref))
+    got, ref = _in_mode(cuda_engine, mode, case), opcases.run_oracle(case)
+    # fp32 mode: double sum as the reference; tf32 mode: expf and an fp32 sum
+    bound = 1.5e-7 if mode == "fp32" else 1e-6
+    assert np.max(np.abs(got - ref)) <= bound, np.max(np.abs(got - ref))
 
 
 @pytest.mark.parametrize("op", ["sum", "mean", "max"])

@@ -258,6 +258,51 @@ __device__ __forceinline__ float js_erf(float x) {
   return r;
 }
 
+// ---- fp32 forms of the transcendental kernels (default math mode) -------------------
+// The reference evaluates exp / erf / tanh in JavaScript doubles and stores fp32; the
+// sequences above reproduce that to the last bit or so, at the price of the double-precision
+// pipe.  The contract for floating-point kernels is a tolerance (2e-3 * max|ref| per layer
+// with TF32 tensor-core inputs), so in the TF32 math mode these kernels evaluate in fp32:
+// the CUDA library's expf / tanhf / expm1f (at most 2 ulp) and the reference's own erf
+// polynomial (tfjs-core/src/ops/erf_util.ts:18-23) with fp32 coefficients, whose result is
+// within 5e-7 absolute of the double evaluation.  TFJS_CUDA_MATH_FP32 keeps the double
+// sequences.  The op numbers below are internal (the launchers substitute them for the
+// public ones); every kernel that evaluates such an op, alone or inside a chain, calls the
+// same device function, so fused and separate launches still agree bit for bit.
+enum {
+  TFJS_CUDA_EXP_F32 = 15,
+  TFJS_CUDA_ERF_F32 = 16,
+  TFJS_CUDA_SIGMOID_F32 = 17,
+  TFJS_CUDA_TANH_F32 = 18,
+  TFJS_CUDA_ELU_F32 = 19,
+  TFJS_CUDA_UNARY_OPS_END = 20
+};
+static inline int fast_unary_op(int op) {
+  switch (op) {
+    case TFJS_CUDA_EXP: return TFJS_CUDA_EXP_F32;
+    case TFJS_CUDA_ERF: return TFJS_CUDA_ERF_F32;
+    case TFJS_CUDA_SIGMOID: return TFJS_CUDA_SIGMOID_F32;
+    case TFJS_CUDA_TANH: return TFJS_CUDA_TANH_F32;
+    case TFJS_CUDA_ELU: return TFJS_CUDA_ELU_F32;
+    default: return op;
+  }
+}
+__device__ __forceinline__ float erf_f32(float x) {
+  const float ax = fabsf(x);
+  const float t = __frcp_rn(__fmaf_rn(0.3275911f, ax, 1.0f));
+  float q = __fmaf_rn(1.061405429f, t, -1.453152027f);
+  q = __fmaf_rn(q, t, 1.421413741f);
+  q = __fmaf_rn(q, t, -0.284496736f);
+  q = __fmaf_rn(q, t, 0.254829592f);
+  q = __fmul_rn(q, t);
+  const float r = __fmaf_rn(-q, expf(-__fmul_rn(ax, ax)), 1.0f);
+  return x == 0.0f ? x : copysignf(r, x);   // sign(0) * anything = 0 in the reference
+}
+__device__ __forceinline__ float sigmoid_f32(float x) {
+  return __frcp_rn(__fadd_rn(1.0f, expf(-x)));
+}
+__device__ __forceinline__ float elu_f32(float x) { return x >= 0.0f ? x : expm1f(x); }
+
 __device__ __forceinline__ float js_relu(float v) {
   return v > 0.0f ? v : (v != v ? v : 0.0f);
 }

@@ -40,6 +40,11 @@ __device__ __forceinline__ float unary_eval(float x, double p0, double p1) {
   if (OP == TFJS_CUDA_ERF) return js_erf(x);
   if (OP == TFJS_CUDA_ABS) return fabsf(x);
   if (OP == TFJS_CUDA_LOG) return (float)log((double)x);
+  if (OP == TFJS_CUDA_EXP_F32) return expf(x);
+  if (OP == TFJS_CUDA_ERF_F32) return erf_f32(x);
+  if (OP == TFJS_CUDA_SIGMOID_F32) return sigmoid_f32(x);
+  if (OP == TFJS_CUDA_TANH_F32) return tanhf(x);
+  if (OP == TFJS_CUDA_ELU_F32) return elu_f32(x);
   return x;
 }
 
@@ -255,6 +260,11 @@ __device__ __forceinline__ void ew_eval(int code, const float* a, const float* b
     EW_UN(TFJS_CUDA_NEG)
     EW_UN(TFJS_CUDA_ABS)
     EW_UN(TFJS_CUDA_LOG)
+    EW_UN(TFJS_CUDA_EXP_F32)
+    EW_UN(TFJS_CUDA_ERF_F32)
+    EW_UN(TFJS_CUDA_SIGMOID_F32)
+    EW_UN(TFJS_CUDA_TANH_F32)
+    EW_UN(TFJS_CUDA_ELU_F32)
     case TFJS_CUDA_EW_UNARY + TFJS_CUDA_ERF:
       js_erf_vec<V>(a, r);
       break;
@@ -652,6 +662,22 @@ struct ProgGeluErfDiv {  // (x * 0.5) * (erf(x / c) + 1)
     return t[j];
   }
 };
+struct ProgGeluErfF32 {  // the same chain with the fp32 erf (TF32 math mode)
+  static constexpr int n_in = 4, n_ops = 5;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[5] = {EW_B(MUL, 0, 1), EW_U(ERF_F32, 4), EW_B(ADD, 5, 2),
+                                      EW_B(MUL, 0, 3), EW_B(MUL, 6, 7)};
+    return t[j];
+  }
+};
+struct ProgGeluErfDivF32 {
+  static constexpr int n_in = 4, n_ops = 5;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[5] = {EW_B(DIV, 0, 1), EW_U(ERF_F32, 4), EW_B(ADD, 5, 2),
+                                      EW_B(MUL, 0, 3), EW_B(MUL, 6, 7)};
+    return t[j];
+  }
+};
 struct ProgScaleShift {  // x * a + b (attention scores * scale + mask, affine maps)
   static constexpr int n_in = 3, n_ops = 2;
   __host__ __device__ static constexpr StaticOp op(int j) {
@@ -764,6 +790,8 @@ static bool ew_launch_catalogued(tfjs_cuda_ctx* ctx, const EwArgs& g, bool vec,
   EW_TRY(ProgLayerNormTailBn)
   EW_TRY(ProgGeluErf)
   EW_TRY(ProgGeluErfDiv)
+  EW_TRY(ProgGeluErfF32)
+  EW_TRY(ProgGeluErfDivF32)
   EW_TRY(ProgScaleShift)
   EW_TRY(ProgAddAdd)
 #undef EW_TRY
@@ -784,12 +812,18 @@ int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int32_t op, double p0, double p1,
   const unsigned grid = grid_for((n + 3) / 4, kThreads, ctx->sm_count);
   const float* xp = (const float*)x->ptr;
   float* yp = (float*)y->ptr;
+  if (op < 0 || op > TFJS_CUDA_LOG)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "unary: unknown op %d", op);
+  // the default math mode evaluates exp / erf / sigmoid / tanh / elu in fp32
+  if (ctx->math_mode == TFJS_CUDA_MATH_TF32) op = fast_unary_op(op);
 #define UN(OP) case OP: unary_kernel<OP><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, n, p0, p1); break;
   switch (op) {
     UN(TFJS_CUDA_RELU) UN(TFJS_CUDA_RELU6) UN(TFJS_CUDA_ELU) UN(TFJS_CUDA_SIGMOID)
     UN(TFJS_CUDA_LEAKYRELU) UN(TFJS_CUDA_EXP) UN(TFJS_CUDA_SQRT) UN(TFJS_CUDA_RSQRT)
     UN(TFJS_CUDA_SQUARE) UN(TFJS_CUDA_TANH) UN(TFJS_CUDA_NEG) UN(TFJS_CUDA_CLIP)
     UN(TFJS_CUDA_ERF) UN(TFJS_CUDA_ABS) UN(TFJS_CUDA_LOG)
+    UN(TFJS_CUDA_EXP_F32) UN(TFJS_CUDA_ERF_F32) UN(TFJS_CUDA_SIGMOID_F32)
+    UN(TFJS_CUDA_TANH_F32) UN(TFJS_CUDA_ELU_F32)
     default: return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "unary: unknown op %d", op);
   }
 #undef UN
@@ -1010,7 +1044,11 @@ int tfjs_cuda_fused_elementwise(tfjs_cuda_ctx* ctx, const tfjs_cuda_ew_program* 
     if (!known || op.a >= limit || (!unary && op.b >= limit))
       return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "fused_elementwise: op %d is malformed", j);
     g.ops[j] = op;
-    if (unary) g.ops[j].b = op.a;
+    if (unary) {
+      g.ops[j].b = op.a;
+      if (ctx->math_mode == TFJS_CUDA_MATH_TF32)
+        g.ops[j].opcode = (int16_t)(TFJS_CUDA_EW_UNARY + fast_unary_op(code));
+    }
   }
   Buffer* o;
   if ((rc = ctx_get(ctx, out_id, p->n * 4, "fused_elementwise out", &o))) return rc;
@@ -1046,7 +1084,15 @@ int tfjs_cuda_fused_elementwise_catalogued(tfjs_cuda_ctx* ctx, const tfjs_cuda_e
   g.n_ops = p->n_ops;
   for (int j = 0; j < p->n_ops; ++j) {
     g.ops[j] = p->ops[j];
-    if (g.ops[j].opcode >= TFJS_CUDA_EW_UNARY) g.ops[j].b = g.ops[j].a;
+    if (g.ops[j].opcode >= TFJS_CUDA_EW_UNARY) {
+      g.ops[j].b = g.ops[j].a;
+      // every catalogued chain with a transcendental op exists in both forms, so the answer
+      // does not depend on the math mode in force
+      if (ctx->math_mode == TFJS_CUDA_MATH_TF32 &&
+          g.ops[j].opcode <= TFJS_CUDA_EW_UNARY + TFJS_CUDA_LOG)
+        g.ops[j].opcode = (int16_t)(TFJS_CUDA_EW_UNARY +
+                                    fast_unary_op(g.ops[j].opcode - TFJS_CUDA_EW_UNARY));
+    }
   }
   *out_yes = ew_launch_catalogued(ctx, g, true, true) ? 1 : 0;
   return TFJS_CUDA_OK;

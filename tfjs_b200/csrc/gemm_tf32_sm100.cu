@@ -167,20 +167,13 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, 
   }
   if (ACT == TFJS_CUDA_ACT_LINEAR) return;
   if (ACT == TFJS_CUDA_ACT_GELU_ERF) {
-    // four independent erf evaluations at a time: each is a chain of ~40 dependent
-    // double operations, and the two epilogue warps of a scheduler have nothing else
-    // to fill its slots with
+    // the tensor-core kernels run in the TF32 math mode only, where erf is the fp32 form
+    // (the same device function as the separate Erf kernel and the chain kernels)
 #pragma unroll
-    for (int j0 = 0; j0 < 32; j0 += 4) {
-      float a[4], e[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        a[u] = g.ap.gelu_divide ? __fdiv_rn(v[j0 + u], g.ap.gelu_scale)
-                                : __fmul_rn(v[j0 + u], g.ap.gelu_scale);
-      js_erf_vec<4>(a, e);
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        v[j0 + u] = __fmul_rn(__fmul_rn(v[j0 + u], g.ap.gelu_half), __fadd_rn(e[u], g.ap.gelu_one));
+    for (int j = 0; j < 32; ++j) {
+      const float a = g.ap.gelu_divide ? __fdiv_rn(v[j], g.ap.gelu_scale)
+                                       : __fmul_rn(v[j], g.ap.gelu_scale);
+      v[j] = __fmul_rn(__fmul_rn(v[j], g.ap.gelu_half), __fadd_rn(erf_f32(a), g.ap.gelu_one));
     }
     return;
   }
@@ -199,9 +192,9 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, 
     } else if (ACT == TFJS_CUDA_ACT_LEAKYRELU) {
       v[j] = js_leakyrelu(t, g.ap.alpha);
     } else if (ACT == TFJS_CUDA_ACT_SIGMOID) {
-      v[j] = js_sigmoid(t);
+      v[j] = sigmoid_f32(t);
     } else if (ACT == TFJS_CUDA_ACT_ELU) {
-      v[j] = js_elu(t);
+      v[j] = elu_f32(t);
     }
   }
 }

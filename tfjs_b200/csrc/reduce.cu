@@ -50,7 +50,15 @@ __device__ __forceinline__ float softmax_logit(const SoftmaxPrologue& pg, const 
   return v;
 }
 
-template <int REGS>
+// FAST (the TF32 math mode): e = expf(a), the sum in fp32 (lanes, then a shuffle tree) and
+// a multiplication by its reciprocal; relative error of a result below 1e-6.
+__device__ __forceinline__ float warp_sum_f32(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int REGS, bool FAST>
 __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ y,
                                uint64_t rows, uint32_t cols, SoftmaxPrologue pg) {
   const int lane = threadIdx.x & 31;
@@ -93,6 +101,23 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
       for (int j = 0; j < R; ++j)
         if (lane + 32 * j < cols) m = nan_max(m, v[j]);
       m = warp_nan_max(m);
+      if (FAST) {
+        float s = 0.0f;
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          if (lane + 32 * j < cols) {
+            v[j] = expf(__fsub_rn(v[j], m));
+            s = __fadd_rn(s, v[j]);
+          }
+        }
+        const float inv = __frcp_rn(warp_sum_f32(s));
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          const uint32_t c = lane + 32 * j;
+          if (c < cols) yr[c] = __fmul_rn(v[j], inv);
+        }
+        continue;
+      }
       double s = 0.0;
 #pragma unroll
       for (int j = 0; j < R; ++j) {
@@ -118,6 +143,17 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
     {
       for (uint32_t c = lane; c < cols; c += 32) m = nan_max(m, softmax_logit(pg, mrow, xr[c], c));
       m = warp_nan_max(m);
+      if (FAST) {
+        float s = 0.0f;
+        for (uint32_t c = lane; c < cols; c += 32) {
+          const float e = expf(__fsub_rn(softmax_logit(pg, mrow, xr[c], c), m));
+          yr[c] = e;
+          s = __fadd_rn(s, e);
+        }
+        const float inv = __frcp_rn(warp_sum_f32(s));
+        for (uint32_t c = lane; c < cols; c += 32) yr[c] = __fmul_rn(yr[c], inv);
+        continue;
+      }
       double s = 0.0;
       for (uint32_t c = lane; c < cols; c += 32) {
         const float e = (float)exp_fast((double)__fsub_rn(softmax_logit(pg, mrow, xr[c], c), m));
@@ -391,7 +427,12 @@ static int softmax_impl(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows, uint64_
   const float* xp = (const float*)x->ptr;
   float* yp = (float*)y->ptr;
   const uint32_t c32 = (uint32_t)cols;
-#define SOFTMAX(R) softmax_kernel<R><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32, pg)
+  const bool fast = ctx->math_mode == TFJS_CUDA_MATH_TF32;
+#define SOFTMAX(R)                                                                          \
+  do {                                                                                      \
+    if (fast) softmax_kernel<R, true><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32, pg); \
+    else softmax_kernel<R, false><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32, pg);     \
+  } while (0)
   if (cols <= 32) SOFTMAX(1);
   else if (cols <= 64) SOFTMAX(2);
   else if (cols <= 128) SOFTMAX(4);
