@@ -135,6 +135,14 @@ int tfjs_cuda_event_elapsed(tfjs_cuda_ctx* ctx, int32_t slot_begin, int32_t slot
 int tfjs_cuda_set_math_mode(tfjs_cuda_ctx* ctx, int mode);
 /* Number of this library's kernels launched on the context so far. */
 int tfjs_cuda_launch_count(tfjs_cuda_ctx* ctx, uint64_t* out_launches);
+/* BackendTimingInfo.getExtraProfileInfo (tfjs-core/src/backends/backend.ts:26-30, printed
+ * per kernel by tfjs-core/src/profiler.ts:74-76): while the log is on, the library notes
+ * the name of every kernel instantiation it launches; launch_log_take writes them to `buf`
+ * as text ("pack_weight_kernel, gemm_tf32_kernel<BN=256,...> x2", cut to cap - 1
+ * characters), reports how many there were and empties the log. */
+int tfjs_cuda_launch_log(tfjs_cuda_ctx* ctx, int32_t enable);
+int tfjs_cuda_launch_log_take(tfjs_cuda_ctx* ctx, char* buf, uint64_t cap,
+                              uint32_t* out_launches);
 /* Clears L2 by overwriting a scratch buffer larger than it (benchmark hygiene). */
 int tfjs_cuda_flush_l2(tfjs_cuda_ctx* ctx);
 
@@ -448,6 +456,20 @@ int tfjs_cuda_batchnorm(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t n,
                         int32_t offset_id, uint64_t n_offset, double epsilon,
                         int32_t out_id);
 
+/* FusedBatchNorm on a [rows, cols] view of x whose parameters are rows or columns of that
+ * view and need not be tiled to its shape first: tfjs-layers' LayerNormalization computes
+ * the moments per row, tiles them and gamma / beta to the input's shape and calls batchNorm
+ * on the tiles (tfjs-layers/src/layers/normalization.ts:578-622); the host layer keeps those
+ * Tile results unmaterialised and passes the untiled tensors here.  Same arithmetic as
+ * tfjs_cuda_batchnorm (BatchNorm.ts:69-87).  Modes: 0 absent (scale and offset only), 1 one
+ * value per column (cols values), 2 one per row (rows values), 3 one per element, 4 one
+ * value in all. */
+int tfjs_cuda_batchnorm_rows(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows, uint64_t cols,
+                             int32_t mean_id, int32_t mean_mode, int32_t var_id,
+                             int32_t var_mode, int32_t scale_id, int32_t scale_mode,
+                             int32_t offset_id, int32_t offset_mode, double epsilon,
+                             int32_t out_id);
+
 /* ---- weight dequantisation at load: tfjs-core/src/io/io_utils.ts:221-227
  * (float32 target) and :243-247 (int32 target).  q_dtype_bytes is 1 (uint8) or 2
  * (uint16).  The 256/65536-entry table fl32(v*scale+min) is built on the host in
@@ -461,6 +483,52 @@ int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_dtype_bytes,
  * values (raw uint16 bits in q) to float32, on the device, so such weights cross PCIe at two
  * bytes per value. */
 int tfjs_cuda_decode_float16(tfjs_cuda_ctx* ctx, int32_t q_id, uint64_t n, int32_t out_id);
+
+/* ---- weight loading: decodeWeights / decodeWeight (tfjs-core/src/io/io_utils.ts:119-135,
+ * :185-292), decodeWeightsStream (:316-353) and the shard fetching of
+ * tfjs-core/src/io/weights_loader.ts:38-131, behind the C ABI.  The caller lists the
+ * manifest entries in order (WeightsManifestEntry, tfjs-core/src/io/types.ts:76-110) and
+ * pushes the concatenated weight bytes in pieces of any size, cut anywhere: whole shards,
+ * shard files by path, or the chunks of a stream.  Pieces are staged through a ring of
+ * pinned host slots and copied with one cudaMemcpyAsync each on the copy stream while the
+ * next slot is being filled (straight from the file for push_file); quantised and
+ * float16-stored tensors are decoded on the device as soon as their bytes have been queued
+ * (same kernels and results, bit for bit, as tfjs_cuda_dequantize / tfjs_cuda_decode_float16).
+ *   storage RAW      the bytes are the tensor's own dtype (float32 / int32: 4 bytes per
+ *                    element, bool: 1)
+ *   storage UINT8 / UINT16  affine quantisation: value = q * scale + min, rounded as
+ *                    io_utils.ts:221-227 (float32) or :243-247 (int32)
+ *   storage FLOAT16  half-precision bits widened exactly (io_utils.ts:228-231)
+ *   skip != 0        the entry's bytes are passed over and no tensor is made (its id is 0):
+ *                    for entries the host keeps itself, such as the small shape / axis
+ *                    constants a graph executor reads on the host
+ * weights_end checks that exactly the bytes of all entries were pushed, waits for the
+ * copies and returns one tensor id per entry, in manifest order (the decode kernels may
+ * still be running; stream order covers their consumers).  out_ids == NULL abandons the
+ * load and frees what it made; so does any failing push followed by weights_end. */
+enum tfjs_cuda_weight_storage {
+  TFJS_CUDA_STORED_RAW = 0,
+  TFJS_CUDA_STORED_UINT8 = 1,
+  TFJS_CUDA_STORED_UINT16 = 2,
+  TFJS_CUDA_STORED_FLOAT16 = 3
+};
+typedef struct tfjs_cuda_weight_spec {
+  uint64_t n;        /* elements */
+  int32_t storage;   /* tfjs_cuda_weight_storage */
+  int32_t dtype;     /* tfjs_cuda_dtype of the decoded tensor */
+  double scale, min; /* UINT8 / UINT16 storage */
+  int32_t skip;
+  int32_t reserved;
+} tfjs_cuda_weight_spec;
+int tfjs_cuda_weights_begin(tfjs_cuda_ctx* ctx, const tfjs_cuda_weight_spec* specs,
+                            int32_t n_specs, int32_t* out_loader);
+int tfjs_cuda_weights_push(tfjs_cuda_ctx* ctx, int32_t loader, const void* bytes,
+                           uint64_t nbytes);
+/* The whole file at `path` (one shard of weightsManifest[].paths), read with pread
+ * directly into the pinned ring. */
+int tfjs_cuda_weights_push_file(tfjs_cuda_ctx* ctx, int32_t loader, const char* path);
+int tfjs_cuda_weights_end(tfjs_cuda_ctx* ctx, int32_t loader, int32_t* out_ids,
+                          uint64_t* out_bytes);
 
 /* ---- tfjs_cuda_dequantize for callers that must not allocate device memory.
  * No counterpart in the reference; it exists for hosts that load weights while

@@ -249,15 +249,44 @@ def test_profile_names_folded_launches(cuda_engine):
         y2 = tf.fused_conv2d(xt, ft, 1, "same", bias=bt)
         m = tf.mul(y2, sc)
         m.dataSync()                  # launches the convolution, then the multiply
+        r.dataSync()                  # launches the convolution with the Add and the Relu
         for t in (y, s, y2):
             t.dispose()
         return r, m
     prof = cuda_engine.profile(run)
     names = [k["name"] for k in prof["kernels"] if not k["deferred"]]
-    assert names == ["FusedConv2D+Add+Relu", "FusedConv2D", "Multiply"], names
+    assert names == ["FusedConv2D", "Multiply", "FusedConv2D+Add+Relu"], names
     assert all(k["kernelTimeMs"] >= 0 for k in prof["kernels"])
+    # the extra information of a record names the kernel instantiations it launched
+    # (BackendTimingInfo.getExtraProfileInfo); deferred records launched nothing themselves
+    launched = {k["name"]: k["extraInfo"] for k in prof["kernels"] if not k["deferred"]}
+    assert "RES=1" in launched["FusedConv2D+Add+Relu"] and "gemm_tf32_kernel<" in launched["FusedConv2D"]
+    assert "RES=0" in launched["FusedConv2D"]
+    assert all(k["extraInfo"] == "" for k in prof["kernels"] if k["deferred"])
     for t in prof["result"] + (xt, ft, bt, sc):
         t.dispose()
+
+
+def test_time_reports_kernel_ms_and_extra_profile_info(cuda_engine):
+    """backend.time(f) is a BackendTimingInfo: kernelMs from CUDA events and
+    getExtraProfileInfo() naming what ran."""
+    from tfjs_b200 import ops as tf
+    a = tf.tensor(np.ones((512, 512), np.float32))
+
+    def work():
+        b = tf.mat_mul(a, a)
+        c = tf.softmax(b)
+        c.dataSync()
+        b.dispose()
+        c.dispose()
+    info = cuda_engine.backend.time(work)
+    assert info["kernelMs"] > 0 and info["wallMs"] >= info["kernelMs"] * 0.5
+    text = info["getExtraProfileInfo"]()
+    assert "gemm_tf32_kernel<" in text and "softmax_kernel" in text
+    # the log is off again: nothing accumulates outside time() / profile()
+    tf.relu(a).dispose()
+    assert cuda_engine.backend.launch_log_take() == ""
+    a.dispose()
 
 
 def test_residual_entry_point_rejects_bad_arguments(cuda_engine):

@@ -265,3 +265,30 @@ def test_erf_gelu_after_a_dense_layer_becomes_its_epilogue():
     _, n = G.fuse_gelu_into_matmul(nodes + [tap], lambda x: x in consts,
                                    lambda x: consts[x].reshape(-1))
     assert n == 11
+
+
+def test_manifest_entry_checks_follow_decode_weight():
+    """The loader's per-entry validation (storage kind, element count, stored bytes) and
+    the reference's error cases (tfjs-core/src/io/io_utils.ts:196-218, :269-272)."""
+    from tfjs_b200 import _cabi, io
+    e = io._entry({"name": "w", "shape": [3, 4], "dtype": "float32"})
+    assert e == (_cabi.STORED_RAW, "float32", 12, 48)
+    e = io._entry({"name": "w", "shape": [5], "dtype": "bool"})
+    assert e == (_cabi.STORED_RAW, "bool", 5, 5)
+    e = io._entry({"name": "w", "shape": [2, 5], "dtype": "int32",
+                   "quantization": {"dtype": "uint16", "scale": 1.0, "min": 0.0}})
+    assert e == (_cabi.STORED_UINT16, "int32", 10, 20)
+    e = io._entry({"name": "w", "shape": [7], "dtype": "float32", "quantization": {"dtype": "float16"}})
+    assert e == (_cabi.STORED_FLOAT16, "float32", 7, 14)
+    import pytest
+    with pytest.raises(ValueError, match="doesn't have corresponding metadata"):
+        io._entry({"name": "w", "shape": [1], "dtype": "float32", "quantization": {"dtype": "uint8"}})
+    with pytest.raises(ValueError, match="only supports weights of type float32"):
+        io._entry({"name": "w", "shape": [1], "dtype": "int32", "quantization": {"dtype": "float16"}})
+    with pytest.raises(ValueError, match="unknown quantization dtype"):
+        io._entry({"name": "w", "shape": [1], "dtype": "float32",
+                   "quantization": {"dtype": "uint4", "scale": 1, "min": 0}})
+    with pytest.raises(ValueError, match="string weights"):
+        io._entry({"name": "w", "shape": [1], "dtype": "string"})
+    with pytest.raises(ValueError, match="Unsupported dtype"):
+        io._entry({"name": "w", "shape": [1], "dtype": "complex64"})

@@ -60,6 +60,14 @@ class MatMulParams(Structure):
             ("gelu_one", c_float), ("gelu_divide", c_int32)]
 
 
+STORED_RAW, STORED_UINT8, STORED_UINT16, STORED_FLOAT16 = 0, 1, 2, 3
+
+
+class WeightSpec(Structure):
+    _fields_ = [("n", c_uint64), ("storage", c_int32), ("dtype", c_int32), ("scale", c_double),
+                ("min", c_double), ("skip", c_int32), ("reserved", c_int32)]
+
+
 # name -> (restype, argtypes); every symbol include/tfjs_cuda.h declares.
 _CTX = c_void_p
 _I64P = POINTER(c_int64)
@@ -88,6 +96,8 @@ SIGNATURES = {
     "tfjs_cuda_set_math_mode": (c_int, [_CTX, c_int]),
     "tfjs_cuda_launch_count": (c_int, [_CTX, POINTER(c_uint64)]),
     "tfjs_cuda_flush_l2": (c_int, [_CTX]),
+    "tfjs_cuda_launch_log": (c_int, [_CTX, c_int32]),
+    "tfjs_cuda_launch_log_take": (c_int, [_CTX, c_char_p, c_uint64, POINTER(c_uint32)]),
     "tfjs_cuda_fused_conv2d": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 5),
     "tfjs_cuda_fused_elementwise": (c_int, [_CTX, POINTER(EwProgram), c_int32]),
     "tfjs_cuda_fused_elementwise_catalogued": (c_int, [_CTX, POINTER(EwProgram),
@@ -133,8 +143,14 @@ SIGNATURES = {
     "tfjs_cuda_batchnorm": (c_int, [_CTX, c_int32, c_uint64, c_int32, c_uint64,
                                     c_int32, c_uint64, c_int32, c_uint64, c_int32,
                                     c_uint64, c_double, c_int32]),
+    "tfjs_cuda_batchnorm_rows": (c_int, [_CTX, c_int32, c_uint64, c_uint64] + [c_int32] * 8 +
+                                 [c_double, c_int32]),
     "tfjs_cuda_dequantize": (c_int, [_CTX, c_int32, c_int32, c_int32, c_double,
                                      c_double, c_uint64, c_int32]),
+    "tfjs_cuda_weights_begin": (c_int, [_CTX, POINTER(WeightSpec), c_int32, POINTER(c_int32)]),
+    "tfjs_cuda_weights_push": (c_int, [_CTX, c_int32, c_void_p, c_uint64]),
+    "tfjs_cuda_weights_push_file": (c_int, [_CTX, c_int32, c_char_p]),
+    "tfjs_cuda_weights_end": (c_int, [_CTX, c_int32, POINTER(c_int32), POINTER(c_uint64)]),
     "tfjs_cuda_dequantize_static": (c_int, [_CTX, c_int32, c_int32, c_int32, c_double,
                                             c_double, c_uint64, c_int32]),
 }

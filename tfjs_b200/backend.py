@@ -90,19 +90,26 @@ class _Record(object):
 
 class PendingConv(object):
     """A FusedConv2D (bias fused, linear activation) not launched yet, optionally with
-    the operand of the Add that consumed it."""
-    __slots__ = ("params", "x", "filt", "bias", "residual", "desc")
+    the operand of the Add that consumed it and the activation that followed (`act`:
+    linear, relu or relu6, applied last)."""
+    __slots__ = ("params", "x", "filt", "bias", "residual", "desc", "act")
 
-    def __init__(self, params, x, filt, bias, residual, desc):
+    def __init__(self, params, x, filt, bias, residual, desc, act="linear"):
         self.params, self.x, self.filt, self.bias = params, x, filt, bias
         self.residual = residual
         self.desc = desc      # profile records of the kernels folded into this launch
+        self.act = act
 
     def deps(self):
         return [d for d in (self.x, self.filt, self.bias, self.residual) if d is not None]
 
+    def with_act(self, act, desc):
+        return PendingConv(self.params, self.x, self.filt, self.bias, self.residual,
+                           self.desc + [desc], act)
+
     def launch(self, backend, out_dev, post_act):
         lib, p = backend.lib, self.params
+        post_act = self.act if post_act == "linear" else post_act
         bias = backend.device_id(self.bias) if self.bias is not None else 0
         if self.residual is None:
             if post_act != "linear":
@@ -116,6 +123,59 @@ class PendingConv(object):
                 backend.ctx, byref(p), backend.device_id(self.x), backend.device_id(self.filt),
                 bias, 0, backend.device_id(self.residual), _cabi.ACTIVATIONS[post_act],
                 out_dev))
+
+
+class PendingDepthwise(object):
+    """A DepthwiseConv2dNative / FusedDepthwiseConv2D with a linear activation not launched
+    yet.  tfjs-layers' DepthwiseConv2D layer issues the convolution, then Add with the bias
+    reshaped to [1, 1, 1, C], then the activation as kernels of their own
+    (tfjs-layers/src/layers/convolutional_depthwise.ts:154-169); here the bias of that Add
+    and a following Relu / Relu6 (spelled Relu then Minimum(6, .) or ClipByValue(., 0, 6) by
+    the Relu6 activation and the ReLU layer) join the convolution's launch, which applies
+    them with the same fp32 roundings."""
+    __slots__ = ("params", "x", "filt", "bias", "desc", "act")
+
+    def __init__(self, params, x, filt, bias, desc, act="linear"):
+        self.params, self.x, self.filt, self.bias = params, x, filt, bias
+        self.desc, self.act = desc, act
+
+    def deps(self):
+        return [d for d in (self.x, self.filt, self.bias) if d is not None]
+
+    def with_bias(self, bias, bias_len, desc):
+        p = _cabi.Conv2DParams.from_buffer_copy(self.params)
+        p.bias_len = bias_len
+        return PendingDepthwise(p, self.x, self.filt, bias, self.desc + [desc], self.act)
+
+    def with_act(self, act, desc):
+        return PendingDepthwise(self.params, self.x, self.filt, self.bias, self.desc + [desc], act)
+
+    def launch(self, backend, out_dev, post_act):
+        p = _cabi.Conv2DParams.from_buffer_copy(self.params)
+        p.activation = _cabi.ACTIVATIONS[self.act if post_act == "linear" else post_act]
+        backend.check(backend.lib.tfjs_cuda_fused_depthwise_conv2d(
+            backend.ctx, byref(p), backend.device_id(self.x), backend.device_id(self.filt),
+            backend.device_id(self.bias) if self.bias is not None else 0, 0, out_dev))
+
+
+class PendingTile(object):
+    """A Tile not launched yet.  A consumer that can index the untiled tensor itself (the
+    batch normalisation behind tfjs-layers' LayerNormalization, which tiles the moments and
+    gamma / beta to the input's shape) reads `src` directly and the tile never exists; any
+    other consumer makes it materialise."""
+    __slots__ = ("src", "src_shape", "reps", "shape", "dtype", "desc")
+
+    def __init__(self, src, src_shape, reps, shape, dtype, desc):
+        self.src, self.src_shape, self.reps = src, [int(v) for v in src_shape], list(reps)
+        self.shape, self.dtype, self.desc = [int(v) for v in shape], dtype, desc
+
+    def deps(self):
+        return [self.src]
+
+    def launch(self, backend, out_dev, post_act):
+        from .kernels import movement
+        movement.tile_into(backend, TensorInfo(self.src, self.src_shape, self.dtype), self.reps,
+                           self.shape, out_dev)
 
 
 class PendingEw(object):
@@ -338,6 +398,7 @@ class CudaBackend(object):
         self.lazy_fusion = os.environ.get("TFJS_CUDA_NO_LAZY_FUSION", "0") in ("", "0")
         self.profiler = None  # the engine, while it profiles (told about deferred launches)
         self.ew_catalogue = {}  # chain signature -> the library has a kernel for it
+        self._log_depth = 0     # nesting of launch_log(True)
 
     # ------------------------------------------------------------ plumbing --
     def check(self, rc):
@@ -445,19 +506,12 @@ class CudaBackend(object):
         rec.pending = None
         self._release(pending)
 
-    def launch_pending(self, info, post_act):
-        """Launch the pending producer of `info` with `post_act` (relu / relu6) folded
-        into its epilogue and return the activated tensor.  `info` itself stays
-        pending: if another kernel consumes it later it is launched again, without
-        the activation."""
+    def with_activation(self, info, act, desc):
+        """The pending convolution behind `info` with `act` (relu / relu6) as the last step
+        of its epilogue, as a new pending tensor.  `info` itself stays pending: if another
+        kernel consumes it later it is launched again, without the activation."""
         pending = self.data[info.dataId].pending
-        out = self.make_output(info.shape, "float32")
-        try:
-            self._launch(pending, self.data[out.dataId].dev, post_act, True)
-        except Exception:
-            self.disposeData(out.dataId)
-            raise
-        return out
+        return self.defer(info.shape, "float32", pending.with_act(act, desc))
 
     def device_id(self, dataId):
         """Device buffer id of a tensor; launches a pending producer or uploads a
@@ -568,13 +622,39 @@ class CudaBackend(object):
                 "poolHighWater": vals[2].value, "numDeviceBuffers": vals[3].value}
 
     def time(self, f):
-        """backend.time(f) -> {kernelMs, wallMs} with CUDA events on the stream."""
+        """backend.time(f) -> BackendTimingInfo (backend.ts:26-30): {kernelMs, wallMs,
+        getExtraProfileInfo} with CUDA events on the stream; the extra information names
+        the kernel instantiations the library launched inside f."""
         t0 = _time.perf_counter()
-        self.check(self.lib.tfjs_cuda_time_begin(self.ctx))
-        f()
-        ms = c_float()
-        self.check(self.lib.tfjs_cuda_time_end(self.ctx, byref(ms)))
-        return {"kernelMs": ms.value, "wallMs": (_time.perf_counter() - t0) * 1e3}
+        nested = self._log_depth > 0
+        self.launch_log(True)
+        try:
+            self.check(self.lib.tfjs_cuda_time_begin(self.ctx))
+            f()
+            ms = c_float()
+            self.check(self.lib.tfjs_cuda_time_end(self.ctx, byref(ms)))
+            info = self.launch_log_take() if not nested else ""
+        finally:
+            self.launch_log(False)
+        return {"kernelMs": ms.value, "wallMs": (_time.perf_counter() - t0) * 1e3,
+                "getExtraProfileInfo": lambda: info}
+
+    def launch_log(self, enable):
+        """Turns the library's launch log on or off (calls nest)."""
+        if enable:
+            self._log_depth += 1
+            if self._log_depth == 1:
+                self.check(self.lib.tfjs_cuda_launch_log(self.ctx, 1))
+        else:
+            self._log_depth -= 1
+            if self._log_depth == 0:
+                self.check(self.lib.tfjs_cuda_launch_log(self.ctx, 0))
+
+    def launch_log_take(self):
+        """Text naming the kernel instantiations launched since the last take."""
+        buf = ctypes.create_string_buffer(4096)
+        self.check(self.lib.tfjs_cuda_launch_log_take(self.ctx, buf, 4096, None))
+        return buf.value.decode()
 
     def event_record(self, slot):
         self.check(self.lib.tfjs_cuda_event_record(self.ctx, int(slot)))

@@ -90,6 +90,10 @@ struct tfjs_cuda_ctx {
   std::string err;
   uint64_t in_use = 0, high_water = 0, n_live = 0;
   uint64_t launches = 0;
+  // names of the kernel instantiations launched while tfjs_cuda_launch_log is on (string
+  // literals or statics: the pointers stay valid)
+  bool log_launches = false;
+  std::vector<const char*> launch_log;
   int math_mode = TFJS_CUDA_MATH_TF32;
   int* d_flag = nullptr;  // device error word written by bounded waits
   int* h_flag = nullptr;  // pinned mirror
@@ -122,6 +126,14 @@ void ctx_drop_packed(tfjs_cuda_ctx* ctx, int32_t id);
 // Marks captured steps that read the packed copy of weight `id` as stale (no memory call).
 void ctx_packed_contents_changed(tfjs_cuda_ctx* ctx, int32_t id);
 
+// Weight decoding on raw device pointers, queued on the compute stream (eltwise.cu); the
+// tensor-id entry points and the weight loader share them.
+int dequant_enqueue(tfjs_cuda_ctx* ctx, const void* q, int q_bytes, int to_dtype, double scale,
+                    double min, uint64_t n, void* out);
+int decode_f16_enqueue(tfjs_cuda_ctx* ctx, const void* q, uint64_t n, void* out);
+// Drops the weight loaders of a context that is being destroyed (loader.cu).
+void loaders_drop(tfjs_cuda_ctx* ctx);
+
 #define CUDA_TRY(ctx, expr)                                   \
   do {                                                        \
     int _rc = ctx_check((ctx), (expr), #expr);                \
@@ -143,6 +155,7 @@ void ctx_packed_contents_changed(tfjs_cuda_ctx* ctx, int32_t id);
 #define LAUNCH_CHECK(ctx, name)                               \
   do {                                                        \
     (ctx)->launches++;                                        \
+    if ((ctx)->log_launches) (ctx)->launch_log.push_back(name); \
     int _rc = ctx_check((ctx), cudaGetLastError(), name);     \
     if (_rc != TFJS_CUDA_OK) return _rc;                      \
   } while (0)

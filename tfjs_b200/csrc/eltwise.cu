@@ -455,6 +455,40 @@ __global__ void batchnorm_kernel(const float* __restrict__ x, uint64_t n,
   }
 }
 
+// The same arithmetic on a [rows, cols] view of x whose parameters are rows or columns of
+// it: tfjs-layers' LayerNormalization tiles the moments (one value per row) and gamma / beta
+// (one per column) to the input's shape and calls batchNorm on the tiles
+// (tfjs-layers/src/layers/normalization.ts:578-622); with the tiles left unmaterialised the
+// kernel indexes the untiled tensors.  Parameter modes: 0 absent, 1 one value per column,
+// 2 one value per row, 3 one value per element, 4 a single value.
+struct BnParam {
+  const float* p;
+  int mode;
+};
+__device__ __forceinline__ double bn_fetch(const BnParam& q, uint64_t i, uint32_t r,
+                                           uint32_t c, double absent) {
+  switch (q.mode) {
+    case 1: return (double)__ldg(q.p + c);
+    case 2: return (double)__ldg(q.p + r);
+    case 3: return (double)__ldg(q.p + i);
+    case 4: return (double)__ldg(q.p);
+    default: return absent;
+  }
+}
+__global__ void batchnorm_rows_kernel(const float* __restrict__ x, uint32_t rows, uint32_t cols,
+                                      BnParam mean, BnParam var, BnParam scale, BnParam off,
+                                      double eps, float* __restrict__ y) {
+  const uint64_t n = (uint64_t)rows * cols;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const uint32_t r = (uint32_t)(i / cols), c = (uint32_t)(i - (uint64_t)r * cols);
+    const double o = bn_fetch(off, i, r, c, 0.0);
+    const double sc = bn_fetch(scale, i, r, c, 1.0);
+    y[i] = (float)(o + ((double)x[i] - bn_fetch(mean, i, r, c, 0.0)) * sc /
+                           sqrt(bn_fetch(var, i, r, c, 1.0) + eps));
+  }
+}
+
 // ------------------------------------------------------------------ cast ----
 // tfjs-backend-cpu/src/kernels/Cast.ts:30-45.
 template <typename TI, typename TO, int MODE>  // 0 convert, 1 to-int32 (JS), 2 to-bool
@@ -678,6 +712,38 @@ struct ProgGeluErfDivF32 {
     return t[j];
   }
 };
+struct ProgGeluLayers {  // x * (0.5 * (erf(x / c) + 1)): the Gelu activation of tfjs-layers
+  static constexpr int n_in = 4, n_ops = 5;   // (tfjs-layers/src/activations.ts:223-233)
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[5] = {EW_B(DIV, 0, 1), EW_U(ERF, 4), EW_B(ADD, 5, 2),
+                                      EW_B(MUL, 6, 3), EW_B(MUL, 7, 0)};
+    return t[j];
+  }
+};
+struct ProgGeluLayersF32 {
+  static constexpr int n_in = 4, n_ops = 5;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[5] = {EW_B(DIV, 0, 1), EW_U(ERF_F32, 4), EW_B(ADD, 5, 2),
+                                      EW_B(MUL, 6, 3), EW_B(MUL, 7, 0)};
+    return t[j];
+  }
+};
+struct ProgBiasGeluLayers {  // t = x + bias; t * (0.5 * (erf(t / c) + 1)): a Dense layer of
+  static constexpr int n_in = 5, n_ops = 6;   // tfjs-layers with the gelu activation
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[6] = {EW_B(ADD, 0, 1), EW_B(DIV, 5, 2), EW_U(ERF, 6), EW_B(ADD, 7, 3),
+                                      EW_B(MUL, 8, 4), EW_B(MUL, 5, 9)};
+    return t[j];
+  }
+};
+struct ProgBiasGeluLayersF32 {
+  static constexpr int n_in = 5, n_ops = 6;
+  __host__ __device__ static constexpr StaticOp op(int j) {
+    constexpr StaticOp t[6] = {EW_B(ADD, 0, 1), EW_B(DIV, 5, 2), EW_U(ERF_F32, 6),
+                                      EW_B(ADD, 7, 3), EW_B(MUL, 8, 4), EW_B(MUL, 5, 9)};
+    return t[j];
+  }
+};
 struct ProgScaleShift {  // x * a + b (attention scores * scale + mask, affine maps)
   static constexpr int n_in = 3, n_ops = 2;
   __host__ __device__ static constexpr StaticOp op(int j) {
@@ -792,6 +858,10 @@ static bool ew_launch_catalogued(tfjs_cuda_ctx* ctx, const EwArgs& g, bool vec,
   EW_TRY(ProgGeluErfDiv)
   EW_TRY(ProgGeluErfF32)
   EW_TRY(ProgGeluErfDivF32)
+  EW_TRY(ProgGeluLayers)
+  EW_TRY(ProgGeluLayersF32)
+  EW_TRY(ProgBiasGeluLayers)
+  EW_TRY(ProgBiasGeluLayersF32)
   EW_TRY(ProgScaleShift)
   EW_TRY(ProgAddAdd)
 #undef EW_TRY
@@ -1154,6 +1224,44 @@ int tfjs_cuda_batchnorm(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t n,
   return TFJS_CUDA_OK;
 }
 
+int tfjs_cuda_batchnorm_rows(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows, uint64_t cols,
+                             int32_t mean_id, int32_t mean_mode, int32_t var_id,
+                             int32_t var_mode, int32_t scale_id, int32_t scale_mode,
+                             int32_t offset_id, int32_t offset_mode, double epsilon,
+                             int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  if (rows > 0xffffffffull || cols > 0xffffffffull)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "batchnorm_rows: view too large");
+  const uint64_t n = rows * cols;
+  Buffer *x, *y;
+  int rc;
+  if ((rc = ctx_get(ctx, x_id, n * 4, "batchnorm_rows x", &x))) return rc;
+  if ((rc = ctx_get(ctx, out_id, n * 4, "batchnorm_rows out", &y))) return rc;
+  const int32_t ids[4] = {mean_id, var_id, scale_id, offset_id};
+  const int32_t modes[4] = {mean_mode, var_mode, scale_mode, offset_mode};
+  BnParam q[4];
+  for (int k = 0; k < 4; ++k) {
+    q[k].p = nullptr;
+    q[k].mode = modes[k];
+    if (modes[k] < 0 || modes[k] > 4 || (k < 2 && modes[k] == 0))
+      return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "batchnorm_rows: parameter %d has mode %d", k,
+                      modes[k]);
+    if (modes[k] == 0) continue;
+    const uint64_t need = modes[k] == 1 ? cols : modes[k] == 2 ? rows : modes[k] == 3 ? n : 1;
+    Buffer* b;
+    if ((rc = ctx_get(ctx, ids[k], need * 4, "batchnorm_rows parameter", &b))) return rc;
+    q[k].p = (const float*)b->ptr;
+  }
+  if (n == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  batchnorm_rows_kernel<<<grid_for(n, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+      (const float*)x->ptr, (uint32_t)rows, (uint32_t)cols, q[0], q[1], q[2], q[3], epsilon,
+      (float*)y->ptr);
+  LAUNCH_CHECK(ctx, "batchnorm_rows_kernel");
+  ctx_mark_written(ctx, out_id);
+  return TFJS_CUDA_OK;
+}
+
 static uint64_t dtype_bytes(int dt) { return dt == TFJS_CUDA_BOOL ? 1 : 4; }
 
 int tfjs_cuda_cast(tfjs_cuda_ctx* ctx, int32_t from, int32_t to, int32_t x_id,
@@ -1411,21 +1519,12 @@ int tfjs_cuda_gather(tfjs_cuda_ctx* ctx, int32_t elem_bytes, int32_t x_id,
   return TFJS_CUDA_OK;
 }
 
-int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_dtype,
-                         int32_t q_id, double scale, double min, uint64_t n,
-                         int32_t out_id) {
-  if (!ctx) return TFJS_CUDA_INVALID_ARG;
-  NOT_WHILE_CAPTURING(ctx, "dequantising weights");
-  if (q_bytes != 1 && q_bytes != 2)
-    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "dequantize: q_dtype_bytes %d", q_bytes);
-  if (to_dtype != TFJS_CUDA_FLOAT32 && to_dtype != TFJS_CUDA_INT32)
-    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "dequantize: target dtype %d", to_dtype);
-  Buffer *q, *o;
-  int rc;
-  if ((rc = ctx_get(ctx, q_id, n * q_bytes, "dequantize q", &q))) return rc;
-  if ((rc = ctx_get(ctx, out_id, n * 4, "dequantize out", &o))) return rc;
-  if (n == 0) return TFJS_CUDA_OK;
-  cudaSetDevice(ctx->device);
+}  // extern "C"
+
+// Pointer-level form shared with the weight loader: table built on the host in double,
+// uploaded, looked up by the kernel.  Everything is queued on the context's compute stream.
+int dequant_enqueue(tfjs_cuda_ctx* ctx, const void* q, int q_bytes, int to_dtype, double scale,
+                    double min, uint64_t n, void* out) {
   const int entries = q_bytes == 1 ? 256 : 65536;
   std::vector<uint32_t> table(entries);
   for (int v = 0; v < entries; ++v) {
@@ -1453,14 +1552,35 @@ int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_dtype,
   if (q_bytes == 1) {
     dequant_u8_kernel<uint32_t><<<grid_for((n + 15) / 16, kThreads, ctx->sm_count),
                                   kThreads, 0, ctx->stream>>>(
-        (const uint8_t*)q->ptr, (const uint32_t*)d_table, (uint32_t*)o->ptr, n);
+        (const uint8_t*)q, (const uint32_t*)d_table, (uint32_t*)out, n);
   } else {
     dequant_u16_kernel<uint32_t><<<grid_for(n, kThreads, ctx->sm_count), kThreads, 0,
                                    ctx->stream>>>(
-        (const uint16_t*)q->ptr, (const uint32_t*)d_table, (uint32_t*)o->ptr, n);
+        (const uint16_t*)q, (const uint32_t*)d_table, (uint32_t*)out, n);
   }
   LAUNCH_CHECK(ctx, "dequant_kernel");
   CUDA_TRY(ctx, cudaFreeAsync(d_table, ctx->stream));
+  return TFJS_CUDA_OK;
+}
+
+extern "C" {
+
+int tfjs_cuda_dequantize(tfjs_cuda_ctx* ctx, int32_t q_bytes, int32_t to_dtype,
+                         int32_t q_id, double scale, double min, uint64_t n,
+                         int32_t out_id) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  NOT_WHILE_CAPTURING(ctx, "dequantising weights");
+  if (q_bytes != 1 && q_bytes != 2)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "dequantize: q_dtype_bytes %d", q_bytes);
+  if (to_dtype != TFJS_CUDA_FLOAT32 && to_dtype != TFJS_CUDA_INT32)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "dequantize: target dtype %d", to_dtype);
+  Buffer *q, *o;
+  int rc;
+  if ((rc = ctx_get(ctx, q_id, n * q_bytes, "dequantize q", &q))) return rc;
+  if ((rc = ctx_get(ctx, out_id, n * 4, "dequantize out", &o))) return rc;
+  if (n == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  if ((rc = dequant_enqueue(ctx, q->ptr, q_bytes, to_dtype, scale, min, n, o->ptr))) return rc;
   Buffer* ob = ctx_buf(ctx, out_id);
   ob->version++;
   ob->from_host = true;  // dequantised weights are constants
@@ -1509,6 +1629,17 @@ __global__ void decode_f16_kernel(const uint16_t* __restrict__ q, uint32_t* __re
   for (uint64_t i = (n8 << 3) + tid; i < n; i += stride) o[i] = half_bits_to_float_bits(q[i]);
 }
 
+}  // extern "C"
+
+int decode_f16_enqueue(tfjs_cuda_ctx* ctx, const void* q, uint64_t n, void* out) {
+  decode_f16_kernel<<<grid_for((n + 7) / 8, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+      (const uint16_t*)q, (uint32_t*)out, n);
+  LAUNCH_CHECK(ctx, "decode_f16_kernel");
+  return TFJS_CUDA_OK;
+}
+
+extern "C" {
+
 int tfjs_cuda_decode_float16(tfjs_cuda_ctx* ctx, int32_t q_id, uint64_t n, int32_t out_id) {
   if (!ctx) return TFJS_CUDA_INVALID_ARG;
   Buffer *q, *o;
@@ -1517,9 +1648,7 @@ int tfjs_cuda_decode_float16(tfjs_cuda_ctx* ctx, int32_t q_id, uint64_t n, int32
   if ((rc = ctx_get(ctx, out_id, n * 4, "decode_float16 out", &o))) return rc;
   if (n == 0) return TFJS_CUDA_OK;
   cudaSetDevice(ctx->device);
-  decode_f16_kernel<<<grid_for((n + 7) / 8, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
-      (const uint16_t*)q->ptr, (uint32_t*)o->ptr, n);
-  LAUNCH_CHECK(ctx, "decode_f16_kernel");
+  if ((rc = decode_f16_enqueue(ctx, q->ptr, n, o->ptr))) return rc;
   Buffer* ob = ctx_buf(ctx, out_id);
   ob->version++;
   ob->from_host = true;  // decoded weights are constants

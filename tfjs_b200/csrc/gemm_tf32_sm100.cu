@@ -1378,7 +1378,12 @@ int launch_cfg(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& t
     g.sk_flags = ctx->sk_flags;
   }
   kern<<<grid, C::THREADS, smem, ctx->stream>>>(tm_a, tm_b, tm_c, tm_r, g);
-  LAUNCH_CHECK(ctx, "gemm_tf32_kernel");
+  // the instantiation's name, for the launch log behind tf.profile's extra information
+  static const std::string name =
+      "gemm_tf32_kernel<BN=" + std::to_string(BN) + ",B_MN=" + std::to_string(B_MN) +
+      ",A_MODE=" + std::to_string(A_MODE) + ",RES=" + std::to_string(RES) +
+      ",EW=" + std::to_string(EW) + ",SK=" + std::to_string(SK) + ">";
+  LAUNCH_CHECK(ctx, name.c_str());
   return TFJS_CUDA_OK;
 }
 

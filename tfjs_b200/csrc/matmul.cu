@@ -98,6 +98,7 @@ int get_packed(tfjs_cuda_ctx* ctx, int32_t id, Buffer* src, int batch, int N, in
     pack_weight_kernel<<<grid_for(total, kThreads, ctx->sm_count), kThreads, 0, ctx->stream>>>(
         (const float*)src->ptr, pw.ptr, total, N, taps, cin, cin_pad, in_is_nk);
     ctx->launches++;
+    if (ctx->log_launches) ctx->launch_log.push_back("pack_weight_kernel");
     int rc = ctx_check(ctx, cudaGetLastError(), "pack_weight_kernel");
     if (rc) {
       cudaFreeAsync(pw.ptr, ctx->stream);

@@ -243,6 +243,7 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  loaders_drop(ctx);
   for (auto& kv : ctx->packed)
     if (kv.second.ptr) cudaFreeAsync(kv.second.ptr, ctx->stream);
   for (auto& b : ctx->bufs)
@@ -818,6 +819,35 @@ int tfjs_cuda_set_math_mode(tfjs_cuda_ctx* ctx, int mode) {
   if (mode != TFJS_CUDA_MATH_TF32 && mode != TFJS_CUDA_MATH_FP32)
     return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "unknown math mode %d", mode);
   ctx->math_mode = mode;
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_launch_log(tfjs_cuda_ctx* ctx, int32_t enable) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  ctx->log_launches = enable != 0;
+  ctx->launch_log.clear();
+  return TFJS_CUDA_OK;
+}
+
+int tfjs_cuda_launch_log_take(tfjs_cuda_ctx* ctx, char* buf, uint64_t cap,
+                              uint32_t* out_launches) {
+  if (!ctx || (cap && !buf)) return TFJS_CUDA_INVALID_ARG;
+  if (out_launches) *out_launches = (uint32_t)ctx->launch_log.size();
+  std::string text;
+  for (size_t i = 0; i < ctx->launch_log.size();) {
+    size_t j = i;
+    while (j < ctx->launch_log.size() && !strcmp(ctx->launch_log[j], ctx->launch_log[i])) ++j;
+    if (!text.empty()) text += ", ";
+    text += ctx->launch_log[i];
+    if (j - i > 1) text += " x" + std::to_string(j - i);
+    i = j;
+  }
+  ctx->launch_log.clear();
+  if (cap) {
+    const size_t n = text.size() < cap - 1 ? text.size() : cap - 1;
+    memcpy(buf, text.data(), n);
+    buf[n] = 0;
+  }
   return TFJS_CUDA_OK;
 }
 

@@ -178,6 +178,10 @@ class Engine(object):
         out = kernel.kernelFunc({"inputs": infos, "attrs": attrs or {}, "backend": self.backend})
         if prof is not None:
             self.backend.event_record(rec["slot"] + 1)
+            # what tfjs-core's profiler prints as the kernel's extra information
+            # (profiler.ts:74-76): the kernel instantiations this call launched
+            rec["extraInfo"] = ", ".join(t for t in rec.pop("_extra", []) +
+                                         [self.backend.launch_log_take()] if t)
             self._prof_stack.pop()
             o = out if isinstance(out, (list, tuple)) else [out]
             rec["outputShapes"] = [list(t.shape) for t in o]
@@ -216,6 +220,9 @@ class Engine(object):
             return launch()
         rec = {"slot": self._take_slots(), "inputShapes": {}, "attrs": {}, "nested": [],
                "deferred": False}
+        # launches noted so far belong to the kernel func that is running
+        if self._prof_stack:
+            self._prof_stack[-1].setdefault("_extra", []).append(self.backend.launch_log_take())
         self.backend.event_record(rec["slot"])
         self._prof_stack.append(rec)      # launches of pending operands nest under this one
         try:
@@ -223,6 +230,8 @@ class Engine(object):
         finally:
             self._prof_stack.pop()
         self.backend.event_record(rec["slot"] + 1)
+        rec["extraInfo"] = ", ".join(t for t in rec.pop("_extra", []) +
+                                     [self.backend.launch_log_take()] if t)
         # a launch may narrow `descs` to what it really covered (a chain that ran as its
         # last kernel only), so the record is named afterwards
         rec.update(name="+".join(d["name"] for d in descs), parts=list(descs),
@@ -241,11 +250,13 @@ class Engine(object):
         self._prof_stack = []
         self._prof_next_slot = 0
         self.backend.profiler = self
+        self.backend.launch_log(True)
         try:
             result = f()
         finally:
             records, self._profile = self._profile, None
             self.backend.profiler = None
+            self.backend.launch_log(False)
         for rec in records:
             ms = self.backend.event_elapsed(rec["slot"], rec["slot"] + 1)
             for slot in rec["nested"]:

@@ -942,7 +942,9 @@ class GraphModel(object):
         specs = []
         for group in self.artifacts.get("weightsManifest", []):
             specs.extend(group["weights"])
-        decode = decode_weights or io.decode_weights
+        # weights go through the library's loader (pinned staging, device-side decode);
+        # io.decode_weights is the per-tensor path with the same results
+        decode = decode_weights or io.load_weights
         self.weights = decode(self.engine, weight_data, specs)
         nodes = [Node(d) for d in topo["node"]]
         for n in nodes:
@@ -955,6 +957,23 @@ class GraphModel(object):
             [n.name for n in self.executor.placeholders]
         self.output_names = list((sig.get("outputs") or {}).keys()) or \
             self.executor.default_outputs
+
+    @classmethod
+    def load(cls, model_json_path, engine=None, replay=None):
+        """tf.loadGraphModel for a model.json on disk: the weight shards named by
+        weightsManifest[].paths (relative to the model.json) are read by the library itself
+        (graph_model.ts:176-234 with the file handler of tfjs-node's io)."""
+        with open(model_json_path) as f:
+            artifacts = json.load(f)
+        base = os.path.dirname(os.path.abspath(model_json_path))
+        eng = engine or ENGINE
+
+        def from_files(engine_, _unused, specs):
+            paths = []
+            for group in artifacts.get("weightsManifest", []):
+                paths.extend(os.path.join(base, p) for p in group["paths"])
+            return io.load_weights_from_files(engine_, paths, specs)
+        return cls(artifacts, None, eng, decode_weights=from_files, replay=replay)
 
     @property
     def inputs(self):

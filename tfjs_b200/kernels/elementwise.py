@@ -5,7 +5,7 @@ binary_impl.ts:25-69 and the per-op files (Add.ts, Relu.ts, Erf.ts, ...);
 BatchNorm.ts:23-90; Cast.ts:27-95.
 """
 from .. import _cabi
-from ..backend import PendingConv, PendingEw, TensorInfo
+from ..backend import (PendingConv, PendingDepthwise, PendingEw, PendingTile, TensorInfo)
 from ..kernel_registry import KernelConfig
 from ..util import assert_and_get_broadcast_shape, size_from_shape
 from .common import BACKEND, assert_not_complex, dev, view
@@ -189,15 +189,66 @@ def deferred_elementwise(backend, name, a, b=None):
                          PendingEw(leaves, leaf_shapes, ops, out_shape, descs, top, depth))
 
 
-def _unary_config(name, p_from_attrs=None):
-    post_act = {"Relu": "relu", "Relu6": "relu6"}.get(name)
+def _fold_activation(backend, name, x, attrs=None, other=None):
+    """Relu / Relu6 over a pending convolution become the last step of its epilogue; so do
+    the two ways tfjs-layers spells relu6 after a Relu: Minimum(6, .) (the Relu6 activation,
+    tfjs-layers/src/activations.ts:83-89) and ClipByValue(., 0, 6) (the ReLU layer with
+    maxValue 6, layers/advanced_activations.ts).  Returns the new pending tensor or None."""
+    pend = backend.pending_of(x.dataId)
+    if not isinstance(pend, (PendingConv, PendingDepthwise)) or x.dtype != "float32":
+        return None
+    act = None
+    if name == "Relu" and pend.act == "linear":
+        act = "relu"
+    elif name == "Relu6" and pend.act in ("linear", "relu"):
+        act = "relu6"
+    elif name == "ClipByValue" and pend.act in ("linear", "relu"):
+        if float(attrs["clipValueMin"]) == 0.0 and float(attrs["clipValueMax"]) == 6.0:
+            act = "relu6"
+    elif name == "Minimum" and pend.act == "relu" and other is not None:
+        six = backend.host_values(other.dataId)
+        if (other.dtype == "float32" and size_from_shape(other.shape) == 1 and six is not None
+                and float(six[0]) == 6.0):
+            act = "relu6"
+    if act is None:
+        return None
+    desc = {"name": name, "inputShapes": {}, "outputShapes": [list(x.shape)], "attrs": {}}
+    return backend.with_activation(x, act, desc)
 
+
+def _depthwise_bias(backend, a, b):
+    """Add of a pending depthwise convolution without a bias and a per-channel (or scalar)
+    float32 operand, the biasAdd of tfjs-layers' DepthwiseConv2D: the convolution with that
+    bias, still pending."""
+    for conv, other in ((a, b), (b, a)):
+        pend = backend.pending_of(conv.dataId)
+        if not (isinstance(pend, PendingDepthwise) and pend.bias is None and
+                pend.act == "linear" and other.dtype == "float32" and conv.dtype == "float32"):
+            continue
+        if backend.pending_of(other.dataId) is not None:
+            continue
+        channels = conv.shape[-1]
+        n = size_from_shape(other.shape)
+        per_channel = (n == channels and len(other.shape) <= len(conv.shape) and
+                       other.shape[-1] == channels)
+        if n != 1 and not per_channel:
+            continue
+        desc = {"name": "Add", "inputShapes": {"b": list(other.shape)},
+                "outputShapes": [list(conv.shape)], "attrs": {}}
+        return backend.defer(conv.shape, "float32",
+                             pend.with_bias(other.dataId, 1 if n == 1 else channels, desc))
+    return None
+
+
+def _unary_config(name, p_from_attrs=None):
     def func(args):
         x = args["inputs"]["x"]
         backend = args["backend"]
         if x.dtype == "float32" and backend.lazy_fusion:
-            if post_act and isinstance(backend.pending_of(x.dataId), PendingConv):
-                return backend.launch_pending(x, post_act)
+            if name in ("Relu", "Relu6", "ClipByValue"):
+                out = _fold_activation(backend, name, x, args["attrs"])
+                if out is not None:
+                    return out
             if name in EW_UNARY:
                 out = deferred_elementwise(backend, name, x)
                 if out is not None:
@@ -216,7 +267,7 @@ def _conv_residual(backend, a, b):
             "outputShapes": [list(a.shape)], "attrs": {}}
     for conv, other in ((a, b), (b, a)):
         pend = backend.pending_of(conv.dataId)
-        if isinstance(pend, PendingConv) and pend.residual is None:
+        if isinstance(pend, PendingConv) and pend.residual is None and pend.act == "linear":
             return backend.defer(a.shape, "float32", PendingConv(
                 pend.params, pend.x, pend.filt, pend.bias, other.dataId, pend.desc + [desc]))
     return None
@@ -229,7 +280,13 @@ def _binary_config(name):
         if name == "Prelu":
             return binary_impl(backend, name, i["x"], i["alpha"])
         if backend.lazy_fusion:
-            out = _conv_residual(backend, i["a"], i["b"]) if name == "Add" else None
+            out = None
+            if name == "Add":
+                out = _conv_residual(backend, i["a"], i["b"]) or \
+                    _depthwise_bias(backend, i["a"], i["b"])
+            elif name == "Minimum":
+                out = _fold_activation(backend, name, i["a"], other=i["b"]) or \
+                    _fold_activation(backend, name, i["b"], other=i["a"])
             if out is None and name in EW_BINARY:
                 out = deferred_elementwise(backend, name, i["a"], i["b"])
             if out is not None:
@@ -256,6 +313,9 @@ def fused_batch_norm(args):
     if eps is None:
         eps = 0.001
     n = size_from_shape(x.shape)
+    rows_form = _batch_norm_rows(backend, x, mean, var, scale, offset, eps)
+    if rows_form is not None:
+        return rows_form
     out = backend.make_output(x.shape, "float32")
     try:
         backend.check(backend.lib.tfjs_cuda_batchnorm(
@@ -264,6 +324,60 @@ def fused_batch_norm(args):
             dev(backend, scale), size_from_shape(scale.shape) if scale is not None else 0,
             dev(backend, offset), size_from_shape(offset.shape) if offset is not None else 0,
             float(eps), dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    return out
+
+
+def _batch_norm_rows(backend, x, mean, var, scale, offset, eps):
+    """tfjs-layers' LayerNormalization tiles the per-row moments and the per-column gamma /
+    beta to x's shape and calls batchNorm on the tiles (layers/normalization.ts:578-622).
+    When those Tile results are still pending, the kernel indexes the untiled tensors
+    (tfjs_cuda_batchnorm_rows) and the tiles are never made.  None when the parameters are
+    not of that form."""
+    if x.dtype != "float32" or len(x.shape) < 1 or size_from_shape(x.shape) == 0:
+        return None
+    cols = x.shape[-1]
+    rows = size_from_shape(x.shape) // cols if cols else 0
+    row_shape, rank = list(x.shape[:-1]) + [1], len(x.shape)
+    ids, modes, any_tile = [], [], False
+    for t in (mean, var, scale, offset):
+        if t is None:
+            ids.append(None)
+            modes.append(0)
+            continue
+        if t.dtype != "float32":
+            return None
+        pend = backend.pending_of(t.dataId)
+        src_id, shape = t.dataId, list(t.shape)
+        if isinstance(pend, PendingTile) and list(pend.shape) == list(x.shape):
+            src_id, shape, any_tile = pend.src, list(pend.src_shape), True
+        elif pend is not None:
+            return None
+        padded = [1] * (rank - len(shape)) + shape
+        if len(padded) != rank:
+            return None
+        if size_from_shape(shape) == 1:
+            mode = 4
+        elif padded == list(x.shape):
+            mode = 3
+        elif padded == row_shape:
+            mode = 2
+        elif padded == [1] * (rank - 1) + [cols]:
+            mode = 1
+        else:
+            return None
+        ids.append(src_id)
+        modes.append(mode)
+    if not any_tile:
+        return None
+    out = backend.make_output(x.shape, "float32")
+    try:
+        d = [backend.device_id(i) if i is not None else 0 for i in ids]
+        backend.check(backend.lib.tfjs_cuda_batchnorm_rows(
+            backend.ctx, dev(backend, x), rows, cols, d[0], modes[0], d[1], modes[1], d[2],
+            modes[2], d[3], modes[3], float(eps), dev(backend, out)))
     except Exception:
         backend.disposeData(out.dataId)
         raise

@@ -247,15 +247,33 @@ def _tile(args):
         raise ValueError("Error in transpose: rank of input %d must match length of reps %s."
                          % (len(x.shape), reps))
     out_shape = [s * r for s, r in zip(x.shape, reps)]
+    if (backend.lazy_fusion and x.dtype == "float32" and size_from_shape(out_shape) and
+            len(out_shape) <= 6 and backend.pending_of(x.dataId) is None):
+        # Deferred: a batch normalisation that can index the untiled tensor never needs it
+        from ..backend import PendingTile
+        desc = {"name": "Tile", "inputShapes": {"x": list(x.shape)},
+                "outputShapes": [out_shape], "attrs": {}}
+        return backend.defer(out_shape, x.dtype,
+                             PendingTile(x.dataId, x.shape, reps, out_shape, x.dtype, [desc]))
     out = backend.make_output(out_shape, x.dtype)
     if size_from_shape(out_shape):
         try:
-            copy_strided(backend, x, 0, compute_strides(x.shape), x.shape, out, 0,
-                         compute_strides(out_shape), out_shape)
+            tile_into(backend, x, reps, out_shape, dev(backend, out))
         except Exception:
             backend.disposeData(out.dataId)
             raise
     return out
+
+
+def tile_into(backend, x, reps, out_shape, out_dev):
+    """The tile of x written to the device buffer out_dev."""
+    rank = len(out_shape)
+    if rank > 6:
+        raise ValueError("rank %d is not supported by the CUDA backend" % rank)
+    backend.check(backend.lib.tfjs_cuda_copy_strided(
+        backend.ctx, _elem_bytes(x.dtype), rank, _I64(out_shape), dev(backend, x), 0,
+        _I64(compute_strides(x.shape)), _I64(x.shape), out_dev, 0,
+        _I64(compute_strides(out_shape))))
 
 
 def _pack(args):
