@@ -266,6 +266,105 @@ napi_value DequantizeStatic(napi_env env, napi_callback_info info) {
   return check(env, a.ctx(0), tfjs_cuda_dequantize_static(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.f64(4), a.f64(5), a.u64(6), a.i32(7)));
 }
 
+napi_value BatchNormRows(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  return check(env, a.ctx(0), tfjs_cuda_batchnorm_rows(a.ctx(0), a.i32(1), a.u64(2), a.u64(3), a.i32(4), a.i32(5),
+      a.i32(6), a.i32(7), a.i32(8), a.i32(9), a.i32(10), a.i32(11), a.f64(12), a.i32(13)));
+}
+
+// ---- the rest of the storage contract ------------------------------------------
+napi_value DeviceCount(napi_env env, napi_callback_info info) {
+  int n = 0; tfjs_cuda_device_count(&n); return num(env, n);
+}
+napi_value Upload(napi_env env, napi_callback_info info) {
+  Args a(env, info); int32_t id = 0;
+  check(env, a.ctx(0), tfjs_cuda_upload(a.ctx(0), a.buffer(1), a.u64(2), &id));
+  return num(env, id);
+}
+napi_value ReadAsync(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  return check(env, a.ctx(0), tfjs_cuda_read_async(a.ctx(0), a.i32(1), a.buffer(2), a.u64(3)));
+}
+napi_value SizeOf(napi_env env, napi_callback_info info) {
+  Args a(env, info); uint64_t n = 0;
+  check(env, a.ctx(0), tfjs_cuda_size_of(a.ctx(0), a.i32(1), &n));
+  return num(env, (double)n);
+}
+napi_value DevicePtr(napi_env env, napi_callback_info info) {
+  Args a(env, info); void* p = nullptr;
+  check(env, a.ctx(0), tfjs_cuda_device_ptr(a.ctx(0), a.i32(1), &p));
+  napi_value r; napi_create_bigint_uint64(env, (uint64_t)(uintptr_t)p, &r); return r;
+}
+napi_value Trim(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_trim(a.ctx(0)));
+}
+// Pinned staging memory as an ArrayBuffer; released with hostFree (the finaliser does
+// nothing, so a buffer that is merely dropped stays pinned until the context goes).
+napi_value HostAlloc(napi_env env, napi_callback_info info) {
+  Args a(env, info); void* p = nullptr;
+  const uint64_t n = a.u64(1);
+  check(env, a.ctx(0), tfjs_cuda_host_alloc(a.ctx(0), n, &p));
+  napi_value ab;
+  napi_create_external_arraybuffer(env, p, (size_t)n, nullptr, nullptr, &ab);
+  return ab;
+}
+napi_value HostFree(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  return check(env, a.ctx(0), tfjs_cuda_host_free(a.ctx(0), a.buffer(1)));
+}
+napi_value EventRecord(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_event_record(a.ctx(0), a.i32(1)));
+}
+napi_value EventElapsed(napi_env env, napi_callback_info info) {
+  Args a(env, info); float ms = 0;
+  check(env, a.ctx(0), tfjs_cuda_event_elapsed(a.ctx(0), a.i32(1), a.i32(2), &ms));
+  return num(env, ms);
+}
+napi_value LaunchCount(napi_env env, napi_callback_info info) {
+  Args a(env, info); uint64_t n = 0;
+  check(env, a.ctx(0), tfjs_cuda_launch_count(a.ctx(0), &n));
+  return num(env, (double)n);
+}
+napi_value LaunchLog(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_launch_log(a.ctx(0), a.i32(1)));
+}
+napi_value LaunchLogTake(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  char text[4096]; uint32_t n = 0;
+  check(env, a.ctx(0), tfjs_cuda_launch_log_take(a.ctx(0), text, sizeof text, &n));
+  napi_value r; napi_create_string_utf8(env, text, NAPI_AUTO_LENGTH, &r); return r;
+}
+napi_value FlushL2(napi_env env, napi_callback_info info) {
+  Args a(env, info); return check(env, a.ctx(0), tfjs_cuda_flush_l2(a.ctx(0)));
+}
+
+// ---- weight loader: the entry list is an ArrayBuffer of packed tfjs_cuda_weight_spec ---
+napi_value WeightsBegin(napi_env env, napi_callback_info info) {
+  Args a(env, info); size_t len = 0; int32_t loader = 0;
+  auto* specs = static_cast<tfjs_cuda_weight_spec*>(a.buffer(1, &len));
+  check(env, a.ctx(0), tfjs_cuda_weights_begin(a.ctx(0), specs, (int32_t)(len / sizeof(tfjs_cuda_weight_spec)), &loader));
+  return num(env, loader);
+}
+napi_value WeightsPush(napi_env env, napi_callback_info info) {
+  Args a(env, info); size_t len = 0;
+  void* p = a.buffer(2, &len);
+  return check(env, a.ctx(0), tfjs_cuda_weights_push(a.ctx(0), a.i32(1), p, (uint64_t)len));
+}
+napi_value WeightsPushFile(napi_env env, napi_callback_info info) {
+  Args a(env, info); char path[4096]; size_t n = 0;
+  napi_get_value_string_utf8(env, a.v[2], path, sizeof path, &n);
+  return check(env, a.ctx(0), tfjs_cuda_weights_push_file(a.ctx(0), a.i32(1), path));
+}
+// weightsEnd(ctx, loader, ids: Int32Array | null): null abandons the load
+napi_value WeightsEnd(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  napi_valuetype t; napi_typeof(env, a.v[2], &t);
+  int32_t* ids = t == napi_null || t == napi_undefined ? nullptr : static_cast<int32_t*>(a.buffer(2));
+  uint64_t bytes = 0;
+  check(env, a.ctx(0), tfjs_cuda_weights_end(a.ctx(0), a.i32(1), ids, &bytes));
+  return num(env, (double)bytes);
+}
+
 napi_value Init(napi_env env, napi_value exports) {
   struct { const char* name; napi_callback fn; } table[] = {
       {"create", Create}, {"alloc", Alloc}, {"free", Free}, {"write", Write}, {"read", Read},
@@ -279,7 +378,14 @@ napi_value Init(napi_env env, napi_value exports) {
       {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm}, {"softmaxScaledMasked", SoftmaxScaledMasked},
       {"reduce", Reduce}, {"argMax", ArgMax}, {"transpose", Transpose}, {"gather", Gather},
       {"cast", Cast}, {"copyStrided", CopyStrided}, {"fill", Fill}, {"batchNorm", BatchNorm},
-      {"dequantize", Dequantize}, {"dequantizeStatic", DequantizeStatic}};
+      {"dequantize", Dequantize}, {"dequantizeStatic", DequantizeStatic},
+      {"batchNormRows", BatchNormRows}, {"deviceCount", DeviceCount}, {"upload", Upload},
+      {"readAsync", ReadAsync}, {"sizeOf", SizeOf}, {"devicePtr", DevicePtr}, {"trim", Trim},
+      {"hostAlloc", HostAlloc}, {"hostFree", HostFree}, {"eventRecord", EventRecord},
+      {"eventElapsed", EventElapsed}, {"launchCount", LaunchCount}, {"launchLog", LaunchLog},
+      {"launchLogTake", LaunchLogTake}, {"flushL2", FlushL2}, {"weightsBegin", WeightsBegin},
+      {"weightsPush", WeightsPush}, {"weightsPushFile", WeightsPushFile},
+      {"weightsEnd", WeightsEnd}};
   for (auto& e : table) {
     napi_value fn;
     napi_create_function(env, e.name, NAPI_AUTO_LENGTH, e.fn, nullptr, &fn);

@@ -9,13 +9,16 @@ import {backend_util, BackendTimingInfo, DataStorage, DataType, engine, KernelBa
         TensorInfo, TypedArray, util} from '@tensorflow/tfjs-core';
 
 import {binding, Ctx} from './binding';
+import {Desc, Pending, PendingConv, PendingDepthwise} from './pending';
 
 interface Record {
-  id: number;          // device buffer id; 0 = host-resident, not uploaded yet
+  id: number;          // device buffer id; 0 = host-resident or not launched yet
   nbytes: number;
   dtype: DataType;
   refCount: number;
   host?: TypedArray;   // kept for small host-written tensors
+  pending?: Pending;   // a deferred launch produces this tensor (pending.ts)
+  held: number;        // how many of refCount belong to pending launches that read it
 }
 
 const HOST_RESIDENT_BYTES = 4096;
@@ -29,6 +32,12 @@ function bytesPerElement(dtype: DataType): number {
 export class CudaBackend extends KernelBackend {
   readonly ctx: Ctx;
   private data: DataStorage<Record>;
+  private hidden = 0;           // records kept alive only by pending launches
+  private logDepth = 0;
+  /** chain signature -> the library has a straight-line kernel for it */
+  readonly ewCatalogue = new Map<string, boolean>();
+  /** Deferred launches; TFJS_CUDA_NO_LAZY_FUSION=1 launches every kernel when called. */
+  lazyFusion = !['1', 'true'].includes(process.env['TFJS_CUDA_NO_LAZY_FUSION'] ?? '0');
 
   constructor(readonly deviceOrdinal = 0) {
     super();
@@ -49,37 +58,104 @@ export class CudaBackend extends KernelBackend {
     if (typed != null && nbytes <= HOST_RESIDENT_BYTES) {
       // The graph executor reads axis / shape / perm constants with dataSync() in its
       // node loop; host-resident small tensors keep those reads off the stream.
-      this.data.set(dataId, {id: 0, nbytes, dtype, refCount, host: typed.slice()});
+      this.data.set(dataId, {id: 0, nbytes, dtype, refCount, host: typed.slice(), held: 0});
       return;
     }
     const id = binding.alloc(this.ctx, nbytes);
     if (typed != null && nbytes > 0) binding.write(this.ctx, id, typed, nbytes);
-    this.data.set(dataId, {id, nbytes, dtype, refCount});
+    this.data.set(dataId, {id, nbytes, dtype, refCount, held: 0});
+  }
+
+  /** A tensor over a device buffer the library made (the weight loader's results). */
+  adopt(id: number, shape: number[], dtype: DataType): TensorInfo {
+    const dataId = {};
+    const nbytes = util.sizeFromShape(shape) * bytesPerElement(dtype);
+    this.data.set(dataId, {id, nbytes, dtype, refCount: 1, held: 0});
+    return {dataId, shape, dtype};
   }
 
   /** Allocates an uninitialised device tensor for a kernel result. */
   makeOutput(shape: number[], dtype: DataType): TensorInfo {
     const nbytes = util.sizeFromShape(shape) * bytesPerElement(dtype);
     const dataId = {};
-    this.data.set(dataId, {id: binding.alloc(this.ctx, nbytes), nbytes, dtype, refCount: 1});
+    this.data.set(dataId, {id: binding.alloc(this.ctx, nbytes), nbytes, dtype, refCount: 1, held: 0});
     return {dataId, shape, dtype};
   }
 
-  /** Device buffer id of a tensor (0 for an absent optional input). */
-  deviceId(t?: TensorInfo): number {
-    if (t == null) return 0;
-    const r = this.data.get(t.dataId);
-    if (r.id === 0) {
+  // ------------------------------------------------------------ deferred launches --
+  /** Changes a record's counts, tracking whether only pending launches keep it alive
+   * (such records are not reported by numDataIds). */
+  private adjust(r: Record, dRef: number, dHeld: number): void {
+    const was = r.held > 0 && r.refCount <= r.held;
+    r.refCount += dRef;
+    r.held += dHeld;
+    const now = r.held > 0 && r.refCount <= r.held;
+    if (was !== now) this.hidden += now ? 1 : -1;
+  }
+
+  /** Output tensor of a kernel whose launch is deferred; its inputs stay alive until the
+   * launch happened or the output was disposed. */
+  defer(shape: number[], dtype: DataType, pending: Pending): TensorInfo {
+    const nbytes = util.sizeFromShape(shape) * bytesPerElement(dtype);
+    const dataId = {};
+    for (const d of pending.deps()) this.adjust(this.data.get(d), 1, 1);
+    this.data.set(dataId, {id: 0, nbytes, dtype, refCount: 1, pending, held: 0});
+    return {dataId, shape, dtype};
+  }
+
+  pendingOf(t: TensorInfo): Pending|undefined { return this.data.get(t.dataId).pending; }
+
+  /** The pending convolution behind `t` with `act` as the last step of its epilogue, as a
+   * new pending tensor; `t` itself stays pending (another consumer launches it without). */
+  withActivation(t: TensorInfo, act: 'relu'|'relu6', desc: Desc): TensorInfo {
+    const p = this.data.get(t.dataId).pending as PendingConv|PendingDepthwise;
+    return this.defer(t.shape, 'float32', p.withAct(act, desc));
+  }
+
+  private release(pending: Pending): void {
+    for (const d of pending.deps()) {
+      const r = this.data.get(d);
+      this.adjust(r, -1, -1);
+      if (r.refCount <= 0) this.drop(d, r);
+    }
+  }
+
+  private resolve(r: Record): void {
+    const pending = r.pending!;
+    const dev = binding.alloc(this.ctx, r.nbytes);
+    try {
+      pending.launch(this, dev);
+    } catch (e) {
+      binding.free(this.ctx, dev);
+      throw e;
+    }
+    r.id = dev;
+    r.pending = undefined;
+    this.release(pending);
+  }
+
+  /** Device buffer id behind a dataId: launches a pending producer or uploads a
+   * host-resident tensor first. */
+  deviceIdOf(dataId: object): number {
+    const r = this.data.get(dataId);
+    if (r.pending != null) {
+      this.resolve(r);
+    } else if (r.id === 0) {
       r.id = binding.alloc(this.ctx, r.nbytes);
-      if (r.nbytes > 0) binding.write(this.ctx, r.id, r.host, r.nbytes);
+      if (r.nbytes > 0) binding.write(this.ctx, r.id, r.host!, r.nbytes);
     }
     return r.id;
   }
 
+  /** Device buffer id of a tensor (0 for an absent optional input). */
+  deviceId(t?: TensorInfo): number { return t == null ? 0 : this.deviceIdOf(t.dataId); }
+
   hostValues(t: TensorInfo): TypedArray|undefined { return this.data.get(t.dataId).host; }
 
+  // ------------------------------------------------------------------------ data --
   override readSync(dataId: object): backend_util.BackendValues {
     const r = this.data.get(dataId);
+    if (r.pending != null) this.resolve(r);
     if (r.host != null) return r.host.slice();
     const out = util.getTypedArrayFromDType(r.dtype as 'float32', r.nbytes / bytesPerElement(r.dtype));
     binding.read(this.ctx, r.id, out, r.nbytes);
@@ -90,6 +166,7 @@ export class CudaBackend extends KernelBackend {
    *  later turn of the event loop, so code between `data()` and `await` keeps launching. */
   override read(dataId: object): Promise<backend_util.BackendValues> {
     const r = this.data.get(dataId);
+    if (r.pending != null) this.resolve(r);
     if (r.host != null) return Promise.resolve(r.host.slice());
     const out = util.getTypedArrayFromDType(r.dtype as 'float32', r.nbytes / bytesPerElement(r.dtype));
     const ticket = binding.readBegin(this.ctx, r.id, out, r.nbytes);
@@ -101,19 +178,31 @@ export class CudaBackend extends KernelBackend {
   override disposeData(dataId: object, force = false): boolean {
     if (!this.data.has(dataId)) return false;
     const r = this.data.get(dataId);
-    r.refCount--;
-    if (!force && r.refCount > 0) return false;
-    if (r.id !== 0) binding.free(this.ctx, r.id);
-    this.data.delete(dataId);
+    this.adjust(r, -1, 0);
+    if (r.refCount > 0 && (!force || r.held > 0)) return false;
+    this.drop(dataId, r);
     return true;
   }
 
-  override refCount(dataId: object): number {
-    return this.data.has(dataId) ? this.data.get(dataId).refCount : 0;
+  private drop(dataId: object, r: Record): void {
+    if (r.held > 0 && r.refCount <= r.held) this.hidden--;
+    this.data.delete(dataId);
+    if (r.id !== 0) binding.free(this.ctx, r.id);
+    if (r.pending != null) {
+      const p = r.pending;
+      r.pending = undefined;
+      this.release(p);
+    }
   }
-  override incRef(dataId: object): void { this.data.get(dataId).refCount++; }
-  decRef(dataId: object): void { if (this.data.has(dataId)) this.data.get(dataId).refCount--; }
-  override numDataIds(): number { return this.data.numDataIds(); }
+
+  override refCount(dataId: object): number {
+    if (!this.data.has(dataId)) return 0;
+    const r = this.data.get(dataId);
+    return r.refCount - r.held;
+  }
+  override incRef(dataId: object): void { this.adjust(this.data.get(dataId), 1, 0); }
+  decRef(dataId: object): void { if (this.data.has(dataId)) this.adjust(this.data.get(dataId), -1, 0); }
+  override numDataIds(): number { return this.data.numDataIds() - this.hidden; }
 
   /** Zero-copy view: same dataId, one more reference. */
   view(t: TensorInfo, shape: number[], dtype = t.dtype): TensorInfo {
@@ -123,10 +212,30 @@ export class CudaBackend extends KernelBackend {
 
   override memory() { return {unreliable: false, ...binding.memory(this.ctx)}; }
 
+  // ---------------------------------------------------------------------- timing --
+  /** Turns the library's launch log on or off (calls nest). */
+  launchLog(enable: boolean): void {
+    this.logDepth += enable ? 1 : -1;
+    if (enable && this.logDepth === 1) binding.launchLog(this.ctx, 1);
+    if (!enable && this.logDepth === 0) binding.launchLog(this.ctx, 0);
+  }
+
+  /** BackendTimingInfo (tfjs-core/src/backends/backend.ts:26-30): kernelMs from CUDA events
+   * on the stream; getExtraProfileInfo names the kernel instantiations launched inside f,
+   * which tf.profile prints per kernel (tfjs-core/src/profiler.ts:74-76). */
   override async time(f: () => void): Promise<BackendTimingInfo> {
-    binding.timeBegin(this.ctx);
-    f();
-    return {kernelMs: binding.timeEnd(this.ctx)};
+    const nested = this.logDepth > 0;
+    this.launchLog(true);
+    let kernelMs: number, info = '';
+    try {
+      binding.timeBegin(this.ctx);
+      f();
+      kernelMs = binding.timeEnd(this.ctx);
+      if (!nested) info = binding.launchLogTake(this.ctx);
+    } finally {
+      this.launchLog(false);
+    }
+    return {kernelMs, getExtraProfileInfo: () => info};
   }
   override timerAvailable(): boolean { return true; }
   override floatPrecision(): 16|32 { return 32; }

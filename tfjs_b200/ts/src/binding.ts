@@ -72,6 +72,27 @@ export interface CudaBinding {
              n: number, out: number): void;
   dequantizeStatic(ctx: Ctx, qBytes: number, toDtype: number, q: number, scale: number,
                    min: number, n: number, out: number): void;
+  batchNormRows(ctx: Ctx, x: number, rows: number, cols: number, mean: number, meanMode: number,
+                variance: number, varMode: number, scale: number, scaleMode: number,
+                offset: number, offsetMode: number, eps: number, out: number): void;
+  deviceCount(): number;
+  upload(ctx: Ctx, data: ArrayBufferView, nbytes: number): number;
+  readAsync(ctx: Ctx, id: number, out: ArrayBufferView, nbytes: number): void;
+  sizeOf(ctx: Ctx, id: number): number;
+  devicePtr(ctx: Ctx, id: number): bigint;
+  trim(ctx: Ctx): void;
+  hostAlloc(ctx: Ctx, nbytes: number): ArrayBuffer;
+  hostFree(ctx: Ctx, buffer: ArrayBuffer): void;
+  eventRecord(ctx: Ctx, slot: number): void;
+  eventElapsed(ctx: Ctx, slotBegin: number, slotEnd: number): number;
+  launchCount(ctx: Ctx): number;
+  launchLog(ctx: Ctx, enable: number): void;
+  launchLogTake(ctx: Ctx): string;
+  flushL2(ctx: Ctx): void;
+  weightsBegin(ctx: Ctx, specs: ArrayBuffer): number;
+  weightsPush(ctx: Ctx, loader: number, chunk: ArrayBufferView|ArrayBuffer): void;
+  weightsPushFile(ctx: Ctx, loader: number, path: string): void;
+  weightsEnd(ctx: Ctx, loader: number, ids: Int32Array|null): number;
 }
 
 export const binding = addon as CudaBinding;
@@ -86,6 +107,57 @@ export const UNARY_OP = {Relu: 0, Relu6: 1, Elu: 2, Sigmoid: 3, LeakyRelu: 4, Ex
                          Rsqrt: 7, Square: 8, Tanh: 9, Neg: 10, ClipByValue: 11, Erf: 12, Abs: 13,
                          Log: 14};
 export const REDUCE_OP = {Sum: 0, Mean: 1, Max: 2};
+export const WEIGHT_STORAGE = {raw: 0, uint8: 1, uint16: 2, float16: 3};
+export const EW = {FULL: 0, PERIODIC: 1, ROW: 2, SCALAR: 3, BATCHED: 4, MAX_INPUTS: 8,
+                   MAX_OPS: 24, UNARY: 32};
+export const STATUS_UNSUPPORTED = 5;
+
+/** tfjs_cuda_weight_spec: u64 n, i32 storage, i32 dtype, f64 scale, f64 min, i32 skip,
+ * i32 reserved = 40 bytes per entry. */
+export function packWeightSpecs(
+    entries: Array<{n: number, storage: number, dtype: number, scale: number, min: number,
+                    skip: boolean}>): ArrayBuffer {
+  const buf = new ArrayBuffer(40 * entries.length);
+  const v = new DataView(buf);
+  entries.forEach((e, i) => {
+    const o = 40 * i;
+    v.setBigUint64(o, BigInt(e.n), true);
+    v.setInt32(o + 8, e.storage, true);
+    v.setInt32(o + 12, e.dtype, true);
+    v.setFloat64(o + 16, e.scale, true);
+    v.setFloat64(o + 24, e.min, true);
+    v.setInt32(o + 32, e.skip ? 1 : 0, true);
+  });
+  return buf;
+}
+
+/** tfjs_cuda_ew_program: i32 n_inputs, i32 n_ops, u64 n, u32 cols, u32 reserved, then
+ * input_id[8], input_mode[8], input_period[8], input_aux[8] (4 bytes each) and 24 ops of
+ * {i16 opcode, u8 a, u8 b, f32 p0, f32 p1} = 24 + 4 * 32 + 24 * 12 = 440 bytes. */
+export function packEwProgram(p: {
+  n: number, cols: number, inputs: Array<{id: number, mode: number, period: number, aux: number}>,
+  ops: Array<{opcode: number, a: number, b: number}>
+}): ArrayBuffer {
+  const buf = new ArrayBuffer(440);
+  const v = new DataView(buf);
+  v.setInt32(0, p.inputs.length, true);
+  v.setInt32(4, p.ops.length, true);
+  v.setBigUint64(8, BigInt(p.n), true);
+  v.setUint32(16, p.cols, true);
+  p.inputs.forEach((inp, k) => {
+    v.setInt32(24 + 4 * k, inp.id, true);
+    v.setInt32(56 + 4 * k, inp.mode, true);
+    v.setUint32(88 + 4 * k, inp.period, true);
+    v.setUint32(120 + 4 * k, inp.aux, true);
+  });
+  p.ops.forEach((op, j) => {
+    const o = 152 + 12 * j;
+    v.setInt16(o, op.opcode, true);
+    v.setUint8(o + 2, op.a);
+    v.setUint8(o + 3, op.b);
+  });
+  return buf;
+}
 
 /** tfjs_cuda_conv2d_params: 18 int32 fields, 4 bytes of padding, one double. */
 export function packConvParams(

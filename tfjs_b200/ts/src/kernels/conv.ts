@@ -7,6 +7,7 @@ import {backend_util, Conv2D, DepthwiseConv2dNative, FusedConv2D, FusedDepthwise
 
 import {CudaBackend} from '../backend_cuda';
 import {ACTIVATION, binding, packConvParams} from '../binding';
+import {PendingConv, PendingDepthwise} from '../pending';
 import {applyActivation, binaryImpl} from './elementwise';
 
 /** 1 for a scalar, `channels` when the tensor broadcasts along the last axis, else null. */
@@ -38,6 +39,21 @@ function convImpl(
   const params = packConvParams(
       convInfo, ACTIVATION[fuseAct ? activation : 'linear'], fuseBias ? biasLen : 0,
       fuseAct ? (preluLen ?? 0) : 0, (attrs['leakyreluAlpha'] as number) ?? 0.2);
+  if (backend.lazyFusion && fuseBias && activation === 'linear' &&
+      util.sizeFromShape(convInfo.outShape) > 0) {
+    // Deferred: a following Add (residual, or the bias of a depthwise convolution) and
+    // Relu / Relu6 / clip fold into this launch's epilogue (kernels/elementwise.ts).
+    const inputShapes: {[k: string]: number[]} = {x: x.shape, filter: filter.shape};
+    if (bias != null) inputShapes['bias'] = bias.shape;
+    const desc = {
+      name: depthwise ? (bias != null ? FusedDepthwiseConv2D : DepthwiseConv2dNative) : FusedConv2D,
+      inputShapes, outputShapes: [convInfo.outShape]
+    };
+    const pending = depthwise ?
+        new PendingDepthwise(params, x.dataId, filter.dataId, bias != null ? bias.dataId : null, [desc]) :
+        new PendingConv(params, x.dataId, filter.dataId, bias != null ? bias.dataId : null, null, [desc]);
+    return backend.defer(convInfo.outShape, 'float32', pending);
+  }
   let out = backend.makeOutput(convInfo.outShape, 'float32');
   const launch = depthwise ? binding.fusedDepthwiseConv2d : binding.fusedConv2d;
   launch(backend.ctx, params, backend.deviceId(x), backend.deviceId(filter),

@@ -7,6 +7,7 @@ import {backend_util, KernelConfig, KernelFunc, slice_util, TensorInfo, util} fr
 
 import {CudaBackend} from '../backend_cuda';
 import {binding, i64, packConvParams, REDUCE_OP} from '../binding';
+import {PendingTile} from '../pending';
 import {castImpl} from './elementwise';
 
 type Args = {inputs: {[k: string]: TensorInfo}, attrs: {[k: string]: unknown}, backend: CudaBackend};
@@ -175,7 +176,15 @@ export const otherConfigs: KernelConfig[] = [
   })},
   {kernelName: 'Tile', backendName: 'cuda', kernelFunc: asFunc(({inputs, attrs, backend}) => {
     const x = inputs['x'];
-    const outShape = x.shape.map((s, i) => s * (attrs['reps'] as number[])[i]);
+    const reps = attrs['reps'] as number[];
+    const outShape = x.shape.map((s, i) => s * reps[i]);
+    if (backend.lazyFusion && x.dtype === 'float32' && util.sizeFromShape(outShape) > 0 &&
+        outShape.length <= 6 && backend.pendingOf(x) == null) {
+      // Deferred: a batch normalisation that can index the untiled tensor never needs it
+      return backend.defer(outShape, x.dtype, new PendingTile(
+          x.dataId, x.shape, reps, outShape, x.dtype,
+          [{name: 'Tile', inputShapes: {x: x.shape}, outputShapes: [outShape]}]));
+    }
     const out = backend.makeOutput(outShape, x.dtype);
     if (util.sizeFromShape(outShape) > 0) copyStrided(backend, x, 0, out, 0, strides(outShape), outShape);
     return out;
