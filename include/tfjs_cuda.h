@@ -177,6 +177,26 @@ int tfjs_cuda_fused_conv2d_residual(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_p
                                     int32_t prelu_id, int32_t residual_id,
                                     int32_t post_activation, int32_t out_id);
 
+/* FusedDepthwiseConv2D (3x3, stride 1 or 2, bias, activation) and the 1x1 FusedConv2D that
+ * consumes its result, as one launch: the depthwise result (the widest tensor of an
+ * inverted-residual block) is produced tile by tile in shared memory as the projection's
+ * operand and never written.  Each value goes through the roundings of the two separate
+ * kernels (tfjs-backend-cpu/src/kernels/FusedDepthwiseConv2D.ts:25-61 then
+ * FusedConv2D.ts:26-95): fp32 per-tap accumulation, bias, activation, then the TF32
+ * rounding the projection applies to its input.  Optionally
+ *   out = post_activation(residual + act(conv1x1(depthwise(x)) + bias))
+ * as in tfjs_cuda_fused_conv2d_residual (residual_id 0 = none).  `dw` describes the
+ * depthwise convolution, `pw` the 1x1 convolution over its output.  Returns
+ * TFJS_CUDA_UNSUPPORTED for shapes the kernel does not take (other filter sizes, strides,
+ * dilations, channel multipliers, the fp32 math mode); the host layer then launches the two
+ * kernels separately. */
+int tfjs_cuda_fused_depthwise_project(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* dw,
+                                      const tfjs_cuda_conv2d_params* pw, int32_t x_id,
+                                      int32_t dw_filter_id, int32_t dw_bias_id,
+                                      int32_t pw_filter_id, int32_t pw_bias_id,
+                                      int32_t residual_id, int32_t post_activation,
+                                      int32_t out_id);
+
 /* ---- whole-step capture and replay ----------------------------------------------------
  * The graph executor launches the same kernels with the same shapes at every
  * GraphModel.execute (tfjs-converter/src/executor/graph_executor.ts:228-310).  Between

@@ -12,8 +12,11 @@ one launch through the deferred-launch path), gelu_<rows>_<cols> (x * 0.5 * (1 +
 sqrt 2)): five elementwise kernels, one catalogued chain launch), ln_<rows>_<cols> (LayerNorm
 tail ((x - mean) * rstd) * gamma + beta: four kernels, one chain launch), lnf_<rows>_<cols>
 (residual Add + the whole layer normalisation: ten kernels of the reference, one launch),
-sm_<rows>_<cols> (softmax of scaled, masked attention scores, rows a multiple of 1536).  Prints ms, TFLOP/s
+sm_<rows>_<cols> (softmax of scaled, masked attention scores, rows a multiple of 1536),
+dwp_<hw>_<c>_<n>_<batch>_<stride>[_res] (3x3 depthwise + relu6 and the 1x1 projection behind it,
+optionally + shortcut: one launch).  Prints ms, TFLOP/s
 and algorithmic GB/s (each tensor moved once).
+Times are device times of graph replays (n calls per graph, best of three replays).
 """
 import sys
 
@@ -26,10 +29,30 @@ eng=tfjs_b200.ENGINE; eng.set_backend('cuda'); be=eng.backend
 case=sys.argv[1]; iters=int(sys.argv[2]) if len(sys.argv)>2 else 3
 r=np.random.default_rng(0)
 def timeit(f, n):
-    for _ in range(2): f().dispose()
+    """ms per call: n calls captured into one CUDA graph and the graph replayed, so the
+    figure is device time even for kernels shorter than a host-side call (eager launches
+    are timed instead when the capture is refused)."""
+    for _ in range(2):
+        y=f(); be.device_id(y.dataId); nbytes=be.data[y.dataId].nbytes; y.dispose()
     be.sync()
-    t=be.time(lambda: [f().dispose() for _ in range(n)])
-    return t['kernelMs']/n
+    be.high_water_reset(); y=f(); be.device_id(y.dataId); y.dispose(); be.sync()
+    peak=be.memory()['poolHighWater']
+    try:
+        be.capture_begin(int(peak*1.5)+(16<<20))
+        for _ in range(n):
+            y=f(); be.device_id(y.dataId); y.dispose()
+        graph=be.capture_end(False)
+    except Exception:
+        try: be.capture_end(True)
+        except Exception: pass
+        def eager():
+            for _ in range(n):
+                y=f(); be.device_id(y.dataId); y.dispose()
+        return be.time(eager)['kernelMs']/n
+    be.graph_launch(graph); be.sync()
+    best=min(be.time(lambda: be.graph_launch(graph))['kernelMs'] for _ in range(3))
+    be.graph_destroy(graph)
+    return best/n
 if case=='mm2a':
     a=ops.tensor(r.standard_normal((4096,1024)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((1024,4096)).astype(np.float32)/32)
     bias=ops.tensor(r.standard_normal(4096).astype(np.float32))
@@ -95,10 +118,23 @@ elif case.startswith('stem'):   # stem_<hw>_<k>_<cout>_<batch>_<stride>
     x=ops.tensor(r.standard_normal((bt,hw,hw,3)).astype(np.float32)); w=ops.tensor(r.standard_normal((k,k,3,co)).astype(np.float32)/8)
     bias=ops.tensor(r.standard_normal(co).astype(np.float32))
     f=lambda: ops.fused_conv2d(x,w,st,'same','NHWC',[1,1],None,bias,'relu6'); ho=(hw+st-1)//st; fl=2*bt*ho*ho*k*k*3*co; by=4*(bt*hw*hw*3+bt*ho*ho*co)
-elif case.startswith('dw'):   # depthwise: dw_<hw>_<c>_<batch>_<stride>
+elif case.startswith('dw_'):   # depthwise: dw_<hw>_<c>_<batch>_<stride>
     _,hw,c,bt,st=case.split('_'); hw,c,bt,st=int(hw),int(c),int(bt),int(st)
     x=ops.tensor(r.standard_normal((bt,hw,hw,c)).astype(np.float32)); w=ops.tensor(r.standard_normal((3,3,c,1)).astype(np.float32)/3)
     bias=ops.tensor(r.standard_normal(c).astype(np.float32))
     f=lambda: ops.fused_depthwise_conv2d(x,w,st,'same','NHWC',[1,1],None,bias,'relu6'); ho=(hw+st-1)//st; fl=2*bt*ho*ho*9*c; by=4*(bt*hw*hw*c+bt*ho*ho*c)
+elif case.startswith('dwp'):   # dwp_<hw>_<c>_<n>_<batch>_<stride>[_res]: 3x3 depthwise + relu6, then 1x1 projection (+ shortcut)
+    parts=case.split('_'); hw,c,n,bt,st=[int(v) for v in parts[1:6]]; res=len(parts)>6
+    x=ops.tensor(r.standard_normal((bt,hw,hw,c)).astype(np.float32)); wd=ops.tensor(r.standard_normal((3,3,c,1)).astype(np.float32)/3)
+    bd=ops.tensor(r.standard_normal(c).astype(np.float32)); wp=ops.tensor(r.standard_normal((1,1,c,n)).astype(np.float32)/8)
+    bp=ops.tensor(r.standard_normal(n).astype(np.float32)); ho=(hw+st-1)//st
+    sc=ops.tensor(r.standard_normal((bt,ho,ho,n)).astype(np.float32)) if res else None
+    def f():
+        h=ops.fused_depthwise_conv2d(x,wd,st,'same','NHWC',[1,1],None,bd,'relu6')
+        y=ops.fused_conv2d(h,wp,1,'same','NHWC',[1,1],None,bp,'linear'); h.dispose()
+        if sc is not None:
+            s2=ops.add(sc,y); y.dispose(); y=s2
+        return y
+    fl=2*bt*ho*ho*c*(9+n); by=4*(bt*hw*hw*c+bt*ho*ho*n*(2 if res else 1))
 ms=timeit(f,iters)
 print('%s: %.4f ms  %.1f TFLOP/s  %.1f GB/s (algorithmic)'%(case,ms,fl/ms/1e9,by/ms/1e6))

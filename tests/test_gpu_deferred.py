@@ -282,7 +282,7 @@ def test_time_reports_kernel_ms_and_extra_profile_info(cuda_engine):
     info = cuda_engine.backend.time(work)
     assert info["kernelMs"] > 0 and info["wallMs"] >= info["kernelMs"] * 0.5
     text = info["getExtraProfileInfo"]()
-    assert "gemm_tf32_kernel<" in text and "softmax_kernel" in text
+    assert "gemm_tf32_" in text and "softmax_kernel" in text
     # the log is off again: nothing accumulates outside time() / profile()
     tf.relu(a).dispose()
     assert cuda_engine.backend.launch_log_take() == ""

@@ -112,6 +112,8 @@ SIGNATURES = {
     "tfjs_cuda_read_begin": (c_int, [_CTX, c_int32, c_void_p, c_uint64, POINTER(c_int32)]),
     "tfjs_cuda_read_wait": (c_int, [_CTX, c_int32]),
     "tfjs_cuda_fused_conv2d_residual": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 7),
+    "tfjs_cuda_fused_depthwise_project": (c_int, [_CTX, POINTER(Conv2DParams), POINTER(Conv2DParams)]
+                                          + [c_int32] * 8),
     "tfjs_cuda_add_activation": (c_int, [_CTX, c_int32, c_int32, c_int32, c_uint64, c_int32]),
     "tfjs_cuda_fused_depthwise_conv2d": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 5),
     "tfjs_cuda_fused_matmul": (c_int, [_CTX, POINTER(MatMulParams)] + [c_int32] * 5),

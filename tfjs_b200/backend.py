@@ -92,13 +92,14 @@ class PendingConv(object):
     """A FusedConv2D (bias fused, linear activation) not launched yet, optionally with
     the operand of the Add that consumed it and the activation that followed (`act`:
     linear, relu or relu6, applied last)."""
-    __slots__ = ("params", "x", "filt", "bias", "residual", "desc", "act")
+    __slots__ = ("params", "x", "filt", "bias", "residual", "desc", "act", "dw_folded")
 
     def __init__(self, params, x, filt, bias, residual, desc, act="linear"):
         self.params, self.x, self.filt, self.bias = params, x, filt, bias
         self.residual = residual
         self.desc = desc      # profile records of the kernels folded into this launch
         self.act = act
+        self.dw_folded = False
 
     def deps(self):
         return [d for d in (self.x, self.filt, self.bias, self.residual) if d is not None]
@@ -107,9 +108,59 @@ class PendingConv(object):
         return PendingConv(self.params, self.x, self.filt, self.bias, self.residual,
                            self.desc + [desc], act)
 
+    def _launch_with_depthwise(self, backend, out_dev, post_act):
+        """If the input is a depthwise convolution that is still pending and this is the
+        1x1 convolution behind it (the projection of an inverted-residual block), both run
+        as one launch and the depthwise result is never written.  False when the pair is
+        not of that form or the library does not take the shapes."""
+        rec = backend.data.get(self.x)
+        dw = rec.pending if rec is not None else None
+        p = self.params
+        if not (backend.fuse_depthwise_project and isinstance(dw, PendingDepthwise)):
+            return False
+        d = dw.params
+        if not (d.filter_h == 3 and d.filter_w == 3 and d.stride_h == d.stride_w and d.stride_h in (1, 2) and
+                d.dilation_h == 1 and d.dilation_w == 1 and d.out_c == d.in_c and
+                d.in_c % 4 == 0 and dw.act in ("linear", "relu", "relu6") and
+                p.filter_h == 1 and p.filter_w == 1 and p.stride_h == 1 and p.stride_w == 1 and
+                p.pad_top == 0 and p.pad_left == 0 and p.out_h == p.in_h and
+                p.out_w == p.in_w and p.out_c % 4 == 0 and 8 <= p.out_c <= 512 and
+                (self.residual is not None or post_act == "linear" or
+                 p.activation == _cabi.ACTIVATIONS["linear"])):
+            return False
+        dp = _cabi.Conv2DParams.from_buffer_copy(d)
+        dp.activation = _cabi.ACTIVATIONS[dw.act]
+        pp = p
+        post = _cabi.ACTIVATIONS["linear"]
+        if self.residual is not None:
+            post = _cabi.ACTIVATIONS[post_act]
+        elif post_act != "linear":
+            pp = _cabi.Conv2DParams.from_buffer_copy(p)
+            pp.activation = _cabi.ACTIVATIONS[post_act]
+        rc = backend.lib.tfjs_cuda_fused_depthwise_project(
+            backend.ctx, byref(dp), byref(pp), backend.device_id(dw.x),
+            backend.device_id(dw.filt),
+            backend.device_id(dw.bias) if dw.bias is not None else 0,
+            backend.device_id(self.filt),
+            backend.device_id(self.bias) if self.bias is not None else 0,
+            backend.device_id(self.residual) if self.residual is not None else 0, post, out_dev)
+        if rc == _cabi.UNSUPPORTED:
+            return False
+        backend.check(rc)
+        if not self.dw_folded:
+            # profile records: the depthwise kernels join this launch, and the convolution
+            # no longer reads its input from memory
+            own = dict(self.desc[0])
+            own["inputShapes"] = {k: v for k, v in own["inputShapes"].items() if k != "x"}
+            self.desc[:] = [dict(t) for t in dw.desc] + [own] + self.desc[1:]
+            self.dw_folded = True
+        return True
+
     def launch(self, backend, out_dev, post_act):
         lib, p = backend.lib, self.params
         post_act = self.act if post_act == "linear" else post_act
+        if self._launch_with_depthwise(backend, out_dev, post_act):
+            return
         bias = backend.device_id(self.bias) if self.bias is not None else 0
         if self.residual is None:
             if post_act != "linear":
@@ -396,6 +447,9 @@ class CudaBackend(object):
         self._pinned = []
         self._hidden = 0      # records kept alive only by pending launches
         self.lazy_fusion = os.environ.get("TFJS_CUDA_NO_LAZY_FUSION", "0") in ("", "0")
+        # a pending 3x3 depthwise convolution consumed by a 1x1 convolution runs inside that
+        # convolution's launch (TFJS_CUDA_NO_DW_PROJECT=1 keeps the two launches)
+        self.fuse_depthwise_project = os.environ.get("TFJS_CUDA_NO_DW_PROJECT", "0") in ("", "0")
         self.profiler = None  # the engine, while it profiles (told about deferred launches)
         self.ew_catalogue = {}  # chain signature -> the library has a kernel for it
         self._log_depth = 0     # nesting of launch_log(True)

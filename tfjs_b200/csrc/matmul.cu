@@ -135,6 +135,13 @@ int fill_act(tfjs_cuda_ctx* ctx, int activation, int prelu_len, int32_t prelu_id
 
 }  // namespace
 
+// The packed copy of a 1x1 convolution's filter, as conv2d_impl builds it (shared cache
+// entry), for kernels outside this file.
+int packed_pointwise_filter(tfjs_cuda_ctx* ctx, int32_t filter_id, Buffer* w, int out_c, int in_c,
+                            const float** out) {
+  return get_packed(ctx, filter_id, w, 1, out_c, 1, in_c, in_c, 0, out);
+}
+
 extern "C" {
 
 static int matmul_impl(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p, int32_t a_id,

@@ -97,16 +97,19 @@ def _conv_impl(backend, x, filt, bias, prelu, attrs, activation, depthwise):
                 "outputShapes": [list(ci.outShape)], "attrs": {}}
         return backend.defer(ci.outShape, "float32", PendingConv(
             p, x.dataId, filt.dataId, bias.dataId if bias is not None else None, None, [desc]))
-    if (backend.lazy_fusion and depthwise and fuse_bias and activation == "linear" and
-            size_from_shape(ci.outShape) > 0):
+    if (backend.lazy_fusion and depthwise and fuse_bias and
+            activation in ("linear", "relu", "relu6") and size_from_shape(ci.outShape) > 0):
         # Deferred: the bias Add and the Relu / Relu6 that tfjs-layers issues after a
-        # depthwise convolution fold into this launch.
+        # depthwise convolution fold into this launch, and a 1x1 convolution that consumes
+        # the result (the projection of an inverted-residual block) absorbs the whole
+        # depthwise convolution into its own launch.
         desc = {"name": "FusedDepthwiseConv2D" if bias is not None else "DepthwiseConv2dNative",
                 "inputShapes": dict([("x", list(x.shape)), ("filter", list(filt.shape))] +
                                     ([("bias", list(bias.shape))] if bias is not None else [])),
                 "outputShapes": [list(ci.outShape)], "attrs": {}}
         return backend.defer(ci.outShape, "float32", PendingDepthwise(
-            p, x.dataId, filt.dataId, bias.dataId if bias is not None else None, [desc]))
+            p, x.dataId, filt.dataId, bias.dataId if bias is not None else None, [desc],
+            activation))
     out = backend.make_output(ci.outShape, "float32")
     fn = (backend.lib.tfjs_cuda_fused_depthwise_conv2d if depthwise
           else backend.lib.tfjs_cuda_fused_conv2d)

@@ -170,6 +170,19 @@ napi_value FusedConv2DResidual(napi_env env, napi_callback_info info) {
   auto* p = static_cast<tfjs_cuda_conv2d_params*>(a.buffer(1));
   return check(env, a.ctx(0), tfjs_cuda_fused_conv2d_residual(a.ctx(0), p, a.i32(2), a.i32(3), a.i32(4), a.i32(5), a.i32(6), a.i32(7), a.i32(8)));
 }
+// Returns false when the library does not take the shapes (the caller then launches the two
+// kernels separately); other errors throw.
+napi_value FusedDepthwiseProject(napi_env env, napi_callback_info info) {
+  Args a(env, info);  // ctx, dwParams, pwParams, x, dwFilter, dwBias, pwFilter, pwBias, residual, postAct, out
+  auto* dw = static_cast<tfjs_cuda_conv2d_params*>(a.buffer(1));
+  auto* pw = static_cast<tfjs_cuda_conv2d_params*>(a.buffer(2));
+  const int rc = tfjs_cuda_fused_depthwise_project(a.ctx(0), dw, pw, a.i32(3), a.i32(4), a.i32(5), a.i32(6),
+                                                   a.i32(7), a.i32(8), a.i32(9), a.i32(10));
+  napi_value r;
+  napi_get_boolean(env, rc == TFJS_CUDA_OK, &r);
+  if (rc != TFJS_CUDA_OK && rc != TFJS_CUDA_UNSUPPORTED) napi_throw_error(env, nullptr, tfjs_cuda_last_error(a.ctx(0)));
+  return r;
+}
 napi_value AddActivation(napi_env env, napi_callback_info info) {
   Args a(env, info);
   return check(env, a.ctx(0), tfjs_cuda_add_activation(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.u64(4), a.i32(5)));
@@ -373,7 +386,8 @@ napi_value Init(napi_env env, napi_value exports) {
       {"graphDestroy", GraphDestroy}, {"copy", Copy}, {"highWaterReset", HighWaterReset},
       {"readBegin", ReadBegin}, {"readWait", ReadWait}, {"sync", Sync}, {"memory", Memory}, {"timeBegin", TimeBegin}, {"timeEnd", TimeEnd},
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},
-      {"fusedConv2dResidual", FusedConv2DResidual}, {"addActivation", AddActivation},
+      {"fusedConv2dResidual", FusedConv2DResidual}, {"fusedDepthwiseProject", FusedDepthwiseProject},
+      {"addActivation", AddActivation},
       {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul}, {"fusedMatMulHeads", FusedMatMulHeads},
       {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm}, {"softmaxScaledMasked", SoftmaxScaledMasked},
       {"reduce", Reduce}, {"argMax", ArgMax}, {"transpose", Transpose}, {"gather", Gather},

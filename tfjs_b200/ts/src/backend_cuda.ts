@@ -38,6 +38,9 @@ export class CudaBackend extends KernelBackend {
   readonly ewCatalogue = new Map<string, boolean>();
   /** Deferred launches; TFJS_CUDA_NO_LAZY_FUSION=1 launches every kernel when called. */
   lazyFusion = !['1', 'true'].includes(process.env['TFJS_CUDA_NO_LAZY_FUSION'] ?? '0');
+  /** A pending 3x3 depthwise convolution consumed by a 1x1 convolution runs inside that
+   * convolution's launch (TFJS_CUDA_NO_DW_PROJECT=1 keeps the two launches). */
+  fuseDepthwiseProject = !['1', 'true'].includes(process.env['TFJS_CUDA_NO_DW_PROJECT'] ?? '0');
 
   constructor(readonly deviceOrdinal = 0) {
     super();
@@ -104,6 +107,7 @@ export class CudaBackend extends KernelBackend {
   }
 
   pendingOf(t: TensorInfo): Pending|undefined { return this.data.get(t.dataId).pending; }
+  pendingOfId(dataId: object): Pending|undefined { return this.data.get(dataId)?.pending; }
 
   /** The pending convolution behind `t` with `act` as the last step of its epilogue, as a
    * new pending tensor; `t` itself stays pending (another consumer launches it without). */

@@ -35,6 +35,10 @@ export interface CudaBinding {
   fusedConv2dResidual(ctx: Ctx, params: ArrayBuffer, x: number, filter: number, bias: number,
                       prelu: number, residual: number, postActivation: number,
                       out: number): void;
+  /** false when the library does not take the shapes: launch the two kernels separately. */
+  fusedDepthwiseProject(ctx: Ctx, dwParams: ArrayBuffer, pwParams: ArrayBuffer, x: number,
+                        dwFilter: number, dwBias: number, pwFilter: number, pwBias: number,
+                        residual: number, postActivation: number, out: number): boolean;
   addActivation(ctx: Ctx, activation: number, a: number, b: number, n: number,
                 out: number): void;
   fusedDepthwiseConv2d(ctx: Ctx, params: ArrayBuffer, x: number, filter: number, bias: number,

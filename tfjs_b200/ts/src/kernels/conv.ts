@@ -39,7 +39,11 @@ function convImpl(
   const params = packConvParams(
       convInfo, ACTIVATION[fuseAct ? activation : 'linear'], fuseBias ? biasLen : 0,
       fuseAct ? (preluLen ?? 0) : 0, (attrs['leakyreluAlpha'] as number) ?? 0.2);
-  if (backend.lazyFusion && fuseBias && activation === 'linear' &&
+  // A depthwise convolution is deferred with its relu / relu6 too: the 1x1 convolution that
+  // consumes it (the projection of an inverted-residual block) absorbs it into its launch.
+  const deferrable = activation === 'linear' ||
+      (depthwise && (activation === 'relu' || activation === 'relu6'));
+  if (backend.lazyFusion && fuseBias && deferrable &&
       util.sizeFromShape(convInfo.outShape) > 0) {
     // Deferred: a following Add (residual, or the bias of a depthwise convolution) and
     // Relu / Relu6 / clip fold into this launch's epilogue (kernels/elementwise.ts).
@@ -50,7 +54,8 @@ function convImpl(
       inputShapes, outputShapes: [convInfo.outShape]
     };
     const pending = depthwise ?
-        new PendingDepthwise(params, x.dataId, filter.dataId, bias != null ? bias.dataId : null, [desc]) :
+        new PendingDepthwise(params, x.dataId, filter.dataId, bias != null ? bias.dataId : null, [desc],
+                             activation as 'linear'|'relu'|'relu6') :
         new PendingConv(params, x.dataId, filter.dataId, bias != null ? bias.dataId : null, null, [desc]);
     return backend.defer(convInfo.outShape, 'float32', pending);
   }

@@ -53,7 +53,37 @@ export class PendingConv implements Pending {
     return new PendingConv(this.params, this.x, this.filter, this.bias, residual,
                            [...this.desc, desc], this.act);
   }
+  /**
+   * If the input is a depthwise convolution that is still pending and this is the 1x1
+   * convolution behind it (the projection of an inverted-residual block), both run as one
+   * launch and the depthwise result is never written.  False when the library does not
+   * take the shapes.
+   */
+  private launchWithDepthwise(backend: CudaBackend, outDev: number): boolean {
+    const dw = backend.pendingOfId(this.x);
+    if (!backend.fuseDepthwiseProject || !(dw instanceof PendingDepthwise)) return false;
+    const bias = this.bias != null ? backend.deviceIdOf(this.bias) : 0;
+    // without a shortcut the trailing activation is the projection's own
+    const pw = this.residual == null ? setActivation(this.params, this.act) : this.params;
+    const ok = binding.fusedDepthwiseProject(
+        backend.ctx, setActivation(dw.params, dw.act), pw, backend.deviceIdOf(dw.x),
+        backend.deviceIdOf(dw.filter), dw.bias != null ? backend.deviceIdOf(dw.bias) : 0,
+        backend.deviceIdOf(this.filter), bias,
+        this.residual != null ? backend.deviceIdOf(this.residual) : 0,
+        this.residual != null ? ACTIVATION[this.act] : ACTIVATION['linear'], outDev);
+    if (ok && !this.dwFolded) {
+      // profile records: the depthwise kernels join this launch, and the convolution no
+      // longer reads its input from memory
+      const {x: _x, ...rest} = this.desc[0].inputShapes;
+      this.desc.splice(0, 1, ...dw.desc, {...this.desc[0], inputShapes: rest});
+      this.dwFolded = true;
+    }
+    return ok;
+  }
+  private dwFolded = false;
+
   launch(backend: CudaBackend, outDev: number): void {
+    if (this.launchWithDepthwise(backend, outDev)) return;
     const bias = this.bias != null ? backend.deviceIdOf(this.bias) : 0;
     if (this.residual == null) {
       binding.fusedConv2d(backend.ctx, setActivation(this.params, this.act),
