@@ -493,6 +493,7 @@ def run_workload(args, model, batch, eng, group, rank, world, local_rank, headli
 
     def step_resident():
         y = gm.execute(resident, [out_name])[0]
+        be.device_id(y.dataId)     # a result whose launch is still pending is launched (no sync)
         y.dispose()
 
     out_probe = gm.execute(resident, [out_name])[0]

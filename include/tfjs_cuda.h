@@ -276,6 +276,22 @@ int tfjs_cuda_fused_matmul_heads(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_para
                                  int32_t layout, int32_t rows_or_heads, int32_t head_dim,
                                  int32_t out_id);
 
+/* Several _FusedMatMul products that share their `a` operand and every dimension, as one
+ * launch: the query, key and value projections of an attention layer read the same
+ * activations, and three products of 1.3 waves of tiles each leave a third of the GPU idle
+ * where one product of 3.9 waves does not.  Member i multiplies by b_ids[i] (a weight
+ * tensor), adds bias_ids[i] (all members carry a bias of N elements, or none) and writes
+ * out_ids[i]; each result is the one tfjs_cuda_fused_matmul (layout 0) or
+ * tfjs_cuda_fused_matmul_heads (layout TFJS_CUDA_HEADS_SPLIT) gives for that member
+ * (tfjs-backend-cpu/src/kernels/_FusedMatMul.ts:26-62).  2 <= count <= 4.  Returns
+ * TFJS_CUDA_UNSUPPORTED for problems the grouped kernel does not take (batched operands,
+ * transpose_a, PReLU, narrow outputs, the fp32 math mode); the caller then launches the
+ * members one by one. */
+int tfjs_cuda_fused_matmul_group(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
+                                 int32_t a_id, int32_t count, const int32_t* b_ids,
+                                 const int32_t* bias_ids, int32_t layout, int32_t rows_or_heads,
+                                 int32_t head_dim, const int32_t* out_ids);
+
 /* ---- MaxPool / AvgPool: tfjs-backend-cpu/src/kernels/MaxPool.ts:24-55,
  * AvgPool.ts:24-55, utils/pool_utils.ts:20-87; attrs kernel_names.ts:83-90,
  * :517-524.  Geometry from computePool2DInfo (conv_util.ts:119-140); filter_h/w

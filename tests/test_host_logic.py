@@ -292,3 +292,31 @@ def test_manifest_entry_checks_follow_decode_weight():
         io._entry({"name": "w", "shape": [1], "dtype": "string"})
     with pytest.raises(ValueError, match="Unsupported dtype"):
         io._entry({"name": "w", "shape": [1], "dtype": "complex64"})
+
+
+def test_hoist_keeps_the_plan_topological_and_groups_projections():
+    """hoist_shared_operand_matmuls moves the products that read one tensor next to each
+    other (with their constants) without breaking the order of dependencies."""
+    from tfjs_b200 import graph_model, model_zoo
+    from tfjs_b200.graph_model import parse_node_name
+    model_json, _ = model_zoo.bert_encoder(2)
+    nodes = [graph_model.Node(n) for n in model_json["modelTopology"]["node"]]
+    consts = set(n.name for n in nodes if n.op == "Const")
+    out, moved = graph_model.hoist_shared_operand_matmuls(nodes, lambda name: name in consts)
+    assert moved > 0 and sorted(n.name for n in out) == sorted(n.name for n in nodes)
+    seen = set()
+    for n in out:
+        for i in n.inputs:
+            assert parse_node_name(i)[0] in seen, (n.name, i)
+        seen.add(n.name)
+    # every layer's query, key and value projections: three products in a row on one operand
+    pos = {n.name: k for k, n in enumerate(out)}
+    by_a = {}
+    for n in out:
+        if n.op == "_FusedMatMul":
+            by_a.setdefault(n.inputs[0], []).append(n)
+    triples = [v for v in by_a.values() if len(v) == 3]
+    assert len(triples) == 12
+    for v in triples:
+        inner = [x for x in out[pos[v[0].name]:pos[v[2].name] + 1] if x.op != "Const"]
+        assert [x.name for x in inner] == [x.name for x in v]

@@ -137,12 +137,13 @@ def test_graph_ops_and_pending_classes_have_their_python_twins():
     from tfjs_b200 import backend, graph_model
     ts = _all_ts()
     pend = ts["src/pending.ts"]
-    for cls in ("PendingConv", "PendingDepthwise", "PendingTile", "PendingEw"):
+    for cls in ("PendingConv", "PendingDepthwise", "PendingMatMul", "PendingTile", "PendingEw"):
         assert hasattr(backend, cls) and "export class %s" % cls in pend
     assert "export function canonicalProgram" in pend and hasattr(backend, "_canonical_program")
     rewrites = ts["src/graph_rewrites.ts"]
     for py, tsname in (("fuse_layer_norms", "fuseLayerNorms"), ("fuse_attention_heads", "fuseAttentionHeads"),
-                       ("fuse_softmax_inputs", "fuseSoftmaxInputs")):
+                       ("fuse_softmax_inputs", "fuseSoftmaxInputs"),
+                       ("hoist_shared_operand_matmuls", "hoistSharedOperandMatMuls")):
         assert hasattr(graph_model, py) and "export function %s" % tsname in rewrites
     for op in ("_FusedLayerNorm", "_MatMulHeads", "_SoftmaxScaledMasked"):
         assert "registerOp('%s'" % op in rewrites

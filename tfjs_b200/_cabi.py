@@ -118,6 +118,9 @@ SIGNATURES = {
     "tfjs_cuda_fused_depthwise_conv2d": (c_int, [_CTX, POINTER(Conv2DParams)] + [c_int32] * 5),
     "tfjs_cuda_fused_matmul": (c_int, [_CTX, POINTER(MatMulParams)] + [c_int32] * 5),
     "tfjs_cuda_fused_matmul_heads": (c_int, [_CTX, POINTER(MatMulParams)] + [c_int32] * 8),
+    "tfjs_cuda_fused_matmul_group": (c_int, [_CTX, POINTER(MatMulParams), c_int32, c_int32,
+                                     POINTER(c_int32), POINTER(c_int32), c_int32, c_int32,
+                                     c_int32, POINTER(c_int32)]),
     "tfjs_cuda_pool2d": (c_int, [_CTX, POINTER(Conv2DParams), c_int32, c_int32, c_int32]),
     "tfjs_cuda_binary": (c_int, [_CTX, c_int32, c_int32, c_int32, c_int32, _I64P,
                                  c_int32, _I64P, c_int32, _I64P]),

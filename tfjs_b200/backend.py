@@ -137,13 +137,18 @@ class PendingConv(object):
         elif post_act != "linear":
             pp = _cabi.Conv2DParams.from_buffer_copy(p)
             pp.activation = _cabi.ACTIVATIONS[post_act]
+        # Operands that are pending themselves launch now, and such a launch may, further
+        # down, need this very depthwise result and materialise it (a block's output feeds
+        # both the next block and that block's shortcut).  So the shortcut and the weights
+        # come first, then the depthwise convolution is looked at again, and its input, which
+        # it keeps alive, comes last.
+        ids = [backend.device_id(t) if t is not None else 0
+               for t in (dw.filt, dw.bias, self.filt, self.bias, self.residual)]
+        if rec.pending is not dw:
+            return False
         rc = backend.lib.tfjs_cuda_fused_depthwise_project(
-            backend.ctx, byref(dp), byref(pp), backend.device_id(dw.x),
-            backend.device_id(dw.filt),
-            backend.device_id(dw.bias) if dw.bias is not None else 0,
-            backend.device_id(self.filt),
-            backend.device_id(self.bias) if self.bias is not None else 0,
-            backend.device_id(self.residual) if self.residual is not None else 0, post, out_dev)
+            backend.ctx, byref(dp), byref(pp), backend.device_id(dw.x), ids[0], ids[1], ids[2],
+            ids[3], ids[4], post, out_dev)
         if rc == _cabi.UNSUPPORTED:
             return False
         backend.check(rc)
@@ -207,6 +212,37 @@ class PendingDepthwise(object):
         backend.check(backend.lib.tfjs_cuda_fused_depthwise_conv2d(
             backend.ctx, byref(p), backend.device_id(self.x), backend.device_id(self.filt),
             backend.device_id(self.bias) if self.bias is not None else 0, 0, out_dev))
+
+
+class PendingMatMul(object):
+    """A _FusedMatMul (or its heads-split form) with a fused bias, not launched yet.  When
+    it is launched, the other products still pending on the same `a` operand with the same
+    dimensions (the query, key and value projections of an attention layer) go with it in
+    one `tfjs_cuda_fused_matmul_group` launch; each member's result is the one its own
+    launch would give."""
+    __slots__ = ("params", "a", "b", "bias", "heads", "desc", "key")
+
+    def __init__(self, params, a, b, bias, heads, desc):
+        self.params, self.a, self.b, self.bias = params, a, b, bias
+        self.heads = heads    # None, or (layout, rows_or_heads, head_dim) of the permuted store
+        self.desc = desc
+        self.key = (bytes(params), heads, bias is None)
+
+    def deps(self):
+        return [d for d in (self.a, self.b, self.bias) if d is not None]
+
+    def launch(self, backend, out_dev, post_act):
+        lib = backend.lib
+        bias = backend.device_id(self.bias) if self.bias is not None else 0
+        if self.heads is None:
+            backend.check(lib.tfjs_cuda_fused_matmul(
+                backend.ctx, byref(self.params), backend.device_id(self.a),
+                backend.device_id(self.b), bias, 0, out_dev))
+        else:
+            backend.check(lib.tfjs_cuda_fused_matmul_heads(
+                backend.ctx, byref(self.params), backend.device_id(self.a),
+                backend.device_id(self.b), bias, 0, self.heads[0], self.heads[1], self.heads[2],
+                out_dev))
 
 
 class PendingTile(object):
@@ -450,6 +486,11 @@ class CudaBackend(object):
         # a pending 3x3 depthwise convolution consumed by a 1x1 convolution runs inside that
         # convolution's launch (TFJS_CUDA_NO_DW_PROJECT=1 keeps the two launches)
         self.fuse_depthwise_project = os.environ.get("TFJS_CUDA_NO_DW_PROJECT", "0") in ("", "0")
+        # products that share their first operand launch together (TFJS_CUDA_NO_MATMUL_GROUP=1
+        # launches each on its own); dataId of `a` -> dataIds of the pending products on it
+        self.math_mode = "tf32"
+        self.group_matmuls = os.environ.get("TFJS_CUDA_NO_MATMUL_GROUP", "0") in ("", "0")
+        self._matmuls_on = {}
         self.profiler = None  # the engine, while it profiles (told about deferred launches)
         self.ew_catalogue = {}  # chain signature -> the library has a kernel for it
         self._log_depth = 0     # nesting of launch_log(True)
@@ -529,7 +570,73 @@ class CudaBackend(object):
         for d in pending.deps():
             self._adjust(self.data[d], 1, 1)
         self.data[dataId] = rec
+        if isinstance(pending, PendingMatMul):
+            if len(self._matmuls_on) > 64:     # forget operands whose products are all gone
+                self._matmuls_on = {a: ids for a, ids in self._matmuls_on.items()
+                                    if any(self._still_pending_matmul(i) for i in ids)}
+            ids = [i for i in self._matmuls_on.get(pending.a, []) if self._still_pending_matmul(i)]
+            self._matmuls_on[pending.a] = ids + [dataId]
         return TensorInfo(dataId, shape, dtype)
+
+    def _still_pending_matmul(self, dataId):
+        rec = self.data.get(dataId)
+        return rec is not None and isinstance(rec.pending, PendingMatMul)
+
+    def _resolve_matmul_group(self, rec, pending):
+        """Launches `pending` together with the other products pending on the same operand
+        (same dimensions, layout and bias kind).  False when there is no such product or the
+        library does not take the group; nothing has been launched then."""
+        ids = self._matmuls_on.get(pending.a, [])
+        mates = [self.data[i] for i in ids if self._still_pending_matmul(i)]
+        mates = [m for m in mates if m is not rec and m.pending.key == pending.key][:3]
+        if not (self.group_matmuls and mates):
+            return False
+        # operands that are pending launch first; the group is what is still pending then
+        a_dev = self.device_id(pending.a)
+        for m in mates:
+            if m.pending is not None:
+                for t in (m.pending.b, m.pending.bias):
+                    if t is not None:
+                        self.device_id(t)
+        for t in (pending.b, pending.bias):
+            if t is not None:
+                self.device_id(t)
+        mates = [m for m in mates if isinstance(m.pending, PendingMatMul)]
+        if rec.pending is not pending or not mates:
+            return False
+        members = [rec] + mates
+        devs = []
+        try:
+            for m in members:
+                devs.append(self._alloc(m.nbytes))
+            n = len(members)
+            arr = c_int32 * n
+            b_ids = arr(*[self.device_id(m.pending.b) for m in members])
+            bias_ids = arr(*[self.device_id(m.pending.bias) if m.pending.bias is not None else 0
+                             for m in members])
+            heads = pending.heads or (0, 0, 0)
+            descs = [d for m in members for d in m.pending.desc]
+
+            def launch():
+                return self.lib.tfjs_cuda_fused_matmul_group(
+                    self.ctx, byref(pending.params), a_dev, n, b_ids, bias_ids,
+                    heads[0], heads[1], heads[2], arr(*devs))
+            rc = launch() if self.profiler is None else \
+                self.profiler.deferred_launch(descs, launch, False)
+            if rc == _cabi.UNSUPPORTED:
+                for d in devs:
+                    self.lib.tfjs_cuda_free(self.ctx, d)
+                return False
+            self.check(rc)
+        except Exception:
+            for d in devs:
+                self.lib.tfjs_cuda_free(self.ctx, d)
+            raise
+        for m, d in zip(members, devs):
+            done, m.pending = m.pending, None
+            m.dev = d
+            self._release(done)
+        return True
 
     def pending_of(self, dataId):
         return self.data[dataId].pending
@@ -550,6 +657,10 @@ class CudaBackend(object):
 
     def _resolve(self, rec):
         pending = rec.pending
+        if isinstance(pending, PendingMatMul) and self._resolve_matmul_group(rec, pending):
+            return
+        if rec.pending is not pending:      # launched meanwhile, by an operand's own launch
+            return
         dev = self._alloc(rec.nbytes)
         try:
             self._launch(pending, dev, "linear", False)
@@ -729,6 +840,7 @@ class CudaBackend(object):
         """'tf32' (tensor cores) or 'fp32' (SIMT fp32 FMA)."""
         self.check(self.lib.tfjs_cuda_set_math_mode(
             self.ctx, {"tf32": _cabi.MATH_TF32, "fp32": _cabi.MATH_FP32}[mode]))
+        self.math_mode = mode
 
     # ------------------------------------------------ whole-step capture / replay --
     def high_water_reset(self):

@@ -66,4 +66,19 @@ struct PatchPlan {
 bool tf32_patch_plan(const ConvGeo& cv, int M, int N, int sm_count, PatchPlan* plan);
 
 int launch_gemm_simt(tfjs_cuda_ctx* ctx, const GemmProblem& pr);
-int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operands& op);
+// Products that share A and every dimension of the problem (the query, key and value
+// projections of an attention layer): member i reads b[i] (K-major, packed) and bias[i] and
+// writes c[i].  One launch walks the tiles of all members, so three products of 1.3 waves
+// each become one of 3.9.  Only the CTA-pair kernel takes a group; for anything else
+// launch_gemm_tf32 returns TFJS_CUDA_UNSUPPORTED and the caller launches the members one
+// by one.
+constexpr int kMaxGemmGroup = 4;
+struct GemmGroup {
+  int count = 0;
+  const float* b[kMaxGemmGroup];
+  const float* bias[kMaxGemmGroup];
+  float* c[kMaxGemmGroup];
+};
+
+int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operands& op,
+                     const GemmGroup* group = nullptr);

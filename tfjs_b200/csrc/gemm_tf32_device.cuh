@@ -50,6 +50,16 @@ struct Tf32Args {
 // K-major B operand, tm_c: 32 x 32 store boxes.  g.tiles_m counts 256-row tiles.
 int launch_gemm_tf32_pair(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                           const CUtensorMap& tm_c, Tf32Args& g, bool im2col);
+// The same for a group of products that share A (GemmGroup): the tile index runs over the
+// members' column tiles side by side.
+struct PairGroupMaps {
+  CUtensorMap b[kMaxGemmGroup];
+  CUtensorMap c[kMaxGemmGroup];
+  const float* bias[kMaxGemmGroup];
+  int count;
+};
+int launch_gemm_tf32_pair_group(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a,
+                                const PairGroupMaps& maps, Tf32Args& g);
 
 namespace {
 
@@ -131,20 +141,25 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
 // dispatch.
 // The bias of column n0 + lane, fetched by each lane ahead of the accumulator (0 when the
 // kernel has no bias or the column lies beyond N).
-__device__ __forceinline__ float chunk_bias(const Tf32Args& g, int n0, int lane) {
+__device__ __forceinline__ float chunk_bias(const Tf32Args& g, int n0, int lane,
+                                            const float* bias) {
   if (g.bias_len == 0) return 0.0f;
-  if (g.bias_len == 1) return __ldg(g.bias);
-  return n0 + lane < g.N ? __ldg(g.bias + n0 + lane) : 0.0f;
+  if (g.bias_len == 1) return __ldg(bias);
+  return n0 + lane < g.N ? __ldg(bias + n0 + lane) : 0.0f;
+}
+__device__ __forceinline__ float chunk_bias(const Tf32Args& g, int n0, int lane) {
+  return chunk_bias(g, n0, lane, g.bias);
 }
 
 template <int ACT>
 __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, float bj,
-                                           bool skip_bias = false) {
+                                           bool skip_bias = false, const float* bias = nullptr) {
+  if (bias == nullptr) bias = g.bias;
   if (g.bias_len != 0 && !skip_bias) {
     if (g.bias_len > 1 && n0 + 32 <= g.N) {
       // every thread owns a row of 32 columns: eight 16-byte loads at a warp-uniform
       // address (served as broadcasts) instead of 32 shuffles
-      const float4* b4 = reinterpret_cast<const float4*>(g.bias + n0);
+      const float4* b4 = reinterpret_cast<const float4*>(bias + n0);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float4 b = __ldg(b4 + j);
@@ -195,16 +210,17 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, 
 }
 
 __device__ __forceinline__ void chunk_math_dispatch(float* v, const Tf32Args& g, int n0,
-                                                    float bj, bool skip_bias = false) {
+                                                    float bj, bool skip_bias = false,
+                                                    const float* bias = nullptr) {
   switch (g.ap.act) {
-    case TFJS_CUDA_ACT_RELU: chunk_math<TFJS_CUDA_ACT_RELU>(v, g, n0, bj, skip_bias); break;
-    case TFJS_CUDA_ACT_RELU6: chunk_math<TFJS_CUDA_ACT_RELU6>(v, g, n0, bj, skip_bias); break;
-    case TFJS_CUDA_ACT_PRELU: chunk_math<TFJS_CUDA_ACT_PRELU>(v, g, n0, bj, skip_bias); break;
-    case TFJS_CUDA_ACT_LEAKYRELU: chunk_math<TFJS_CUDA_ACT_LEAKYRELU>(v, g, n0, bj, skip_bias); break;
-    case TFJS_CUDA_ACT_SIGMOID: chunk_math<TFJS_CUDA_ACT_SIGMOID>(v, g, n0, bj, skip_bias); break;
-    case TFJS_CUDA_ACT_ELU: chunk_math<TFJS_CUDA_ACT_ELU>(v, g, n0, bj, skip_bias); break;
-    case TFJS_CUDA_ACT_GELU_ERF: chunk_math<TFJS_CUDA_ACT_GELU_ERF>(v, g, n0, bj, skip_bias); break;
-    default: chunk_math<TFJS_CUDA_ACT_LINEAR>(v, g, n0, bj, skip_bias); break;
+    case TFJS_CUDA_ACT_RELU: chunk_math<TFJS_CUDA_ACT_RELU>(v, g, n0, bj, skip_bias, bias); break;
+    case TFJS_CUDA_ACT_RELU6: chunk_math<TFJS_CUDA_ACT_RELU6>(v, g, n0, bj, skip_bias, bias); break;
+    case TFJS_CUDA_ACT_PRELU: chunk_math<TFJS_CUDA_ACT_PRELU>(v, g, n0, bj, skip_bias, bias); break;
+    case TFJS_CUDA_ACT_LEAKYRELU: chunk_math<TFJS_CUDA_ACT_LEAKYRELU>(v, g, n0, bj, skip_bias, bias); break;
+    case TFJS_CUDA_ACT_SIGMOID: chunk_math<TFJS_CUDA_ACT_SIGMOID>(v, g, n0, bj, skip_bias, bias); break;
+    case TFJS_CUDA_ACT_ELU: chunk_math<TFJS_CUDA_ACT_ELU>(v, g, n0, bj, skip_bias, bias); break;
+    case TFJS_CUDA_ACT_GELU_ERF: chunk_math<TFJS_CUDA_ACT_GELU_ERF>(v, g, n0, bj, skip_bias, bias); break;
+    default: chunk_math<TFJS_CUDA_ACT_LINEAR>(v, g, n0, bj, skip_bias, bias); break;
   }
 }
 

@@ -101,11 +101,15 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
 }
 
 // A_MODE 0: A tiles by tiled TMA ([batch][M][K] map, 128-row boxes); 2: TMA im2col over NHWC x.
-template <int A_MODE, int EW>
+// GROUP: several products share A (PairGroupMaps); g.tiles_n counts the column tiles of all
+// members side by side and tiles_n_each those of one member.
+template <int A_MODE, int EW, int GROUP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<EW>::THREADS), 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                       const __grid_constant__ CUtensorMap tm_b,
-                      const __grid_constant__ CUtensorMap tm_c, const Tf32Args g) {
+                      const __grid_constant__ CUtensorMap tm_c,
+                      const __grid_constant__ PairGroupMaps grp, const Tf32Args g,
+                      const int tiles_n_each) {
   constexpr int STAGES = PairCfg<EW>::STAGES;
   constexpr int ACC = kPairAcc;
   constexpr int EPI_STEP = (EW / 4) * 32;   // columns between the chunks one warp takes
@@ -162,10 +166,16 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       uint32_t phase = 0;
       bool alive = true;
       for (int tile = pair; alive && tile < g.total_tiles; tile += npairs) {
-        const int nt = tile % g.tiles_n;
+        int nt = tile % g.tiles_n;
         const int rest = tile / g.tiles_n;
         const int mt = rest % g.tiles_m;
         const int bz = rest / g.tiles_m;
+        const CUtensorMap* map_b = &tm_b;
+        if (GROUP) {
+          const int member = nt / tiles_n_each;
+          nt -= member * tiles_n_each;
+          map_b = &grp.b[member];
+        }
         const int m0 = mt * 256 + (int)rank * 128;
         const int n0 = nt * BN + (int)rank * 128;
         int pix_w = 0, pix_h = 0, pix_n = 0;
@@ -194,7 +204,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
             tma_load_im2col_pair(a_base + stage * A_STAGE_BYTES, &tm_a, fb, cc, pix_w, pix_h,
                                  pix_n, (uint16_t)(fc * g.conv.d_w), (uint16_t)(fr * g.conv.d_h));
           }
-          tma_load_3d_pair(b_base + stage * kPairBStageBytes, &tm_b, fb, ks * BK, n0,
+          tma_load_3d_pair(b_base + stage * kPairBStageBytes, map_b, fb, ks * BK, n0,
                            bz % g.batch_b);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -252,13 +262,21 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                                          map_to_rank(tempty_bar(1), 0)};
     int it = 0;
     for (int tile = pair; tile < g.total_tiles; tile += npairs, ++it) {
-      const int nt = tile % g.tiles_n;
+      int nt = tile % g.tiles_n;
       const int rest = tile / g.tiles_n;
       const int mt = rest % g.tiles_m;
       const int bz = rest / g.tiles_m;
+      const CUtensorMap* map_c = &tm_c;
+      const float* bias = g.bias;
+      if (GROUP) {
+        const int member = nt / tiles_n_each;
+        nt -= member * tiles_n_each;
+        map_c = &grp.c[member];
+        bias = grp.bias[member];
+      }
       const int acc = it % ACC;
       const uint32_t aphase = (it / ACC) & 1;
-      float bj = chunk_bias(g, nt * BN + part * 32, lane);
+      float bj = chunk_bias(g, nt * BN + part * 32, lane, bias);
       if (!mbar_wait(tfull_bar(acc), aphase)) {
         if (lane == 0) atomicExch(g.flag, 4);
         break;
@@ -280,8 +298,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           if (lane == 0) mbar_arrive_cluster(leader_tempty[acc]);
           released = true;
         }
-        chunk_math_dispatch(v, g, n0, bj);
-        if (c0 + EPI_STEP < BN) bj = chunk_bias(g, n0 + EPI_STEP, lane);
+        chunk_math_dispatch(v, g, n0, bj, false, bias);
+        if (c0 + EPI_STEP < BN) bj = chunk_bias(g, n0 + EPI_STEP, lane, bias);
         // the bulk store that last used the staging tile must have finished reading it
         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         __syncwarp();
@@ -297,7 +315,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           if (g.out_perm == 0) {
             asm volatile(
                 "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                ::"l"(&tm_c), "r"(stage_buf), "r"(n0), "r"(m_base), "r"(bz)
+                ::"l"(map_c), "r"(stage_buf), "r"(n0), "r"(m_base), "r"(bz)
                 : "memory");
           } else {
             // 4-D map over the permuted result: (d, s, h, b) for the heads split,
@@ -312,7 +330,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
             }
             asm volatile(
                 "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-                ::"l"(&tm_c), "r"(stage_buf), "r"(c0p), "r"(c1), "r"(c2), "r"(c3)
+                ::"l"(map_c), "r"(stage_buf), "r"(c0p), "r"(c1), "r"(c2), "r"(c3)
                 : "memory");
           }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -339,10 +357,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   }
 }
 
-template <int A_MODE, int EW>
+template <int A_MODE, int EW, int GROUP>
 int launch_pair(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
-                const CUtensorMap& tm_c, Tf32Args& g) {
-  auto kern = gemm_tf32_pair_kernel<A_MODE, EW>;
+                const CUtensorMap& tm_c, const PairGroupMaps* maps, Tf32Args& g) {
+  auto kern = gemm_tf32_pair_kernel<A_MODE, EW, GROUP>;
   using C = PairCfg<EW>;
   static bool configured[64] = {false};  // per device ordinal
   if (ctx->device >= 64 || !configured[ctx->device]) {
@@ -350,13 +368,18 @@ int launch_pair(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& 
                                        C::SMEM_BYTES));
     if (ctx->device < 64) configured[ctx->device] = true;
   }
-  g.tiles_n = (g.N + 255) / 256;
+  const int tiles_n_each = (g.N + 255) / 256;
+  g.tiles_n = tiles_n_each * (GROUP ? maps->count : 1);
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int pairs_max = ctx->sm_count / 2;
   const int pairs = g.total_tiles < pairs_max ? g.total_tiles : pairs_max;
-  kern<<<2 * pairs, C::THREADS, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, tm_c, g);
+  static const PairGroupMaps no_group = {};
+  kern<<<2 * pairs, C::THREADS, C::SMEM_BYTES, ctx->stream>>>(tm_a, tm_b, tm_c,
+                                                             GROUP ? *maps : no_group, g,
+                                                             tiles_n_each);
   static const std::string name =
-      "gemm_tf32_pair_kernel<A_MODE=" + std::to_string(A_MODE) + ",EW=" + std::to_string(EW) + ">";
+      "gemm_tf32_pair_kernel<A_MODE=" + std::to_string(A_MODE) + ",EW=" + std::to_string(EW) +
+      ",GROUP=" + std::to_string(GROUP) + ">";
   LAUNCH_CHECK(ctx, name.c_str());
   return TFJS_CUDA_OK;
 }
@@ -368,9 +391,14 @@ int launch_gemm_tf32_pair(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUt
   static int ew = -1;  // epilogue warps per CTA (tuning knob)
   if (ew < 0) ew = getenv("TFJS_CUDA_PAIR_EPILOGUE_WARPS") ? atoi(getenv("TFJS_CUDA_PAIR_EPILOGUE_WARPS")) : 8;
   if (ew == 16) {
-    if (im2col) return launch_pair<2, 16>(ctx, tm_a, tm_b, tm_c, g);
-    return launch_pair<0, 16>(ctx, tm_a, tm_b, tm_c, g);
+    if (im2col) return launch_pair<2, 16, 0>(ctx, tm_a, tm_b, tm_c, nullptr, g);
+    return launch_pair<0, 16, 0>(ctx, tm_a, tm_b, tm_c, nullptr, g);
   }
-  if (im2col) return launch_pair<2, 8>(ctx, tm_a, tm_b, tm_c, g);
-  return launch_pair<0, 8>(ctx, tm_a, tm_b, tm_c, g);
+  if (im2col) return launch_pair<2, 8, 0>(ctx, tm_a, tm_b, tm_c, nullptr, g);
+  return launch_pair<0, 8, 0>(ctx, tm_a, tm_b, tm_c, nullptr, g);
+}
+
+int launch_gemm_tf32_pair_group(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a,
+                                const PairGroupMaps& maps, Tf32Args& g) {
+  return launch_pair<0, 8, 1>(ctx, tm_a, maps.b[0], maps.c[0], &maps, g);
 }

@@ -1254,7 +1254,59 @@ bool tf32_patch_plan(const ConvGeo& cv, int M, int N, int sm_count, PatchPlan* p
   return true;
 }
 
-int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operands& op) {
+// Output map of the heads-permuted store: every 32 x 32 store tile is one box of the
+// permuted tensor ((d, s, h, b) for the split, (d, h, s, b) for the merge).
+static int make_heads_c_map(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const float* c,
+                            CUtensorMap* tm) {
+  const int S = pr.out_perm == 1 ? pr.perm_p : pr.M, D = pr.perm_d;
+  const bool shape_ok =
+      pr.out_perm == 1 ? (pr.batch == 1 && pr.perm_p > 0 && D > 0 && pr.M % pr.perm_p == 0 &&
+                          pr.N % D == 0)
+                       : (pr.out_perm == 2 && pr.perm_p > 0 && pr.batch % pr.perm_p == 0 &&
+                          D == pr.N);
+  if (!shape_ok || (S & 31) || (D & 31) || ((uintptr_t)c & 15) || pr.residual)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
+                    "heads-permuted store: sequence and head sizes must be multiples of 32");
+  EncodeTiledFn enc = get_encode();
+  const cuuint64_t B = pr.out_perm == 1 ? pr.M / pr.perm_p : pr.batch / pr.perm_p;
+  const cuuint64_t H = pr.out_perm == 1 ? pr.N / D : pr.perm_p;
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+  dims[0] = D; dims[3] = B;
+  if (pr.out_perm == 1) {  // physical [B, H, S, D]
+    dims[1] = S; dims[2] = H;
+    strides[0] = (cuuint64_t)D * 4; strides[1] = (cuuint64_t)S * D * 4;
+    box[0] = 32; box[1] = 32; box[2] = 1; box[3] = 1;
+  } else {                 // physical [B, S, H, D]
+    dims[1] = H; dims[2] = S;
+    strides[0] = (cuuint64_t)D * 4; strides[1] = (cuuint64_t)H * D * 4;
+    box[0] = 32; box[1] = 1; box[2] = 32; box[3] = 1;
+  }
+  strides[2] = (cuuint64_t)H * S * D * 4;
+  if (!enc || enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)c, dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "heads-permuted store: tensor map refused");
+  return TFJS_CUDA_OK;
+}
+
+// Map over a row-major [batch][M][N] tensor for the epilogue's bulk stores (or the prefetch
+// of the residual): dims (N, M, batch), 32 x 32 boxes.
+static bool make_plain_c_map(const GemmProblem& pr, const float* base, CUtensorMap* tm,
+                             CUtensorMapL2promotion l2) {
+  EncodeTiledFn enc = get_encode();
+  cuuint64_t dims[3] = {(cuuint64_t)pr.N, (cuuint64_t)pr.M, (cuuint64_t)pr.batch};
+  cuuint64_t strides[2] = {(cuuint64_t)pr.N * 4, (cuuint64_t)pr.M * pr.N * 4};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc && enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, l2,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operands& op,
+                     const GemmGroup* group) {
   Tf32Args g;
   g.c = pr.c;
   g.bias = pr.bias;
@@ -1302,57 +1354,18 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   g.perm_p = pr.perm_p;
   g.perm_d = pr.perm_d;
   if (pr.out_perm != 0) {
-    // every 32 x 32 store tile must be one box of the permuted tensor
-    const int S = pr.out_perm == 1 ? pr.perm_p : pr.M, D = pr.perm_d;
-    const bool shape_ok =
-        pr.out_perm == 1 ? (pr.batch == 1 && pr.perm_p > 0 && D > 0 && pr.M % pr.perm_p == 0 &&
-                            pr.N % D == 0)
-                         : (pr.out_perm == 2 && pr.perm_p > 0 && pr.batch % pr.perm_p == 0 &&
-                            D == pr.N);
-    if (!shape_ok || (S & 31) || (D & 31) || ((uintptr_t)pr.c & 15) || pr.residual)
-      return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED,
-                      "heads-permuted store: sequence and head sizes must be multiples of 32");
-    EncodeTiledFn enc = get_encode();
-    const cuuint64_t B = pr.out_perm == 1 ? pr.M / pr.perm_p : pr.batch / pr.perm_p;
-    const cuuint64_t H = pr.out_perm == 1 ? pr.N / D : pr.perm_p;
-    cuuint64_t dims[4], strides[3];
-    cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
-    dims[0] = D; dims[3] = B;
-    if (pr.out_perm == 1) {  // physical [B, H, S, D]
-      dims[1] = S; dims[2] = H;
-      strides[0] = (cuuint64_t)D * 4; strides[1] = (cuuint64_t)S * D * 4;
-      box[0] = 32; box[1] = 32; box[2] = 1; box[3] = 1;
-    } else {                 // physical [B, S, H, D]
-      dims[1] = H; dims[2] = S;
-      strides[0] = (cuuint64_t)D * 4; strides[1] = (cuuint64_t)H * D * 4;
-      box[0] = 32; box[1] = 1; box[2] = 32; box[3] = 1;
-    }
-    strides[2] = (cuuint64_t)H * S * D * 4;
-    if (!enc || enc(&tm_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)pr.c, dims, strides, box,
-                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "heads-permuted store: tensor map refused");
+    if ((rc = make_heads_c_map(ctx, pr, pr.c, &tm_c))) return rc;
     g.c_tma = 1;
   } else
   if ((pr.N & 3) == 0 && ((uintptr_t)pr.c & 15) == 0 && ((uintptr_t)pr.residual & 15) == 0) {
-    EncodeTiledFn enc = get_encode();
-    cuuint64_t dims[3] = {(cuuint64_t)pr.N, (cuuint64_t)pr.M, (cuuint64_t)pr.batch};
-    cuuint64_t strides[2] = {(cuuint64_t)pr.N * 4, (cuuint64_t)pr.M * pr.N * 4};
-    cuuint32_t box[3] = {32, 32, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    auto encode = [&](CUtensorMap* tm, const void* base, CUtensorMapL2promotion l2) {
-      return enc && enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box,
-                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, l2,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-    };
     static int no_tma_store = -1;
     if (no_tma_store < 0) no_tma_store = getenv("TFJS_CUDA_NO_TMA_STORE") ? 1 : 0;  // debugging knob
-    const bool ok = !no_tma_store && encode(&tm_c, pr.c, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+    const bool ok = !no_tma_store &&
+                    make_plain_c_map(pr, pr.c, &tm_c, CU_TENSOR_MAP_L2_PROMOTION_NONE);
     if (!pr.residual) {
       g.c_tma = ok ? 1 : 0;
     } else if (ok && op.b_layout == B_K_MAJOR && (op.a_gather == 0 || op.a_gather == 1) &&
-               encode(&tm_r, pr.residual, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
+               make_plain_c_map(pr, pr.residual, &tm_r, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) {
       // the residual epilogue exists for the TMA-fed A operand modes
       res_tma = true;
     }
@@ -1400,11 +1413,40 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
   // 67.8 -> 62.8 us; with at most two waves of pair tiles the two forms tie, and where the
   // single-CTA form splits the K loop of its last wave ([8192, 3072] x [3072, 768], the 3x3
   // convolutions at 14 x 14 and 7 x 7) that form is 5-20% faster, so those keep it.
-  const long long pair_tiles = (long long)((pr.M + 255) / 256) * ((pr.N + 255) / 256) * pr.batch;
-  if (pair_k > 0 && op.k_steps >= pair_k && op.b_layout == B_K_MAJOR && pr.N > 128 &&
-      g.c_tma && !pr.residual && ctx->sm_count >= 2 &&
+  const long long pair_tiles = (long long)((pr.M + 255) / 256) * ((pr.N + 255) / 256) * pr.batch *
+                               (group ? group->count : 1);
+  const bool pair_shape = op.b_layout == B_K_MAJOR && pr.N > 128 && g.c_tma && !pr.residual &&
+                          ctx->sm_count >= 2 &&
+                          (op.a_gather == 0 || (op.a_gather == 1 && !no_im2col));
+  if (group) {
+    // a group exists in the pair kernel only
+    if (!pair_shape || op.a_gather != 0 || group->count < 2 || group->count > kMaxGemmGroup)
+      return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "grouped matMul: shape not taken by the pair kernel");
+    PairGroupMaps maps;
+    memset(&maps, 0, sizeof maps);
+    maps.count = group->count;
+    if ((rc = make_map(ctx, &tm_a, op.a, (uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.batch_a,
+                       (uint64_t)op.lda, (uint64_t)pr.M * op.lda, BM)))
+      return rc;
+    const uint64_t kk = (uint64_t)op.k_steps * BK < (uint64_t)op.ldb
+                            ? (uint64_t)op.k_steps * BK : (uint64_t)op.ldb;
+    for (int i = 0; i < group->count; ++i) {
+      if ((rc = make_map(ctx, &maps.b[i], group->b[i], kk, (uint64_t)pr.N, (uint64_t)pr.batch_b,
+                         (uint64_t)op.ldb, (uint64_t)pr.N * op.ldb, 128u)))
+        return rc;
+      if (pr.out_perm != 0) {
+        if ((rc = make_heads_c_map(ctx, pr, group->c[i], &maps.c[i]))) return rc;
+      } else if (((uintptr_t)group->c[i] & 15) ||
+                 !make_plain_c_map(pr, group->c[i], &maps.c[i], CU_TENSOR_MAP_L2_PROMOTION_NONE)) {
+        return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "grouped matMul: output map refused");
+      }
+      maps.bias[i] = group->bias[i];
+    }
+    g.tiles_m = (pr.M + 255) / 256;
+    return launch_gemm_tf32_pair_group(ctx, tm_a, maps, g);
+  }
+  if (pair_k > 0 && op.k_steps >= pair_k && pair_shape &&
       pair_tiles > 2ll * (ctx->sm_count / 2) &&
-      (op.a_gather == 0 || (op.a_gather == 1 && !no_im2col)) &&
       !(bn == 256 && use_k_split(ctx, g.tiles_m * ((pr.N + 255) / 256) * pr.batch, op.k_steps))) {
     memset(&tm_a, 0, sizeof tm_a);
     bool ok;

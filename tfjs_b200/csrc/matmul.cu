@@ -254,6 +254,76 @@ int tfjs_cuda_fused_matmul_heads(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_para
                      out_id);
 }
 
+int tfjs_cuda_fused_matmul_group(tfjs_cuda_ctx* ctx, const tfjs_cuda_matmul_params* p,
+                                 int32_t a_id, int32_t count, const int32_t* b_ids,
+                                 const int32_t* bias_ids, int32_t layout, int32_t rows_or_heads,
+                                 int32_t head_dim, const int32_t* out_ids) {
+  if (!ctx) return TFJS_CUDA_INVALID_ARG;
+  const char* who = "fused_matmul_group";
+  if (!p || !b_ids || !out_ids || count < 2 || count > kMaxGemmGroup)
+    return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "%s: bad arguments", who);
+  if (p->batch_a != 1 || p->batch_b != 1 || p->m <= 0 || p->n <= 0 || p->k <= 0 ||
+      p->transpose_a || (p->k % 4) != 0 || p->activation == TFJS_CUDA_ACT_PRELU ||
+      p->activation == TFJS_CUDA_ACT_GELU_ERF || ctx->math_mode != TFJS_CUDA_MATH_TF32 ||
+      (p->bias_len != 0 && p->bias_len != p->n))
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "%s: problem not taken by the grouped kernel", who);
+  if (layout != 0 && layout != TFJS_CUDA_HEADS_SPLIT)
+    return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "%s: layout %d", who, layout);
+  Buffer* a;
+  int rc;
+  if ((rc = ctx_get(ctx, a_id, (uint64_t)p->m * p->k * 4, "fused_matmul_group a", &a))) return rc;
+  GemmProblem pr;
+  if ((rc = fill_act(ctx, p->activation, 0, 0, p->leakyrelu_alpha, p->n, who, &pr.ap))) return rc;
+  cudaSetDevice(ctx->device);
+  GemmGroup grp;
+  grp.count = count;
+  for (int i = 0; i < count; ++i) {
+    Buffer *b, *bias = nullptr, *out;
+    if ((rc = ctx_get(ctx, b_ids[i], (uint64_t)p->k * p->n * 4, "fused_matmul_group b", &b))) return rc;
+    if (p->bias_len &&
+        (rc = ctx_get(ctx, bias_ids ? bias_ids[i] : 0, (uint64_t)p->bias_len * 4, "fused_matmul_group bias", &bias)))
+      return rc;
+    if ((rc = ctx_get(ctx, out_ids[i], (uint64_t)p->m * p->n * 4, "fused_matmul_group out", &out))) return rc;
+    for (int j = 0; j < i; ++j)
+      if (out_ids[j] == out_ids[i])
+        return ctx_fail(ctx, TFJS_CUDA_INVALID_ARG, "%s: two members share an output", who);
+    if (b->from_host) {
+      const float* packed;
+      if ((rc = get_packed(ctx, b_ids[i], b, 1, p->n, 1, p->k, p->k, p->transpose_b ? 1 : 0, &packed)))
+        return rc;
+      grp.b[i] = packed;
+    } else if (p->transpose_b) {
+      grp.b[i] = (const float*)b->ptr;
+    } else {
+      return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "%s: the members' B operands must be weights", who);
+    }
+    grp.bias[i] = bias ? (const float*)bias->ptr : nullptr;
+    grp.c[i] = (float*)out->ptr;
+  }
+  pr.a = (const float*)a->ptr;
+  pr.b = grp.b[0];
+  pr.c = grp.c[0];
+  pr.bias = grp.bias[0];
+  pr.bias_len = p->bias_len;
+  pr.M = p->m; pr.N = p->n; pr.K = p->k;
+  pr.batch = pr.batch_a = pr.batch_b = 1;
+  pr.trans_b = p->transpose_b != 0;
+  pr.out_perm = layout;
+  pr.perm_p = rows_or_heads;
+  pr.perm_d = head_dim;
+  Tf32Operands op;
+  op.a = pr.a;
+  op.lda = p->k;
+  op.k_steps = (p->k + 31) / 32;
+  op.b = grp.b[0];
+  op.ldb = p->k;
+  op.b_layout = B_K_MAJOR;
+  rc = launch_gemm_tf32(ctx, pr, op, &grp);
+  if (rc == TFJS_CUDA_OK)
+    for (int i = 0; i < count; ++i) ctx_mark_written(ctx, out_ids[i]);
+  return rc;
+}
+
 static int conv2d_impl(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p, int32_t x_id,
                        int32_t filter_id, int32_t bias_id, int32_t prelu_id,
                        int32_t residual_id, int32_t post_activation, int32_t out_id) {

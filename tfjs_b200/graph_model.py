@@ -755,6 +755,46 @@ def fuse_attention_heads(ordered, is_const, const_value, protected=()):
     return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
 
 
+def hoist_shared_operand_matmuls(ordered, is_const):
+    """Plan rewrite (scheduling only): products whose first operand is the same tensor and
+    whose other operands are constants run next to each other.  The backend launches the
+    products pending on one operand as a group; in the stored order of an attention layer
+    the value projection comes after the softmax and would miss the group of the query and
+    key projections."""
+    MATMULS = ("_FusedMatMul", "MatMul", "_MatMulHeads")
+    first, moved = {}, {}
+    for n in ordered:
+        if n.op not in MATMULS or len(n.inputs) < 2:
+            continue
+        if not all(is_const(parse_node_name(i)[0]) for i in n.inputs[1:]):
+            continue
+        a = n.inputs[0]
+        if a in first:
+            moved.setdefault(first[a], []).append(n)
+        else:
+            first[a] = n.name
+    if not moved:
+        return list(ordered), 0
+    late = set(m.name for ms in moved.values() for m in ms)
+    by_name = {n.name: n for n in ordered}
+    out, placed = [], set()
+    for n in ordered:
+        if n.name in late or n.name in placed:
+            continue
+        out.append(n)
+        placed.add(n.name)
+        for m in moved.get(n.name, ()):
+            # the constants a moved product reads must precede it
+            for i in m.inputs[1:]:
+                cname = parse_node_name(i)[0]
+                if cname not in placed and cname in by_name:
+                    out.append(by_name[cname])
+                    placed.add(cname)
+            out.append(m)
+            placed.add(m.name)
+    return out, len(late)
+
+
 # ------------------------------------------------------------------- executor --
 class GraphExecutor(object):
     def __init__(self, nodes, weight_map):
@@ -778,6 +818,7 @@ class GraphExecutor(object):
         self.fused_heads = 0
         self.fused_softmaxes = 0
         self.fused_gelus = 0
+        self.hoisted_matmuls = 0
         self.keep_intermediates = False
         self.intermediates = {}
 
@@ -851,6 +892,8 @@ class GraphExecutor(object):
                                                               protected=prot)
         if fuse and "softmax" not in self.fuse_skip:
             ordered, j = fuse_softmax_inputs(ordered, consts[0], consts[1], protected=prot)
+        if fuse and "hoist" not in self.fuse_skip:
+            ordered, self.hoisted_matmuls = hoist_shared_operand_matmuls(ordered, consts[0])
         if fuse:
             self.fused_subgraphs = n
             self.fused_heads = k

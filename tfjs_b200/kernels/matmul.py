@@ -9,6 +9,7 @@ from ctypes import byref
 import numpy as np
 
 from .. import _cabi
+from ..backend import PendingMatMul
 from ..kernel_registry import KernelConfig
 from ..util import assert_and_get_broadcast_shape, size_from_shape
 from .common import BACKEND, assert_not_complex, dev, per_channel_len, require_float32
@@ -55,6 +56,34 @@ def _matmul_impl(backend, a, b, transpose_a, transpose_b, bias, prelu, activatio
         raise _cabi.CudaError(_cabi.UNSUPPORTED, "matMul: gelu_erf needs a fusable bias")
     if heads is not None and not (fuse_bias and fuse_act and size_from_shape(out_shape)):
         raise _cabi.CudaError(_cabi.UNSUPPORTED, "matMul heads: bias / activation not fusable")
+    if (backend.lazy_fusion and backend.group_matmuls and fuse_bias and fuse_act and
+            batch_a == 1 and batch_b == 1 and not transpose_a and inner_a % 4 == 0 and
+            outer_b > 128 and activation not in ("prelu", "gelu_erf") and
+            (bias is None or bias_len == outer_b) and
+            # a heads-permuted store the library may decline must be refused here, at the
+            # call, where the node executor can still fall back to product + Reshape + Transpose
+            (heads is None or (heads[0] == _cabi.HEADS_SPLIT and backend.math_mode == "tf32" and
+                               heads[1] % 32 == 0 and heads[2] % 32 == 0)) and
+            size_from_shape(out_shape)):
+        # Deferred: products that share `a` and these dimensions launch as one group when
+        # the first of them is needed (the Q, K and V projections of an attention layer).
+        p = _cabi.MatMulParams()
+        p.batch_a, p.batch_b = 1, 1
+        p.m, p.n, p.k = outer_a, outer_b, inner_a
+        p.transpose_a, p.transpose_b = 0, int(bool(transpose_b))
+        p.activation = _cabi.ACTIVATIONS[activation]
+        p.bias_len = bias_len
+        p.prelu_len = 0
+        p.leakyrelu_alpha = 0.2 if alpha is None else float(alpha)
+        shape = out_shape if heads is None else heads[3]
+        desc = {"name": "_FusedMatMul" if heads is None else "_MatMulHeads",
+                "inputShapes": dict([("a", list(a.shape)), ("b", list(b.shape))] +
+                                    ([("bias", list(bias.shape))] if bias is not None else [])),
+                "outputShapes": [list(shape)],
+                "attrs": {"transposeA": False, "transposeB": bool(transpose_b)}}
+        return backend.defer(shape, "float32", PendingMatMul(
+            p, a.dataId, b.dataId, bias.dataId if bias is not None else None,
+            None if heads is None else tuple(heads[:3]), [desc]))
     out = backend.make_output(out_shape if heads is None else heads[3], "float32")
     if size_from_shape(out_shape) and batch_a and batch_b:
         p = _cabi.MatMulParams()

@@ -50,6 +50,19 @@ struct Args {
     if (len) *len = n;
     return p;
   }
+  // An Int32Array argument (element count in *count), or nullptr for null / undefined.
+  const int32_t* i32array(size_t i, size_t* count) const {
+    bool is_ta = false;
+    if (i < v.size()) napi_is_typedarray(env, v[i], &is_ta);
+    if (!is_ta) {
+      if (count) *count = 0;
+      return nullptr;
+    }
+    size_t n = 0;   // typed arrays report their length in elements
+    void* p = buffer(i, &n);
+    if (count) *count = n;
+    return static_cast<const int32_t*>(p);
+  }
 };
 
 napi_value undefined(napi_env env) { napi_value u; napi_get_undefined(env, &u); return u; }
@@ -202,6 +215,23 @@ napi_value FusedMatMulHeads(napi_env env, napi_callback_info info) {
   auto* p = static_cast<tfjs_cuda_matmul_params*>(a.buffer(1));
   return check(env, a.ctx(0), tfjs_cuda_fused_matmul_heads(a.ctx(0), p, a.i32(2), a.i32(3), a.i32(4), a.i32(5),
                                                            a.i32(6), a.i32(7), a.i32(8), a.i32(9)));
+}
+// ctx, params, aId, bIds (Int32Array), biasIds (Int32Array or null), layout, rowsOrHeads, headDim,
+// outIds (Int32Array).  Returns false when the library does not take the group (the caller
+// then launches the members one by one); other errors throw.
+napi_value FusedMatMulGroup(napi_env env, napi_callback_info info) {
+  Args a(env, info);
+  auto* p = static_cast<tfjs_cuda_matmul_params*>(a.buffer(1));
+  size_t count = 0;
+  const int32_t* b_ids = a.i32array(3, &count);
+  const int32_t* bias_ids = a.i32array(4, nullptr);
+  const int32_t* out_ids = a.i32array(8, nullptr);
+  const int rc = tfjs_cuda_fused_matmul_group(a.ctx(0), p, a.i32(2), (int32_t)count, b_ids, bias_ids,
+                                              a.i32(5), a.i32(6), a.i32(7), out_ids);
+  napi_value r;
+  napi_get_boolean(env, rc == TFJS_CUDA_OK, &r);
+  if (rc != TFJS_CUDA_OK && rc != TFJS_CUDA_UNSUPPORTED) napi_throw_error(env, nullptr, tfjs_cuda_last_error(a.ctx(0)));
+  return r;
 }
 napi_value Pool2D(napi_env env, napi_callback_info info) {
   Args a(env, info);
@@ -388,7 +418,7 @@ napi_value Init(napi_env env, napi_value exports) {
       {"setMathMode", SetMathMode}, {"fusedConv2d", FusedConv2D},
       {"fusedConv2dResidual", FusedConv2DResidual}, {"fusedDepthwiseProject", FusedDepthwiseProject},
       {"addActivation", AddActivation},
-      {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul}, {"fusedMatMulHeads", FusedMatMulHeads},
+      {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul}, {"fusedMatMulHeads", FusedMatMulHeads}, {"fusedMatMulGroup", FusedMatMulGroup},
       {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm}, {"softmaxScaledMasked", SoftmaxScaledMasked},
       {"reduce", Reduce}, {"argMax", ArgMax}, {"transpose", Transpose}, {"gather", Gather},
       {"cast", Cast}, {"copyStrided", CopyStrided}, {"fill", Fill}, {"batchNorm", BatchNorm},

@@ -9,7 +9,7 @@ import {backend_util, BackendTimingInfo, DataStorage, DataType, engine, KernelBa
         TensorInfo, TypedArray, util} from '@tensorflow/tfjs-core';
 
 import {binding, Ctx} from './binding';
-import {Desc, Pending, PendingConv, PendingDepthwise} from './pending';
+import {Desc, Pending, PendingConv, PendingDepthwise, PendingMatMul} from './pending';
 
 interface Record {
   id: number;          // device buffer id; 0 = host-resident or not launched yet
@@ -103,6 +103,7 @@ export class CudaBackend extends KernelBackend {
     const dataId = {};
     for (const d of pending.deps()) this.adjust(this.data.get(d), 1, 1);
     this.data.set(dataId, {id: 0, nbytes, dtype, refCount: 1, pending, held: 0});
+    if (pending instanceof PendingMatMul) this.noteMatMul(dataId, pending);
     return {dataId, shape, dtype};
   }
 
@@ -124,8 +125,74 @@ export class CudaBackend extends KernelBackend {
     }
   }
 
+  /** Products that share their first operand launch together (TFJS_CUDA_NO_MATMUL_GROUP=1
+   * launches each on its own); dataId of `a` -> dataIds of the pending products on it. */
+  groupMatMuls = !['1', 'true'].includes(process.env['TFJS_CUDA_NO_MATMUL_GROUP'] ?? '0');
+  private matMulsOn = new Map<object, object[]>();
+
+  private stillPendingMatMul(dataId: object): boolean {
+    return this.data.has(dataId) && this.data.get(dataId).pending instanceof PendingMatMul;
+  }
+
+  private noteMatMul(dataId: object, pending: PendingMatMul): void {
+    const ids = (this.matMulsOn.get(pending.a) ?? []).filter(d => this.stillPendingMatMul(d));
+    this.matMulsOn.set(pending.a, [...ids, dataId]);
+    if (this.matMulsOn.size > 64) {   // forget operands whose products are all gone
+      for (const [a, list] of this.matMulsOn) {
+        if (!list.some(d => this.stillPendingMatMul(d))) this.matMulsOn.delete(a);
+      }
+    }
+  }
+
+  /** Launches `pending` together with the other products pending on the same operand (same
+   * dimensions, layout and bias kind).  False when there is none or the library does not
+   * take the group; nothing has been launched then. */
+  private resolveMatMulGroup(r: Record, pending: PendingMatMul): boolean {
+    const mates = (this.matMulsOn.get(pending.a) ?? [])
+                      .filter(d => this.stillPendingMatMul(d))
+                      .map(d => this.data.get(d) as Record)
+                      .filter(m => m !== r && (m.pending as PendingMatMul).key === pending.key)
+                      .slice(0, 3);
+    if (!this.groupMatMuls || mates.length === 0) return false;
+    // operands that are pending launch first; the group is what is still pending then
+    const of0 = (m: Record) => m.pending as PendingMatMul;
+    this.deviceIdOf(pending.a);
+    for (const m of [r, ...mates]) {
+      if (m.pending instanceof PendingMatMul) {
+        this.deviceIdOf(of0(m).b);
+        if (of0(m).bias != null) this.deviceIdOf(of0(m).bias!);
+      }
+    }
+    const ready = mates.filter(m => m.pending instanceof PendingMatMul);
+    if (r.pending !== pending || ready.length === 0) return false;
+    const members = [r, ...ready];
+    const devs = members.map(m => binding.alloc(this.ctx, m.nbytes));
+    let ok = false;
+    try {
+      const of = (m: Record) => m.pending as PendingMatMul;
+      const heads = pending.heads ?? [0, 0, 0];
+      ok = binding.fusedMatMulGroup(
+          this.ctx, pending.params, this.deviceIdOf(pending.a),
+          Int32Array.from(members.map(m => this.deviceIdOf(of(m).b))),
+          Int32Array.from(members.map(m => of(m).bias != null ? this.deviceIdOf(of(m).bias!) : 0)),
+          heads[0], heads[1], heads[2], Int32Array.from(devs));
+    } finally {
+      if (!ok) devs.forEach(d => binding.free(this.ctx, d));
+    }
+    if (!ok) return false;
+    members.forEach((m, i) => {
+      const done = m.pending!;
+      m.pending = undefined;
+      m.id = devs[i];
+      this.release(done);
+    });
+    return true;
+  }
+
   private resolve(r: Record): void {
     const pending = r.pending!;
+    if (pending instanceof PendingMatMul && this.resolveMatMulGroup(r, pending)) return;
+    if (r.pending !== pending) return;     // launched meanwhile, by an operand's own launch
     const dev = binding.alloc(this.ctx, r.nbytes);
     try {
       pending.launch(this, dev);
@@ -244,6 +311,10 @@ export class CudaBackend extends KernelBackend {
   override timerAvailable(): boolean { return true; }
   override floatPrecision(): 16|32 { return 32; }
   override epsilon(): number { return 1e-7; }
-  setMathMode(mode: 'tf32'|'fp32'): void { binding.setMathMode(this.ctx, mode === 'tf32' ? 0 : 1); }
+  mathMode: 'tf32'|'fp32' = 'tf32';
+  setMathMode(mode: 'tf32'|'fp32'): void {
+    binding.setMathMode(this.ctx, mode === 'tf32' ? 0 : 1);
+    this.mathMode = mode;
+  }
   override dispose(): void { /* the context is destroyed when the external is collected */ }
 }

@@ -48,6 +48,10 @@ export interface CudaBinding {
   fusedMatMulHeads(ctx: Ctx, params: ArrayBuffer, a: number, b: number, bias: number,
                    prelu: number, layout: number, rowsOrHeads: number, headDim: number,
                    out: number): void;
+  /** Products sharing `a`; false when the library does not take the group (launch the
+   * members one by one). */
+  fusedMatMulGroup(ctx: Ctx, params: ArrayBuffer, a: number, b: Int32Array, bias: Int32Array|null,
+                   layout: number, rowsOrHeads: number, headDim: number, out: Int32Array): boolean;
   pool2d(ctx: Ctx, params: ArrayBuffer, isMax: number, x: number, out: number): void;
   binary(ctx: Ctx, op: number, dtype: number, rank: number, a: number, aShape: BigInt64Array,
          b: number, bShape: BigInt64Array, out: number, outShape: BigInt64Array): void;

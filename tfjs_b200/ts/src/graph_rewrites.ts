@@ -10,6 +10,8 @@
  *   fuseAttentionHeads  matMul + Reshape + Transpose([0,2,1,3]) and batchMatMul + Transpose +
  *                       Reshape -> _MatMulHeads
  *   fuseSoftmaxInputs   Softmax(AddV2(Mul(scores, c), mask)) -> _SoftmaxScaledMasked
+ *   hoistSharedOperandMatMuls  products on one operand run next to each other, so that the
+ *                       backend launches them as a group
  *
  * A subgraph is replaced only if its intermediates have no consumer outside it and are not
  * among the model's signature outputs; the new node keeps the name of the subgraph's last
@@ -213,6 +215,53 @@ export function fuseSoftmaxInputs(nodes: NodeDef[], consts: Consts, prot: Set<st
   return apply(nodes, removed, replaced);
 }
 
+/**
+ * Scheduling only: products whose first operand is the same tensor and whose other operands
+ * are constants are moved next to the first of them in the stored node list (with the
+ * constants they read).  The backend launches the products pending on one operand as a
+ * group (PendingMatMul); in the stored order of an attention layer the value projection
+ * comes after the softmax and would miss the group of the query and key projections.  The
+ * converter derives its execution order from this list (children are visited in list
+ * order), so products that become ready together stay together; where its traversal
+ * separates them anyway, only the ones pending at the same time form a group.
+ * Python twin: hoist_shared_operand_matmuls (tfjs_b200/graph_model.py).
+ */
+export function hoistSharedOperandMatMuls(nodes: NodeDef[]): NodeDef[] {
+  const MATMULS = new Set(['_FusedMatMul', 'MatMul', '_MatMulHeads']);
+  const byName = new Map(nodes.map(n => [n.name, n] as [string, NodeDef]));
+  const isConst = (inp: string) => byName.get(nodeName(inp))?.op === 'Const';
+  const first = new Map<string, string>();
+  const moved = new Map<string, NodeDef[]>();
+  for (const n of nodes) {
+    const inputs = n.input ?? [];
+    if (!MATMULS.has(n.op) || inputs.length < 2 || !inputs.slice(1).every(isConst)) continue;
+    const lead = first.get(inputs[0]);
+    if (lead != null) moved.set(lead, [...(moved.get(lead) ?? []), n]);
+    else first.set(inputs[0], n.name);
+  }
+  if (moved.size === 0) return nodes;
+  const late = new Set([...moved.values()].flat().map(n => n.name));
+  const out: NodeDef[] = [];
+  const placed = new Set<string>();
+  for (const n of nodes) {
+    if (late.has(n.name) || placed.has(n.name)) continue;
+    out.push(n);
+    placed.add(n.name);
+    for (const m of moved.get(n.name) ?? []) {
+      for (const inp of (m.input ?? []).slice(1)) {      // its constants must precede it
+        const c = byName.get(nodeName(inp));
+        if (c != null && !placed.has(c.name)) {
+          out.push(c);
+          placed.add(c.name);
+        }
+      }
+      out.push(m);
+      placed.add(m.name);
+    }
+  }
+  return out;
+}
+
 /** The three rewrites over a loaded model's topology (in place on a copy of the artifacts).
  * TFJS_CUDA_NO_GRAPH_FUSION = 1 | all switches them off; a comma-separated list of
  * layernorm, heads, softmax switches single ones off. */
@@ -229,6 +278,7 @@ export function rewriteArtifacts(artifacts: io.ModelArtifacts): io.ModelArtifact
   if (!skip.has('layernorm')) nodes = fuseLayerNorms(nodes, consts, prot);
   if (!skip.has('heads')) nodes = fuseAttentionHeads(nodes, consts, prot);
   if (!skip.has('softmax')) nodes = fuseSoftmaxInputs(nodes, consts, prot);
+  if (!skip.has('hoist')) nodes = hoistSharedOperandMatMuls(nodes);
   topology.node = nodes;
   return {...artifacts, modelTopology: topology};
 }

@@ -13,6 +13,7 @@ import {KernelConfig, KernelFunc, TensorInfo, util} from '@tensorflow/tfjs-core'
 import {CudaBackend} from '../backend_cuda';
 import {ACTIVATION, binding, packMatMulParams} from '../binding';
 import {perChannelLen} from './conv';
+import {deferMatMul} from './matmul';
 
 type Args = {inputs: {[k: string]: TensorInfo}, attrs: {[k: string]: unknown}, backend: CudaBackend};
 const asFunc = (f: (a: Args) => TensorInfo) => f as unknown as KernelFunc;
@@ -87,6 +88,10 @@ export const fusedGraphOpConfigs: KernelConfig[] = [
     const biasLen = perChannelLen(bias, n);
     if (biasLen == null) throw new UnsupportedByLibrary('matMul heads: bias shape');
     const outShape = split ? [B, H, S, D] : [B, S, H, D];
+    const activation = (attrs['activation'] as string) ?? 'linear';
+    const deferred = deferMatMul(backend, a, b, bias, activation, 0.2, ta, tb, batchA, batchB, m, n, k,
+                                 biasLen, [split ? 1 : 2, split ? S : H, D], outShape);
+    if (deferred != null) return deferred;
     const out = backend.makeOutput(outShape, 'float32');
     try {
       binding.fusedMatMulHeads(

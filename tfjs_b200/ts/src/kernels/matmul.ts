@@ -4,8 +4,38 @@ import {_FusedMatMul, BatchMatMul, broadcast_util, KernelConfig, KernelFunc, Ten
 
 import {CudaBackend} from '../backend_cuda';
 import {ACTIVATION, binding, packMatMulParams} from '../binding';
+import {PendingMatMul} from '../pending';
 import {perChannelLen} from './conv';
 import {applyActivation, binaryImpl} from './elementwise';
+
+/**
+ * Deferred: products that share `a` and these dimensions launch as one group when the first
+ * of them is needed (the Q, K and V projections of an attention layer); null when this
+ * product does not qualify (batched operands, a transposed `a`, narrow outputs, PReLU, a bias
+ * that is not one value per column).
+ */
+export function deferMatMul(
+    backend: CudaBackend, a: TensorInfo, b: TensorInfo, bias: TensorInfo|undefined, activation: string,
+    alpha: number, transposeA: boolean, transposeB: boolean, batchA: number, batchB: number, m: number,
+    n: number, k: number, biasLen: number|null, heads: [number, number, number]|null,
+    outShape: number[]): TensorInfo|null {
+  if (!(backend.lazyFusion && backend.groupMatMuls && biasLen != null && batchA === 1 && batchB === 1 &&
+        !transposeA && k % 4 === 0 && n > 128 && activation !== 'prelu' &&
+        (bias == null || biasLen === n) &&
+        // a heads-permuted store the library may decline is refused at the call, where the
+        // node executor can still fall back to product + Reshape + Transpose
+        (heads == null || (heads[0] === 1 && backend.mathMode === 'tf32' && heads[1] % 32 === 0 &&
+                           heads[2] % 32 === 0)) &&
+        util.sizeFromShape(outShape) > 0)) {
+    return null;
+  }
+  const inputShapes: {[key: string]: number[]} = {a: a.shape, b: b.shape};
+  if (bias != null) inputShapes['bias'] = bias.shape;
+  const desc = {name: heads == null ? _FusedMatMul : '_MatMulHeads', inputShapes, outputShapes: [outShape]};
+  return backend.defer(outShape, 'float32', new PendingMatMul(
+      packMatMulParams(1, 1, m, n, k, false, transposeB, ACTIVATION[activation], biasLen, 0, alpha),
+      a.dataId, b.dataId, bias != null ? bias.dataId : null, heads, [desc]));
+}
 
 function matMulImpl(
     backend: CudaBackend, a: TensorInfo, b: TensorInfo, transposeA: boolean, transposeB: boolean,
@@ -26,6 +56,10 @@ function matMulImpl(
   const preluLen = activation === 'prelu' ? perChannelLen(prelu, outerB) : 0;
   const fuseBias = biasLen != null;
   const fuseAct = fuseBias && (activation !== 'prelu' || preluLen != null);
+  const deferred = deferMatMul(backend, a, b, bias, activation, alpha, transposeA, transposeB,
+                               batchA, batchB, outerA, outerB, innerA, fuseBias && fuseAct ? biasLen : null,
+                               null, outShape);
+  if (deferred != null) return deferred;
   let out = backend.makeOutput(outShape, 'float32');
   if (util.sizeFromShape(outShape) > 0) {
     binding.fusedMatMul(

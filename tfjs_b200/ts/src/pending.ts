@@ -62,14 +62,19 @@ export class PendingConv implements Pending {
   private launchWithDepthwise(backend: CudaBackend, outDev: number): boolean {
     const dw = backend.pendingOfId(this.x);
     if (!backend.fuseDepthwiseProject || !(dw instanceof PendingDepthwise)) return false;
-    const bias = this.bias != null ? backend.deviceIdOf(this.bias) : 0;
     // without a shortcut the trailing activation is the projection's own
     const pw = this.residual == null ? setActivation(this.params, this.act) : this.params;
+    // Operands that are pending themselves launch now, and such a launch may, further down,
+    // need this very depthwise result and materialise it (a block's output feeds both the
+    // next block and that block's shortcut).  So the shortcut and the weights come first,
+    // then the depthwise convolution is looked at again, and its input, which it keeps
+    // alive, comes last.
+    const ids = [dw.filter, dw.bias, this.filter, this.bias, this.residual]
+                    .map(d => d != null ? backend.deviceIdOf(d) : 0);
+    if (backend.pendingOfId(this.x) !== dw) return false;
     const ok = binding.fusedDepthwiseProject(
-        backend.ctx, setActivation(dw.params, dw.act), pw, backend.deviceIdOf(dw.x),
-        backend.deviceIdOf(dw.filter), dw.bias != null ? backend.deviceIdOf(dw.bias) : 0,
-        backend.deviceIdOf(this.filter), bias,
-        this.residual != null ? backend.deviceIdOf(this.residual) : 0,
+        backend.ctx, setActivation(dw.params, dw.act), pw, backend.deviceIdOf(dw.x), ids[0], ids[1],
+        ids[2], ids[3], ids[4],
         this.residual != null ? ACTIVATION[this.act] : ACTIVATION['linear'], outDev);
     if (ok && !this.dwFolded) {
       // profile records: the depthwise kernels join this launch, and the convolution no
@@ -122,6 +127,36 @@ export class PendingDepthwise implements Pending {
         backend.ctx, setActivation(this.params, this.act), backend.deviceIdOf(this.x),
         backend.deviceIdOf(this.filter), this.bias != null ? backend.deviceIdOf(this.bias) : 0, 0,
         outDev);
+  }
+}
+
+/**
+ * A _FusedMatMul (or its heads-split form) with a fused bias, not launched yet.  When it is
+ * launched, the other products still pending on the same `a` operand with the same
+ * dimensions (the query, key and value projections of an attention layer) go with it in
+ * one `fusedMatMulGroup` launch (CudaBackend.resolveMatMulGroup); each member's result is
+ * the one its own launch would give.
+ */
+export class PendingMatMul implements Pending {
+  readonly key: string;
+  constructor(
+      readonly params: ArrayBuffer, readonly a: object, readonly b: object,
+      readonly bias: object|null,
+      /** [layout, rowsOrHeads, headDim] of the permuted store, or null */
+      readonly heads: [number, number, number]|null, readonly desc: Desc[]) {
+    this.key = `${Array.from(new Uint8Array(params)).join(',')}|${heads}|${bias == null}`;
+  }
+  deps(): object[] { return [this.a, this.b, this.bias].filter(d => d != null) as object[]; }
+  launch(backend: CudaBackend, outDev: number): void {
+    const bias = this.bias != null ? backend.deviceIdOf(this.bias) : 0;
+    if (this.heads == null) {
+      binding.fusedMatMul(backend.ctx, this.params, backend.deviceIdOf(this.a),
+                          backend.deviceIdOf(this.b), bias, 0, outDev);
+    } else {
+      binding.fusedMatMulHeads(backend.ctx, this.params, backend.deviceIdOf(this.a),
+                               backend.deviceIdOf(this.b), bias, 0, this.heads[0], this.heads[1],
+                               this.heads[2], outDev);
+    }
   }
 }
 
