@@ -4,7 +4,8 @@ op front end with CUDA events on the backend's stream.
     python kernel_bench.py <case> [iterations]
 
 cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072),
-mm_<m>_<k>_<n> (fused matMul + bias),
+mm_<m>_<k>_<n> (fused matMul + bias), qkv_<m>_<k>_<n> (three of them on one activation: one
+grouped launch),
 pw_<hw>_<cin>_<cout>_<batch> (1x1 conv), c3_<hw>_<cin>_<cout>_<batch>_<stride> (3x3
 conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<batch>_<stride>
 (3x3 depthwise), res_<hw>_<cin>_<cout>_<batch> (1x1 conv + bias, Add of a shortcut, Relu:
@@ -61,6 +62,17 @@ elif case=='ffn':
     a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
     bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
     f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'linear'); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
+elif case.startswith('qkv_'):   # qkv_<m>_<k>_<n>: three fused matMuls + bias on one activation (one grouped launch)
+    _,m,k,n=case.split('_'); m,k,n=int(m),int(k),int(n)
+    a0=ops.tensor(r.standard_normal((m,k)).astype(np.float32)/32); zero=ops.tensor(np.float32(0)); a=ops.add(a0,zero); be.device_id(a.dataId)
+    ws=[ops.tensor(r.standard_normal((k,n)).astype(np.float32)/32) for _ in range(3)]
+    bs=[ops.tensor(r.standard_normal(n).astype(np.float32)) for _ in range(3)]
+    def f():
+        ys=[ops.fused_mat_mul(a,w,False,False,b,'linear') for w,b in zip(ws,bs)]
+        for y in ys: be.device_id(y.dataId)
+        for y in ys[1:]: y.dispose()
+        return ys[0]
+    fl=3*2*m*n*k; by=4*(m*k+3*k*n+3*m*n)
 elif case.startswith('mm_'):   # mm_<m>_<k>_<n>: fused matMul + bias
     _,m,k,n=case.split('_'); m,k,n=int(m),int(k),int(n)
     a=ops.tensor(r.standard_normal((m,k)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((k,n)).astype(np.float32)/32)

@@ -37,7 +37,7 @@ struct Tf32Args {
   int patch_pitch;        // floats between patch rows (left margin + image row + right margin)
   int patch_ml;           // floats of left margin
   int patch_rows;         // image rows a buffer holds; row `patch_rows` stays zero
-  int patch_bufs;         // patch buffers (2 to 4); tiles are staged patch_bufs - 1 ahead
+  int patch_bufs;         // patch buffers (2 to 8); tiles are staged patch_bufs - 1 ahead
   uint32_t ow_mul, ow_shr, oh_mul, oh_shr;  // division by out_w / out_h as multiply-shift
   // gathered convolution
   const float* x;

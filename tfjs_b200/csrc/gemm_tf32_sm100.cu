@@ -35,6 +35,11 @@
 
 namespace {
 
+// Input patches of the staged-row gather that may be in flight (a tile's rows are fetched
+// this many tiles ahead, less one): the copies come from DRAM, and with 13-30 KB per patch
+// it takes several of them to cover its latency.
+constexpr int kMaxPatchBufs = 8;
+
 // RES: the epilogue adds a residual tile that the TMA unit prefetches into the
 // staging tile of the next chunk (two staging tiles per warp, and at BN = 256 one
 // pipeline stage fewer to make room for them).
@@ -53,7 +58,7 @@ struct Cfg {
       (kMaxSmemBytes - 1024 - kBarrierBytes - EW * EPI_BUFS * 4096) /
       (A_STAGE_BYTES + B_STAGE_BYTES);
   static constexpr int STAGES =
-      A_MODE == 3 ? (BN == 32 ? 5 : (BN == 64 ? 4 : 3))
+      A_MODE == 3 ? (BN <= 64 ? 3 : 2)
                   : (STAGES_FIT < STAGES_WANTED ? STAGES_FIT : STAGES_WANTED);
   // TMEM accumulator stages.  A tile's accumulator is handed back and forth through
   // two barriers whose wake-ups cost more than a short tile's MMAs, so narrow tiles
@@ -126,7 +131,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
         mbar_init(res_bar(w, 1), 1);
       }
     if (A_MODE == 3) {  // "patch landed" barriers (this mode has no residual epilogue)
-      for (int b = 0; b < 4; ++b) mbar_init(res_bar(b >> 1, b & 1), 1);
+      for (int b = 0; b < kMaxPatchBufs; ++b) mbar_init(res_bar(b >> 1, b & 1), 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1246,7 +1251,7 @@ bool tf32_patch_plan(const ConvGeo& cv, int M, int N, int sm_count, PatchPlan* p
   const int bn = pick_bn(M, N, 1, sm_count);
   long long bufs = (kMaxSmemBytes - smem_base_mode3(bn)) / bytes;
   if (bufs < 2) return false;
-  plan->bufs = bufs > 4 ? 4 : (int)bufs;
+  plan->bufs = bufs > kMaxPatchBufs ? kMaxPatchBufs : (int)bufs;
   plan->bytes = (int)bytes;
   plan->pitch = (int)pitch;
   plan->ml = ml;
