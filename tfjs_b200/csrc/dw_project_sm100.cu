@@ -423,6 +423,7 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       {
         // plain loads (not asm) so the compiler may schedule them among the arithmetic
         const uint8_t* wk = smem_raw + (w_base - smem0) + (uint32_t)(ks * 80 + c4) * 16u;
+        __builtin_assume(__isShared(wk));
 #pragma unroll
         for (int k = 0; k < 9; ++k) {
           const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(wk + k * 128);
@@ -444,6 +445,9 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       if (active) {
         const uint8_t* patch = smem_raw + (p_base - smem0) + (uint32_t)ps * T::PATCH_BYTES + patch_off;
         uint8_t* a_tile = smem_raw + (a_base - smem0) + (uint32_t)as * A_STAGE_BYTES;
+        // these are shared-memory addresses: ld.shared / st.shared, not generic accesses
+        __builtin_assume(__isShared(patch));
+        __builtin_assume(__isShared(a_tile));
         unsigned long long a2[3][T::S][2];
 #pragma unroll
         for (int a = 0; a < 3; ++a)
