@@ -114,6 +114,10 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  if (threadIdx.x == 96) {
+    prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_b);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < 8; ++s) {
       mbar_init(patch_full(s), 1);

@@ -80,6 +80,11 @@ __device__ __forceinline__ void tma_load_im2col(uint32_t dst, const CUtensorMap*
       "l"(tm), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
       : "memory");
 }
+// Starts the fetch of a tensor map (a kernel parameter) into the TMA unit's descriptor
+// cache, so that the first load or store through it does not wait for it.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }

@@ -132,6 +132,18 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int pair = (int)(blockIdx.x >> 1);
   const int npairs = (int)(gridDim.x >> 1);
 
+  if (threadIdx.x == 32) {
+    prefetch_tensormap(&tm_a);
+    if (GROUP) {
+      for (int i = 0; i < grp.count; ++i) {
+        prefetch_tensormap(&grp.b[i]);
+        prefetch_tensormap(&grp.c[i]);
+      }
+    } else {
+      prefetch_tensormap(&tm_b);
+      prefetch_tensormap(&tm_c);
+    }
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);    // the leader's expect_tx arrival (used in the leader only)

@@ -116,6 +116,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  if (threadIdx.x == 32) {
+    if (A_MODE == 0 || A_MODE == 2 || SWAP) prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+    if (g.c_tma) prefetch_tensormap(&tm_c);
+    if (RES && g.residual) prefetch_tensormap(&tm_r);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), (A_MODE == 1 || A_MODE == 3) ? 1 + 4 : 1);  // producer + 4 gather warps
