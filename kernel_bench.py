@@ -3,7 +3,8 @@ op front end with CUDA events on the backend's stream.
 
     python kernel_bench.py <case> [iterations]
 
-cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072),
+cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072), ffng (ffn with
+the erf GELU as epilogue),
 mm_<m>_<k>_<n> (fused matMul + bias), qkv_<m>_<k>_<n> (three of them on one activation: one
 grouped launch),
 pw_<hw>_<cin>_<cout>_<batch> (1x1 conv), c3_<hw>_<cin>_<cout>_<batch>_<stride> (3x3
@@ -62,6 +63,10 @@ elif case=='ffn':
     a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
     bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
     f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'linear'); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
+elif case=='ffng':   # the same product with the erf GELU as its epilogue
+    a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
+    bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
+    f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'gelu_erf',None,0.2,[float(np.float32(1/np.sqrt(2))),0.5,1.0,0.0]); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
 elif case.startswith('qkv_'):   # qkv_<m>_<k>_<n>: three fused matMuls + bias on one activation (one grouped launch)
     _,m,k,n=case.split('_'); m,k,n=int(m),int(k),int(n)
     a0=ops.tensor(r.standard_normal((m,k)).astype(np.float32)/32); zero=ops.tensor(np.float32(0)); a=ops.add(a0,zero); be.device_id(a.dataId)

@@ -274,7 +274,7 @@ def test_bert_with_folded_head_transposes_matches_the_stored_graph(cuda_engine):
         outs.append(y.arraySync())
         assert gm.executor.fused_heads == (8 if fuse else 0)
         assert gm.executor.fused_softmaxes == (2 if fuse else 0)
-        assert gm.executor.fused_gelus == 0   # opt-in (slower than the chain kernel)
+        assert gm.executor.fused_gelus == (2 if fuse else 0)
         y.dispose()
         assert be.numDataIds() == before
         for t in ins.values():

@@ -283,9 +283,10 @@ def _in_mode(engine, mode, case):
 
 # Bounds of the default mode's fp32 evaluations against the double-precision oracle: a few
 # units in the last place for exp / sigmoid / tanh / elu; erf is the reference's polynomial
-# in fp32, whose cancellation near zero leaves an absolute error.
+# in fp32 with the special-function unit's reciprocal and exponential (1 and 2 units in the
+# last place), whose cancellation near zero leaves an absolute error.
 FP32_EVAL_REL = 6e-7
-FP32_ERF_ABS = 5e-7
+FP32_ERF_ABS = 8e-7
 
 
 @pytest.mark.parametrize("mode", ["fp32", "tf32"])

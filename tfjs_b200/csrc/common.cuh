@@ -277,8 +277,10 @@ __device__ __forceinline__ float js_erf(float x) {
 // pipe.  The contract for floating-point kernels is a tolerance (2e-3 * max|ref| per layer
 // with TF32 tensor-core inputs), so in the TF32 math mode these kernels evaluate in fp32:
 // the CUDA library's expf / tanhf / expm1f (at most 2 ulp) and the reference's own erf
-// polynomial (tfjs-core/src/ops/erf_util.ts:18-23) with fp32 coefficients, whose result is
-// within 5e-7 absolute of the double evaluation.  TFJS_CUDA_MATH_FP32 keeps the double
+// polynomial (tfjs-core/src/ops/erf_util.ts:18-23) with fp32 coefficients, its reciprocal
+// and exponential on the special-function unit (rcp.approx, ex2.approx: a branch-free
+// sequence of about 17 instructions that a GEMM epilogue can afford), whose result is
+// within 8e-7 absolute of the double evaluation.  TFJS_CUDA_MATH_FP32 keeps the double
 // sequences.  The op numbers below are internal (the launchers substitute them for the
 // public ones); every kernel that evaluates such an op, alone or inside a chain, calls the
 // same device function, so fused and separate launches still agree bit for bit.
@@ -300,16 +302,81 @@ static inline int fast_unary_op(int op) {
     default: return op;
   }
 }
+__device__ __forceinline__ float exp2_approx(float a) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+  return r;
+}
+__device__ __forceinline__ float rcp_approx(float a) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+  return r;
+}
 __device__ __forceinline__ float erf_f32(float x) {
   const float ax = fabsf(x);
-  const float t = __frcp_rn(__fmaf_rn(0.3275911f, ax, 1.0f));
+  const float t = rcp_approx(__fmaf_rn(0.3275911f, ax, 1.0f));   // argument in [1, inf]
   float q = __fmaf_rn(1.061405429f, t, -1.453152027f);
   q = __fmaf_rn(q, t, 1.421413741f);
   q = __fmaf_rn(q, t, -0.284496736f);
   q = __fmaf_rn(q, t, 0.254829592f);
   q = __fmul_rn(q, t);
-  const float r = __fmaf_rn(-q, expf(-__fmul_rn(ax, ax)), 1.0f);
+  // exp(-x^2) = 2^(-x^2 * log2(e)); beyond |x| = 4 the term is below fp32 resolution of 1
+  const float e = exp2_approx(__fmul_rn(__fmul_rn(ax, ax), -1.4426950408889634f));
+  const float r = __fmaf_rn(-q, e, 1.0f);
   return x == 0.0f ? x : copysignf(r, x);   // sign(0) * anything = 0 in the reference
+}
+// Two fp32 values in one 64-bit register for the packed arithmetic of sm_100
+// (fma / mul / add .rn.f32x2: the same IEEE operation on each half, one instruction).
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a,
+                                                        unsigned long long b,
+                                                        unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a,
+                                                        unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a,
+                                                        unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// erf_f32 of two values: the same operations with the same roundings, the multiplications
+// and fused multiply-adds two at a time.  The polynomial runs with negated coefficients
+// (exactly -q), which saves negating q for the last step.
+__device__ __forceinline__ unsigned long long erf_f32x2(unsigned long long x) {
+  float x0, x1;
+  unpack_f32x2(x, x0, x1);
+  const unsigned long long ax = pack_f32x2(fabsf(x0), fabsf(x1));
+#define TFJS_K2(c) pack_f32x2(c, c)
+  float d0, d1;
+  unpack_f32x2(fma_f32x2(TFJS_K2(0.3275911f), ax, TFJS_K2(1.0f)), d0, d1);
+  const unsigned long long t = pack_f32x2(rcp_approx(d0), rcp_approx(d1));
+  unsigned long long q = fma_f32x2(TFJS_K2(-1.061405429f), t, TFJS_K2(1.453152027f));
+  q = fma_f32x2(q, t, TFJS_K2(-1.421413741f));
+  q = fma_f32x2(q, t, TFJS_K2(0.284496736f));
+  q = fma_f32x2(q, t, TFJS_K2(-0.254829592f));
+  q = mul_f32x2(q, t);
+  float g0, g1;
+  unpack_f32x2(mul_f32x2(mul_f32x2(ax, ax), TFJS_K2(-1.4426950408889634f)), g0, g1);
+  const unsigned long long e = pack_f32x2(exp2_approx(g0), exp2_approx(g1));
+  float r0, r1;
+  unpack_f32x2(fma_f32x2(q, e, TFJS_K2(1.0f)), r0, r1);
+#undef TFJS_K2
+  return pack_f32x2(x0 == 0.0f ? x0 : copysignf(r0, x0), x1 == 0.0f ? x1 : copysignf(r1, x1));
 }
 __device__ __forceinline__ float sigmoid_f32(float x) {
   return __frcp_rn(__fadd_rn(1.0f, expf(-x)));

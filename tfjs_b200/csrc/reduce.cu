@@ -166,6 +166,85 @@ __global__ void softmax_kernel(const float* __restrict__ x, float* __restrict__ 
   }
 }
 
+// FAST for rows of a multiple of four floats at 16-byte aligned addresses: a lane holds
+// 16-byte pieces of its row (R4 of them: rows up to 128 * R4 floats), so a row of 128 is one
+// load, one mask load and one store per lane.  Pieces beyond the row hold -inf, whose
+// exponential is 0: the reductions need no predicates.  max.NaN keeps a NaN as the
+// reference's Math.max does; e = 2^((x - max) * log2(e)) on the special-function unit
+// (two units in the last place; the argument's rounding adds |x - max| * 2^-24 relative, at
+// most 2e-8 of the largest term).
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+template <int R4>
+__global__ void __launch_bounds__(kThreads, R4 == 1 ? 8 : 1)
+softmax_vec_kernel(const float* __restrict__ x, float* __restrict__ y, uint64_t rows,
+                   uint32_t cols, SoftmaxPrologue pg) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  const uint32_t n4 = cols >> 2;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 nx[R4], nm[R4];
+  auto fetch = [&](uint64_t row) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+    const uint64_t mrow_idx = (row | pg.rows_per_mask) >> 32
+                                  ? row / pg.rows_per_mask
+                                  : (uint64_t)((uint32_t)row / (uint32_t)pg.rows_per_mask);
+    const float4* mr =
+        pg.mask ? reinterpret_cast<const float4*>(pg.mask + mrow_idx * cols) : nullptr;
+#pragma unroll
+    for (int j = 0; j < R4; ++j) {
+      const uint32_t c = lane + 32 * j;
+      nx[j] = c < n4 ? xr[c] : zero;
+      nm[j] = (mr != nullptr && c < n4) ? __ldg(mr + c) : zero;
+    }
+  };
+  if (warp < rows) fetch(warp);
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    float4* yr = reinterpret_cast<float4*>(y + r * cols);
+    float v[R4][4];
+#pragma unroll
+    for (int j = 0; j < R4; ++j) {
+      const float q[4] = {nx[j].x, nx[j].y, nx[j].z, nx[j].w};
+      const float mk[4] = {nm[j].x, nm[j].y, nm[j].z, nm[j].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float t = q[k];
+        if (pg.has_scale) t = __fmul_rn(t, pg.scale);
+        if (pg.mask) t = __fadd_rn(t, mk[k]);
+        v[j][k] = lane + 32 * j < n4 ? t : -INFINITY;
+      }
+    }
+    if (r + nwarps < rows) fetch(r + nwarps);
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < R4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) m = max_nan(m, v[j][k]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < R4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        v[j][k] = exp2_approx(__fmul_rn(__fsub_rn(v[j][k], m), 1.4426950408889634f));
+        s = __fadd_rn(s, v[j][k]);
+      }
+    const float inv = __frcp_rn(warp_sum_f32(s));
+#pragma unroll
+    for (int j = 0; j < R4; ++j) {
+      const uint32_t c = lane + 32 * j;
+      if (c < n4)
+        yr[c] = make_float4(__fmul_rn(v[j][0], inv), __fmul_rn(v[j][1], inv),
+                            __fmul_rn(v[j][2], inv), __fmul_rn(v[j][3], inv));
+    }
+  }
+}
+
 // ---- layer normalisation over the last axis, as the converter leaves it in a graph:
 //   mean = Mean(x); var = Mean(SquaredDifference(x, mean)); rs = Rsqrt(var + eps);
 //   y = ((x - mean) * rs) * gamma + beta
@@ -433,7 +512,16 @@ static int softmax_impl(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t rows, uint64_
     if (fast) softmax_kernel<R, true><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32, pg); \
     else softmax_kernel<R, false><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32, pg);     \
   } while (0)
-  if (cols <= 32) SOFTMAX(1);
+  const bool vec = fast && (cols & 3) == 0 && cols > 64 && cols <= 1024 &&
+                   (((uintptr_t)xp | (uintptr_t)yp | (uintptr_t)pg.mask) & 15) == 0;
+#define SOFTMAX_VEC(R4) \
+  softmax_vec_kernel<R4><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, rows, c32, pg)
+  if (vec && cols <= 128) SOFTMAX_VEC(1);
+  else if (vec && cols <= 256) SOFTMAX_VEC(2);
+  else if (vec && cols <= 512) SOFTMAX_VEC(4);
+  else if (vec) SOFTMAX_VEC(8);
+#undef SOFTMAX_VEC
+  else if (cols <= 32) SOFTMAX(1);
   else if (cols <= 64) SOFTMAX(2);
   else if (cols <= 128) SOFTMAX(4);
   else if (cols <= 256) SOFTMAX(8);
