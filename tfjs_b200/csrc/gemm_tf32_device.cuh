@@ -50,6 +50,10 @@ struct Tf32Args {
 // K-major B operand, tm_c: 32 x 32 store boxes.  g.tiles_m counts 256-row tiles.
 int launch_gemm_tf32_pair(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                           const CUtensorMap& tm_c, Tf32Args& g, bool im2col);
+// 256 x 384 tiles (two N = 192 MMAs per K slice, one accumulator stage): tm_b holds 96-row
+// boxes.  For outputs whose 256 x 384 tiles all run at once.
+int launch_gemm_tf32_pair_wide(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a,
+                               const CUtensorMap& tm_b, const CUtensorMap& tm_c, Tf32Args& g);
 // The same for a group of products that share A (GemmGroup): the tile index runs over the
 // members' column tiles side by side.
 struct PairGroupMaps {
@@ -179,8 +183,9 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, 
       for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], __shfl_sync(0xffffffffu, bj, j));
     }
   }
-  if (ACT == TFJS_CUDA_ACT_LINEAR) return;
-  if (ACT == TFJS_CUDA_ACT_GELU_ERF) {
+  if constexpr (ACT == TFJS_CUDA_ACT_LINEAR) {
+    return;
+  } else if constexpr (ACT == TFJS_CUDA_ACT_GELU_ERF) {
     // the tensor-core kernels run in the TF32 math mode only, where erf is the fp32 form
     // (the same device function as the separate Erf kernel and the chain kernels)
     // two columns at a time (packed fp32 arithmetic): an epilogue warp has one issue slot
@@ -198,8 +203,7 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, 
       unpack_f32x2(mul_f32x2(mul_f32x2(x, half2), add_f32x2(erf_f32x2(a), one2)), v[j],
                    v[j + 1]);
     }
-    return;
-  }
+  } else {
 #pragma unroll
   for (int j = 0; j < 32; ++j) {
     const float t = v[j];
@@ -220,6 +224,7 @@ __device__ __forceinline__ void chunk_math(float* v, const Tf32Args& g, int n0, 
     } else if (ACT == TFJS_CUDA_ACT_ELU) {
       v[j] = elu_f32(t);
     }
+  }
   }
 }
 

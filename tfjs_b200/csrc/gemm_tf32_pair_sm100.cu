@@ -30,18 +30,23 @@
 
 namespace {
 
-constexpr int kPairBStageBytes = 128 * BK * 4;   // this CTA's half of the 256-row B tile
-constexpr int kPairStageBytes = A_STAGE_BYTES + kPairBStageBytes;
-constexpr int kPairAcc = 2;                       // accumulator stages of 256 columns
+// BN = 256: two accumulator stages of 256 columns, so the epilogue of one tile runs under the
+// main loop of the next.  BN = 384 (256 x 384 tiles, two N = 192 MMAs per K slice, one
+// accumulator of 384 columns): for outputs whose tiles all run at once, where the wider tile
+// turns 1.3 waves of 256 x 256 tiles into one wave and pulls 20% less from L2 per flop.
 // EW epilogue warps (8 or 16: two or four per TMEM lane quarter), one 4 KB staging tile
-// each; the pipeline gets the stages that fit beside them (6 or 5)
-template <int EW>
+// each; the pipeline gets the stages that fit beside them (6 or 5; 4 at BN = 384)
+template <int EW, int BN>
 struct PairCfg {
+  static constexpr int B_STAGE_BYTES = (BN / 2) * BK * 4;   // this CTA's half of the B tile
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int ACC = BN == 256 ? 2 : 1;              // accumulator stages
   static constexpr int STAGES =
-      (kMaxSmemBytes - 1024 - kBarrierBytes - EW * 4096) / kPairStageBytes;
+      (kMaxSmemBytes - 1024 - kBarrierBytes - EW * 4096) / STAGE_BYTES;
   static constexpr int THREADS = 64 + EW * 32;
-  static constexpr int SMEM_BYTES = 1024 + STAGES * kPairStageBytes + EW * 4096 + kBarrierBytes;
-  static_assert(STAGES >= 4 && 2 * STAGES + 2 * kPairAcc + 1 <= kBarrierBytes / 8, "pair kernel layout");
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EW * 4096 + kBarrierBytes;
+  static_assert(BN == 256 || BN == 384, "pair kernel tile width");
+  static_assert(STAGES >= 4 && 2 * STAGES + 2 * ACC + 1 <= kBarrierBytes / 8, "pair kernel layout");
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -103,17 +108,20 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
 // A_MODE 0: A tiles by tiled TMA ([batch][M][K] map, 128-row boxes); 2: TMA im2col over NHWC x.
 // GROUP: several products share A (PairGroupMaps); g.tiles_n counts the column tiles of all
 // members side by side and tiles_n_each those of one member.
-template <int A_MODE, int EW, int GROUP>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<EW>::THREADS), 1)
+template <int A_MODE, int EW, int GROUP, int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<EW, BN>::THREADS), 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                       const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_c,
                       const __grid_constant__ PairGroupMaps grp, const Tf32Args g,
                       const int tiles_n_each) {
-  constexpr int STAGES = PairCfg<EW>::STAGES;
-  constexpr int ACC = kPairAcc;
+  using Cfg = PairCfg<EW, BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int ACC = Cfg::ACC;
+  constexpr int kPairBStageBytes = Cfg::B_STAGE_BYTES;
+  constexpr int kPairStageBytes = Cfg::STAGE_BYTES;
   constexpr int EPI_STEP = (EW / 4) * 32;   // columns between the chunks one warp takes
-  constexpr int BN = 256;
+  constexpr int MMA_N = BN == 256 ? 256 : 192;   // BN = 384: two MMAs side by side
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_base = smem_base;
@@ -159,7 +167,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (warp == 1) {
     asm volatile(
         "tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
-        "r"((uint32_t)(ACC * BN))
+        "r"(512u)
         : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
@@ -189,7 +197,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           map_b = &grp.b[member];
         }
         const int m0 = mt * 256 + (int)rank * 128;
-        const int n0 = nt * BN + (int)rank * 128;
+        // this CTA's rows of the B tile: half of each MMA's N
+        const int n0 = nt * BN + (int)rank * (MMA_N / 2);
         int pix_w = 0, pix_h = 0, pix_n = 0;
         if (A_MODE == 2) {
           const int ow = m0 % g.conv.out_w;
@@ -218,6 +227,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           }
           tma_load_3d_pair(b_base + stage * kPairBStageBytes, map_b, fb, ks * BK, n0,
                            bz % g.batch_b);
+          if (BN == 384)
+            tma_load_3d_pair(b_base + stage * kPairBStageBytes + (MMA_N / 2) * BK * 4, map_b, fb,
+                             ks * BK, n0 + MMA_N, bz % g.batch_b);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -225,8 +237,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   } else if (warp == 1) {
     // ------------------------------------------- MMA issuer (leader CTA) --
     if (rank == 0 && lane == 0) {
-      // instruction descriptor: D = f32, A = B = tf32, both K-major, N = 256, M = 256
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+      // instruction descriptor: D = f32, A = B = tf32, both K-major, N = MMA_N, M = 256
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(MMA_N >> 3) << 17) |
                              ((uint32_t)(256 >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
@@ -251,9 +263,14 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           const uint32_t sa = a_base + stage * A_STAGE_BYTES;
           const uint32_t sb = b_base + stage * kPairBStageBytes;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
+          for (int k = 0; k < BK / UMMA_K; ++k) {
             tc_mma_tf32_pair(d_tmem, desc_k_major(sa + k * UMMA_K * 4),
                              desc_k_major(sb + k * UMMA_K * 4), idesc, (ks | k) != 0 ? 1u : 0u);
+            if (BN == 384)
+              tc_mma_tf32_pair(d_tmem + MMA_N, desc_k_major(sa + k * UMMA_K * 4),
+                               desc_k_major(sb + (MMA_N / 2) * BK * 4 + k * UMMA_K * 4), idesc,
+                               (ks | k) != 0 ? 1u : 0u);
+          }
           tc_commit_pair(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -270,8 +287,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     const uint32_t stage_buf = epi_base + (uint32_t)(warp - 2) * 4096u;
     const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
     const uint32_t sw = (uint32_t)(lane & 7);
-    const uint32_t leader_tempty[ACC] = {map_to_rank(tempty_bar(0), 0),
-                                         map_to_rank(tempty_bar(1), 0)};
+    uint32_t leader_tempty[ACC];
+#pragma unroll
+    for (int a = 0; a < ACC; ++a) leader_tempty[a] = map_to_rank(tempty_bar(a), 0);
     int it = 0;
     for (int tile = pair; tile < g.total_tiles; tile += npairs, ++it) {
       int nt = tile % g.tiles_n;
@@ -364,23 +382,23 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"((uint32_t)(ACC * BN))
+                 "r"(512u)
                  : "memory");
   }
 }
 
-template <int A_MODE, int EW, int GROUP>
+template <int A_MODE, int EW, int GROUP, int BN = 256>
 int launch_pair(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& tm_b,
                 const CUtensorMap& tm_c, const PairGroupMaps* maps, Tf32Args& g) {
-  auto kern = gemm_tf32_pair_kernel<A_MODE, EW, GROUP>;
-  using C = PairCfg<EW>;
+  auto kern = gemm_tf32_pair_kernel<A_MODE, EW, GROUP, BN>;
+  using C = PairCfg<EW, BN>;
   static bool configured[64] = {false};  // per device ordinal
   if (ctx->device >= 64 || !configured[ctx->device]) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        C::SMEM_BYTES));
     if (ctx->device < 64) configured[ctx->device] = true;
   }
-  const int tiles_n_each = (g.N + 255) / 256;
+  const int tiles_n_each = (g.N + BN - 1) / BN;
   g.tiles_n = tiles_n_each * (GROUP ? maps->count : 1);
   g.total_tiles = g.tiles_m * g.tiles_n * g.total_tiles;  // total_tiles held the batch
   const int pairs_max = ctx->sm_count / 2;
@@ -391,7 +409,7 @@ int launch_pair(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUtensorMap& 
                                                              tiles_n_each);
   static const std::string name =
       "gemm_tf32_pair_kernel<A_MODE=" + std::to_string(A_MODE) + ",EW=" + std::to_string(EW) +
-      ",GROUP=" + std::to_string(GROUP) + ">";
+      ",GROUP=" + std::to_string(GROUP) + (BN == 256 ? "" : ",BN=" + std::to_string(BN)) + ">";
   LAUNCH_CHECK(ctx, name.c_str());
   return TFJS_CUDA_OK;
 }
@@ -408,6 +426,11 @@ int launch_gemm_tf32_pair(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a, const CUt
   }
   if (im2col) return launch_pair<2, 8, 0>(ctx, tm_a, tm_b, tm_c, nullptr, g);
   return launch_pair<0, 8, 0>(ctx, tm_a, tm_b, tm_c, nullptr, g);
+}
+
+int launch_gemm_tf32_pair_wide(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a,
+                               const CUtensorMap& tm_b, const CUtensorMap& tm_c, Tf32Args& g) {
+  return launch_pair<0, 16, 0, 384>(ctx, tm_a, tm_b, tm_c, nullptr, g);
 }
 
 int launch_gemm_tf32_pair_group(tfjs_cuda_ctx* ctx, const CUtensorMap& tm_a,

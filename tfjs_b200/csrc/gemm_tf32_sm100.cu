@@ -1456,6 +1456,25 @@ int launch_gemm_tf32(tfjs_cuda_ctx* ctx, const GemmProblem& pr, const Tf32Operan
     g.tiles_m = (pr.M + 255) / 256;
     return launch_gemm_tf32_pair_group(ctx, tm_a, maps, g);
   }
+  // Between one and 1.5 waves of 256 x 256 pair tiles: 256 x 384 tiles run as a single wave
+  // ([8192, 3072] x [3072, 768] and [8192, 768] x [768, 768]: 96 tiles -> 64 on 74 pairs).
+  static int pair_wide = -1;
+  if (pair_wide < 0) pair_wide = getenv("TFJS_CUDA_NO_PAIR_WIDE") ? 0 : 1;
+  const long long wide_tiles = (long long)((pr.M + 255) / 256) * ((pr.N + 383) / 384) * pr.batch;
+  if (pair_wide && pair_k > 0 && op.k_steps >= pair_k && pair_shape && op.a_gather == 0 &&
+      pr.N > 256 && pair_tiles > ctx->sm_count / 2 && wide_tiles <= ctx->sm_count / 2) {
+    memset(&tm_a, 0, sizeof tm_a);
+    if (make_map(ctx, &tm_a, op.a, (uint64_t)pr.K, (uint64_t)pr.M, (uint64_t)pr.batch_a,
+                 (uint64_t)op.lda, (uint64_t)pr.M * op.lda, BM) == TFJS_CUDA_OK) {
+      const uint64_t kk = (uint64_t)op.k_steps * BK < (uint64_t)op.ldb
+                              ? (uint64_t)op.k_steps * BK : (uint64_t)op.ldb;
+      if ((rc = make_map(ctx, &tm_b, op.b, kk, (uint64_t)pr.N, (uint64_t)pr.batch_b,
+                         (uint64_t)op.ldb, (uint64_t)pr.N * op.ldb, 96u)))
+        return rc;
+      g.tiles_m = (pr.M + 255) / 256;
+      return launch_gemm_tf32_pair_wide(ctx, tm_a, tm_b, tm_c, g);
+    }
+  }
   if (pair_k > 0 && op.k_steps >= pair_k && pair_shape &&
       pair_tiles > 2ll * (ctx->sm_count / 2) &&
       !(bn == 256 && use_k_split(ctx, g.tiles_m * ((pr.N + 255) / 256) * pr.batch, op.k_steps))) {
