@@ -417,6 +417,25 @@ int tfjs_cuda_softmax_scaled_masked(tfjs_cuda_ctx* ctx, int32_t x_id, uint64_t r
                                     uint64_t cols, int32_t has_scale, float scale,
                                     int32_t mask_id, uint64_t rows_per_mask, int32_t out_id);
 
+/* ---- One attention layer as one launch: out = softmax(fl32(fl32(q k^T * scale) + mask)) v
+ * for q, k, v of shape [batch, heads, seq, head_dim] (the heads-split store of
+ * tfjs_cuda_fused_matmul_heads) and out stored [batch, seq, heads, head_dim] (heads merged).
+ * It stands for four kernels of the reference and the transposes around them: BatchMatMul
+ * with adj_y (tfjs-backend-cpu/src/kernels/BatchMatMul.ts:29-113), Multiply by a scalar
+ * (Multiply.ts), Add of the mask (Add.ts), Softmax (Softmax.ts:50-67), BatchMatMul, Transpose
+ * [0, 2, 1, 3]; the [batch, heads, seq, seq] scores and probabilities are never stored.
+ * has_scale = 0 skips the product, mask_id = 0 the sum.  The mask holds ceil(batch * heads /
+ * units_per_mask) rows of seq floats; head u = b * heads + h uses mask row u / units_per_mask
+ * (units_per_mask = heads for a [batch, 1, 1, seq] mask).  TF32 products with fp32
+ * accumulation and the fp32 softmax of the TF32 math mode; the probabilities are rounded to
+ * TF32 as the operand load of the separate product rounds them.  Only seq = 128 and
+ * head_dim = 64 in the TF32 math mode are taken: anything else returns
+ * TFJS_CUDA_UNSUPPORTED and launches nothing (the caller issues the separate kernels). */
+int tfjs_cuda_fused_attention(tfjs_cuda_ctx* ctx, int32_t q_id, int32_t k_id, int32_t v_id,
+                              int32_t mask_id, int32_t has_scale, float scale, int32_t batch,
+                              int32_t heads, int32_t seq, int32_t head_dim,
+                              int32_t units_per_mask, int32_t out_id);
+
 /* ---- Layer normalisation over the last axis of a [rows, cols] view, in the decomposed
  * form a converted graph holds: y = ((x - mean) * rsqrt(var + epsilon)) * gamma + beta with
  * mean = Mean(x), var = Mean(SquaredDifference(x, mean)).  One launch for the nine (ten with the residual Add) kernels

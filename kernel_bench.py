@@ -6,7 +6,8 @@ op front end with CUDA events on the backend's stream.
 cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072), ffng (ffn with
 the erf GELU as epilogue),
 mm_<m>_<k>_<n> (fused matMul + bias), qkv_<m>_<k>_<n> (three of them on one activation: one
-grouped launch),
+grouped launch), attn_<batch>_<heads>[_sep] (one attention layer, heads of 128 x 64: one launch, or
+the three separate ones),
 pw_<hw>_<cin>_<cout>_<batch> (1x1 conv), c3_<hw>_<cin>_<cout>_<batch>_<stride> (3x3
 conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<batch>_<stride>
 (3x3 depthwise), res_<hw>_<cin>_<cout>_<batch> (1x1 conv + bias, Add of a shortcut, Relu:
@@ -67,6 +68,15 @@ elif case=='ffng':   # the same product with the erf GELU as its epilogue
     a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
     bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
     f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'gelu_erf',None,0.2,[float(np.float32(1/np.sqrt(2))),0.5,1.0,0.0]); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
+elif case.startswith('attn_'):   # attn_<batch>_<heads>[_sep]: softmax(q k^T / 8 + mask) v, heads of 128 x 64
+    parts=case.split('_'); B,H=int(parts[1]),int(parts[2]); sep=len(parts)>3
+    q,k,v=[ops.tensor(r.standard_normal((B,H,128,64)).astype(np.float32)) for _ in range(3)]
+    mask=ops.tensor(np.zeros((B,1,1,128),np.float32))
+    def f():
+        if not sep: return ops.fused_attention(q,k,v,0.125,mask)
+        s=ops.mat_mul(q,k,False,True); p=ops.softmax_scaled_masked(s,0.125,mask); o=ops.mat_mul_heads(p,v,'merge',[B,128,H,64])
+        be.device_id(o.dataId); s.dispose(); p.dispose(); return o
+    fl=4*B*H*128*128*64; by=4*4*B*H*128*64
 elif case.startswith('qkv_'):   # qkv_<m>_<k>_<n>: three fused matMuls + bias on one activation (one grouped launch)
     _,m,k,n=case.split('_'); m,k,n=int(m),int(k),int(n)
     a0=ops.tensor(r.standard_normal((m,k)).astype(np.float32)/32); zero=ops.tensor(np.float32(0)); a=ops.add(a0,zero); be.device_id(a.dataId)

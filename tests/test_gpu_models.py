@@ -196,6 +196,8 @@ def test_bert_with_fused_layer_norms_matches_the_stored_graph(cuda_engine):
     for fuse in (True, False):
         gm = GraphModel(model_json, weights, cuda_engine, replay=False)
         gm.executor.fuse = fuse
+        # (the one-launch attention is the one rewrite that does not keep the bits)
+        gm.executor.fuse_skip = {"attention"} if fuse else set()
         ins = {k: cuda_engine.make_tensor(v, list(v.shape), "int32" if v.dtype == np.int32
                                           else "float32") for k, v in feeds.items()}
         before = be.numDataIds()
@@ -264,9 +266,12 @@ def test_bert_with_folded_head_transposes_matches_the_stored_graph(cuda_engine):
              "attention_mask": np.ones((2, 128), np.float32)}
     outs, launches = [], []
     be = cuda_engine.backend
-    for fuse in (True, False):
+    # every rewrite but the one-launch attention keeps the bits of the stored graph; the
+    # attention kernel forms the softmax's sum in another order
+    for fuse, skip in ((True, {"attention"}), (False, set()), (True, set())):
         gm = GraphModel(model_json, weights, cuda_engine, replay=False)
         gm.executor.fuse = fuse
+        gm.executor.fuse_skip = set(skip)
         ins = {k: cuda_engine.make_tensor(v, list(v.shape), "int32" if v.dtype == np.int32
                                           else "float32") for k, v in feeds.items()}
         before = be.numDataIds()
@@ -275,12 +280,14 @@ def test_bert_with_folded_head_transposes_matches_the_stored_graph(cuda_engine):
         assert gm.executor.fused_heads == (8 if fuse else 0)
         assert gm.executor.fused_softmaxes == (2 if fuse else 0)
         assert gm.executor.fused_gelus == (2 if fuse else 0)
+        assert gm.executor.fused_attentions == (2 if fuse and not skip else 0)
         y.dispose()
         assert be.numDataIds() == before
         for t in ins.values():
             t.dispose()
         gm.dispose()
     assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    assert np.max(np.abs(outs[2] - outs[1])) <= 1e-3 * np.max(np.abs(outs[1]))
 
 
 # ------------------------------------------------- plan rewrite: softmax of scores --

@@ -233,6 +233,41 @@ def test_scaled_masked_softmax_of_bert_is_one_node():
     assert n == 11
 
 
+# --------------------------------------------- plan rewrite: one node per attention --
+def test_attention_of_bert_becomes_one_node_per_layer():
+    G, nodes, consts = _bert_plan()
+    is_const, value = (lambda x: x in consts), (lambda x: consts[x].reshape(-1))
+    heads, k = G.fuse_attention_heads(nodes, is_const, value)
+    soft, j = G.fuse_softmax_inputs(heads, is_const, value)
+    new, n = G.fuse_attention(soft)
+    assert (k, j, n) == (48, 12, 12)
+    assert len(new) == len(soft) - 2 * n         # scores and probabilities are gone
+    by_name = {x.name: x for x in new}
+    for x in new:
+        assert x.op not in ("BatchMatMul", "BatchMatMulV2", "Softmax", "_SoftmaxScaledMasked")
+        if x.op != "_FusedAttention":
+            continue
+        assert len(x.inputs) == 4                # q, k, v, mask
+        for i in x.inputs[:3]:                   # the three heads-split projections
+            assert by_name[G.parse_node_name(i)[0]].op == "_MatMulHeads"
+        assert abs(G.attr_number(x.attrs, "_scale") - 0.125) < 1e-12
+        assert G.attr_number_list(x.attrs, "_dims") == [256, 768]
+    pos = {x.name: i for i, x in enumerate(new)}
+    for x in new:
+        for i in x.inputs:
+            assert pos[G.parse_node_name(i)[0]] < pos[x.name]
+    # scores that something else reads stay
+    sc = next(x for x in soft if x.op in ("BatchMatMul", "BatchMatMulV2"))
+    tap = G.Node({"name": "tap", "op": "Identity", "input": [sc.name]})
+    _, n = G.fuse_attention(soft + [tap])
+    assert n == 11
+    _, n = G.fuse_attention(soft, protected=[sc.name])
+    assert n == 11
+    # without the softmax rewrite the Mul / AddV2 sit between the product and the softmax
+    _, n = G.fuse_attention(heads)
+    assert n == 0
+
+
 def test_softmax_mask_rows():
     from tfjs_b200.kernels.reduce import softmax_mask_rows as f
     assert f([64, 12, 128, 128], [64, 1, 1, 128]) == 12 * 128

@@ -143,9 +143,10 @@ def test_graph_ops_and_pending_classes_have_their_python_twins():
     rewrites = ts["src/graph_rewrites.ts"]
     for py, tsname in (("fuse_layer_norms", "fuseLayerNorms"), ("fuse_attention_heads", "fuseAttentionHeads"),
                        ("fuse_softmax_inputs", "fuseSoftmaxInputs"),
+                       ("fuse_attention", "fuseAttention"),
                        ("hoist_shared_operand_matmuls", "hoistSharedOperandMatMuls")):
         assert hasattr(graph_model, py) and "export function %s" % tsname in rewrites
-    for op in ("_FusedLayerNorm", "_MatMulHeads", "_SoftmaxScaledMasked"):
+    for op in ("_FusedLayerNorm", "_MatMulHeads", "_SoftmaxScaledMasked", "_FusedAttention"):
         assert "registerOp('%s'" % op in rewrites
         assert 'op == "%s"' % op in open(os.path.join(ROOT, "tfjs_b200", "graph_model.py")).read()
     replay = ts["src/graph_model_cuda.ts"]

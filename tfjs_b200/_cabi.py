@@ -129,6 +129,9 @@ SIGNATURES = {
     "tfjs_cuda_softmax": (c_int, [_CTX, c_int32, c_uint64, c_uint64, c_int32]),
     "tfjs_cuda_softmax_scaled_masked": (c_int, [_CTX, c_int32, c_uint64, c_uint64, c_int32, c_float,
                                                 c_int32, c_uint64, c_int32]),
+    "tfjs_cuda_fused_attention": (c_int, [_CTX, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                          c_float, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                          c_int32]),
     "tfjs_cuda_layer_norm": (c_int, [_CTX, c_int32, c_int32, c_int32, c_int32, c_uint64, c_uint64,
                                      c_float, c_int32]),
     "tfjs_cuda_reduce": (c_int, [_CTX, c_int32, c_int32, c_uint64, c_uint64,

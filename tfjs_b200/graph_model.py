@@ -269,6 +269,8 @@ def execute_op(node, inp):
         return _exec_softmax_fused(node, inp)
     if op == "_FusedMatMulGelu":
         return _exec_matmul_gelu(node, inp)
+    if op == "_FusedAttention":
+        return _exec_fused_attention(node, inp)
     if op in ("FusedBatchNorm", "FusedBatchNormV2", "FusedBatchNormV3"):
         return ops.batch_norm(inp[0], inp[3], inp[4], inp[2], inp[1],
                               attr_number(node.attrs, "epsilon", 0.001))
@@ -755,6 +757,97 @@ def fuse_attention_heads(ordered, is_const, const_value, protected=()):
     return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
 
 
+_ATTENTION_REFUSED = set()   # operand shapes the library has declined once
+
+
+def _exec_fused_attention(node, inp):
+    """softmax(q k^T * scale + mask) v stored with the heads merged, as one launch; the
+    batched product, the scaled, masked softmax and the heads-merging product one after the
+    other when the library declines the shape."""
+    from ._cabi import CudaError, UNSUPPORTED
+    q, k, v = inp[0], inp[1], inp[2]
+    mask = inp[3] if len(inp) > 3 else None
+    scale = attr_number(node.attrs, "_scale")
+    dims = attr_number_list(node.attrs, "_dims")
+    sig = (tuple(q.shape), tuple(k.shape), tuple(v.shape),
+           tuple(mask.shape) if mask is not None else None)
+    if sig not in _ATTENTION_REFUSED:
+        try:
+            y = ops.fused_attention(q, k, v, scale, mask)
+            try:
+                return ops.reshape(y, dims)
+            finally:
+                y.dispose()
+        except CudaError as e:
+            if e.code != UNSUPPORTED:
+                raise
+            _ATTENTION_REFUSED.add(sig)
+    scores = ops.mat_mul(q, k, False, True)
+    try:
+        attrs = {} if scale is None else {"_scale": {"f": scale}}
+        sm = Node({"name": node.name, "op": "_SoftmaxScaledMasked", "input": [], "attr": attrs})
+        probs = _exec_softmax_fused(sm, [scores] if mask is None else [scores, mask])
+    finally:
+        scores.dispose()
+    try:
+        enc = lambda t: {"s": base64.b64encode(t.encode()).decode()}
+        merge = Node({"name": node.name, "op": "_MatMulHeads", "input": [],
+                      "attr": {"_layout": enc("merge"), "_op": enc("BatchMatMulV2"),
+                               "_dims": node.attrs["_dims"]}})
+        return _exec_matmul_heads(merge, [probs, v])
+    finally:
+        probs.dispose()
+
+
+def fuse_attention(ordered, protected=()):
+    """Plan rewrite: the heads-merging product of softmax(scores) and v, with scores =
+    batchMatMul(q, k, adj_y) (scaled and masked on the way into the softmax or not), becomes
+    one `_FusedAttention(q, k, v[, mask]; scale)` node named like the merge, when the scores
+    and the probabilities have no other consumer and are not in `protected`.  Runs after
+    fuse_attention_heads and fuse_softmax_inputs, whose nodes it matches."""
+    by_name = {n.name: n for n in ordered}
+    consumers = {}
+    for n in ordered:
+        for i in n.inputs:
+            consumers.setdefault(parse_node_name(i)[0], []).append(n.name)
+    protected = set(protected)
+
+    def node(inp, op):
+        name, idx = parse_node_name(inp)
+        n = by_name.get(name)
+        return n if n is not None and idx == 0 and n.op in op else None
+
+    def only(n, user):
+        return consumers.get(n.name, []) == [user.name] and n.name not in protected
+
+    removed, replaced = set(), {}
+    for last in ordered:
+        if last.op != "_MatMulHeads" or attr_string(last.attrs, "_layout") != "merge" or \
+                len(last.inputs) != 2:
+            continue
+        if not attr_string(last.attrs, "_op", keep_case=True).startswith("BatchMatMul") or \
+                attr_bool(last.attrs, "adj_x") or attr_bool(last.attrs, "adj_y"):
+            continue
+        sm = node(last.inputs[0], ("_SoftmaxScaledMasked", "Softmax"))
+        if sm is None or not only(sm, last) or not 1 <= len(sm.inputs) <= 2:
+            continue
+        sc = node(sm.inputs[0], ("BatchMatMul", "BatchMatMulV2"))
+        if sc is None or len(sc.inputs) != 2 or not only(sc, sm) or \
+                attr_bool(sc.attrs, "adj_x") or not attr_bool(sc.attrs, "adj_y"):
+            continue
+        attrs = {"_dims": last.attrs["_dims"]}
+        if sm.op == "_SoftmaxScaledMasked" and "_scale" in sm.attrs:
+            attrs["_scale"] = sm.attrs["_scale"]
+        removed.update((sc.name, sm.name))
+        replaced[last.name] = Node({"name": last.name, "op": "_FusedAttention",
+                                    "input": [sc.inputs[0], sc.inputs[1], last.inputs[1]] +
+                                             list(sm.inputs[1:]),
+                                    "attr": attrs})
+    if not replaced:
+        return list(ordered), 0
+    return [replaced.get(n.name, n) for n in ordered if n.name not in removed], len(replaced)
+
+
 def hoist_shared_operand_matmuls(ordered, is_const):
     """Plan rewrite (scheduling only): products whose first operand is the same tensor and
     whose other operands are constants run next to each other.  The backend launches the
@@ -818,6 +911,7 @@ class GraphExecutor(object):
         self.fused_heads = 0
         self.fused_softmaxes = 0
         self.fused_gelus = 0
+        self.fused_attentions = 0
         self.hoisted_matmuls = 0
         self.keep_intermediates = False
         self.intermediates = {}
@@ -892,6 +986,8 @@ class GraphExecutor(object):
                                                               protected=prot)
         if fuse and "softmax" not in self.fuse_skip:
             ordered, j = fuse_softmax_inputs(ordered, consts[0], consts[1], protected=prot)
+        if fuse and "attention" not in self.fuse_skip:
+            ordered, self.fused_attentions = fuse_attention(ordered, protected=prot)
         if fuse and "hoist" not in self.fuse_skip:
             ordered, self.hoisted_matmuls = hoist_shared_operand_matmuls(ordered, consts[0])
         if fuse:

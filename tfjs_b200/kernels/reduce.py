@@ -179,6 +179,37 @@ def _softmax_scaled_masked(args):
     return out
 
 
+def _fused_attention(args):
+    """softmax(q k^T * scale + mask) v for q, k, v of shape [B, H, S, D], stored [B, S, H, D]:
+    one launch for the two batched products, the scaled, masked softmax between them and
+    the transpose behind them (graph_model.fuse_attention).  Raises CudaError(UNSUPPORTED)
+    for shapes the library does not take; nothing has been launched then."""
+    backend, inp, at = args["backend"], args["inputs"], args["attrs"]
+    q, k, v, mask = inp["q"], inp["k"], inp["v"], inp.get("mask")
+    scale = at.get("scale")
+    if len(q.shape) != 4 or list(k.shape) != list(q.shape) or list(v.shape) != list(q.shape) \
+            or any(t.dtype != "float32" for t in (q, k, v)):
+        raise _cabi.CudaError(_cabi.UNSUPPORTED, "_FusedAttention: q, k, v of one 4-D shape")
+    B, H, S, D = [int(d) for d in q.shape]
+    upm = 1
+    if mask is not None:
+        rpm = softmax_mask_rows([B, H, S, S], mask.shape) if mask.dtype == "float32" else None
+        if rpm is None or rpm % S != 0:
+            raise _cabi.CudaError(_cabi.UNSUPPORTED,
+                                  "_FusedAttention: mask %s is not one row per head" % (mask.shape,))
+        upm = rpm // S
+    out = backend.make_output([B, S, H, D], "float32")
+    try:
+        backend.check(backend.lib.tfjs_cuda_fused_attention(
+            backend.ctx, dev(backend, q), dev(backend, k), dev(backend, v), dev(backend, mask),
+            int(scale is not None), float(np.float32(scale if scale is not None else 1.0)),
+            B, H, S, D, upm, dev(backend, out)))
+    except Exception:
+        backend.disposeData(out.dataId)
+        raise
+    return out
+
+
 def layer_norm_supported(x_shape, gamma_shape, beta_shape):
     """Shapes the one-launch layer normalisation takes: rows of a multiple of 4 up to 1024
     floats, gamma and beta one value per column."""
@@ -227,4 +258,5 @@ CONFIGS = [
     KernelConfig("Softmax", BACKEND, _softmax),
     KernelConfig("_FusedLayerNorm", BACKEND, _fused_layer_norm),
     KernelConfig("_SoftmaxScaledMasked", BACKEND, _softmax_scaled_masked),
+    KernelConfig("_FusedAttention", BACKEND, _fused_attention),
 ]

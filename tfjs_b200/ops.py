@@ -312,6 +312,14 @@ def softmax_scaled_masked(logits, scale=None, mask=None):
     return _run("_SoftmaxScaledMasked", {"logits": logits, "mask": mask}, {"scale": scale})
 
 
+def fused_attention(q, k, v, scale=None, mask=None):
+    """softmax(q k^T * scale + mask) v for q, k, v of shape [B, H, S, D], returned as
+    [B, S, H, D]: one kernel of the 'cuda' backend with no counterpart among the
+    reference's ops (the graph executor substitutes it for batchMatMul + mul + add + softmax
+    + batchMatMul + transpose); raises CudaError(UNSUPPORTED) for shapes it does not take."""
+    return _run("_FusedAttention", {"q": q, "k": k, "v": v, "mask": mask}, {"scale": scale})
+
+
 def fused_layer_norm(x, gamma, beta, epsilon, residual=None):
     """Layer normalisation over the last axis in the decomposed form of a converted graph,
     as one kernel of the 'cuda' backend (no counterpart among the reference's ops; the

@@ -257,6 +257,17 @@ napi_value SoftmaxScaledMasked(napi_env env, napi_callback_info info) {
   return check(env, a.ctx(0), tfjs_cuda_softmax_scaled_masked(a.ctx(0), a.i32(1), a.u64(2), a.u64(3), a.i32(4),
                                                               static_cast<float>(a.f64(5)), a.i32(6), a.u64(7), a.i32(8)));
 }
+napi_value FusedAttention(napi_env env, napi_callback_info info) {
+  Args a(env, info);  // ctx, qId, kId, vId, maskId (0: none), hasScale, scale, batch, heads, seq, headDim,
+                      // unitsPerMask, outId; false when the library does not take the shape
+  const int rc = tfjs_cuda_fused_attention(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.i32(4), a.i32(5),
+                                           static_cast<float>(a.f64(6)), a.i32(7), a.i32(8), a.i32(9),
+                                           a.i32(10), a.i32(11), a.i32(12));
+  napi_value r;
+  napi_get_boolean(env, rc == TFJS_CUDA_OK, &r);
+  if (rc != TFJS_CUDA_OK && rc != TFJS_CUDA_UNSUPPORTED) napi_throw_error(env, nullptr, tfjs_cuda_last_error(a.ctx(0)));
+  return r;
+}
 napi_value LayerNorm(napi_env env, napi_callback_info info) {
   Args a(env, info);  // ctx, xId, residualId (0: none), gammaId, betaId, rows, cols, epsilon, outId
   return check(env, a.ctx(0), tfjs_cuda_layer_norm(a.ctx(0), a.i32(1), a.i32(2), a.i32(3), a.i32(4), a.u64(5),
@@ -419,7 +430,7 @@ napi_value Init(napi_env env, napi_value exports) {
       {"fusedConv2dResidual", FusedConv2DResidual}, {"fusedDepthwiseProject", FusedDepthwiseProject},
       {"addActivation", AddActivation},
       {"fusedDepthwiseConv2d", FusedDepthwiseConv2D}, {"fusedMatMul", FusedMatMul}, {"fusedMatMulHeads", FusedMatMulHeads}, {"fusedMatMulGroup", FusedMatMulGroup},
-      {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm}, {"softmaxScaledMasked", SoftmaxScaledMasked},
+      {"pool2d", Pool2D}, {"binary", Binary}, {"unary", Unary}, {"softmax", Softmax}, {"layerNorm", LayerNorm}, {"softmaxScaledMasked", SoftmaxScaledMasked}, {"fusedAttention", FusedAttention},
       {"reduce", Reduce}, {"argMax", ArgMax}, {"transpose", Transpose}, {"gather", Gather},
       {"cast", Cast}, {"copyStrided", CopyStrided}, {"fill", Fill}, {"batchNorm", BatchNorm},
       {"dequantize", Dequantize}, {"dequantizeStatic", DequantizeStatic},

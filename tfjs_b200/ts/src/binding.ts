@@ -59,6 +59,11 @@ export interface CudaBinding {
   softmax(ctx: Ctx, x: number, rows: number, cols: number, out: number): void;
   softmaxScaledMasked(ctx: Ctx, x: number, rows: number, cols: number, hasScale: number,
                       scale: number, mask: number, rowsPerMask: number, out: number): void;
+  /** softmax(q k^T * scale + mask) v for [batch, heads, seq, headDim] operands, stored with
+   * the heads merged; false when the library does not take the shape (nothing launched). */
+  fusedAttention(ctx: Ctx, q: number, k: number, v: number, mask: number, hasScale: number,
+                 scale: number, batch: number, heads: number, seq: number, headDim: number,
+                 unitsPerMask: number, out: number): boolean;
   layerNorm(ctx: Ctx, x: number, residual: number, gamma: number, beta: number, rows: number,
             cols: number, epsilon: number, out: number): void;
   reduce(ctx: Ctx, op: number, x: number, outer: number, reduce: number, inner: number,

@@ -10,6 +10,7 @@
  *   fuseAttentionHeads  matMul + Reshape + Transpose([0,2,1,3]) and batchMatMul + Transpose +
  *                       Reshape -> _MatMulHeads
  *   fuseSoftmaxInputs   Softmax(AddV2(Mul(scores, c), mask)) -> _SoftmaxScaledMasked
+ *   fuseAttention       _MatMulHeads(merge)(softmax(batchMatMul(q, k, adj_y) ...), v) -> _FusedAttention
  *   hoistSharedOperandMatMuls  products on one operand run next to each other, so that the
  *                       backend launches them as a group
  *
@@ -20,7 +21,7 @@
  * through `loadGraphModelCuda` (graph_model_cuda.ts) instead of tf.loadGraphModel.
  *
  * Python twin (executed by the tests): fuse_layer_norms / fuse_attention_heads /
- * fuse_softmax_inputs and the _exec_* functions of tfjs_b200/graph_model.py.
+ * fuse_softmax_inputs / fuse_attention and the _exec_* functions of tfjs_b200/graph_model.py.
  */
 import * as tfc from '@tensorflow/tfjs-core';
 import {io, Tensor} from '@tensorflow/tfjs-core';
@@ -216,6 +217,39 @@ export function fuseSoftmaxInputs(nodes: NodeDef[], consts: Consts, prot: Set<st
 }
 
 /**
+ * The heads-merging product of softmax(scores) and v, with scores = batchMatMul(q, k, adj_y)
+ * (scaled and masked on the way into the softmax or not), becomes one
+ * _FusedAttention(q, k, v[, mask]; _scale) node named like the merge.  Runs after
+ * fuseAttentionHeads and fuseSoftmaxInputs, whose nodes it matches.
+ * Python twin: fuse_attention (tfjs_b200/graph_model.py).
+ */
+export function fuseAttention(nodes: NodeDef[], consts: Consts, prot: Set<string>): NodeDef[] {
+  const g = new Graph(nodes, consts, prot);
+  const str = (n: NodeDef, key: string) => Buffer.from(n.attr?.[key]?.s ?? '', 'base64').toString();
+  const flag = (n: NodeDef, key: string) => !!n.attr?.[key]?.b;
+  const removed = new Set<string>(), replaced = new Map<string, NodeDef>();
+  for (const last of nodes) {
+    if (last.op !== '_MatMulHeads' || str(last, '_layout') !== 'merge' || (last.input ?? []).length !== 2 ||
+        !str(last, '_op').startsWith('BatchMatMul') || flag(last, 'adj_x') || flag(last, 'adj_y')) {
+      continue;
+    }
+    const sm = g.node(last.input![0], ['_SoftmaxScaledMasked', 'Softmax']);
+    if (sm == null || !g.only(sm, [last]) || (sm.input ?? []).length < 1 || (sm.input ?? []).length > 2) continue;
+    const sc = g.node(sm.input![0], ['BatchMatMul', 'BatchMatMulV2']);
+    if (sc == null || (sc.input ?? []).length !== 2 || !g.only(sc, [sm]) || flag(sc, 'adj_x') || !flag(sc, 'adj_y')) {
+      continue;
+    }
+    const attr: {[k: string]: any} = {_dims: last.attr!['_dims']};
+    if (sm.op === '_SoftmaxScaledMasked' && sm.attr?.['_scale'] != null) attr['_scale'] = sm.attr['_scale'];
+    removed.add(sc.name);
+    removed.add(sm.name);
+    replaced.set(last.name, {name: last.name, op: '_FusedAttention',
+                             input: [sc.input![0], sc.input![1], last.input![1], ...sm.input!.slice(1)], attr});
+  }
+  return apply(nodes, removed, replaced);
+}
+
+/**
  * Scheduling only: products whose first operand is the same tensor and whose other operands
  * are constants are moved next to the first of them in the stored node list (with the
  * constants they read).  The backend launches the products pending on one operand as a
@@ -264,7 +298,7 @@ export function hoistSharedOperandMatMuls(nodes: NodeDef[]): NodeDef[] {
 
 /** The three rewrites over a loaded model's topology (in place on a copy of the artifacts).
  * TFJS_CUDA_NO_GRAPH_FUSION = 1 | all switches them off; a comma-separated list of
- * layernorm, heads, softmax switches single ones off. */
+ * layernorm, heads, softmax, attention, hoist switches single ones off. */
 export function rewriteArtifacts(artifacts: io.ModelArtifacts): io.ModelArtifacts {
   const off = process.env['TFJS_CUDA_NO_GRAPH_FUSION'] ?? '0';
   if (off === '1' || off === 'all') return artifacts;
@@ -278,6 +312,7 @@ export function rewriteArtifacts(artifacts: io.ModelArtifacts): io.ModelArtifact
   if (!skip.has('layernorm')) nodes = fuseLayerNorms(nodes, consts, prot);
   if (!skip.has('heads')) nodes = fuseAttentionHeads(nodes, consts, prot);
   if (!skip.has('softmax')) nodes = fuseSoftmaxInputs(nodes, consts, prot);
+  if (!skip.has('attention')) nodes = fuseAttention(nodes, consts, prot);
   if (!skip.has('hoist')) nodes = hoistSharedOperandMatMuls(nodes);
   topology.node = nodes;
   return {...artifacts, modelTopology: topology};
@@ -323,6 +358,26 @@ export function registerGraphOps(
     let y = scale != null ? tfc.mul(x, tfc.scalar(scale)) : x;
     if (mask != null) y = tfc.add(y, mask);
     return tfc.softmax(y);
+  }));
+
+  const refusedAttention = new Set<string>();   // operand shapes the library has declined once
+  registerOp('_FusedAttention', node => tfc.tidy(() => {
+    const scale = node.attrs['_scale'] as number|undefined;
+    const dims = node.attrs['_dims'] as number[];
+    const [q, k, v, mask] = node.inputs;
+    const sig = [q.shape, k.shape, v.shape, mask?.shape].join(';');
+    if (!refusedAttention.has(sig)) {
+      try {
+        return tfc.reshape(kernel('_FusedAttention', {q, k, v, mask}, {scale}), dims);
+      } catch (e) {
+        refusedAttention.add(sig);   // not 128 positions x 64 features, fp32 math mode: the stored ops
+      }
+    }
+    let s = tfc.matMul(q, k, false, true);
+    if (scale != null) s = tfc.mul(s, tfc.scalar(scale));
+    if (mask != null) s = tfc.add(s, mask);
+    const o = tfc.matMul(tfc.softmax(s), v);
+    return tfc.reshape(tfc.transpose(o, [0, 2, 1, 3]), dims);
   }));
 
   const refused = new Set<string>();   // (layout, operand shapes) the library has declined once

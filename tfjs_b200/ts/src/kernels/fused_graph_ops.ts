@@ -5,6 +5,7 @@
  *   _MatMulHeads          matMul whose result is stored through the permutation that splits
  *                         or merges attention heads
  *   _SoftmaxScaledMasked  softmax(x * scale + mask)
+ *   _FusedAttention       softmax(q k^T * scale + mask) v with the heads merged
  * Python twins: _fused_layer_norm / _softmax_scaled_masked in tfjs_b200/kernels/reduce.py,
  * matmul_heads in tfjs_b200/kernels/matmul.py, _pack in movement.py.
  */
@@ -71,6 +72,36 @@ export const fusedGraphOpConfigs: KernelConfig[] = [
     binding.softmaxScaledMasked(backend.ctx, backend.deviceId(x), util.sizeFromShape(x.shape) / cols, cols,
                                 scale != null ? 1 : 0, Math.fround(scale ?? 1), backend.deviceId(mask),
                                 rowsPerMask, backend.deviceId(out));
+    return out;
+  })},
+  {kernelName: '_FusedAttention', backendName: 'cuda', kernelFunc: asFunc(({inputs, attrs, backend}) => {
+    // softmax(q k^T * scale + mask) v for q, k, v of shape [B, H, S, D], stored [B, S, H, D]
+    const {q, k, v, mask} = inputs;
+    const scale = attrs['scale'] as number|undefined;
+    const same = (a: number[], b: number[]) => a.length === b.length && a.every((d, i) => d === b[i]);
+    if (q.shape.length !== 4 || !same(k.shape, q.shape) || !same(v.shape, q.shape) ||
+        [q, k, v].some(t => t.dtype !== 'float32')) {
+      throw new UnsupportedByLibrary('_FusedAttention: q, k, v of one 4-D shape');
+    }
+    const [B, H, S, D] = q.shape;
+    let unitsPerMask = 1;
+    if (mask != null) {
+      const rpm = mask.dtype === 'float32' ? softmaxMaskRows([B, H, S, S], mask.shape) : null;
+      if (rpm == null || rpm % S !== 0) {
+        throw new UnsupportedByLibrary(`_FusedAttention: mask ${mask.shape} is not one row per head`);
+      }
+      unitsPerMask = rpm / S;
+    }
+    const out = backend.makeOutput([B, S, H, D], 'float32');
+    let taken = false;
+    try {
+      taken = binding.fusedAttention(backend.ctx, backend.deviceId(q), backend.deviceId(k), backend.deviceId(v),
+                                     backend.deviceId(mask), scale != null ? 1 : 0, Math.fround(scale ?? 1),
+                                     B, H, S, D, unitsPerMask, backend.deviceId(out));
+    } finally {
+      if (!taken) backend.disposeData(out.dataId);
+    }
+    if (!taken) throw new UnsupportedByLibrary('_FusedAttention: shape not taken by the library');
     return out;
   })},
   {kernelName: '_MatMulHeads', backendName: 'cuda', kernelFunc: asFunc(({inputs, attrs, backend}) => {
