@@ -13,10 +13,11 @@
 //              K = 64) into tensor memory, and O = P V (M = 128, N = 64, K = 128) with P read
 //              from tensor memory as the A operand
 //   warps 2-9  two groups of four; a group takes every second unit: each thread owns one
-//              row of S (tcgen05.ld), forms x * scale + mask, the row maximum, e = 2^((x -
+//              row of S (tcgen05.ld), forms x * scale + mask (the mask row staged in shared
+//              memory by the group, fetched one unit ahead), the row maximum, e = 2^((x -
 //              max) log2 e), the sum and p = e * (1 / sum) in registers (the arithmetic of the
 //              stand-alone softmax kernel; the sum runs along the row instead of across
-//              lanes), rounds p to TF32 as the TMA load of the stand-alone product would, and
+//              lanes), rounds p to TF32 (nearest) as the TMA load of the stand-alone product would, and
 //              writes it over S (tcgen05.st); later it takes O out of tensor memory and
 //              stores it through a swizzled staging tile with bulk tensor stores
 // Every wait is bounded; a wait that gives up records where in the context's error word.
@@ -32,8 +33,9 @@ constexpr int kSlots = 2;
 constexpr int kGroupWarps = 4;
 constexpr int kAttnThreads = 64 + kSlots * kGroupWarps * 32;
 constexpr int kAttnBarriers = 7 * kSlots;
+constexpr int kMaskBytes = kSlots * kS * 4;   // one mask row per group
 constexpr int kAttnSmem = 1024 + kSlots * (kQKBytes + kVBytes) + kSlots * kGroupWarps * 4096 +
-                          kAttnBarriers * 8 + 16;
+                          kMaskBytes + kAttnBarriers * 8 + 16 + 8;
 static_assert(kAttnSmem <= kMaxSmemBytes, "attention kernel: shared memory");
 
 struct AttnArgs {
@@ -100,10 +102,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   auto qk_base = [&](int s) { return smem_base + (uint32_t)s * kQKBytes; };
   auto v_base = [&](int s) { return smem_base + kSlots * kQKBytes + (uint32_t)s * kVBytes; };
   const uint32_t epi_base = smem_base + kSlots * (kQKBytes + kVBytes);
-  const uint32_t bar_base = epi_base + kSlots * kGroupWarps * 4096u;
+  const uint32_t mask_base = epi_base + kSlots * kGroupWarps * 4096u;
+  const uint32_t bar_base = mask_base + kMaskBytes;
   auto bar = [&](int kind, int s) { return bar_base + 8u * (uint32_t)(kind * kSlots + s); };
   enum { QK_FULL = 0, QK_EMPTY, V_FULL, V_EMPTY, S_FULL, P_FULL, O_FULL };
   const uint32_t tmem_slot = bar_base + 8u * kAttnBarriers;
+  const uint32_t dead_word = tmem_slot + 4u;   // + 4 * group: that group gave up on a wait
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -124,6 +128,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(bar(P_FULL, s), kGroupWarps);
       mbar_init(bar(O_FULL, s), 1);
     }
+    for (int s = 0; s < kSlots; ++s)
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(dead_word + 4u * s), "r"(0u) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -231,12 +237,35 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t stage_buf = epi_base + (uint32_t)(warp - 2) * 4096u;
     const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
     const uint32_t sw = (uint32_t)(lane & 7);
+    // The unit's mask row goes through shared memory: every thread needs all 128 values,
+    // and 32 dependent global loads per thread cost more than the rest of the softmax.
+    // Thread t of the group fetches value t one unit ahead.
+    const int tg = (int)threadIdx.x - 64 - grp * (kGroupWarps * 32);
+    const uint32_t mask_buf = mask_base + (uint32_t)grp * (kS * 4);
+    auto mask_value = [&](int unit) {
+      return g.mask ? __ldg(g.mask + (size_t)(unit / g.units_per_mask) * kS + tg) : 0.0f;
+    };
+    float mask_next = grp < n_local ? mask_value(first + grp * step) : 0.0f;
     for (int i = grp; i < n_local; i += kSlots) {
       const int u = first + i * step;
       const uint32_t ph = (uint32_t)(i >> 1) & 1u;
+      // (first barrier: the group has finished reading the previous unit's row.  A warp
+      // whose wait ran out does not leave on its own, which would strand the others at
+      // this barrier: it marks the group and all four leave together here.)
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(kGroupWarps * 32) : "memory");
+      uint32_t dead;
+      asm volatile("ld.shared.u32 %0, [%1];" : "=r"(dead) : "r"(dead_word + 4u * grp) : "memory");
+      if (dead) break;
+      asm volatile("st.shared.f32 [%0], %1;" ::"r"(mask_buf + (uint32_t)tg * 4u), "f"(mask_next)
+                   : "memory");
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(kGroupWarps * 32) : "memory");
+      if (i + kSlots < n_local) mask_next = mask_value(first + (i + kSlots) * step);
       if (!mbar_wait(bar(S_FULL, grp), ph)) {
-        if (lane == 0) atomicExch(g.flag, 4);
-        break;
+        if (lane == 0) {
+          atomicExch(g.flag, 4);
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(dead_word + 4u * grp), "r"(1u) : "memory");
+        }
+        continue;
       }
       tc_fence_after();
       uint32_t raw[kS];
@@ -245,19 +274,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tc_ld32_nowait(s_tmem(grp) + lane_sel + (uint32_t)(c * 32), raw + c * 32);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       float v[kS];
-      const float4* mrow = g.mask ? reinterpret_cast<const float4*>(
-                                        g.mask + (size_t)(u / g.units_per_mask) * kS)
-                                  : nullptr;
+      const bool masked = g.mask != nullptr;
+      // (plain loads, so that the compiler may schedule them among the arithmetic)
+      const float4* mrow = reinterpret_cast<const float4*>(smem_raw + (mask_buf - smem_u32(smem_raw)));
+      __builtin_assume(__isShared(mrow));
 #pragma unroll
       for (int j = 0; j < kS / 4; ++j) {
-        float4 mk = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (mrow) mk = __ldg(mrow + j);
-        const float mv[4] = {mk.x, mk.y, mk.z, mk.w};
+        float mv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (masked) {
+          const float4 mk = mrow[j];
+          mv[0] = mk.x; mv[1] = mk.y; mv[2] = mk.z; mv[3] = mk.w;
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           float t = __uint_as_float(raw[4 * j + k]);
           if (g.has_scale) t = __fmul_rn(t, g.scale);
-          if (mrow) t = __fadd_rn(t, mv[k]);
+          if (masked) t = __fadd_rn(t, mv[k]);
           v[4 * j + k] = t;
         }
       }
@@ -272,9 +304,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         s4[j & 3] = __fadd_rn(s4[j & 3], v[j]);
       }
       const float inv = __frcp_rn(__fadd_rn(__fadd_rn(s4[0], s4[1]), __fadd_rn(s4[2], s4[3])));
+      // p = e * inv rounded to TF32 (11 significant bits) with three fp32 operations
+      // (Veltkamp's splitting by 2^13 + 1: the nearest 11-bit value; exact for p in [0, 1]
+      // and for NaN) - the conversion instruction shares the special-function unit with
+      // the exponentials, which already bound this phase
 #pragma unroll
-      for (int j = 0; j < kS; ++j)
-        asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(raw[j]) : "f"(__fmul_rn(v[j], inv)));
+      for (int j = 0; j < kS; ++j) {
+        const float p = __fmul_rn(v[j], inv);
+        const float c = __fmul_rn(p, 8193.0f);
+        raw[j] = __float_as_uint(__fsub_rn(c, __fsub_rn(c, p)));
+      }
 #pragma unroll
       for (int c = 0; c < kS / 32; ++c)
         tc_st32(s_tmem(grp) + lane_sel + (uint32_t)(c * 32), raw + c * 32);
@@ -285,8 +324,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
       // the unit's output: 128 x 64, this warp's 32 rows as two 32 x 32 boxes
       if (!mbar_wait(bar(O_FULL, grp), ph)) {
-        if (lane == 0) atomicExch(g.flag, 5);
-        break;
+        if (lane == 0) {
+          atomicExch(g.flag, 5);
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(dead_word + 4u * grp), "r"(1u) : "memory");
+        }
+        continue;
       }
       tc_fence_after();
       const int b = u / g.heads, h = u - b * g.heads;
