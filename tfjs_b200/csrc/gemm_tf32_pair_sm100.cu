@@ -34,21 +34,17 @@ namespace {
 // main loop of the next.  BN = 384 (256 x 384 tiles, two N = 192 MMAs per K slice, one
 // accumulator of 384 columns): for outputs whose tiles all run at once, where the wider tile
 // turns 1.3 waves of 256 x 256 tiles into one wave and pulls 20% less from L2 per flop.
-// EW epilogue warps (8 or 16: two or four per TMEM lane quarter) with two or one 4 KB
-// staging tiles each; the pipeline gets the stages that fit beside them (5; 4 at BN = 384)
+// EW epilogue warps (8 or 16: two or four per TMEM lane quarter), one 4 KB staging tile
+// each; the pipeline gets the stages that fit beside them (6 or 5; 4 at BN = 384)
 template <int EW, int BN>
 struct PairCfg {
   static constexpr int B_STAGE_BYTES = (BN / 2) * BK * 4;   // this CTA's half of the B tile
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int ACC = BN == 256 ? 2 : 1;              // accumulator stages
-  // staging tiles per epilogue warp: with two, a warp fills one while the TMA unit still
-  // reads the other
-  static constexpr int EPI_BUFS = EW == 8 ? 2 : 1;
   static constexpr int STAGES =
-      (kMaxSmemBytes - 1024 - kBarrierBytes - EW * EPI_BUFS * 4096) / STAGE_BYTES;
+      (kMaxSmemBytes - 1024 - kBarrierBytes - EW * 4096) / STAGE_BYTES;
   static constexpr int THREADS = 64 + EW * 32;
-  static constexpr int SMEM_BYTES =
-      1024 + STAGES * STAGE_BYTES + EW * EPI_BUFS * 4096 + kBarrierBytes;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EW * 4096 + kBarrierBytes;
   static_assert(BN == 256 || BN == 384, "pair kernel tile width");
   static_assert(STAGES >= 4 && 2 * STAGES + 2 * ACC + 1 <= kBarrierBytes / 8, "pair kernel layout");
 };
@@ -131,7 +127,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
   const uint32_t a_base = smem_base;
   const uint32_t b_base = smem_base + STAGES * A_STAGE_BYTES;
   const uint32_t epi_base = b_base + STAGES * kPairBStageBytes;
-  const uint32_t bar_base = epi_base + (uint32_t)(EW * Cfg::EPI_BUFS) * 4096u;
+  const uint32_t bar_base = epi_base + (uint32_t)EW * 4096u;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
@@ -288,8 +284,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
     // leaves as one bulk tensor store, clipped at the tensor's edge by the TMA unit.
     const int q = warp & 3;
     const int part = (warp - 2) >> 2;
-    const uint32_t stage_base = epi_base + (uint32_t)(warp - 2) * (Cfg::EPI_BUFS * 4096u);
-    uint32_t ebuf = 0;
+    const uint32_t stage_buf = epi_base + (uint32_t)(warp - 2) * 4096u;
+    const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
     const uint32_t sw = (uint32_t)(lane & 7);
     uint32_t leader_tempty[ACC];
 #pragma unroll
@@ -334,14 +330,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
         }
         chunk_math_dispatch(v, g, n0, bj, false, bias);
         if (c0 + EPI_STEP < BN) bj = chunk_bias(g, n0 + EPI_STEP, lane, bias);
-        // the bulk store that last used this staging tile must have finished reading it
-        const uint32_t stage_buf = stage_base + ebuf * 4096u;
-        const uint32_t my_row = stage_buf + (uint32_t)lane * 128u;
-        if (Cfg::EPI_BUFS == 2) ebuf ^= 1;
-        if (lane == 0) {
-          if (Cfg::EPI_BUFS == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        }
+        // the bulk store that last used the staging tile must have finished reading it
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 8; ++j)
