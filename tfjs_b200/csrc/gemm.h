@@ -63,6 +63,10 @@ struct PatchPlan {
   int bytes, pitch, ml, rows;  // per buffer; floats between rows; left margin; rows held
   int bufs;                    // buffers that fit (2 to 4)
 };
+// Direct fp32 kernel for a 3-channel image, 3 x 3 stride-2 filter, 32 output channels
+// (stem_conv.cu): whether it takes the problem, and its launch.
+bool stem_conv_supported(const GemmProblem& pr);
+int launch_stem_conv(tfjs_cuda_ctx* ctx, const GemmProblem& pr);
 bool tf32_patch_plan(const ConvGeo& cv, int M, int N, int sm_count, PatchPlan* plan);
 
 int launch_gemm_simt(tfjs_cuda_ctx* ctx, const GemmProblem& pr);

@@ -379,6 +379,18 @@ static int conv2d_impl(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d_params* p, int
   cv.s_h = p->stride_h; cv.s_w = p->stride_w; cv.d_h = p->dilation_h; cv.d_w = p->dilation_w;
   cv.pad_t = p->pad_top; cv.pad_l = p->pad_left;
 
+  if (ctx->math_mode == TFJS_CUDA_MATH_TF32 && K64 > 0 && stem_conv_supported(pr)) {
+    // 3-channel image, 3 x 3 stride 2, 32 output channels: 27 multiply-adds per output, too
+    // few to feed a tensor-core tile; a direct fp32 kernel (TFJS_CUDA_NO_DIRECT_STEM=1: the
+    // staged-row GEMM below)
+    static int off = -1;
+    if (off < 0) off = getenv("TFJS_CUDA_NO_DIRECT_STEM") ? 1 : 0;
+    if (!off) {
+      rc = launch_stem_conv(ctx, pr);
+      if (rc == TFJS_CUDA_OK) ctx_mark_written(ctx, out_id);
+      return rc;
+    }
+  }
   if (ctx->math_mode == TFJS_CUDA_MATH_TF32 && K64 > 0) {
     Tf32Operands op;
     const float* packed;
