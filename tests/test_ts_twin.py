@@ -56,7 +56,7 @@ def test_enum_tables_match_the_header():
     from tfjs_b200 import _cabi
     src = _read("src", "binding.ts")
     act = _ts_table(src, "ACTIVATION")
-    assert act == {k: v for k, v in _cabi.ACTIVATIONS.items() if k != "gelu_erf"}
+    assert act == _cabi.ACTIVATIONS
     assert _ts_table(src, "DTYPE") == _cabi.DTYPES
     assert _ts_table(src, "BINARY_OP") == _cabi.BINARY_OPS
     assert _ts_table(src, "UNARY_OP") == _cabi.UNARY_OPS
@@ -144,9 +144,11 @@ def test_graph_ops_and_pending_classes_have_their_python_twins():
     for py, tsname in (("fuse_layer_norms", "fuseLayerNorms"), ("fuse_attention_heads", "fuseAttentionHeads"),
                        ("fuse_softmax_inputs", "fuseSoftmaxInputs"),
                        ("fuse_attention", "fuseAttention"),
+                       ("fuse_gelu_into_matmul", "fuseGeluIntoMatMul"),
                        ("hoist_shared_operand_matmuls", "hoistSharedOperandMatMuls")):
         assert hasattr(graph_model, py) and "export function %s" % tsname in rewrites
-    for op in ("_FusedLayerNorm", "_MatMulHeads", "_SoftmaxScaledMasked", "_FusedAttention"):
+    for op in ("_FusedLayerNorm", "_MatMulHeads", "_SoftmaxScaledMasked", "_FusedAttention",
+               "_FusedMatMulGelu"):
         assert "registerOp('%s'" % op in rewrites
         assert 'op == "%s"' % op in open(os.path.join(ROOT, "tfjs_b200", "graph_model.py")).read()
     replay = ts["src/graph_model_cuda.ts"]

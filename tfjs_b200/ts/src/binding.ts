@@ -112,7 +112,7 @@ export const binding = addon as CudaBinding;
 
 /** Enum values of include/tfjs_cuda.h. */
 export const ACTIVATION: {[name: string]: number} =
-    {linear: 0, relu: 1, relu6: 2, prelu: 3, leakyrelu: 4, sigmoid: 5, elu: 6};
+    {linear: 0, relu: 1, relu6: 2, prelu: 3, leakyrelu: 4, sigmoid: 5, elu: 6, gelu_erf: 7};
 export const DTYPE: {[name: string]: number} = {float32: 0, int32: 1, bool: 2};
 export const BINARY_OP = {Add: 0, Sub: 1, Multiply: 2, RealDiv: 3, Maximum: 4, Minimum: 5, Pow: 6,
                           SquaredDifference: 7, Prelu: 8};

@@ -10,6 +10,7 @@
  *   fuseAttentionHeads  matMul + Reshape + Transpose([0,2,1,3]) and batchMatMul + Transpose +
  *                       Reshape -> _MatMulHeads
  *   fuseSoftmaxInputs   Softmax(AddV2(Mul(scores, c), mask)) -> _SoftmaxScaledMasked
+ *   fuseGeluIntoMatMul  _FusedMatMul + the five nodes of the erf GELU -> _FusedMatMulGelu
  *   fuseAttention       _MatMulHeads(merge)(softmax(batchMatMul(q, k, adj_y) ...), v) -> _FusedAttention
  *   hoistSharedOperandMatMuls  products on one operand run next to each other, so that the
  *                       backend launches them as a group
@@ -21,7 +22,8 @@
  * through `loadGraphModelCuda` (graph_model_cuda.ts) instead of tf.loadGraphModel.
  *
  * Python twin (executed by the tests): fuse_layer_norms / fuse_attention_heads /
- * fuse_softmax_inputs / fuse_attention and the _exec_* functions of tfjs_b200/graph_model.py.
+ * fuse_softmax_inputs / fuse_gelu_into_matmul / fuse_attention and the _exec_* functions of
+ * tfjs_b200/graph_model.py.
  */
 import * as tfc from '@tensorflow/tfjs-core';
 import {io, Tensor} from '@tensorflow/tfjs-core';
@@ -217,6 +219,59 @@ export function fuseSoftmaxInputs(nodes: NodeDef[], consts: Consts, prot: Set<st
 }
 
 /**
+ * h = _FusedMatMul(a, b, bias) (no activation) followed by the erf GELU a converted graph
+ * spells as Mul(Mul(h, half), AddV2(Erf(Mul(h, scale)), one)) (or Erf(RealDiv(h, scale))), with
+ * scalar constants and h consumed by those two products only, becomes that product with the
+ * GELU as its epilogue (`_FusedMatMulGelu`, named like the final Mul).  The epilogue performs
+ * the same fp32 operations on the same h, so the bits do not change.
+ * Python twin: fuse_gelu_into_matmul (tfjs_b200/graph_model.py).
+ */
+export function fuseGeluIntoMatMul(nodes: NodeDef[], consts: Consts, prot: Set<string>): NodeDef[] {
+  const g = new Graph(nodes, consts, prot);
+  /** [other input, constant] of a two-input node one of whose inputs is a scalar constant. */
+  const withConst = (n: NodeDef|null, commutative = true): [string, number]|null => {
+    const ins = n?.input ?? [];
+    if (n == null || ins.length !== 2) return null;
+    const pairs = commutative ? [[ins[0], ins[1]], [ins[1], ins[0]]] : [[ins[0], ins[1]]];
+    for (const [a, b] of pairs) {
+      const c = g.scalar(b);
+      if (c != null && g.scalar(a) == null) return [a, c];
+    }
+    return null;
+  };
+  const removed = new Set<string>(), replaced = new Map<string, NodeDef>();
+  for (const out of nodes) {
+    if (out.op !== 'Mul' || (out.input ?? []).length !== 2) continue;
+    for (const [mi, ai] of [[out.input![0], out.input![1]], [out.input![1], out.input![0]]]) {
+      const m2 = g.node(mi, ['Mul']), add = g.node(ai, ['Add', 'AddV2']);
+      const hm = withConst(m2), ea = withConst(add);
+      if (m2 == null || add == null || hm == null || ea == null) continue;
+      const erf = g.node(ea[0], ['Erf']);
+      if (erf == null) continue;
+      const inner = g.node(erf.input![0], ['Mul', 'RealDiv', 'Div']);
+      const hs = withConst(inner, inner != null && inner.op === 'Mul');
+      if (inner == null || hs == null || hs[0] !== hm[0]) continue;
+      const mm = g.node(hm[0], ['_FusedMatMul']);
+      if (mm == null || removed.has(mm.name)) continue;
+      const fused = ((mm.attr?.['fused_ops']?.list?.s ?? []) as string[])
+                        .map(x => Buffer.from(x, 'base64').toString().toLowerCase());
+      if (fused.join() !== 'biasadd' || Number(mm.attr?.['num_args']?.i ?? 0) !== 1) continue;
+      if (!g.only(mm, [m2, inner]) || !g.only(m2, [out]) || !g.only(add, [out]) || !g.only(erf, [add]) ||
+          !g.only(inner, [erf])) {
+        continue;
+      }
+      [mm, m2, add, erf, inner].forEach(n => removed.add(n.name));
+      replaced.set(out.name, {
+        name: out.name, op: '_FusedMatMulGelu', input: [...(mm.input ?? [])],
+        attr: {...(mm.attr ?? {}), _gelu: {list: {f: [hs[1], hm[1], ea[1], inner.op !== 'Mul' ? 1 : 0]}}}
+      });
+      break;
+    }
+  }
+  return apply(nodes, removed, replaced);
+}
+
+/**
  * The heads-merging product of softmax(scores) and v, with scores = batchMatMul(q, k, adj_y)
  * (scaled and masked on the way into the softmax or not), becomes one
  * _FusedAttention(q, k, v[, mask]; _scale) node named like the merge.  Runs after
@@ -298,7 +353,7 @@ export function hoistSharedOperandMatMuls(nodes: NodeDef[]): NodeDef[] {
 
 /** The three rewrites over a loaded model's topology (in place on a copy of the artifacts).
  * TFJS_CUDA_NO_GRAPH_FUSION = 1 | all switches them off; a comma-separated list of
- * layernorm, heads, softmax, attention, hoist switches single ones off. */
+ * layernorm, heads, gelu, softmax, attention, hoist switches single ones off. */
 export function rewriteArtifacts(artifacts: io.ModelArtifacts): io.ModelArtifacts {
   const off = process.env['TFJS_CUDA_NO_GRAPH_FUSION'] ?? '0';
   if (off === '1' || off === 'all') return artifacts;
@@ -311,6 +366,9 @@ export function rewriteArtifacts(artifacts: io.ModelArtifacts): io.ModelArtifact
   let nodes = topology.node;
   if (!skip.has('layernorm')) nodes = fuseLayerNorms(nodes, consts, prot);
   if (!skip.has('heads')) nodes = fuseAttentionHeads(nodes, consts, prot);
+  if (!skip.has('gelu') && !['1', 'true'].includes(process.env['TFJS_CUDA_NO_FUSE_GELU'] ?? '')) {
+    nodes = fuseGeluIntoMatMul(nodes, consts, prot);
+  }
   if (!skip.has('softmax')) nodes = fuseSoftmaxInputs(nodes, consts, prot);
   if (!skip.has('attention')) nodes = fuseAttention(nodes, consts, prot);
   if (!skip.has('hoist')) nodes = hoistSharedOperandMatMuls(nodes);
@@ -358,6 +416,25 @@ export function registerGraphOps(
     let y = scale != null ? tfc.mul(x, tfc.scalar(scale)) : x;
     if (mask != null) y = tfc.add(y, mask);
     return tfc.softmax(y);
+  }));
+
+  registerOp('_FusedMatMulGelu', node => tfc.tidy(() => {
+    // _FusedMatMul(a, b, bias) whose epilogue is the erf GELU the five following nodes spelled out
+    const [a, b, bias] = node.inputs;
+    const [scale, half, one, divide] = node.attrs['_gelu'] as number[];
+    const ta = !!node.attrs['transpose_a'], tb = !!node.attrs['transpose_b'];
+    if (bias != null) {
+      try {
+        return kernel('_FusedMatMul', {a, b, bias},
+                      {transposeA: ta, transposeB: tb, activation: 'gelu_erf',
+                       geluParams: [scale, half, one, divide !== 0]});
+      } catch (e) {
+        // the fp32 math mode, a bias that does not fuse: the stored ops
+      }
+    }
+    const h = tfc.fused.matMul({a, b, transposeA: ta, transposeB: tb, bias});
+    const inner = divide !== 0 ? tfc.div(h, tfc.scalar(scale)) : tfc.mul(h, tfc.scalar(scale));
+    return tfc.mul(tfc.mul(h, tfc.scalar(half)), tfc.add(tfc.erf(inner), tfc.scalar(one)));
   }));
 
   const refusedAttention = new Set<string>();   // operand shapes the library has declined once

@@ -39,7 +39,8 @@ export function deferMatMul(
 
 function matMulImpl(
     backend: CudaBackend, a: TensorInfo, b: TensorInfo, transposeA: boolean, transposeB: boolean,
-    bias?: TensorInfo, prelu?: TensorInfo, activation = 'linear', alpha = 0.2): TensorInfo {
+    bias?: TensorInfo, prelu?: TensorInfo, activation = 'linear', alpha = 0.2,
+    gelu?: [number, number, number, boolean]): TensorInfo {
   const ar = a.shape.length, br = b.shape.length;
   const innerA = transposeA ? a.shape[ar - 2] : a.shape[ar - 1];
   const innerB = transposeB ? b.shape[br - 1] : b.shape[br - 2];
@@ -56,7 +57,11 @@ function matMulImpl(
   const preluLen = activation === 'prelu' ? perChannelLen(prelu, outerB) : 0;
   const fuseBias = biasLen != null;
   const fuseAct = fuseBias && (activation !== 'prelu' || preluLen != null);
-  const deferred = deferMatMul(backend, a, b, bias, activation, alpha, transposeA, transposeB,
+  if (activation === 'gelu_erf' && !(fuseAct && gelu != null)) {
+    // only exists as a fused epilogue (graph_rewrites.fuseGeluIntoMatMul)
+    throw new Error('matMul: gelu_erf needs a fusable bias');
+  }
+  const deferred = activation === 'gelu_erf' ? null : deferMatMul(backend, a, b, bias, activation, alpha, transposeA, transposeB,
                                batchA, batchB, outerA, outerB, innerA, fuseBias && fuseAct ? biasLen : null,
                                null, outShape);
   if (deferred != null) return deferred;
@@ -66,7 +71,7 @@ function matMulImpl(
         backend.ctx,
         packMatMulParams(batchA, batchB, outerA, outerB, innerA, transposeA, transposeB,
                          ACTIVATION[fuseAct ? activation : 'linear'], fuseBias ? biasLen : 0,
-                         fuseAct ? (preluLen ?? 0) : 0, alpha),
+                         fuseAct ? (preluLen ?? 0) : 0, alpha, activation === 'gelu_erf' ? gelu : undefined),
         backend.deviceId(a), backend.deviceId(b), fuseBias ? backend.deviceId(bias) : 0,
         fuseAct && activation === 'prelu' ? backend.deviceId(prelu) : 0, backend.deviceId(out));
   }
@@ -90,7 +95,8 @@ export const matMulConfigs: KernelConfig[] = [
    kernelFunc: (({inputs, attrs, backend}: Args) => matMulImpl(
        backend, inputs['a'], inputs['b'], !!attrs['transposeA'], !!attrs['transposeB'], inputs['bias'],
        inputs['preluActivationWeights'], (attrs['activation'] as string) ?? 'linear',
-       (attrs['leakyreluAlpha'] as number) ?? 0.2)) as unknown as KernelFunc},
+       (attrs['leakyreluAlpha'] as number) ?? 0.2,
+       attrs['geluParams'] as [number, number, number, boolean]|undefined)) as unknown as KernelFunc},
   {kernelName: BatchMatMul, backendName: 'cuda',
    kernelFunc: (({inputs, attrs, backend}: Args) => matMulImpl(
        backend, inputs['a'], inputs['b'], !!attrs['transposeA'], !!attrs['transposeB'])) as unknown as KernelFunc},
