@@ -143,13 +143,30 @@ def test_no_data_id_leak_across_executes(cuda_engine):
 
 
 # ------------------------------------------------- plan rewrite: layer normalisation --
+@pytest.mark.parametrize("mode", ["fp32", "tf32"])
 @pytest.mark.parametrize("residual", [None, "same", "broadcast"])
 @pytest.mark.parametrize("shape", [(64, 128, 768), (5, 7, 100), (3, 1024), (9, 4), (2, 3, 6),
                                    (4, 2048)])
-def test_fused_layer_norm_has_the_bits_of_the_separate_kernels(cuda_engine, shape, residual):
+def test_fused_layer_norm_has_the_bits_of_the_separate_kernels(cuda_engine, shape, residual, mode):
     """One launch against the nine kernels it replaces; shapes the kernel does not take
-    (a row that is not a multiple of 4, or beyond 1024) run the separate kernels."""
+    (a row that is not a multiple of 4, or beyond 1024) run the separate kernels.  fp32 math
+    mode: the same double-precision sums in the same order, bit for bit.  TF32 math mode (the
+    default): the one-launch kernel forms its two sums in fp32, within a few units in the
+    last place of the separate kernels."""
     from tfjs_b200 import graph_model, ops
+    cuda_engine.backend.set_math_mode(mode)
+    try:
+        got, ref = _layer_norm_both_ways(graph_model, ops, shape, residual)
+    finally:
+        cuda_engine.backend.set_math_mode("tf32")
+    assert got.shape == ref.shape
+    if mode == "fp32":
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    else:
+        assert np.max(np.abs(got - ref)) <= 4e-6 * np.max(np.abs(ref))
+
+
+def _layer_norm_both_ways(graph_model, ops, shape, residual):
     r = np.random.default_rng(sum(shape))
     x = ops.tensor((r.standard_normal(shape) * 3 + 0.5).astype(np.float32))
     extra = []
@@ -182,11 +199,26 @@ def test_fused_layer_norm_has_the_bits_of_the_separate_kernels(cuda_engine, shap
     ref = ref_t.arraySync()
     for t in [got_t, mean, sq, var, e, ve, rs, sub, norm, ng, ref_t, x, gamma, beta] + extra:
         t.dispose()
-    assert got.shape == ref.shape
-    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    return got, ref
 
 
-def test_bert_with_fused_layer_norms_matches_the_stored_graph(cuda_engine):
+@pytest.mark.parametrize("mode", ["fp32", "tf32"])
+def test_bert_with_fused_layer_norms_matches_the_stored_graph(cuda_engine, mode):
+    """fp32 math mode: every rewrite keeps the bits of the stored graph (the attention kernel
+    declines that mode).  TF32 math mode: the one-launch layer normalisation sums in fp32 and
+    the attention kernel sums its softmax in another order: a tolerance."""
+    cuda_engine.backend.set_math_mode(mode)
+    try:
+        outs = _bert_fused_and_stored(cuda_engine)
+    finally:
+        cuda_engine.backend.set_math_mode("tf32")
+    if mode == "fp32":
+        assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    else:
+        assert np.max(np.abs(outs[0] - outs[1])) <= 1e-3 * np.max(np.abs(outs[1]))
+
+
+def _bert_fused_and_stored(cuda_engine):
     model_json, weights = model_zoo.bert_encoder(2, layers=2)
     r = np.random.default_rng(3)
     feeds = {"input_ids": r.integers(0, 30522, (2, 128)).astype(np.int32),
@@ -196,8 +228,6 @@ def test_bert_with_fused_layer_norms_matches_the_stored_graph(cuda_engine):
     for fuse in (True, False):
         gm = GraphModel(model_json, weights, cuda_engine, replay=False)
         gm.executor.fuse = fuse
-        # (the one-launch attention is the one rewrite that does not keep the bits)
-        gm.executor.fuse_skip = {"attention"} if fuse else set()
         ins = {k: cuda_engine.make_tensor(v, list(v.shape), "int32" if v.dtype == np.int32
                                           else "float32") for k, v in feeds.items()}
         before = be.numDataIds()
@@ -209,7 +239,7 @@ def test_bert_with_fused_layer_norms_matches_the_stored_graph(cuda_engine):
         for t in ins.values():
             t.dispose()
         gm.dispose()
-    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    return outs
 
 
 # ---------------------------------------------------- plan rewrite: attention heads --
@@ -266,9 +296,10 @@ def test_bert_with_folded_head_transposes_matches_the_stored_graph(cuda_engine):
              "attention_mask": np.ones((2, 128), np.float32)}
     outs, launches = [], []
     be = cuda_engine.backend
-    # every rewrite but the one-launch attention keeps the bits of the stored graph; the
-    # attention kernel forms the softmax's sum in another order
-    for fuse, skip in ((True, {"attention"}), (False, set()), (True, set())):
+    # every rewrite but two keeps the bits of the stored graph in the default math mode: the
+    # attention kernel forms the softmax's sum in another order, the one-launch layer
+    # normalisation its two sums in fp32
+    for fuse, skip in ((True, {"attention", "layernorm"}), (False, set()), (True, set())):
         gm = GraphModel(model_json, weights, cuda_engine, replay=False)
         gm.executor.fuse = fuse
         gm.executor.fuse_skip = set(skip)

@@ -256,7 +256,12 @@ softmax_vec_kernel(const float* __restrict__ x, float* __restrict__ y, uint64_t 
 // NV = 16-byte pieces per lane (rows up to 128 * NV floats).  With `res` the normalised
 // tensor is Add(x, res) (the residual connection in front of the normalisation), formed
 // in registers.
-template <int NV>
+// FAST (the TF32 math mode, whose contract is a tolerance): the two sums in fp32 - mean =
+// sum(x) * (1 / n), var = sum((x - mean)^2) * (1 / n) with fused multiply-adds - and the
+// reciprocal square root in fp32; the normalisation itself keeps the reference's four
+// roundings.  About a quarter of the instructions: the double-precision form is bound by
+// its conversions, IEEE divisions and fp64 adds, this one by HBM.
+template <int NV, bool FAST>
 __global__ void layer_norm_rows_kernel(const float* __restrict__ x,
                                        const float* __restrict__ res,
                                        const float* __restrict__ gamma,
@@ -283,27 +288,50 @@ __global__ void layer_norm_rows_kernel(const float* __restrict__ x,
         v[u][2] = __fadd_rn(v[u][2], t.z); v[u][3] = __fadd_rn(v[u][3], t.w);
       }
     }
-    double acc = 0.0;
+    float mean, rs;
+    if (FAST) {
+      const float rn = __frcp_rn(nf);
+      float s = 0.0f;
 #pragma unroll
-    for (int u = 0; u < NV; ++u) {
-      if (u * 32 + lane >= n4) continue;
+      for (int u = 0; u < NV; ++u)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) acc += (double)__fdiv_rn(v[u][k], nf);
-    }
-    const float mean = (float)warp_sum(acc);
-    acc = 0.0;
+        for (int k = 0; k < 4; ++k) s = __fadd_rn(s, v[u][k]);     // pieces beyond the row hold 0
+      mean = __fmul_rn(warp_sum_f32(s), rn);
+      s = 0.0f;
 #pragma unroll
-    for (int u = 0; u < NV; ++u) {
-      if (u * 32 + lane >= n4) continue;
+      for (int u = 0; u < NV; ++u) {
+        if (u * 32 + lane >= n4) continue;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        // SquaredDifference.ts: the difference and its square in double, stored as fp32
-        const double d = (double)v[u][k] - (double)mean;
-        acc += (double)__fdiv_rn((float)(d * d), nf);
+        for (int k = 0; k < 4; ++k) {
+          const float d = __fsub_rn(v[u][k], mean);
+          s = __fmaf_rn(d, d, s);
+        }
       }
+      const float var = __fmul_rn(warp_sum_f32(s), rn);
+      rs = __frsqrt_rn(__fadd_rn(var, eps));
+    } else {
+      double acc = 0.0;
+#pragma unroll
+      for (int u = 0; u < NV; ++u) {
+        if (u * 32 + lane >= n4) continue;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc += (double)__fdiv_rn(v[u][k], nf);
+      }
+      mean = (float)warp_sum(acc);
+      acc = 0.0;
+#pragma unroll
+      for (int u = 0; u < NV; ++u) {
+        if (u * 32 + lane >= n4) continue;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // SquaredDifference.ts: the difference and its square in double, stored as fp32
+          const double d = (double)v[u][k] - (double)mean;
+          acc += (double)__fdiv_rn((float)(d * d), nf);
+        }
+      }
+      const float var = (float)warp_sum(acc);
+      rs = (float)(1.0 / sqrt((double)__fadd_rn(var, eps)));
     }
-    const float var = (float)warp_sum(acc);
-    const float rs = (float)(1.0 / sqrt((double)__fadd_rn(var, eps)));
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
       const uint32_t j = u * 32 + lane;
@@ -566,11 +594,18 @@ int tfjs_cuda_layer_norm(tfjs_cuda_ctx* ctx, int32_t x_id, int32_t residual_id, 
                     "layer norm: rows of a multiple of 4 up to 1024 floats, 16-byte aligned");
   cudaSetDevice(ctx->device);
   const unsigned grid = grid_for(rows * 32, kThreads, ctx->sm_count);
+  const bool fast = ctx->math_mode == TFJS_CUDA_MATH_TF32;
 #define LNORM(NV)                                                                          \
-  layer_norm_rows_kernel<NV><<<grid, kThreads, 0, ctx->stream>>>(                          \
-      (const float*)x->ptr, res ? (const float*)res->ptr : nullptr, (const float*)g->ptr,  \
-      (const float*)b->ptr, (float*)y->ptr,                                                \
-      rows, (uint32_t)cols, (float)cols, epsilon)
+  do {                                                                                     \
+    if (fast)                                                                              \
+      layer_norm_rows_kernel<NV, true><<<grid, kThreads, 0, ctx->stream>>>(                \
+          (const float*)x->ptr, res ? (const float*)res->ptr : nullptr, (const float*)g->ptr, \
+          (const float*)b->ptr, (float*)y->ptr, rows, (uint32_t)cols, (float)cols, epsilon); \
+    else                                                                                   \
+      layer_norm_rows_kernel<NV, false><<<grid, kThreads, 0, ctx->stream>>>(               \
+          (const float*)x->ptr, res ? (const float*)res->ptr : nullptr, (const float*)g->ptr, \
+          (const float*)b->ptr, (float*)y->ptr, rows, (uint32_t)cols, (float)cols, epsilon); \
+  } while (0)
   if (cols <= 128) LNORM(1);
   else if (cols <= 256) LNORM(2);
   else if (cols <= 512) LNORM(4);
