@@ -106,7 +106,10 @@ int tfjs_cuda_read_async(tfjs_cuda_ctx* ctx, int32_t id, void* host,
  * the D2H copy behind the kernels already launched and returns a ticket at once;
  * read_wait blocks until that copy has landed (and reports a pending device timeout).
  * The caller keeps `host` (ideally pinned) alive and untouched in between; a ticket is
- * collected exactly once. */
+ * collected exactly once.  The tensor itself may be freed or overwritten as soon as
+ * read_begin returns (stream-ordered).  Downloads of 4 MB and more leave the device through
+ * a staging copy on a stream of their own, so kernels launched after read_begin run while
+ * the bytes travel; tfjs_cuda_sync covers them as well. */
 int tfjs_cuda_read_begin(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes,
                          int32_t* out_ticket);
 int tfjs_cuda_read_wait(tfjs_cuda_ctx* ctx, int32_t ticket);

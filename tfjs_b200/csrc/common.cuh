@@ -64,6 +64,7 @@ struct tfjs_cuda_ctx {
   int sm_count = 148;
   cudaStream_t stream = nullptr;
   cudaStream_t copy_stream = nullptr;       // uploads that overlap compute
+  cudaStream_t read_stream = nullptr;       // large downloads that overlap the next kernels
   std::vector<cudaEvent_t> event_pool;      // recycled upload-completion events
   // Exact-size cache of freed blocks.  A graph model asks for the same sizes every
   // step; handing a freed block straight to the next request of that size keeps the
@@ -102,6 +103,7 @@ struct tfjs_cuda_ctx {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::vector<cudaEvent_t> prof_events;  // numbered events for per-kernel timing
   std::vector<cudaEvent_t> read_events;  // tickets of tfjs_cuda_read_begin (index + 1)
+  std::vector<cudaEvent_t> read_order;   // per ticket: orders the read stream behind the compute stream
   std::vector<int*> read_flags;          // one pinned copy of the device error word per ticket
   std::vector<int> read_free;            // ticket slots free for reuse
   void* l2_scratch = nullptr;

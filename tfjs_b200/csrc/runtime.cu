@@ -5,7 +5,9 @@
 // host-side DataStorage, as in the reference's WASM backend where the C++ side
 // only maps tensor ids to memory (tfjs-backend-wasm/src/cc/backend.cc:124-152).
 //
-// Everything runs on ONE in-order stream: kernels, H2D, D2H and frees.  The
+// Kernels, small transfers and frees run on ONE in-order stream (overlapped uploads and
+// large downloads have a copy stream and a read stream of their own, ordered against it by
+// events).  The
 // graph executor disposes an intermediate as soon as its last consumer has
 // been *enqueued* (tfjs-converter/src/executor/graph_executor.ts:382-409), so
 // frees are stream-ordered (cudaFreeAsync) and a block can be handed to a later
@@ -213,6 +215,7 @@ int tfjs_cuda_create(int device_ordinal, tfjs_cuda_ctx** out_ctx) {
   bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) ==
             cudaSuccess;
   ok = ok && cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithFlags(&ctx->read_stream, cudaStreamNonBlocking) == cudaSuccess;
   ok = ok && cudaDeviceGetDefaultMemPool(&ctx->pool, device_ordinal) ==
                  cudaSuccess;
   if (ok) {
@@ -261,7 +264,12 @@ void tfjs_cuda_destroy(tfjs_cuda_ctx* ctx) {
   for (cudaEvent_t e : ctx->prof_events)
     if (e) cudaEventDestroy(e);
   for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
+  if (ctx->read_stream) {
+    cudaStreamSynchronize(ctx->read_stream);
+    cudaStreamDestroy(ctx->read_stream);
+  }
   for (cudaEvent_t e : ctx->read_events) cudaEventDestroy(e);
+  for (cudaEvent_t e : ctx->read_order) cudaEventDestroy(e);
   for (int* w : ctx->read_flags) cudaFreeHost(w);
   for (ReplayGraph& g : ctx->graphs)
     if (g.exec) {
@@ -506,6 +514,7 @@ int tfjs_cuda_sync(tfjs_cuda_ctx* ctx) {
   int rc = fetch_flag(ctx, ctx->h_flag);
   if (rc) return rc;
   CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  CUDA_TRY(ctx, cudaStreamSynchronize(ctx->read_stream));   // staged downloads (read_begin)
   return report_flag(ctx, ctx->h_flag);
 }
 
@@ -526,12 +535,39 @@ int tfjs_cuda_read_async(tfjs_cuda_ctx* ctx, int32_t id, void* host,
 
 // backend.read(): the D2H copy and an event are queued behind the kernels already on
 // the stream; the host keeps launching and collects the bytes with read_wait.
+// A large download (megabytes: a hundred microseconds and more of PCIe time) does not
+// hold up the kernels launched after it: the tensor is copied to a staging block on the
+// compute stream (device to device: microseconds) and travels to the host on the read
+// stream, so the next step runs meanwhile and the tensor itself - which may be freed, or
+// belong to the arena of a captured step that the next replay overwrites - is not touched
+// after the compute stream has passed this point.
+constexpr uint64_t kStagedReadBytes = 4ull << 20;
+
 int tfjs_cuda_read_begin(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nbytes,
                          int32_t* out_ticket) {
   if (!ctx || !out_ticket) return TFJS_CUDA_INVALID_ARG;
   *out_ticket = 0;
-  int rc = tfjs_cuda_read_async(ctx, id, host, nbytes);
-  if (rc) return rc;
+  void* staged = nullptr;
+  int rc;
+  if (nbytes >= kStagedReadBytes && host != nullptr && !ctx->capturing) {
+    Buffer* b;
+    if ((rc = ctx_get(ctx, id, nbytes, "read", &b))) return rc;
+    cudaSetDevice(ctx->device);
+    if (cudaMallocAsync(&staged, nbytes, ctx->stream) != cudaSuccess) {
+      cudaGetLastError();        // no room for the staging block: the direct copy below
+      staged = nullptr;
+    } else {
+      cudaError_t e = cudaMemcpyAsync(staged, b->ptr, nbytes, cudaMemcpyDeviceToDevice, ctx->stream);
+      if (e != cudaSuccess) {
+        cudaFreeAsync(staged, ctx->stream);
+        return ctx_check(ctx, e, "cudaMemcpyAsync");
+      }
+    }
+  }
+  if (staged == nullptr) {
+    rc = tfjs_cuda_read_async(ctx, id, host, nbytes);
+    if (rc) return rc;
+  }
   int slot;
   if (!ctx->read_free.empty()) {
     slot = ctx->read_free.back();
@@ -546,16 +582,40 @@ int tfjs_cuda_read_begin(tfjs_cuda_ctx* ctx, int32_t id, void* host, uint64_t nb
       cudaFreeHost(word);
       return ctx_check(ctx, e, "cudaEventCreateWithFlags");
     }
+    cudaEvent_t order;
+    e = cudaEventCreateWithFlags(&order, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+      cudaFreeHost(word);
+      cudaEventDestroy(ev);
+      if (staged) cudaFreeAsync(staged, ctx->stream);
+      return ctx_check(ctx, e, "cudaEventCreateWithFlags");
+    }
     ctx->read_events.push_back(ev);
+    ctx->read_order.push_back(order);
     ctx->read_flags.push_back(word);
     slot = (int)ctx->read_events.size() - 1;
   }
   // the device error word travels with every read, as it does with a blocking one, into
   // a pinned word that belongs to this ticket
   rc = fetch_flag(ctx, ctx->read_flags[slot]);
-  if (rc == TFJS_CUDA_OK) rc = ctx_check(ctx, cudaEventRecord(ctx->read_events[slot], ctx->stream),
-                                         "cudaEventRecord");
+  if (rc == TFJS_CUDA_OK && staged != nullptr) {
+    // read stream: behind the staging copy and the flag word, then host copy, release of the
+    // staging block (stream-ordered) and the ticket's event
+    cudaError_t e = cudaEventRecord(ctx->read_order[slot], ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->read_stream, ctx->read_order[slot], 0);
+    if (e == cudaSuccess)
+      e = cudaMemcpyAsync(host, staged, nbytes, cudaMemcpyDeviceToHost, ctx->read_stream);
+    if (e == cudaSuccess) {
+      cudaFreeAsync(staged, ctx->read_stream);
+      staged = nullptr;
+      e = cudaEventRecord(ctx->read_events[slot], ctx->read_stream);
+    }
+    rc = ctx_check(ctx, e, "staged read");
+  } else if (rc == TFJS_CUDA_OK) {
+    rc = ctx_check(ctx, cudaEventRecord(ctx->read_events[slot], ctx->stream), "cudaEventRecord");
+  }
   if (rc) {
+    if (staged) cudaFreeAsync(staged, ctx->stream);
     ctx->read_free.push_back(slot);
     return rc;
   }
