@@ -3,7 +3,7 @@ softmax(q k^T * scale + mask) v for heads of 128 positions x 64 features, stored
 heads merged.
 
 Checked against the CPU oracle's chain of the reference's kernels (BatchMatMul.ts:29-113,
-Multiply.ts, Add.ts, Softmax.ts:50-67, Transpose) within north_star's bound for TF32
+Multiply.ts, Add.ts, Softmax.ts:50-67, Transpose) within the floating-point bound for TF32
 products, 2e-3 * max|ref|, and against the separate launches of this library, from which it
 may differ only by the order of the softmax's fp32 sum."""
 import numpy as np

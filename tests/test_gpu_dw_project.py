@@ -7,7 +7,7 @@ separate kernels (TFJS_CUDA_NO_DW_PROJECT semantics, `fuse_depthwise_project = F
 and through the CPU oracle (FusedDepthwiseConv2D.ts:25-61 then FusedConv2D.ts:26-95, Add,
 Relu6).  Folded and separate must agree bit for bit: the folded kernel performs the same
 fp32 operations per element and rounds the projection's operand to TF32 the way the TMA
-unit does for the separate kernel.  Against the oracle the bound is north_star's
+unit does for the separate kernel.  Against the oracle the bound is the floating-point one,
 2e-3 * max|ref| for TF32 tensor-core inputs.
 """
 import zlib

@@ -4,7 +4,7 @@ backend's pending launches (`PendingMatMul`).
 
 Each member's result must be the one its own launch gives (bit for bit: the same K steps
 in the same order feed the same fp32 accumulators) and agree with the CPU oracle
-(_FusedMatMul.ts:26-62) within north_star's 2e-3 * max|ref| for TF32 inputs.
+(_FusedMatMul.ts:26-62) within the floating-point bound for TF32 inputs, 2e-3 * max|ref|.
 """
 from ctypes import byref, c_int32, c_void_p
 

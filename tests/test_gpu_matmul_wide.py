@@ -1,7 +1,7 @@
 """Products whose 256 x 256 tiles would need between one and one and a half waves of CTA
 pairs run on 256 x 384 tiles instead (`gemm_tf32_pair_kernel<..., BN=384>`: two N = 192
 MMAs per K slice, one accumulator stage).  Results against the CPU oracle
-(_FusedMatMul.ts:26-62) within north_star's 2e-3 * max|ref| for TF32 inputs."""
+(_FusedMatMul.ts:26-62) within the floating-point bound for TF32 inputs, 2e-3 * max|ref|."""
 import numpy as np
 import pytest
 

@@ -4,7 +4,7 @@ as a direct fp32 kernel (`stem_conv3x3s2_kernel`) in the default math mode.
 Against the CPU oracle (FusedConv2D.ts:26-95): the kernel performs the reference's fp32
 multiply-adds in the reference's order (filter row, filter column, input channel; bias and
 activation afterwards), so the bound is that of the last bit of each accumulation, far
-inside north_star's 2e-3 * max|ref| for the TF32 product it replaces."""
+inside the 2e-3 * max|ref| that bounds the TF32 product it replaces."""
 import numpy as np
 import pytest
 
