@@ -232,6 +232,10 @@ DW_CASES = {
     "mbv2_112_c32_s1": lambda: dw_case(0, (2, 112, 112, 32), (3, 3, 32, 1)),
     "mbv2_112_c96_s2": lambda: dw_case(1, (2, 112, 112, 96), (3, 3, 96, 1), strides=2),
     "mbv2_7_c960": lambda: dw_case(2, (4, 7, 7, 960), (3, 3, 960, 1)),
+    # widths that are multiples of 28 take 28-wide tiles with seven outputs per thread
+    "mbv2_56_c144_s1": lambda: dw_case(7, (2, 56, 56, 144), (3, 3, 144, 1)),
+    "w28_c40_h13_valid": lambda: dw_case(8, (3, 15, 30, 40), (3, 3, 40, 1), pad="valid", act="relu"),
+    "w84_c8": lambda: dw_case(9, (1, 20, 84, 8), (3, 3, 8, 1), act="linear", bias=False),
     "chmul2": lambda: dw_case(3, (2, 9, 11, 6), (3, 3, 6, 2), act="relu"),
     "c5_scalar_path": lambda: dw_case(4, (1, 10, 10, 5), (3, 3, 5, 1), pad="valid", act="elu"),
     "dilated": lambda: dw_case(5, (1, 16, 16, 8), (3, 3, 8, 1), dilations=2, act="linear", bias=False),

@@ -252,9 +252,10 @@ void launch_depthwise3x3(tfjs_cuda_ctx* ctx, const float* x, const float* w, con
 // the current one.  A thread owns 4 channels of S adjacent output columns.
 template <int STRIDE, int TW_>
 struct DwTile {
-  static constexpr int TW = TW_;                      // output tile width (16 or 14)
+  static constexpr int TW = TW_;                      // output tile width (16, 14 or 28)
   static constexpr int TH = STRIDE == 1 ? 8 : 4;      // output tile height
-  static constexpr int S = (STRIDE == 1 && TW_ == 16) ? 4 : 2;  // outputs per strip
+  // outputs per strip; 28-wide tiles take 7, so that a tile is exactly 32 strips (one pass)
+  static constexpr int S = TW_ == 28 ? 7 : (STRIDE == 1 && TW_ == 16) ? 4 : 2;
   static constexpr int NSTRIPS = (TW / S) * TH;       // strips per tile, 32 per pass
   static constexpr int IW = (TW - 1) * STRIDE + 3;    // input patch
   static constexpr int IH = (TH - 1) * STRIDE + 3;
@@ -578,13 +579,23 @@ int tfjs_cuda_fused_depthwise_conv2d(tfjs_cuda_ctx* ctx,
   if (no_tma < 0) no_tma = getenv("TFJS_CUDA_NO_DW_TMA") ? 1 : 0;  // debugging knob
   // 16-wide tiles measured faster than 14-wide ones even on 56 / 28 / 14 wide maps;
   // maps narrower than 12 keep the register-strip kernel
-  const int tw = g.out_w >= 12 ? 16 : 0;
+  // Stride-1 maps whose width is a multiple of 28 (56, 28, 84) take 28-wide tiles with seven
+  // outputs per thread: 16-wide tiles leave an eighth of the last tile column empty there and
+  // fetch a wider halo (56 x 56 x 144 at batch 256: 197 -> 148 us, 0.97 of the measured copy
+  // bandwidth; 28 x 28 x 192: 67 -> 51 us).  112-wide maps are 16 x 7 and stay (142 against
+  // 148 us).  TFJS_CUDA_NO_DW_TILE28=1: 16-wide tiles everywhere.
+  static int wide28 = -1;
+  if (wide28 < 0) wide28 = getenv("TFJS_CUDA_NO_DW_TILE28") ? 0 : 1;
+  const int tw = g.out_w >= 12
+                     ? ((wide28 && g.s_h == 1 && g.out_w % 28 == 0 && g.out_w % 112 != 0) ? 28 : 16)
+                     : 0;
   int launched = -1;
   if (fast3x3 && !no_tma && tw) {
     const float* xp = (const float*)x->ptr;
     const float* wp = (const float*)w->ptr;
     float* yp = (float*)y->ptr;
-    if (g.s_h == 1 && tw == 16) launched = launch_depthwise3x3_tma<1, 16>(ctx, xp, wp, bp, bl, ap, yp, g);
+    if (g.s_h == 1 && tw == 28) launched = launch_depthwise3x3_tma<1, 28>(ctx, xp, wp, bp, bl, ap, yp, g);
+    else if (g.s_h == 1 && tw == 16) launched = launch_depthwise3x3_tma<1, 16>(ctx, xp, wp, bp, bl, ap, yp, g);
     else if (g.s_h == 1) launched = launch_depthwise3x3_tma<1, 14>(ctx, xp, wp, bp, bl, ap, yp, g);
     else if (tw == 16) launched = launch_depthwise3x3_tma<2, 16>(ctx, xp, wp, bp, bl, ap, yp, g);
     else launched = launch_depthwise3x3_tma<2, 14>(ctx, xp, wp, bp, bl, ap, yp, g);
