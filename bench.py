@@ -432,13 +432,13 @@ def cpu_baselines(model, unit, headline):
 NCU_TRAFFIC = {
     # "<workload>/<kind>": (profile summary, launches per step, dram bytes per step)
     "mobilenet_v2_1.0_224_b256_graphmodel/FusedConv2D":
-        ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 19, 4607592192),
+        ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 19, 4604911104),
     "mobilenet_v2_1.0_224_b256_graphmodel/FusedDepthwiseConv2D":
-        ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 2, 1787352320),
+        ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 2, 1780078080),
     "mobilenet_v2_1.0_224_b256_graphmodel/FusedDepthwiseConv2D+FusedConv2D":
-        ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 6, 2261365248),
+        ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 6, 2263849472),
     "mobilenet_v2_1.0_224_b256_graphmodel/FusedDepthwiseConv2D+FusedConv2D+Add":
-        ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 9, 1025360896),
+        ("profiles/bench_dram_traffic_mobilenet_v2_b256.md", 9, 1038357760),
     "resnet50_v1.5_224_b128_uint8weights_graphmodel/FusedConv2D":
         ("profiles/bench_dram_traffic_resnet50_b128.md", 37, 6562264832),
     "resnet50_v1.5_224_b128_uint8weights_graphmodel/FusedConv2D+Add+Relu":
