@@ -6,7 +6,7 @@ op front end with CUDA events on the backend's stream.
 cases: mm2a (fused matMul 4096x1024x4096 + bias + relu6), ffn (8192x768x3072), ffng (ffn with
 the erf GELU as epilogue),
 mm_<m>_<k>_<n> (fused matMul + bias), qkv_<m>_<k>_<n> (three of them on one activation: one
-grouped launch), mean_<batch>_<hw>_<c> (global average pooling), attn_<batch>_<heads>[_sep] (one attention layer, heads of 128 x 64: one launch, or
+grouped launch), mean_<batch>_<hw>_<c> (global average pooling), maxpool_<batch>_<hw>_<c> (3x3 stride-2 max pooling), attn_<batch>_<heads>[_sep] (one attention layer, heads of 128 x 64: one launch, or
 the three separate ones),
 pw_<hw>_<cin>_<cout>_<batch> (1x1 conv), c3_<hw>_<cin>_<cout>_<batch>_<stride> (3x3
 conv), stem_<hw>_<k>_<cout>_<batch>_<stride> (3-channel input), dw_<hw>_<c>_<batch>_<stride>
@@ -68,6 +68,10 @@ elif case=='ffng':   # the same product with the erf GELU as its epilogue
     a=ops.tensor(r.standard_normal((8192,768)).astype(np.float32)/32); b=ops.tensor(r.standard_normal((768,3072)).astype(np.float32)/32)
     bias=ops.tensor(r.standard_normal(3072).astype(np.float32))
     f=lambda: ops.fused_mat_mul(a,b,False,False,bias,'gelu_erf',None,0.2,[float(np.float32(1/np.sqrt(2))),0.5,1.0,0.0]); fl=2*8192*3072*768; by=4*(8192*768+768*3072+8192*3072)
+elif case.startswith('maxpool_'):   # maxpool_<batch>_<hw>_<c>: 3x3 stride-2 'same' max pooling
+    _,bt,hw,c=case.split('_'); bt,hw,c=int(bt),int(hw),int(c)
+    x=ops.tensor(r.standard_normal((bt,hw,hw,c)).astype(np.float32))
+    f=lambda: ops.max_pool(x,3,2,'same'); fl=0; by=4*(bt*hw*hw*c+bt*((hw+1)//2)**2*c)
 elif case.startswith('mean_'):   # mean_<batch>_<hw>_<c>: Mean over the two spatial axes of an NHWC map (global pooling)
     _,bt,hw,c=case.split('_'); bt,hw,c=int(bt),int(hw),int(c)
     x=ops.tensor(r.standard_normal((bt,hw,hw,c)).astype(np.float32))

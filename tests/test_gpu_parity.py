@@ -253,7 +253,10 @@ def test_fused_depthwise(cuda_engine, name):
 # ------------------------------------------------------------------- pools --
 @pytest.mark.parametrize("kind", ["max_pool", "avg_pool"])
 @pytest.mark.parametrize("cfg", [((2, 112, 112, 64), 3, 2, "same"), ((1, 9, 9, 5), 2, 1, "valid"),
-                                 ((2, 7, 7, 32), 7, 1, "valid"), ((1, 8, 8, 4), 3, 1, 1)])
+                                 ((2, 7, 7, 32), 7, 1, "valid"), ((1, 8, 8, 4), 3, 1, 1),
+                                 # 3x3 stride 2 with channels % 4 == 0: the four-column max kernel
+                                 ((3, 15, 13, 8), 3, 2, "valid"), ((2, 9, 10, 4), 3, 2, "same"),
+                                 ((1, 12, 21, 12), 3, 2, 1)])
 def test_pool(cuda_engine, kind, cfg):
     shape, fsz, stride, pad = cfg
     x = f32(rng(3).standard_normal(shape))
@@ -266,6 +269,14 @@ def test_maxpool_ignores_nan(cuda_engine):
     x = f32(rng(4).standard_normal((1, 6, 6, 4)))
     x[0, 2, 2, 1] = np.nan
     case = {"op": "max_pool", "inputs": {"x": x}, "attrs": {"filterSize": 2, "strides": 2, "pad": "valid"}}
+    assert np.array_equal(opcases.run_cuda(case), opcases.run_oracle(case), equal_nan=True)
+
+
+def test_maxpool3x3s2_ignores_nan_and_handles_all_nan_windows(cuda_engine):
+    x = f32(rng(5).standard_normal((2, 11, 14, 8)))
+    x[0, 4, 6, 3] = np.nan
+    x[1, 0:3, 0:3, 5] = np.nan          # a whole window: the result stays -inf, as in the reference
+    case = {"op": "max_pool", "inputs": {"x": x}, "attrs": {"filterSize": 3, "strides": 2, "pad": "valid"}}
     assert np.array_equal(opcases.run_cuda(case), opcases.run_oracle(case), equal_nan=True)
 
 
