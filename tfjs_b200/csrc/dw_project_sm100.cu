@@ -209,11 +209,26 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
   } else if (warp == 1) {
     // --------------------------------------------------------- MMA issuer --
+    // One thread, a chain of dependent scalar instructions per K step, and only four short
+    // MMAs (N <= 256) to hide it behind: the loop is kept to the waits, one add per
+    // descriptor, the MMAs and the commits.  The descriptors of all stages and K sub-steps
+    // differ only in the start-address field (16-byte units, bits 0-13) of the low word.
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) |
                              ((uint32_t)(g.n_mma >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint64_t proto = desc_k_major(0);
+      const uint32_t d_hi = (uint32_t)(proto >> 32);
+      const uint32_t a_lo0 = (uint32_t)proto | ((a_base >> 4) & 0x3fffu);
+      const uint32_t b_lo0 = (uint32_t)proto | ((b_base >> 4) & 0x3fffu);
+      const uint32_t a_inc = A_STAGE_BYTES >> 4, b_inc = b_stage_bytes >> 4;
+      const uint32_t kk = (UMMA_K * 4) >> 4;                     // one K sub-step
+      const uint32_t j_inc = ((uint32_t)g.n_mma * 128u) >> 4;    // the second MMA's filter rows
+      const int n_blk = g.n_blk, n_mma = g.n_mma;
+      auto mk = [&](uint32_t lo) { return ((uint64_t)d_hi << 32) | lo; };
       int as = 0, bs = 0;
-      uint32_t aph = 0, bph = 0;
+      uint32_t aph = 0, bph = 0, a_lo = a_lo0, b_lo = b_lo0;
+      uint32_t a_full_bar = a_full(0), a_empty_bar = a_empty(0);
+      uint32_t b_full_bar = b_full(0), b_empty_bar = b_empty(0);
       bool alive = true;
       int it = 0;
       for (int tile = blockIdx.x; alive && tile < g.total_tiles; tile += gridDim.x, ++it) {
@@ -225,27 +240,33 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * g.n_pad);
+#pragma unroll 1
         for (int ks = 0; ks < k_steps; ++ks) {
-          if (!mbar_wait(b_full(bs), bph) || !mbar_wait(a_full(as), aph)) {
+          if (!mbar_wait(b_full_bar, bph) || !mbar_wait(a_full_bar, aph)) {
             atomicExch(g.flag, 3);
             alive = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = a_base + (uint32_t)as * A_STAGE_BYTES;
-          const uint32_t sb = b_base + (uint32_t)bs * b_stage_bytes;
+          if (n_blk == 1) {
+            tc_mma_tf32(d_tmem, mk(a_lo), mk(b_lo), idesc, ks != 0 ? 1u : 0u);
+            tc_mma_tf32(d_tmem, mk(a_lo + kk), mk(b_lo + kk), idesc, 1u);
+            tc_mma_tf32(d_tmem, mk(a_lo + 2 * kk), mk(b_lo + 2 * kk), idesc, 1u);
+            tc_mma_tf32(d_tmem, mk(a_lo + 3 * kk), mk(b_lo + 3 * kk), idesc, 1u);
+          } else {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t ad = desc_k_major(sa + k * UMMA_K * 4);
-            for (int j = 0; j < g.n_blk; ++j)
-              tc_mma_tf32(d_tmem + (uint32_t)(j * g.n_mma), ad,
-                          desc_k_major(sb + (uint32_t)(j * g.n_mma) * 128u + k * UMMA_K * 4), idesc,
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              tc_mma_tf32(d_tmem, mk(a_lo + k * kk), mk(b_lo + k * kk), idesc, (ks | k) != 0 ? 1u : 0u);
+              tc_mma_tf32(d_tmem + (uint32_t)n_mma, mk(a_lo + k * kk), mk(b_lo + j_inc + k * kk), idesc,
                           (ks | k) != 0 ? 1u : 0u);
+            }
           }
-          tc_commit(a_empty(as));
-          tc_commit(b_empty(bs));
-          if (++as == AS) { as = 0; aph ^= 1; }
-          if (++bs == BS) { bs = 0; bph ^= 1; }
+          tc_commit(a_empty_bar);
+          tc_commit(b_empty_bar);
+          a_lo += a_inc; a_full_bar += 8; a_empty_bar += 8;
+          if (++as == AS) { as = 0; aph ^= 1; a_lo = a_lo0; a_full_bar = a_full(0); a_empty_bar = a_empty(0); }
+          b_lo += b_inc; b_full_bar += 8; b_empty_bar += 8;
+          if (++bs == BS) { bs = 0; bph ^= 1; b_lo = b_lo0; b_full_bar = b_full(0); b_empty_bar = b_empty(0); }
         }
         if (alive) tc_commit(tfull_bar(acc));
       }
@@ -601,11 +622,19 @@ int launch_tile(tfjs_cuda_ctx* ctx, const float* x, const float* packed_b, DpArg
   };
   if (need() > kMaxSmemBytes)
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "depthwise + projection: tile does not fit");
+  static int inflight = -1;
+  if (inflight < 0) inflight = getenv("TFJS_CUDA_DP_INFLIGHT") ? atoi(getenv("TFJS_CUDA_DP_INFLIGHT")) : 1;
+  while (g.patch_stages < 8 && g.patch_stages < T::G + inflight &&
+         need() + T::PATCH_BYTES <= kMaxSmemBytes)
+    g.patch_stages++;
   for (int round = 0; round < 2; ++round) {
-    if (g.patch_stages < 8 && need() + T::PATCH_BYTES <= kMaxSmemBytes) g.patch_stages++;
+    if (round && g.patch_stages < 8 && need() + T::PATCH_BYTES <= kMaxSmemBytes) g.patch_stages++;
     if (g.a_stages < 8 && need() + A_STAGE_BYTES <= kMaxSmemBytes) g.a_stages++;
     if (g.b_stages < 4 && need() + b_stage <= kMaxSmemBytes) g.b_stages++;
   }
+  if (getenv("TFJS_CUDA_DP_VERBOSE"))
+    fprintf(stderr, "dw_project tile %dx%dx%d S=%d G=%d: PS=%d AS=%d BS=%d smem=%d\n", T::TW, T::TH,
+            T::TN, T::S, T::G, g.patch_stages, g.a_stages, g.b_stages, need());
   const int smem = need();
   g.acc_stages = 2 * g.n_pad <= 512 ? 2 : 1;
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
@@ -681,7 +710,9 @@ int tfjs_cuda_fused_depthwise_project(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d
   // 112 x 112 maps at stride 1 its per-tile hand-offs cost more than the saved traffic
   // (0.33 against 0.31 ms, 0.39 against 0.26 ms), so those stay two launches.
   // TFJS_CUDA_DW_PROJECT_ALL=1 takes every shape the kernel can run.
-  if (dw->stride_h == 1 && (dw->out_w > 28 || dw->out_h > 28)) {
+  static int maxw = -1;
+  if (maxw < 0) maxw = getenv("TFJS_CUDA_DP_MAXW") ? atoi(getenv("TFJS_CUDA_DP_MAXW")) : 28;
+  if (dw->stride_h == 1 && (dw->out_w > maxw || dw->out_h > maxw)) {
     const char* all = getenv("TFJS_CUDA_DW_PROJECT_ALL");
     if (!all || all[0] == '0')
       return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "%s: large stride-1 maps run as two launches", who);
@@ -727,15 +758,21 @@ int tfjs_cuda_fused_depthwise_project(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d
   g.flag = ctx->d_flag;
   const float* xp = (const float*)x->ptr;
   // spatial tile by the width of the output map
+  static int s1 = -1;
+  if (s1 < 0) s1 = getenv("TFJS_CUDA_DP_S1") ? atoi(getenv("TFJS_CUDA_DP_S1")) : 1;
   if (dw->stride_h == 1) {
     if (g.out_w <= 7 && g.out_h <= 7)
       rc = launch_tile<DpTile<1, 7, 7, 2, 1, 1>>(ctx, xp, packed, g);
     else if (g.out_w % 16 == 0 || g.out_w > 56)
-      rc = launch_tile<DpTile<1, 16, 8, 1, 2, 1>>(ctx, xp, packed, g);
+      rc = s1 == 2 ? launch_tile<DpTile<1, 16, 8, 1, 1, 2>>(ctx, xp, packed, g)
+           : s1 ? launch_tile<DpTile<1, 16, 8, 1, 1, 1>>(ctx, xp, packed, g)
+                : launch_tile<DpTile<1, 16, 8, 1, 2, 1>>(ctx, xp, packed, g);
     else if (g.out_h % 8 == 0 || g.out_h > 28)
-      rc = launch_tile<DpTile<1, 14, 8, 1, 2, 1>>(ctx, xp, packed, g);
+      rc = s1 ? launch_tile<DpTile<1, 14, 8, 1, 1, 1>>(ctx, xp, packed, g)
+              : launch_tile<DpTile<1, 14, 8, 1, 2, 1>>(ctx, xp, packed, g);
     else
-      rc = launch_tile<DpTile<1, 14, 7, 1, 2, 1>>(ctx, xp, packed, g);
+      rc = s1 ? launch_tile<DpTile<1, 14, 7, 1, 1, 1>>(ctx, xp, packed, g)
+              : launch_tile<DpTile<1, 14, 7, 1, 2, 1>>(ctx, xp, packed, g);
   } else {
     if (g.out_w <= 7 && g.out_h <= 7)
       rc = launch_tile<DpTile<2, 7, 7, 2, 1, 1>>(ctx, xp, packed, g);
