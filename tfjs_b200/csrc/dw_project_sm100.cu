@@ -8,9 +8,9 @@
 // patch of the CTA's spatial tile with its halo (out-of-image pixels read as zero, which is
 // what skipping those taps amounts to), eight SIMT warps run the 3x3 taps with the
 // arithmetic of the stand-alone depthwise kernel (fmaf per tap in (row, column) order, fp32
-// bias add, activation) - a thread walks a two-column strip down the tile so that each input
-// row is read from shared memory once, and groups of warps work on different K steps at the
-// same time - round each value to TF32 the way the TMA unit rounds the operand
+// bias add, activation) - a thread walks a strip of one or two columns down the tile so that
+// each input row is read from shared memory once, and groups of warps work on different K
+// steps at the same time - round each value to TF32 the way the TMA unit rounds the operand
 // of the stand-alone projection (nearest even) and store it in the 128-byte-swizzled K-major
 // layout; one elected thread issues tcgen05.mma.kind::tf32 against the projection filter
 // (streamed per K step by TMA) into a TMEM accumulator; four epilogue warps add the bias,
@@ -622,19 +622,13 @@ int launch_tile(tfjs_cuda_ctx* ctx, const float* x, const float* packed_b, DpArg
   };
   if (need() > kMaxSmemBytes)
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "depthwise + projection: tile does not fit");
-  static int inflight = -1;
-  if (inflight < 0) inflight = getenv("TFJS_CUDA_DP_INFLIGHT") ? atoi(getenv("TFJS_CUDA_DP_INFLIGHT")) : 1;
-  while (g.patch_stages < 8 && g.patch_stages < T::G + inflight &&
-         need() + T::PATCH_BYTES <= kMaxSmemBytes)
-    g.patch_stages++;
+  // (more patches in flight change nothing: with up to six beyond the groups' own the
+  // stride-1 layers of MobileNetV2 ran within 1%)
   for (int round = 0; round < 2; ++round) {
-    if (round && g.patch_stages < 8 && need() + T::PATCH_BYTES <= kMaxSmemBytes) g.patch_stages++;
+    if (g.patch_stages < 8 && need() + T::PATCH_BYTES <= kMaxSmemBytes) g.patch_stages++;
     if (g.a_stages < 8 && need() + A_STAGE_BYTES <= kMaxSmemBytes) g.a_stages++;
     if (g.b_stages < 4 && need() + b_stage <= kMaxSmemBytes) g.b_stages++;
   }
-  if (getenv("TFJS_CUDA_DP_VERBOSE"))
-    fprintf(stderr, "dw_project tile %dx%dx%d S=%d G=%d: PS=%d AS=%d BS=%d smem=%d\n", T::TW, T::TH,
-            T::TN, T::S, T::G, g.patch_stages, g.a_stages, g.b_stages, need());
   const int smem = need();
   g.acc_stages = 2 * g.n_pad <= 512 ? 2 : 1;
   const int grid = g.total_tiles < ctx->sm_count ? g.total_tiles : ctx->sm_count;
@@ -706,13 +700,11 @@ int tfjs_cuda_fused_depthwise_project(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d
       post_activation != TFJS_CUDA_ACT_RELU6)
     return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "%s: post activation must be linear, relu or relu6", who);
   // Measured on B200 (MobileNetV2 blocks, batch 256): the fused kernel wins for strided
-  // depthwise convolutions (12-36%) and for maps up to 28 x 28 (up to 27%); on 56 x 56 and
-  // 112 x 112 maps at stride 1 its per-tile hand-offs cost more than the saved traffic
-  // (0.33 against 0.31 ms, 0.39 against 0.26 ms), so those stay two launches.
+  // depthwise convolutions (12-44%) and for maps up to 28 x 28 (27-43%); on 56 x 56 and
+  // 112 x 112 maps at stride 1 a tile has one to five K steps and its epilogue bounds the
+  // kernel (0.27 against 0.25 ms, 0.32 against 0.25 ms), so those stay two launches.
   // TFJS_CUDA_DW_PROJECT_ALL=1 takes every shape the kernel can run.
-  static int maxw = -1;
-  if (maxw < 0) maxw = getenv("TFJS_CUDA_DP_MAXW") ? atoi(getenv("TFJS_CUDA_DP_MAXW")) : 28;
-  if (dw->stride_h == 1 && (dw->out_w > maxw || dw->out_h > maxw)) {
+  if (dw->stride_h == 1 && (dw->out_w > 28 || dw->out_h > 28)) {
     const char* all = getenv("TFJS_CUDA_DW_PROJECT_ALL");
     if (!all || all[0] == '0')
       return ctx_fail(ctx, TFJS_CUDA_UNSUPPORTED, "%s: large stride-1 maps run as two launches", who);
@@ -758,21 +750,26 @@ int tfjs_cuda_fused_depthwise_project(tfjs_cuda_ctx* ctx, const tfjs_cuda_conv2d
   g.flag = ctx->d_flag;
   const float* xp = (const float*)x->ptr;
   // spatial tile by the width of the output map
-  static int s1 = -1;
-  if (s1 < 0) s1 = getenv("TFJS_CUDA_DP_S1") ? atoi(getenv("TFJS_CUDA_DP_S1")) : 1;
+  // Depthwise units at stride 1 are one output column wide (four warps per K step, two K
+  // steps in flight): MobileNetV2 b256 2.709 ms per step against 2.730 with two-column units
+  // (two warps per K step, four in flight), which TFJS_CUDA_DP_TWO_COLUMN_UNITS=1 selects.
+  static int two_col = -1;
+  if (two_col < 0) {
+    const char* e = getenv("TFJS_CUDA_DP_TWO_COLUMN_UNITS");
+    two_col = (e && e[0] != '0') ? 1 : 0;
+  }
   if (dw->stride_h == 1) {
     if (g.out_w <= 7 && g.out_h <= 7)
       rc = launch_tile<DpTile<1, 7, 7, 2, 1, 1>>(ctx, xp, packed, g);
     else if (g.out_w % 16 == 0 || g.out_w > 56)
-      rc = s1 == 2 ? launch_tile<DpTile<1, 16, 8, 1, 1, 2>>(ctx, xp, packed, g)
-           : s1 ? launch_tile<DpTile<1, 16, 8, 1, 1, 1>>(ctx, xp, packed, g)
-                : launch_tile<DpTile<1, 16, 8, 1, 2, 1>>(ctx, xp, packed, g);
+      rc = two_col ? launch_tile<DpTile<1, 16, 8, 1, 2, 1>>(ctx, xp, packed, g)
+                   : launch_tile<DpTile<1, 16, 8, 1, 1, 1>>(ctx, xp, packed, g);
     else if (g.out_h % 8 == 0 || g.out_h > 28)
-      rc = s1 ? launch_tile<DpTile<1, 14, 8, 1, 1, 1>>(ctx, xp, packed, g)
-              : launch_tile<DpTile<1, 14, 8, 1, 2, 1>>(ctx, xp, packed, g);
+      rc = two_col ? launch_tile<DpTile<1, 14, 8, 1, 2, 1>>(ctx, xp, packed, g)
+                   : launch_tile<DpTile<1, 14, 8, 1, 1, 1>>(ctx, xp, packed, g);
     else
-      rc = s1 ? launch_tile<DpTile<1, 14, 7, 1, 1, 1>>(ctx, xp, packed, g)
-              : launch_tile<DpTile<1, 14, 7, 1, 2, 1>>(ctx, xp, packed, g);
+      rc = two_col ? launch_tile<DpTile<1, 14, 7, 1, 2, 1>>(ctx, xp, packed, g)
+                   : launch_tile<DpTile<1, 14, 7, 1, 1, 1>>(ctx, xp, packed, g);
   } else {
     if (g.out_w <= 7 && g.out_h <= 7)
       rc = launch_tile<DpTile<2, 7, 7, 2, 1, 1>>(ctx, xp, packed, g);
