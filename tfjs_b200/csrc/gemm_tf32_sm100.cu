@@ -205,6 +205,17 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           pix_h = (t % g.conv.out_h) * g.conv.s_h - g.conv.pad_t;
           pix_n = t / g.conv.out_h;
         }
+        // im2col walk over (filter row, filter column, channel chunk): divided once per
+        // item, stepped per K step (this thread's instructions are the producer's latency)
+        int cc = 0, fr = 0, fc = 0;
+        if (LOAD == 2) {
+          const int tap = ks0 / g.chunks_per_tap;
+          cc = (ks0 - tap * g.chunks_per_tap) * BK;
+          fr = tap / g.conv.f_w;
+          fc = tap - fr * g.conv.f_w;
+        }
+        const int cc_end = g.chunks_per_tap * BK;
+        const int bz_a = bz % g.batch_a, bz_b = bz % g.batch_b;
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
             atomicExch(g.flag, 1);
@@ -216,40 +227,36 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
           if (SWAP) {
             // weights (all N <= 128 rows, zero-filled beyond) into the 128-row operand
             // slot, 256 pixels into the wide one
-            tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_b, fb, ks * BK, 0, bz % g.batch_b);
+            tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_b, fb, ks * BK, 0, bz_b);
             const uint32_t pdst = b_base + stage * C::B_STAGE_BYTES;
             if (LOAD == 0) {
-              tma_load_3d(pdst, &tm_a, fb, ks * BK, mt * kTileRows, bz % g.batch_a);
+              tma_load_3d(pdst, &tm_a, fb, ks * BK, mt * kTileRows, bz_a);
             } else {
-              const int tap = ks / g.chunks_per_tap;
-              const int cc = (ks - tap * g.chunks_per_tap) * BK;
-              const int fr = tap / g.conv.f_w, fc = tap - fr * g.conv.f_w;
               tma_load_im2col(pdst, &tm_a, fb, cc, pix_w, pix_h, pix_n,
                               (uint16_t)(fc * g.conv.d_w), (uint16_t)(fr * g.conv.d_h));
+              cc += BK;
+              if (cc >= cc_end) { cc = 0; if (++fc == g.conv.f_w) { fc = 0; ++fr; } }
             }
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
             continue;
           }
           if (A_MODE == 0) {
-            tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_a, fb, ks * BK, mt * BM,
-                        bz % g.batch_a);
+            tma_load_3d(a_base + stage * A_STAGE_BYTES, &tm_a, fb, ks * BK, mt * BM, bz_a);
           } else if (A_MODE == 2) {
             // im2col load: 128 consecutive output pixels starting at the tile's
             // first one, 32 channels of filter tap (fr, fc)
-            const int tap = ks / g.chunks_per_tap;
-            const int cc = (ks - tap * g.chunks_per_tap) * BK;
-            const int fr = tap / g.conv.f_w, fc = tap - fr * g.conv.f_w;
             tma_load_im2col(a_base + stage * A_STAGE_BYTES, &tm_a, fb, cc, pix_w, pix_h, pix_n,
                             (uint16_t)(fc * g.conv.d_w), (uint16_t)(fr * g.conv.d_h));
+            cc += BK;
+            if (cc >= cc_end) { cc = 0; if (++fc == g.conv.f_w) { fc = 0; ++fr; } }
           }
           const uint32_t bdst = b_base + stage * C::B_STAGE_BYTES;
           if (!B_MN) {
-            tma_load_3d(bdst, &tm_b, fb, ks * BK, nt * BN, bz % g.batch_b);
+            tma_load_3d(bdst, &tm_b, fb, ks * BK, nt * BN, bz_b);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 32; ++j)
-              tma_load_3d(bdst + j * 4096, &tm_b, fb, nt * BN + j * 32, ks * BK,
-                          bz % g.batch_b);
+              tma_load_3d(bdst + j * 4096, &tm_b, fb, nt * BN + j * 32, ks * BK, bz_b);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -263,6 +270,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) |
                              ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) |
                              ((uint32_t)(BM >> 4) << 24);
+      const uint64_t a_proto = desc_k_major(a_base);
+      const uint64_t b_proto = B_MN ? desc_mn_major(b_base) : desc_k_major(b_base);
+      const uint32_t a_hi = (uint32_t)(a_proto >> 32), a_lo0 = (uint32_t)a_proto;
+      const uint32_t b_hi = (uint32_t)(b_proto >> 32), b_lo0 = (uint32_t)b_proto;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0;
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
@@ -286,17 +298,19 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tm_a,
             break;
           }
           tc_fence_after();
-          const uint32_t sa = a_base + stage * A_STAGE_BYTES;
-          const uint32_t sb = b_base + stage * C::B_STAGE_BYTES;
+          // the descriptors of all stages and K sub-steps differ only in the start-address
+          // field of the low word (16-byte units): one add each
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t ad = desc_k_major(sa + k * UMMA_K * 4);
-            const uint64_t bd = B_MN ? desc_mn_major(sb + k * 1024)
-                                     : desc_k_major(sb + k * UMMA_K * 4);
+            const uint64_t ad = ((uint64_t)a_hi << 32) | (a_lo + (uint32_t)(k * ((UMMA_K * 4) >> 4)));
+            const uint64_t bd = ((uint64_t)b_hi << 32) |
+                                (b_lo + (uint32_t)(k * (B_MN ? (1024 >> 4) : ((UMMA_K * 4) >> 4))));
             tc_mma_tf32(d_tmem, ad, bd, idesc, ((ks - ks0) | k) != 0 ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          a_lo += A_STAGE_BYTES >> 4;
+          b_lo += C::B_STAGE_BYTES >> 4;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
         }
         if (alive) tc_commit(tfull_bar(acc));
       }
