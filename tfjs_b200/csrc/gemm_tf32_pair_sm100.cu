@@ -207,6 +207,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           pix_h = (t % g.conv.out_h) * g.conv.s_h - g.conv.pad_t;
           pix_n = t / g.conv.out_h;
         }
+        // (filter row, filter column, channel chunk) of the im2col walk, stepped per K step
+        int cc = 0, fr = 0, fc = 0;
+        const int cc_end = g.chunks_per_tap * BK;
+        const int bz_a = bz % g.batch_a, bz_b = bz % g.batch_b;
         for (int ks = 0; ks < k_steps; ++ks) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1)) {
             atomicExch(g.flag, 1);
@@ -216,20 +220,17 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
           if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * (uint32_t)kPairStageBytes);
           const uint32_t fb = map_to_rank(full_bar(stage), 0);
           if (A_MODE == 0) {
-            tma_load_3d_pair(a_base + stage * A_STAGE_BYTES, &tm_a, fb, ks * BK, m0,
-                             bz % g.batch_a);
+            tma_load_3d_pair(a_base + stage * A_STAGE_BYTES, &tm_a, fb, ks * BK, m0, bz_a);
           } else {
-            const int tap = ks / g.chunks_per_tap;
-            const int cc = (ks - tap * g.chunks_per_tap) * BK;
-            const int fr = tap / g.conv.f_w, fc = tap - fr * g.conv.f_w;
             tma_load_im2col_pair(a_base + stage * A_STAGE_BYTES, &tm_a, fb, cc, pix_w, pix_h,
                                  pix_n, (uint16_t)(fc * g.conv.d_w), (uint16_t)(fr * g.conv.d_h));
+            cc += BK;
+            if (cc >= cc_end) { cc = 0; if (++fc == g.conv.f_w) { fc = 0; ++fr; } }
           }
-          tma_load_3d_pair(b_base + stage * kPairBStageBytes, map_b, fb, ks * BK, n0,
-                           bz % g.batch_b);
+          tma_load_3d_pair(b_base + stage * kPairBStageBytes, map_b, fb, ks * BK, n0, bz_b);
           if (BN == 384)
             tma_load_3d_pair(b_base + stage * kPairBStageBytes + (MMA_N / 2) * BK * 4, map_b, fb,
-                             ks * BK, n0 + MMA_N, bz % g.batch_b);
+                             ks * BK, n0 + MMA_N, bz_b);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -240,6 +241,14 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
       // instruction descriptor: D = f32, A = B = tf32, both K-major, N = MMA_N, M = 256
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(MMA_N >> 3) << 17) |
                              ((uint32_t)(256 >> 4) << 24);
+      // the descriptors of all stages and K sub-steps differ only in the start-address
+      // field of the low word (16-byte units): running values, one add per MMA
+      const uint64_t a_proto = desc_k_major(a_base), b_proto = desc_k_major(b_base);
+      const uint32_t a_hi = (uint32_t)(a_proto >> 32), a_lo0 = (uint32_t)a_proto;
+      const uint32_t b_hi = (uint32_t)(b_proto >> 32), b_lo0 = (uint32_t)b_proto;
+      auto mk = [](uint32_t hi, uint32_t lo) { return ((uint64_t)hi << 32) | lo; };
+      constexpr uint32_t kk = (UMMA_K * 4) >> 4;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0;
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
@@ -260,19 +269,19 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
             break;
           }
           tc_fence_after();
-          const uint32_t sa = a_base + stage * A_STAGE_BYTES;
-          const uint32_t sb = b_base + stage * kPairBStageBytes;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            tc_mma_tf32_pair(d_tmem, desc_k_major(sa + k * UMMA_K * 4),
-                             desc_k_major(sb + k * UMMA_K * 4), idesc, (ks | k) != 0 ? 1u : 0u);
+            tc_mma_tf32_pair(d_tmem, mk(a_hi, a_lo + k * kk), mk(b_hi, b_lo + k * kk), idesc,
+                             (ks | k) != 0 ? 1u : 0u);
             if (BN == 384)
-              tc_mma_tf32_pair(d_tmem + MMA_N, desc_k_major(sa + k * UMMA_K * 4),
-                               desc_k_major(sb + (MMA_N / 2) * BK * 4 + k * UMMA_K * 4), idesc,
+              tc_mma_tf32_pair(d_tmem + MMA_N, mk(a_hi, a_lo + k * kk),
+                               mk(b_hi, b_lo + (((MMA_N / 2) * BK * 4) >> 4) + k * kk), idesc,
                                (ks | k) != 0 ? 1u : 0u);
           }
           tc_commit_pair(empty_bar(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          a_lo += A_STAGE_BYTES >> 4;
+          b_lo += kPairBStageBytes >> 4;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
         }
         if (alive) tc_commit_pair(tfull_bar(acc));
       }
