@@ -189,6 +189,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                ((uint32_t)(128 >> 4) << 24);
       const uint32_t idesc_o = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) |
                                ((uint32_t)(kD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      // Descriptors per slot, built once: the MMAs of a unit differ from them only in the
+      // start-address field of the low word (16-byte units), so issuing one costs an add.
+      // (This thread's scalar instructions are what separates P_FULL from O_FULL.)
+      static_assert(kSlots == 2, "the low words below are selected by the slot's parity");
+      const uint32_t k_hi = (uint32_t)(desc_k_major(0) >> 32);
+      const uint32_t v_hi = (uint32_t)(desc_mn_major(0) >> 32);
+      const uint32_t q_lo0 = (uint32_t)desc_k_major(qk_base(0));
+      const uint32_t q_lo1 = (uint32_t)desc_k_major(qk_base(1));
+      const uint32_t v_lo0 = (uint32_t)desc_mn_major(v_base(0));
+      const uint32_t v_lo1 = (uint32_t)desc_mn_major(v_base(1));
+      auto mk = [](uint32_t hi, uint32_t lo) { return ((uint64_t)hi << 32) | lo; };
       bool alive = true;
       auto issue_pv = [&](int i) {
         const int s = i & 1;
@@ -199,11 +210,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           return;
         }
         tc_fence_after();
+        const uint32_t v_lo = s ? v_lo1 : v_lo0;
 #pragma unroll
         for (int kk = 0; kk < kS / UMMA_K; ++kk)
           tc_mma_tf32_tmem_a(o_tmem(s), s_tmem(s) + (uint32_t)(kk * UMMA_K),
-                             desc_mn_major(v_base(s) + (uint32_t)(kk >> 2) * (kD / 32) * 4096u +
-                                           (uint32_t)(kk & 3) * 1024u),
+                             mk(v_hi, v_lo + (((uint32_t)(kk >> 2) * (kD / 32) * 4096u +
+                                                  (uint32_t)(kk & 3) * 1024u) >> 4)),
                              idesc_o, kk != 0 ? 1u : 0u);
         tc_commit(bar(V_EMPTY, s));
         tc_commit(bar(O_FULL, s));
@@ -217,11 +229,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           break;
         }
         tc_fence_after();
+        const uint32_t q_lo = s ? q_lo1 : q_lo0;
 #pragma unroll
         for (int kk = 0; kk < kD / UMMA_K; ++kk) {
           const uint32_t off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * (UMMA_K * 4);
-          tc_mma_tf32(s_tmem(s), desc_k_major(qk_base(s) + off),
-                      desc_k_major(qk_base(s) + 32768u + off), idesc_s, kk != 0 ? 1u : 0u);
+          tc_mma_tf32(s_tmem(s), mk(k_hi, q_lo + (off >> 4)),
+                      mk(k_hi, q_lo + ((32768u + off) >> 4)), idesc_s, kk != 0 ? 1u : 0u);
         }
         tc_commit(bar(QK_EMPTY, s));
         tc_commit(bar(S_FULL, s));
