@@ -430,6 +430,16 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         (uint32_t)(((tn * T::IH + th0 * T::STRIDE) * T::IW + cb * T::S * T::STRIDE)) * 128u +
         (uint32_t)c4 * 16u;
     const uint32_t arow0 = (uint32_t)((tn * T::TH + th0) * T::TW + cb * T::S);
+    // where this thread's outputs go inside an A stage (row r = pixel, 16-byte chunk c4
+    // under the 128-byte swizzle): the same for every K step, computed once
+    uint32_t a_off[T::RH][T::S];
+#pragma unroll
+    for (int t = 0; t < T::RH; ++t)
+#pragma unroll
+      for (int s2 = 0; s2 < T::S; ++s2) {
+        const uint32_t r = arow0 + (uint32_t)(t * T::TW + s2);
+        a_off[t][s2] = r * 128u + ((((uint32_t)c4) ^ (r & 7u)) << 4);
+      }
     // the CTA's K steps in issue order, dealt to the groups in turn
     const int my_tiles = g.total_tiles > (int)blockIdx.x
                              ? (g.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x
@@ -444,7 +454,7 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
       // fma.rn.f32x2 (two independent fp32 FMAs per instruction); channels beyond C read
       // zeros here and in the patch, and the projection filter is zero there too
       unsigned long long wv[9][2];
-      float4 bv;
+      ulonglong2 bv;
       {
         // plain loads (not asm) so the compiler may schedule them among the arithmetic
         const uint8_t* wk = smem_raw + (w_base - smem0) + (uint32_t)(ks * 80 + c4) * 16u;
@@ -455,7 +465,7 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
           wv[k][0] = t.x;
           wv[k][1] = t.y;
         }
-        bv = *reinterpret_cast<const float4*>(wk + 9 * 128);
+        bv = *reinterpret_cast<const ulonglong2*>(wk + 9 * 128);
       }
       if (!mbar_wait(patch_full(ps), pphase)) {
         if (lane == 0) atomicExch(g.flag, 7);
@@ -511,15 +521,19 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             // output row t is complete: bias, activation, TF32 rounding, A tile
 #pragma unroll
             for (int s = 0; s < T::S; ++s) {
+              if (g.dw_bias_len) {
+                // fp32 bias add, two channels per instruction (rounded like add.rn.f32)
+                asm("add.rn.f32x2 %0, %0, %1;" : "+l"(a2[a][s][0]) : "l"(bv.x));
+                asm("add.rn.f32x2 %0, %0, %1;" : "+l"(a2[a][s][1]) : "l"(bv.y));
+              }
               float o[4];
               asm("mov.b64 {%0, %1}, %2;" : "=f"(o[0]), "=f"(o[1]) : "l"(a2[a][s][0]));
               asm("mov.b64 {%0, %1}, %2;" : "=f"(o[2]), "=f"(o[3]) : "l"(a2[a][s][1]));
               a2[a][s][0] = a2[a][s][1] = 0ull;
-              const float bb[4] = {bv.x, bv.y, bv.z, bv.w};
               uint32_t t32[4];
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                float v = g.dw_bias_len ? __fadd_rn(o[k], bb[k]) : o[k];
+                float v = o[k];
                 // max.NaN / min.NaN keep a NaN input, as Math.max / Math.min do
                 if (DW_ACT == TFJS_CUDA_ACT_RELU) {
                   asm("max.NaN.f32 %0, %0, 0f00000000;" : "+f"(v));
@@ -531,8 +545,7 @@ dw_project_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 }
                 asm("cvt.rn.tf32.f32 %0, %1;" : "=r"(t32[k]) : "f"(v));
               }
-              const uint32_t r = arow0 + (uint32_t)(t * T::TW + s);
-              *reinterpret_cast<uint4*>(a_tile + r * 128u + ((((uint32_t)c4) ^ (r & 7u)) << 4)) =
+              *reinterpret_cast<uint4*>(a_tile + a_off[t][s]) =
                   make_uint4(t32[0], t32[1], t32[2], t32[3]);
             }
           }
