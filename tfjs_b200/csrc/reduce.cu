@@ -439,44 +439,6 @@ __global__ void reduce_mid_kernel(const float* __restrict__ x,
   }
 }
 
-// The same with four adjacent inner positions per thread (inner a multiple of 4, 16-byte
-// aligned tensors): 16-byte loads, eight of them in flight, every output's accumulation in
-// the order j = 0, 1, ... as above.  A global pooling over a [batch, 7, 7, channels] map has
-// too few outputs to cover the memory latency with 4-byte loads.
-template <int OP>
-__global__ void reduce_mid4_kernel(const float4* __restrict__ x, float4* __restrict__ y,
-                                   uint64_t outer, uint64_t reduce, uint64_t inner4, float nf) {
-  const uint64_t n = outer * inner4;
-  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const uint64_t o = i / inner4, in = i % inner4;
-    const float4* xp = x + o * reduce * inner4 + in;
-    double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
-    float4 mx = __ldg(xp);
-    auto take = [&](const float4 v) {
-      if (OP == 0) {
-        a0 += (double)v.x; a1 += (double)v.y; a2 += (double)v.z; a3 += (double)v.w;
-      } else if (OP == 1) {
-        a0 += (double)__fdiv_rn(v.x, nf); a1 += (double)__fdiv_rn(v.y, nf);
-        a2 += (double)__fdiv_rn(v.z, nf); a3 += (double)__fdiv_rn(v.w, nf);
-      } else {
-        mx.x = nan_max(mx.x, v.x); mx.y = nan_max(mx.y, v.y);
-        mx.z = nan_max(mx.z, v.z); mx.w = nan_max(mx.w, v.w);
-      }
-    };
-    uint64_t j = 0;
-    for (; j + 8 <= reduce; j += 8) {
-      float4 v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldg(xp + (j + u) * inner4);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) take(v[u]);
-    }
-    for (; j < reduce; ++j) take(__ldg(xp + j * inner4));
-    y[i] = OP == 2 ? mx : make_float4((float)a0, (float)a1, (float)a2, (float)a3);
-  }
-}
-
 // ---- argmax: tfjs-backend-cpu/src/kernels/ArgMax.ts:55-66 ---------------------
 // Sequential semantics: max starts at element 0 and moves on `value > max`, so
 // the answer is 0 when element 0 is NaN, else the first index of the largest
@@ -680,14 +642,6 @@ int tfjs_cuda_reduce(tfjs_cuda_ctx* ctx, int32_t op, int32_t x_id,
     if (op == 0) reduce_rows_kernel<0><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, outer, reduce, nf);
     else if (op == 1) reduce_rows_kernel<1><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, outer, reduce, nf);
     else reduce_rows_kernel<2><<<grid, kThreads, 0, ctx->stream>>>(xp, yp, outer, reduce, nf);
-  } else if ((inner & 3) == 0 && (((uintptr_t)xp | (uintptr_t)yp) & 15) == 0) {
-    const uint64_t inner4 = inner / 4;
-    const unsigned grid = grid_for(outer * inner4, 128, ctx->sm_count);
-    const float4* x4 = (const float4*)xp;
-    float4* y4 = (float4*)yp;
-    if (op == 0) reduce_mid4_kernel<0><<<grid, 128, 0, ctx->stream>>>(x4, y4, outer, reduce, inner4, nf);
-    else if (op == 1) reduce_mid4_kernel<1><<<grid, 128, 0, ctx->stream>>>(x4, y4, outer, reduce, inner4, nf);
-    else reduce_mid4_kernel<2><<<grid, 128, 0, ctx->stream>>>(x4, y4, outer, reduce, inner4, nf);
   } else {
     const unsigned grid = grid_for(outer * inner, 128, ctx->sm_count);
     if (op == 0) reduce_mid_kernel<0><<<grid, 128, 0, ctx->stream>>>(xp, yp, outer, reduce, inner, nf);
